@@ -1,0 +1,144 @@
+/*
+ * exodus_b200 -- C ABI of the B200 (sm_100a) neuron kernels.
+ *
+ * libexodus_b200.so replaces the pybind11 module `exodus_cuda` of the
+ * reference (cuda/bindings.cu:362-373).  Every entry point takes raw device
+ * pointers and sizes, launches on the stream it is given, allocates nothing,
+ * keeps no state between calls and returns an int status (0 = EXB_OK).  No
+ * exception crosses this boundary; exb_last_error() gives the text of the
+ * calling thread's most recent failure.
+ *
+ * Tensors.  A problem is N = B*M independent neurons over T time steps, all
+ * float32.  Neuron n = b*M + m.  Two storage layouts of a [N, T] tensor:
+ *
+ *   EXB_LAYOUT_NT   element (n, t) at  n*T + t            (time contiguous; the
+ *                   layout of the reference's kernels and autograd Functions)
+ *   EXB_LAYOUT_BTM  element (b, t, m) at (b*T + t)*M + m  (neurons contiguous,
+ *                   "time-major"; a layer's own (batch, time, ...) tensor, so
+ *                   every time step is one coalesced sweep over neurons)
+ *
+ * Per-neuron parameters (alpha, threshold, ...) are never expanded to N
+ * values by the caller; each comes with a mode:
+ *
+ *   EXB_PARAM_SCALAR   one value                       p[0]
+ *   EXB_PARAM_PER_M    M values shared over the batch  p[m]
+ *   EXB_PARAM_PER_N    N values                        p[b*M + m]
+ *
+ * State vectors (v_init, v_post_last, grad_init, per-instance alpha grads) are
+ * always N values indexed b*M + m, in both layouts.
+ */
+#ifndef EXODUS_B200_H
+#define EXODUS_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { EXB_OK = 0, EXB_ERR_ARG = 1, EXB_ERR_ALIGN = 2, EXB_ERR_LAUNCH = 3, EXB_ERR_UNSUPPORTED = 4,
+       EXB_ERR_DEVICE = 5, EXB_ERR_TIMEOUT = 6 };
+
+enum { EXB_LAYOUT_NT = 0, EXB_LAYOUT_BTM = 1 };
+enum { EXB_PARAM_SCALAR = 0, EXB_PARAM_PER_M = 1, EXB_PARAM_PER_N = 2 };
+
+/* What happens to the membrane after a step that emitted spikes.
+ * SUBTRACT: v <- v - a*c       (the reference's only mode, cuda/lif_kernels.h:63)
+ * TO_VALUE: v <- c where a > 0 (extension: `subtract` then holds the reset value) */
+enum { EXB_RESET_SUBTRACT = 0, EXB_RESET_TO_VALUE = 1 };
+
+/* Surrogate gradient ds/dv evaluated inside the backward kernel from the saved
+ * membrane potential.  p0, p1 are the two float parameters.
+ * GENERIC            : read a caller-computed tensor `surr` (any callable)
+ * SINGLE_EXPONENTIAL : p1/(p0*theta) * exp(-|v-theta| / (p0*theta))     p0=grad_width p1=grad_scale
+ * HEAVISIDE          : [v >= theta - p0] / theta                        p0=window
+ * PERIODIC_EXPONENTIAL: u=v-theta/2; w = v<theta ? u : u-floor(u/theta);
+ *                       p1 * exp(-|w-theta/2| / p0) / theta             p0=grad_width p1=grad_scale */
+enum { EXB_SURR_GENERIC = 0, EXB_SURR_SINGLE_EXPONENTIAL = 1, EXB_SURR_HEAVISIDE = 2,
+       EXB_SURR_PERIODIC_EXPONENTIAL = 3 };
+
+#define EXB_MAX_SPIKES_UNLIMITED 0xFFFFFFFFu
+
+const char *exb_version(void);
+const char *exb_last_error(void);
+const char *exb_status_string(int status);
+
+/* Forward spike scan.  Replaces lifForward (cuda/bindings.cu:14-70, kernel
+ * cuda/lif_kernels.h:40-93).  Per neuron and step:
+ *     v <- (v - a*c)*alpha + in_t ; v <- max(v, theta_low) ; a <- v >= theta ? min(trunc(v/theta), max_spikes) : 0
+ * spikes_t = a, v_mem_t = v (before the reset).  v_init is the state after the
+ * previous reset (NULL = 0).  theta_low NULL = no lower bound.  in_scale
+ * (NULL = 1) multiplies in_t per neuron and fuses the layer's norm_input
+ * factor (layers/lif.py:206-209).
+ * Optional fused outputs (NULL to skip): v_post_last[N] = state after the
+ * reset of the last step; spike_count[1] += total number of spikes (exact
+ * integer; the caller zeroes it). */
+int exb_lif_forward(float *spikes, float *v_mem, const float *input, const float *v_init,
+                    const float *in_scale, int in_scale_mode,
+                    const float *alpha, int alpha_mode,
+                    const float *subtract, int subtract_mode,
+                    const float *theta, int theta_mode,
+                    const float *theta_low, int theta_low_mode,
+                    uint32_t max_spikes, int reset_mode,
+                    float *v_post_last, unsigned long long *spike_count,
+                    int64_t B, int64_t T, int64_t M, int layout,
+                    int device, void *stream);
+
+/* Fused reverse-time EXODUS backward.  Replaces lifBackward + lifBackwardAlpha
+ * (cuda/bindings.cu:72-158, kernels cuda/lif_kernels.h:122-168, 199-246) and
+ * the tensor glue of IntegrateAndFire.backward (sinabs/exodus/spike.py:251-289):
+ * one pass over the saved v_mem computes the surrogate s_t, the clip gate
+ * n_t = [v_t > theta_low], g_t = s_t*grad_spikes_t + grad_v_mem_t and
+ *     R_t = n_t * (g_t + (alpha - alpha*c*s_t) * R_{t+1}),  grad_input_t = R_t.
+ * grad_v_mem may be NULL (no gradient through v_mem).  grad_v_last[N] (may be
+ * NULL) is a gradient w.r.t. v_post_last of the forward call.
+ * grad_init[N] (may be NULL) = alpha * R_0 (spike.py:289).
+ * grad_alpha[N] (may be NULL) = per-instance d/d alpha (needs v_init or NULL=0);
+ * the spike counts are recomputed from v_mem, so `spikes` is not read.
+ * `surr` is read only with EXB_SURR_GENERIC.  With in_scale the kernel writes
+ * grad_input_t = scale*R_t, and grad_scale[N] (may be NULL) = sum_t R_t*in_t,
+ * which needs `input` (the forward's unscaled input). */
+int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, float *grad_scale,
+                     const float *grad_spikes, const float *grad_v_mem, const float *grad_v_last,
+                     const float *v_mem, const float *surr, const float *v_init, const float *input,
+                     const float *in_scale, int in_scale_mode,
+                     const float *alpha, int alpha_mode,
+                     const float *subtract, int subtract_mode,
+                     const float *theta, int theta_mode,
+                     const float *theta_low, int theta_low_mode,
+                     uint32_t max_spikes, int reset_mode,
+                     int surrogate_kind, float surr_p0, float surr_p1,
+                     int64_t B, int64_t T, int64_t M, int layout,
+                     int device, void *stream);
+
+/* Leaky integrator forward, v_t = alpha*v_{t-1} + scale*in_t.  Replaces
+ * leakyForward (cuda/bindings.cu:163-193, kernel cuda/leaky_kernels.h:29-58).
+ * in_scale (NULL = 1) is a per-neuron factor on the input that fuses the
+ * layer's decay_early / norm_input multiplications (layers/lif.py:194-195,
+ * 206-214).  v_last[N] (may be NULL) receives v_{T-1}. */
+int exb_leaky_forward(float *out, const float *input, const float *v_init,
+                      const float *alpha, int alpha_mode,
+                      const float *in_scale, int in_scale_mode,
+                      float *v_last,
+                      int64_t B, int64_t T, int64_t M, int layout,
+                      int device, void *stream);
+
+/* Leaky integrator backward, G_t = alpha*G_{t+1} + grad_out_t, grad_input_t =
+ * scale*G_t.  Replaces leakyBackward + leakyBackwardAlpha (cuda/bindings.cu:195-257,
+ * kernels cuda/leaky_kernels.h:82-110, 133-165).  grad_v_last[N] (may be NULL)
+ * is added to grad_out at t = T-1.  grad_init[N] (may be NULL) = alpha*G_0.
+ * grad_alpha[N] (may be NULL) = sum_t G_t * out_{t-1}, out_{-1} = v_init; it
+ * needs `out` (the forward result).  grad_scale[N] (may be NULL) =
+ * sum_t G_t * in_t needs `input`. */
+int exb_leaky_backward(float *grad_input, float *grad_alpha, float *grad_init, float *grad_scale,
+                       const float *grad_out, const float *grad_v_last,
+                       const float *out, const float *input, const float *v_init,
+                       const float *alpha, int alpha_mode,
+                       const float *in_scale, int in_scale_mode,
+                       int64_t B, int64_t T, int64_t M, int layout,
+                       int device, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EXODUS_B200_H */

@@ -1,0 +1,176 @@
+"""ctypes binding of ``libexodus_b200.so`` (declared in ``include/exodus_b200.h``).
+
+The library is the only compute path.  If it is missing or a call fails, an
+exception is raised; there is no PyTorch or CPU substitute.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional, Tuple
+
+import torch
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, "libexodus_b200.so")
+
+LAYOUT_NT = 0
+LAYOUT_BTM = 1
+PARAM_SCALAR = 0
+PARAM_PER_M = 1
+PARAM_PER_N = 2
+RESET_SUBTRACT = 0
+RESET_TO_VALUE = 1
+SURR_GENERIC = 0
+SURR_SINGLE_EXPONENTIAL = 1
+SURR_HEAVISIDE = 2
+SURR_PERIODIC_EXPONENTIAL = 3
+MAX_SPIKES_UNLIMITED = 0xFFFFFFFF
+
+_vp = ctypes.c_void_p
+_i = ctypes.c_int
+_i64 = ctypes.c_int64
+_u32 = ctypes.c_uint32
+_f = ctypes.c_float
+
+_lib: Optional[ctypes.CDLL] = None
+
+EXPORTS = (
+    "exb_version", "exb_last_error", "exb_status_string",
+    "exb_lif_forward", "exb_lif_backward", "exb_leaky_forward", "exb_leaky_backward",
+)
+
+
+class ExodusLibraryError(RuntimeError):
+    """The CUDA library is missing or one of its entry points reported a failure."""
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ExodusLibraryError(
+            f"{LIB_PATH} not found. Build it with `python -m sinabs_exodus_b200.build` "
+            "(needs nvcc). There is no fallback implementation.")
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.exb_version.restype = ctypes.c_char_p
+    lib.exb_last_error.restype = ctypes.c_char_p
+    lib.exb_status_string.restype = ctypes.c_char_p
+    lib.exb_status_string.argtypes = [_i]
+    geometry = [_i64, _i64, _i64, _i, _i, _vp]
+    lib.exb_lif_forward.restype = _i
+    lib.exb_lif_forward.argtypes = [_vp, _vp, _vp, _vp,
+                                    _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _i,
+                                    _u32, _i, _vp, _vp] + geometry
+    lib.exb_lif_backward.restype = _i
+    lib.exb_lif_backward.argtypes = [_vp, _vp, _vp, _vp,
+                                     _vp, _vp, _vp,
+                                     _vp, _vp, _vp, _vp,
+                                     _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _i,
+                                     _u32, _i, _i, _f, _f] + geometry
+    lib.exb_leaky_forward.restype = _i
+    lib.exb_leaky_forward.argtypes = [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp] + geometry
+    lib.exb_leaky_backward.restype = _i
+    lib.exb_leaky_backward.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                       _vp, _i, _vp, _i] + geometry
+    _lib = lib
+    return lib
+
+
+def version() -> str:
+    return load().exb_version().decode()
+
+
+def _check(status: int, what: str) -> None:
+    if status != 0:
+        lib = load()
+        raise ExodusLibraryError(
+            f"{what} failed: {lib.exb_status_string(status).decode()} -- {lib.exb_last_error().decode()}")
+
+
+def ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _require_cuda(*tensors: Optional[torch.Tensor]) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise ExodusLibraryError(
+                "exodus_b200 kernels only run on CUDA tensors; got a tensor on "
+                f"{t.device}. There is no CPU implementation in this package.")
+        if t.dtype != torch.float32:
+            raise ExodusLibraryError(f"exodus_b200 kernels are float32 only; got {t.dtype}")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ExodusLibraryError(f"tensors on different devices: {dev} and {t.device}")
+    assert dev is not None
+    return dev
+
+
+def _stream(dev: torch.device):
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+class ParamSpec(tuple):
+    """(tensor | None, mode) pair for a per-neuron parameter."""
+
+    def __new__(cls, tensor: Optional[torch.Tensor], mode: int = PARAM_SCALAR):
+        return super().__new__(cls, (tensor, mode))
+
+
+def lif_forward(spikes, v_mem, inp, v_init, in_scale: Tuple, alpha: Tuple, subtract: Tuple, theta: Tuple,
+                theta_low: Tuple, max_spikes: Optional[int], reset_mode: int, v_post_last, spike_count,
+                B: int, T: int, M: int, layout: int) -> None:
+    dev = _require_cuda(spikes, v_mem, inp, v_init, in_scale[0], alpha[0], subtract[0], theta[0], theta_low[0],
+                        v_post_last)
+    ms = MAX_SPIKES_UNLIMITED if max_spikes is None else int(max_spikes)
+    st = load().exb_lif_forward(
+        ptr(spikes), ptr(v_mem), ptr(inp), ptr(v_init),
+        ptr(in_scale[0]), in_scale[1], ptr(alpha[0]), alpha[1], ptr(subtract[0]), subtract[1],
+        ptr(theta[0]), theta[1], ptr(theta_low[0]), theta_low[1],
+        ms, reset_mode, ptr(v_post_last), ptr(spike_count),
+        B, T, M, layout, dev.index, _stream(dev))
+    _check(st, "exb_lif_forward")
+
+
+def lif_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, grad_v_mem, grad_v_last,
+                 v_mem, surr, v_init, inp, in_scale: Tuple, alpha: Tuple, subtract: Tuple, theta: Tuple,
+                 theta_low: Tuple, max_spikes: Optional[int], reset_mode: int,
+                 surr_kind: int, p0: float, p1: float, B: int, T: int, M: int, layout: int) -> None:
+    dev = _require_cuda(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, grad_v_mem, grad_v_last,
+                        v_mem, surr, v_init, inp, in_scale[0], alpha[0], subtract[0], theta[0], theta_low[0])
+    ms = MAX_SPIKES_UNLIMITED if max_spikes is None else int(max_spikes)
+    st = load().exb_lif_backward(
+        ptr(grad_input), ptr(grad_alpha), ptr(grad_init), ptr(grad_scale),
+        ptr(grad_spikes), ptr(grad_v_mem), ptr(grad_v_last),
+        ptr(v_mem), ptr(surr), ptr(v_init), ptr(inp),
+        ptr(in_scale[0]), in_scale[1], ptr(alpha[0]), alpha[1], ptr(subtract[0]), subtract[1],
+        ptr(theta[0]), theta[1], ptr(theta_low[0]), theta_low[1],
+        ms, reset_mode, surr_kind, float(p0), float(p1),
+        B, T, M, layout, dev.index, _stream(dev))
+    _check(st, "exb_lif_backward")
+
+
+def leaky_forward(out, inp, v_init, alpha: Tuple, in_scale: Tuple, v_last, B: int, T: int, M: int,
+                  layout: int) -> None:
+    dev = _require_cuda(out, inp, v_init, alpha[0], in_scale[0], v_last)
+    st = load().exb_leaky_forward(ptr(out), ptr(inp), ptr(v_init), ptr(alpha[0]), alpha[1],
+                                  ptr(in_scale[0]), in_scale[1], ptr(v_last),
+                                  B, T, M, layout, dev.index, _stream(dev))
+    _check(st, "exb_leaky_forward")
+
+
+def leaky_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad_v_last, out, inp, v_init,
+                   alpha: Tuple, in_scale: Tuple, B: int, T: int, M: int, layout: int) -> None:
+    dev = _require_cuda(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad_v_last, out, inp, v_init,
+                        alpha[0], in_scale[0])
+    st = load().exb_leaky_backward(ptr(grad_input), ptr(grad_alpha), ptr(grad_init), ptr(grad_scale),
+                                   ptr(grad_out), ptr(grad_v_last), ptr(out), ptr(inp), ptr(v_init),
+                                   ptr(alpha[0]), alpha[1], ptr(in_scale[0]), in_scale[1],
+                                   B, T, M, layout, dev.index, _stream(dev))
+    _check(st, "exb_leaky_backward")

@@ -1,0 +1,219 @@
+// C-ABI front end: argument validation, device selection, dispatch.
+// Nothing here allocates device memory or keeps state between calls; the only
+// per-thread state is the text of the last error.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "exb_kernels.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+// Makes `device` current for the duration of one entry point and restores the
+// previous device afterwards (the reference calls cudaSetDevice without
+// restoring, cuda/bindings.cu:45).
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int device)
+    {
+        if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+        if (device >= 0 && device != prev && cudaSetDevice(device) != cudaSuccess) ok = false;
+    }
+    ~DeviceGuard()
+    {
+        int cur = -1;
+        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+    }
+};
+
+bool mode_ok(int mode) { return mode == EXB_PARAM_SCALAR || mode == EXB_PARAM_PER_M || mode == EXB_PARAM_PER_N; }
+
+int check_geometry(int64_t B, int64_t T, int64_t M, int layout)
+{
+    if (B < 0 || T < 0 || M < 0) return fail(EXB_ERR_ARG, "negative size (B=%lld T=%lld M=%lld)", (long long)B, (long long)T, (long long)M);
+    if (layout != EXB_LAYOUT_NT && layout != EXB_LAYOUT_BTM) return fail(EXB_ERR_ARG, "unknown layout %d", layout);
+    // Kernel grids are 1-D in units of 128..1024 neurons; keep far away from 2^31 blocks.
+    if (B > 0 && M > 0 && (double)B * (double)M > 1.0e11) return fail(EXB_ERR_ARG, "B*M too large");
+    return EXB_OK;
+}
+
+int launch_status(cudaError_t e, const char *what)
+{
+    if (e == cudaSuccess) return EXB_OK;
+    return fail(EXB_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *exb_version(void) { return "exodus_b200 0.1.0 (sm_100a)"; }
+
+const char *exb_last_error(void) { return g_err; }
+
+const char *exb_status_string(int status)
+{
+    switch (status) {
+    case EXB_OK: return "ok";
+    case EXB_ERR_ARG: return "invalid argument";
+    case EXB_ERR_ALIGN: return "misaligned pointer";
+    case EXB_ERR_LAUNCH: return "kernel launch failed";
+    case EXB_ERR_UNSUPPORTED: return "unsupported configuration";
+    case EXB_ERR_DEVICE: return "cannot select device";
+    case EXB_ERR_TIMEOUT: return "device-side wait ran out";
+    default: return "unknown status";
+    }
+}
+
+int exb_lif_forward(float *spikes, float *v_mem, const float *input, const float *v_init,
+                    const float *in_scale, int in_scale_mode,
+                    const float *alpha, int alpha_mode,
+                    const float *subtract, int subtract_mode,
+                    const float *theta, int theta_mode,
+                    const float *theta_low, int theta_low_mode,
+                    uint32_t max_spikes, int reset_mode,
+                    float *v_post_last, unsigned long long *spike_count,
+                    int64_t B, int64_t T, int64_t M, int layout,
+                    int device, void *stream)
+{
+    if (int st = check_geometry(B, T, M, layout)) return st;
+    if (!spikes || !v_mem || !input) return fail(EXB_ERR_ARG, "exb_lif_forward: spikes, v_mem and input are required");
+    if (!alpha || !theta) return fail(EXB_ERR_ARG, "exb_lif_forward: alpha and theta are required");
+    if (!mode_ok(alpha_mode) || !mode_ok(theta_mode) || (subtract && !mode_ok(subtract_mode)) ||
+        (theta_low && !mode_ok(theta_low_mode)) || (in_scale && !mode_ok(in_scale_mode)))
+        return fail(EXB_ERR_ARG, "exb_lif_forward: bad parameter mode");
+    if (reset_mode != EXB_RESET_SUBTRACT && reset_mode != EXB_RESET_TO_VALUE)
+        return fail(EXB_ERR_ARG, "exb_lif_forward: bad reset mode %d", reset_mode);
+    if (reset_mode == EXB_RESET_TO_VALUE && !subtract)
+        return fail(EXB_ERR_ARG, "exb_lif_forward: reset-to-value needs the value in `subtract`");
+    if (B == 0 || M == 0 || T == 0) return EXB_OK;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_lif_forward: cannot select device %d", device);
+
+    exb::LifFwdArgs a;
+    a.spikes = spikes; a.v_mem = v_mem; a.input = input; a.v_init = v_init;
+    a.np.alpha = exb::make_param(alpha, alpha_mode, M);
+    a.np.c = exb::make_param(subtract, subtract_mode, M);
+    a.np.th = exb::make_param(theta, theta_mode, M);
+    a.np.lo = exb::make_param(theta_low, theta_low_mode, M);
+    a.np.scale = exb::make_param(in_scale, in_scale_mode, M);
+    a.maxs = max_spikes;
+    a.v_post_last = v_post_last; a.spike_count = spike_count;
+    a.B = B; a.T = T; a.M = M;
+    return launch_status(exb::launch_lif_forward(a, layout, reset_mode, (cudaStream_t)stream), "exb_lif_forward");
+}
+
+int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, float *grad_scale,
+                     const float *grad_spikes, const float *grad_v_mem, const float *grad_v_last,
+                     const float *v_mem, const float *surr, const float *v_init, const float *input,
+                     const float *in_scale, int in_scale_mode,
+                     const float *alpha, int alpha_mode,
+                     const float *subtract, int subtract_mode,
+                     const float *theta, int theta_mode,
+                     const float *theta_low, int theta_low_mode,
+                     uint32_t max_spikes, int reset_mode,
+                     int surrogate_kind, float surr_p0, float surr_p1,
+                     int64_t B, int64_t T, int64_t M, int layout,
+                     int device, void *stream)
+{
+    if (int st = check_geometry(B, T, M, layout)) return st;
+    if (!grad_input || !grad_spikes || !v_mem)
+        return fail(EXB_ERR_ARG, "exb_lif_backward: grad_input, grad_spikes and v_mem are required");
+    if (!alpha || !theta) return fail(EXB_ERR_ARG, "exb_lif_backward: alpha and theta are required");
+    if (!mode_ok(alpha_mode) || !mode_ok(theta_mode) || (subtract && !mode_ok(subtract_mode)) ||
+        (theta_low && !mode_ok(theta_low_mode)) || (in_scale && !mode_ok(in_scale_mode)))
+        return fail(EXB_ERR_ARG, "exb_lif_backward: bad parameter mode");
+    if (reset_mode != EXB_RESET_SUBTRACT && reset_mode != EXB_RESET_TO_VALUE)
+        return fail(EXB_ERR_ARG, "exb_lif_backward: bad reset mode %d", reset_mode);
+    if (reset_mode == EXB_RESET_TO_VALUE && !subtract)
+        return fail(EXB_ERR_ARG, "exb_lif_backward: reset-to-value needs the value in `subtract`");
+    if (surrogate_kind < EXB_SURR_GENERIC || surrogate_kind > EXB_SURR_PERIODIC_EXPONENTIAL)
+        return fail(EXB_ERR_ARG, "exb_lif_backward: unknown surrogate kind %d", surrogate_kind);
+    if (surrogate_kind == EXB_SURR_GENERIC && !surr)
+        return fail(EXB_ERR_ARG, "exb_lif_backward: the generic surrogate needs the `surr` tensor");
+    if (grad_scale && !input) return fail(EXB_ERR_ARG, "exb_lif_backward: grad_scale needs `input`");
+    if (B == 0 || M == 0 || T == 0) return EXB_OK;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_lif_backward: cannot select device %d", device);
+
+    exb::LifBwdArgs a;
+    a.grad_input = grad_input; a.grad_alpha = grad_alpha; a.grad_init = grad_init; a.grad_scale = grad_scale;
+    a.go = grad_spikes; a.gv = grad_v_mem; a.g_last = grad_v_last; a.v_mem = v_mem;
+    a.surr = (surrogate_kind == EXB_SURR_GENERIC) ? surr : nullptr;
+    a.v_init = v_init; a.input = input;
+    a.np.alpha = exb::make_param(alpha, alpha_mode, M);
+    a.np.c = exb::make_param(subtract, subtract_mode, M);
+    a.np.th = exb::make_param(theta, theta_mode, M);
+    a.np.lo = exb::make_param(theta_low, theta_low_mode, M);
+    a.np.scale = exb::make_param(in_scale, in_scale_mode, M);
+    a.maxs = max_spikes; a.p0 = surr_p0; a.p1 = surr_p1;
+    a.B = B; a.T = T; a.M = M;
+    return launch_status(exb::launch_lif_backward(a, layout, reset_mode, surrogate_kind, (cudaStream_t)stream),
+                         "exb_lif_backward");
+}
+
+int exb_leaky_forward(float *out, const float *input, const float *v_init,
+                      const float *alpha, int alpha_mode,
+                      const float *in_scale, int in_scale_mode,
+                      float *v_last,
+                      int64_t B, int64_t T, int64_t M, int layout,
+                      int device, void *stream)
+{
+    if (int st = check_geometry(B, T, M, layout)) return st;
+    if (!out || !input || !alpha) return fail(EXB_ERR_ARG, "exb_leaky_forward: out, input and alpha are required");
+    if (!mode_ok(alpha_mode) || (in_scale && !mode_ok(in_scale_mode)))
+        return fail(EXB_ERR_ARG, "exb_leaky_forward: bad parameter mode");
+    if (B == 0 || M == 0 || T == 0) return EXB_OK;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_leaky_forward: cannot select device %d", device);
+
+    exb::LeakyFwdArgs a;
+    a.out = out; a.input = input; a.v_init = v_init;
+    a.alpha = exb::make_param(alpha, alpha_mode, M);
+    a.scale = exb::make_param(in_scale, in_scale_mode, M);
+    a.v_last = v_last;
+    a.B = B; a.T = T; a.M = M;
+    return launch_status(exb::launch_leaky_forward(a, layout, (cudaStream_t)stream), "exb_leaky_forward");
+}
+
+int exb_leaky_backward(float *grad_input, float *grad_alpha, float *grad_init, float *grad_scale,
+                       const float *grad_out, const float *grad_v_last,
+                       const float *out, const float *input, const float *v_init,
+                       const float *alpha, int alpha_mode,
+                       const float *in_scale, int in_scale_mode,
+                       int64_t B, int64_t T, int64_t M, int layout,
+                       int device, void *stream)
+{
+    if (int st = check_geometry(B, T, M, layout)) return st;
+    if (!grad_input || !grad_out || !alpha)
+        return fail(EXB_ERR_ARG, "exb_leaky_backward: grad_input, grad_out and alpha are required");
+    if (!mode_ok(alpha_mode) || (in_scale && !mode_ok(in_scale_mode)))
+        return fail(EXB_ERR_ARG, "exb_leaky_backward: bad parameter mode");
+    if (grad_alpha && !out) return fail(EXB_ERR_ARG, "exb_leaky_backward: grad_alpha needs `out`");
+    if (grad_scale && !input) return fail(EXB_ERR_ARG, "exb_leaky_backward: grad_scale needs `input`");
+    if (B == 0 || M == 0 || T == 0) return EXB_OK;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_leaky_backward: cannot select device %d", device);
+
+    exb::LeakyBwdArgs a;
+    a.grad_input = grad_input; a.grad_alpha = grad_alpha; a.grad_init = grad_init; a.grad_scale = grad_scale;
+    a.go = grad_out; a.g_last = grad_v_last; a.out = out; a.input = input; a.v_init = v_init;
+    a.alpha = exb::make_param(alpha, alpha_mode, M);
+    a.scale = exb::make_param(in_scale, in_scale_mode, M);
+    a.B = B; a.T = T; a.M = M;
+    return launch_status(exb::launch_leaky_backward(a, layout, (cudaStream_t)stream), "exb_leaky_backward");
+}
+
+}  // extern "C"

@@ -1,0 +1,58 @@
+// Argument blocks and launcher prototypes shared between the kernel
+// translation units and the C-ABI front end.
+#pragma once
+
+#include "exb_math.cuh"
+
+namespace exb {
+
+struct LifFwdArgs {
+    float *spikes, *v_mem;
+    const float *input, *v_init;
+    NeuronParams np;
+    unsigned maxs;
+    float *v_post_last;
+    unsigned long long *spike_count;
+    int64_t B, T, M;
+};
+
+struct LifBwdArgs {
+    float *grad_input, *grad_alpha, *grad_init, *grad_scale;
+    const float *go, *gv, *g_last, *v_mem, *surr, *v_init, *input;
+    NeuronParams np;
+    unsigned maxs;
+    float p0, p1;
+    int64_t B, T, M;
+};
+
+struct LeakyFwdArgs {
+    float *out;
+    const float *input, *v_init;
+    Param alpha, scale;
+    float *v_last;
+    int64_t B, T, M;
+};
+
+struct LeakyBwdArgs {
+    float *grad_input, *grad_alpha, *grad_init, *grad_scale;
+    const float *go, *g_last, *out, *input, *v_init;
+    Param alpha, scale;
+    int64_t B, T, M;
+};
+
+// Each launcher returns a cudaError_t from the launch (cudaPeekAtLastError).
+cudaError_t launch_lif_forward(const LifFwdArgs &a, int layout, int reset_mode, cudaStream_t s);
+cudaError_t launch_lif_backward(const LifBwdArgs &a, int layout, int reset_mode, int surr_kind, cudaStream_t s);
+cudaError_t launch_leaky_forward(const LeakyFwdArgs &a, int layout, cudaStream_t s);
+cudaError_t launch_leaky_backward(const LeakyBwdArgs &a, int layout, cudaStream_t s);
+
+__device__ __forceinline__ unsigned long long warp_sum_u64(unsigned long long x)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    return x;
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace exb

@@ -1,0 +1,387 @@
+// Leaky-integrator kernels (ExpLeak layer and the synaptic stage of LIF):
+//     forward   v_t = alpha*v_{t-1} + scale*in_t
+//     backward  G_t = alpha*G_{t+1} + grad_out_t,  grad_in_t = scale*G_t
+//               d/d alpha = sum_t G_t*v_{t-1},     d/d scale = sum_t G_t*in_t
+//
+// Time-major (B,T,M): one thread owns V adjacent neurons and walks through
+// time with the state in registers.
+//
+// [N,T]: the recurrence is linear, so one warp owns one neuron row and scans
+// it 32*E time steps at a time: every lane integrates E consecutive steps,
+// a warp-shuffle scan combines the 32 lane aggregates (multipliers
+// alpha^(E*2^d)), and the carry of the segment moves on in a register.  Loads
+// and stores are contiguous along time, no transposition is needed.
+#include "exb_kernels.cuh"
+
+namespace exb {
+
+// ===========================================================================
+// time-major
+// ===========================================================================
+template <int V, int U>
+__global__ void __launch_bounds__(256) leaky_fwd_btm_kernel(const LeakyFwdArgs A)
+{
+    const int64_t MV = A.M / V;
+    const int64_t gid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (gid >= A.B * MV) return;
+    const int64_t b = gid / MV;
+    const int64_t m = (gid - b * MV) * V;
+    const int64_t n = b * A.M + m;
+    const int64_t T = A.T, M = A.M;
+    float al[V], sc[V], v[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        al[j] = A.alpha.get(b, m + j, 1.0f);
+        sc[j] = A.scale.get(b, m + j, 1.0f);
+        v[j] = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
+    }
+    const int64_t base = (b * T) * M + m;
+    const float *in = A.input + base;
+    float *out = A.out + base;
+
+    float xc[U][V], xn[U][V];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) { xc[u][j] = 0.0f; xn[u][j] = 0.0f; }
+        if (u < T) ldv<V>(xc[u], in + u * M);
+    }
+    for (int64_t t = 0; t < T; t += U) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t tt = t + U + u;
+            if (tt < T) ldv<V>(xn[u], in + tt * M);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t tt = t + u;
+            if (tt < T) {
+#pragma unroll
+                for (int j = 0; j < V; ++j) v[j] = __fmaf_rn(v[j], al[j], __fmul_rn(sc[j], xc[u][j]));
+                stv<V>(out + tt * M, v);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int j = 0; j < V; ++j) xc[u][j] = xn[u][j];
+    }
+    if (A.v_last) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) A.v_last[n + j] = v[j];
+    }
+}
+
+template <int V, bool WA, bool WS, int U>
+__global__ void __launch_bounds__(256) leaky_bwd_btm_kernel(const LeakyBwdArgs A)
+{
+    const int64_t MV = A.M / V;
+    const int64_t gid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (gid >= A.B * MV) return;
+    const int64_t b = gid / MV;
+    const int64_t m = (gid - b * MV) * V;
+    const int64_t n = b * A.M + m;
+    const int64_t T = A.T, M = A.M;
+    float al[V], sc[V], G[V], ag[V], sg[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        al[j] = A.alpha.get(b, m + j, 1.0f);
+        sc[j] = A.scale.get(b, m + j, 1.0f);
+        G[j] = 0.0f; ag[j] = 0.0f; sg[j] = 0.0f;
+    }
+    const int64_t base = (b * T) * M + m;
+    const float *go = A.go + base;
+    const float *vo = WA ? A.out + base : nullptr;
+    const float *xin = WS ? A.input + base : nullptr;
+    float *gi = A.grad_input + base;
+
+    for (int64_t t = T - 1; t >= 0; t -= U) {
+        float rgo[U][V], ro[U][V], rx[U][V];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t tt = t - u;
+#pragma unroll
+            for (int j = 0; j < V; ++j) { rgo[u][j] = 0.0f; ro[u][j] = 0.0f; rx[u][j] = 0.0f; }
+            if (tt >= 0) {
+                ldv<V>(rgo[u], go + tt * M);
+                if (WA) ldv<V>(ro[u], vo + tt * M);
+                if (WS) ldv<V>(rx[u], xin + tt * M);
+            }
+        }
+        if (t == T - 1 && A.g_last) {
+#pragma unroll
+            for (int j = 0; j < V; ++j) rgo[0][j] = __fadd_rn(rgo[0][j], __ldg(A.g_last + n + j));
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t tt = t - u;
+            if (tt >= 0) {
+                float r[V];
+#pragma unroll
+                for (int j = 0; j < V; ++j) {
+                    if (WA) ag[j] = __fmaf_rn(G[j], ro[u][j], ag[j]);      // G_{t+1} * v_t
+                    G[j] = __fmaf_rn(G[j], al[j], rgo[u][j]);
+                    if (WS) sg[j] = __fmaf_rn(G[j], rx[u][j], sg[j]);
+                    r[j] = __fmul_rn(sc[j], G[j]);
+                }
+                stv<V>(gi + tt * M, r);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        if (A.grad_init) A.grad_init[n + j] = __fmul_rn(al[j], G[j]);
+        if (WA) A.grad_alpha[n + j] = __fmaf_rn(G[j], A.v_init ? __ldg(A.v_init + n + j) : 0.0f, ag[j]);
+        if (WS) A.grad_scale[n + j] = sg[j];
+    }
+}
+
+// ===========================================================================
+// [N,T]: warp-shuffle scan over time
+// ===========================================================================
+constexpr int SCAN_WARPS = 8;
+
+struct ScanPowers {
+    float a;        // alpha
+    float pw[5];    // alpha^(E*2^d)
+    float fwd;      // alpha^(E*lane)
+    float bwd;      // alpha^(E*(31-lane))
+};
+
+template <int E>
+__device__ __forceinline__ ScanPowers scan_powers(float alpha, int lane)
+{
+    ScanPowers p;
+    p.a = alpha;
+    float aE = alpha;
+#pragma unroll
+    for (int e = 1; e < E; ++e) aE = __fmul_rn(aE, alpha);
+    p.pw[0] = aE;
+#pragma unroll
+    for (int d = 1; d < 5; ++d) p.pw[d] = __fmul_rn(p.pw[d - 1], p.pw[d - 1]);
+    p.fwd = 1.0f;
+    p.bwd = 1.0f;
+#pragma unroll
+    for (int d = 0; d < 5; ++d) {
+        if (lane & (1 << d)) p.fwd = __fmul_rn(p.fwd, p.pw[d]);
+        if ((31 - lane) & (1 << d)) p.bwd = __fmul_rn(p.bwd, p.pw[d]);
+    }
+    return p;
+}
+
+template <int E>
+__device__ __forceinline__ void load_seg(float (&x)[E], const float *row, int64_t t, int64_t T)
+{
+    if (E == 4) {
+        if (t + 4 <= T) {
+            ldv<4>(reinterpret_cast<float(&)[4]>(x), row + t);
+        } else {
+#pragma unroll
+            for (int e = 0; e < E; ++e) x[e] = (t + e < T) ? __ldcs(row + t + e) : 0.0f;
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < E; ++e) x[e] = (t + e < T) ? __ldcs(row + t + e) : 0.0f;
+    }
+}
+
+template <int E>
+__device__ __forceinline__ void store_seg(float *row, const float (&x)[E], int64_t t, int64_t T)
+{
+    if (E == 4 && t + 4 <= T) {
+        stv<4>(row + t, reinterpret_cast<const float(&)[4]>(x));
+    } else {
+#pragma unroll
+        for (int e = 0; e < E; ++e)
+            if (t + e < T) __stcs(row + t + e, x[e]);
+    }
+}
+
+template <int E>
+__global__ void __launch_bounds__(SCAN_WARPS * 32) leaky_fwd_nt_kernel(const LeakyFwdArgs A)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t n = blockIdx.x * (int64_t)SCAN_WARPS + (threadIdx.x >> 5);
+    const int64_t N = A.B * A.M, T = A.T;
+    if (n >= N) return;
+    const int64_t b = n / A.M, m = n - b * A.M;
+    const ScanPowers p = scan_powers<E>(A.alpha.get(b, m, 1.0f), lane);
+    const float sc = A.scale.get(b, m, 1.0f);
+    float carry = A.v_init ? __ldg(A.v_init + n) : 0.0f;
+    const float *rin = A.input + n * T;
+    float *rout = A.out + n * T;
+
+    float x[E], xnext[E];
+    load_seg<E>(x, rin, (int64_t)lane * E, T);
+    for (int64_t t0 = 0; t0 < T; t0 += 32 * E) {
+        const int64_t t = t0 + (int64_t)lane * E;
+        load_seg<E>(xnext, rin, t + 32 * E, T);
+        float y = 0.0f;
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            x[e] = __fmul_rn(sc, x[e]);
+            y = __fmaf_rn(y, p.a, x[e]);
+        }
+#pragma unroll
+        for (int d = 0; d < 5; ++d) {
+            const float up = __shfl_up_sync(0xffffffffu, y, 1 << d);
+            if (lane >= (1 << d)) y = __fmaf_rn(p.pw[d], up, y);
+        }
+        float ex = __shfl_up_sync(0xffffffffu, y, 1);
+        if (lane == 0) ex = 0.0f;
+        float o = __fmaf_rn(p.fwd, carry, ex);
+        float res[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            o = __fmaf_rn(o, p.a, x[e]);
+            res[e] = o;
+        }
+        store_seg<E>(rout, res, t, T);
+        if (A.v_last) {
+#pragma unroll
+            for (int e = 0; e < E; ++e)
+                if (t + e == T - 1) A.v_last[n] = res[e];
+        }
+        carry = __shfl_sync(0xffffffffu, o, 31);
+#pragma unroll
+        for (int e = 0; e < E; ++e) x[e] = xnext[e];
+    }
+}
+
+template <int E, bool WA, bool WS>
+__global__ void __launch_bounds__(SCAN_WARPS * 32) leaky_bwd_nt_kernel(const LeakyBwdArgs A)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t n = blockIdx.x * (int64_t)SCAN_WARPS + (threadIdx.x >> 5);
+    const int64_t N = A.B * A.M, T = A.T;
+    if (n >= N) return;
+    const int64_t b = n / A.M, m = n - b * A.M;
+    const ScanPowers p = scan_powers<E>(A.alpha.get(b, m, 1.0f), lane);
+    const float sc = A.scale.get(b, m, 1.0f);
+    const float vinit = A.v_init ? __ldg(A.v_init + n) : 0.0f;
+    const float glast = A.g_last ? __ldg(A.g_last + n) : 0.0f;
+    const float *rgo = A.go + n * T;
+    const float *rout = WA ? A.out + n * T : nullptr;
+    const float *rin = WS ? A.input + n * T : nullptr;
+    float *rgi = A.grad_input + n * T;
+    float carry = 0.0f, ag = 0.0f, sg = 0.0f;
+    constexpr int SEG = 32 * E;
+
+    for (int64_t t0 = ((T - 1) / SEG) * SEG; t0 >= 0; t0 -= SEG) {
+        const int64_t t = t0 + (int64_t)lane * E;
+        float g[E], o[E], x[E];
+        load_seg<E>(g, rgo, t, T);
+        if (WA) load_seg<E>(o, rout, t, T);
+        if (WS) load_seg<E>(x, rin, t, T);
+#pragma unroll
+        for (int e = 0; e < E; ++e)
+            if (t + e == T - 1) g[e] = __fadd_rn(g[e], glast);
+        float y = 0.0f;
+#pragma unroll
+        for (int e = E - 1; e >= 0; --e) y = __fmaf_rn(y, p.a, g[e]);
+#pragma unroll
+        for (int d = 0; d < 5; ++d) {
+            const float dn = __shfl_down_sync(0xffffffffu, y, 1 << d);
+            if (lane + (1 << d) < 32) y = __fmaf_rn(p.pw[d], dn, y);
+        }
+        float ex = __shfl_down_sync(0xffffffffu, y, 1);
+        if (lane == 31) ex = 0.0f;
+        float G = __fmaf_rn(p.bwd, carry, ex);
+        float res[E], Gs[E];
+#pragma unroll
+        for (int e = E - 1; e >= 0; --e) {
+            G = __fmaf_rn(G, p.a, g[e]);
+            Gs[e] = G;
+            res[e] = __fmul_rn(sc, G);
+            if (WS) sg = __fmaf_rn(G, x[e], sg);
+        }
+        store_seg<E>(rgi, res, t, T);
+        if (WA) {
+            // v_{t-1} for the lane's first step comes from the lane to the left;
+            // lane 0 fetches it from memory (or takes v_init at t = 0).
+            float prev = __shfl_up_sync(0xffffffffu, o[E - 1], 1);
+            if (lane == 0) prev = (t0 > 0) ? __ldg(rout + t0 - 1) : vinit;
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                if (t + e < T) ag = __fmaf_rn(Gs[e], prev, ag);
+                prev = o[e];
+            }
+        }
+        carry = __shfl_sync(0xffffffffu, G, 0);
+    }
+    if (A.grad_init && lane == 0) A.grad_init[n] = __fmul_rn(p.a, carry);
+    if (WA) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ag += __shfl_xor_sync(0xffffffffu, ag, off);
+        if (lane == 0) A.grad_alpha[n] = ag;
+    }
+    if (WS) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sg += __shfl_xor_sync(0xffffffffu, sg, off);
+        if (lane == 0) A.grad_scale[n] = sg;
+    }
+}
+
+// ===========================================================================
+// launchers
+// ===========================================================================
+static inline bool all_aligned16(std::initializer_list<const void *> ptrs)
+{
+    for (const void *p : ptrs)
+        if (p && !aligned16(p)) return false;
+    return true;
+}
+
+cudaError_t launch_leaky_forward(const LeakyFwdArgs &a, int layout, cudaStream_t s)
+{
+    if (layout == EXB_LAYOUT_BTM) {
+        if (a.M % 4 == 0 && all_aligned16({a.out, a.input})) {
+            const int64_t total = a.B * (a.M / 4);
+            leaky_fwd_btm_kernel<4, 4><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+        } else {
+            const int64_t total = a.B * a.M;
+            leaky_fwd_btm_kernel<1, 8><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+        }
+    } else {
+        const int64_t N = a.B * a.M;
+        const unsigned grid = (unsigned)((N + SCAN_WARPS - 1) / SCAN_WARPS);
+        if (a.T % 4 == 0 && all_aligned16({a.out, a.input}))
+            leaky_fwd_nt_kernel<4><<<grid, SCAN_WARPS * 32, 0, s>>>(a);
+        else
+            leaky_fwd_nt_kernel<1><<<grid, SCAN_WARPS * 32, 0, s>>>(a);
+    }
+    return cudaPeekAtLastError();
+}
+
+template <bool WA, bool WS>
+static cudaError_t launch_leaky_bwd_t(const LeakyBwdArgs &a, int layout, cudaStream_t s)
+{
+    if (layout == EXB_LAYOUT_BTM) {
+        if (a.M % 4 == 0 && all_aligned16({a.grad_input, a.go, a.out, a.input})) {
+            const int64_t total = a.B * (a.M / 4);
+            leaky_bwd_btm_kernel<4, WA, WS, 4><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+        } else {
+            const int64_t total = a.B * a.M;
+            leaky_bwd_btm_kernel<1, WA, WS, 8><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+        }
+    } else {
+        const int64_t N = a.B * a.M;
+        const unsigned grid = (unsigned)((N + SCAN_WARPS - 1) / SCAN_WARPS);
+        if (a.T % 4 == 0 && all_aligned16({a.grad_input, a.go, a.out, a.input}))
+            leaky_bwd_nt_kernel<4, WA, WS><<<grid, SCAN_WARPS * 32, 0, s>>>(a);
+        else
+            leaky_bwd_nt_kernel<1, WA, WS><<<grid, SCAN_WARPS * 32, 0, s>>>(a);
+    }
+    return cudaPeekAtLastError();
+}
+
+cudaError_t launch_leaky_backward(const LeakyBwdArgs &a, int layout, cudaStream_t s)
+{
+    const bool wa = a.grad_alpha != nullptr, ws = a.grad_scale != nullptr;
+    if (wa && ws) return launch_leaky_bwd_t<true, true>(a, layout, s);
+    if (wa) return launch_leaky_bwd_t<true, false>(a, layout, s);
+    if (ws) return launch_leaky_bwd_t<false, true>(a, layout, s);
+    return launch_leaky_bwd_t<false, false>(a, layout, s);
+}
+
+}  // namespace exb

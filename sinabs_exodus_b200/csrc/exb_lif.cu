@@ -1,0 +1,394 @@
+// Spiking-neuron kernels: forward spike scan and fused reverse-time EXODUS
+// backward, for the time-major (B,T,M) layout and for the [N,T] layout.
+//
+// Time-major kernels: one thread owns V (4 or 1) adjacent neurons of one batch
+// item and walks through time; at every step a warp touches one contiguous
+// 128*V-byte span per tensor.  The membrane state, spike count and all
+// gradients accumulators live in registers for the whole sweep.
+//
+// [N,T] kernels: one warp owns 32 neurons; 32x32 tiles are moved between
+// global memory (coalesced along time) and shared memory (padded, read along
+// neurons), so the same per-thread sweep runs on a transposed tile.
+#include "exb_kernels.cuh"
+
+namespace exb {
+
+// ===========================================================================
+// time-major forward
+// ===========================================================================
+template <int V, int RESET, int U>
+__global__ void __launch_bounds__(256) lif_fwd_btm_kernel(const LifFwdArgs A)
+{
+    const int64_t MV = A.M / V;
+    const int64_t total = A.B * MV;
+    int64_t gid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    const bool valid = gid < total;
+    if (!valid) gid = total - 1;   // keeps the warp whole for the final reduction; stores are skipped
+    const int64_t b = gid / MV;
+    const int64_t m = (gid - b * MV) * V;
+    const int64_t n = b * A.M + m;
+
+    Neuron q[V];
+    float v[V];
+    unsigned a[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        q[j] = A.np.load(b, m + j);
+        v[j] = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
+        a[j] = 0u;
+    }
+    const int64_t base = (b * A.T) * A.M + m;
+    const float *in = A.input + base;
+    float *sp = A.spikes + base;
+    float *vm = A.v_mem + base;
+    const int64_t T = A.T, M = A.M;
+    unsigned long long cnt = 0ull;
+
+    float xc[U][V], xn[U][V];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) { xc[u][j] = 0.0f; xn[u][j] = 0.0f; }
+        if (u < T) ldv<V>(xc[u], in + u * M);
+    }
+    for (int64_t t = 0; t < T; t += U) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t tt = t + U + u;
+            if (tt < T) ldv<V>(xn[u], in + tt * M);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t tt = t + u;
+            if (tt < T) {
+                float s[V];
+#pragma unroll
+                for (int j = 0; j < V; ++j) {
+                    lif_step<RESET>(v[j], a[j], xc[u][j], q[j], A.maxs);
+                    s[j] = __uint2float_rn(a[j]);
+                    cnt += a[j];
+                }
+                if (valid) {
+                    stv<V>(sp + tt * M, s);
+                    stv<V>(vm + tt * M, v);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int j = 0; j < V; ++j) xc[u][j] = xn[u][j];
+    }
+    if (A.v_post_last && valid) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) A.v_post_last[n + j] = post_reset<RESET>(v[j], a[j], q[j]);
+    }
+    if (A.spike_count) {
+        cnt = warp_sum_u64(valid ? cnt : 0ull);
+        if ((threadIdx.x & 31) == 0 && cnt) atomicAdd(A.spike_count, cnt);
+    }
+}
+
+// ===========================================================================
+// time-major backward
+// ===========================================================================
+template <int V, int SURR, int RESET, bool WA, bool WS, int U>
+__global__ void __launch_bounds__(256) lif_bwd_btm_kernel(const LifBwdArgs A)
+{
+    const int64_t MV = A.M / V;
+    const int64_t total = A.B * MV;
+    const int64_t gid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (gid >= total) return;
+    const int64_t b = gid / MV;
+    const int64_t m = (gid - b * MV) * V;
+    const int64_t n = b * A.M + m;
+    const int64_t T = A.T, M = A.M;
+
+    Neuron q[V];
+    SurrConst sc[V];
+    float cp[V];
+    BwdState st[V];
+    float Rprev[V], f0[V];
+    bool n0[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        q[j] = A.np.load(b, m + j);
+        sc[j] = surr_prepare<SURR>(q[j], A.p0, A.p1);
+        cp[j] = __fmul_rn(q[j].alpha, q[j].c);
+        st[j].R = 0.0f; st[j].ag = 0.0f; st[j].sg = 0.0f;
+        Rprev[j] = 0.0f; f0[j] = 0.0f; n0[j] = true;
+    }
+    const int64_t base = (b * T) * M + m;
+    const float *go = A.go + base;
+    const float *vm = A.v_mem + base;
+    const float *gv = A.gv ? A.gv + base : nullptr;
+    const float *sl = (SURR == EXB_SURR_GENERIC) ? A.surr + base : nullptr;
+    const float *xin = WS ? A.input + base : nullptr;
+    float *gi = A.grad_input + base;
+
+    for (int64_t t = T - 1; t >= 0; t -= U) {
+        float rgo[U][V], rv[U][V], rgv[U][V], rsl[U][V], rx[U][V];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t tt = t - u;
+#pragma unroll
+            for (int j = 0; j < V; ++j) { rgv[u][j] = 0.0f; rsl[u][j] = 0.0f; rx[u][j] = 0.0f; rgo[u][j] = 0.0f; rv[u][j] = 0.0f; }
+            if (tt >= 0) {
+                ldv<V>(rgo[u], go + tt * M);
+                ldv<V>(rv[u], vm + tt * M);
+                if (gv) ldv<V>(rgv[u], gv + tt * M);
+                if (SURR == EXB_SURR_GENERIC) ldv<V>(rsl[u], sl + tt * M);
+                if (WS) ldv<V>(rx[u], xin + tt * M);
+            }
+        }
+        if (t == T - 1 && A.g_last) {
+#pragma unroll
+            for (int j = 0; j < V; ++j)
+                fold_last_state_grad<RESET>(rgo[0][j], rgv[0][j], __ldg(A.g_last + n + j), rv[0][j], q[j], A.maxs);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t tt = t - u;
+            if (tt >= 0) {
+                float r[V];
+#pragma unroll
+                for (int j = 0; j < V; ++j) {
+                    Rprev[j] = st[j].R;
+                    const float Rt = lif_bwd_step<SURR, RESET, WA, WS>(st[j], rv[u][j], rgo[u][j], rgv[u][j], rsl[u][j],
+                                                                      rx[u][j], q[j], sc[j], cp[j], A.maxs, f0[j], n0[j]);
+                    r[j] = __fmul_rn(q[j].scale, Rt);
+                }
+                stv<V>(gi + tt * M, r);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        if (A.grad_init) A.grad_init[n + j] = __fmul_rn(q[j].alpha, st[j].R);
+        if (WA) {
+            const float vi = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
+            A.grad_alpha[n + j] = alpha_grad_finish<RESET>(st[j], vi, Rprev[j], f0[j], n0[j]);
+        }
+        if (WS) A.grad_scale[n + j] = st[j].sg;
+    }
+}
+
+// ===========================================================================
+// [N,T] layout: warp-private 32x32 tiles, padded to 33 columns
+// ===========================================================================
+constexpr int TILE = 32;
+constexpr int TSTR = 33;
+constexpr int TILE_FLOATS = TILE * TSTR;
+constexpr int NT_WARPS = 4;
+
+__device__ __forceinline__ void tile_load(float *tile, const float *src, int64_t T, int rows, int tc, int lane)
+{
+    if (lane < tc) {
+#pragma unroll 8
+        for (int r = 0; r < rows; ++r) tile[r * TSTR + lane] = __ldcs(src + r * T + lane);
+    }
+}
+
+__device__ __forceinline__ void tile_store(float *dst, const float *tile, int64_t T, int rows, int tc, int lane)
+{
+    if (lane < tc) {
+#pragma unroll 8
+        for (int r = 0; r < rows; ++r) __stcs(dst + r * T + lane, tile[r * TSTR + lane]);
+    }
+}
+
+template <int RESET>
+__global__ void __launch_bounds__(NT_WARPS * 32) lif_fwd_nt_kernel(const LifFwdArgs A)
+{
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t N = A.B * A.M, T = A.T;
+    const int64_t n0 = (blockIdx.x * (int64_t)NT_WARPS + warp) * TILE;
+    if (n0 >= N) return;   // whole warp leaves together
+    float *tx = smem + warp * (2 * TILE_FLOATS);
+    float *ts = tx + TILE_FLOATS;
+    const int rows = (int)min((int64_t)TILE, N - n0);
+    const bool valid = lane < rows;
+    const int64_t n = valid ? n0 + lane : n0;
+    const int64_t b = n / A.M, m = n - b * A.M;
+    const Neuron q = A.np.load(b, m);
+    float v = A.v_init ? __ldg(A.v_init + n) : 0.0f;
+    unsigned a = 0u;
+    unsigned long long cnt = 0ull;
+
+    for (int64_t t0 = 0; t0 < T; t0 += TILE) {
+        const int tc = (int)min((int64_t)TILE, T - t0);
+        tile_load(tx, A.input + n0 * T + t0, T, rows, tc, lane);
+        __syncwarp();
+        if (valid) {
+            for (int t = 0; t < tc; ++t) {
+                lif_step<RESET>(v, a, tx[lane * TSTR + t], q, A.maxs);
+                ts[lane * TSTR + t] = __uint2float_rn(a);
+                tx[lane * TSTR + t] = v;
+                cnt += a;
+            }
+        }
+        __syncwarp();
+        tile_store(A.spikes + n0 * T + t0, ts, T, rows, tc, lane);
+        tile_store(A.v_mem + n0 * T + t0, tx, T, rows, tc, lane);
+        __syncwarp();
+    }
+    if (A.v_post_last && valid) A.v_post_last[n] = post_reset<RESET>(v, a, q);
+    if (A.spike_count) {
+        cnt = warp_sum_u64(valid ? cnt : 0ull);
+        if (lane == 0 && cnt) atomicAdd(A.spike_count, cnt);
+    }
+}
+
+template <int SURR, int RESET, bool WA, bool WS>
+__global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_nt_kernel(const LifBwdArgs A, int ntiles)
+{
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t N = A.B * A.M, T = A.T;
+    const int64_t n0 = (blockIdx.x * (int64_t)NT_WARPS + warp) * TILE;
+    if (n0 >= N) return;
+    float *tg = smem + warp * (ntiles * TILE_FLOATS);   // grad_spikes in, grad_input out
+    float *tv = tg + TILE_FLOATS;
+    float *nxt = tv + TILE_FLOATS;
+    float *tgv = nullptr, *tsl = nullptr, *txi = nullptr;
+    if (A.gv) { tgv = nxt; nxt += TILE_FLOATS; }
+    if (SURR == EXB_SURR_GENERIC) { tsl = nxt; nxt += TILE_FLOATS; }
+    if (WS) { txi = nxt; nxt += TILE_FLOATS; }
+
+    const int rows = (int)min((int64_t)TILE, N - n0);
+    const bool valid = lane < rows;
+    const int64_t n = valid ? n0 + lane : n0;
+    const int64_t b = n / A.M, m = n - b * A.M;
+    const Neuron q = A.np.load(b, m);
+    const SurrConst sc = surr_prepare<SURR>(q, A.p0, A.p1);
+    const float cp = __fmul_rn(q.alpha, q.c);
+    BwdState st;
+    st.R = 0.0f; st.ag = 0.0f; st.sg = 0.0f;
+    float Rprev = 0.0f, f0 = 0.0f;
+    bool nc0 = true;
+    const float glast = (A.g_last && valid) ? __ldg(A.g_last + n) : 0.0f;
+
+    for (int64_t t0 = ((T - 1) / TILE) * TILE; t0 >= 0; t0 -= TILE) {
+        const int tc = (int)min((int64_t)TILE, T - t0);
+        const int64_t off = n0 * T + t0;
+        tile_load(tg, A.go + off, T, rows, tc, lane);
+        tile_load(tv, A.v_mem + off, T, rows, tc, lane);
+        if (tgv) tile_load(tgv, A.gv + off, T, rows, tc, lane);
+        if (SURR == EXB_SURR_GENERIC) tile_load(tsl, A.surr + off, T, rows, tc, lane);
+        if (WS) tile_load(txi, A.input + off, T, rows, tc, lane);
+        __syncwarp();
+        if (valid) {
+            for (int t = tc - 1; t >= 0; --t) {
+                const int i = lane * TSTR + t;
+                float go = tg[i], gv = tgv ? tgv[i] : 0.0f;
+                const float v = tv[i];
+                if (A.g_last && t0 + t == T - 1) fold_last_state_grad<RESET>(go, gv, glast, v, q, A.maxs);
+                Rprev = st.R;
+                const float Rt = lif_bwd_step<SURR, RESET, WA, WS>(st, v, go, gv, (SURR == EXB_SURR_GENERIC) ? tsl[i] : 0.0f,
+                                                                  WS ? txi[i] : 0.0f, q, sc, cp, A.maxs, f0, nc0);
+                tg[i] = __fmul_rn(q.scale, Rt);
+            }
+        }
+        __syncwarp();
+        tile_store(A.grad_input + off, tg, T, rows, tc, lane);
+        __syncwarp();
+    }
+    if (valid) {
+        if (A.grad_init) A.grad_init[n] = __fmul_rn(q.alpha, st.R);
+        if (WA) A.grad_alpha[n] = alpha_grad_finish<RESET>(st, A.v_init ? __ldg(A.v_init + n) : 0.0f, Rprev, f0, nc0);
+        if (WS) A.grad_scale[n] = st.sg;
+    }
+}
+
+// ===========================================================================
+// launchers
+// ===========================================================================
+static inline bool can_vec4(int64_t M, std::initializer_list<const void *> ptrs)
+{
+    if (M % 4) return false;
+    for (const void *p : ptrs)
+        if (p && !aligned16(p)) return false;
+    return true;
+}
+
+template <int RESET>
+static cudaError_t launch_fwd_t(const LifFwdArgs &a, int layout, cudaStream_t s)
+{
+    if (layout == EXB_LAYOUT_BTM) {
+        if (can_vec4(a.M, {a.spikes, a.v_mem, a.input})) {
+            const int64_t total = a.B * (a.M / 4);
+            lif_fwd_btm_kernel<4, RESET, 4><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+        } else {
+            const int64_t total = a.B * a.M;
+            lif_fwd_btm_kernel<1, RESET, 8><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+        }
+    } else {
+        const int64_t N = a.B * a.M;
+        const int64_t warps = (N + TILE - 1) / TILE;
+        const size_t sm = NT_WARPS * 2 * TILE_FLOATS * sizeof(float);
+        lif_fwd_nt_kernel<RESET><<<(unsigned)((warps + NT_WARPS - 1) / NT_WARPS), NT_WARPS * 32, sm, s>>>(a);
+    }
+    return cudaPeekAtLastError();
+}
+
+cudaError_t launch_lif_forward(const LifFwdArgs &a, int layout, int reset_mode, cudaStream_t s)
+{
+    return reset_mode == EXB_RESET_SUBTRACT ? launch_fwd_t<EXB_RESET_SUBTRACT>(a, layout, s)
+                                            : launch_fwd_t<EXB_RESET_TO_VALUE>(a, layout, s);
+}
+
+template <int SURR, int RESET, bool WA, bool WS>
+static cudaError_t launch_bwd_t(const LifBwdArgs &a, int layout, cudaStream_t s)
+{
+    if (layout == EXB_LAYOUT_BTM) {
+        if (can_vec4(a.M, {a.grad_input, a.go, a.gv, a.v_mem, a.surr, a.input})) {
+            const int64_t total = a.B * (a.M / 4);
+            lif_bwd_btm_kernel<4, SURR, RESET, WA, WS, 2><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+        } else {
+            const int64_t total = a.B * a.M;
+            lif_bwd_btm_kernel<1, SURR, RESET, WA, WS, 4><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+        }
+    } else {
+        const int64_t N = a.B * a.M;
+        const int64_t warps = (N + TILE - 1) / TILE;
+        const int ntiles = 2 + (a.gv ? 1 : 0) + (SURR == EXB_SURR_GENERIC ? 1 : 0) + (WS ? 1 : 0);
+        const size_t sm = (size_t)NT_WARPS * ntiles * TILE_FLOATS * sizeof(float);
+        auto kern = lif_bwd_nt_kernel<SURR, RESET, WA, WS>;
+        if (sm > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+            if (e != cudaSuccess) return e;
+        }
+        kern<<<(unsigned)((warps + NT_WARPS - 1) / NT_WARPS), NT_WARPS * 32, sm, s>>>(a, ntiles);
+    }
+    return cudaPeekAtLastError();
+}
+
+template <int SURR, int RESET>
+static cudaError_t launch_bwd_flags(const LifBwdArgs &a, int layout, cudaStream_t s)
+{
+    const bool wa = a.grad_alpha != nullptr, ws = a.grad_scale != nullptr;
+    if (wa && ws) return launch_bwd_t<SURR, RESET, true, true>(a, layout, s);
+    if (wa) return launch_bwd_t<SURR, RESET, true, false>(a, layout, s);
+    if (ws) return launch_bwd_t<SURR, RESET, false, true>(a, layout, s);
+    return launch_bwd_t<SURR, RESET, false, false>(a, layout, s);
+}
+
+template <int RESET>
+static cudaError_t launch_bwd_surr(const LifBwdArgs &a, int layout, int surr_kind, cudaStream_t s)
+{
+    switch (surr_kind) {
+    case EXB_SURR_GENERIC: return launch_bwd_flags<EXB_SURR_GENERIC, RESET>(a, layout, s);
+    case EXB_SURR_SINGLE_EXPONENTIAL: return launch_bwd_flags<EXB_SURR_SINGLE_EXPONENTIAL, RESET>(a, layout, s);
+    case EXB_SURR_HEAVISIDE: return launch_bwd_flags<EXB_SURR_HEAVISIDE, RESET>(a, layout, s);
+    default: return launch_bwd_flags<EXB_SURR_PERIODIC_EXPONENTIAL, RESET>(a, layout, s);
+    }
+}
+
+cudaError_t launch_lif_backward(const LifBwdArgs &a, int layout, int reset_mode, int surr_kind, cudaStream_t s)
+{
+    return reset_mode == EXB_RESET_SUBTRACT ? launch_bwd_surr<EXB_RESET_SUBTRACT>(a, layout, surr_kind, s)
+                                            : launch_bwd_surr<EXB_RESET_TO_VALUE>(a, layout, surr_kind, s);
+}
+
+}  // namespace exb

@@ -1,0 +1,225 @@
+// Per-step neuron arithmetic shared by every kernel of the library, plus the
+// small vector load/store helpers.  Everything here is float32 with the
+// roundings written out (__fmaf_rn, __fmul_rn, ...) so that the association is
+// the same in every kernel and does not depend on compiler contraction.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <math.h>
+
+#include "../../include/exodus_b200.h"
+
+namespace exb {
+
+// A per-neuron parameter that is not expanded by the caller:
+// value(b, m) = p[b*sb + m*sm]; scalar (0,0), per-m (0,1), per-n (M,1).
+struct Param {
+    const float *p;
+    int64_t sb, sm;
+    __device__ __forceinline__ float get(int64_t b, int64_t m, float dflt) const
+    {
+        return p ? __ldg(p + b * sb + m * sm) : dflt;
+    }
+};
+
+__host__ inline Param make_param(const float *p, int mode, int64_t M)
+{
+    Param r;
+    r.p = p;
+    r.sb = (mode == EXB_PARAM_PER_N) ? M : 0;
+    r.sm = (mode == EXB_PARAM_SCALAR) ? 0 : 1;
+    return r;
+}
+
+// Constants of one neuron, loaded once before the time loop.
+struct Neuron {
+    float alpha;   // decay
+    float c;       // subtract value (or reset value)
+    float th;      // threshold
+    float th2;     // 2*threshold
+    float lo;      // lower bound, -inf when there is none
+    float scale;   // input scale, 1 when there is none
+};
+
+struct NeuronParams {
+    Param alpha, c, th, lo, scale;
+    __device__ __forceinline__ Neuron load(int64_t b, int64_t m) const
+    {
+        Neuron q;
+        q.alpha = alpha.get(b, m, 1.0f);
+        q.th = th.get(b, m, 1.0f);
+        q.c = c.get(b, m, q.th);
+        q.th2 = __fadd_rn(q.th, q.th);
+        q.lo = lo.get(b, m, -INFINITY);
+        q.scale = scale.get(b, m, 1.0f);
+        return q;
+    }
+};
+
+// Number of spikes for membrane potential v: min(trunc(v/th), maxs) when
+// v >= th, else 0 (cuda/lif_kernels.h:80-84 of the reference).  For
+// th <= v < 2*th the correctly rounded quotient v/th is always in [1, 2), so
+// the division is skipped there; the result is identical.
+__device__ __forceinline__ unsigned spike_count(float v, const Neuron &q, unsigned maxs)
+{
+    unsigned a = 0u;
+    if (v >= q.th) {
+        a = (v < q.th2) ? 1u : __float2uint_rz(__fdiv_rn(v, q.th));
+        a = min(a, maxs);
+    }
+    return a;
+}
+
+// One forward step (cuda/lif_kernels.h:61-84): reset with the previous count,
+// decay, integrate, clip from below, count spikes.
+template <int RESET>
+__device__ __forceinline__ void lif_step(float &v, unsigned &a, float x, const Neuron &q, unsigned maxs)
+{
+    if (RESET == EXB_RESET_SUBTRACT) v = __fmaf_rn(-__uint2float_rn(a), q.c, v);
+    else v = a ? q.c : v;
+    v = __fmaf_rn(v, q.alpha, __fmul_rn(q.scale, x));
+    v = (v < q.lo) ? q.lo : v;
+    a = spike_count(v, q, maxs);
+}
+
+// State after the reset that follows a step.
+template <int RESET>
+__device__ __forceinline__ float post_reset(float v, unsigned a, const Neuron &q)
+{
+    if (RESET == EXB_RESET_SUBTRACT) return __fmaf_rn(-__uint2float_rn(a), q.c, v);
+    return a ? q.c : v;
+}
+
+// Surrogate-gradient constants of one neuron.
+struct SurrConst {
+    float k0, k1, k2;
+};
+
+template <int SURR>
+__device__ __forceinline__ SurrConst surr_prepare(const Neuron &q, float p0, float p1)
+{
+    SurrConst s;
+    s.k0 = s.k1 = s.k2 = 0.0f;
+    if (SURR == EXB_SURR_SINGLE_EXPONENTIAL) {
+        const float w = __fmul_rn(q.th, p0);
+        s.k0 = __fdiv_rn(1.0f, w);        // 1/width
+        s.k1 = __fdiv_rn(p1, w);          // amplitude
+    } else if (SURR == EXB_SURR_HEAVISIDE) {
+        s.k0 = __fsub_rn(q.th, p0);       // window edge
+        s.k1 = __fdiv_rn(1.0f, q.th);
+    } else if (SURR == EXB_SURR_PERIODIC_EXPONENTIAL) {
+        s.k0 = __fdiv_rn(1.0f, p0);
+        s.k1 = __fdiv_rn(p1, q.th);
+        s.k2 = __fmul_rn(q.th, 0.5f);
+    }
+    return s;
+}
+
+template <int SURR>
+__device__ __forceinline__ float surrogate(float v, const Neuron &q, const SurrConst &s, float loaded)
+{
+    if (SURR == EXB_SURR_SINGLE_EXPONENTIAL) {
+        return __fmul_rn(s.k1, expf(-fabsf(__fsub_rn(v, q.th)) * s.k0));
+    } else if (SURR == EXB_SURR_HEAVISIDE) {
+        return (v >= s.k0) ? s.k1 : 0.0f;
+    } else if (SURR == EXB_SURR_PERIODIC_EXPONENTIAL) {
+        const float u = __fsub_rn(v, s.k2);
+        const float w = (v < q.th) ? u : __fsub_rn(u, floorf(__fdiv_rn(u, q.th)));
+        return __fmul_rn(s.k1, expf(-fabsf(__fsub_rn(w, s.k2)) * s.k0));
+    }
+    return loaded;
+}
+
+// Running state of the reverse-time sweep of one neuron.
+struct BwdState {
+    float R;    // R_{t+1}: gradient w.r.t. the membrane potential one step later
+    float ag;   // alpha-gradient accumulator
+    float sg;   // input-scale-gradient accumulator
+};
+
+// One reverse step.  v: saved pre-reset membrane potential; go/gv: incoming
+// gradients w.r.t. spikes and v_mem at this step; sl: caller-supplied surrogate
+// (generic mode); x: unscaled forward input (only when WANT_SCALE_GRAD).
+// Returns R_t; on return st.R == R_t.  `f_out`, `n_out` give the step's
+// propagation factor and clip gate for the caller's first-step handling.
+template <int SURR, int RESET, bool WANT_ALPHA_GRAD, bool WANT_SCALE_GRAD>
+__device__ __forceinline__ float lif_bwd_step(BwdState &st, float v, float go, float gv, float sl, float x,
+                                              const Neuron &q, const SurrConst &sc, float cp, unsigned maxs,
+                                              float &f_out, bool &n_out)
+{
+    const float s = surrogate<SURR>(v, q, sc, sl);
+    const bool n = v > q.lo;
+    const float g = __fadd_rn(__fmul_rn(s, go), gv);
+    unsigned a = 0u;
+    if (RESET == EXB_RESET_TO_VALUE || WANT_ALPHA_GRAD) a = spike_count(v, q, maxs);
+    float f;
+    if (RESET == EXB_RESET_SUBTRACT) f = __fmaf_rn(-cp, s, q.alpha);   // alpha - (alpha*c)*s
+    else f = a ? 0.0f : q.alpha;
+    if (WANT_ALPHA_GRAD) st.ag = __fmaf_rn(st.R, post_reset<RESET>(v, a, q), st.ag);
+    const float Rt = n ? __fmaf_rn(f, st.R, g) : 0.0f;
+    if (WANT_SCALE_GRAD) st.sg = __fmaf_rn(Rt, x, st.sg);
+    st.R = Rt;
+    f_out = f;
+    n_out = n;
+    return Rt;
+}
+
+// A gradient G w.r.t. the post-reset state of the LAST step enters the sweep
+// through that step's two incoming gradients: v_post = v - c*a gives
+// go += -c*G and gv += G (reset-to-value: gv += G where no spike occurred).
+template <int RESET>
+__device__ __forceinline__ void fold_last_state_grad(float &go, float &gv, float G, float v,
+                                                     const Neuron &q, unsigned maxs)
+{
+    if (RESET == EXB_RESET_SUBTRACT) {
+        go = __fmaf_rn(-q.c, G, go);
+        gv = __fadd_rn(gv, G);
+    } else {
+        gv = __fadd_rn(gv, spike_count(v, q, maxs) ? 0.0f : G);
+    }
+}
+
+// Terms of the alpha gradient that involve the initial state, added after the
+// sweep reached t = 0 (st.R == R_0).  R1 is R_1 (0 when T == 1), f0/n0 the
+// factor and clip gate of step 0.  The second term reproduces
+// cuda/lif_kernels.h:219-238 of the reference, where the t = 0 accumulator is
+// carried into t = 1 without the t = 0 clip gate.
+template <int RESET>
+__device__ __forceinline__ float alpha_grad_finish(const BwdState &st, float v_init, float R1, float f0, bool n0)
+{
+    float ag = __fmaf_rn(st.R, v_init, st.ag);
+    if (RESET == EXB_RESET_SUBTRACT && !n0) ag = __fmaf_rn(__fmul_rn(v_init, f0), R1, ag);
+    return ag;
+}
+
+// ---- small vector helpers -------------------------------------------------
+template <int V>
+__device__ __forceinline__ void ldv(float (&d)[V], const float *p)
+{
+    if (V == 4) {
+        const float4 t = __ldcs(reinterpret_cast<const float4 *>(p));
+        d[0] = t.x; d[1] = t.y; d[2] = t.z; d[3] = t.w;
+    } else if (V == 2) {
+        const float2 t = __ldcs(reinterpret_cast<const float2 *>(p));
+        d[0] = t.x; d[1] = t.y;
+    } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) d[j] = __ldcs(p + j);
+    }
+}
+
+template <int V>
+__device__ __forceinline__ void stv(float *p, const float (&d)[V])
+{
+    if (V == 4) {
+        __stcs(reinterpret_cast<float4 *>(p), make_float4(d[0], d[1], d[2], d[3]));
+    } else if (V == 2) {
+        __stcs(reinterpret_cast<float2 *>(p), make_float2(d[0], d[1]));
+    } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) __stcs(p + j, d[j]);
+    }
+}
+
+}  // namespace exb

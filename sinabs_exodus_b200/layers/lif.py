@@ -1,0 +1,226 @@
+"""EXODUS ``LIF`` layer on the B200 kernels.
+
+Same constructor, state handling, recordings, ``firing_rate`` and ``repr`` as the
+reference layer (``sinabs/exodus/layers/lif.py:47-329``).  What differs is how the
+work reaches the GPU: the layer's own ``(batch, time, *neurons)`` tensor is used
+as it is (time-major), parameters are passed un-expanded, and the ``decay_early``
+/ ``norm_input`` multiplications, the state after the last reset and the spike
+count are produced by the same kernel launch.  The reference's transpose copy
+(``lif.py:181``), parameter broadcasts (``:188,204,226-243``), ``v - c*spikes``
+pass (``:256``) and ``sum()/numel()`` pass (``:305``) have no counterpart here.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple, Union
+
+import torch
+
+from .. import _lib
+from ..compat.activation import (
+    MaxSpike,
+    MembraneReset,
+    MembraneSubtract,
+    MultiSpike,
+    SingleExponential,
+    SingleSpike,
+)
+from ..compat.layers import LIF as LIFBase
+from ..compat.layers import SqueezeMixin
+from ..leaky import LeakyIntegratorTM
+from ..spike import IntegrateAndFireTM
+
+__all__ = ["LIF", "LIFSqueeze"]
+
+
+def expand_to_1d_contiguous(value: Union[float, torch.Tensor], shape: Tuple[int]) -> torch.Tensor:
+    """Expand ``value`` to ``shape``, flatten, make contiguous (reference ``lif.py:20-44``).
+
+    Kept for API compatibility; the layers themselves never expand parameters.
+    """
+    return torch.as_tensor(value).expand(shape).float().flatten().contiguous()
+
+
+def _flat_param(value, trailing: Tuple[int, ...], batch: int, device) -> Optional[torch.Tensor]:
+    """Bring a parameter to 1, M or B*M elements without breaking its autograd graph.
+
+    A value that broadcasts against the neuron dimensions becomes M elements, one
+    that needs the batch dimension too becomes B*M, a single value stays single.
+    """
+    if value is None:
+        return None
+    t = value if isinstance(value, torch.Tensor) else torch.as_tensor(value, dtype=torch.float32)
+    t = t.to(device=device, dtype=torch.float32)
+    if t.numel() == 1:
+        return t.reshape(1)
+    try:
+        return t.expand(trailing).reshape(-1)
+    except RuntimeError:
+        return t.expand((batch, *trailing)).reshape(-1)
+
+
+class LIF(LIFBase):
+    """Leaky integrate-and-fire layer, forward and exact backward on the GPU.
+
+    Parameters are those of the reference layer: ``tau_mem``, ``tau_syn``,
+    ``spike_threshold``, ``spike_fn`` (``MultiSpike``, ``SingleSpike`` or
+    ``MaxSpike(k)``; ``None`` for a non-spiking integrator), ``reset_fn``,
+    ``surrogate_grad_fn``, ``min_v_mem``, ``train_alphas``, ``shape``,
+    ``norm_input``, ``record_states`` and ``decay_early``.
+
+    Beyond the reference, ``reset_fn`` may be ``MembraneReset(value)``: the
+    membrane is then set to ``value`` wherever a spike occurred, and the reset is
+    treated as a constant mask in the backward pass.
+    """
+
+    def __init__(
+        self,
+        tau_mem: Union[float, torch.Tensor],
+        tau_syn: Optional[Union[float, torch.Tensor]] = None,
+        spike_threshold: Optional[Union[float, torch.Tensor]] = 1.0,
+        spike_fn: Callable = MultiSpike,
+        reset_fn: Callable = MembraneSubtract(),
+        surrogate_grad_fn: Callable = SingleExponential(),
+        min_v_mem: Optional[Union[float, torch.Tensor]] = None,
+        train_alphas: bool = False,
+        shape: Optional[torch.Size] = None,
+        norm_input: bool = True,
+        record_states: bool = False,
+        decay_early: bool = True,
+    ):
+        self._parse_activation_fn(spike_fn, reset_fn)
+        super().__init__(
+            tau_mem=tau_mem,
+            tau_syn=tau_syn,
+            spike_threshold=spike_threshold,
+            spike_fn=spike_fn,
+            reset_fn=reset_fn,
+            surrogate_grad_fn=surrogate_grad_fn,
+            min_v_mem=min_v_mem,
+            train_alphas=train_alphas,
+            shape=shape,
+            norm_input=norm_input,
+            record_states=record_states,
+        )
+        self.decay_early = decay_early
+
+    def _parse_activation_fn(self, spike_fn, reset_fn):
+        if spike_fn is None:
+            return
+        spike_ok = spike_fn in (MultiSpike, SingleSpike) or isinstance(spike_fn, MaxSpike)
+        reset_ok = isinstance(reset_fn, (MembraneSubtract, MembraneReset))
+        if not spike_ok or not reset_ok:
+            raise NotImplementedError(
+                "Spike mechanism config not supported. "
+                "Use MultiSpike/SingleSpike/MaxSpike and MembraneSubtract (or MembraneReset) functions.")
+        if isinstance(spike_fn, MaxSpike):
+            self.max_num_spikes_per_bin = spike_fn.max_num_spikes_per_bin
+        elif spike_fn == MultiSpike:
+            self.max_num_spikes_per_bin = None
+        else:
+            self.max_num_spikes_per_bin = 1
+
+    # ------------------------------------------------------------------
+    def _prepare_input(self, input_data: torch.Tensor):
+        """Initialise states if needed and view the input as (B, T, M)."""
+        batch_size, time_steps, *trailing_dim = input_data.shape
+        if not self.is_state_initialised() or not self.state_has_shape((batch_size, *trailing_dim)):
+            self.init_state_with_shape((batch_size, *trailing_dim))
+        x = input_data
+        if x.dtype != torch.float32:
+            x = x.float()
+        x = x.reshape(batch_size, time_steps, -1)
+        if not x.is_contiguous():
+            x = x.contiguous()
+        return x, (batch_size, time_steps, *trailing_dim)
+
+    def _forward_synaptic(self, x: torch.Tensor, batch: int, trailing):
+        alpha_syn = _flat_param(self.alpha_syn_calculated, trailing, batch, x.device)
+        return LeakyIntegratorTM.apply(
+            x, alpha_syn, self.i_syn.reshape(-1), alpha_syn if self.decay_early else None)
+
+    def _forward_membrane(self, i_syn: torch.Tensor, batch: int, trailing):
+        dev = i_syn.device
+        alpha_mem = _flat_param(self.alpha_mem_calculated, trailing, batch, dev)
+        scale = (1.0 - alpha_mem) if self.norm_input else None
+
+        if self.spike_fn is None:
+            if self.decay_early:
+                scale = alpha_mem if scale is None else scale * alpha_mem
+            v_mem, v_last = LeakyIntegratorTM.apply(i_syn, alpha_mem, self.v_mem.reshape(-1), scale)
+            return v_mem, v_mem, v_last, None
+
+        threshold = _flat_param(self.spike_threshold, trailing, batch, dev)
+        min_v_mem = _flat_param(self.min_v_mem, trailing, batch, dev)
+        if isinstance(self.reset_fn, MembraneReset):
+            reset_mode = _lib.RESET_TO_VALUE
+            subtract = _flat_param(self.reset_fn.reset_value, trailing, batch, dev)
+        else:
+            reset_mode = _lib.RESET_SUBTRACT
+            subtract = _flat_param(self.reset_fn.subtract_value, trailing, batch, dev)
+        with torch.no_grad():
+            a = alpha_mem.detach()
+            if bool(((a < 0) | (a > 1)).any()):
+                raise ValueError("'alpha' must be between 0 and 1.")
+            if self.min_v_mem is not None:
+                th = torch.as_tensor(self.spike_threshold, dtype=torch.float32, device=dev)
+                lo = torch.as_tensor(self.min_v_mem, dtype=torch.float32, device=dev)
+                if bool((th <= lo).any()):
+                    raise ValueError("`threshold` must be greater than `min_v_mem`.")
+        count = torch.zeros(1, dtype=torch.int64, device=dev)
+        spikes, v_pre, v_post_last = IntegrateAndFireTM.apply(
+            i_syn, alpha_mem, self.v_mem.reshape(-1), threshold, subtract, min_v_mem, scale,
+            self.surrogate_grad_fn, self.max_num_spikes_per_bin, reset_mode, count)
+        if self.record_states:
+            c = threshold if subtract is None else subtract
+            c = c if c.numel() == 1 else (c.view(1, 1, -1) if c.numel() == v_pre.shape[2] else c.view(batch, 1, -1))
+            if reset_mode == _lib.RESET_SUBTRACT:
+                v_rec = v_pre - c * spikes
+            else:
+                v_rec = torch.where(spikes > 0, c.expand_as(v_pre), v_pre)
+        else:
+            v_rec = None
+        return spikes, v_rec, v_post_last, count
+
+    def forward(self, input_data: torch.Tensor):
+        """``input_data``: (batch, time, ...) on a CUDA device.  Returns a tensor of the same shape."""
+        x, original_shape = self._prepare_input(input_data)
+        batch_size, time_steps, *trailing_dim = original_shape
+        trailing = tuple(trailing_dim)
+        self.recordings = dict()
+
+        if self.tau_syn_calculated is None:
+            i_syn = x
+        else:
+            i_syn, i_last = self._forward_synaptic(x, batch_size, trailing)
+            self.i_syn = i_last.reshape(batch_size, *trailing)
+            if self.record_states:
+                self.recordings["i_syn"] = i_syn.reshape(original_shape)
+
+        output, v_rec, v_last, count = self._forward_membrane(i_syn, batch_size, trailing)
+        if self.record_states:
+            self.recordings["v_mem"] = v_rec.reshape(original_shape)
+        self.v_mem = v_last.reshape(batch_size, *trailing)
+        output_full = output.reshape(original_shape)
+        if count is not None:
+            self.firing_rate = count[0].to(torch.float32) / output_full.numel()
+        else:
+            self.firing_rate = output_full.detach().sum() / output_full.numel()
+        return output_full
+
+    def __repr__(self):
+        return "EXODUS " + super().__repr__()
+
+
+class LIFSqueeze(LIF, SqueezeMixin):
+    """``LIF`` for 4D input (batch*time, channel, height, width)."""
+
+    def __init__(self, batch_size=None, num_timesteps=None, **kwargs):
+        super().__init__(**kwargs)
+        self.squeeze_init(batch_size, num_timesteps)
+
+    def forward(self, input_data: torch.Tensor) -> torch.Tensor:
+        return self.squeeze_forward(input_data, super().forward)
+
+    @property
+    def _param_dict(self) -> dict:
+        return self.squeeze_param_dict(super()._param_dict)

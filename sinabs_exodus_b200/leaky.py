@@ -1,0 +1,126 @@
+"""Leaky-integrator autograd Functions.
+
+``LeakyIntegrator`` keeps the signature, validation and return values of the
+reference Function (``sinabs/exodus/leaky.py:5-76``) on ``[N, T]`` tensors.
+``LeakyIntegratorTM`` is the same recurrence on a layer's time-major
+``(B, T, M)`` tensor with un-expanded parameters and a fused input scale.
+
+Forward is one launch of ``exb_leaky_forward``; backward one launch of
+``exb_leaky_backward`` (input gradient, alpha gradient, scale gradient and
+``grad_init`` in the same reverse sweep).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from .spike import _flat32, _mode_of, _reduce_to_param
+
+
+class _LeakyCore:
+    @staticmethod
+    def forward(ctx, inp, alpha, v_init, in_scale, B, T, M, layout):
+        N = B * M
+        a_f, sc_f, vi_f = _flat32(alpha), _flat32(in_scale), _flat32(v_init)
+        modes = dict(alpha=_mode_of(a_f, M, N, "alpha"), scale=_mode_of(sc_f, M, N, "in_scale"))
+        out = torch.empty_like(inp)
+        v_last = torch.empty(N, dtype=torch.float32, device=inp.device)
+        _lib.leaky_forward(out, inp, vi_f, (a_f, modes["alpha"]), (sc_f, modes["scale"]), v_last, B, T, M, layout)
+        ctx.set_materialize_grads(False)
+        ctx.geometry = (B, T, M, layout)
+        ctx.modes = modes
+        ctx.want_alpha = alpha.requires_grad
+        ctx.want_scale = in_scale is not None and in_scale.requires_grad
+        ctx.alpha_shape = alpha.shape
+        ctx.scale_shape = None if in_scale is None else in_scale.shape
+        ctx.v_init_shape = None if v_init is None else v_init.shape
+        ctx.has = (sc_f is not None, vi_f is not None)
+        saved = [a_f] + [t for t in (sc_f, vi_f) if t is not None]
+        if ctx.want_alpha:
+            saved.append(out)
+        if ctx.want_scale:
+            saved.append(inp)
+        ctx.save_for_backward(*saved)
+        return out, v_last
+
+    @staticmethod
+    def backward(ctx, grad_out, grad_v_last):
+        B, T, M, layout = ctx.geometry
+        N = B * M
+        saved = list(ctx.saved_tensors)
+        a_f = saved.pop(0)
+        sc_f = saved.pop(0) if ctx.has[0] else None
+        vi_f = saved.pop(0) if ctx.has[1] else None
+        out = saved.pop(0) if ctx.want_alpha else None
+        inp = saved.pop(0) if ctx.want_scale else None
+        dev = a_f.device
+        if grad_out is None:
+            shape = (N, T) if layout == _lib.LAYOUT_NT else (B, T, M)
+            grad_out = torch.zeros(shape, dtype=torch.float32, device=dev)
+        grad_out = grad_out.contiguous()
+        if grad_v_last is not None:
+            grad_v_last = grad_v_last.to(torch.float32).reshape(-1).contiguous()
+        grad_input = torch.empty_like(grad_out)
+        grad_init = torch.empty(N, dtype=torch.float32, device=dev) if ctx.v_init_shape is not None else None
+        ga = torch.empty(N, dtype=torch.float32, device=dev) if ctx.want_alpha else None
+        gs = torch.empty(N, dtype=torch.float32, device=dev) if ctx.want_scale else None
+        _lib.leaky_backward(grad_input, ga, grad_init, gs, grad_out, grad_v_last, out, inp, vi_f,
+                            (a_f, ctx.modes["alpha"]), (sc_f, ctx.modes["scale"]), B, T, M, layout)
+        grad_alpha = _reduce_to_param(ga, ctx.alpha_shape, ctx.modes["alpha"], B, M) if ctx.want_alpha else None
+        grad_scale = _reduce_to_param(gs, ctx.scale_shape, ctx.modes["scale"], B, M) if ctx.want_scale else None
+        if grad_init is not None:
+            grad_init = grad_init.reshape(ctx.v_init_shape)
+        return grad_input, grad_alpha, grad_init, grad_scale
+
+
+class LeakyIntegrator(torch.autograd.Function):
+    """Drop-in for the reference ``LeakyIntegrator``: ``apply(inp, alpha, v_mem_init) -> out`` on ``[N, T]``."""
+
+    @staticmethod
+    def forward(ctx, inp, alpha, v_mem_init):
+        if not inp.ndim == 2:
+            raise ValueError("'inp' must be 2D, (N, Time)")
+        if not inp.is_contiguous():
+            raise ValueError("'inp' has to be contiguous.")
+        if not alpha.ndim == 1:
+            raise ValueError("'alpha' must be 1D, (N,)")
+        if not alpha.is_contiguous():
+            raise ValueError("'alpha' has to be contiguous.")
+        if not v_mem_init.ndim == 1:
+            raise ValueError("'v_mem_init' must be 1D, (N,)")
+        if not v_mem_init.is_contiguous():
+            raise ValueError("'v_mem_init' has to be contiguous.")
+        N, T = inp.shape
+        if alpha.numel() != N or v_mem_init.numel() != N:
+            raise ValueError(f"'alpha' and 'v_mem_init' must have one element per row of 'inp' ({N})")
+        out, _ = _LeakyCore.forward(ctx, inp, alpha, v_mem_init, None, 1, T, N, _lib.LAYOUT_NT)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        grad_input, grad_alpha, grad_init, _ = _LeakyCore.backward(ctx, grad_output, None)
+        return grad_input, grad_alpha, grad_init
+
+
+class LeakyIntegratorTM(torch.autograd.Function):
+    """Leaky integrator on a time-major ``(B, T, M)`` tensor.
+
+    ``apply(inp, alpha, v_init, in_scale) -> (out, v_last)``; parameters hold 1, M or
+    B*M values.  ``v_last`` (B*M,) equals ``out[:, -1]`` and carries its own gradient,
+    so that keeping the state for the next call costs no full-size tensor.
+    """
+
+    @staticmethod
+    def forward(ctx, inp, alpha, v_init, in_scale):
+        if inp.ndim != 3:
+            raise ValueError("'inp' must be 3D, (batch, time, neurons)")
+        if not inp.is_contiguous():
+            raise ValueError("'inp' has to be contiguous.")
+        B, T, M = inp.shape
+        if v_init is not None and v_init.numel() != B * M:
+            raise ValueError("'v_init' must hold one value per batch item and neuron")
+        return _LeakyCore.forward(ctx, inp, alpha, v_init, in_scale, B, T, M, _lib.LAYOUT_BTM)
+
+    @staticmethod
+    def backward(ctx, grad_out, grad_v_last):
+        return _LeakyCore.backward(ctx, grad_out, grad_v_last)

@@ -1,0 +1,227 @@
+"""Spiking autograd Functions.
+
+``IntegrateAndFire`` keeps the signature, validation, return values and error
+types of the reference Function (``sinabs/exodus/spike.py:107-291``) and runs on
+``[N, T]`` tensors.  ``IntegrateAndFireTM`` is the same computation on a layer's
+own time-major ``(B, T, M)`` tensor with un-expanded parameters; the layers use it
+so that no transpose or parameter broadcast is ever materialised.
+
+Forward is one launch of ``exb_lif_forward``.  Backward is one launch of
+``exb_lif_backward``, which replaces the reference's surrogate evaluation, clip
+mask, gradient combination, ``lifBackward``, ``lifBackwardAlpha`` and
+``grad_init`` (``spike.py:251-289``).
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+
+from . import _lib
+from .surrogate import classify
+
+
+def _mode_of(t: Optional[torch.Tensor], M: int, N: int, name: str) -> int:
+    if t is None:
+        return _lib.PARAM_SCALAR
+    k = t.numel()
+    if k == 1:
+        return _lib.PARAM_SCALAR
+    if k == M:
+        return _lib.PARAM_PER_M
+    if k == N:
+        return _lib.PARAM_PER_N
+    raise ValueError(f"'{name}' has {k} elements; expected 1, {M} (per neuron) or {N} (per batch item and neuron)")
+
+
+def _reduce_to_param(per_instance: torch.Tensor, shape, mode: int, B: int, M: int) -> torch.Tensor:
+    """Sum a per-instance (N,) gradient down to the parameter's own shape."""
+    if mode == _lib.PARAM_PER_N:
+        g = per_instance
+    elif mode == _lib.PARAM_PER_M:
+        g = per_instance.view(B, M).sum(0)
+    else:
+        g = per_instance.sum()
+    return g.reshape(shape)
+
+
+def _flat32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    if t is None:
+        return None
+    return t.detach().to(torch.float32).reshape(-1).contiguous()
+
+
+class _LifCore:
+    """Shared forward/backward bodies; ``layout`` decides how (B, T, M) maps to memory."""
+
+    @staticmethod
+    def forward(ctx, inp, alpha, v_init, theta, subtract, min_v_mem, in_scale, surrogate_fn, max_spikes,
+                reset_mode, spike_count, B, T, M, layout):
+        N = B * M
+        a_f, th_f, c_f, lo_f, sc_f = map(_flat32, (alpha, theta, subtract, min_v_mem, in_scale))
+        modes = dict(
+            alpha=_mode_of(a_f, M, N, "alpha"), theta=_mode_of(th_f, M, N, "threshold"),
+            subtract=_mode_of(c_f, M, N, "membrane_subtract"), lo=_mode_of(lo_f, M, N, "min_v_mem"),
+            scale=_mode_of(sc_f, M, N, "in_scale"))
+        vi_f = _flat32(v_init)
+        spikes = torch.empty_like(inp)
+        v_mem = torch.empty_like(inp)
+        v_post_last = torch.empty(N, dtype=torch.float32, device=inp.device)
+        _lib.lif_forward(spikes, v_mem, inp, vi_f, (sc_f, modes["scale"]), (a_f, modes["alpha"]),
+                         (c_f, modes["subtract"]), (th_f, modes["theta"]), (lo_f, modes["lo"]),
+                         max_spikes, reset_mode, v_post_last, spike_count, B, T, M, layout)
+        ctx.set_materialize_grads(False)
+        ctx.geometry = (B, T, M, layout)
+        ctx.modes = modes
+        ctx.surrogate_fn = surrogate_fn
+        ctx.max_spikes = max_spikes
+        ctx.reset_mode = reset_mode
+        ctx.want_alpha = alpha is not None and alpha.requires_grad
+        ctx.want_scale = in_scale is not None and in_scale.requires_grad
+        ctx.alpha_shape = None if alpha is None else alpha.shape
+        ctx.scale_shape = None if in_scale is None else in_scale.shape
+        ctx.v_init_shape = None if v_init is None else v_init.shape
+        ctx.has = tuple(t is not None for t in (c_f, lo_f, sc_f, vi_f))
+        saved = [v_mem, a_f, th_f]
+        saved += [t for t in (c_f, lo_f, sc_f, vi_f) if t is not None]
+        if ctx.want_scale:
+            saved.append(inp)
+        ctx.save_for_backward(*saved)
+        return spikes, v_mem, v_post_last
+
+    @staticmethod
+    def backward(ctx, grad_spikes, grad_v_mem, grad_v_last):
+        B, T, M, layout = ctx.geometry
+        N = B * M
+        saved = list(ctx.saved_tensors)
+        v_mem, a_f, th_f = saved[:3]
+        rest = saved[3:]
+        c_f = rest.pop(0) if ctx.has[0] else None
+        lo_f = rest.pop(0) if ctx.has[1] else None
+        sc_f = rest.pop(0) if ctx.has[2] else None
+        vi_f = rest.pop(0) if ctx.has[3] else None
+        inp = rest.pop(0) if ctx.want_scale else None
+        modes = ctx.modes
+        dev = v_mem.device
+
+        if grad_spikes is None:
+            grad_spikes = torch.zeros_like(v_mem)
+        grad_spikes = grad_spikes.contiguous()
+        if grad_v_mem is not None:
+            grad_v_mem = grad_v_mem.contiguous()
+        if grad_v_last is not None:
+            grad_v_last = grad_v_last.to(torch.float32).reshape(-1).contiguous()
+
+        kind, p0, p1 = classify(ctx.surrogate_fn)
+        surr = None
+        if kind == _lib.SURR_GENERIC:
+            # Any callable: evaluate it with PyTorch exactly like spike.py:251.
+            if layout == _lib.LAYOUT_NT:
+                th_b = th_f.reshape(-1, 1) if th_f.numel() > 1 else th_f
+            else:
+                th_b = th_f if th_f.numel() == 1 else (
+                    th_f.view(1, 1, M) if modes["theta"] == _lib.PARAM_PER_M else th_f.view(B, 1, M))
+            surr = ctx.surrogate_fn(v_mem, th_b).to(torch.float32).contiguous()
+
+        grad_input = torch.empty_like(v_mem)
+        grad_init = torch.empty(N, dtype=torch.float32, device=dev) if ctx.v_init_shape is not None else None
+        ga = torch.empty(N, dtype=torch.float32, device=dev) if ctx.want_alpha else None
+        gs = torch.empty(N, dtype=torch.float32, device=dev) if ctx.want_scale else None
+        _lib.lif_backward(grad_input, ga, grad_init, gs, grad_spikes, grad_v_mem, grad_v_last, v_mem, surr, vi_f,
+                          inp, (sc_f, modes["scale"]), (a_f, modes["alpha"]), (c_f, modes["subtract"]),
+                          (th_f, modes["theta"]), (lo_f, modes["lo"]), ctx.max_spikes, ctx.reset_mode,
+                          kind, p0, p1, B, T, M, layout)
+        grad_alpha = None
+        if ctx.want_alpha:
+            grad_alpha = _reduce_to_param(ga, ctx.alpha_shape, modes["alpha"], B, M)
+        grad_scale = None
+        if ctx.want_scale:
+            grad_scale = _reduce_to_param(gs, ctx.scale_shape, modes["scale"], B, M)
+        if grad_init is not None:
+            grad_init = grad_init.reshape(ctx.v_init_shape)
+        return grad_input, grad_alpha, grad_init, grad_scale
+
+
+def _validate_1d(t: torch.Tensor, name: str) -> None:
+    if not t.ndim == 1:
+        raise ValueError(f"'{name}' must be 1D, (N,)")
+    if not t.is_contiguous():
+        raise ValueError(f"'{name}' has to be contiguous.")
+
+
+class IntegrateAndFire(torch.autograd.Function):
+    """Drop-in for the reference ``IntegrateAndFire`` (``[N, T]`` tensors, per-row parameters).
+
+    ``apply(inp, alpha, v_mem_init, threshold, membrane_subtract, min_v_mem,
+    surrogate_grad_fn, max_num_spikes_per_bin=None) -> (output_spikes, v_mem)``
+    with ``v_mem`` the membrane potential before the reset of each step.
+    """
+
+    @staticmethod
+    def forward(ctx, inp, alpha, v_mem_init, threshold, membrane_subtract, min_v_mem,
+                surrogate_grad_fn: Callable, max_num_spikes_per_bin: Optional[int] = None):
+        if membrane_subtract is None:                       # spike.py:157-158
+            membrane_subtract = torch.ones_like(alpha) * threshold
+        apply_min_v_mem = min_v_mem is not None
+        if not inp.ndim == 2:
+            raise ValueError("'inp' must be 2D, (N, Time)")
+        if not inp.is_contiguous():
+            raise ValueError("'inp' has to be contiguous.")
+        _validate_1d(alpha, "alpha")
+        _validate_1d(membrane_subtract, "membrane_subtract")
+        _validate_1d(v_mem_init, "v_mem_init")
+        _validate_1d(threshold, "threshold")
+        if (alpha < 0).any() or (alpha > 1).any():
+            raise ValueError("'alpha' must be between 0 and 1.")
+        if apply_min_v_mem:
+            _validate_1d(min_v_mem, "min_v_mem")
+            if (threshold <= min_v_mem).any():
+                raise ValueError("`threshold` must be greater than `min_v_mem`.")
+        N, T = inp.shape
+        for t, name in ((alpha, "alpha"), (membrane_subtract, "membrane_subtract"),
+                        (v_mem_init, "v_mem_init"), (threshold, "threshold")):
+            if t.numel() != N:
+                raise ValueError(f"'{name}' must have one element per row of 'inp' ({N}), got {t.numel()}")
+        spikes, v_mem, _ = _LifCore.forward(
+            ctx, inp, alpha, v_mem_init, threshold, membrane_subtract, min_v_mem, None, surrogate_grad_fn,
+            max_num_spikes_per_bin, _lib.RESET_SUBTRACT, None, 1, T, N, _lib.LAYOUT_NT)
+        return spikes, v_mem
+
+    @staticmethod
+    def backward(ctx, grad_output, grad_v_mem):
+        grad_input, grad_alpha, grad_init, _ = _LifCore.backward(ctx, grad_output, grad_v_mem, None)
+        return grad_input, grad_alpha, grad_init, None, None, None, None, None
+
+
+class IntegrateAndFireTM(torch.autograd.Function):
+    """Spike scan on a time-major ``(B, T, M)`` tensor.
+
+    ``apply(inp, alpha, v_init, threshold, membrane_subtract, min_v_mem, in_scale,
+    surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count)
+    -> (spikes, v_mem, v_post_last)``.
+
+    Parameters hold 1, M or B*M values and are read in place.  ``in_scale``
+    multiplies the input per neuron.  ``v_post_last`` (B*M,) is the state after the
+    last reset; a gradient arriving on it is folded into the sweep.  ``spike_count``
+    is an optional zero-initialised int64 tensor of one element that receives the
+    total number of spikes.
+    """
+
+    @staticmethod
+    def forward(ctx, inp, alpha, v_init, threshold, membrane_subtract, min_v_mem, in_scale,
+                surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count):
+        if inp.ndim != 3:
+            raise ValueError("'inp' must be 3D, (batch, time, neurons)")
+        if not inp.is_contiguous():
+            raise ValueError("'inp' has to be contiguous.")
+        B, T, M = inp.shape
+        if v_init is not None and v_init.numel() != B * M:
+            raise ValueError("'v_init' must hold one value per batch item and neuron")
+        return _LifCore.forward(ctx, inp, alpha, v_init, threshold, membrane_subtract, min_v_mem, in_scale,
+                                surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count,
+                                B, T, M, _lib.LAYOUT_BTM)
+
+    @staticmethod
+    def backward(ctx, grad_spikes, grad_v_mem, grad_v_last):
+        grad_input, grad_alpha, grad_init, grad_scale = _LifCore.backward(ctx, grad_spikes, grad_v_mem, grad_v_last)
+        return grad_input, grad_alpha, grad_init, None, None, None, grad_scale, None, None, None, None

@@ -1,0 +1,110 @@
+"""numpy-in / numpy-out helpers that call the C-ABI of libexodus_b200.so on cuda:0.
+
+Problems are given in the [N, T] layout with N = B*M (row n = b*M + m); the
+helpers rearrange them to the requested device layout, call the entry point
+through ``sinabs_exodus_b200._lib`` (ctypes), and bring the results back to [N, T].
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from sinabs_exodus_b200 import _lib
+
+DEV = "cuda:0"
+
+
+def to_dev(a_nt, B, M, layout):
+    """[N,T] numpy -> device tensor in `layout`."""
+    if a_nt is None:
+        return None
+    N, T = a_nt.shape
+    t = torch.tensor(np.ascontiguousarray(a_nt, np.float32), device=DEV)
+    if layout == _lib.LAYOUT_BTM:
+        t = t.view(B, M, T).permute(0, 2, 1).contiguous()
+    return t
+
+
+def from_dev(t, B, M, layout):
+    if layout == _lib.LAYOUT_BTM:
+        t = t.permute(0, 2, 1).contiguous().view(B * M, -1)
+    return t.cpu().numpy()
+
+
+def param(vec_n, mode, B, M):
+    """Pick the representation of a per-neuron vector for `mode`; vec_n has N entries that
+    must already be consistent with the mode (constant / periodic in M / free)."""
+    if vec_n is None:
+        return (None, _lib.PARAM_SCALAR)
+    v = np.asarray(vec_n, np.float32)
+    if mode == _lib.PARAM_SCALAR:
+        v = v[:1]
+    elif mode == _lib.PARAM_PER_M:
+        v = v[:M]
+    return (torch.tensor(np.ascontiguousarray(v), device=DEV), mode)
+
+
+def vec(a):
+    return None if a is None else torch.tensor(np.ascontiguousarray(a, np.float32), device=DEV)
+
+
+def lif_forward(cs, B, M, layout, mode=_lib.PARAM_PER_N, max_spikes=None, reset_mode=_lib.RESET_SUBTRACT,
+                in_scale=None, want_count=True):
+    N, T = cs["inp"].shape
+    x = to_dev(cs["inp"], B, M, layout)
+    spikes = torch.full_like(x, float("nan")); v_mem = torch.full_like(x, float("nan"))
+    v_post = torch.empty(N, device=DEV)
+    count = torch.zeros(1, dtype=torch.int64, device=DEV) if want_count else None
+    _lib.lif_forward(spikes, v_mem, x, vec(cs["v_init"]), param(in_scale, mode, B, M), param(cs["alpha"], mode, B, M),
+                     param(cs["subtract"], mode, B, M), param(cs["theta"], mode, B, M),
+                     param(cs["theta_low"], mode, B, M), max_spikes, reset_mode, v_post, count, B, T, M, layout)
+    torch.cuda.synchronize()
+    return (from_dev(spikes, B, M, layout), from_dev(v_mem, B, M, layout), v_post.cpu().numpy(),
+            int(count.item()) if want_count else None)
+
+
+def lif_backward(cs, v_mem, go, B, M, layout, mode=_lib.PARAM_PER_N, gv=None, g_last=None, surr=None,
+                 kind=_lib.SURR_GENERIC, p0=0.0, p1=0.0, max_spikes=None, reset_mode=_lib.RESET_SUBTRACT,
+                 want_alpha=False, in_scale=None, want_scale=False, want_init=True):
+    N, T = v_mem.shape
+    gi = torch.full((N, T), float("nan"), device=DEV)
+    gi = to_dev(gi.cpu().numpy(), B, M, layout)
+    ga = torch.empty(N, device=DEV) if want_alpha else None
+    g0 = torch.empty(N, device=DEV) if want_init else None
+    gs = torch.empty(N, device=DEV) if want_scale else None
+    _lib.lif_backward(gi, ga, g0, gs, to_dev(go, B, M, layout), to_dev(gv, B, M, layout), vec(g_last),
+                      to_dev(v_mem, B, M, layout), to_dev(surr, B, M, layout), vec(cs["v_init"]),
+                      to_dev(cs["inp"], B, M, layout) if want_scale else None,
+                      param(in_scale, mode, B, M), param(cs["alpha"], mode, B, M), param(cs["subtract"], mode, B, M),
+                      param(cs["theta"], mode, B, M), param(cs["theta_low"], mode, B, M), max_spikes, reset_mode,
+                      kind, p0, p1, B, T, M, layout)
+    torch.cuda.synchronize()
+    cpu = lambda t: None if t is None else t.cpu().numpy()
+    return from_dev(gi, B, M, layout), cpu(ga), cpu(g0), cpu(gs)
+
+
+def leaky_forward(inp, v_init, alpha, B, M, layout, mode=_lib.PARAM_PER_N, in_scale=None):
+    N, T = inp.shape
+    x = to_dev(inp, B, M, layout)
+    out = torch.full_like(x, float("nan"))
+    v_last = torch.empty(N, device=DEV)
+    _lib.leaky_forward(out, x, vec(v_init), param(alpha, mode, B, M), param(in_scale, mode, B, M), v_last,
+                       B, T, M, layout)
+    torch.cuda.synchronize()
+    return from_dev(out, B, M, layout), v_last.cpu().numpy()
+
+
+def leaky_backward(go, alpha, B, M, layout, mode=_lib.PARAM_PER_N, out=None, inp=None, v_init=None, g_last=None,
+                   in_scale=None, want_alpha=False, want_scale=False):
+    N, T = go.shape
+    g = to_dev(go, B, M, layout)
+    gi = torch.full_like(g, float("nan"))
+    ga = torch.empty(N, device=DEV) if want_alpha else None
+    g0 = torch.empty(N, device=DEV)
+    gs = torch.empty(N, device=DEV) if want_scale else None
+    _lib.leaky_backward(gi, ga, g0, gs, g, vec(g_last), to_dev(out, B, M, layout) if want_alpha else None,
+                        to_dev(inp, B, M, layout) if want_scale else None, vec(v_init),
+                        param(alpha, mode, B, M), param(in_scale, mode, B, M), B, T, M, layout)
+    torch.cuda.synchronize()
+    cpu = lambda t: None if t is None else t.cpu().numpy()
+    return from_dev(gi, B, M, layout), cpu(ga), cpu(g0), cpu(gs)

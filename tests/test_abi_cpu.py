@@ -1,0 +1,64 @@
+"""The C-ABI library loads and exports everything ``include/exodus_b200.h`` declares (no GPU needed)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from sinabs_exodus_b200 import build, _lib
+    if not os.path.exists(_lib.LIB_PATH):
+        build.build()
+    return _lib.load()
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "exodus_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(exb_\w+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = declared_symbols()
+    assert len(names) >= 7
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in include/exodus_b200.h but not exported"
+
+
+def test_python_binding_covers_header(lib):
+    from sinabs_exodus_b200 import _lib
+    assert set(declared_symbols()) == set(_lib.EXPORTS)
+
+
+def test_version_and_status_strings(lib):
+    assert b"sm_100a" in lib.exb_version()
+    assert lib.exb_status_string(0) == b"ok"
+    assert lib.exb_status_string(1) == b"invalid argument"
+
+
+def test_argument_validation_without_gpu(lib):
+    """Bad arguments are rejected before any CUDA call is made."""
+    null = None
+    one = ctypes.c_void_p(16)   # never dereferenced: validation fails first
+    st = lib.exb_leaky_forward(null, one, null, one, 0, null, 0, null, 1, 1, 1, 0, 0, null)
+    assert st == 1 and b"required" in lib.exb_last_error()
+    st = lib.exb_leaky_forward(one, one, null, one, 0, null, 0, null, -1, 1, 1, 0, 0, null)
+    assert st == 1 and b"negative" in lib.exb_last_error()
+    st = lib.exb_leaky_forward(one, one, null, one, 7, null, 0, null, 1, 1, 1, 0, 0, null)
+    assert st == 1 and b"mode" in lib.exb_last_error()
+    st = lib.exb_leaky_forward(one, one, null, one, 0, null, 0, null, 1, 1, 1, 9, 0, null)
+    assert st == 1 and b"layout" in lib.exb_last_error()
+    # empty problems are a successful no-op
+    assert lib.exb_leaky_forward(one, one, null, one, 0, null, 0, null, 0, 5, 3, 0, 0, null) == 0
+
+
+def test_missing_library_is_loud(monkeypatch, tmp_path):
+    from sinabs_exodus_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(_lib.ExodusLibraryError):
+        _lib.load()

@@ -1,0 +1,278 @@
+"""Autograd Functions and layers on the GPU against the CPU checker.  Needs a GPU."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from oracle.torch_loop import lif_loop
+from tests._cases import lif_case, near_threshold_rows, rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+
+
+def cu(a, grad=False):
+    return torch.tensor(np.ascontiguousarray(a, np.float32), device="cuda:0", requires_grad=grad)
+
+
+@pytest.mark.parametrize("surrogate", ["single_exp", "heaviside", "periodic", "callable"])
+@pytest.mark.parametrize("backward_var", ["spikes", "vmem", "sum"])
+def test_integrate_and_fire_chained(surrogate, backward_var):
+    """Three chained calls that carry the state, as reference tests/test_spike_functions.py:69-146."""
+    from sinabs_exodus_b200 import IntegrateAndFire
+    from sinabs_exodus_b200.compat import activation as sa
+    fn_gpu, fn_np = {
+        "single_exp": (sa.SingleExponential(), lambda v, th: orc.surrogate_single_exponential(v, th)),
+        "heaviside": (sa.Heaviside(0.5), lambda v, th: orc.surrogate_heaviside(v, th, 0.5)),
+        "periodic": (sa.PeriodicExponential(), lambda v, th: orc.surrogate_periodic_exponential(v, th)),
+        "callable": (lambda v, th: 0.5 / (1.0 + (v - th) ** 2), lambda v, th: (0.5 / (1.0 + (v - th) ** 2)).astype(np.float32)),
+    }[surrogate]
+    N, T, E = 20, 50, 3
+    cs = lif_case(31, N, T * E, clamp=True)
+    max_spikes = 2
+    inp = cu(cs["inp"], True); alpha = cu(cs["alpha"], True); v0 = cu(cs["v_init"], True)
+    theta, c, lo = cu(cs["theta"]), cu(cs["subtract"]), cu(cs["theta_low"])
+    v_state = v0
+    outs, vms = [], []
+    for e in range(E):
+        s, vm = IntegrateAndFire.apply(inp[:, e * T:(e + 1) * T].contiguous(), alpha, v_state, theta, c, lo, fn_gpu, max_spikes)
+        v_state = vm[:, -1] - c * s[:, -1]
+        outs.append(s); vms.append(vm)
+    S = torch.cat(outs, 1); V = torch.cat(vms, 1)
+    s_ref, v_ref = orc.lif_forward(cs["inp"], cs["v_init"], cs["alpha"], cs["subtract"], cs["theta"], cs["theta_low"], max_spikes)
+    np.testing.assert_array_equal(S.detach().cpu().numpy(), s_ref)
+    assert rel_err(V.detach().cpu().numpy(), v_ref) < TOL
+    rng = np.random.default_rng(2)
+    w_s = rng.random((N, T * E)).astype(np.float32); w_v = rng.random((N, T * E)).astype(np.float32)
+    if backward_var == "spikes":
+        w_v[:] = 0
+    elif backward_var == "vmem":
+        w_s[:] = 0
+    (S * cu(w_s) + V * cu(w_v)).sum().backward()
+    gi, ga, g0 = orc.integrate_and_fire_backward(w_s, w_v, v_ref, s_ref, cs["v_init"], cs["alpha"], cs["subtract"],
+                                                 cs["theta"], cs["theta_low"], fn_np, True)
+    surr = fn_np(v_ref, cs["theta"][:, None])
+    nc = (v_ref > cs["theta_low"][:, None]).astype(np.float32)
+    g = (surr * w_s).astype(np.float32) + w_v
+    vpost = (v_ref - cs["subtract"][:, None] * s_ref).astype(np.float32)
+    gi64, ga64 = orc.lif_backward_f64(g, surr, nc, cs["alpha"], cs["subtract"], vpost, cs["v_init"])
+    assert rel_err(inp.grad.cpu().numpy(), gi64) < TOL
+    assert rel_err(v0.grad.cpu().numpy(), cs["alpha"] * gi64[:, 0]) < TOL
+    # the chained alpha gradient equals the single-call one except for the reference's
+    # first-step term, which chained calls apply at every call boundary
+    ok = (nc[:, 0] == 1) & (nc[:, T] == 1) & (nc[:, 2 * T] == 1)
+    assert rel_err(alpha.grad.cpu().numpy()[ok], ga64[ok]) < TOL
+
+
+def test_integrate_and_fire_errors():
+    from sinabs_exodus_b200 import IntegrateAndFire
+    from sinabs_exodus_b200._lib import ExodusLibraryError
+    from sinabs_exodus_b200.compat.activation import Heaviside
+    N, T = 2, 10
+    x = torch.rand(N, T, device="cuda:0"); a = torch.full((N,), 0.9, device="cuda:0"); z = torch.zeros(N, device="cuda:0")
+    th = torch.ones(N, device="cuda:0")
+    fn = Heaviside(0)
+    with pytest.raises(ValueError):
+        IntegrateAndFire.apply(x, a, z, th, th, torch.tensor([1.2, 0.0], device="cuda:0"), fn)   # min_v_mem >= threshold
+    with pytest.raises(ValueError):
+        IntegrateAndFire.apply(x.t(), a, z, th, th, None, fn)                                      # not contiguous
+    with pytest.raises(ValueError):
+        IntegrateAndFire.apply(x[0], a, z, th, th, None, fn)                                       # not 2D
+    with pytest.raises(ValueError):
+        IntegrateAndFire.apply(x, a * 2, z, th, th, None, fn)                                      # alpha > 1
+    with pytest.raises(ExodusLibraryError):
+        IntegrateAndFire.apply(x.cpu(), a.cpu(), z.cpu(), th.cpu(), th.cpu(), None, fn)            # no CPU path
+    s, v = IntegrateAndFire.apply(x, a, z, th, None, None, fn)                                     # subtract=None -> threshold
+    assert s.shape == v.shape == (N, T)
+
+
+def test_leaky_integrator_chained():
+    """Reference tests/test_leak_functions.py:28-75: forward, input, initial-state and alpha gradients."""
+    from sinabs_exodus_b200 import LeakyIntegrator
+    N, T, E = 24, 64, 3
+    rng = np.random.default_rng(1)
+    x_np = rng.random((N, T * E)).astype(np.float32)
+    a_np = rng.uniform(0.2, 1.0, N).astype(np.float32); v0_np = rng.standard_normal(N).astype(np.float32)
+    w_np = rng.random((N, T * E)).astype(np.float32)
+    x, alpha, v0 = cu(x_np, True), cu(a_np, True), cu(v0_np, True)
+    state = v0
+    outs = []
+    for e in range(E):
+        o = LeakyIntegrator.apply(x[:, e * T:(e + 1) * T].contiguous(), alpha, state)
+        state = o[:, -1]
+        outs.append(o)
+    O = torch.cat(outs, 1)
+    (O * cu(w_np)).sum().backward()
+    assert rel_err(O.detach().cpu().numpy(), orc.leaky_forward_f64(x_np, v0_np, a_np)) < TOL
+    gi64, ag64 = orc.leaky_backward_f64(w_np, a_np, x_np, v0_np)
+    assert rel_err(x.grad.cpu().numpy(), gi64) < TOL
+    assert rel_err(alpha.grad.cpu().numpy(), ag64) < 2 * TOL
+    assert rel_err(v0.grad.cpu().numpy(), a_np * gi64[:, 0]) < TOL
+    with pytest.raises(ValueError):
+        LeakyIntegrator.apply(x.t(), alpha, v0)
+
+
+def _loop_ref(layer_kwargs, x_np, **loop_kwargs):
+    """CPU ground truth for a layer call: time-stepped loop + autograd."""
+    x = torch.tensor(x_np, requires_grad=True)
+    res = lif_loop(x, **loop_kwargs)
+    return x, res
+
+
+def test_layer_lif_config1():
+    """BASELINE config 1: LIF(tau_mem=20, threshold 1, subtract, MultiSpike, SingleExponential(0.5), min_v_mem=-1),
+    input (8,100,128) ~ N(0.3,0.5) seed 0, upstream gradient of ones."""
+    from sinabs_exodus_b200.layers import LIF
+    from sinabs_exodus_b200.compat.activation import SingleExponential
+    torch.manual_seed(0)
+    x_cpu = 0.3 + 0.5 * torch.randn(8, 100, 128)
+    layer = LIF(tau_mem=20.0, spike_threshold=1.0, surrogate_grad_fn=SingleExponential(grad_width=0.5), min_v_mem=-1.0).cuda()
+    x = x_cpu.cuda().requires_grad_(True)
+    out = layer(x)
+    out.sum().backward()
+    assert out.shape == x.shape and out.is_contiguous()
+    assert "EXODUS" in repr(layer)
+    # ground truth
+    tau = torch.tensor(20.0, requires_grad=True)
+    alpha = torch.exp(-1.0 / tau)
+    xr = x_cpu.clone().requires_grad_(True)
+    res = lif_loop(xr, alpha, torch.zeros(8, 128), torch.tensor(1.0), torch.tensor(1.0), torch.tensor(-1.0),
+                   SingleExponential(grad_width=0.5), None, norm_input=True)
+    res["spikes"].sum().backward()
+    v_ref = res["v_mem_pre"].detach().permute(0, 2, 1).reshape(-1, 100).numpy()
+    safe = ~near_threshold_rows(v_ref, np.ones(v_ref.shape[0], np.float32))
+    s_gpu = out.detach().cpu().permute(0, 2, 1).reshape(-1, 100).numpy()
+    s_ref = res["spikes"].detach().permute(0, 2, 1).reshape(-1, 100).numpy()
+    np.testing.assert_array_equal(s_gpu[safe], s_ref[safe])
+    assert safe.mean() > 0.95
+    g_gpu = x.grad.cpu().permute(0, 2, 1).reshape(-1, 100).numpy()
+    g_ref = xr.grad.permute(0, 2, 1).reshape(-1, 100).numpy()
+    assert rel_err(g_gpu[safe], g_ref[safe]) < 1e-4
+    assert abs(layer.tau_mem.grad.item() - tau.grad.item()) <= 1e-3 * abs(tau.grad.item()) + 1e-6
+    np.testing.assert_allclose(layer.firing_rate.item(), s_ref.mean(), rtol=1e-3)
+    np.testing.assert_allclose(layer.v_mem.detach().cpu().numpy()[safe.reshape(8, 128)],
+                               res["v_last"].detach().numpy()[safe.reshape(8, 128)], rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("train_alphas", [False, True])
+@pytest.mark.parametrize("norm_input", [False, True])
+def test_layer_lif_synaptic_gradients(train_alphas, norm_input):
+    """LIF with synaptic stage, per-neuron time constants, non-zero states, two chained calls."""
+    from sinabs_exodus_b200.layers import LIF
+    from sinabs_exodus_b200.compat.activation import PeriodicExponential, SingleSpike
+    B, T, M = 4, 40, 12
+    rng = np.random.default_rng(3)
+    tau_mem = torch.tensor(rng.uniform(10, 40, M).astype(np.float32))
+    x_np = (0.2 + 0.6 * rng.standard_normal((2, B, T, M))).astype(np.float32)
+    fn = PeriodicExponential()
+    layer = LIF(tau_mem=tau_mem.clone(), tau_syn=10.0, spike_fn=SingleSpike, surrogate_grad_fn=fn, min_v_mem=-1.0,
+                train_alphas=train_alphas, norm_input=norm_input, record_states=True).cuda()
+    w = torch.tensor(rng.standard_normal((B, T, M)).astype(np.float32))
+    xs = [torch.tensor(x_np[e], device="cuda:0", requires_grad=True) for e in range(2)]
+    loss = 0
+    for e in range(2):
+        out = layer(xs[e])
+        loss = loss + (out * w.cuda()).sum()
+    loss.backward()
+    assert set(layer.recordings) == {"i_syn", "v_mem"}
+
+    # ground truth with the same parameterisation
+    if train_alphas:
+        p_mem = torch.exp(-1 / tau_mem).clone().requires_grad_(True); a_mem = p_mem
+        p_syn = torch.exp(-1 / torch.tensor(10.0)).clone().requires_grad_(True); a_syn = p_syn
+    else:
+        p_mem = tau_mem.clone().requires_grad_(True); a_mem = torch.exp(-1 / p_mem)
+        p_syn = torch.tensor(10.0, requires_grad=True); a_syn = torch.exp(-1 / p_syn)
+    xr = [torch.tensor(x_np[e], requires_grad=True) for e in range(2)]
+    v, i = torch.zeros(B, M), torch.zeros(B, M)
+    loss_r = 0
+    all_v = []
+    for e in range(2):
+        res = lif_loop(xr[e], a_mem, v, torch.tensor(1.0), torch.tensor(1.0), torch.tensor(-1.0), fn, 1,
+                       alpha_syn=a_syn, i_syn_init=i, norm_input=norm_input, decay_early=True)
+        v, i = res["v_last"], res["i_last"]
+        loss_r = loss_r + (res["spikes"] * w).sum()
+        all_v.append(res["v_mem_pre"].detach())
+        last = res
+    loss_r.backward()
+    v_rows = torch.cat(all_v, 1).permute(0, 2, 1).reshape(B * M, -1).numpy()
+    safe = ~near_threshold_rows(v_rows, np.ones(B * M, np.float32), rel=1e-4)
+    safe_bm = torch.tensor(safe.reshape(B, M))
+    for e in range(2):
+        g_gpu = xs[e].grad.cpu().permute(0, 2, 1)[safe_bm].numpy()
+        g_ref = xr[e].grad.permute(0, 2, 1)[safe_bm].numpy()
+        assert rel_err(g_gpu, g_ref) < 1e-4
+    if safe.all():
+        p_gpu_mem = (layer.alpha_mem if train_alphas else layer.tau_mem).grad.cpu().numpy()
+        p_gpu_syn = (layer.alpha_syn if train_alphas else layer.tau_syn).grad.cpu().numpy()
+        assert rel_err(p_gpu_mem, p_mem.grad.numpy()) < 1e-3
+        assert rel_err(p_gpu_syn, p_syn.grad.numpy()) < 1e-3
+    np.testing.assert_allclose(layer.recordings["i_syn"].detach().cpu().numpy(), last["i_syn"].detach().numpy(),
+                               rtol=1e-4, atol=1e-5)
+
+
+def test_layer_iaf_squeeze_and_state():
+    """IAFSqueeze on (B*T, C, H, W); state is carried between calls and reset_states clears it."""
+    from sinabs_exodus_b200.layers import IAF, IAFSqueeze
+    from sinabs_exodus_b200.compat.activation import Heaviside
+    B, T, C, H, W = 2, 20, 3, 4, 5
+    torch.manual_seed(1)
+    x = (0.4 * torch.poisson(torch.full((B, T, C, H, W), 0.4))).cuda()
+    sq = IAFSqueeze(batch_size=B, surrogate_grad_fn=Heaviside()).cuda()
+    plain = IAF(surrogate_grad_fn=Heaviside()).cuda()
+    out_sq = sq(x.reshape(B * T, C, H, W))
+    out = plain(x)
+    assert out_sq.shape == (B * T, C, H, W)
+    torch.testing.assert_close(out_sq.reshape(B, T, C, H, W), out)
+    # charge conservation of IAF with subtract = threshold, no clamp: sum(in) = v_post + sum(spikes)
+    total_in = x.sum(1)
+    torch.testing.assert_close(plain.v_mem + out.sum(1), total_in, rtol=1e-4, atol=1e-4)
+    v_before = plain.v_mem.clone()
+    out2 = plain(x)
+    assert not torch.equal(plain.v_mem, v_before) or torch.equal(out2, out)
+    plain.reset_states()
+    assert (plain.v_mem == 0).all()
+    torch.testing.assert_close(plain(x), out)
+
+
+@pytest.mark.parametrize("train_alphas", [False, True])
+@pytest.mark.parametrize("norm_input", [False, True])
+@pytest.mark.parametrize("decay_early", [False, True])
+def test_layer_exp_leak(train_alphas, norm_input, decay_early):
+    from sinabs_exodus_b200.layers import ExpLeak
+    B, T, M = 3, 60, 10
+    rng = np.random.default_rng(6)
+    x_np = rng.standard_normal((B, T, M)).astype(np.float32)
+    w_np = rng.standard_normal((B, T, M)).astype(np.float32)
+    layer = ExpLeak(tau_mem=30.0, train_alphas=train_alphas, norm_input=norm_input, decay_early=decay_early).cuda()
+    x = torch.tensor(x_np, device="cuda:0", requires_grad=True)
+    out = layer(x)
+    (out * torch.tensor(w_np, device="cuda:0")).sum().backward()
+    if train_alphas:
+        p = torch.exp(torch.tensor(-1 / 30.0)).clone().requires_grad_(True); a = p
+    else:
+        p = torch.tensor(30.0, requires_grad=True); a = torch.exp(-1 / p)
+    xr = torch.tensor(x_np, requires_grad=True)
+    res = lif_loop(xr, a, torch.zeros(B, M), spiking=False, norm_input=norm_input, decay_early=decay_early)
+    (res["v_mem_pre"] * torch.tensor(w_np)).sum().backward()
+    assert rel_err(out.detach().cpu().numpy(), res["v_mem_pre"].detach().numpy()) < TOL
+    assert rel_err(x.grad.cpu().numpy(), xr.grad.numpy()) < TOL
+    g = (layer.alpha_mem if train_alphas else layer.tau_mem).grad.item()
+    assert abs(g - p.grad.item()) <= 1e-4 * abs(p.grad.item()) + 1e-6
+    # decay_early relation (reference tests/test_exp_leak.py:23-37)
+    if decay_early and not norm_input:
+        other = ExpLeak(tau_mem=30.0, decay_early=False).cuda()
+        torch.testing.assert_close(out.detach(), other(x.detach()) * float(np.exp(-1 / 30.0)), rtol=1e-5, atol=1e-6)
+
+
+def test_layer_rejects_cpu_and_bad_config():
+    from sinabs_exodus_b200._lib import ExodusLibraryError
+    from sinabs_exodus_b200.layers import LIF
+    layer = LIF(tau_mem=10.0)
+    with pytest.raises(ExodusLibraryError):
+        layer(torch.zeros(1, 4, 3))
+    with pytest.raises(NotImplementedError):
+        LIF(tau_mem=10.0, spike_fn=lambda *a: None)
+    bad = LIF(tau_mem=10.0, min_v_mem=2.0).cuda()
+    with pytest.raises(ValueError):
+        bad(torch.zeros(1, 4, 3, device="cuda:0"))
