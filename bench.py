@@ -1,0 +1,485 @@
+"""Benchmark of the neuron hot path: neuron-timesteps per second, forward + backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl ours|reference]
+
+One "step" is one forward + backward pass of one layer over one batch of
+synthetic input (the configurations of BASELINE.json; default ``c2``, the IAF
+layer on conv feature maps).  With N > 1 the script is launched by torchrun, one
+rank per GPU; every rank owns its own batch shard of the same size (weak scaling)
+and the only collective is the allreduce of time-constant gradients (``c4``).
+
+Rank 0 prints ONE JSON line:
+* ``value``        whole-job neuron-timesteps/s with inputs resident in HBM, device-timed
+                   (CUDA events, max over ranks)
+* ``roofline``     the dominant kernel's algorithmic bytes / its event-timed duration
+                   against the measured HBM copy bandwidth
+* ``e2e``          the same metric through the public layer API with pinned HOST buffers:
+                   input and upstream gradient copied in, spikes and input gradient copied out,
+                   every step, inside the timed region
+* ``cpu_baseline`` a time-stepped PyTorch layer loop (the stand-in for sinabs' CPU layers,
+                   which are not installed) on the host cores, on a bounded sample
+
+``--impl reference`` times that CPU loop alone, on the same workload definition.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np
+import torch
+
+METRIC = "neuron_timesteps_per_s_fwd_bwd"
+UNIT = "nts/s"
+
+
+# --------------------------------------------------------------------------
+# workloads (BASELINE.json configs; shapes are per GPU)
+# --------------------------------------------------------------------------
+WORKLOADS = {
+    "c1": dict(desc="LIF tau_mem=20 thr=1 subtract MultiSpike SingleExponential(0.5) min_v_mem=-1, "
+                    "input (8,100,128) N(0.3,0.5) seed 0, grad ones",
+               shape=(8, 100, 128), kind="lif", bytes_fwd=12, bytes_bwd=12),
+    "c2": dict(desc="IAF thr=1 subtract MultiSpike Heaviside, input (32,300,32,34,34) = 0.4*Poisson(0.1) seed 1, "
+                    "grad N(0,1)",
+               shape=(32, 300, 32, 34, 34), kind="iaf", bytes_fwd=12, bytes_bwd=12),
+    "c3": dict(desc="ExpLeak tau_mem=50 shared, input (64,4000,512) N(0,1) seed 2, grad N(0,1)",
+               shape=(64, 4000, 512), kind="expleak", bytes_fwd=8, bytes_bwd=8),
+    "c4": dict(desc="LIF tau_syn=10 + per-neuron tau_mem~U(10,40), train_alphas, SingleSpike, reset to zero, "
+                    "PeriodicExponential, input (128,500,1024) N(0.2,0.6) seed 3, grad N(0,1)",
+               shape=(128, 500, 1024), kind="lif_syn", bytes_fwd=16, bytes_bwd=16),
+    "c5": dict(desc="LIF tau_mem=20 subtract MultiSpike SingleExponential, input (32,500,64,64,64) per GPU "
+                    "N(0.25,0.5), grad N(0,1)",
+               shape=(32, 500, 64, 64, 64), kind="lif5", bytes_fwd=12, bytes_bwd=12),
+}
+
+
+def make_layer(kind: str, neurons_shape, device):
+    import sinabs_exodus_b200.layers as el
+    from sinabs_exodus_b200.compat import activation as sa
+
+    if kind == "lif":
+        layer = el.LIF(tau_mem=20.0, spike_threshold=1.0, surrogate_grad_fn=sa.SingleExponential(grad_width=0.5),
+                       min_v_mem=-1.0)
+    elif kind == "iaf":
+        layer = el.IAF(spike_threshold=1.0, surrogate_grad_fn=sa.Heaviside())
+    elif kind == "expleak":
+        layer = el.ExpLeak(tau_mem=50.0)
+    elif kind == "lif_syn":
+        g = torch.Generator().manual_seed(3)
+        tau = 10.0 + 30.0 * torch.rand(neurons_shape, generator=g)
+        layer = el.LIF(tau_mem=tau, tau_syn=10.0, train_alphas=True, spike_fn=sa.SingleSpike,
+                       reset_fn=sa.MembraneReset(0.0), surrogate_grad_fn=sa.PeriodicExponential())
+    elif kind == "lif5":
+        layer = el.LIF(tau_mem=20.0, surrogate_grad_fn=sa.SingleExponential())
+    else:
+        raise ValueError(kind)
+    return layer.to(device)
+
+
+def make_input(name: str, shape, device, rank: int, batch=None):
+    """Seeded synthetic input and upstream gradient with the configuration's value distribution."""
+    seed = {"c1": 0, "c2": 1, "c3": 2, "c4": 3, "c5": 100}[name] + (rank if name != "c5" else rank)
+    shape = tuple(shape) if batch is None else (batch,) + tuple(shape[1:])
+    g = torch.Generator(device=device).manual_seed(seed)
+    if name == "c2":
+        x = torch.empty(shape, device=device)
+        for b in range(shape[0]):      # per item: keeps the temporary small
+            x[b] = 0.4 * torch.poisson(torch.full(shape[1:], 0.1, device=device), generator=g)
+    else:
+        mean, std = {"c1": (0.3, 0.5), "c3": (0.0, 1.0), "c4": (0.2, 0.6), "c5": (0.25, 0.5)}[name]
+        x = torch.empty(shape, device=device).normal_(mean, std, generator=g)
+    g2 = torch.Generator(device=device).manual_seed(seed + 1000)
+    grad = torch.ones(shape, device=device) if name == "c1" else torch.empty(shape, device=device).normal_(0, 1, generator=g2)
+    return x, grad
+
+
+# --------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while a region runs."""
+
+    FIELDS = ("uuid,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.rows = []
+        self.proc = None
+        try:
+            uuid = torch.cuda.get_device_properties(device_index).uuid
+            self.uuid = "GPU-" + str(uuid) if not str(uuid).startswith("GPU-") else str(uuid)
+        except Exception:
+            self.uuid = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for row in self.rows:
+            parts = [p.strip() for p in row.split(",")]
+            if len(parts) < 8 or (self.uuid and parts[0] != self.uuid):
+                continue
+            try:
+                sm.append(float(parts[1])); smax.append(float(parts[2])); power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[4:8]):
+                if val == "Active":
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------
+# kernel event timing: wraps the C-ABI calls with CUDA events on the launch stream
+# --------------------------------------------------------------------------
+class KernelTimer:
+    NAMES = ("lif_forward", "lif_backward", "leaky_forward", "leaky_backward")
+
+    def __init__(self):
+        from sinabs_exodus_b200 import _lib
+        self.lib = _lib
+        self.orig = {n: getattr(_lib, n) for n in self.NAMES}
+        self.events = {n: [] for n in self.NAMES}
+        self.enabled = False
+        for n in self.NAMES:
+            setattr(_lib, n, self._wrap(n))
+
+    def _wrap(self, name):
+        orig = self.orig[name]
+
+        def call(*args, **kwargs):
+            if not self.enabled:
+                return orig(*args, **kwargs)
+            s = torch.cuda.Event(enable_timing=True); e = torch.cuda.Event(enable_timing=True)
+            s.record()                       # torch's current stream == the stream the kernel is launched on
+            orig(*args, **kwargs)
+            e.record()
+            self.events[name].append((s, e))
+        return call
+
+    def launches(self):
+        return sum(len(v) for v in self.events.values())
+
+    def summary(self):
+        out = {}
+        for n, evs in self.events.items():
+            if evs:
+                ms = [s.elapsed_time(e) for s, e in evs]
+                out[n] = {"launches": len(ms), "avg_ms": sum(ms) / len(ms), "min_ms": min(ms)}
+        return out
+
+    def reset(self):
+        self.events = {n: [] for n in self.NAMES}
+
+
+# --------------------------------------------------------------------------
+# CPU arm: time-stepped PyTorch layer loop on the host cores
+# --------------------------------------------------------------------------
+def cpu_step(name: str, kind: str, x: torch.Tensor, grad: torch.Tensor):
+    """One forward+backward of the time-stepped PyTorch loop on CPU tensors (layer semantics of `kind`)."""
+    from oracle.torch_loop import lif_loop
+    from sinabs_exodus_b200.compat import activation as sa
+
+    B, T = x.shape[:2]
+    xr = x.reshape(B, T, -1).clone().requires_grad_(True)
+    M = xr.shape[2]
+    zeros = torch.zeros(B, M)
+    one = torch.tensor(1.0)
+    if kind == "lif":
+        tau = torch.tensor(20.0, requires_grad=True)
+        res = lif_loop(xr, torch.exp(-1 / tau), zeros, one, one, torch.tensor(-1.0), sa.SingleExponential(0.5), None,
+                       norm_input=True)
+        out = res["spikes"]
+    elif kind == "iaf":
+        res = lif_loop(xr, torch.tensor(1.0), zeros, one, one, None, sa.Heaviside(), None)
+        out = res["spikes"]
+    elif kind == "expleak":
+        tau = torch.tensor(50.0, requires_grad=True)
+        res = lif_loop(xr, torch.exp(-1 / tau), zeros, spiking=False, decay_early=False)
+        out = res["v_mem_pre"]
+    elif kind == "lif_syn":
+        g = torch.Generator().manual_seed(3)
+        a_mem = torch.exp(-1 / (10.0 + 30.0 * torch.rand(M, generator=g))).requires_grad_(True)
+        a_syn = torch.exp(torch.tensor(-1 / 10.0)).requires_grad_(True)
+        res = lif_loop(xr, a_mem, zeros, one, None, None, sa.PeriodicExponential(), 1, reset_value=0.0,
+                       alpha_syn=a_syn, i_syn_init=zeros, norm_input=True, decay_early=True)
+        out = res["spikes"]
+    else:
+        tau = torch.tensor(20.0, requires_grad=True)
+        res = lif_loop(xr, torch.exp(-1 / tau), zeros, one, one, None, sa.SingleExponential(), None, norm_input=True)
+        out = res["spikes"]
+    out.backward(grad.reshape(B, T, -1))
+    return xr.grad
+
+
+def cpu_sample(name: str, wl: dict, budget_s: float, steps: int, warmup: int):
+    """Times `steps` CPU steps on a batch/neuron sample sized to fit `budget_s` in total.
+    Returns (nts_per_s, sample description, cores, ms_per_step)."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    shape = wl["shape"]
+    B, T = shape[0], shape[1]
+    M = int(np.prod(shape[2:]))
+    # calibrate on a small neuron slice of one batch item
+    m0 = min(M, 4096)
+    x, g = make_input(name, (1, T, m0), "cpu", 0)
+    t0 = time.perf_counter(); cpu_step(name, wl["kind"], x, g); dt = time.perf_counter() - t0
+    t0 = time.perf_counter(); cpu_step(name, wl["kind"], x, g); dt = min(dt, time.perf_counter() - t0)
+    rate = T * m0 / dt                                    # nts/s at small size (pessimistic for large)
+    per_step = budget_s / max(1, steps + warmup)
+    want = max(T * m0, rate * per_step)                   # nts per step that fit the budget
+    neurons = int(min(B * M, max(m0, want // T)))
+    b = max(1, min(B, neurons // M)) if neurons >= M else 1
+    m = M if neurons >= M else max(1, neurons)
+    x, g = make_input(name, (b, T, m), "cpu", 0)
+    for _ in range(warmup):
+        cpu_step(name, wl["kind"], x, g)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_step(name, wl["kind"], x, g)
+    dt = time.perf_counter() - t0
+    nts = b * m * T * steps
+    sample = f"{steps} fwd+bwd steps of a time-stepped PyTorch loop on batch {b} x {m} neurons x {T} steps of {name}"
+    return nts / dt, sample, cores, dt / steps * 1e3
+
+
+# --------------------------------------------------------------------------
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return 6650.0, "fallback (earlier pool measurement)"
+
+
+def run_reference(args, wl):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    value, sample, cores, ms = cpu_sample(args.workload, wl, args.cpu_seconds_reference, args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {wl['desc']}", "note": "CPU arm runs a bounded sample per step"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, wl):
+    import torch.distributed as dist
+    import sinabs_exodus_b200 as ex
+    from sinabs_exodus_b200 import distributed as exd
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ex._lib.load()
+
+    name = args.workload
+    shape = wl["shape"]
+    B, T = shape[0], shape[1]
+    M = int(np.prod(shape[2:]))
+    layer = make_layer(wl["kind"], shape[2:], dev)
+    x, grad = make_input(name, shape, dev, rank)
+    x.requires_grad_(True)
+    tc_params = exd.time_constant_parameters(layer)
+
+    def step():
+        layer.zero_grad(set_to_none=True)
+        x.grad = None
+        layer.reset_states()
+        out = layer(x)
+        out.backward(grad)
+        if world > 1 and tc_params:
+            exd.allreduce_gradients(tc_params)
+        return out
+
+    timer = KernelTimer()
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+
+    # ---- timed region: K steps, device-timed, barrier + synchronize on both sides
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    timer.enabled = True
+    ev0 = torch.cuda.Event(enable_timing=True); ev1 = torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    torch.cuda.synchronize()
+    timer.enabled = False
+    if world > 1:
+        dist.barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    t = torch.tensor([ms_total], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    launches = timer.launches()
+    kernels = timer.summary()
+    nts_step = B * T * M
+    value = nts_step * world * args.steps / (ms_total * 1e-3)
+
+    # ---- end to end with host buffers (public layer API; copies inside the timed region)
+    e2e = None
+    if not args.no_e2e:
+        timer.reset()
+        xh = torch.empty(shape, pin_memory=True); xh.copy_(x.detach())
+        gh = torch.empty(shape, pin_memory=True); gh.copy_(grad)
+        oh = torch.empty(shape, pin_memory=True); gih = torch.empty(shape, pin_memory=True)
+        xd = torch.empty(shape, device=dev, requires_grad=True)
+        gd = torch.empty(shape, device=dev)
+
+        def e2e_step():
+            layer.zero_grad(set_to_none=True)
+            xd.grad = None
+            layer.reset_states()
+            with torch.no_grad():
+                xd.copy_(xh, non_blocking=True)
+                gd.copy_(gh, non_blocking=True)
+            out = layer(xd)
+            out.backward(gd)
+            if world > 1 and tc_params:
+                exd.allreduce_gradients(tc_params)
+            oh.copy_(out.detach(), non_blocking=True)
+            gih.copy_(xd.grad, non_blocking=True)
+
+        k_e2e = max(3, min(args.steps, args.e2e_steps))
+        for _ in range(2):
+            e2e_step()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(k_e2e):
+            e2e_step()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        te = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        bytes_t = nts_step * 4
+        e2e = {"value": nts_step * world * k_e2e / (float(te.item()) * 1e-3), "unit": UNIT,
+               "h2d_bytes_per_step": 2 * bytes_t, "d2h_bytes_per_step": 2 * bytes_t, "steps": k_e2e,
+               "ms_per_step": float(te.item()) / k_e2e,
+               "what": "layer forward+backward; input and upstream gradient copied from pinned host memory, "
+                       "spikes/output and input gradient copied back, every step"}
+        del xh, gh, oh, gih, xd, gd
+
+    clocks = sampler.stop() if sampler else None
+
+    if rank == 0:
+        peak, peak_src = measured_peak_gbs()
+        # dominant kernel = largest total time; bytes per launch = bytes/nts of that pass * nts per launch
+        per_kernel_bytes = {
+            "lif_forward": 12, "lif_backward": 12, "leaky_forward": 8, "leaky_backward": 8,
+        }
+        if wl["kind"] in ("lif", "lif5"):        # trainable tau: alpha and scale gradients read the input too
+            per_kernel_bytes["lif_backward"] = 12
+        roof = None
+        if kernels:
+            dom = max(kernels, key=lambda k: kernels[k]["avg_ms"] * kernels[k]["launches"])
+            bts = per_kernel_bytes[dom] * nts_step
+            ach = bts / (kernels[dom]["avg_ms"] * 1e-3) / 1e9
+            roof = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                    "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": bts,
+                    "avg_launch_ms": kernels[dom]["avg_ms"],
+                    "all_kernels": {k: dict(v, gbs=per_kernel_bytes[k] * nts_step / (v["avg_ms"] * 1e-3) / 1e9)
+                                    for k, v in kernels.items()}}
+        step_bytes = (wl["bytes_fwd"] + wl["bytes_bwd"]) * nts_step
+        cpu = None
+        if not args.no_cpu:
+            v, sample, cores, _ = cpu_sample(name, wl, args.cpu_seconds, 3, 1)
+            cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{name}: {wl['desc']}", "per_gpu_shape": list(shape),
+                       "l2": f"each tensor is {nts_step * 4 / 1e6:.0f} MB (L2 is 126 MB); no flush between steps",
+                       "parallelism": f"batch-sharded x{world}", "api": "sinabs_exodus_b200.layers"},
+            "step_fraction_of_hbm_roofline": (step_bytes / (ms_total / args.steps * 1e-3) / 1e9) / peak,
+            "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the cpu_baseline leg")
+    ap.add_argument("--cpu-seconds-reference", type=float, default=120.0, help="budget of --impl reference")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, wl)
+    else:
+        run_ours(args, wl)
+
+
+if __name__ == "__main__":
+    main()

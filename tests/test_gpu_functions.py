@@ -99,7 +99,7 @@ def test_leaky_integrator_chained():
     outs = []
     for e in range(E):
         o = LeakyIntegrator.apply(x[:, e * T:(e + 1) * T].contiguous(), alpha, state)
-        state = o[:, -1]
+        state = o[:, -1].contiguous()
         outs.append(o)
     O = torch.cat(outs, 1)
     (O * cu(w_np)).sum().backward()

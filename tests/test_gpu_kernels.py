@@ -272,10 +272,7 @@ def test_golden_vectors_gpu():
                 s, v, _, _ = _gpu.lif_forward(cs, 1, N, layout, 2, ms)
                 np.testing.assert_array_equal(v, g["ref_v_mem"])
                 np.testing.assert_array_equal(s, g["ref_spikes"])
-                gi, ga, _, _ = _gpu.lif_backward(cs, g["ref_v_mem"], g["g"], 1, N, layout, surr=g["surr"], max_spikes=ms,
-                                                 want_alpha=True, gv=None)
-                # g already contains surr*go+gv: feed it as grad_v_mem-only problem is not possible with the
-                # generic surrogate (g = surr*go + gv), so compare through go' = 0, gv' = g
+                # the stored g already is surr*go + gv: feed it as go' = 0, gv' = g
                 gi, ga, _, _ = _gpu.lif_backward(cs, g["ref_v_mem"], np.zeros_like(g["g"]), 1, N, layout, gv=g["g"],
                                                  surr=g["surr"], max_spikes=ms, want_alpha=True)
                 assert rel_err(gi, g["ref_grad_input"]) < TOL
