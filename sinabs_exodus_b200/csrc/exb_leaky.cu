@@ -148,24 +148,30 @@ struct ScanPowers {
     float bwd;      // alpha^(E*(31-lane))
 };
 
+// The powers are formed in double and rounded once: a float power built by
+// repeated squaring carries tens of ulps, which the carry chain of a long,
+// slowly decaying row (alpha close to 1) would accumulate segment by segment.
 template <int E>
 __device__ __forceinline__ ScanPowers scan_powers(float alpha, int lane)
 {
     ScanPowers p;
     p.a = alpha;
-    float aE = alpha;
+    double pw[5];
+    double aE = (double)alpha;
 #pragma unroll
-    for (int e = 1; e < E; ++e) aE = __fmul_rn(aE, alpha);
-    p.pw[0] = aE;
+    for (int e = 1; e < E; ++e) aE *= (double)alpha;
+    pw[0] = aE;
 #pragma unroll
-    for (int d = 1; d < 5; ++d) p.pw[d] = __fmul_rn(p.pw[d - 1], p.pw[d - 1]);
-    p.fwd = 1.0f;
-    p.bwd = 1.0f;
+    for (int d = 1; d < 5; ++d) pw[d] = pw[d - 1] * pw[d - 1];
+    double f = 1.0, b = 1.0;
 #pragma unroll
     for (int d = 0; d < 5; ++d) {
-        if (lane & (1 << d)) p.fwd = __fmul_rn(p.fwd, p.pw[d]);
-        if ((31 - lane) & (1 << d)) p.bwd = __fmul_rn(p.bwd, p.pw[d]);
+        p.pw[d] = (float)pw[d];
+        if (lane & (1 << d)) f *= pw[d];
+        if ((31 - lane) & (1 << d)) b *= pw[d];
     }
+    p.fwd = (float)f;
+    p.bwd = (float)b;
     return p;
 }
 

@@ -157,15 +157,7 @@ class LIF(LIFBase):
         else:
             reset_mode = _lib.RESET_SUBTRACT
             subtract = _flat_param(self.reset_fn.subtract_value, trailing, batch, dev)
-        with torch.no_grad():
-            a = alpha_mem.detach()
-            if bool(((a < 0) | (a > 1)).any()):
-                raise ValueError("'alpha' must be between 0 and 1.")
-            if self.min_v_mem is not None:
-                th = torch.as_tensor(self.spike_threshold, dtype=torch.float32, device=dev)
-                lo = torch.as_tensor(self.min_v_mem, dtype=torch.float32, device=dev)
-                if bool((th <= lo).any()):
-                    raise ValueError("`threshold` must be greater than `min_v_mem`.")
+        self._validate_once(alpha_mem, dev)
         count = torch.zeros(1, dtype=torch.int64, device=dev)
         spikes, v_pre, v_post_last = IntegrateAndFireTM.apply(
             i_syn, alpha_mem, self.v_mem.reshape(-1), threshold, subtract, min_v_mem, scale,
@@ -180,6 +172,27 @@ class LIF(LIFBase):
         else:
             v_rec = None
         return spikes, v_rec, v_post_last, count
+
+    def _validate_once(self, alpha_mem: torch.Tensor, dev) -> None:
+        """Value checks of the reference Function (``spike.py:183,190``): 0 <= alpha <= 1 and
+        threshold > min_v_mem.  Each check reads a result back from the GPU, which stalls the
+        launch queue, so the outcome is remembered until one of the inputs changes."""
+        def stamp(t):
+            return (id(t), t._version) if isinstance(t, torch.Tensor) else t
+        sources = [getattr(self, n, None) for n in ("tau_mem", "alpha_mem")]
+        key = (str(dev),) + tuple(stamp(t) for t in sources) + (stamp(self.spike_threshold), stamp(self.min_v_mem))
+        if getattr(self, "_validated_key", None) == key:
+            return
+        with torch.no_grad():
+            a = alpha_mem.detach()
+            if bool(((a < 0) | (a > 1)).any()):
+                raise ValueError("'alpha' must be between 0 and 1.")
+            if self.min_v_mem is not None:
+                th = torch.as_tensor(self.spike_threshold, dtype=torch.float32, device=dev)
+                lo = torch.as_tensor(self.min_v_mem, dtype=torch.float32, device=dev)
+                if bool((th <= lo).any()):
+                    raise ValueError("`threshold` must be greater than `min_v_mem`.")
+        self._validated_key = key
 
     def forward(self, input_data: torch.Tensor):
         """``input_data``: (batch, time, ...) on a CUDA device.  Returns a tensor of the same shape."""
