@@ -3,8 +3,9 @@
  *
  * libexodus_b200.so replaces the pybind11 module `exodus_cuda` of the
  * reference (cuda/bindings.cu:362-373).  Every entry point takes raw device
- * pointers and sizes, launches on the stream it is given, allocates nothing,
- * keeps no state between calls and returns an int status (0 = EXB_OK).  No
+ * pointers and sizes, launches on the stream it is given, allocates nothing
+ * and returns an int status (0 = EXB_OK).  The only state kept between calls
+ * is one device status word (see exb_device_status).  No
  * exception crosses this boundary; exb_last_error() gives the text of the
  * calling thread's most recent failure.
  *
@@ -62,6 +63,14 @@ enum { EXB_SURR_GENERIC = 0, EXB_SURR_SINGLE_EXPONENTIAL = 1, EXB_SURR_HEAVISIDE
 const char *exb_version(void);
 const char *exb_last_error(void);
 const char *exb_status_string(int status);
+
+/* Kernels that stage data through TMA wait on shared-memory barriers; every such
+ * wait is bounded.  If one ever runs out, the kernel records it in a device
+ * status word and returns normally.  exb_device_status waits for `stream`,
+ * returns EXB_ERR_TIMEOUT if that happened since the last query (and clears the
+ * word), EXB_OK otherwise.  No counterpart in the reference, whose kernels
+ * never wait (cuda/lif_kernels.h, cuda/leaky_kernels.h). */
+int exb_device_status(int device, void *stream);
 
 /* Forward spike scan.  Replaces lifForward (cuda/bindings.cu:14-70, kernel
  * cuda/lif_kernels.h:40-93).  Per neuron and step:

@@ -36,7 +36,7 @@ _f = ctypes.c_float
 _lib: Optional[ctypes.CDLL] = None
 
 EXPORTS = (
-    "exb_version", "exb_last_error", "exb_status_string",
+    "exb_version", "exb_last_error", "exb_status_string", "exb_device_status",
     "exb_lif_forward", "exb_lif_backward", "exb_leaky_forward", "exb_leaky_backward",
 )
 
@@ -58,6 +58,8 @@ def load() -> ctypes.CDLL:
     lib.exb_last_error.restype = ctypes.c_char_p
     lib.exb_status_string.restype = ctypes.c_char_p
     lib.exb_status_string.argtypes = [_i]
+    lib.exb_device_status.restype = _i
+    lib.exb_device_status.argtypes = [_i, _vp]
     geometry = [_i64, _i64, _i64, _i, _i, _vp]
     lib.exb_lif_forward.restype = _i
     lib.exb_lif_forward.argtypes = [_vp, _vp, _vp, _vp,
@@ -87,6 +89,12 @@ def _check(status: int, what: str) -> None:
         lib = load()
         raise ExodusLibraryError(
             f"{what} failed: {lib.exb_status_string(status).decode()} -- {lib.exb_last_error().decode()}")
+
+
+def device_status(device: Optional[torch.device] = None) -> None:
+    """Wait for the current stream of ``device`` and raise if a bounded device-side wait ran out."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    _check(load().exb_device_status(dev.index, _stream(dev)), "exb_device_status")
 
 
 def ptr(t: Optional[torch.Tensor]):

@@ -77,6 +77,17 @@ const char *exb_status_string(int status)
     }
 }
 
+int exb_device_status(int device, void *stream)
+{
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_device_status: cannot select device %d", device);
+    unsigned int code = 0;
+    cudaError_t e = exb::read_device_status((cudaStream_t)stream, &code);
+    if (e != cudaSuccess) return fail(EXB_ERR_LAUNCH, "exb_device_status: %s", cudaGetErrorString(e));
+    if (code) return fail(EXB_ERR_TIMEOUT, "a bounded device-side wait ran out (code %u); results of the affected call are incomplete", code);
+    return EXB_OK;
+}
+
 int exb_lif_forward(float *spikes, float *v_mem, const float *input, const float *v_init,
                     const float *in_scale, int in_scale_mode,
                     const float *alpha, int alpha_mode,

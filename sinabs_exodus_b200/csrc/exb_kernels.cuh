@@ -46,6 +46,16 @@ cudaError_t launch_lif_backward(const LifBwdArgs &a, int layout, int reset_mode,
 cudaError_t launch_leaky_forward(const LeakyFwdArgs &a, int layout, cudaStream_t s);
 cudaError_t launch_leaky_backward(const LeakyBwdArgs &a, int layout, cudaStream_t s);
 
+// TMA-staged variants (time-major layout only).  `*used` tells whether the launch happened;
+// when false (shape or alignment not eligible) the caller takes the plain-load kernel.
+cudaError_t launch_lif_forward_tma(const LifFwdArgs &a, int reset_mode, cudaStream_t s, bool *used);
+cudaError_t launch_lif_backward_tma(const LifBwdArgs &a, int reset_mode, int surr_kind, cudaStream_t s, bool *used);
+cudaError_t launch_leaky_forward_tma(const LeakyFwdArgs &a, cudaStream_t s, bool *used);
+cudaError_t launch_leaky_backward_tma(const LeakyBwdArgs &a, cudaStream_t s, bool *used);
+cudaError_t read_device_status(cudaStream_t s, unsigned int *out);
+// EXB_DISABLE_TMA=1 in the environment forces the plain-load kernels (debugging aid).
+bool tma_enabled();
+
 __device__ __forceinline__ unsigned long long warp_sum_u64(unsigned long long x)
 {
 #pragma unroll

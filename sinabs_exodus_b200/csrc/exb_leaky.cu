@@ -340,6 +340,11 @@ static inline bool all_aligned16(std::initializer_list<const void *> ptrs)
 
 cudaError_t launch_leaky_forward(const LeakyFwdArgs &a, int layout, cudaStream_t s)
 {
+    if (layout == EXB_LAYOUT_BTM && tma_enabled()) {
+        bool used = false;
+        cudaError_t e = launch_leaky_forward_tma(a, s, &used);
+        if (e != cudaSuccess || used) return e;
+    }
     if (layout == EXB_LAYOUT_BTM) {
         if (a.M % 4 == 0 && all_aligned16({a.out, a.input})) {
             const int64_t total = a.B * (a.M / 4);
@@ -383,6 +388,11 @@ static cudaError_t launch_leaky_bwd_t(const LeakyBwdArgs &a, int layout, cudaStr
 
 cudaError_t launch_leaky_backward(const LeakyBwdArgs &a, int layout, cudaStream_t s)
 {
+    if (layout == EXB_LAYOUT_BTM && tma_enabled()) {
+        bool used = false;
+        cudaError_t e = launch_leaky_backward_tma(a, s, &used);
+        if (e != cudaSuccess || used) return e;
+    }
     const bool wa = a.grad_alpha != nullptr, ws = a.grad_scale != nullptr;
     if (wa && ws) return launch_leaky_bwd_t<true, true>(a, layout, s);
     if (wa) return launch_leaky_bwd_t<true, false>(a, layout, s);

@@ -334,6 +334,11 @@ static cudaError_t launch_fwd_t(const LifFwdArgs &a, int layout, cudaStream_t s)
 
 cudaError_t launch_lif_forward(const LifFwdArgs &a, int layout, int reset_mode, cudaStream_t s)
 {
+    if (layout == EXB_LAYOUT_BTM && tma_enabled()) {
+        bool used = false;
+        cudaError_t e = launch_lif_forward_tma(a, reset_mode, s, &used);
+        if (e != cudaSuccess || used) return e;
+    }
     return reset_mode == EXB_RESET_SUBTRACT ? launch_fwd_t<EXB_RESET_SUBTRACT>(a, layout, s)
                                             : launch_fwd_t<EXB_RESET_TO_VALUE>(a, layout, s);
 }
@@ -387,6 +392,11 @@ static cudaError_t launch_bwd_surr(const LifBwdArgs &a, int layout, int surr_kin
 
 cudaError_t launch_lif_backward(const LifBwdArgs &a, int layout, int reset_mode, int surr_kind, cudaStream_t s)
 {
+    if (layout == EXB_LAYOUT_BTM && tma_enabled()) {
+        bool used = false;
+        cudaError_t e = launch_lif_backward_tma(a, reset_mode, surr_kind, s, &used);
+        if (e != cudaSuccess || used) return e;
+    }
     return reset_mode == EXB_RESET_SUBTRACT ? launch_bwd_surr<EXB_RESET_SUBTRACT>(a, layout, surr_kind, s)
                                             : launch_bwd_surr<EXB_RESET_TO_VALUE>(a, layout, surr_kind, s);
 }

@@ -1,0 +1,139 @@
+// TMA + mbarrier plumbing for the time-major kernels.
+//
+// A CTA owns a tile of W adjacent neurons of one batch item and walks through
+// time.  A producer warp streams [TC time steps x W neurons] chunks of every
+// input tensor into a ring of S shared-memory stages with
+// cp.async.bulk.tensor (TMA); consumer warps read one float4 per thread and
+// step from the stage, keep all neuron state in registers, and write results
+// straight to global memory.  The bytes in flight are set by S*TC*W, not by
+// the number of resident threads, so small problems and the last partial wave
+// of large ones still keep HBM busy.
+//
+// Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the kernel
+// records a code in a device status word (read by exb_device_status), stops
+// issuing work, waits -- again bounded -- for its own copies in flight, and
+// returns normally.  No multicast loads are used anywhere.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace exb {
+
+// Status word: 0 = fine; otherwise the code of the first wait that ran out.
+// This header is included by exactly one translation unit, which also owns
+// the host-side accessor (read_device_status).
+__device__ unsigned int g_exb_status = 0;
+
+enum { EXB_STATUS_FULL_WAIT = 1, EXB_STATUS_EMPTY_WAIT = 2, EXB_STATUS_DRAIN_WAIT = 3, EXB_STATUS_LOOKBACK_WAIT = 4 };
+
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_fence_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+
+// Bounded wait for the completion of the phase with the given parity.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+{
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void report_timeout(unsigned int code) { atomicCAS(&g_exb_status, 0u, code); }
+
+// 3-D tiled load (x = neuron, y = time step, z = batch item) into shared memory,
+// completion signalled on `bar` as transferred bytes.  x must be a multiple of 4.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ float4 lds128(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+
+// Ring of S stages with one "full" (bytes landed) and one "empty" (all consumer
+// warps done) barrier per stage.  Lives at the end of the CTA's dynamic shared memory.
+template <int S>
+struct Ring {
+    uint64_t full[S];
+    uint64_t empty[S];
+    int issued;     // chunks the producer has issued (written before the final barrier)
+    int aborted;    // set by any thread whose wait ran out
+};
+
+template <int S>
+__device__ __forceinline__ void ring_init(Ring<S> *r, int consumer_warps)
+{
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+            mbar_init(smem_u32(&r->full[s]), 1);
+            mbar_init(smem_u32(&r->empty[s]), consumer_warps);
+        }
+        r->issued = 0;
+        r->aborted = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+}
+
+// Called by all threads at the end of the kernel.  In the normal case consumers
+// have waited for every issued chunk, so nothing is in flight.  After an abort,
+// thread 0 waits (bounded) for the newest chunk of every stage so that no copy
+// can land in shared memory that has already been handed to another CTA.
+template <int S>
+__device__ __forceinline__ void ring_finish(Ring<S> *r)
+{
+    __syncthreads();
+    if (threadIdx.x == 0 && r->aborted) {
+        const int issued = r->issued;
+        for (int s = 0; s < S; ++s) {
+            int k = issued - 1;
+            while (k >= 0 && (k % S) != s) --k;
+            if (k >= 0 && !mbar_wait(smem_u32(&r->full[s]), (uint32_t)((k / S) & 1))) report_timeout(EXB_STATUS_DRAIN_WAIT);
+        }
+    }
+}
+
+// ---- host side ------------------------------------------------------------
+// Builds a tensor map for a float32 (B, T, M) tensor with box (box_m, box_t, 1).
+// Returns false when TMA cannot be used (alignment, sizes, driver entry point).
+bool make_btm_tensor_map(CUtensorMap *map, const float *base, int64_t B, int64_t T, int64_t M, int box_m, int box_t);
+
+}  // namespace exb

@@ -14,7 +14,9 @@ pytestmark = pytest.mark.gpu
 
 TOL = 1e-5
 
-SHAPES = [(1, 1, 1), (2, 3, 5), (3, 33, 37), (2, 64, 128), (1, 100, 257), (4, 31, 32), (2, 130, 36), (5, 7, 4)]
+# the last two are wide enough (B * ceil(M/512) >= 296) for the 512-neuron TMA tiles
+SHAPES = [(1, 1, 1), (2, 3, 5), (3, 33, 37), (2, 64, 128), (1, 100, 257), (4, 31, 32), (2, 130, 36), (5, 7, 4),
+          (300, 9, 516), (150, 21, 1024)]
 
 
 def _tile_case(seed, B, T, M, mode, **kw):
@@ -74,7 +76,7 @@ def _surrogates():
 
 
 @pytest.mark.parametrize("layout", [0, 1])
-@pytest.mark.parametrize("B,T,M", [(2, 3, 5), (3, 33, 37), (2, 64, 128), (1, 100, 257), (4, 31, 32), (1, 1, 3)])
+@pytest.mark.parametrize("B,T,M", [(2, 3, 5), (3, 33, 37), (2, 64, 128), (1, 100, 257), (4, 31, 32), (1, 1, 3), (300, 9, 516)])
 @pytest.mark.parametrize("surr_idx", [0, 1, 2, 3])
 def test_lif_backward_parity(layout, B, T, M, surr_idx):
     from tests import _gpu
@@ -198,7 +200,8 @@ def test_reset_to_value_vs_bptt(layout):
     assert rel_err(g0[safe], v0.grad.reshape(N).numpy()[safe]) < 5 * TOL
 
 
-LEAKY_SHAPES = [(1, 1, 1), (2, 3, 5), (3, 33, 37), (2, 64, 128), (1, 300, 7), (2, 129, 4), (1, 1000, 3), (4, 128, 8)]
+LEAKY_SHAPES = [(1, 1, 1), (2, 3, 5), (3, 33, 37), (2, 64, 128), (1, 300, 7), (2, 129, 4), (1, 1000, 3), (4, 128, 8),
+                (300, 11, 516)]
 
 
 @pytest.mark.parametrize("layout", [0, 1])
@@ -285,3 +288,9 @@ def test_golden_vectors_gpu():
                                                    v_init=g["v_init"], want_alpha=True)
                 assert rel_err(gi, g["ref_grad_input"]) < TOL
                 assert rel_err(ga, g["ref_grad_alpha"]) < TOL
+
+
+def test_device_status_clean():
+    """After all the launches above no bounded device-side wait has run out."""
+    from sinabs_exodus_b200 import _lib
+    _lib.device_status()
