@@ -28,21 +28,22 @@ __global__ void __launch_bounds__(256) lif_fwd_btm_kernel(const LifFwdArgs A)
     const int64_t m = (gid - b * MV) * V;
     const int64_t n = b * A.M + m;
 
+    const SpikeCfg cfg = make_spike_cfg(A.maxs);
     Neuron q[V];
-    float v[V];
-    unsigned a[V];
+    float v[V], af[V];
 #pragma unroll
     for (int j = 0; j < V; ++j) {
-        q[j] = A.np.load(b, m + j);
+        q[j] = A.np.load(b, m + j, cfg);
         v[j] = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
-        a[j] = 0u;
+        af[j] = 0.0f;
     }
     const int64_t base = (b * A.T) * A.M + m;
     const float *in = A.input + base;
     float *sp = A.spikes + base;
     float *vm = A.v_mem + base;
     const int64_t T = A.T, M = A.M;
-    unsigned long long cnt = 0ull;
+    SpikeTotal cnt;
+    cnt.c32 = 0u; cnt.c64 = 0ull;
 
     float xc[U][V], xn[U][V];
 #pragma unroll
@@ -61,15 +62,10 @@ __global__ void __launch_bounds__(256) lif_fwd_btm_kernel(const LifFwdArgs A)
         for (int u = 0; u < U; ++u) {
             const int64_t tt = t + u;
             if (tt < T) {
-                float s[V];
 #pragma unroll
-                for (int j = 0; j < V; ++j) {
-                    lif_step<RESET>(v[j], a[j], xc[u][j], q[j], A.maxs);
-                    s[j] = __uint2float_rn(a[j]);
-                    cnt += a[j];
-                }
+                for (int j = 0; j < V; ++j) lif_step<RESET>(v[j], af[j], xc[u][j], q[j], cfg, cnt);
                 if (valid) {
-                    stv<V>(sp + tt * M, s);
+                    stv<V>(sp + tt * M, af);
                     stv<V>(vm + tt * M, v);
                 }
             }
@@ -81,11 +77,11 @@ __global__ void __launch_bounds__(256) lif_fwd_btm_kernel(const LifFwdArgs A)
     }
     if (A.v_post_last && valid) {
 #pragma unroll
-        for (int j = 0; j < V; ++j) A.v_post_last[n + j] = post_reset<RESET>(v[j], a[j], q[j]);
+        for (int j = 0; j < V; ++j) A.v_post_last[n + j] = post_reset<RESET>(v[j], af[j], q[j]);
     }
     if (A.spike_count) {
-        cnt = warp_sum_u64(valid ? cnt : 0ull);
-        if ((threadIdx.x & 31) == 0 && cnt) atomicAdd(A.spike_count, cnt);
+        const unsigned long long tot = warp_sum_u64(valid ? cnt.total() : 0ull);
+        if ((threadIdx.x & 31) == 0 && tot) atomicAdd(A.spike_count, tot);
     }
 }
 
@@ -104,6 +100,7 @@ __global__ void __launch_bounds__(256) lif_bwd_btm_kernel(const LifBwdArgs A)
     const int64_t n = b * A.M + m;
     const int64_t T = A.T, M = A.M;
 
+    const SpikeCfg cfg = make_spike_cfg(A.maxs);
     Neuron q[V];
     SurrConst sc[V];
     float cp[V];
@@ -112,7 +109,7 @@ __global__ void __launch_bounds__(256) lif_bwd_btm_kernel(const LifBwdArgs A)
     bool n0[V];
 #pragma unroll
     for (int j = 0; j < V; ++j) {
-        q[j] = A.np.load(b, m + j);
+        q[j] = A.np.load(b, m + j, cfg);
         sc[j] = surr_prepare<SURR>(q[j], A.p0, A.p1);
         cp[j] = __fmul_rn(q[j].alpha, q[j].c);
         st[j].R = 0.0f; st[j].ag = 0.0f; st[j].sg = 0.0f;
@@ -144,7 +141,7 @@ __global__ void __launch_bounds__(256) lif_bwd_btm_kernel(const LifBwdArgs A)
         if (t == T - 1 && A.g_last) {
 #pragma unroll
             for (int j = 0; j < V; ++j)
-                fold_last_state_grad<RESET>(rgo[0][j], rgv[0][j], __ldg(A.g_last + n + j), rv[0][j], q[j], A.maxs);
+                fold_last_state_grad<RESET>(rgo[0][j], rgv[0][j], __ldg(A.g_last + n + j), rv[0][j], q[j], cfg);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -155,7 +152,7 @@ __global__ void __launch_bounds__(256) lif_bwd_btm_kernel(const LifBwdArgs A)
                 for (int j = 0; j < V; ++j) {
                     Rprev[j] = st[j].R;
                     const float Rt = lif_bwd_step<SURR, RESET, WA, WS>(st[j], rv[u][j], rgo[u][j], rgv[u][j], rsl[u][j],
-                                                                      rx[u][j], q[j], sc[j], cp[j], A.maxs, f0[j], n0[j]);
+                                                                      rx[u][j], q[j], sc[j], cp[j], cfg, f0[j], n0[j]);
                     r[j] = __fmul_rn(q[j].scale, Rt);
                 }
                 stv<V>(gi + tt * M, r);
@@ -211,10 +208,12 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_fwd_nt_kernel(const LifFwdA
     const bool valid = lane < rows;
     const int64_t n = valid ? n0 + lane : n0;
     const int64_t b = n / A.M, m = n - b * A.M;
-    const Neuron q = A.np.load(b, m);
+    const SpikeCfg cfg = make_spike_cfg(A.maxs);
+    const Neuron q = A.np.load(b, m, cfg);
     float v = A.v_init ? __ldg(A.v_init + n) : 0.0f;
-    unsigned a = 0u;
-    unsigned long long cnt = 0ull;
+    float af = 0.0f;
+    SpikeTotal cnt;
+    cnt.c32 = 0u; cnt.c64 = 0ull;
 
     for (int64_t t0 = 0; t0 < T; t0 += TILE) {
         const int tc = (int)min((int64_t)TILE, T - t0);
@@ -222,10 +221,9 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_fwd_nt_kernel(const LifFwdA
         __syncwarp();
         if (valid) {
             for (int t = 0; t < tc; ++t) {
-                lif_step<RESET>(v, a, tx[lane * TSTR + t], q, A.maxs);
-                ts[lane * TSTR + t] = __uint2float_rn(a);
+                lif_step<RESET>(v, af, tx[lane * TSTR + t], q, cfg, cnt);
+                ts[lane * TSTR + t] = af;
                 tx[lane * TSTR + t] = v;
-                cnt += a;
             }
         }
         __syncwarp();
@@ -233,10 +231,10 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_fwd_nt_kernel(const LifFwdA
         tile_store(A.v_mem + n0 * T + t0, tx, T, rows, tc, lane);
         __syncwarp();
     }
-    if (A.v_post_last && valid) A.v_post_last[n] = post_reset<RESET>(v, a, q);
+    if (A.v_post_last && valid) A.v_post_last[n] = post_reset<RESET>(v, af, q);
     if (A.spike_count) {
-        cnt = warp_sum_u64(valid ? cnt : 0ull);
-        if (lane == 0 && cnt) atomicAdd(A.spike_count, cnt);
+        const unsigned long long tot = warp_sum_u64(valid ? cnt.total() : 0ull);
+        if (lane == 0 && tot) atomicAdd(A.spike_count, tot);
     }
 }
 
@@ -260,7 +258,8 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_nt_kernel(const LifBwdA
     const bool valid = lane < rows;
     const int64_t n = valid ? n0 + lane : n0;
     const int64_t b = n / A.M, m = n - b * A.M;
-    const Neuron q = A.np.load(b, m);
+    const SpikeCfg cfg = make_spike_cfg(A.maxs);
+    const Neuron q = A.np.load(b, m, cfg);
     const SurrConst sc = surr_prepare<SURR>(q, A.p0, A.p1);
     const float cp = __fmul_rn(q.alpha, q.c);
     BwdState st;
@@ -283,10 +282,10 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_nt_kernel(const LifBwdA
                 const int i = lane * TSTR + t;
                 float go = tg[i], gv = tgv ? tgv[i] : 0.0f;
                 const float v = tv[i];
-                if (A.g_last && t0 + t == T - 1) fold_last_state_grad<RESET>(go, gv, glast, v, q, A.maxs);
+                if (A.g_last && t0 + t == T - 1) fold_last_state_grad<RESET>(go, gv, glast, v, q, cfg);
                 Rprev = st.R;
                 const float Rt = lif_bwd_step<SURR, RESET, WA, WS>(st, v, go, gv, (SURR == EXB_SURR_GENERIC) ? tsl[i] : 0.0f,
-                                                                  WS ? txi[i] : 0.0f, q, sc, cp, A.maxs, f0, nc0);
+                                                                  WS ? txi[i] : 0.0f, q, sc, cp, cfg, f0, nc0);
                 tg[i] = __fmul_rn(q.scale, Rt);
             }
         }

@@ -32,63 +32,93 @@ __host__ inline Param make_param(const float *p, int mode, int64_t M)
     return r;
 }
 
+// Limit on the number of spikes per step, in the forms the step needs.
+struct SpikeCfg {
+    unsigned maxs;   // maximum count (0xFFFFFFFF = no limit)
+    unsigned oneu;   // min(1, maxs)
+    float onef;      // the same as float
+};
+
+__host__ __device__ inline SpikeCfg make_spike_cfg(unsigned maxs)
+{
+    SpikeCfg c;
+    c.maxs = maxs;
+    c.oneu = maxs >= 1u ? 1u : 0u;
+    c.onef = maxs >= 1u ? 1.0f : 0.0f;
+    return c;
+}
+
 // Constants of one neuron, loaded once before the time loop.
 struct Neuron {
     float alpha;   // decay
     float c;       // subtract value (or reset value)
     float th;      // threshold
-    float th2;     // 2*threshold
+    float th2;     // potential from which the spike count needs the division (see spike_count_f)
     float lo;      // lower bound, -inf when there is none
     float scale;   // input scale, 1 when there is none
 };
 
 struct NeuronParams {
     Param alpha, c, th, lo, scale;
-    __device__ __forceinline__ Neuron load(int64_t b, int64_t m) const
+    __device__ __forceinline__ Neuron load(int64_t b, int64_t m, const SpikeCfg &cfg) const
     {
         Neuron q;
         q.alpha = alpha.get(b, m, 1.0f);
         q.th = th.get(b, m, 1.0f);
         q.c = c.get(b, m, q.th);
-        q.th2 = __fadd_rn(q.th, q.th);
+        // For a positive threshold and th <= v < 2*th the correctly rounded quotient v/th lies in
+        // [1, 2), so the count is 1 without dividing; with at most one spike allowed the division is
+        // never needed.  A non-positive threshold always takes the exact path.
+        q.th2 = (q.th > 0.0f) ? ((cfg.maxs <= 1u) ? INFINITY : __fadd_rn(q.th, q.th)) : q.th;
         q.lo = lo.get(b, m, -INFINITY);
         q.scale = scale.get(b, m, 1.0f);
         return q;
     }
 };
 
-// Number of spikes for membrane potential v: min(trunc(v/th), maxs) when
-// v >= th, else 0 (cuda/lif_kernels.h:80-84 of the reference).  For
-// th <= v < 2*th the correctly rounded quotient v/th is always in [1, 2), so
-// the division is skipped there; the result is identical.
-__device__ __forceinline__ unsigned spike_count(float v, const Neuron &q, unsigned maxs)
+// Spike count as float for membrane potential v: min(trunc(v/th), maxs) where v >= th, else 0
+// (cuda/lif_kernels.h:80-84 of the reference).
+__device__ __forceinline__ float spike_count_f(float v, const Neuron &q, const SpikeCfg &cfg)
 {
-    unsigned a = 0u;
-    if (v >= q.th) {
-        a = (v < q.th2) ? 1u : __float2uint_rz(__fdiv_rn(v, q.th));
-        a = min(a, maxs);
-    }
-    return a;
+    float af = (v >= q.th) ? cfg.onef : 0.0f;
+    if (v >= q.th2) af = __uint2float_rn(min(__float2uint_rz(__fdiv_rn(v, q.th)), cfg.maxs));
+    return af;
 }
 
-// One forward step (cuda/lif_kernels.h:61-84): reset with the previous count,
-// decay, integrate, clip from below, count spikes.
+// Exact spike total of one thread: c32 counts steps with at least one spike, c64 the rest
+// (modulo 2^64, so that a correction below zero cancels against c32).
+struct SpikeTotal {
+    unsigned c32;
+    unsigned long long c64;
+    __device__ __forceinline__ unsigned long long total() const { return c64 + c32; }
+};
+
+// One forward step (cuda/lif_kernels.h:61-84): reset with the previous count `af`, decay,
+// integrate, clip from below, count spikes.  The common case (0 or 1 spike) is branch-free.
 template <int RESET>
-__device__ __forceinline__ void lif_step(float &v, unsigned &a, float x, const Neuron &q, unsigned maxs)
+__device__ __forceinline__ void lif_step(float &v, float &af, float x, const Neuron &q, const SpikeCfg &cfg,
+                                         SpikeTotal &cnt)
 {
-    if (RESET == EXB_RESET_SUBTRACT) v = __fmaf_rn(-__uint2float_rn(a), q.c, v);
-    else v = a ? q.c : v;
+    if (RESET == EXB_RESET_SUBTRACT) v = __fmaf_rn(-af, q.c, v);
+    else v = (af != 0.0f) ? q.c : v;
     v = __fmaf_rn(v, q.alpha, __fmul_rn(q.scale, x));
     v = (v < q.lo) ? q.lo : v;
-    a = spike_count(v, q, maxs);
+    const bool sp = v >= q.th;
+    af = sp ? cfg.onef : 0.0f;
+    cnt.c32 += sp ? cfg.oneu : 0u;
+    if (v >= q.th2) {
+        const unsigned a = min(__float2uint_rz(__fdiv_rn(v, q.th)), cfg.maxs);
+        af = __uint2float_rn(a);
+        cnt.c64 += (unsigned long long)a - (unsigned long long)cfg.oneu;
+    }
 }
 
-// State after the reset that follows a step.
+// State after the reset that follows a step with spike count `af`.
 template <int RESET>
-__device__ __forceinline__ float post_reset(float v, unsigned a, const Neuron &q)
+__device__ __forceinline__ float post_reset(float v, float af, const Neuron &q)
 {
-    if (RESET == EXB_RESET_SUBTRACT) return __fmaf_rn(-__uint2float_rn(a), q.c, v);
-    return a ? q.c : v;
+    if (RESET == EXB_RESET_SUBTRACT) return __fmaf_rn(-af, q.c, v);
+    return (af != 0.0f) ? q.c : v;
 }
 
 // Surrogate-gradient constants of one neuron.
@@ -145,18 +175,18 @@ struct BwdState {
 // propagation factor and clip gate for the caller's first-step handling.
 template <int SURR, int RESET, bool WANT_ALPHA_GRAD, bool WANT_SCALE_GRAD>
 __device__ __forceinline__ float lif_bwd_step(BwdState &st, float v, float go, float gv, float sl, float x,
-                                              const Neuron &q, const SurrConst &sc, float cp, unsigned maxs,
+                                              const Neuron &q, const SurrConst &sc, float cp, const SpikeCfg &cfg,
                                               float &f_out, bool &n_out)
 {
     const float s = surrogate<SURR>(v, q, sc, sl);
     const bool n = v > q.lo;
     const float g = __fadd_rn(__fmul_rn(s, go), gv);
-    unsigned a = 0u;
-    if (RESET == EXB_RESET_TO_VALUE || WANT_ALPHA_GRAD) a = spike_count(v, q, maxs);
+    float af = 0.0f;
+    if (RESET == EXB_RESET_TO_VALUE || WANT_ALPHA_GRAD) af = spike_count_f(v, q, cfg);
     float f;
     if (RESET == EXB_RESET_SUBTRACT) f = __fmaf_rn(-cp, s, q.alpha);   // alpha - (alpha*c)*s
-    else f = a ? 0.0f : q.alpha;
-    if (WANT_ALPHA_GRAD) st.ag = __fmaf_rn(st.R, post_reset<RESET>(v, a, q), st.ag);
+    else f = (af != 0.0f) ? 0.0f : q.alpha;
+    if (WANT_ALPHA_GRAD) st.ag = __fmaf_rn(st.R, post_reset<RESET>(v, af, q), st.ag);
     const float Rt = n ? __fmaf_rn(f, st.R, g) : 0.0f;
     if (WANT_SCALE_GRAD) st.sg = __fmaf_rn(Rt, x, st.sg);
     st.R = Rt;
@@ -170,13 +200,13 @@ __device__ __forceinline__ float lif_bwd_step(BwdState &st, float v, float go, f
 // go += -c*G and gv += G (reset-to-value: gv += G where no spike occurred).
 template <int RESET>
 __device__ __forceinline__ void fold_last_state_grad(float &go, float &gv, float G, float v,
-                                                     const Neuron &q, unsigned maxs)
+                                                     const Neuron &q, const SpikeCfg &cfg)
 {
     if (RESET == EXB_RESET_SUBTRACT) {
         go = __fmaf_rn(-q.c, G, go);
         gv = __fadd_rn(gv, G);
     } else {
-        gv = __fadd_rn(gv, spike_count(v, q, maxs) ? 0.0f : G);
+        gv = __fadd_rn(gv, (spike_count_f(v, q, cfg) != 0.0f) ? 0.0f : G);
     }
 }
 

@@ -87,22 +87,21 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
 
 __device__ __forceinline__ float4 lds128(const float *p) { return *reinterpret_cast<const float4 *>(p); }
 
-// Ring of S stages with one "full" (bytes landed) and one "empty" (all consumer
-// warps done) barrier per stage.  Lives at the end of the CTA's dynamic shared memory.
-template <int S>
+// Ring of up to MAX_STAGES stages with one "full" (bytes landed) and one "empty" (all
+// consumer warps done) barrier per stage.  Lives at the end of the CTA's dynamic shared memory.
+constexpr int MAX_STAGES = 8;
+
 struct Ring {
-    uint64_t full[S];
-    uint64_t empty[S];
+    uint64_t full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
     int issued;     // chunks the producer has issued (written before the final barrier)
     int aborted;    // set by any thread whose wait ran out
 };
 
-template <int S>
-__device__ __forceinline__ void ring_init(Ring<S> *r, int consumer_warps)
+__device__ __forceinline__ void ring_init(Ring *r, int stages, int consumer_warps)
 {
     if (threadIdx.x == 0) {
-#pragma unroll
-        for (int s = 0; s < S; ++s) {
+        for (int s = 0; s < stages; ++s) {
             mbar_init(smem_u32(&r->full[s]), 1);
             mbar_init(smem_u32(&r->empty[s]), consumer_warps);
         }
@@ -117,16 +116,16 @@ __device__ __forceinline__ void ring_init(Ring<S> *r, int consumer_warps)
 // have waited for every issued chunk, so nothing is in flight.  After an abort,
 // thread 0 waits (bounded) for the newest chunk of every stage so that no copy
 // can land in shared memory that has already been handed to another CTA.
-template <int S>
-__device__ __forceinline__ void ring_finish(Ring<S> *r)
+__device__ __forceinline__ void ring_finish(Ring *r, int stages)
 {
     __syncthreads();
     if (threadIdx.x == 0 && r->aborted) {
         const int issued = r->issued;
-        for (int s = 0; s < S; ++s) {
+        for (int s = 0; s < stages; ++s) {
             int k = issued - 1;
-            while (k >= 0 && (k % S) != s) --k;
-            if (k >= 0 && !mbar_wait(smem_u32(&r->full[s]), (uint32_t)((k / S) & 1))) report_timeout(EXB_STATUS_DRAIN_WAIT);
+            while (k >= 0 && (k % stages) != s) --k;
+            if (k >= 0 && !mbar_wait(smem_u32(&r->full[s]), (uint32_t)((k / stages) & 1)))
+                report_timeout(EXB_STATUS_DRAIN_WAIT);
         }
     }
 }

@@ -20,22 +20,39 @@ struct TileGeom {
     static constexpr int NBOX = W / BW;
 };
 
-// Shared-memory float offset of (time step tt, neuron column c) inside one tensor's part of a stage.
-template <int NW, int TC>
-__device__ __forceinline__ int tile_off(int tt, int c)
+// Resident CTAs per SM the kernels are compiled for (caps registers at 64 per thread).
+// Light kernels fit 64 registers; the backward with alpha/scale gradients or an exponential
+// surrogate keeps four neurons' constants and accumulators live and gets 96.
+template <int NW, bool HEAVY = false>
+struct MinBlocks {
+    static constexpr int value = (NW == 4) ? (HEAVY ? 4 : 6) : (HEAVY ? 10 : 16);
+};
+
+// Shared-memory float offset of neuron column c inside one tensor's part of a stage, at time
+// step 0 of the stage; consecutive time steps are BW floats apart.
+template <int NW>
+__device__ __forceinline__ int tile_col_off(int tc, int c)
 {
     using G = TileGeom<NW>;
-    return ((c / G::BW) * TC + tt) * G::BW + (c % G::BW);
+    return (c / G::BW) * tc * G::BW + (c % G::BW);
 }
 
-// Producer: issues chunk k of `nmaps` tensors into stage k % S.
-template <int NW, int TC, int S>
-__device__ __forceinline__ void produce(Ring<S> *ring, float *stages, const CUtensorMap *const *maps, int nmaps,
-                                        int nchunks, int m0, int b)
+// Pipeline shape chosen by the launcher: time steps per stage and number of stages.
+struct PipeCfg {
+    int tc;
+    int stages;
+};
+
+// Producer: issues chunk k (k-th in processing order; `reverse` walks time backwards) of
+// `nmaps` tensors into stage k % S.
+template <int NW>
+__device__ __forceinline__ void produce(Ring *ring, float *stages, const CUtensorMap *const *maps, int nmaps,
+                                        int nchunks, int m0, int b, PipeCfg pc, bool reverse)
 {
     using G = TileGeom<NW>;
-    constexpr int TENSOR_FLOATS = TC * G::W;
-    const int stage_floats = nmaps * TENSOR_FLOATS;
+    const int tensor_floats = pc.tc * G::W;
+    const int stage_floats = nmaps * tensor_floats;
+    const int S = pc.stages;
     int k = 0;
     for (; k < nchunks; ++k) {
         const int s = k % S;
@@ -47,39 +64,12 @@ __device__ __forceinline__ void produce(Ring<S> *ring, float *stages, const CUte
         const uint32_t bar = smem_u32(&ring->full[s]);
         mbar_arrive_expect_tx(bar, (uint32_t)(stage_floats * sizeof(float)));
         float *dst = stages + (size_t)s * stage_floats;
+        const int chunk = reverse ? (nchunks - 1 - k) : k;
         for (int i = 0; i < nmaps; ++i) {
 #pragma unroll
             for (int j = 0; j < G::NBOX; ++j)
-                tma_load_3d(smem_u32(dst + i * TENSOR_FLOATS + j * TC * G::BW), maps[i], m0 + j * G::BW, k * TC, b, bar);
-        }
-    }
-    ring->issued = k;
-}
-
-// Reverse-time producer: chunk index kk counts from the end of the sequence.
-template <int NW, int TC, int S>
-__device__ __forceinline__ void produce_reverse(Ring<S> *ring, float *stages, const CUtensorMap *const *maps, int nmaps,
-                                                int nchunks, int m0, int b)
-{
-    using G = TileGeom<NW>;
-    constexpr int TENSOR_FLOATS = TC * G::W;
-    const int stage_floats = nmaps * TENSOR_FLOATS;
-    int k = 0;
-    for (; k < nchunks; ++k) {
-        const int s = k % S;
-        if (k >= S && !mbar_wait(smem_u32(&ring->empty[s]), (uint32_t)(((k / S) - 1) & 1))) {
-            report_timeout(EXB_STATUS_EMPTY_WAIT);
-            ring->aborted = 1;
-            break;
-        }
-        const uint32_t bar = smem_u32(&ring->full[s]);
-        mbar_arrive_expect_tx(bar, (uint32_t)(stage_floats * sizeof(float)));
-        float *dst = stages + (size_t)s * stage_floats;
-        const int chunk = nchunks - 1 - k;
-        for (int i = 0; i < nmaps; ++i) {
-#pragma unroll
-            for (int j = 0; j < G::NBOX; ++j)
-                tma_load_3d(smem_u32(dst + i * TENSOR_FLOATS + j * TC * G::BW), maps[i], m0 + j * G::BW, chunk * TC, b, bar);
+                tma_load_3d(smem_u32(dst + i * tensor_floats + j * pc.tc * G::BW), maps[i], m0 + j * G::BW,
+                            chunk * pc.tc, b, bar);
         }
     }
     ring->issued = k;
@@ -89,35 +79,56 @@ struct TmaMaps {
     CUtensorMap m[5];
 };
 
-template <int NW, int TC, int S>
-constexpr size_t tma_smem_bytes(int nmaps)
+template <int NW>
+static size_t tma_smem_bytes(int nmaps, PipeCfg pc)
 {
-    return (size_t)S * nmaps * TC * TileGeom<NW>::W * sizeof(float) + sizeof(Ring<S>) + 128;
+    return (size_t)pc.stages * nmaps * pc.tc * TileGeom<NW>::W * sizeof(float) + sizeof(Ring) + 128;
+}
+
+// Consumer-side wait for chunk k; marks the ring aborted when the wait runs out.
+__device__ __forceinline__ bool wait_chunk(Ring *ring, int k, int S)
+{
+    if (mbar_wait(smem_u32(&ring->full[k % S]), (uint32_t)((k / S) & 1))) return true;
+    report_timeout(EXB_STATUS_FULL_WAIT);
+    ring->aborted = 1;
+    return false;
+}
+
+__device__ __forceinline__ void release_chunk(Ring *ring, int k, int S, int lane)
+{
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&ring->empty[k % S]));
+}
+
+__device__ __forceinline__ void unpack(float (&d)[4], const float4 &t)
+{
+    d[0] = t.x; d[1] = t.y; d[2] = t.z; d[3] = t.w;
 }
 
 // ===========================================================================
 // spike scan forward
 // ===========================================================================
-template <int RESET, int NW, int TC, int S>
-__global__ void __launch_bounds__((NW + 1) * 32)
-lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, const int tiles_m)
+template <int RESET, int NW>
+__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW>::value)
+lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, const int tiles_m, const PipeCfg pc)
 {
     using G = TileGeom<NW>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float *stages = reinterpret_cast<float *>(smem_raw);
-    Ring<S> *ring = reinterpret_cast<Ring<S> *>(smem_raw + (size_t)S * TC * G::W * sizeof(float));
-    ring_init<S>(ring, NW);
+    const int tensor_floats = pc.tc * G::W;
+    Ring *ring = reinterpret_cast<Ring *>(smem_raw + (size_t)pc.stages * tensor_floats * sizeof(float));
+    ring_init(ring, pc.stages, NW);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.x / tiles_m;
     const int m0 = (blockIdx.x - b * tiles_m) * G::W;
     const int T = (int)A.T;
-    const int nchunks = (T + TC - 1) / TC;
+    const int nchunks = (T + pc.tc - 1) / pc.tc;
 
     if (warp == NW) {
         if (lane == 0) {
             const CUtensorMap *mp[1] = {&maps.m[0]};
-            produce<NW, TC, S>(ring, stages, mp, 1, nchunks, m0, b);
+            produce<NW>(ring, stages, mp, 1, nchunks, m0, b, pc, false);
         }
     } else {
         const int c = threadIdx.x * 4;                 // column inside the tile
@@ -125,93 +136,84 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
         const bool valid = m < A.M;                    // M % 4 == 0: all four neurons or none
         const int64_t mm = valid ? m : 0;
         const int64_t n = (int64_t)b * A.M + mm;
+        const SpikeCfg cfg = make_spike_cfg(A.maxs);
         Neuron q[4];
-        float v[4];
-        unsigned a[4];
+        float v[4], af[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            q[j] = A.np.load(b, mm + j);
+            q[j] = A.np.load(b, mm + j, cfg);
             v[j] = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
-            a[j] = 0u;
+            af[j] = 0.0f;
         }
         const int64_t base = ((int64_t)b * T) * A.M + mm;
         float *sp = A.spikes + base;
         float *vm = A.v_mem + base;
-        unsigned long long cnt = 0ull;
+        const int64_t M = A.M;
+        const int col = tile_col_off<NW>(pc.tc, c);
+        SpikeTotal cnt;
+        cnt.c32 = 0u; cnt.c64 = 0ull;
         bool ok = true;
-        for (int k = 0; k < nchunks && ok; ++k) {
-            const int s = k % S;
-            if (!mbar_wait(smem_u32(&ring->full[s]), (uint32_t)((k / S) & 1))) {
-                report_timeout(EXB_STATUS_FULL_WAIT);
-                ring->aborted = 1;
-                ok = false;
-                break;
-            }
-            const float *st = stages + (size_t)s * TC * G::W;
-            const int tmax = min(TC, T - k * TC);
+        for (int k = 0; k < nchunks; ++k) {
+            if (!wait_chunk(ring, k, pc.stages)) { ok = false; break; }
+            const float *st = stages + (size_t)(k % pc.stages) * tensor_floats + col;
+            const int tmax = min(pc.tc, T - k * pc.tc);
+#pragma unroll 4
+            for (int tt = 0; tt < tmax; ++tt) {
+                float xs[4];
+                unpack(xs, lds128(st + tt * G::BW));
 #pragma unroll
-            for (int tt = 0; tt < TC; ++tt) {
-                if (tt < tmax) {
-                    const float4 x = lds128(st + tile_off<NW, TC>(tt, c));
-                    const float xs[4] = {x.x, x.y, x.z, x.w};
-                    float sv[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        lif_step<RESET>(v[j], a[j], xs[j], q[j], A.maxs);
-                        sv[j] = __uint2float_rn(a[j]);
-                        cnt += a[j];
-                    }
-                    if (valid) {
-                        const int64_t off = (int64_t)(k * TC + tt) * A.M;
-                        stv<4>(sp + off, sv);
-                        stv<4>(vm + off, v);
-                    }
+                for (int j = 0; j < 4; ++j) lif_step<RESET>(v[j], af[j], xs[j], q[j], cfg, cnt);
+                if (valid) {
+                    stv<4>(sp, af);
+                    stv<4>(vm, v);
                 }
+                sp += M;
+                vm += M;
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ring->empty[s]));
+            release_chunk(ring, k, pc.stages, lane);
         }
         if (ok && valid && A.v_post_last) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) A.v_post_last[n + j] = post_reset<RESET>(v[j], a[j], q[j]);
+            for (int j = 0; j < 4; ++j) A.v_post_last[n + j] = post_reset<RESET>(v[j], af[j], q[j]);
         }
         if (A.spike_count) {
-            cnt = warp_sum_u64((valid && ok) ? cnt : 0ull);
-            if (lane == 0 && cnt) atomicAdd(A.spike_count, cnt);
+            const unsigned long long tot = warp_sum_u64((valid && ok) ? cnt.total() : 0ull);
+            if (lane == 0 && tot) atomicAdd(A.spike_count, tot);
         }
     }
-    ring_finish<S>(ring);
+    ring_finish(ring, pc.stages);
 }
 
 // ===========================================================================
 // fused reverse-time backward
 // ===========================================================================
-template <int SURR, int RESET, bool WA, bool WS, int NW, int TC, int S>
-__global__ void __launch_bounds__((NW + 1) * 32)
-lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, const int tiles_m, const int nmaps)
+template <int SURR, int RESET, bool WA, bool WS, int NW>
+__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, (WA || WS || SURR == EXB_SURR_GENERIC || SURR == EXB_SURR_PERIODIC_EXPONENTIAL || SURR == EXB_SURR_SINGLE_EXPONENTIAL)>::value)
+lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, const int tiles_m, const int nmaps,
+                   const PipeCfg pc)
 {
     using G = TileGeom<NW>;
-    constexpr int TENSOR_FLOATS = TC * G::W;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float *stages = reinterpret_cast<float *>(smem_raw);
-    Ring<S> *ring = reinterpret_cast<Ring<S> *>(smem_raw + (size_t)S * nmaps * TENSOR_FLOATS * sizeof(float));
-    ring_init<S>(ring, NW);
+    const int tensor_floats = pc.tc * G::W;
+    const int stage_floats = nmaps * tensor_floats;
+    Ring *ring = reinterpret_cast<Ring *>(smem_raw + (size_t)pc.stages * stage_floats * sizeof(float));
+    ring_init(ring, pc.stages, NW);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.x / tiles_m;
     const int m0 = (blockIdx.x - b * tiles_m) * G::W;
     const int T = (int)A.T;
-    const int nchunks = (T + TC - 1) / TC;
-    // stage layout: [go][v_mem]([grad_v_mem])([surr])([input])
+    const int nchunks = (T + pc.tc - 1) / pc.tc;
+    // stage layout: [grad_spikes][v_mem]([grad_v_mem])([surr])([input])
     const bool has_gv = A.gv != nullptr;
-    const int i_gv = 2;
     const int i_sl = 2 + (has_gv ? 1 : 0);
     const int i_x = i_sl + ((SURR == EXB_SURR_GENERIC) ? 1 : 0);
 
     if (warp == NW) {
         if (lane == 0) {
             const CUtensorMap *mp[5] = {&maps.m[0], &maps.m[1], &maps.m[2], &maps.m[3], &maps.m[4]};
-            produce_reverse<NW, TC, S>(ring, stages, mp, nmaps, nchunks, m0, b);
+            produce<NW>(ring, stages, mp, nmaps, nchunks, m0, b, pc, true);
         }
     } else {
         const int c = threadIdx.x * 4;
@@ -219,6 +221,7 @@ lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, con
         const bool valid = m < A.M;
         const int64_t mm = valid ? m : 0;
         const int64_t n = (int64_t)b * A.M + mm;
+        const SpikeCfg cfg = make_spike_cfg(A.maxs);
         Neuron q[4];
         SurrConst sc[4];
         float cp[4], Rprev[4], f0[4], glast[4];
@@ -226,65 +229,49 @@ lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, con
         BwdState st[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            q[j] = A.np.load(b, mm + j);
+            q[j] = A.np.load(b, mm + j, cfg);
             sc[j] = surr_prepare<SURR>(q[j], A.p0, A.p1);
             cp[j] = __fmul_rn(q[j].alpha, q[j].c);
             st[j].R = 0.0f; st[j].ag = 0.0f; st[j].sg = 0.0f;
             Rprev[j] = 0.0f; f0[j] = 0.0f; n0[j] = true;
             glast[j] = A.g_last ? __ldg(A.g_last + n + j) : 0.0f;
         }
-        float *gi = A.grad_input + ((int64_t)b * T) * A.M + mm;
+        const int64_t M = A.M;
+        float *gi_base = A.grad_input + ((int64_t)b * T) * M + mm;
+        const int col = tile_col_off<NW>(pc.tc, c);
         bool ok = true;
-        for (int k = 0; k < nchunks && ok; ++k) {
-            const int s = k % S;
-            if (!mbar_wait(smem_u32(&ring->full[s]), (uint32_t)((k / S) & 1))) {
-                report_timeout(EXB_STATUS_FULL_WAIT);
-                ring->aborted = 1;
-                ok = false;
-                break;
-            }
-            const float *stg = stages + (size_t)s * nmaps * TENSOR_FLOATS;
+        for (int k = 0; k < nchunks; ++k) {
+            if (!wait_chunk(ring, k, pc.stages)) { ok = false; break; }
+            const float *stg = stages + (size_t)(k % pc.stages) * stage_floats + col;
             const int chunk = nchunks - 1 - k;
-            const int tmax = min(TC, T - chunk * TC);
+            const int tmax = min(pc.tc, T - chunk * pc.tc);
+            float *gi = gi_base + (int64_t)(chunk * pc.tc + tmax - 1) * M;
+#pragma unroll 2
+            for (int tt = tmax - 1; tt >= 0; --tt) {
+                const float *e = stg + tt * G::BW;
+                float go[4], vv[4];
+                float gv[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sl[4] = {0.0f, 0.0f, 0.0f, 0.0f}, xx[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                unpack(go, lds128(e));
+                unpack(vv, lds128(e + tensor_floats));
+                if (has_gv) unpack(gv, lds128(e + 2 * tensor_floats));
+                if (SURR == EXB_SURR_GENERIC) unpack(sl, lds128(e + i_sl * tensor_floats));
+                if (WS) unpack(xx, lds128(e + i_x * tensor_floats));
+                if (A.g_last && chunk * pc.tc + tt == T - 1) {
 #pragma unroll
-            for (int tt = TC - 1; tt >= 0; --tt) {
-                if (tt < tmax) {
-                    const int o = tile_off<NW, TC>(tt, c);
-                    const float4 g4 = lds128(stg + o);
-                    const float4 v4 = lds128(stg + TENSOR_FLOATS + o);
-                    float go[4] = {g4.x, g4.y, g4.z, g4.w};
-                    const float vv[4] = {v4.x, v4.y, v4.z, v4.w};
-                    float gv[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sl[4] = {0.0f, 0.0f, 0.0f, 0.0f}, xx[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    if (has_gv) {
-                        const float4 t4 = lds128(stg + i_gv * TENSOR_FLOATS + o);
-                        gv[0] = t4.x; gv[1] = t4.y; gv[2] = t4.z; gv[3] = t4.w;
-                    }
-                    if (SURR == EXB_SURR_GENERIC) {
-                        const float4 t4 = lds128(stg + i_sl * TENSOR_FLOATS + o);
-                        sl[0] = t4.x; sl[1] = t4.y; sl[2] = t4.z; sl[3] = t4.w;
-                    }
-                    if (WS) {
-                        const float4 t4 = lds128(stg + i_x * TENSOR_FLOATS + o);
-                        xx[0] = t4.x; xx[1] = t4.y; xx[2] = t4.z; xx[3] = t4.w;
-                    }
-                    const int t = chunk * TC + tt;
-                    if (A.g_last && t == T - 1) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) fold_last_state_grad<RESET>(go[j], gv[j], glast[j], vv[j], q[j], A.maxs);
-                    }
-                    float r[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        Rprev[j] = st[j].R;
-                        const float Rt = lif_bwd_step<SURR, RESET, WA, WS>(st[j], vv[j], go[j], gv[j], sl[j], xx[j], q[j],
-                                                                          sc[j], cp[j], A.maxs, f0[j], n0[j]);
-                        r[j] = __fmul_rn(q[j].scale, Rt);
-                    }
-                    if (valid) stv<4>(gi + (int64_t)t * A.M, r);
+                    for (int j = 0; j < 4; ++j) fold_last_state_grad<RESET>(go[j], gv[j], glast[j], vv[j], q[j], cfg);
                 }
+                float r[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    Rprev[j] = st[j].R;
+                    const float Rt = lif_bwd_step<SURR, RESET, WA, WS>(st[j], vv[j], go[j], gv[j], sl[j], xx[j], q[j], sc[j],
+                                                                      cp[j], cfg, f0[j], n0[j]);
+                    r[j] = __fmul_rn(q[j].scale, Rt);
+                }
+                if (valid) stv<4>(gi, r);
+                gi -= M;
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ring->empty[s]));
+            release_chunk(ring, k, pc.stages, lane);
         }
         if (ok && valid) {
 #pragma unroll
@@ -298,32 +285,33 @@ lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, con
             }
         }
     }
-    ring_finish<S>(ring);
+    ring_finish(ring, pc.stages);
 }
 
 // ===========================================================================
 // leaky integrator
 // ===========================================================================
-template <int NW, int TC, int S>
-__global__ void __launch_bounds__((NW + 1) * 32)
-leaky_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A, const int tiles_m)
+template <int NW>
+__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW>::value)
+leaky_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A, const int tiles_m, const PipeCfg pc)
 {
     using G = TileGeom<NW>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float *stages = reinterpret_cast<float *>(smem_raw);
-    Ring<S> *ring = reinterpret_cast<Ring<S> *>(smem_raw + (size_t)S * TC * G::W * sizeof(float));
-    ring_init<S>(ring, NW);
+    const int tensor_floats = pc.tc * G::W;
+    Ring *ring = reinterpret_cast<Ring *>(smem_raw + (size_t)pc.stages * tensor_floats * sizeof(float));
+    ring_init(ring, pc.stages, NW);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.x / tiles_m;
     const int m0 = (blockIdx.x - b * tiles_m) * G::W;
     const int T = (int)A.T;
-    const int nchunks = (T + TC - 1) / TC;
+    const int nchunks = (T + pc.tc - 1) / pc.tc;
 
     if (warp == NW) {
         if (lane == 0) {
             const CUtensorMap *mp[1] = {&maps.m[0]};
-            produce<NW, TC, S>(ring, stages, mp, 1, nchunks, m0, b);
+            produce<NW>(ring, stages, mp, 1, nchunks, m0, b, pc, false);
         }
     } else {
         const int c = threadIdx.x * 4;
@@ -338,62 +326,58 @@ leaky_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A,
             sc[j] = A.scale.get(b, mm + j, 1.0f);
             v[j] = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
         }
-        float *out = A.out + ((int64_t)b * T) * A.M + mm;
+        const int64_t M = A.M;
+        float *out = A.out + ((int64_t)b * T) * M + mm;
+        const int col = tile_col_off<NW>(pc.tc, c);
         bool ok = true;
-        for (int k = 0; k < nchunks && ok; ++k) {
-            const int s = k % S;
-            if (!mbar_wait(smem_u32(&ring->full[s]), (uint32_t)((k / S) & 1))) {
-                report_timeout(EXB_STATUS_FULL_WAIT);
-                ring->aborted = 1;
-                ok = false;
-                break;
-            }
-            const float *st = stages + (size_t)s * TC * G::W;
-            const int tmax = min(TC, T - k * TC);
+        for (int k = 0; k < nchunks; ++k) {
+            if (!wait_chunk(ring, k, pc.stages)) { ok = false; break; }
+            const float *st = stages + (size_t)(k % pc.stages) * tensor_floats + col;
+            const int tmax = min(pc.tc, T - k * pc.tc);
+#pragma unroll 4
+            for (int tt = 0; tt < tmax; ++tt) {
+                float xs[4];
+                unpack(xs, lds128(st + tt * G::BW));
 #pragma unroll
-            for (int tt = 0; tt < TC; ++tt) {
-                if (tt < tmax) {
-                    const float4 x = lds128(st + tile_off<NW, TC>(tt, c));
-                    const float xs[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) v[j] = __fmaf_rn(v[j], al[j], __fmul_rn(sc[j], xs[j]));
-                    if (valid) stv<4>(out + (int64_t)(k * TC + tt) * A.M, v);
-                }
+                for (int j = 0; j < 4; ++j) v[j] = __fmaf_rn(v[j], al[j], __fmul_rn(sc[j], xs[j]));
+                if (valid) stv<4>(out, v);
+                out += M;
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ring->empty[s]));
+            release_chunk(ring, k, pc.stages, lane);
         }
         if (ok && valid && A.v_last) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) A.v_last[n + j] = v[j];
         }
     }
-    ring_finish<S>(ring);
+    ring_finish(ring, pc.stages);
 }
 
-template <bool WA, bool WS, int NW, int TC, int S>
-__global__ void __launch_bounds__((NW + 1) * 32)
-leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A, const int tiles_m, const int nmaps)
+template <bool WA, bool WS, int NW>
+__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, (WA && WS)>::value)
+leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A, const int tiles_m, const int nmaps,
+                     const PipeCfg pc)
 {
     using G = TileGeom<NW>;
-    constexpr int TENSOR_FLOATS = TC * G::W;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float *stages = reinterpret_cast<float *>(smem_raw);
-    Ring<S> *ring = reinterpret_cast<Ring<S> *>(smem_raw + (size_t)S * nmaps * TENSOR_FLOATS * sizeof(float));
-    ring_init<S>(ring, NW);
+    const int tensor_floats = pc.tc * G::W;
+    const int stage_floats = nmaps * tensor_floats;
+    Ring *ring = reinterpret_cast<Ring *>(smem_raw + (size_t)pc.stages * stage_floats * sizeof(float));
+    ring_init(ring, pc.stages, NW);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.x / tiles_m;
     const int m0 = (blockIdx.x - b * tiles_m) * G::W;
     const int T = (int)A.T;
-    const int nchunks = (T + TC - 1) / TC;
+    const int nchunks = (T + pc.tc - 1) / pc.tc;
     // stage layout: [grad_out]([out])([input])
     const int i_x = WA ? 2 : 1;
 
     if (warp == NW) {
         if (lane == 0) {
             const CUtensorMap *mp[5] = {&maps.m[0], &maps.m[1], &maps.m[2], &maps.m[3], &maps.m[4]};
-            produce_reverse<NW, TC, S>(ring, stages, mp, nmaps, nchunks, m0, b);
+            produce<NW>(ring, stages, mp, nmaps, nchunks, m0, b, pc, true);
         }
     } else {
         const int c = threadIdx.x * 4;
@@ -409,49 +393,38 @@ leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A,
             G_[j] = 0.0f; ag[j] = 0.0f; sg[j] = 0.0f;
             glast[j] = A.g_last ? __ldg(A.g_last + n + j) : 0.0f;
         }
-        float *gi = A.grad_input + ((int64_t)b * T) * A.M + mm;
+        const int64_t M = A.M;
+        float *gi_base = A.grad_input + ((int64_t)b * T) * M + mm;
+        const int col = tile_col_off<NW>(pc.tc, c);
         bool ok = true;
-        for (int k = 0; k < nchunks && ok; ++k) {
-            const int s = k % S;
-            if (!mbar_wait(smem_u32(&ring->full[s]), (uint32_t)((k / S) & 1))) {
-                report_timeout(EXB_STATUS_FULL_WAIT);
-                ring->aborted = 1;
-                ok = false;
-                break;
-            }
-            const float *stg = stages + (size_t)s * nmaps * TENSOR_FLOATS;
+        for (int k = 0; k < nchunks; ++k) {
+            if (!wait_chunk(ring, k, pc.stages)) { ok = false; break; }
+            const float *stg = stages + (size_t)(k % pc.stages) * stage_floats + col;
             const int chunk = nchunks - 1 - k;
-            const int tmax = min(TC, T - chunk * TC);
+            const int tmax = min(pc.tc, T - chunk * pc.tc);
+            float *gi = gi_base + (int64_t)(chunk * pc.tc + tmax - 1) * M;
+#pragma unroll 4
+            for (int tt = tmax - 1; tt >= 0; --tt) {
+                const float *e = stg + tt * G::BW;
+                float go[4];
+                float vo[4] = {0.0f, 0.0f, 0.0f, 0.0f}, xx[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                unpack(go, lds128(e));
+                if (WA) unpack(vo, lds128(e + tensor_floats));
+                if (WS) unpack(xx, lds128(e + i_x * tensor_floats));
+                const bool last = (chunk * pc.tc + tt == T - 1);
+                float r[4];
 #pragma unroll
-            for (int tt = TC - 1; tt >= 0; --tt) {
-                if (tt < tmax) {
-                    const int o = tile_off<NW, TC>(tt, c);
-                    const float4 g4 = lds128(stg + o);
-                    float go[4] = {g4.x, g4.y, g4.z, g4.w};
-                    float vo[4] = {0.0f, 0.0f, 0.0f, 0.0f}, xx[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    if (WA) {
-                        const float4 t4 = lds128(stg + TENSOR_FLOATS + o);
-                        vo[0] = t4.x; vo[1] = t4.y; vo[2] = t4.z; vo[3] = t4.w;
-                    }
-                    if (WS) {
-                        const float4 t4 = lds128(stg + i_x * TENSOR_FLOATS + o);
-                        xx[0] = t4.x; xx[1] = t4.y; xx[2] = t4.z; xx[3] = t4.w;
-                    }
-                    const int t = chunk * TC + tt;
-                    float r[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if (t == T - 1) go[j] = __fadd_rn(go[j], glast[j]);
-                        if (WA) ag[j] = __fmaf_rn(G_[j], vo[j], ag[j]);
-                        G_[j] = __fmaf_rn(G_[j], al[j], go[j]);
-                        if (WS) sg[j] = __fmaf_rn(G_[j], xx[j], sg[j]);
-                        r[j] = __fmul_rn(sc[j], G_[j]);
-                    }
-                    if (valid) stv<4>(gi + (int64_t)t * A.M, r);
+                for (int j = 0; j < 4; ++j) {
+                    if (last) go[j] = __fadd_rn(go[j], glast[j]);
+                    if (WA) ag[j] = __fmaf_rn(G_[j], vo[j], ag[j]);
+                    G_[j] = __fmaf_rn(G_[j], al[j], go[j]);
+                    if (WS) sg[j] = __fmaf_rn(G_[j], xx[j], sg[j]);
+                    r[j] = __fmul_rn(sc[j], G_[j]);
                 }
+                if (valid) stv<4>(gi, r);
+                gi -= M;
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ring->empty[s]));
+            release_chunk(ring, k, pc.stages, lane);
         }
         if (ok && valid) {
 #pragma unroll
@@ -462,7 +435,7 @@ leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A,
             }
         }
     }
-    ring_finish<S>(ring);
+    ring_finish(ring, pc.stages);
 }
 
 // ===========================================================================
@@ -498,12 +471,38 @@ bool make_btm_tensor_map(CUtensorMap *map, const float *base, int64_t B, int64_t
     return r == CUDA_SUCCESS;
 }
 
-// Tile shape choice: wide tiles (512 neurons, 4+1 warps) when they alone fill the
-// GPU, narrow tiles (128 neurons, 1+1 warps, longer time chunks) otherwise.
+// Tile shape choice: wide tiles (512 neurons, 4+1 warps) when they alone fill the GPU,
+// narrow tiles (128 neurons, 1+1 warps, longer time chunks) otherwise.  The pipeline shape
+// (time steps per stage, stages) keeps one stage at about 8-16 KB.  EXB_TMA_TC / EXB_TMA_STAGES
+// in the environment override it (tuning aid).
 static bool use_wide(int64_t B, int64_t M)
 {
     const int64_t wide_tiles = B * ((M + 511) / 512);
     return wide_tiles >= 2 * 148;
+}
+
+static int env_int(const char *name, int dflt)
+{
+    const char *v = getenv(name);
+    return (v && *v) ? atoi(v) : dflt;
+}
+
+static PipeCfg pipe_cfg(bool wide, int nmaps)
+{
+    static const int env_tc = env_int("EXB_TMA_TC", 0);
+    static const int env_st = env_int("EXB_TMA_STAGES", 0);
+    PipeCfg pc;
+    const int w = wide ? 512 : 128;
+    // target ~8 KB per stage across all streamed tensors
+    int tc = (8 * 1024) / (w * 4 * nmaps);
+    if (tc < 2) tc = 2;
+    if (!wide && tc > 32) tc = 32;
+    pc.tc = tc;
+    pc.stages = 4;
+    if (env_tc > 0) pc.tc = env_tc;
+    if (env_st > 1 && env_st <= MAX_STAGES) pc.stages = env_st;
+    if (pc.tc > 256) pc.tc = 256;
+    return pc;
 }
 
 template <typename K>
@@ -513,18 +512,26 @@ static cudaError_t set_smem(K kern, size_t bytes)
     return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 }
 
-template <int RESET, int NW, int TC, int S>
+static bool eligible(int64_t B, int64_t T, int64_t M)
+{
+    return M % 4 == 0 && B * ((M + 127) / 128) <= 0x7fffffffll && T <= 0x7fffffffll;
+}
+
+template <int RESET, int NW>
 static cudaError_t run_lif_fwd(const LifFwdArgs &a, cudaStream_t s, bool *used)
 {
     using G = TileGeom<NW>;
+    const PipeCfg pc = pipe_cfg(NW == 4, 1);
     TmaMaps maps;
-    if (!make_btm_tensor_map(&maps.m[0], a.input, a.B, a.T, a.M, G::BW, TC)) return cudaSuccess;
+    if (!make_btm_tensor_map(&maps.m[0], a.input, a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
+    for (int i = 1; i < 5; ++i) maps.m[i] = maps.m[0];
     const int tiles_m = (int)((a.M + G::W - 1) / G::W);
-    const size_t smem = tma_smem_bytes<NW, TC, S>(1);
-    auto kern = lif_fwd_tma_kernel<RESET, NW, TC, S>;
+    const size_t smem = tma_smem_bytes<NW>(1, pc);
+    if (smem > 200 * 1024) return cudaSuccess;
+    auto kern = lif_fwd_tma_kernel<RESET, NW>;
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
-    kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m);
+    kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m, pc);
     *used = true;
     return cudaPeekAtLastError();
 }
@@ -532,15 +539,14 @@ static cudaError_t run_lif_fwd(const LifFwdArgs &a, cudaStream_t s, bool *used)
 cudaError_t launch_lif_forward_tma(const LifFwdArgs &a, int reset_mode, cudaStream_t s, bool *used)
 {
     *used = false;
-    if (a.M % 4 || !aligned16(a.spikes) || !aligned16(a.v_mem) || !aligned16(a.input)) return cudaSuccess;
-    if (a.B * ((a.M + 127) / 128) > 0x7fffffffll || a.T > 0x7fffffffll) return cudaSuccess;
+    if (!eligible(a.B, a.T, a.M) || !aligned16(a.spikes) || !aligned16(a.v_mem) || !aligned16(a.input)) return cudaSuccess;
     const bool wide = use_wide(a.B, a.M);
     if (reset_mode == EXB_RESET_SUBTRACT)
-        return wide ? run_lif_fwd<EXB_RESET_SUBTRACT, 4, 8, 4>(a, s, used) : run_lif_fwd<EXB_RESET_SUBTRACT, 1, 32, 4>(a, s, used);
-    return wide ? run_lif_fwd<EXB_RESET_TO_VALUE, 4, 8, 4>(a, s, used) : run_lif_fwd<EXB_RESET_TO_VALUE, 1, 32, 4>(a, s, used);
+        return wide ? run_lif_fwd<EXB_RESET_SUBTRACT, 4>(a, s, used) : run_lif_fwd<EXB_RESET_SUBTRACT, 1>(a, s, used);
+    return wide ? run_lif_fwd<EXB_RESET_TO_VALUE, 4>(a, s, used) : run_lif_fwd<EXB_RESET_TO_VALUE, 1>(a, s, used);
 }
 
-template <int SURR, int RESET, bool WA, bool WS, int NW, int TC, int S>
+template <int SURR, int RESET, bool WA, bool WS, int NW>
 static cudaError_t run_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
 {
     using G = TileGeom<NW>;
@@ -550,16 +556,17 @@ static cudaError_t run_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
     if (a.gv) ptrs[nmaps++] = a.gv;
     if (SURR == EXB_SURR_GENERIC) ptrs[nmaps++] = a.surr;
     if (WS) ptrs[nmaps++] = a.input;
+    const PipeCfg pc = pipe_cfg(NW == 4, nmaps);
     for (int i = 0; i < nmaps; ++i)
-        if (!make_btm_tensor_map(&maps.m[i], ptrs[i], a.B, a.T, a.M, G::BW, TC)) return cudaSuccess;
+        if (!make_btm_tensor_map(&maps.m[i], ptrs[i], a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
     for (int i = nmaps; i < 5; ++i) maps.m[i] = maps.m[0];
     const int tiles_m = (int)((a.M + G::W - 1) / G::W);
-    const size_t smem = tma_smem_bytes<NW, TC, S>(nmaps);
+    const size_t smem = tma_smem_bytes<NW>(nmaps, pc);
     if (smem > 200 * 1024) return cudaSuccess;
-    auto kern = lif_bwd_tma_kernel<SURR, RESET, WA, WS, NW, TC, S>;
+    auto kern = lif_bwd_tma_kernel<SURR, RESET, WA, WS, NW>;
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
-    kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m, nmaps);
+    kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m, nmaps, pc);
     *used = true;
     return cudaPeekAtLastError();
 }
@@ -567,8 +574,8 @@ static cudaError_t run_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
 template <int SURR, int RESET, bool WA, bool WS>
 static cudaError_t pick_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
 {
-    return use_wide(a.B, a.M) ? run_lif_bwd<SURR, RESET, WA, WS, 4, 4, 4>(a, s, used)
-                              : run_lif_bwd<SURR, RESET, WA, WS, 1, 16, 4>(a, s, used);
+    return use_wide(a.B, a.M) ? run_lif_bwd<SURR, RESET, WA, WS, 4>(a, s, used)
+                              : run_lif_bwd<SURR, RESET, WA, WS, 1>(a, s, used);
 }
 
 template <int SURR, int RESET>
@@ -595,24 +602,26 @@ static cudaError_t surr_lif_bwd(const LifBwdArgs &a, int kind, cudaStream_t s, b
 cudaError_t launch_lif_backward_tma(const LifBwdArgs &a, int reset_mode, int surr_kind, cudaStream_t s, bool *used)
 {
     *used = false;
-    if (a.M % 4 || !aligned16(a.grad_input)) return cudaSuccess;
-    if (a.B * ((a.M + 127) / 128) > 0x7fffffffll || a.T > 0x7fffffffll) return cudaSuccess;
+    if (!eligible(a.B, a.T, a.M) || !aligned16(a.grad_input)) return cudaSuccess;
     return reset_mode == EXB_RESET_SUBTRACT ? surr_lif_bwd<EXB_RESET_SUBTRACT>(a, surr_kind, s, used)
                                             : surr_lif_bwd<EXB_RESET_TO_VALUE>(a, surr_kind, s, used);
 }
 
-template <int NW, int TC, int S>
+template <int NW>
 static cudaError_t run_leaky_fwd(const LeakyFwdArgs &a, cudaStream_t s, bool *used)
 {
     using G = TileGeom<NW>;
+    const PipeCfg pc = pipe_cfg(NW == 4, 1);
     TmaMaps maps;
-    if (!make_btm_tensor_map(&maps.m[0], a.input, a.B, a.T, a.M, G::BW, TC)) return cudaSuccess;
+    if (!make_btm_tensor_map(&maps.m[0], a.input, a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
+    for (int i = 1; i < 5; ++i) maps.m[i] = maps.m[0];
     const int tiles_m = (int)((a.M + G::W - 1) / G::W);
-    const size_t smem = tma_smem_bytes<NW, TC, S>(1);
-    auto kern = leaky_fwd_tma_kernel<NW, TC, S>;
+    const size_t smem = tma_smem_bytes<NW>(1, pc);
+    if (smem > 200 * 1024) return cudaSuccess;
+    auto kern = leaky_fwd_tma_kernel<NW>;
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
-    kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m);
+    kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m, pc);
     *used = true;
     return cudaPeekAtLastError();
 }
@@ -620,12 +629,11 @@ static cudaError_t run_leaky_fwd(const LeakyFwdArgs &a, cudaStream_t s, bool *us
 cudaError_t launch_leaky_forward_tma(const LeakyFwdArgs &a, cudaStream_t s, bool *used)
 {
     *used = false;
-    if (a.M % 4 || !aligned16(a.out) || !aligned16(a.input)) return cudaSuccess;
-    if (a.B * ((a.M + 127) / 128) > 0x7fffffffll || a.T > 0x7fffffffll) return cudaSuccess;
-    return use_wide(a.B, a.M) ? run_leaky_fwd<4, 8, 4>(a, s, used) : run_leaky_fwd<1, 32, 4>(a, s, used);
+    if (!eligible(a.B, a.T, a.M) || !aligned16(a.out) || !aligned16(a.input)) return cudaSuccess;
+    return use_wide(a.B, a.M) ? run_leaky_fwd<4>(a, s, used) : run_leaky_fwd<1>(a, s, used);
 }
 
-template <bool WA, bool WS, int NW, int TC, int S>
+template <bool WA, bool WS, int NW>
 static cudaError_t run_leaky_bwd(const LeakyBwdArgs &a, cudaStream_t s, bool *used)
 {
     using G = TileGeom<NW>;
@@ -634,15 +642,17 @@ static cudaError_t run_leaky_bwd(const LeakyBwdArgs &a, cudaStream_t s, bool *us
     int nmaps = 1;
     if (WA) ptrs[nmaps++] = a.out;
     if (WS) ptrs[nmaps++] = a.input;
+    const PipeCfg pc = pipe_cfg(NW == 4, nmaps);
     for (int i = 0; i < nmaps; ++i)
-        if (!make_btm_tensor_map(&maps.m[i], ptrs[i], a.B, a.T, a.M, G::BW, TC)) return cudaSuccess;
+        if (!make_btm_tensor_map(&maps.m[i], ptrs[i], a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
     for (int i = nmaps; i < 5; ++i) maps.m[i] = maps.m[0];
     const int tiles_m = (int)((a.M + G::W - 1) / G::W);
-    const size_t smem = tma_smem_bytes<NW, TC, S>(nmaps);
-    auto kern = leaky_bwd_tma_kernel<WA, WS, NW, TC, S>;
+    const size_t smem = tma_smem_bytes<NW>(nmaps, pc);
+    if (smem > 200 * 1024) return cudaSuccess;
+    auto kern = leaky_bwd_tma_kernel<WA, WS, NW>;
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
-    kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m, nmaps);
+    kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m, nmaps, pc);
     *used = true;
     return cudaPeekAtLastError();
 }
@@ -650,14 +660,13 @@ static cudaError_t run_leaky_bwd(const LeakyBwdArgs &a, cudaStream_t s, bool *us
 template <bool WA, bool WS>
 static cudaError_t pick_leaky_bwd(const LeakyBwdArgs &a, cudaStream_t s, bool *used)
 {
-    return use_wide(a.B, a.M) ? run_leaky_bwd<WA, WS, 4, 4, 4>(a, s, used) : run_leaky_bwd<WA, WS, 1, 16, 4>(a, s, used);
+    return use_wide(a.B, a.M) ? run_leaky_bwd<WA, WS, 4>(a, s, used) : run_leaky_bwd<WA, WS, 1>(a, s, used);
 }
 
 cudaError_t launch_leaky_backward_tma(const LeakyBwdArgs &a, cudaStream_t s, bool *used)
 {
     *used = false;
-    if (a.M % 4 || !aligned16(a.grad_input)) return cudaSuccess;
-    if (a.B * ((a.M + 127) / 128) > 0x7fffffffll || a.T > 0x7fffffffll) return cudaSuccess;
+    if (!eligible(a.B, a.T, a.M) || !aligned16(a.grad_input)) return cudaSuccess;
     const bool wa = a.grad_alpha != nullptr, ws = a.grad_scale != nullptr;
     if (wa && ws) return pick_leaky_bwd<true, true>(a, s, used);
     if (wa) return pick_leaky_bwd<true, false>(a, s, used);

@@ -46,7 +46,8 @@ class IAF(LIF):
 
     @property
     def alpha_mem_calculated(self):
-        return torch.tensor(1.0).to(self.v_mem.device)
+        # created on the device (no host-to-device copy, which would stall the launch queue)
+        return torch.ones((), device=self.v_mem.device)
 
     @property
     def _param_dict(self) -> dict:

@@ -48,8 +48,12 @@ def _flat_param(value, trailing: Tuple[int, ...], batch: int, device) -> Optiona
     """
     if value is None:
         return None
+    if isinstance(value, (int, float)):
+        # A fill kernel instead of a host-to-device copy: the copy would wait for all queued work.
+        return torch.full((1,), float(value), dtype=torch.float32, device=device)
     t = value if isinstance(value, torch.Tensor) else torch.as_tensor(value, dtype=torch.float32)
-    t = t.to(device=device, dtype=torch.float32)
+    if t.device != torch.device(device) or t.dtype != torch.float32:
+        t = t.to(device=device, dtype=torch.float32)
     if t.numel() == 1:
         return t.reshape(1)
     try:

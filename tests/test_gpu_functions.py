@@ -268,7 +268,7 @@ def test_layer_exp_leak(train_alphas, norm_input, decay_early):
     if decay_early and not norm_input:
         other = ExpLeak(tau_mem=30.0, decay_early=False).cuda()
         want = other(x.detach()) * float(np.exp(-1 / 30.0))
-        assert rel_err(out.detach().cpu().numpy(), want.cpu().numpy()) < TOL
+        assert rel_err(out.detach().cpu().numpy(), want.detach().cpu().numpy()) < TOL
 
 
 def test_layer_rejects_cpu_and_bad_config():
