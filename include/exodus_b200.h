@@ -147,6 +147,32 @@ int exb_leaky_backward(float *grad_input, float *grad_alpha, float *grad_init, f
                        int64_t B, int64_t T, int64_t M, int layout,
                        int device, void *stream);
 
+/* Time-parallel variants of the leaky integrator for long sequences with few neurons
+ * (time-major layout only).  The reference has one thread per neuron walking through all of
+ * T (cuda/leaky_kernels.h:41-56, 96-108), which leaves the GPU empty when N is small; here
+ * the time axis is cut into segments that run in different CTAs and exchange their end states
+ * through `workspace`, caller-provided device scratch memory of at least
+ * exb_leaky_scan_workspace_bytes(B, T, M) bytes, 16-byte aligned.  That function returns 0 when
+ * splitting is not applicable (short T, M % 4 != 0); the scan entry points then return
+ * EXB_ERR_UNSUPPORTED and the caller uses exb_leaky_forward / exb_leaky_backward.  Arguments
+ * and results are those of the plain entry points; results agree to rounding (the carry
+ * across segments is folded in a different order). */
+int64_t exb_leaky_scan_workspace_bytes(int64_t B, int64_t T, int64_t M);
+
+int exb_leaky_forward_scan(float *out, const float *input, const float *v_init,
+                           const float *alpha, int alpha_mode,
+                           const float *in_scale, int in_scale_mode,
+                           float *v_last, void *workspace, int64_t workspace_bytes,
+                           int64_t B, int64_t T, int64_t M, int device, void *stream);
+
+int exb_leaky_backward_scan(float *grad_input, float *grad_alpha, float *grad_init, float *grad_scale,
+                            const float *grad_out, const float *grad_v_last,
+                            const float *out, const float *input, const float *v_init,
+                            const float *alpha, int alpha_mode,
+                            const float *in_scale, int in_scale_mode,
+                            void *workspace, int64_t workspace_bytes,
+                            int64_t B, int64_t T, int64_t M, int device, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

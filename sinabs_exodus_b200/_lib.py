@@ -38,6 +38,7 @@ _lib: Optional[ctypes.CDLL] = None
 EXPORTS = (
     "exb_version", "exb_last_error", "exb_status_string", "exb_device_status",
     "exb_lif_forward", "exb_lif_backward", "exb_leaky_forward", "exb_leaky_backward",
+    "exb_leaky_scan_workspace_bytes", "exb_leaky_forward_scan", "exb_leaky_backward_scan",
 )
 
 
@@ -76,6 +77,13 @@ def load() -> ctypes.CDLL:
     lib.exb_leaky_backward.restype = _i
     lib.exb_leaky_backward.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                        _vp, _i, _vp, _i] + geometry
+    lib.exb_leaky_scan_workspace_bytes.restype = _i64
+    lib.exb_leaky_scan_workspace_bytes.argtypes = [_i64, _i64, _i64]
+    scan_tail = [_vp, _i64, _i64, _i64, _i64, _i, _vp]
+    lib.exb_leaky_forward_scan.restype = _i
+    lib.exb_leaky_forward_scan.argtypes = [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp] + scan_tail
+    lib.exb_leaky_backward_scan.restype = _i
+    lib.exb_leaky_backward_scan.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i] + scan_tail
     _lib = lib
     return lib
 
@@ -182,3 +190,30 @@ def leaky_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad
                                    ptr(alpha[0]), alpha[1], ptr(in_scale[0]), in_scale[1],
                                    B, T, M, layout, dev.index, _stream(dev))
     _check(st, "exb_leaky_backward")
+
+
+def leaky_scan_workspace_bytes(B: int, T: int, M: int) -> int:
+    """Scratch bytes the time-parallel leaky scan needs for this shape; 0 when it does not apply."""
+    return int(load().exb_leaky_scan_workspace_bytes(B, T, M))
+
+
+def leaky_forward_scan(out, inp, v_init, alpha: Tuple, in_scale: Tuple, v_last, workspace, B: int, T: int,
+                       M: int) -> None:
+    dev = _require_cuda(out, inp, v_init, alpha[0], in_scale[0], v_last)
+    st = load().exb_leaky_forward_scan(ptr(out), ptr(inp), ptr(v_init), ptr(alpha[0]), alpha[1],
+                                       ptr(in_scale[0]), in_scale[1], ptr(v_last),
+                                       workspace.data_ptr(), workspace.numel() * workspace.element_size(),
+                                       B, T, M, dev.index, _stream(dev))
+    _check(st, "exb_leaky_forward_scan")
+
+
+def leaky_backward_scan(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad_v_last, out, inp, v_init,
+                        alpha: Tuple, in_scale: Tuple, workspace, B: int, T: int, M: int) -> None:
+    dev = _require_cuda(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad_v_last, out, inp, v_init,
+                        alpha[0], in_scale[0])
+    st = load().exb_leaky_backward_scan(ptr(grad_input), ptr(grad_alpha), ptr(grad_init), ptr(grad_scale),
+                                        ptr(grad_out), ptr(grad_v_last), ptr(out), ptr(inp), ptr(v_init),
+                                        ptr(alpha[0]), alpha[1], ptr(in_scale[0]), in_scale[1],
+                                        workspace.data_ptr(), workspace.numel() * workspace.element_size(),
+                                        B, T, M, dev.index, _stream(dev))
+    _check(st, "exb_leaky_backward_scan")

@@ -227,4 +227,69 @@ int exb_leaky_backward(float *grad_input, float *grad_alpha, float *grad_init, f
     return launch_status(exb::launch_leaky_backward(a, layout, (cudaStream_t)stream), "exb_leaky_backward");
 }
 
+int64_t exb_leaky_scan_workspace_bytes(int64_t B, int64_t T, int64_t M)
+{
+    if (B <= 0 || T <= 0 || M <= 0) return 0;
+    return exb::leaky_scan_workspace_bytes(B, T, M);
+}
+
+int exb_leaky_forward_scan(float *out, const float *input, const float *v_init,
+                           const float *alpha, int alpha_mode,
+                           const float *in_scale, int in_scale_mode,
+                           float *v_last, void *workspace, int64_t workspace_bytes,
+                           int64_t B, int64_t T, int64_t M, int device, void *stream)
+{
+    if (int st = check_geometry(B, T, M, EXB_LAYOUT_BTM)) return st;
+    if (!out || !input || !alpha) return fail(EXB_ERR_ARG, "exb_leaky_forward_scan: out, input and alpha are required");
+    if (!mode_ok(alpha_mode) || (in_scale && !mode_ok(in_scale_mode)))
+        return fail(EXB_ERR_ARG, "exb_leaky_forward_scan: bad parameter mode");
+    if (!workspace) return fail(EXB_ERR_ARG, "exb_leaky_forward_scan: workspace is required");
+    if (B == 0 || M == 0 || T == 0) return EXB_OK;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_leaky_forward_scan: cannot select device %d", device);
+    exb::LeakyFwdArgs a;
+    a.out = out; a.input = input; a.v_init = v_init;
+    a.alpha = exb::make_param(alpha, alpha_mode, M);
+    a.scale = exb::make_param(in_scale, in_scale_mode, M);
+    a.v_last = v_last;
+    a.B = B; a.T = T; a.M = M;
+    bool used = false;
+    cudaError_t e = exb::launch_leaky_forward_scan(a, workspace, workspace_bytes, (cudaStream_t)stream, &used);
+    if (e != cudaSuccess) return launch_status(e, "exb_leaky_forward_scan");
+    if (!used) return fail(EXB_ERR_UNSUPPORTED, "exb_leaky_forward_scan: shape, alignment or workspace not eligible");
+    return EXB_OK;
+}
+
+int exb_leaky_backward_scan(float *grad_input, float *grad_alpha, float *grad_init, float *grad_scale,
+                            const float *grad_out, const float *grad_v_last,
+                            const float *out, const float *input, const float *v_init,
+                            const float *alpha, int alpha_mode,
+                            const float *in_scale, int in_scale_mode,
+                            void *workspace, int64_t workspace_bytes,
+                            int64_t B, int64_t T, int64_t M, int device, void *stream)
+{
+    if (int st = check_geometry(B, T, M, EXB_LAYOUT_BTM)) return st;
+    if (!grad_input || !grad_out || !alpha)
+        return fail(EXB_ERR_ARG, "exb_leaky_backward_scan: grad_input, grad_out and alpha are required");
+    if (!mode_ok(alpha_mode) || (in_scale && !mode_ok(in_scale_mode)))
+        return fail(EXB_ERR_ARG, "exb_leaky_backward_scan: bad parameter mode");
+    if (grad_alpha && !out) return fail(EXB_ERR_ARG, "exb_leaky_backward_scan: grad_alpha needs `out`");
+    if (grad_scale && !input) return fail(EXB_ERR_ARG, "exb_leaky_backward_scan: grad_scale needs `input`");
+    if (!workspace) return fail(EXB_ERR_ARG, "exb_leaky_backward_scan: workspace is required");
+    if (B == 0 || M == 0 || T == 0) return EXB_OK;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_leaky_backward_scan: cannot select device %d", device);
+    exb::LeakyBwdArgs a;
+    a.grad_input = grad_input; a.grad_alpha = grad_alpha; a.grad_init = grad_init; a.grad_scale = grad_scale;
+    a.go = grad_out; a.g_last = grad_v_last; a.out = out; a.input = input; a.v_init = v_init;
+    a.alpha = exb::make_param(alpha, alpha_mode, M);
+    a.scale = exb::make_param(in_scale, in_scale_mode, M);
+    a.B = B; a.T = T; a.M = M;
+    bool used = false;
+    cudaError_t e = exb::launch_leaky_backward_scan(a, workspace, workspace_bytes, (cudaStream_t)stream, &used);
+    if (e != cudaSuccess) return launch_status(e, "exb_leaky_backward_scan");
+    if (!used) return fail(EXB_ERR_UNSUPPORTED, "exb_leaky_backward_scan: shape, alignment or workspace not eligible");
+    return EXB_OK;
+}
+
 }  // extern "C"

@@ -52,6 +52,13 @@ cudaError_t launch_lif_forward_tma(const LifFwdArgs &a, int reset_mode, cudaStre
 cudaError_t launch_lif_backward_tma(const LifBwdArgs &a, int reset_mode, int surr_kind, cudaStream_t s, bool *used);
 cudaError_t launch_leaky_forward_tma(const LeakyFwdArgs &a, cudaStream_t s, bool *used);
 cudaError_t launch_leaky_backward_tma(const LeakyBwdArgs &a, cudaStream_t s, bool *used);
+// Time-parallel leaky integrator (time-major layout): the time axis is cut into segments that
+// run in different CTAs.  Needs caller-provided scratch memory of leaky_scan_workspace_bytes().
+int64_t leaky_scan_workspace_bytes(int64_t B, int64_t T, int64_t M);
+cudaError_t launch_leaky_forward_scan(const LeakyFwdArgs &a, void *workspace, int64_t workspace_bytes, cudaStream_t s,
+                                      bool *used);
+cudaError_t launch_leaky_backward_scan(const LeakyBwdArgs &a, void *workspace, int64_t workspace_bytes, cudaStream_t s,
+                                       bool *used);
 cudaError_t read_device_status(cudaStream_t s, unsigned int *out);
 // EXB_DISABLE_TMA=1 in the environment forces the plain-load kernels (debugging aid).
 bool tma_enabled();

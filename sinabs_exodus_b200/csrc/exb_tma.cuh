@@ -96,6 +96,7 @@ struct Ring {
     uint64_t empty[MAX_STAGES];
     int issued;     // chunks the producer has issued (written before the final barrier)
     int aborted;    // set by any thread whose wait ran out
+    unsigned int ticket;   // work item of this CTA (time-parallel scan kernels)
 };
 
 __device__ __forceinline__ void ring_init(Ring *r, int stages, int consumer_warps)

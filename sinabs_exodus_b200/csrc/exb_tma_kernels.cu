@@ -1,8 +1,9 @@
 // TMA-staged time-major kernels (spike scan forward, fused EXODUS backward,
 // leaky integrator forward and backward).  See exb_tma.cuh for the pipeline.
 //
-// Tile geometry: NW consumer warps, every consumer thread owns 4 adjacent
-// neurons, so a CTA covers W = NW*128 neurons of one batch item.  One stage
+// Tile geometry: NW consumer warps, every consumer thread owns V (4 or 1)
+// adjacent neurons, so a CTA covers W = NW*32*V neurons of one batch item.
+// V = 1 is for problems with too few neurons to fill the GPU four per thread.  One stage
 // holds TC time steps of every streamed tensor; a tensor's part of the stage
 // is W/BW boxes of [TC][BW] floats (a TMA box is at most 256 elements wide).
 #include "exb_kernels.cuh"
@@ -13,9 +14,9 @@
 
 namespace exb {
 
-template <int NW>
+template <int NW, int V>
 struct TileGeom {
-    static constexpr int W = NW * 128;
+    static constexpr int W = NW * 32 * V;
     static constexpr int BW = (W > 256) ? 256 : W;
     static constexpr int NBOX = W / BW;
 };
@@ -23,17 +24,17 @@ struct TileGeom {
 // Resident CTAs per SM the kernels are compiled for (caps registers at 64 per thread).
 // Light kernels fit 64 registers; the backward with alpha/scale gradients or an exponential
 // surrogate keeps four neurons' constants and accumulators live and gets 96.
-template <int NW, bool HEAVY = false>
+template <int NW, int V, bool HEAVY = false>
 struct MinBlocks {
-    static constexpr int value = (NW == 4) ? (HEAVY ? 4 : 6) : (HEAVY ? 10 : 16);
+    static constexpr int value = (V == 4) ? (HEAVY ? 4 : 6) : (HEAVY ? 6 : 8);
 };
 
 // Shared-memory float offset of neuron column c inside one tensor's part of a stage, at time
 // step 0 of the stage; consecutive time steps are BW floats apart.
-template <int NW>
+template <int NW, int V>
 __device__ __forceinline__ int tile_col_off(int tc, int c)
 {
-    using G = TileGeom<NW>;
+    using G = TileGeom<NW, V>;
     return (c / G::BW) * tc * G::BW + (c % G::BW);
 }
 
@@ -45,11 +46,11 @@ struct PipeCfg {
 
 // Producer: issues chunk k (k-th in processing order; `reverse` walks time backwards) of
 // `nmaps` tensors into stage k % S.
-template <int NW>
+template <int NW, int V>
 __device__ __forceinline__ void produce(Ring *ring, float *stages, const CUtensorMap *const *maps, int nmaps,
                                         int nchunks, int m0, int b, PipeCfg pc, bool reverse)
 {
-    using G = TileGeom<NW>;
+    using G = TileGeom<NW, V>;
     const int tensor_floats = pc.tc * G::W;
     const int stage_floats = nmaps * tensor_floats;
     const int S = pc.stages;
@@ -79,10 +80,10 @@ struct TmaMaps {
     CUtensorMap m[5];
 };
 
-template <int NW>
+template <int NW, int V>
 static size_t tma_smem_bytes(int nmaps, PipeCfg pc)
 {
-    return (size_t)pc.stages * nmaps * pc.tc * TileGeom<NW>::W * sizeof(float) + sizeof(Ring) + 128;
+    return (size_t)pc.stages * nmaps * pc.tc * TileGeom<NW, V>::W * sizeof(float) + sizeof(Ring) + 128;
 }
 
 // Consumer-side wait for chunk k; marks the ring aborted when the wait runs out.
@@ -100,19 +101,27 @@ __device__ __forceinline__ void release_chunk(Ring *ring, int k, int S, int lane
     if (lane == 0) mbar_arrive(smem_u32(&ring->empty[k % S]));
 }
 
-__device__ __forceinline__ void unpack(float (&d)[4], const float4 &t)
+// V floats of one consumer thread from a stage.
+template <int V>
+__device__ __forceinline__ void lds_vec(float (&d)[V], const float *p)
 {
-    d[0] = t.x; d[1] = t.y; d[2] = t.z; d[3] = t.w;
+    if (V == 4) {
+        const float4 t = *reinterpret_cast<const float4 *>(p);
+        d[0] = t.x; d[1] = t.y; d[2] = t.z; d[3] = t.w;
+    } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) d[j] = p[j];
+    }
 }
 
 // ===========================================================================
 // spike scan forward
 // ===========================================================================
-template <int RESET, int NW>
-__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW>::value)
+template <int RESET, int NW, int V>
+__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V>::value)
 lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, const int tiles_m, const PipeCfg pc)
 {
-    using G = TileGeom<NW>;
+    using G = TileGeom<NW, V>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float *stages = reinterpret_cast<float *>(smem_raw);
     const int tensor_floats = pc.tc * G::W;
@@ -128,19 +137,19 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
     if (warp == NW) {
         if (lane == 0) {
             const CUtensorMap *mp[1] = {&maps.m[0]};
-            produce<NW>(ring, stages, mp, 1, nchunks, m0, b, pc, false);
+            produce<NW, V>(ring, stages, mp, 1, nchunks, m0, b, pc, false);
         }
     } else {
-        const int c = threadIdx.x * 4;                 // column inside the tile
+        const int c = threadIdx.x * V;                 // column inside the tile
         const int64_t m = (int64_t)m0 + c;
-        const bool valid = m < A.M;                    // M % 4 == 0: all four neurons or none
+        const bool valid = m < A.M;                    // M % 4 == 0 and V in {1, 4}: all V neurons or none
         const int64_t mm = valid ? m : 0;
         const int64_t n = (int64_t)b * A.M + mm;
         const SpikeCfg cfg = make_spike_cfg(A.maxs);
-        Neuron q[4];
-        float v[4], af[4];
+        Neuron q[V];
+        float v[V], af[V];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < V; ++j) {
             q[j] = A.np.load(b, mm + j, cfg);
             v[j] = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
             af[j] = 0.0f;
@@ -149,7 +158,7 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
         float *sp = A.spikes + base;
         float *vm = A.v_mem + base;
         const int64_t M = A.M;
-        const int col = tile_col_off<NW>(pc.tc, c);
+        const int col = tile_col_off<NW, V>(pc.tc, c);
         SpikeTotal cnt;
         cnt.c32 = 0u; cnt.c64 = 0ull;
         bool ok = true;
@@ -159,13 +168,13 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
             const int tmax = min(pc.tc, T - k * pc.tc);
 #pragma unroll 4
             for (int tt = 0; tt < tmax; ++tt) {
-                float xs[4];
-                unpack(xs, lds128(st + tt * G::BW));
+                float xs[V];
+                lds_vec<V>(xs, st + tt * G::BW);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) lif_step<RESET>(v[j], af[j], xs[j], q[j], cfg, cnt);
+                for (int j = 0; j < V; ++j) lif_step<RESET>(v[j], af[j], xs[j], q[j], cfg, cnt);
                 if (valid) {
-                    stv<4>(sp, af);
-                    stv<4>(vm, v);
+                    stv<V>(sp, af);
+                    stv<V>(vm, v);
                 }
                 sp += M;
                 vm += M;
@@ -174,7 +183,7 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
         }
         if (ok && valid && A.v_post_last) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) A.v_post_last[n + j] = post_reset<RESET>(v[j], af[j], q[j]);
+            for (int j = 0; j < V; ++j) A.v_post_last[n + j] = post_reset<RESET>(v[j], af[j], q[j]);
         }
         if (A.spike_count) {
             const unsigned long long tot = warp_sum_u64((valid && ok) ? cnt.total() : 0ull);
@@ -187,12 +196,12 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
 // ===========================================================================
 // fused reverse-time backward
 // ===========================================================================
-template <int SURR, int RESET, bool WA, bool WS, int NW>
-__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, (WA || WS || SURR == EXB_SURR_GENERIC || SURR == EXB_SURR_PERIODIC_EXPONENTIAL || SURR == EXB_SURR_SINGLE_EXPONENTIAL)>::value)
+template <int SURR, int RESET, bool WA, bool WS, int NW, int V>
+__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V, (WA || WS || SURR == EXB_SURR_GENERIC || SURR == EXB_SURR_PERIODIC_EXPONENTIAL || SURR == EXB_SURR_SINGLE_EXPONENTIAL)>::value)
 lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, const int tiles_m, const int nmaps,
                    const PipeCfg pc)
 {
-    using G = TileGeom<NW>;
+    using G = TileGeom<NW, V>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float *stages = reinterpret_cast<float *>(smem_raw);
     const int tensor_floats = pc.tc * G::W;
@@ -212,23 +221,23 @@ lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, con
 
     if (warp == NW) {
         if (lane == 0) {
-            const CUtensorMap *mp[5] = {&maps.m[0], &maps.m[1], &maps.m[2], &maps.m[3], &maps.m[4]};
-            produce<NW>(ring, stages, mp, nmaps, nchunks, m0, b, pc, true);
+            const CUtensorMap *mp[5] = {&maps.m[0], &maps.m[1], &maps.m[2], &maps.m[3], &maps.m[V]};
+            produce<NW, V>(ring, stages, mp, nmaps, nchunks, m0, b, pc, true);
         }
     } else {
-        const int c = threadIdx.x * 4;
+        const int c = threadIdx.x * V;
         const int64_t m = (int64_t)m0 + c;
         const bool valid = m < A.M;
         const int64_t mm = valid ? m : 0;
         const int64_t n = (int64_t)b * A.M + mm;
         const SpikeCfg cfg = make_spike_cfg(A.maxs);
-        Neuron q[4];
-        SurrConst sc[4];
-        float cp[4], Rprev[4], f0[4], glast[4];
-        bool n0[4];
-        BwdState st[4];
+        Neuron q[V];
+        SurrConst sc[V];
+        float cp[V], Rprev[V], f0[V], glast[V];
+        bool n0[V];
+        BwdState st[V];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < V; ++j) {
             q[j] = A.np.load(b, mm + j, cfg);
             sc[j] = surr_prepare<SURR>(q[j], A.p0, A.p1);
             cp[j] = __fmul_rn(q[j].alpha, q[j].c);
@@ -238,7 +247,7 @@ lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, con
         }
         const int64_t M = A.M;
         float *gi_base = A.grad_input + ((int64_t)b * T) * M + mm;
-        const int col = tile_col_off<NW>(pc.tc, c);
+        const int col = tile_col_off<NW, V>(pc.tc, c);
         bool ok = true;
         for (int k = 0; k < nchunks; ++k) {
             if (!wait_chunk(ring, k, pc.stages)) { ok = false; break; }
@@ -249,33 +258,33 @@ lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, con
 #pragma unroll 2
             for (int tt = tmax - 1; tt >= 0; --tt) {
                 const float *e = stg + tt * G::BW;
-                float go[4], vv[4];
-                float gv[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sl[4] = {0.0f, 0.0f, 0.0f, 0.0f}, xx[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                unpack(go, lds128(e));
-                unpack(vv, lds128(e + tensor_floats));
-                if (has_gv) unpack(gv, lds128(e + 2 * tensor_floats));
-                if (SURR == EXB_SURR_GENERIC) unpack(sl, lds128(e + i_sl * tensor_floats));
-                if (WS) unpack(xx, lds128(e + i_x * tensor_floats));
+                float go[V], vv[V];
+                float gv[V] = {}, sl[V] = {}, xx[V] = {};
+                lds_vec<V>(go, e);
+                lds_vec<V>(vv, e + tensor_floats);
+                if (has_gv) lds_vec<V>(gv, e + 2 * tensor_floats);
+                if (SURR == EXB_SURR_GENERIC) lds_vec<V>(sl, e + i_sl * tensor_floats);
+                if (WS) lds_vec<V>(xx, e + i_x * tensor_floats);
                 if (A.g_last && chunk * pc.tc + tt == T - 1) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) fold_last_state_grad<RESET>(go[j], gv[j], glast[j], vv[j], q[j], cfg);
+                    for (int j = 0; j < V; ++j) fold_last_state_grad<RESET>(go[j], gv[j], glast[j], vv[j], q[j], cfg);
                 }
-                float r[4];
+                float r[V];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < V; ++j) {
                     Rprev[j] = st[j].R;
                     const float Rt = lif_bwd_step<SURR, RESET, WA, WS>(st[j], vv[j], go[j], gv[j], sl[j], xx[j], q[j], sc[j],
                                                                       cp[j], cfg, f0[j], n0[j]);
                     r[j] = __fmul_rn(q[j].scale, Rt);
                 }
-                if (valid) stv<4>(gi, r);
+                if (valid) stv<V>(gi, r);
                 gi -= M;
             }
             release_chunk(ring, k, pc.stages, lane);
         }
         if (ok && valid) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < V; ++j) {
                 if (A.grad_init) A.grad_init[n + j] = __fmul_rn(q[j].alpha, st[j].R);
                 if (WA) {
                     const float vi = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
@@ -291,11 +300,11 @@ lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, con
 // ===========================================================================
 // leaky integrator
 // ===========================================================================
-template <int NW>
-__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW>::value)
+template <int NW, int V>
+__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V>::value)
 leaky_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A, const int tiles_m, const PipeCfg pc)
 {
-    using G = TileGeom<NW>;
+    using G = TileGeom<NW, V>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float *stages = reinterpret_cast<float *>(smem_raw);
     const int tensor_floats = pc.tc * G::W;
@@ -311,24 +320,24 @@ leaky_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A,
     if (warp == NW) {
         if (lane == 0) {
             const CUtensorMap *mp[1] = {&maps.m[0]};
-            produce<NW>(ring, stages, mp, 1, nchunks, m0, b, pc, false);
+            produce<NW, V>(ring, stages, mp, 1, nchunks, m0, b, pc, false);
         }
     } else {
-        const int c = threadIdx.x * 4;
+        const int c = threadIdx.x * V;
         const int64_t m = (int64_t)m0 + c;
         const bool valid = m < A.M;
         const int64_t mm = valid ? m : 0;
         const int64_t n = (int64_t)b * A.M + mm;
-        float al[4], sc[4], v[4];
+        float al[V], sc[V], v[V];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < V; ++j) {
             al[j] = A.alpha.get(b, mm + j, 1.0f);
             sc[j] = A.scale.get(b, mm + j, 1.0f);
             v[j] = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
         }
         const int64_t M = A.M;
         float *out = A.out + ((int64_t)b * T) * M + mm;
-        const int col = tile_col_off<NW>(pc.tc, c);
+        const int col = tile_col_off<NW, V>(pc.tc, c);
         bool ok = true;
         for (int k = 0; k < nchunks; ++k) {
             if (!wait_chunk(ring, k, pc.stages)) { ok = false; break; }
@@ -336,29 +345,29 @@ leaky_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A,
             const int tmax = min(pc.tc, T - k * pc.tc);
 #pragma unroll 4
             for (int tt = 0; tt < tmax; ++tt) {
-                float xs[4];
-                unpack(xs, lds128(st + tt * G::BW));
+                float xs[V];
+                lds_vec<V>(xs, st + tt * G::BW);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) v[j] = __fmaf_rn(v[j], al[j], __fmul_rn(sc[j], xs[j]));
-                if (valid) stv<4>(out, v);
+                for (int j = 0; j < V; ++j) v[j] = __fmaf_rn(v[j], al[j], __fmul_rn(sc[j], xs[j]));
+                if (valid) stv<V>(out, v);
                 out += M;
             }
             release_chunk(ring, k, pc.stages, lane);
         }
         if (ok && valid && A.v_last) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) A.v_last[n + j] = v[j];
+            for (int j = 0; j < V; ++j) A.v_last[n + j] = v[j];
         }
     }
     ring_finish(ring, pc.stages);
 }
 
-template <bool WA, bool WS, int NW>
-__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, (WA && WS)>::value)
+template <bool WA, bool WS, int NW, int V>
+__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V, (WA && WS)>::value)
 leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A, const int tiles_m, const int nmaps,
                      const PipeCfg pc)
 {
-    using G = TileGeom<NW>;
+    using G = TileGeom<NW, V>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float *stages = reinterpret_cast<float *>(smem_raw);
     const int tensor_floats = pc.tc * G::W;
@@ -376,18 +385,18 @@ leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A,
 
     if (warp == NW) {
         if (lane == 0) {
-            const CUtensorMap *mp[5] = {&maps.m[0], &maps.m[1], &maps.m[2], &maps.m[3], &maps.m[4]};
-            produce<NW>(ring, stages, mp, nmaps, nchunks, m0, b, pc, true);
+            const CUtensorMap *mp[5] = {&maps.m[0], &maps.m[1], &maps.m[2], &maps.m[3], &maps.m[V]};
+            produce<NW, V>(ring, stages, mp, nmaps, nchunks, m0, b, pc, true);
         }
     } else {
-        const int c = threadIdx.x * 4;
+        const int c = threadIdx.x * V;
         const int64_t m = (int64_t)m0 + c;
         const bool valid = m < A.M;
         const int64_t mm = valid ? m : 0;
         const int64_t n = (int64_t)b * A.M + mm;
-        float al[4], sc[4], G_[4], ag[4], sg[4], glast[4];
+        float al[V], sc[V], G_[V], ag[V], sg[V], glast[V];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < V; ++j) {
             al[j] = A.alpha.get(b, mm + j, 1.0f);
             sc[j] = A.scale.get(b, mm + j, 1.0f);
             G_[j] = 0.0f; ag[j] = 0.0f; sg[j] = 0.0f;
@@ -395,7 +404,7 @@ leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A,
         }
         const int64_t M = A.M;
         float *gi_base = A.grad_input + ((int64_t)b * T) * M + mm;
-        const int col = tile_col_off<NW>(pc.tc, c);
+        const int col = tile_col_off<NW, V>(pc.tc, c);
         bool ok = true;
         for (int k = 0; k < nchunks; ++k) {
             if (!wait_chunk(ring, k, pc.stages)) { ok = false; break; }
@@ -406,29 +415,29 @@ leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A,
 #pragma unroll 4
             for (int tt = tmax - 1; tt >= 0; --tt) {
                 const float *e = stg + tt * G::BW;
-                float go[4];
-                float vo[4] = {0.0f, 0.0f, 0.0f, 0.0f}, xx[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                unpack(go, lds128(e));
-                if (WA) unpack(vo, lds128(e + tensor_floats));
-                if (WS) unpack(xx, lds128(e + i_x * tensor_floats));
+                float go[V];
+                float vo[V] = {}, xx[V] = {};
+                lds_vec<V>(go, e);
+                if (WA) lds_vec<V>(vo, e + tensor_floats);
+                if (WS) lds_vec<V>(xx, e + i_x * tensor_floats);
                 const bool last = (chunk * pc.tc + tt == T - 1);
-                float r[4];
+                float r[V];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < V; ++j) {
                     if (last) go[j] = __fadd_rn(go[j], glast[j]);
                     if (WA) ag[j] = __fmaf_rn(G_[j], vo[j], ag[j]);
                     G_[j] = __fmaf_rn(G_[j], al[j], go[j]);
                     if (WS) sg[j] = __fmaf_rn(G_[j], xx[j], sg[j]);
                     r[j] = __fmul_rn(sc[j], G_[j]);
                 }
-                if (valid) stv<4>(gi, r);
+                if (valid) stv<V>(gi, r);
                 gi -= M;
             }
             release_chunk(ring, k, pc.stages, lane);
         }
         if (ok && valid) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < V; ++j) {
                 if (A.grad_init) A.grad_init[n + j] = __fmul_rn(al[j], G_[j]);
                 if (WA) A.grad_alpha[n + j] = __fmaf_rn(G_[j], A.v_init ? __ldg(A.v_init + n + j) : 0.0f, ag[j]);
                 if (WS) A.grad_scale[n + j] = sg[j];
@@ -437,6 +446,10 @@ leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A,
     }
     ring_finish(ring, pc.stages);
 }
+
+}  // namespace exb
+#include "exb_leaky_scan.cuh"
+namespace exb {
 
 // ===========================================================================
 // host side
@@ -480,6 +493,7 @@ static bool use_wide(int64_t B, int64_t M)
     const int64_t wide_tiles = B * ((M + 511) / 512);
     return wide_tiles >= 2 * 148;
 }
+constexpr int NWARPS = 4;   // consumer warps per CTA in both tile shapes
 
 static int env_int(const char *name, int dflt)
 {
@@ -487,7 +501,7 @@ static int env_int(const char *name, int dflt)
     return (v && *v) ? atoi(v) : dflt;
 }
 
-static PipeCfg pipe_cfg(bool wide, int nmaps)
+static PipeCfg pipe_cfg(bool wide, int nmaps)  // wide: 4 neurons per thread (W = 512), else 1 (W = 128)
 {
     static const int env_tc = env_int("EXB_TMA_TC", 0);
     static const int env_st = env_int("EXB_TMA_STAGES", 0);
@@ -496,7 +510,7 @@ static PipeCfg pipe_cfg(bool wide, int nmaps)
     // target ~8 KB per stage across all streamed tensors
     int tc = (8 * 1024) / (w * 4 * nmaps);
     if (tc < 2) tc = 2;
-    if (!wide && tc > 32) tc = 32;
+    if (tc > 32) tc = 32;
     pc.tc = tc;
     pc.stages = 4;
     if (env_tc > 0) pc.tc = env_tc;
@@ -517,18 +531,18 @@ static bool eligible(int64_t B, int64_t T, int64_t M)
     return M % 4 == 0 && B * ((M + 127) / 128) <= 0x7fffffffll && T <= 0x7fffffffll;
 }
 
-template <int RESET, int NW>
+template <int RESET, int NW, int V>
 static cudaError_t run_lif_fwd(const LifFwdArgs &a, cudaStream_t s, bool *used)
 {
-    using G = TileGeom<NW>;
-    const PipeCfg pc = pipe_cfg(NW == 4, 1);
+    using G = TileGeom<NW, V>;
+    const PipeCfg pc = pipe_cfg(V == 4, 1);
     TmaMaps maps;
     if (!make_btm_tensor_map(&maps.m[0], a.input, a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
     for (int i = 1; i < 5; ++i) maps.m[i] = maps.m[0];
     const int tiles_m = (int)((a.M + G::W - 1) / G::W);
-    const size_t smem = tma_smem_bytes<NW>(1, pc);
+    const size_t smem = tma_smem_bytes<NW, V>(1, pc);
     if (smem > 200 * 1024) return cudaSuccess;
-    auto kern = lif_fwd_tma_kernel<RESET, NW>;
+    auto kern = lif_fwd_tma_kernel<RESET, NW, V>;
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
     kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m, pc);
@@ -542,28 +556,28 @@ cudaError_t launch_lif_forward_tma(const LifFwdArgs &a, int reset_mode, cudaStre
     if (!eligible(a.B, a.T, a.M) || !aligned16(a.spikes) || !aligned16(a.v_mem) || !aligned16(a.input)) return cudaSuccess;
     const bool wide = use_wide(a.B, a.M);
     if (reset_mode == EXB_RESET_SUBTRACT)
-        return wide ? run_lif_fwd<EXB_RESET_SUBTRACT, 4>(a, s, used) : run_lif_fwd<EXB_RESET_SUBTRACT, 1>(a, s, used);
-    return wide ? run_lif_fwd<EXB_RESET_TO_VALUE, 4>(a, s, used) : run_lif_fwd<EXB_RESET_TO_VALUE, 1>(a, s, used);
+        return wide ? run_lif_fwd<EXB_RESET_SUBTRACT, NWARPS, 4>(a, s, used) : run_lif_fwd<EXB_RESET_SUBTRACT, NWARPS, 1>(a, s, used);
+    return wide ? run_lif_fwd<EXB_RESET_TO_VALUE, NWARPS, 4>(a, s, used) : run_lif_fwd<EXB_RESET_TO_VALUE, NWARPS, 1>(a, s, used);
 }
 
-template <int SURR, int RESET, bool WA, bool WS, int NW>
+template <int SURR, int RESET, bool WA, bool WS, int NW, int V>
 static cudaError_t run_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
 {
-    using G = TileGeom<NW>;
+    using G = TileGeom<NW, V>;
     TmaMaps maps;
     const float *ptrs[5] = {a.go, a.v_mem, nullptr, nullptr, nullptr};
     int nmaps = 2;
     if (a.gv) ptrs[nmaps++] = a.gv;
     if (SURR == EXB_SURR_GENERIC) ptrs[nmaps++] = a.surr;
     if (WS) ptrs[nmaps++] = a.input;
-    const PipeCfg pc = pipe_cfg(NW == 4, nmaps);
+    const PipeCfg pc = pipe_cfg(V == 4, nmaps);
     for (int i = 0; i < nmaps; ++i)
         if (!make_btm_tensor_map(&maps.m[i], ptrs[i], a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
     for (int i = nmaps; i < 5; ++i) maps.m[i] = maps.m[0];
     const int tiles_m = (int)((a.M + G::W - 1) / G::W);
-    const size_t smem = tma_smem_bytes<NW>(nmaps, pc);
+    const size_t smem = tma_smem_bytes<NW, V>(nmaps, pc);
     if (smem > 200 * 1024) return cudaSuccess;
-    auto kern = lif_bwd_tma_kernel<SURR, RESET, WA, WS, NW>;
+    auto kern = lif_bwd_tma_kernel<SURR, RESET, WA, WS, NW, V>;
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
     kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m, nmaps, pc);
@@ -574,8 +588,8 @@ static cudaError_t run_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
 template <int SURR, int RESET, bool WA, bool WS>
 static cudaError_t pick_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
 {
-    return use_wide(a.B, a.M) ? run_lif_bwd<SURR, RESET, WA, WS, 4>(a, s, used)
-                              : run_lif_bwd<SURR, RESET, WA, WS, 1>(a, s, used);
+    return use_wide(a.B, a.M) ? run_lif_bwd<SURR, RESET, WA, WS, NWARPS, 4>(a, s, used)
+                              : run_lif_bwd<SURR, RESET, WA, WS, NWARPS, 1>(a, s, used);
 }
 
 template <int SURR, int RESET>
@@ -607,18 +621,18 @@ cudaError_t launch_lif_backward_tma(const LifBwdArgs &a, int reset_mode, int sur
                                             : surr_lif_bwd<EXB_RESET_TO_VALUE>(a, surr_kind, s, used);
 }
 
-template <int NW>
+template <int NW, int V>
 static cudaError_t run_leaky_fwd(const LeakyFwdArgs &a, cudaStream_t s, bool *used)
 {
-    using G = TileGeom<NW>;
-    const PipeCfg pc = pipe_cfg(NW == 4, 1);
+    using G = TileGeom<NW, V>;
+    const PipeCfg pc = pipe_cfg(V == 4, 1);
     TmaMaps maps;
     if (!make_btm_tensor_map(&maps.m[0], a.input, a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
     for (int i = 1; i < 5; ++i) maps.m[i] = maps.m[0];
     const int tiles_m = (int)((a.M + G::W - 1) / G::W);
-    const size_t smem = tma_smem_bytes<NW>(1, pc);
+    const size_t smem = tma_smem_bytes<NW, V>(1, pc);
     if (smem > 200 * 1024) return cudaSuccess;
-    auto kern = leaky_fwd_tma_kernel<NW>;
+    auto kern = leaky_fwd_tma_kernel<NW, V>;
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
     kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m, pc);
@@ -630,26 +644,26 @@ cudaError_t launch_leaky_forward_tma(const LeakyFwdArgs &a, cudaStream_t s, bool
 {
     *used = false;
     if (!eligible(a.B, a.T, a.M) || !aligned16(a.out) || !aligned16(a.input)) return cudaSuccess;
-    return use_wide(a.B, a.M) ? run_leaky_fwd<4>(a, s, used) : run_leaky_fwd<1>(a, s, used);
+    return use_wide(a.B, a.M) ? run_leaky_fwd<NWARPS, 4>(a, s, used) : run_leaky_fwd<NWARPS, 1>(a, s, used);
 }
 
-template <bool WA, bool WS, int NW>
+template <bool WA, bool WS, int NW, int V>
 static cudaError_t run_leaky_bwd(const LeakyBwdArgs &a, cudaStream_t s, bool *used)
 {
-    using G = TileGeom<NW>;
+    using G = TileGeom<NW, V>;
     TmaMaps maps;
     const float *ptrs[5] = {a.go, nullptr, nullptr, nullptr, nullptr};
     int nmaps = 1;
     if (WA) ptrs[nmaps++] = a.out;
     if (WS) ptrs[nmaps++] = a.input;
-    const PipeCfg pc = pipe_cfg(NW == 4, nmaps);
+    const PipeCfg pc = pipe_cfg(V == 4, nmaps);
     for (int i = 0; i < nmaps; ++i)
         if (!make_btm_tensor_map(&maps.m[i], ptrs[i], a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
     for (int i = nmaps; i < 5; ++i) maps.m[i] = maps.m[0];
     const int tiles_m = (int)((a.M + G::W - 1) / G::W);
-    const size_t smem = tma_smem_bytes<NW>(nmaps, pc);
+    const size_t smem = tma_smem_bytes<NW, V>(nmaps, pc);
     if (smem > 200 * 1024) return cudaSuccess;
-    auto kern = leaky_bwd_tma_kernel<WA, WS, NW>;
+    auto kern = leaky_bwd_tma_kernel<WA, WS, NW, V>;
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
     kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m, nmaps, pc);
@@ -660,7 +674,7 @@ static cudaError_t run_leaky_bwd(const LeakyBwdArgs &a, cudaStream_t s, bool *us
 template <bool WA, bool WS>
 static cudaError_t pick_leaky_bwd(const LeakyBwdArgs &a, cudaStream_t s, bool *used)
 {
-    return use_wide(a.B, a.M) ? run_leaky_bwd<WA, WS, 4>(a, s, used) : run_leaky_bwd<WA, WS, 1>(a, s, used);
+    return use_wide(a.B, a.M) ? run_leaky_bwd<WA, WS, NWARPS, 4>(a, s, used) : run_leaky_bwd<WA, WS, NWARPS, 1>(a, s, used);
 }
 
 cudaError_t launch_leaky_backward_tma(const LeakyBwdArgs &a, cudaStream_t s, bool *used)
@@ -672,6 +686,125 @@ cudaError_t launch_leaky_backward_tma(const LeakyBwdArgs &a, cudaStream_t s, boo
     if (wa) return pick_leaky_bwd<true, false>(a, s, used);
     if (ws) return pick_leaky_bwd<false, true>(a, s, used);
     return pick_leaky_bwd<false, false>(a, s, used);
+}
+
+// ---- time-parallel leaky scan ----------------------------------------------------------
+constexpr int SCAN_V = 1;       // one neuron per thread: most CTAs for few neurons
+
+// Splits T into segments so that about 8 CTAs per SM exist; false when splitting is pointless.
+// The segment length is a multiple of 16 steps whatever the number of streamed tensors, so that
+// forward and backward (which stream 1 to 3 tensors) agree on the scratch size; the pipeline
+// chunk is the power of two <= 16 that keeps a stage near 8 KB.
+constexpr int SCAN_ALIGN = 16;
+
+static bool scan_geometry(int64_t B, int64_t T, int64_t M, int nmaps, PipeCfg *pc, ScanGeom *sg, int *tiles_m)
+{
+    using G = TileGeom<NWARPS, SCAN_V>;
+    if (!eligible(B, T, M)) return false;
+    pc->stages = 4;
+    pc->tc = SCAN_ALIGN;
+    while (pc->tc > 2 && pc->tc * G::W * 4 * nmaps > 8 * 1024) pc->tc /= 2;
+    *tiles_m = (int)((M + G::W - 1) / G::W);
+    const int64_t ntiles = B * *tiles_m;
+    if (ntiles > (1 << 24)) return false;
+    const int64_t want = (8 * 148 + ntiles - 1) / ntiles;
+    const int64_t max_by_len = T / (4 * SCAN_ALIGN);
+    int64_t nseg = want < max_by_len ? want : max_by_len;
+    if (nseg > SCAN_MAX_SEGMENTS) nseg = SCAN_MAX_SEGMENTS;
+    if (nseg < 2) return false;
+    int64_t L = (T + nseg - 1) / nseg;
+    L = (L + SCAN_ALIGN - 1) / SCAN_ALIGN * SCAN_ALIGN;
+    nseg = (T + L - 1) / L;
+    if (nseg < 2) return false;
+    sg->nseg = (int)nseg;
+    sg->L = (int)L;
+    sg->ntiles = (int)ntiles;
+    return true;
+}
+
+int64_t leaky_scan_workspace_bytes(int64_t B, int64_t T, int64_t M)
+{
+    PipeCfg pc;
+    ScanGeom sg;
+    int tiles_m;
+    if (!scan_geometry(B, T, M, 1, &pc, &sg, &tiles_m)) return 0;
+    return (int64_t)(scan_ws_words(sg.ntiles, sg.nseg, TileGeom<NWARPS, SCAN_V>::W) * 4);
+}
+
+static bool scan_workspace(void *workspace, int64_t bytes, const ScanGeom &sg, ScanWs *ws, size_t *zero_bytes)
+{
+    const int W = TileGeom<NWARPS, SCAN_V>::W;
+    const size_t words = scan_ws_words(sg.ntiles, sg.nseg, W);
+    if (!workspace || bytes < (int64_t)(words * 4) || (reinterpret_cast<uintptr_t>(workspace) & 15u)) return false;
+    unsigned int *w = static_cast<unsigned int *>(workspace);
+    const size_t flags = ((size_t)sg.ntiles * sg.nseg + 15) / 16 * 16;
+    ws->ticket = w;
+    ws->flags = w + 16;
+    ws->agg = reinterpret_cast<float *>(w + 16 + flags);
+    *zero_bytes = (16 + flags) * 4;
+    return true;
+}
+
+cudaError_t launch_leaky_forward_scan(const LeakyFwdArgs &a, void *workspace, int64_t workspace_bytes, cudaStream_t s,
+                                      bool *used)
+{
+    using G = TileGeom<NWARPS, SCAN_V>;
+    *used = false;
+    PipeCfg pc;
+    ScanGeom sg;
+    int tiles_m;
+    if (!aligned16(a.out) || !aligned16(a.input)) return cudaSuccess;
+    if (!scan_geometry(a.B, a.T, a.M, 1, &pc, &sg, &tiles_m)) return cudaSuccess;
+    ScanWs ws;
+    size_t zero_bytes;
+    if (!scan_workspace(workspace, workspace_bytes, sg, &ws, &zero_bytes)) return cudaSuccess;
+    TmaMaps maps;
+    if (!make_btm_tensor_map(&maps.m[0], a.input, a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
+    for (int i = 1; i < 5; ++i) maps.m[i] = maps.m[0];
+    const size_t smem = tma_smem_bytes<NWARPS, SCAN_V>(1, pc);
+    auto kern = leaky_fwd_scan_kernel<NWARPS, SCAN_V>;
+    cudaError_t e = set_smem(kern, smem);
+    if (e != cudaSuccess) return e;
+    e = cudaMemsetAsync(workspace, 0, zero_bytes, s);
+    if (e != cudaSuccess) return e;
+    kern<<<(unsigned)((int64_t)sg.ntiles * sg.nseg), (NWARPS + 1) * 32, smem, s>>>(maps, a, tiles_m, pc, sg, ws);
+    *used = true;
+    return cudaPeekAtLastError();
+}
+
+cudaError_t launch_leaky_backward_scan(const LeakyBwdArgs &a, void *workspace, int64_t workspace_bytes, cudaStream_t s,
+                                       bool *used)
+{
+    using G = TileGeom<NWARPS, SCAN_V>;
+    *used = false;
+    if (!aligned16(a.grad_input)) return cudaSuccess;
+    const float *ptrs[5] = {a.go, nullptr, nullptr, nullptr, nullptr};
+    int nmaps = 1;
+    if (a.grad_alpha) ptrs[nmaps++] = a.out;
+    if (a.grad_scale) ptrs[nmaps++] = a.input;
+    PipeCfg pc;
+    ScanGeom sg;
+    int tiles_m;
+    if (!scan_geometry(a.B, a.T, a.M, nmaps, &pc, &sg, &tiles_m)) return cudaSuccess;
+    ScanWs ws;
+    size_t zero_bytes;
+    if (!scan_workspace(workspace, workspace_bytes, sg, &ws, &zero_bytes)) return cudaSuccess;
+    TmaMaps maps;
+    for (int i = 0; i < nmaps; ++i)
+        if (!make_btm_tensor_map(&maps.m[i], ptrs[i], a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
+    for (int i = nmaps; i < 5; ++i) maps.m[i] = maps.m[0];
+    const size_t smem = tma_smem_bytes<NWARPS, SCAN_V>(nmaps, pc);
+    auto kern = leaky_bwd_scan_kernel<NWARPS, SCAN_V>;
+    cudaError_t e = set_smem(kern, smem);
+    if (e != cudaSuccess) return e;
+    e = cudaMemsetAsync(workspace, 0, zero_bytes, s);
+    const size_t nbytes = (size_t)(a.B * a.M) * sizeof(float);
+    if (e == cudaSuccess && a.grad_alpha) e = cudaMemsetAsync(a.grad_alpha, 0, nbytes, s);
+    if (e == cudaSuccess && a.grad_scale) e = cudaMemsetAsync(a.grad_scale, 0, nbytes, s);
+    if (e != cudaSuccess) return e;
+    kern<<<(unsigned)((int64_t)sg.ntiles * sg.nseg), (NWARPS + 1) * 32, smem, s>>>(maps, a, tiles_m, nmaps, pc, sg, ws);
+    *used = true;
+    return cudaPeekAtLastError();
 }
 
 bool tma_enabled()

@@ -16,6 +16,20 @@ import torch
 from . import _lib
 from .spike import _flat32, _mode_of, _reduce_to_param
 
+# Below this many 128-neuron tiles the sequential kernels cannot give every SM a CTA, and the
+# time axis is split instead (exb_leaky_*_scan).
+_SCAN_MAX_TILES = 148
+
+
+def _scan_workspace(B: int, T: int, M: int, layout: int, device):
+    """Scratch tensor for the time-parallel scan, or None when the plain kernels are the better choice."""
+    if layout != _lib.LAYOUT_BTM or B * ((M + 127) // 128) >= _SCAN_MAX_TILES:
+        return None
+    nbytes = _lib.leaky_scan_workspace_bytes(B, T, M)
+    if nbytes <= 0:
+        return None
+    return torch.empty((nbytes + 3) // 4, dtype=torch.int32, device=device)
+
 
 class _LeakyCore:
     @staticmethod
@@ -25,7 +39,11 @@ class _LeakyCore:
         modes = dict(alpha=_mode_of(a_f, M, N, "alpha"), scale=_mode_of(sc_f, M, N, "in_scale"))
         out = torch.empty_like(inp)
         v_last = torch.empty(N, dtype=torch.float32, device=inp.device)
-        _lib.leaky_forward(out, inp, vi_f, (a_f, modes["alpha"]), (sc_f, modes["scale"]), v_last, B, T, M, layout)
+        ws = _scan_workspace(B, T, M, layout, inp.device)
+        if ws is not None:
+            _lib.leaky_forward_scan(out, inp, vi_f, (a_f, modes["alpha"]), (sc_f, modes["scale"]), v_last, ws, B, T, M)
+        else:
+            _lib.leaky_forward(out, inp, vi_f, (a_f, modes["alpha"]), (sc_f, modes["scale"]), v_last, B, T, M, layout)
         ctx.set_materialize_grads(False)
         ctx.geometry = (B, T, M, layout)
         ctx.modes = modes
@@ -64,8 +82,13 @@ class _LeakyCore:
         grad_init = torch.empty(N, dtype=torch.float32, device=dev) if ctx.v_init_shape is not None else None
         ga = torch.empty(N, dtype=torch.float32, device=dev) if ctx.want_alpha else None
         gs = torch.empty(N, dtype=torch.float32, device=dev) if ctx.want_scale else None
-        _lib.leaky_backward(grad_input, ga, grad_init, gs, grad_out, grad_v_last, out, inp, vi_f,
-                            (a_f, ctx.modes["alpha"]), (sc_f, ctx.modes["scale"]), B, T, M, layout)
+        ws = _scan_workspace(B, T, M, layout, dev)
+        if ws is not None:
+            _lib.leaky_backward_scan(grad_input, ga, grad_init, gs, grad_out, grad_v_last, out, inp, vi_f,
+                                     (a_f, ctx.modes["alpha"]), (sc_f, ctx.modes["scale"]), ws, B, T, M)
+        else:
+            _lib.leaky_backward(grad_input, ga, grad_init, gs, grad_out, grad_v_last, out, inp, vi_f,
+                                (a_f, ctx.modes["alpha"]), (sc_f, ctx.modes["scale"]), B, T, M, layout)
         grad_alpha = _reduce_to_param(ga, ctx.alpha_shape, ctx.modes["alpha"], B, M) if ctx.want_alpha else None
         grad_scale = _reduce_to_param(gs, ctx.scale_shape, ctx.modes["scale"], B, M) if ctx.want_scale else None
         if grad_init is not None:

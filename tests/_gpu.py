@@ -108,3 +108,40 @@ def leaky_backward(go, alpha, B, M, layout, mode=_lib.PARAM_PER_N, out=None, inp
     torch.cuda.synchronize()
     cpu = lambda t: None if t is None else t.cpu().numpy()
     return from_dev(gi, B, M, layout), cpu(ga), cpu(g0), cpu(gs)
+
+
+def leaky_forward_scan(inp, v_init, alpha, B, M, mode=_lib.PARAM_PER_N, in_scale=None):
+    """Time-parallel variant; returns None when the library says the shape is not eligible."""
+    N, T = inp.shape
+    nbytes = _lib.leaky_scan_workspace_bytes(B, T, M)
+    if nbytes == 0:
+        return None
+    ws = torch.empty((nbytes + 3) // 4, dtype=torch.int32, device=DEV)
+    x = to_dev(inp, B, M, _lib.LAYOUT_BTM)
+    out = torch.full_like(x, float("nan"))
+    v_last = torch.empty(N, device=DEV)
+    _lib.leaky_forward_scan(out, x, vec(v_init), param(alpha, mode, B, M), param(in_scale, mode, B, M), v_last, ws,
+                            B, T, M)
+    torch.cuda.synchronize()
+    return from_dev(out, B, M, _lib.LAYOUT_BTM), v_last.cpu().numpy()
+
+
+def leaky_backward_scan(go, alpha, B, M, mode=_lib.PARAM_PER_N, out=None, inp=None, v_init=None, g_last=None,
+                        in_scale=None, want_alpha=False, want_scale=False):
+    N, T = go.shape
+    nbytes = _lib.leaky_scan_workspace_bytes(B, T, M)
+    if nbytes == 0:
+        return None
+    ws = torch.empty((nbytes + 3) // 4, dtype=torch.int32, device=DEV)
+    L = _lib.LAYOUT_BTM
+    g = to_dev(go, B, M, L)
+    gi = torch.full_like(g, float("nan"))
+    ga = torch.full((N,), float("nan"), device=DEV) if want_alpha else None
+    g0 = torch.empty(N, device=DEV)
+    gs = torch.full((N,), float("nan"), device=DEV) if want_scale else None
+    _lib.leaky_backward_scan(gi, ga, g0, gs, g, vec(g_last), to_dev(out, B, M, L) if want_alpha else None,
+                             to_dev(inp, B, M, L) if want_scale else None, vec(v_init),
+                             param(alpha, mode, B, M), param(in_scale, mode, B, M), ws, B, T, M)
+    torch.cuda.synchronize()
+    cpu = lambda t: None if t is None else t.cpu().numpy()
+    return from_dev(gi, B, M, L), cpu(ga), cpu(g0), cpu(gs)

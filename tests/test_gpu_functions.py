@@ -271,6 +271,33 @@ def test_layer_exp_leak(train_alphas, norm_input, decay_early):
         assert rel_err(out.detach().cpu().numpy(), want.detach().cpu().numpy()) < TOL
 
 
+def test_layer_exp_leak_long_sequence_uses_scan():
+    """Few neurons, long sequence: the layer routes through the time-parallel scan; same results."""
+    from sinabs_exodus_b200 import _lib
+    from sinabs_exodus_b200.layers import ExpLeak
+    B, T, M = 2, 3000, 16
+    assert _lib.leaky_scan_workspace_bytes(B, T, M) > 0
+    rng = np.random.default_rng(12)
+    x_np = rng.standard_normal((B, T, M)).astype(np.float32)
+    w_np = rng.standard_normal((B, T, M)).astype(np.float32)
+    layer = ExpLeak(tau_mem=torch.tensor(rng.uniform(20, 200, M).astype(np.float32)), norm_input=True).cuda()
+    x = torch.tensor(x_np, device="cuda:0", requires_grad=True)
+    out = layer(x)
+    (out * torch.tensor(w_np, device="cuda:0")).sum().backward()
+    # ground truth in float64 from the SAME float32 decay factors (over 3000 steps the result is
+    # sensitive to the last bit of alpha); d/d tau follows by the chain rule
+    tau = layer.tau_mem.detach().cpu()
+    a = torch.exp(-1.0 / tau).double().requires_grad_(True)
+    xr = torch.tensor(x_np, dtype=torch.float64, requires_grad=True)
+    res = lif_loop(xr, a, torch.zeros(B, M, dtype=torch.float64), spiking=False, norm_input=True, decay_early=False)
+    (res["v_mem_pre"] * torch.tensor(w_np, dtype=torch.float64)).sum().backward()
+    assert rel_err(out.detach().cpu().numpy(), res["v_mem_pre"].detach().numpy()) < 2 * TOL
+    assert rel_err(x.grad.cpu().numpy(), xr.grad.numpy()) < 2 * TOL
+    tau_grad = (a.grad * a.detach() / tau.double() ** 2).numpy()
+    assert rel_err(layer.tau_mem.grad.cpu().numpy(), tau_grad) < 1e-4
+    _lib.device_status()
+
+
 def test_layer_rejects_cpu_and_bad_config():
     from sinabs_exodus_b200._lib import ExodusLibraryError
     from sinabs_exodus_b200.layers import LIF

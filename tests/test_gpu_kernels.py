@@ -257,6 +257,51 @@ def test_leaky_in_scale():
         assert rel_err(gs, (gi64 * x).sum(1)) < 2 * TOL
 
 
+@pytest.mark.parametrize("B,T,M", [(1, 4000, 128), (2, 1000, 36), (1, 5003, 4), (3, 777, 260), (1, 20000, 8)])
+@pytest.mark.parametrize("mode", [0, 2])
+def test_leaky_time_parallel_scan(B, T, M, mode):
+    """Long sequences with few neurons: the time axis is split across CTAs (needs scratch memory)."""
+    from sinabs_exodus_b200 import _lib
+    from tests import _gpu
+    N = B * M
+    assert _lib.leaky_scan_workspace_bytes(B, T, M) > 0
+    rng = np.random.default_rng(T + M)
+    x = rng.standard_normal((N, T)).astype(np.float32)
+    go = rng.standard_normal((N, T)).astype(np.float32)
+    base = rng.uniform(0.8, 1.0, N).astype(np.float32)
+    alpha = base if mode == 2 else np.full(N, base[0], np.float32)
+    scale = (1.0 - alpha).astype(np.float32)
+    v0 = rng.standard_normal(N).astype(np.float32)
+    G = rng.standard_normal(N).astype(np.float32)
+    xs = (scale[:, None] * x).astype(np.float32)
+    out, v_last = _gpu.leaky_forward_scan(x, v0, alpha, B, M, mode, in_scale=scale)
+    ref = orc.leaky_forward_f64(xs, v0, alpha)
+    assert rel_err(out, ref) < TOL
+    np.testing.assert_array_equal(v_last, out[:, -1])
+    # same answer (to rounding) as the sequential entry point
+    out_seq, _ = _gpu.leaky_forward(x, v0, alpha, B, M, 1, mode, in_scale=scale)
+    assert rel_err(out, out_seq) < TOL
+    go2 = go.copy(); go2[:, -1] += G
+    gi64, ag64 = orc.leaky_backward_f64(go2, alpha, xs, v0)
+    out32 = orc.leaky_forward(xs, v0, alpha)
+    for _ in range(2):      # twice: the scratch memory is reused
+        gi, ga, g0, gs = _gpu.leaky_backward_scan(go, alpha, B, M, mode, out=out32, inp=x, v_init=v0, g_last=G,
+                                                  in_scale=scale, want_alpha=True, want_scale=True)
+        assert rel_err(gi, scale[:, None] * gi64) < TOL
+        assert rel_err(ga, ag64) < 2 * TOL
+        assert rel_err(g0, alpha.astype(np.float64) * gi64[:, 0]) < TOL
+        assert rel_err(gs, (gi64 * x.astype(np.float64)).sum(1)) < 2 * TOL
+    gi_b, ga_b, _, _ = _gpu.leaky_backward_scan(go, alpha, B, M, mode, g_last=G, in_scale=scale)
+    np.testing.assert_array_equal(gi_b, gi)
+
+
+def test_leaky_scan_not_applicable():
+    from sinabs_exodus_b200 import _lib
+    assert _lib.leaky_scan_workspace_bytes(4, 100, 128) == 0        # too short to split
+    assert _lib.leaky_scan_workspace_bytes(1, 4000, 130) == 0       # M % 4 != 0: no TMA
+    assert _lib.leaky_scan_workspace_bytes(64, 4000, 8192) == 0     # enough tiles already
+
+
 def test_golden_vectors_gpu():
     """The CUDA path against the committed outputs of the reference's kernels."""
     import glob, os
