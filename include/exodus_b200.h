@@ -173,6 +173,36 @@ int exb_leaky_backward_scan(float *grad_input, float *grad_alpha, float *grad_in
                             void *workspace, int64_t workspace_bytes,
                             int64_t B, int64_t T, int64_t M, int device, void *stream);
 
+/* exb_leaky_forward_scan for callers that have no scratch memory to give.  No counterpart in
+ * the reference (its kernels use no scratch memory at all).
+ *
+ * Who needs it: a host whose device memory was handed out once at start-up and that may not
+ * allocate afterwards -- an inference or real-time service with a fixed memory budget, or code
+ * running inside another framework's memory pool where a raw allocation would bypass (and can
+ * exhaust or fragment) that pool and stalls the device while it happens.  Such a caller still
+ * passes its input and output tensors, but the scratch the scan needs is a fixed 1 MiB array
+ * that is part of the library image (EXB_STATIC_SCRATCH_BYTES; every GPU that loads the library
+ * holds it until the process ends).  This entry point calls no allocating routine of any kind.
+ *
+ * Limits and rules:
+ *  - a shape whose scratch need (exb_leaky_scan_workspace_bytes) exceeds EXB_STATIC_SCRATCH_BYTES
+ *    is rejected with EXB_ERR_ARG and a message that says how much was needed; shapes the scan
+ *    does not apply to give EXB_ERR_UNSUPPORTED, as with exb_leaky_forward_scan;
+ *  - the first call on each device looks up the array's device address (once per device, with
+ *    that device current); make that first call before any stream capture begins;
+ *  - all calls on a device share the one array, and it keeps what the previous call left in it.
+ *    Each call clears the part that must start from zero (work ticket and ready flags) on
+ *    `stream` ahead of its kernel, so calls issued one after another on a stream are fine.  Two
+ *    calls that can run on the GPU at the same time (different streams, different host threads)
+ *    would use the same flags and aggregates and corrupt each other: do not overlap them.
+ * Arguments and results are those of exb_leaky_forward_scan without the workspace pair. */
+#define EXB_STATIC_SCRATCH_BYTES (1u << 20)
+int exb_leaky_forward_scan_static(float *out, const float *input, const float *v_init,
+                                  const float *alpha, int alpha_mode,
+                                  const float *in_scale, int in_scale_mode,
+                                  float *v_last,
+                                  int64_t B, int64_t T, int64_t M, int device, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

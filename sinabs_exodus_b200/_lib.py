@@ -39,6 +39,7 @@ EXPORTS = (
     "exb_version", "exb_last_error", "exb_status_string", "exb_device_status",
     "exb_lif_forward", "exb_lif_backward", "exb_leaky_forward", "exb_leaky_backward",
     "exb_leaky_scan_workspace_bytes", "exb_leaky_forward_scan", "exb_leaky_backward_scan",
+    "exb_leaky_forward_scan_static",
 )
 
 
@@ -84,6 +85,8 @@ def load() -> ctypes.CDLL:
     lib.exb_leaky_forward_scan.argtypes = [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp] + scan_tail
     lib.exb_leaky_backward_scan.restype = _i
     lib.exb_leaky_backward_scan.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i] + scan_tail
+    lib.exb_leaky_forward_scan_static.restype = _i
+    lib.exb_leaky_forward_scan_static.argtypes = [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _i, _vp]
     _lib = lib
     return lib
 
@@ -217,3 +220,20 @@ def leaky_backward_scan(grad_input, grad_alpha, grad_init, grad_scale, grad_out,
                                         workspace.data_ptr(), workspace.numel() * workspace.element_size(),
                                         B, T, M, dev.index, _stream(dev))
     _check(st, "exb_leaky_backward_scan")
+
+
+STATIC_SCRATCH_BYTES = 1 << 20
+
+
+def leaky_forward_scan_static(out, inp, v_init, alpha: Tuple, in_scale: Tuple, v_last, B: int, T: int, M: int) -> None:
+    """``exb_leaky_forward_scan_static``: the forward scan on the library's built-in scratch array.
+
+    For hosts that must not allocate device memory once they are running (fixed memory budget,
+    foreign memory pool).  Shapes that need more than ``STATIC_SCRATCH_BYTES`` raise.  Calls share
+    the array: do not let two of them run on the GPU at the same time.
+    """
+    dev = _require_cuda(out, inp, v_init, alpha[0], in_scale[0], v_last)
+    st = load().exb_leaky_forward_scan_static(ptr(out), ptr(inp), ptr(v_init), ptr(alpha[0]), alpha[1],
+                                              ptr(in_scale[0]), in_scale[1], ptr(v_last),
+                                              B, T, M, dev.index, _stream(dev))
+    _check(st, "exb_leaky_forward_scan_static")

@@ -292,4 +292,44 @@ int exb_leaky_backward_scan(float *grad_input, float *grad_alpha, float *grad_in
     return EXB_OK;
 }
 
+// Time-parallel leaky forward for callers that cannot supply scratch memory (see the header).
+// Nothing is allocated here or below: the workspace is a fixed array inside the library.
+int exb_leaky_forward_scan_static(float *out, const float *input, const float *v_init,
+                                  const float *alpha, int alpha_mode,
+                                  const float *in_scale, int in_scale_mode,
+                                  float *v_last,
+                                  int64_t B, int64_t T, int64_t M, int device, void *stream)
+{
+    if (int st = check_geometry(B, T, M, EXB_LAYOUT_BTM)) return st;
+    if (!out || !input || !alpha)
+        return fail(EXB_ERR_ARG, "exb_leaky_forward_scan_static: out, input and alpha are required");
+    if (!mode_ok(alpha_mode) || (in_scale && !mode_ok(in_scale_mode)))
+        return fail(EXB_ERR_ARG, "exb_leaky_forward_scan_static: bad parameter mode");
+    if (B == 0 || M == 0 || T == 0) return EXB_OK;
+    const int64_t need = exb::leaky_scan_workspace_bytes(B, T, M);
+    if (need == 0)
+        return fail(EXB_ERR_UNSUPPORTED, "exb_leaky_forward_scan_static: the time-parallel scan does not apply to "
+                    "B=%lld T=%lld M=%lld (use exb_leaky_forward)", (long long)B, (long long)T, (long long)M);
+    if ((size_t)need > exb::leaky_scan_static_capacity())
+        return fail(EXB_ERR_ARG, "exb_leaky_forward_scan_static: this shape needs %lld bytes of scratch, the built-in "
+                    "array holds %zu; use exb_leaky_forward_scan with a caller-provided workspace",
+                    (long long)need, exb::leaky_scan_static_capacity());
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_leaky_forward_scan_static: cannot select device %d", device);
+    int current = -1;
+    if (cudaGetDevice(&current) != cudaSuccess)
+        return fail(EXB_ERR_DEVICE, "exb_leaky_forward_scan_static: cannot query the current device");
+    exb::LeakyFwdArgs a;
+    a.out = out; a.input = input; a.v_init = v_init;
+    a.alpha = exb::make_param(alpha, alpha_mode, M);
+    a.scale = exb::make_param(in_scale, in_scale_mode, M);
+    a.v_last = v_last;
+    a.B = B; a.T = T; a.M = M;
+    bool used = false;
+    cudaError_t e = exb::launch_leaky_forward_scan_static(a, current, (cudaStream_t)stream, &used);
+    if (e != cudaSuccess) return launch_status(e, "exb_leaky_forward_scan_static");
+    if (!used) return fail(EXB_ERR_UNSUPPORTED, "exb_leaky_forward_scan_static: shape or alignment not eligible");
+    return EXB_OK;
+}
+
 }  // extern "C"

@@ -11,6 +11,7 @@
 
 #include <cudaTypedefs.h>
 #include <cstdlib>
+#include <mutex>
 
 namespace exb {
 
@@ -805,6 +806,52 @@ cudaError_t launch_leaky_backward_scan(const LeakyBwdArgs &a, void *workspace, i
     kern<<<(unsigned)((int64_t)sg.ntiles * sg.nseg), (NWARPS + 1) * 32, smem, s>>>(maps, a, tiles_m, nmaps, pc, sg, ws);
     *used = true;
     return cudaPeekAtLastError();
+}
+
+// ---- time-parallel leaky forward on library-owned scratch -------------------------------
+// Some hosts cannot hand the library a scratch buffer: an inference server or embedded runtime
+// whose whole device-memory budget was carved up at start-up, or a plug-in that lives inside
+// another framework's memory pool, has nowhere to get one from once it is running, and
+// allocating behind the owner's back (cudaMalloc synchronises the device and can fail or
+// fragment a nearly full GPU) is exactly what such hosts forbid.  For them the scan's scratch
+// lives in this fixed array, part of the library image: every GPU that loads the library
+// holds these bytes until the process exits.
+constexpr size_t STATIC_SCRATCH_BYTES = 1u << 20;   // 1 MiB: covers every shape with up to ~1300 (tile, segment) pairs
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+
+// Device address of the array on `device`, which must be the current device.  In host code the
+// array's name is only a handle; the address a kernel can use comes from cudaGetSymbolAddress.
+// Looked up once per device and remembered.
+static cudaError_t static_scratch_address(int device, void **out)
+{
+    constexpr int MAX_DEVICES = 64;
+    static void *cached[MAX_DEVICES] = {};
+    static std::mutex mu;
+    if (device < 0 || device >= MAX_DEVICES) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cached[device]) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return e;
+        cached[device] = p;
+    }
+    *out = cached[device];
+    return cudaSuccess;
+}
+
+size_t leaky_scan_static_capacity() { return STATIC_SCRATCH_BYTES; }
+
+// Same launch as launch_leaky_forward_scan, with the library's own array as the workspace.
+// `device` is the current device.  The launcher clears the ticket and the ready flags at the
+// head of the array on the stream before the kernel, so whatever the previous call left there
+// does not matter; the aggregates behind them are written before they are read.
+cudaError_t launch_leaky_forward_scan_static(const LeakyFwdArgs &a, int device, cudaStream_t s, bool *used)
+{
+    *used = false;
+    void *scratch = nullptr;
+    cudaError_t e = static_scratch_address(device, &scratch);
+    if (e != cudaSuccess) return e;
+    return launch_leaky_forward_scan(a, scratch, (int64_t)STATIC_SCRATCH_BYTES, s, used);
 }
 
 bool tma_enabled()
