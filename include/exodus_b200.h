@@ -105,8 +105,11 @@ int exb_lif_forward(float *spikes, float *v_mem, const float *input, const float
  * grad_alpha[N] (may be NULL) = per-instance d/d alpha (needs v_init or NULL=0);
  * the spike counts are recomputed from v_mem, so `spikes` is not read.
  * `surr` is read only with EXB_SURR_GENERIC.  With in_scale the kernel writes
- * grad_input_t = scale*R_t, and grad_scale[N] (may be NULL) = sum_t R_t*in_t,
- * which needs `input` (the forward's unscaled input). */
+ * grad_input_t = scale*R_t, and grad_scale[N] (may be NULL) = sum_t R_t*in_t.
+ * With `input` (the forward's unscaled input) given, that sum reads it.  With
+ * input == NULL it is rebuilt from v_mem alone, using
+ * scale*in_t = v_t - alpha*vpost_{t-1} wherever R_t != 0, at no extra memory
+ * traffic; this needs every scale to be non-zero. */
 int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, float *grad_scale,
                      const float *grad_spikes, const float *grad_v_mem, const float *grad_v_last,
                      const float *v_mem, const float *surr, const float *v_init, const float *input,

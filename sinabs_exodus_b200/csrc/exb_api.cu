@@ -154,7 +154,8 @@ int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, flo
         return fail(EXB_ERR_ARG, "exb_lif_backward: unknown surrogate kind %d", surrogate_kind);
     if (surrogate_kind == EXB_SURR_GENERIC && !surr)
         return fail(EXB_ERR_ARG, "exb_lif_backward: the generic surrogate needs the `surr` tensor");
-    if (grad_scale && !input) return fail(EXB_ERR_ARG, "exb_lif_backward: grad_scale needs `input`");
+    if (grad_scale && !input && !in_scale)
+        return fail(EXB_ERR_ARG, "exb_lif_backward: grad_scale without `input` is rebuilt from v_mem and needs in_scale");
     if (B == 0 || M == 0 || T == 0) return EXB_OK;
     DeviceGuard guard(device);
     if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_lif_backward: cannot select device %d", device);

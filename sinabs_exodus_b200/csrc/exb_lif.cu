@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(256) lif_fwd_btm_kernel(const LifFwdArgs A)
 // ===========================================================================
 // time-major backward
 // ===========================================================================
-template <int V, int SURR, int RESET, bool WA, bool WS, int U>
+template <int V, int SURR, int RESET, bool WA, int WS, int U>
 __global__ void __launch_bounds__(256) lif_bwd_btm_kernel(const LifBwdArgs A)
 {
     const int64_t MV = A.M / V;
@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(256) lif_bwd_btm_kernel(const LifBwdArgs A)
         q[j] = A.np.load(b, m + j, cfg);
         sc[j] = surr_prepare<SURR>(q[j], A.p0, A.p1);
         cp[j] = __fmul_rn(q[j].alpha, q[j].c);
-        st[j].R = 0.0f; st[j].ag = 0.0f; st[j].sg = 0.0f;
+        st[j].R = 0.0f; st[j].ag = 0.0f; st[j].sg = 0.0f; st[j].vnext = 0.0f;
         Rprev[j] = 0.0f; f0[j] = 0.0f; n0[j] = true;
     }
     const int64_t base = (b * T) * M + m;
@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(256) lif_bwd_btm_kernel(const LifBwdArgs A)
     const float *vm = A.v_mem + base;
     const float *gv = A.gv ? A.gv + base : nullptr;
     const float *sl = (SURR == EXB_SURR_GENERIC) ? A.surr + base : nullptr;
-    const float *xin = WS ? A.input + base : nullptr;
+    const float *xin = (WS == SCALE_GRAD_FROM_INPUT) ? A.input + base : nullptr;
     float *gi = A.grad_input + base;
 
     for (int64_t t = T - 1; t >= 0; t -= U) {
@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(256) lif_bwd_btm_kernel(const LifBwdArgs A)
                 ldv<V>(rv[u], vm + tt * M);
                 if (gv) ldv<V>(rgv[u], gv + tt * M);
                 if (SURR == EXB_SURR_GENERIC) ldv<V>(rsl[u], sl + tt * M);
-                if (WS) ldv<V>(rx[u], xin + tt * M);
+                if (WS == SCALE_GRAD_FROM_INPUT) ldv<V>(rx[u], xin + tt * M);
             }
         }
         if (t == T - 1 && A.g_last) {
@@ -162,11 +162,9 @@ __global__ void __launch_bounds__(256) lif_bwd_btm_kernel(const LifBwdArgs A)
 #pragma unroll
     for (int j = 0; j < V; ++j) {
         if (A.grad_init) A.grad_init[n + j] = __fmul_rn(q[j].alpha, st[j].R);
-        if (WA) {
-            const float vi = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
-            A.grad_alpha[n + j] = alpha_grad_finish<RESET>(st[j], vi, Rprev[j], f0[j], n0[j]);
-        }
-        if (WS) A.grad_scale[n + j] = st[j].sg;
+        const float vi = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
+        if (WA) A.grad_alpha[n + j] = alpha_grad_finish<RESET>(st[j], vi, Rprev[j], f0[j], n0[j]);
+        if (WS) A.grad_scale[n + j] = scale_grad_finish<WS>(st[j], vi, q[j]);
     }
 }
 
@@ -238,7 +236,7 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_fwd_nt_kernel(const LifFwdA
     }
 }
 
-template <int SURR, int RESET, bool WA, bool WS>
+template <int SURR, int RESET, bool WA, int WS>
 __global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_nt_kernel(const LifBwdArgs A, int ntiles)
 {
     extern __shared__ float smem[];
@@ -252,7 +250,7 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_nt_kernel(const LifBwdA
     float *tgv = nullptr, *tsl = nullptr, *txi = nullptr;
     if (A.gv) { tgv = nxt; nxt += TILE_FLOATS; }
     if (SURR == EXB_SURR_GENERIC) { tsl = nxt; nxt += TILE_FLOATS; }
-    if (WS) { txi = nxt; nxt += TILE_FLOATS; }
+    if (WS == SCALE_GRAD_FROM_INPUT) { txi = nxt; nxt += TILE_FLOATS; }
 
     const int rows = (int)min((int64_t)TILE, N - n0);
     const bool valid = lane < rows;
@@ -263,7 +261,7 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_nt_kernel(const LifBwdA
     const SurrConst sc = surr_prepare<SURR>(q, A.p0, A.p1);
     const float cp = __fmul_rn(q.alpha, q.c);
     BwdState st;
-    st.R = 0.0f; st.ag = 0.0f; st.sg = 0.0f;
+    st.R = 0.0f; st.ag = 0.0f; st.sg = 0.0f; st.vnext = 0.0f;
     float Rprev = 0.0f, f0 = 0.0f;
     bool nc0 = true;
     const float glast = (A.g_last && valid) ? __ldg(A.g_last + n) : 0.0f;
@@ -275,7 +273,7 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_nt_kernel(const LifBwdA
         tile_load(tv, A.v_mem + off, T, rows, tc, lane);
         if (tgv) tile_load(tgv, A.gv + off, T, rows, tc, lane);
         if (SURR == EXB_SURR_GENERIC) tile_load(tsl, A.surr + off, T, rows, tc, lane);
-        if (WS) tile_load(txi, A.input + off, T, rows, tc, lane);
+        if (WS == SCALE_GRAD_FROM_INPUT) tile_load(txi, A.input + off, T, rows, tc, lane);
         __syncwarp();
         if (valid) {
             for (int t = tc - 1; t >= 0; --t) {
@@ -285,7 +283,7 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_nt_kernel(const LifBwdA
                 if (A.g_last && t0 + t == T - 1) fold_last_state_grad<RESET>(go, gv, glast, v, q, cfg);
                 Rprev = st.R;
                 const float Rt = lif_bwd_step<SURR, RESET, WA, WS>(st, v, go, gv, (SURR == EXB_SURR_GENERIC) ? tsl[i] : 0.0f,
-                                                                  WS ? txi[i] : 0.0f, q, sc, cp, cfg, f0, nc0);
+                                                                  (WS == SCALE_GRAD_FROM_INPUT) ? txi[i] : 0.0f, q, sc, cp, cfg, f0, nc0);
                 tg[i] = __fmul_rn(q.scale, Rt);
             }
         }
@@ -295,8 +293,9 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_nt_kernel(const LifBwdA
     }
     if (valid) {
         if (A.grad_init) A.grad_init[n] = __fmul_rn(q.alpha, st.R);
-        if (WA) A.grad_alpha[n] = alpha_grad_finish<RESET>(st, A.v_init ? __ldg(A.v_init + n) : 0.0f, Rprev, f0, nc0);
-        if (WS) A.grad_scale[n] = st.sg;
+        const float vi = A.v_init ? __ldg(A.v_init + n) : 0.0f;
+        if (WA) A.grad_alpha[n] = alpha_grad_finish<RESET>(st, vi, Rprev, f0, nc0);
+        if (WS) A.grad_scale[n] = scale_grad_finish<WS>(st, vi, q);
     }
 }
 
@@ -342,7 +341,7 @@ cudaError_t launch_lif_forward(const LifFwdArgs &a, int layout, int reset_mode, 
                                             : launch_fwd_t<EXB_RESET_TO_VALUE>(a, layout, s);
 }
 
-template <int SURR, int RESET, bool WA, bool WS>
+template <int SURR, int RESET, bool WA, int WS>
 static cudaError_t launch_bwd_t(const LifBwdArgs &a, int layout, cudaStream_t s)
 {
     if (layout == EXB_LAYOUT_BTM) {
@@ -356,7 +355,7 @@ static cudaError_t launch_bwd_t(const LifBwdArgs &a, int layout, cudaStream_t s)
     } else {
         const int64_t N = a.B * a.M;
         const int64_t warps = (N + TILE - 1) / TILE;
-        const int ntiles = 2 + (a.gv ? 1 : 0) + (SURR == EXB_SURR_GENERIC ? 1 : 0) + (WS ? 1 : 0);
+        const int ntiles = 2 + (a.gv ? 1 : 0) + (SURR == EXB_SURR_GENERIC ? 1 : 0) + (WS == SCALE_GRAD_FROM_INPUT ? 1 : 0);
         const size_t sm = (size_t)NT_WARPS * ntiles * TILE_FLOATS * sizeof(float);
         auto kern = lif_bwd_nt_kernel<SURR, RESET, WA, WS>;
         if (sm > 48 * 1024) {
@@ -371,11 +370,16 @@ static cudaError_t launch_bwd_t(const LifBwdArgs &a, int layout, cudaStream_t s)
 template <int SURR, int RESET>
 static cudaError_t launch_bwd_flags(const LifBwdArgs &a, int layout, cudaStream_t s)
 {
-    const bool wa = a.grad_alpha != nullptr, ws = a.grad_scale != nullptr;
-    if (wa && ws) return launch_bwd_t<SURR, RESET, true, true>(a, layout, s);
-    if (wa) return launch_bwd_t<SURR, RESET, true, false>(a, layout, s);
-    if (ws) return launch_bwd_t<SURR, RESET, false, true>(a, layout, s);
-    return launch_bwd_t<SURR, RESET, false, false>(a, layout, s);
+    const bool wa = a.grad_alpha != nullptr;
+    const int ws = a.grad_scale ? (a.input ? SCALE_GRAD_FROM_INPUT : SCALE_GRAD_FROM_STATE) : SCALE_GRAD_NONE;
+    if (wa) {
+        if (ws == SCALE_GRAD_FROM_INPUT) return launch_bwd_t<SURR, RESET, true, SCALE_GRAD_FROM_INPUT>(a, layout, s);
+        if (ws == SCALE_GRAD_FROM_STATE) return launch_bwd_t<SURR, RESET, true, SCALE_GRAD_FROM_STATE>(a, layout, s);
+        return launch_bwd_t<SURR, RESET, true, SCALE_GRAD_NONE>(a, layout, s);
+    }
+    if (ws == SCALE_GRAD_FROM_INPUT) return launch_bwd_t<SURR, RESET, false, SCALE_GRAD_FROM_INPUT>(a, layout, s);
+    if (ws == SCALE_GRAD_FROM_STATE) return launch_bwd_t<SURR, RESET, false, SCALE_GRAD_FROM_STATE>(a, layout, s);
+    return launch_bwd_t<SURR, RESET, false, SCALE_GRAD_NONE>(a, layout, s);
 }
 
 template <int RESET>

@@ -163,17 +163,25 @@ __device__ __forceinline__ float surrogate(float v, const Neuron &q, const SurrC
 
 // Running state of the reverse-time sweep of one neuron.
 struct BwdState {
-    float R;    // R_{t+1}: gradient w.r.t. the membrane potential one step later
-    float ag;   // alpha-gradient accumulator
-    float sg;   // input-scale-gradient accumulator
+    float R;      // R_{t+1}: gradient w.r.t. the membrane potential one step later
+    float ag;     // alpha-gradient accumulator
+    float sg;     // input-scale-gradient accumulator
+    float vnext;  // v_{t+1} (only for SCALE_GRAD_FROM_STATE)
 };
+
+// How the gradient w.r.t. the input scale, sum_t R_t * x_t, is formed.
+//   SCALE_GRAD_FROM_INPUT  reads the forward input x_t (one more tensor to stream)
+//   SCALE_GRAD_FROM_STATE  uses scale*x_t = v_t - alpha*vpost_{t-1}, which holds wherever R_t != 0
+//                          (a clipped step has R_t = 0), and divides the sum by scale at the end:
+//                          nothing but v_mem is read.  Needs scale != 0.
+enum { SCALE_GRAD_NONE = 0, SCALE_GRAD_FROM_INPUT = 1, SCALE_GRAD_FROM_STATE = 2 };
 
 // One reverse step.  v: saved pre-reset membrane potential; go/gv: incoming
 // gradients w.r.t. spikes and v_mem at this step; sl: caller-supplied surrogate
 // (generic mode); x: unscaled forward input (only when WANT_SCALE_GRAD).
 // Returns R_t; on return st.R == R_t.  `f_out`, `n_out` give the step's
 // propagation factor and clip gate for the caller's first-step handling.
-template <int SURR, int RESET, bool WANT_ALPHA_GRAD, bool WANT_SCALE_GRAD>
+template <int SURR, int RESET, bool WANT_ALPHA_GRAD, int WANT_SCALE_GRAD>
 __device__ __forceinline__ float lif_bwd_step(BwdState &st, float v, float go, float gv, float sl, float x,
                                               const Neuron &q, const SurrConst &sc, float cp, const SpikeCfg &cfg,
                                               float &f_out, bool &n_out)
@@ -182,13 +190,21 @@ __device__ __forceinline__ float lif_bwd_step(BwdState &st, float v, float go, f
     const bool n = v > q.lo;
     const float g = __fadd_rn(__fmul_rn(s, go), gv);
     float af = 0.0f;
-    if (RESET == EXB_RESET_TO_VALUE || WANT_ALPHA_GRAD) af = spike_count_f(v, q, cfg);
+    if (RESET == EXB_RESET_TO_VALUE || WANT_ALPHA_GRAD || WANT_SCALE_GRAD == SCALE_GRAD_FROM_STATE)
+        af = spike_count_f(v, q, cfg);
     float f;
     if (RESET == EXB_RESET_SUBTRACT) f = __fmaf_rn(-cp, s, q.alpha);   // alpha - (alpha*c)*s
     else f = (af != 0.0f) ? 0.0f : q.alpha;
-    if (WANT_ALPHA_GRAD) st.ag = __fmaf_rn(st.R, post_reset<RESET>(v, af, q), st.ag);
+    if (WANT_ALPHA_GRAD || WANT_SCALE_GRAD == SCALE_GRAD_FROM_STATE) {
+        const float vpost = post_reset<RESET>(v, af, q);
+        if (WANT_ALPHA_GRAD) st.ag = __fmaf_rn(st.R, vpost, st.ag);
+        if (WANT_SCALE_GRAD == SCALE_GRAD_FROM_STATE) {
+            st.sg = __fmaf_rn(st.R, __fmaf_rn(-q.alpha, vpost, st.vnext), st.sg);   // R_{t+1} * scale*x_{t+1}
+            st.vnext = v;
+        }
+    }
     const float Rt = n ? __fmaf_rn(f, st.R, g) : 0.0f;
-    if (WANT_SCALE_GRAD) st.sg = __fmaf_rn(Rt, x, st.sg);
+    if (WANT_SCALE_GRAD == SCALE_GRAD_FROM_INPUT) st.sg = __fmaf_rn(Rt, x, st.sg);
     st.R = Rt;
     f_out = f;
     n_out = n;
@@ -221,6 +237,15 @@ __device__ __forceinline__ float alpha_grad_finish(const BwdState &st, float v_i
     float ag = __fmaf_rn(st.R, v_init, st.ag);
     if (RESET == EXB_RESET_SUBTRACT && !n0) ag = __fmaf_rn(__fmul_rn(v_init, f0), R1, ag);
     return ag;
+}
+
+// Gradient w.r.t. the input scale after the sweep reached t = 0 (st.R == R_0, st.vnext == v_0).
+template <int WANT_SCALE_GRAD>
+__device__ __forceinline__ float scale_grad_finish(const BwdState &st, float v_init, const Neuron &q)
+{
+    if (WANT_SCALE_GRAD == SCALE_GRAD_FROM_STATE)
+        return __fdiv_rn(__fmaf_rn(st.R, __fmaf_rn(-q.alpha, v_init, st.vnext), st.sg), q.scale);
+    return st.sg;
 }
 
 // ---- small vector helpers -------------------------------------------------

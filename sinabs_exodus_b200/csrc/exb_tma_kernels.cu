@@ -197,8 +197,8 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
 // ===========================================================================
 // fused reverse-time backward
 // ===========================================================================
-template <int SURR, int RESET, bool WA, bool WS, int NW, int V>
-__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V, (WA || WS || SURR == EXB_SURR_GENERIC || SURR == EXB_SURR_PERIODIC_EXPONENTIAL || SURR == EXB_SURR_SINGLE_EXPONENTIAL)>::value)
+template <int SURR, int RESET, bool WA, int WS, int NW, int V>
+__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V, (WA || WS != 0 || SURR == EXB_SURR_GENERIC || SURR == EXB_SURR_PERIODIC_EXPONENTIAL || SURR == EXB_SURR_SINGLE_EXPONENTIAL)>::value)
 lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, const int tiles_m, const int nmaps,
                    const PipeCfg pc)
 {
@@ -242,7 +242,7 @@ lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, con
             q[j] = A.np.load(b, mm + j, cfg);
             sc[j] = surr_prepare<SURR>(q[j], A.p0, A.p1);
             cp[j] = __fmul_rn(q[j].alpha, q[j].c);
-            st[j].R = 0.0f; st[j].ag = 0.0f; st[j].sg = 0.0f;
+            st[j].R = 0.0f; st[j].ag = 0.0f; st[j].sg = 0.0f; st[j].vnext = 0.0f;
             Rprev[j] = 0.0f; f0[j] = 0.0f; n0[j] = true;
             glast[j] = A.g_last ? __ldg(A.g_last + n + j) : 0.0f;
         }
@@ -265,7 +265,7 @@ lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, con
                 lds_vec<V>(vv, e + tensor_floats);
                 if (has_gv) lds_vec<V>(gv, e + 2 * tensor_floats);
                 if (SURR == EXB_SURR_GENERIC) lds_vec<V>(sl, e + i_sl * tensor_floats);
-                if (WS) lds_vec<V>(xx, e + i_x * tensor_floats);
+                if (WS == SCALE_GRAD_FROM_INPUT) lds_vec<V>(xx, e + i_x * tensor_floats);
                 if (A.g_last && chunk * pc.tc + tt == T - 1) {
 #pragma unroll
                     for (int j = 0; j < V; ++j) fold_last_state_grad<RESET>(go[j], gv[j], glast[j], vv[j], q[j], cfg);
@@ -287,11 +287,9 @@ lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, con
 #pragma unroll
             for (int j = 0; j < V; ++j) {
                 if (A.grad_init) A.grad_init[n + j] = __fmul_rn(q[j].alpha, st[j].R);
-                if (WA) {
-                    const float vi = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
-                    A.grad_alpha[n + j] = alpha_grad_finish<RESET>(st[j], vi, Rprev[j], f0[j], n0[j]);
-                }
-                if (WS) A.grad_scale[n + j] = st[j].sg;
+                const float vi = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
+                if (WA) A.grad_alpha[n + j] = alpha_grad_finish<RESET>(st[j], vi, Rprev[j], f0[j], n0[j]);
+                if (WS) A.grad_scale[n + j] = scale_grad_finish<WS>(st[j], vi, q[j]);
             }
         }
     }
@@ -363,7 +361,7 @@ leaky_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A,
     ring_finish(ring, pc.stages);
 }
 
-template <bool WA, bool WS, int NW, int V>
+template <bool WA, int WS, int NW, int V>
 __global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V, (WA && WS)>::value)
 leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A, const int tiles_m, const int nmaps,
                      const PipeCfg pc)
@@ -561,7 +559,7 @@ cudaError_t launch_lif_forward_tma(const LifFwdArgs &a, int reset_mode, cudaStre
     return wide ? run_lif_fwd<EXB_RESET_TO_VALUE, NWARPS, 4>(a, s, used) : run_lif_fwd<EXB_RESET_TO_VALUE, NWARPS, 1>(a, s, used);
 }
 
-template <int SURR, int RESET, bool WA, bool WS, int NW, int V>
+template <int SURR, int RESET, bool WA, int WS, int NW, int V>
 static cudaError_t run_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
 {
     using G = TileGeom<NW, V>;
@@ -570,7 +568,7 @@ static cudaError_t run_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
     int nmaps = 2;
     if (a.gv) ptrs[nmaps++] = a.gv;
     if (SURR == EXB_SURR_GENERIC) ptrs[nmaps++] = a.surr;
-    if (WS) ptrs[nmaps++] = a.input;
+    if (WS == SCALE_GRAD_FROM_INPUT) ptrs[nmaps++] = a.input;
     const PipeCfg pc = pipe_cfg(V == 4, nmaps);
     for (int i = 0; i < nmaps; ++i)
         if (!make_btm_tensor_map(&maps.m[i], ptrs[i], a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
@@ -586,7 +584,7 @@ static cudaError_t run_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
     return cudaPeekAtLastError();
 }
 
-template <int SURR, int RESET, bool WA, bool WS>
+template <int SURR, int RESET, bool WA, int WS>
 static cudaError_t pick_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
 {
     return use_wide(a.B, a.M) ? run_lif_bwd<SURR, RESET, WA, WS, NWARPS, 4>(a, s, used)
@@ -596,11 +594,16 @@ static cudaError_t pick_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
 template <int SURR, int RESET>
 static cudaError_t flags_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
 {
-    const bool wa = a.grad_alpha != nullptr, ws = a.grad_scale != nullptr;
-    if (wa && ws) return pick_lif_bwd<SURR, RESET, true, true>(a, s, used);
-    if (wa) return pick_lif_bwd<SURR, RESET, true, false>(a, s, used);
-    if (ws) return pick_lif_bwd<SURR, RESET, false, true>(a, s, used);
-    return pick_lif_bwd<SURR, RESET, false, false>(a, s, used);
+    const bool wa = a.grad_alpha != nullptr;
+    const int ws = a.grad_scale ? (a.input ? SCALE_GRAD_FROM_INPUT : SCALE_GRAD_FROM_STATE) : SCALE_GRAD_NONE;
+    if (wa) {
+        if (ws == SCALE_GRAD_FROM_INPUT) return pick_lif_bwd<SURR, RESET, true, SCALE_GRAD_FROM_INPUT>(a, s, used);
+        if (ws == SCALE_GRAD_FROM_STATE) return pick_lif_bwd<SURR, RESET, true, SCALE_GRAD_FROM_STATE>(a, s, used);
+        return pick_lif_bwd<SURR, RESET, true, SCALE_GRAD_NONE>(a, s, used);
+    }
+    if (ws == SCALE_GRAD_FROM_INPUT) return pick_lif_bwd<SURR, RESET, false, SCALE_GRAD_FROM_INPUT>(a, s, used);
+    if (ws == SCALE_GRAD_FROM_STATE) return pick_lif_bwd<SURR, RESET, false, SCALE_GRAD_FROM_STATE>(a, s, used);
+    return pick_lif_bwd<SURR, RESET, false, SCALE_GRAD_NONE>(a, s, used);
 }
 
 template <int RESET>
@@ -648,7 +651,7 @@ cudaError_t launch_leaky_forward_tma(const LeakyFwdArgs &a, cudaStream_t s, bool
     return use_wide(a.B, a.M) ? run_leaky_fwd<NWARPS, 4>(a, s, used) : run_leaky_fwd<NWARPS, 1>(a, s, used);
 }
 
-template <bool WA, bool WS, int NW, int V>
+template <bool WA, int WS, int NW, int V>
 static cudaError_t run_leaky_bwd(const LeakyBwdArgs &a, cudaStream_t s, bool *used)
 {
     using G = TileGeom<NW, V>;
@@ -672,7 +675,7 @@ static cudaError_t run_leaky_bwd(const LeakyBwdArgs &a, cudaStream_t s, bool *us
     return cudaPeekAtLastError();
 }
 
-template <bool WA, bool WS>
+template <bool WA, int WS>
 static cudaError_t pick_leaky_bwd(const LeakyBwdArgs &a, cudaStream_t s, bool *used)
 {
     return use_wide(a.B, a.M) ? run_leaky_bwd<WA, WS, NWARPS, 4>(a, s, used) : run_leaky_bwd<WA, WS, NWARPS, 1>(a, s, used);

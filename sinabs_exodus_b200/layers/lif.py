@@ -165,7 +165,8 @@ class LIF(LIFBase):
         count = torch.zeros(1, dtype=torch.int64, device=dev)
         spikes, v_pre, v_post_last = IntegrateAndFireTM.apply(
             i_syn, alpha_mem, self.v_mem.reshape(-1), threshold, subtract, min_v_mem, scale,
-            self.surrogate_grad_fn, self.max_num_spikes_per_bin, reset_mode, count)
+            self.surrogate_grad_fn, self.max_num_spikes_per_bin, reset_mode, count,
+            scale is not None and getattr(self, "_scale_nonzero", False))
         if self.record_states:
             c = threshold if subtract is None else subtract
             c = c if c.numel() == 1 else (c.view(1, 1, -1) if c.numel() == v_pre.shape[2] else c.view(batch, 1, -1))
@@ -189,8 +190,14 @@ class LIF(LIFBase):
             return
         with torch.no_grad():
             a = alpha_mem.detach()
-            if bool(((a < 0) | (a > 1)).any()):
+            bad, near_one = (((a < 0) | (a > 1)).any(), (a > 0.99).any())
+            bad, near_one = torch.stack((bad, near_one)).tolist()      # one read-back for both
+            if bad:
                 raise ValueError("'alpha' must be between 0 and 1.")
+            # 1 - alpha is the input scale under norm_input.  While it is at least 0.01 the backward
+            # rebuilds the scale gradient from v_mem (relative error ~ulp(v)/(scale*x), far below
+            # 1e-5) and need not keep or re-read the input; closer to zero it reads the input.
+            self._scale_nonzero = not near_one
             if self.min_v_mem is not None:
                 th = torch.as_tensor(self.spike_threshold, dtype=torch.float32, device=dev)
                 lo = torch.as_tensor(self.min_v_mem, dtype=torch.float32, device=dev)

@@ -56,7 +56,7 @@ class _LifCore:
 
     @staticmethod
     def forward(ctx, inp, alpha, v_init, theta, subtract, min_v_mem, in_scale, surrogate_fn, max_spikes,
-                reset_mode, spike_count, B, T, M, layout):
+                reset_mode, spike_count, B, T, M, layout, scale_grad_from_state=False):
         N = B * M
         a_f, th_f, c_f, lo_f, sc_f = map(_flat32, (alpha, theta, subtract, min_v_mem, in_scale))
         modes = dict(
@@ -78,13 +78,16 @@ class _LifCore:
         ctx.reset_mode = reset_mode
         ctx.want_alpha = alpha is not None and alpha.requires_grad
         ctx.want_scale = in_scale is not None and in_scale.requires_grad
+        # The scale gradient either reads the forward input again or is rebuilt from v_mem alone
+        # (no extra tensor kept alive or streamed); the latter needs every scale to be non-zero.
+        ctx.save_input = ctx.want_scale and not scale_grad_from_state
         ctx.alpha_shape = None if alpha is None else alpha.shape
         ctx.scale_shape = None if in_scale is None else in_scale.shape
         ctx.v_init_shape = None if v_init is None else v_init.shape
         ctx.has = tuple(t is not None for t in (c_f, lo_f, sc_f, vi_f))
         saved = [v_mem, a_f, th_f]
         saved += [t for t in (c_f, lo_f, sc_f, vi_f) if t is not None]
-        if ctx.want_scale:
+        if ctx.save_input:
             saved.append(inp)
         ctx.save_for_backward(*saved)
         return spikes, v_mem, v_post_last
@@ -100,7 +103,7 @@ class _LifCore:
         lo_f = rest.pop(0) if ctx.has[1] else None
         sc_f = rest.pop(0) if ctx.has[2] else None
         vi_f = rest.pop(0) if ctx.has[3] else None
-        inp = rest.pop(0) if ctx.want_scale else None
+        inp = rest.pop(0) if ctx.save_input else None
         modes = ctx.modes
         dev = v_mem.device
 
@@ -204,12 +207,14 @@ class IntegrateAndFireTM(torch.autograd.Function):
     multiplies the input per neuron.  ``v_post_last`` (B*M,) is the state after the
     last reset; a gradient arriving on it is folded into the sweep.  ``spike_count``
     is an optional zero-initialised int64 tensor of one element that receives the
-    total number of spikes.
+    total number of spikes.  ``scale_grad_from_state=True`` makes the backward rebuild the
+    gradient w.r.t. ``in_scale`` from the saved membrane potential instead of keeping and re-reading
+    the input; the caller guarantees that no scale is zero.
     """
 
     @staticmethod
     def forward(ctx, inp, alpha, v_init, threshold, membrane_subtract, min_v_mem, in_scale,
-                surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count):
+                surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count, scale_grad_from_state=False):
         if inp.ndim != 3:
             raise ValueError("'inp' must be 3D, (batch, time, neurons)")
         if not inp.is_contiguous():
@@ -219,9 +224,9 @@ class IntegrateAndFireTM(torch.autograd.Function):
             raise ValueError("'v_init' must hold one value per batch item and neuron")
         return _LifCore.forward(ctx, inp, alpha, v_init, threshold, membrane_subtract, min_v_mem, in_scale,
                                 surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count,
-                                B, T, M, _lib.LAYOUT_BTM)
+                                B, T, M, _lib.LAYOUT_BTM, scale_grad_from_state)
 
     @staticmethod
     def backward(ctx, grad_spikes, grad_v_mem, grad_v_last):
         grad_input, grad_alpha, grad_init, grad_scale = _LifCore.backward(ctx, grad_spikes, grad_v_mem, grad_v_last)
-        return grad_input, grad_alpha, grad_init, None, None, None, grad_scale, None, None, None, None
+        return grad_input, grad_alpha, grad_init, None, None, None, grad_scale, None, None, None, None, None

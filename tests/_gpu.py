@@ -65,7 +65,7 @@ def lif_forward(cs, B, M, layout, mode=_lib.PARAM_PER_N, max_spikes=None, reset_
 
 def lif_backward(cs, v_mem, go, B, M, layout, mode=_lib.PARAM_PER_N, gv=None, g_last=None, surr=None,
                  kind=_lib.SURR_GENERIC, p0=0.0, p1=0.0, max_spikes=None, reset_mode=_lib.RESET_SUBTRACT,
-                 want_alpha=False, in_scale=None, want_scale=False, want_init=True):
+                 want_alpha=False, in_scale=None, want_scale=False, want_init=True, scale_from_state=False):
     N, T = v_mem.shape
     gi = torch.full((N, T), float("nan"), device=DEV)
     gi = to_dev(gi.cpu().numpy(), B, M, layout)
@@ -74,7 +74,7 @@ def lif_backward(cs, v_mem, go, B, M, layout, mode=_lib.PARAM_PER_N, gv=None, g_
     gs = torch.empty(N, device=DEV) if want_scale else None
     _lib.lif_backward(gi, ga, g0, gs, to_dev(go, B, M, layout), to_dev(gv, B, M, layout), vec(g_last),
                       to_dev(v_mem, B, M, layout), to_dev(surr, B, M, layout), vec(cs["v_init"]),
-                      to_dev(cs["inp"], B, M, layout) if want_scale else None,
+                      to_dev(cs["inp"], B, M, layout) if (want_scale and not scale_from_state) else None,
                       param(in_scale, mode, B, M), param(cs["alpha"], mode, B, M), param(cs["subtract"], mode, B, M),
                       param(cs["theta"], mode, B, M), param(cs["theta_low"], mode, B, M), max_spikes, reset_mode,
                       kind, p0, p1, B, T, M, layout)

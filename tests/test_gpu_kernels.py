@@ -138,6 +138,7 @@ def test_in_scale_and_state_gradient(layout):
     B, T, M = 3, 40, 20
     N = B * M
     cs = lif_case(77, N, T, clamp=True)
+    cs["alpha"] = np.minimum(cs["alpha"], np.float32(0.97))
     scale = (1.0 - cs["alpha"]).astype(np.float32)
     scaled = dict(cs, inp=(scale[:, None] * cs["inp"]).astype(np.float32))
     s_ref, v_ref = orc.lif_forward(scaled["inp"], cs["v_init"], cs["alpha"], cs["subtract"], cs["theta"], cs["theta_low"])
@@ -161,6 +162,13 @@ def test_in_scale_and_state_gradient(layout):
     assert rel_err(gi, scale[:, None].astype(np.float64) * R64) < TOL
     assert rel_err(gs, (R64 * cs["inp"].astype(np.float64)).sum(1)) < TOL
     assert rel_err(g0, cs["alpha"].astype(np.float64) * R64[:, 0]) < TOL
+    # the same scale gradient rebuilt from v_mem alone (no input tensor passed), with and without alpha gradient
+    for want_alpha in (False, True):
+        gi2, _, _, gs2 = _gpu.lif_backward(cs, v_ref, go, B, M, layout, g_last=G, kind=_lib.SURR_SINGLE_EXPONENTIAL,
+                                           p0=0.5, p1=1.0, in_scale=scale, want_scale=True, scale_from_state=True,
+                                           want_alpha=want_alpha)
+        np.testing.assert_array_equal(gi2, gi)
+        assert rel_err(gs2, (R64 * cs["inp"].astype(np.float64)).sum(1)) < TOL
 
 
 @pytest.mark.parametrize("layout", [0, 1])
