@@ -4,6 +4,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 
 #include "exb_kernels.cuh"
 
@@ -81,9 +82,11 @@ int exb_device_status(int device, void *stream)
 {
     DeviceGuard guard(device);
     if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_device_status: cannot select device %d", device);
-    unsigned int code = 0;
+    unsigned int code = 0, code2 = 0;
     cudaError_t e = exb::read_device_status((cudaStream_t)stream, &code);
+    if (e == cudaSuccess) e = exb::read_device_status_lif_bwd((cudaStream_t)stream, &code2);
     if (e != cudaSuccess) return fail(EXB_ERR_LAUNCH, "exb_device_status: %s", cudaGetErrorString(e));
+    if (!code) code = code2;
     if (code) return fail(EXB_ERR_TIMEOUT, "a bounded device-side wait ran out (code %u); results of the affected call are incomplete", code);
     return EXB_OK;
 }

@@ -63,6 +63,7 @@ cudaError_t launch_leaky_backward_scan(const LeakyBwdArgs &a, void *workspace, i
 size_t leaky_scan_static_capacity();
 cudaError_t launch_leaky_forward_scan_static(const LeakyFwdArgs &a, int device, cudaStream_t s, bool *used);
 cudaError_t read_device_status(cudaStream_t s, unsigned int *out);
+cudaError_t read_device_status_lif_bwd(cudaStream_t s, unsigned int *out);
 // EXB_DISABLE_TMA=1 in the environment forces the plain-load kernels (debugging aid).
 bool tma_enabled();
 

@@ -97,9 +97,10 @@ __device__ __forceinline__ void produce_segment(Ring *ring, float *stages, const
     const int stage_floats = nmaps * tensor_floats;
     const int S = pc.stages;
     int k = 0;
+    int s = 0;
+    uint32_t par = 0u;             // (k / S) & 1, kept incrementally
     for (; k < nA + nB; ++k) {
-        const int s = k % S;
-        if (k >= S && !mbar_wait(smem_u32(&ring->empty[s]), (uint32_t)(((k / S) - 1) & 1))) {
+        if (k >= S && !mbar_wait(smem_u32(&ring->empty[s]), par ^ 1u)) {
             report_timeout(EXB_STATUS_EMPTY_WAIT);
             ring->aborted = 1;
             break;
@@ -118,6 +119,7 @@ __device__ __forceinline__ void produce_segment(Ring *ring, float *stages, const
                 tma_load_3d(smem_u32(dst + i * tensor_floats + j * pc.tc * G::BW), maps[i], m0 + j * G::BW,
                             t0 + chunk * pc.tc, b, bar);
         }
+        if (++s == S) { s = 0; par ^= 1u; }
     }
     ring->issued = k;
 }
@@ -188,11 +190,12 @@ leaky_fwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A
         const int64_t M = A.M;
         const int col = tile_col_off<NW, V>(pc.tc, c);
         bool ok = true;
+        RingPos pos = {0, 0u};
         int k = 0;
         // ---- pass A: aggregate from a zero state
         for (; k < nA; ++k) {
-            if (!wait_chunk(ring, k, pc.stages)) { ok = false; break; }
-            const float *st = stages + (size_t)(k % pc.stages) * tensor_floats + col;
+            if (!wait_chunk(ring, pos)) { ok = false; break; }
+            const float *st = stages + (size_t)pos.s * tensor_floats + col;
             const int tmax = min(pc.tc, nsteps - k * pc.tc);
 #pragma unroll 4
             for (int tt = 0; tt < tmax; ++tt) {
@@ -201,7 +204,8 @@ leaky_fwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A
 #pragma unroll
                 for (int j = 0; j < V; ++j) v[j] = __fmaf_rn(v[j], al[j], __fmul_rn(sc[j], xs[j]));
             }
-            release_chunk(ring, k, pc.stages, lane);
+            release_chunk(ring, pos, lane);
+            pos.advance(pc.stages);
         }
         if (nA > 0) publish_aggregate<NW, V>(ws, ring, ok, tile * sg.nseg + seg, c, v);
         // ---- carry: v_init folded with the aggregates of all earlier segments
@@ -227,8 +231,8 @@ leaky_fwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A
         // ---- pass B: the real thing
         float *out = A.out + ((int64_t)b * T + t0) * M + mm;
         for (int kb = 0; kb < nck && ok; ++kb, ++k) {
-            if (!wait_chunk(ring, k, pc.stages)) { ok = false; break; }
-            const float *st = stages + (size_t)(k % pc.stages) * tensor_floats + col;
+            if (!wait_chunk(ring, pos)) { ok = false; break; }
+            const float *st = stages + (size_t)pos.s * tensor_floats + col;
             const int tmax = min(pc.tc, nsteps - kb * pc.tc);
 #pragma unroll 4
             for (int tt = 0; tt < tmax; ++tt) {
@@ -239,7 +243,8 @@ leaky_fwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A
                 if (valid) stv<V>(out, v);
                 out += M;
             }
-            release_chunk(ring, k, pc.stages, lane);
+            release_chunk(ring, pos, lane);
+            pos.advance(pc.stages);
         }
         if (ok && valid && last_seg && A.v_last) {
 #pragma unroll
@@ -304,11 +309,12 @@ leaky_bwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A
         const int64_t M = A.M;
         const int col = tile_col_off<NW, V>(pc.tc, c);
         bool ok = true;
+        RingPos pos = {0, 0u};
         int k = 0;
         // ---- pass A: aggregate (value at the first step of the segment) from a zero carry
         for (; k < nA; ++k) {
-            if (!wait_chunk(ring, k, pc.stages)) { ok = false; break; }
-            const float *stg = stages + (size_t)(k % pc.stages) * stage_floats + col;
+            if (!wait_chunk(ring, pos)) { ok = false; break; }
+            const float *stg = stages + (size_t)pos.s * stage_floats + col;
             const int chunk = nck - 1 - k;
             const int tmax = min(pc.tc, nsteps - chunk * pc.tc);
 #pragma unroll 4
@@ -322,7 +328,8 @@ leaky_bwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A
                     Gv[j] = __fmaf_rn(Gv[j], al[j], go[j]);
                 }
             }
-            release_chunk(ring, k, pc.stages, lane);
+            release_chunk(ring, pos, lane);
+            pos.advance(pc.stages);
         }
         if (nA > 0) publish_aggregate<NW, V>(ws, ring, ok, tile * sg.nseg + seg, c, Gv);
         // ---- carry from all later time segments (earlier in scan order); they all have L steps
@@ -352,8 +359,8 @@ leaky_bwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A
         for (int j = 0; j < V; ++j) { ag[j] = 0.0f; sgr[j] = 0.0f; }
         float *gi_base = A.grad_input + ((int64_t)b * T + t0) * M + mm;
         for (int kb = 0; kb < nck && ok; ++kb, ++k) {
-            if (!wait_chunk(ring, k, pc.stages)) { ok = false; break; }
-            const float *stg = stages + (size_t)(k % pc.stages) * stage_floats + col;
+            if (!wait_chunk(ring, pos)) { ok = false; break; }
+            const float *stg = stages + (size_t)pos.s * stage_floats + col;
             const int chunk = nck - 1 - kb;
             const int tmax = min(pc.tc, nsteps - chunk * pc.tc);
             float *gi = gi_base + (int64_t)(chunk * pc.tc + tmax - 1) * M;
@@ -377,7 +384,8 @@ leaky_bwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A
                 if (valid) stv<V>(gi, r);
                 gi -= M;
             }
-            release_chunk(ring, k, pc.stages, lane);
+            release_chunk(ring, pos, lane);
+            pos.advance(pc.stages);
         }
         if (ok && valid) {
 #pragma unroll

@@ -62,8 +62,7 @@ __global__ void __launch_bounds__(256) lif_fwd_btm_kernel(const LifFwdArgs A)
         for (int u = 0; u < U; ++u) {
             const int64_t tt = t + u;
             if (tt < T) {
-#pragma unroll
-                for (int j = 0; j < V; ++j) lif_step<RESET>(v[j], af[j], xc[u][j], q[j], cfg, cnt);
+                lif_step_vec<RESET, V, V>(v, af, xc[u], q, cfg, cnt);
                 if (valid) {
                     stv<V>(sp + tt * M, af);
                     stv<V>(vm + tt * M, v);
@@ -80,7 +79,7 @@ __global__ void __launch_bounds__(256) lif_fwd_btm_kernel(const LifFwdArgs A)
         for (int j = 0; j < V; ++j) A.v_post_last[n + j] = post_reset<RESET>(v[j], af[j], q[j]);
     }
     if (A.spike_count) {
-        const unsigned long long tot = warp_sum_u64(valid ? cnt.total() : 0ull);
+        const unsigned long long tot = warp_sum_u64(valid ? cnt.total(cfg) : 0ull);
         if ((threadIdx.x & 31) == 0 && tot) atomicAdd(A.spike_count, tot);
     }
 }
@@ -231,7 +230,7 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_fwd_nt_kernel(const LifFwdA
     }
     if (A.v_post_last && valid) A.v_post_last[n] = post_reset<RESET>(v, af, q);
     if (A.spike_count) {
-        const unsigned long long tot = warp_sum_u64(valid ? cnt.total() : 0ull);
+        const unsigned long long tot = warp_sum_u64(valid ? cnt.total(cfg) : 0ull);
         if (lane == 0 && tot) atomicAdd(A.spike_count, tot);
     }
 }

@@ -60,6 +60,14 @@ struct Neuron {
 
 struct NeuronParams {
     Param alpha, c, th, lo, scale;
+    // true when no parameter varies between neurons
+    __host__ bool uniform() const
+    {
+        const Param *all[5] = {&alpha, &c, &th, &lo, &scale};
+        for (const Param *q : all)
+            if (q->p && (q->sb != 0 || q->sm != 0)) return false;
+        return true;
+    }
     __device__ __forceinline__ Neuron load(int64_t b, int64_t m, const SpikeCfg &cfg) const
     {
         Neuron q;
@@ -85,12 +93,15 @@ __device__ __forceinline__ float spike_count_f(float v, const Neuron &q, const S
     return af;
 }
 
-// Exact spike total of one thread: c32 counts steps with at least one spike, c64 the rest
-// (modulo 2^64, so that a correction below zero cancels against c32).
+// Exact spike total of one thread: c32 counts steps that reached the threshold, c64 collects what
+// the exact path adds or takes away (modulo 2^64, so that a correction below zero cancels).
 struct SpikeTotal {
     unsigned c32;
     unsigned long long c64;
-    __device__ __forceinline__ unsigned long long total() const { return c64 + c32; }
+    __device__ __forceinline__ unsigned long long total(const SpikeCfg &cfg) const
+    {
+        return c64 + (unsigned long long)c32 * cfg.oneu;
+    }
 };
 
 // One forward step (cuda/lif_kernels.h:61-84): reset with the previous count `af`, decay,
@@ -105,11 +116,45 @@ __device__ __forceinline__ void lif_step(float &v, float &af, float x, const Neu
     v = (v < q.lo) ? q.lo : v;
     const bool sp = v >= q.th;
     af = sp ? cfg.onef : 0.0f;
-    cnt.c32 += sp ? cfg.oneu : 0u;
+    cnt.c32 += sp ? 1u : 0u;
     if (v >= q.th2) {
         const unsigned a = min(__float2uint_rz(__fdiv_rn(v, q.th)), cfg.maxs);
         af = __uint2float_rn(a);
         cnt.c64 += (unsigned long long)a - (unsigned long long)cfg.oneu;
+    }
+}
+
+// The same step for the V neurons of one thread, with ONE branch for the rare exact path
+// instead of one per neuron.
+// NQ is V (one set of constants per neuron) or 1 (all parameters are single values, so the
+// thread keeps one set for its V neurons: fewer registers, nothing recomputed).
+template <int RESET, int V, int NQ>
+__device__ __forceinline__ void lif_step_vec(float (&v)[V], float (&af)[V], const float (&x)[V], const Neuron (&qs)[NQ],
+                                             const SpikeCfg &cfg, SpikeTotal &cnt)
+{
+    bool exact = false;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        const Neuron &q = qs[NQ == 1 ? 0 : j];
+        if (RESET == EXB_RESET_SUBTRACT) v[j] = __fmaf_rn(-af[j], q.c, v[j]);
+        else v[j] = (af[j] != 0.0f) ? q.c : v[j];
+        v[j] = __fmaf_rn(v[j], q.alpha, __fmul_rn(q.scale, x[j]));
+        v[j] = (v[j] < q.lo) ? q.lo : v[j];
+        const bool sp = v[j] >= q.th;
+        af[j] = sp ? cfg.onef : 0.0f;
+        cnt.c32 += sp ? 1u : 0u;
+        exact |= (v[j] >= q.th2);
+    }
+    if (exact) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const Neuron &q = qs[NQ == 1 ? 0 : j];
+            if (v[j] >= q.th2) {
+                const unsigned a = min(__float2uint_rz(__fdiv_rn(v[j], q.th)), cfg.maxs);
+                af[j] = __uint2float_rn(a);
+                cnt.c64 += (unsigned long long)a - (unsigned long long)cfg.oneu;
+            }
+        }
     }
 }
 

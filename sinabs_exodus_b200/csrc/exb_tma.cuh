@@ -21,10 +21,10 @@
 
 namespace exb {
 
-// Status word: 0 = fine; otherwise the code of the first wait that ran out.
-// This header is included by exactly one translation unit, which also owns
-// the host-side accessor (read_device_status).
-__device__ unsigned int g_exb_status = 0;
+// Status word: 0 = fine; otherwise the code of the first wait that ran out.  One per
+// translation unit that includes this header (static); each such unit exports a reader, and
+// exb_device_status looks at all of them.
+static __device__ unsigned int g_exb_status = 0;
 
 enum { EXB_STATUS_FULL_WAIT = 1, EXB_STATUS_EMPTY_WAIT = 2, EXB_STATUS_DRAIN_WAIT = 3, EXB_STATUS_LOOKBACK_WAIT = 4 };
 
@@ -130,10 +130,5 @@ __device__ __forceinline__ void ring_finish(Ring *r, int stages)
         }
     }
 }
-
-// ---- host side ------------------------------------------------------------
-// Builds a tensor map for a float32 (B, T, M) tensor with box (box_m, box_t, 1).
-// Returns false when TMA cannot be used (alignment, sizes, driver entry point).
-bool make_btm_tensor_map(CUtensorMap *map, const float *base, int64_t B, int64_t T, int64_t M, int box_m, int box_t);
 
 }  // namespace exb

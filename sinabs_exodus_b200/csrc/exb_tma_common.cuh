@@ -1,0 +1,208 @@
+// Pieces shared by the translation units that hold TMA-staged kernels: tile geometry, the
+// producer loop, ring bookkeeping, and the host-side helpers (tensor maps, pipeline shape).
+// Everything is `static`/inline so that every including translation unit is self-contained.
+#pragma once
+
+#include "exb_kernels.cuh"
+#include "exb_tma.cuh"
+
+#include <cudaTypedefs.h>
+#include <cstdlib>
+
+namespace exb {
+
+template <int NW, int V>
+struct TileGeom {
+    static constexpr int W = NW * 32 * V;
+    static constexpr int BW = (W > 256) ? 256 : W;
+    static constexpr int NBOX = W / BW;
+};
+
+// Resident CTAs per SM the kernels are compiled for (caps registers at 64 per thread).
+// Light kernels fit 64 registers; the backward with alpha/scale gradients or an exponential
+// surrogate keeps four neurons' constants and accumulators live and gets 96.
+template <int NW, int V, bool HEAVY = false>
+struct MinBlocks {
+    static constexpr int value = (V == 4) ? (HEAVY ? 4 : 6) : (HEAVY ? 6 : 8);
+};
+
+// Shared-memory float offset of neuron column c inside one tensor's part of a stage, at time
+// step 0 of the stage; consecutive time steps are BW floats apart.
+template <int NW, int V>
+__device__ __forceinline__ int tile_col_off(int tc, int c)
+{
+    using G = TileGeom<NW, V>;
+    return (c / G::BW) * tc * G::BW + (c % G::BW);
+}
+
+// Pipeline shape chosen by the launcher: time steps per stage and number of stages.
+struct PipeCfg {
+    int tc;
+    int stages;
+};
+
+// Producer: issues chunk k (k-th in processing order; `reverse` walks time backwards) of
+// `nmaps` tensors into stage k % S.
+template <int NW, int V>
+__device__ __forceinline__ void produce(Ring *ring, float *stages, const CUtensorMap *const *maps, int nmaps,
+                                        int nchunks, int m0, int b, PipeCfg pc, bool reverse)
+{
+    using G = TileGeom<NW, V>;
+    const int tensor_floats = pc.tc * G::W;
+    const int stage_floats = nmaps * tensor_floats;
+    const int S = pc.stages;
+    int k = 0;
+    int s = 0;
+    uint32_t par = 0u;             // (k / S) & 1, kept incrementally
+    for (; k < nchunks; ++k) {
+        if (k >= S && !mbar_wait(smem_u32(&ring->empty[s]), par ^ 1u)) {
+            report_timeout(EXB_STATUS_EMPTY_WAIT);
+            ring->aborted = 1;
+            break;
+        }
+        const uint32_t bar = smem_u32(&ring->full[s]);
+        mbar_arrive_expect_tx(bar, (uint32_t)(stage_floats * sizeof(float)));
+        float *dst = stages + (size_t)s * stage_floats;
+        const int chunk = reverse ? (nchunks - 1 - k) : k;
+        for (int i = 0; i < nmaps; ++i) {
+#pragma unroll
+            for (int j = 0; j < G::NBOX; ++j)
+                tma_load_3d(smem_u32(dst + i * tensor_floats + j * pc.tc * G::BW), maps[i], m0 + j * G::BW,
+                            chunk * pc.tc, b, bar);
+        }
+        if (++s == S) { s = 0; par ^= 1u; }
+    }
+    ring->issued = k;
+}
+
+struct TmaMaps {
+    CUtensorMap m[5];
+};
+
+template <int NW, int V>
+static size_t tma_smem_bytes(int nmaps, PipeCfg pc)
+{
+    return (size_t)pc.stages * nmaps * pc.tc * TileGeom<NW, V>::W * sizeof(float) + sizeof(Ring) + 128;
+}
+
+// Position in the ring: stage index and the parity of the phase being used there.  Advanced
+// incrementally (a `%` by a run-time stage count would cost an integer division per chunk).
+struct RingPos {
+    int s;
+    uint32_t phase;
+    __device__ __forceinline__ void advance(int S)
+    {
+        if (++s == S) { s = 0; phase ^= 1u; }
+    }
+};
+
+// Consumer-side wait for the chunk at `pos`; marks the ring aborted when the wait runs out.
+__device__ __forceinline__ bool wait_chunk(Ring *ring, const RingPos &pos)
+{
+    if (mbar_wait(smem_u32(&ring->full[pos.s]), pos.phase)) return true;
+    report_timeout(EXB_STATUS_FULL_WAIT);
+    ring->aborted = 1;
+    return false;
+}
+
+__device__ __forceinline__ void release_chunk(Ring *ring, const RingPos &pos, int lane)
+{
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&ring->empty[pos.s]));
+}
+
+// V floats of one consumer thread from a stage.
+template <int V>
+__device__ __forceinline__ void lds_vec(float (&d)[V], const float *p)
+{
+    if (V == 4) {
+        const float4 t = *reinterpret_cast<const float4 *>(p);
+        d[0] = t.x; d[1] = t.y; d[2] = t.z; d[3] = t.w;
+    } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) d[j] = p[j];
+    }
+}
+
+
+// ===========================================================================
+// host side
+// ===========================================================================
+static PFN_cuTensorMapEncodeTiled get_encode_fn()
+{
+    static PFN_cuTensorMapEncodeTiled fn = []() -> PFN_cuTensorMapEncodeTiled {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<PFN_cuTensorMapEncodeTiled>(p);
+    }();
+    return fn;
+}
+
+static bool make_btm_tensor_map(CUtensorMap *map, const float *base, int64_t B, int64_t T, int64_t M, int box_m, int box_t)
+{
+    PFN_cuTensorMapEncodeTiled enc = get_encode_fn();
+    if (!enc || !base) return false;
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) || (M % 4) || M <= 0 || T <= 0 || B <= 0) return false;
+    if (M > (1ll << 31) || T > (1ll << 31) || B > (1ll << 31)) return false;
+    if ((double)T * (double)M * 4.0 >= 1.0e12) return false;    // stride limit is 2^40 bytes
+    cuuint64_t gdim[3] = {(cuuint64_t)M, (cuuint64_t)T, (cuuint64_t)B};
+    cuuint64_t gstr[2] = {(cuuint64_t)M * 4u, (cuuint64_t)T * (cuuint64_t)M * 4u};
+    cuuint32_t box[3] = {(cuuint32_t)box_m, (cuuint32_t)box_t, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(base), gdim, gstr, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+// Tile shape choice: wide tiles (512 neurons, 4+1 warps) when they alone fill the GPU,
+// narrow tiles (128 neurons, 1+1 warps, longer time chunks) otherwise.  The pipeline shape
+// (time steps per stage, stages) keeps one stage at about 8-16 KB.  EXB_TMA_TC / EXB_TMA_STAGES
+// in the environment override it (tuning aid).
+static bool use_wide(int64_t B, int64_t M)
+{
+    const int64_t wide_tiles = B * ((M + 511) / 512);
+    return wide_tiles >= 2 * 148;
+}
+constexpr int NWARPS = 4;   // consumer warps per CTA in both tile shapes
+
+static int env_int(const char *name, int dflt)
+{
+    const char *v = getenv(name);
+    return (v && *v) ? atoi(v) : dflt;
+}
+
+static PipeCfg pipe_cfg(bool wide, int nmaps)  // wide: 4 neurons per thread (W = 512), else 1 (W = 128)
+{
+    static const int env_tc = env_int("EXB_TMA_TC", 0);
+    static const int env_st = env_int("EXB_TMA_STAGES", 0);
+    PipeCfg pc;
+    const int w = wide ? 512 : 128;
+    // target ~8 KB per stage across all streamed tensors
+    int tc = (8 * 1024) / (w * 4 * nmaps);
+    if (tc < 2) tc = 2;
+    if (tc > 32) tc = 32;
+    pc.tc = tc;
+    pc.stages = 4;
+    if (env_tc > 0) pc.tc = env_tc;
+    if (env_st > 1 && env_st <= MAX_STAGES) pc.stages = env_st;
+    if (pc.tc > 256) pc.tc = 256;
+    return pc;
+}
+
+template <typename K>
+static cudaError_t set_smem(K kern, size_t bytes)
+{
+    if (bytes <= 48 * 1024) return cudaSuccess;
+    return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+static bool eligible(int64_t B, int64_t T, int64_t M)
+{
+    return M % 4 == 0 && B * ((M + 127) / 128) <= 0x7fffffffll && T <= 0x7fffffffll;
+}
+
+}  // namespace exb

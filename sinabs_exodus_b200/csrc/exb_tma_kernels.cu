@@ -1,125 +1,17 @@
-// TMA-staged time-major kernels (spike scan forward, fused EXODUS backward,
-// leaky integrator forward and backward).  See exb_tma.cuh for the pipeline.
-//
-// Tile geometry: NW consumer warps, every consumer thread owns V (4 or 1)
-// adjacent neurons, so a CTA covers W = NW*32*V neurons of one batch item.
-// V = 1 is for problems with too few neurons to fill the GPU four per thread.  One stage
-// holds TC time steps of every streamed tensor; a tensor's part of the stage
-// is W/BW boxes of [TC][BW] floats (a TMA box is at most 256 elements wide).
-#include "exb_kernels.cuh"
-#include "exb_tma.cuh"
+// TMA-staged time-major kernels: spike scan forward, leaky integrator forward and backward,
+// the time-parallel leaky scan, and their launchers.  The fused LIF backward lives in
+// exb_tma_lif_bwd.cu.  See exb_tma.cuh for the pipeline.
+#include "exb_tma_common.cuh"
 
-#include <cudaTypedefs.h>
-#include <cstdlib>
 #include <mutex>
 
 namespace exb {
 
-template <int NW, int V>
-struct TileGeom {
-    static constexpr int W = NW * 32 * V;
-    static constexpr int BW = (W > 256) ? 256 : W;
-    static constexpr int NBOX = W / BW;
-};
-
-// Resident CTAs per SM the kernels are compiled for (caps registers at 64 per thread).
-// Light kernels fit 64 registers; the backward with alpha/scale gradients or an exponential
-// surrogate keeps four neurons' constants and accumulators live and gets 96.
-template <int NW, int V, bool HEAVY = false>
-struct MinBlocks {
-    static constexpr int value = (V == 4) ? (HEAVY ? 4 : 6) : (HEAVY ? 6 : 8);
-};
-
-// Shared-memory float offset of neuron column c inside one tensor's part of a stage, at time
-// step 0 of the stage; consecutive time steps are BW floats apart.
-template <int NW, int V>
-__device__ __forceinline__ int tile_col_off(int tc, int c)
-{
-    using G = TileGeom<NW, V>;
-    return (c / G::BW) * tc * G::BW + (c % G::BW);
-}
-
-// Pipeline shape chosen by the launcher: time steps per stage and number of stages.
-struct PipeCfg {
-    int tc;
-    int stages;
-};
-
-// Producer: issues chunk k (k-th in processing order; `reverse` walks time backwards) of
-// `nmaps` tensors into stage k % S.
-template <int NW, int V>
-__device__ __forceinline__ void produce(Ring *ring, float *stages, const CUtensorMap *const *maps, int nmaps,
-                                        int nchunks, int m0, int b, PipeCfg pc, bool reverse)
-{
-    using G = TileGeom<NW, V>;
-    const int tensor_floats = pc.tc * G::W;
-    const int stage_floats = nmaps * tensor_floats;
-    const int S = pc.stages;
-    int k = 0;
-    for (; k < nchunks; ++k) {
-        const int s = k % S;
-        if (k >= S && !mbar_wait(smem_u32(&ring->empty[s]), (uint32_t)(((k / S) - 1) & 1))) {
-            report_timeout(EXB_STATUS_EMPTY_WAIT);
-            ring->aborted = 1;
-            break;
-        }
-        const uint32_t bar = smem_u32(&ring->full[s]);
-        mbar_arrive_expect_tx(bar, (uint32_t)(stage_floats * sizeof(float)));
-        float *dst = stages + (size_t)s * stage_floats;
-        const int chunk = reverse ? (nchunks - 1 - k) : k;
-        for (int i = 0; i < nmaps; ++i) {
-#pragma unroll
-            for (int j = 0; j < G::NBOX; ++j)
-                tma_load_3d(smem_u32(dst + i * tensor_floats + j * pc.tc * G::BW), maps[i], m0 + j * G::BW,
-                            chunk * pc.tc, b, bar);
-        }
-    }
-    ring->issued = k;
-}
-
-struct TmaMaps {
-    CUtensorMap m[5];
-};
-
-template <int NW, int V>
-static size_t tma_smem_bytes(int nmaps, PipeCfg pc)
-{
-    return (size_t)pc.stages * nmaps * pc.tc * TileGeom<NW, V>::W * sizeof(float) + sizeof(Ring) + 128;
-}
-
-// Consumer-side wait for chunk k; marks the ring aborted when the wait runs out.
-__device__ __forceinline__ bool wait_chunk(Ring *ring, int k, int S)
-{
-    if (mbar_wait(smem_u32(&ring->full[k % S]), (uint32_t)((k / S) & 1))) return true;
-    report_timeout(EXB_STATUS_FULL_WAIT);
-    ring->aborted = 1;
-    return false;
-}
-
-__device__ __forceinline__ void release_chunk(Ring *ring, int k, int S, int lane)
-{
-    __syncwarp();
-    if (lane == 0) mbar_arrive(smem_u32(&ring->empty[k % S]));
-}
-
-// V floats of one consumer thread from a stage.
-template <int V>
-__device__ __forceinline__ void lds_vec(float (&d)[V], const float *p)
-{
-    if (V == 4) {
-        const float4 t = *reinterpret_cast<const float4 *>(p);
-        d[0] = t.x; d[1] = t.y; d[2] = t.z; d[3] = t.w;
-    } else {
-#pragma unroll
-        for (int j = 0; j < V; ++j) d[j] = p[j];
-    }
-}
-
 // ===========================================================================
 // spike scan forward
 // ===========================================================================
-template <int RESET, int NW, int V>
-__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V>::value)
+template <int RESET, int NW, int V, bool UNI>
+__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V, (V == 4 && !UNI)>::value)
 lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, const int tiles_m, const PipeCfg pc)
 {
     using G = TileGeom<NW, V>;
@@ -147,11 +39,13 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
         const int64_t mm = valid ? m : 0;
         const int64_t n = (int64_t)b * A.M + mm;
         const SpikeCfg cfg = make_spike_cfg(A.maxs);
-        Neuron q[V];
+        constexpr int NQ = UNI ? 1 : V;       // UNI: every parameter is a single value
+        Neuron q[NQ];
         float v[V], af[V];
 #pragma unroll
+        for (int j = 0; j < NQ; ++j) q[j] = A.np.load(b, mm + j, cfg);
+#pragma unroll
         for (int j = 0; j < V; ++j) {
-            q[j] = A.np.load(b, mm + j, cfg);
             v[j] = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
             af[j] = 0.0f;
         }
@@ -163,16 +57,16 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
         SpikeTotal cnt;
         cnt.c32 = 0u; cnt.c64 = 0ull;
         bool ok = true;
+        RingPos pos = {0, 0u};
         for (int k = 0; k < nchunks; ++k) {
-            if (!wait_chunk(ring, k, pc.stages)) { ok = false; break; }
-            const float *st = stages + (size_t)(k % pc.stages) * tensor_floats + col;
+            if (!wait_chunk(ring, pos)) { ok = false; break; }
+            const float *st = stages + (size_t)pos.s * tensor_floats + col;
             const int tmax = min(pc.tc, T - k * pc.tc);
 #pragma unroll 4
             for (int tt = 0; tt < tmax; ++tt) {
                 float xs[V];
                 lds_vec<V>(xs, st + tt * G::BW);
-#pragma unroll
-                for (int j = 0; j < V; ++j) lif_step<RESET>(v[j], af[j], xs[j], q[j], cfg, cnt);
+                lif_step_vec<RESET, V, NQ>(v, af, xs, q, cfg, cnt);
                 if (valid) {
                     stv<V>(sp, af);
                     stv<V>(vm, v);
@@ -180,117 +74,16 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
                 sp += M;
                 vm += M;
             }
-            release_chunk(ring, k, pc.stages, lane);
+            release_chunk(ring, pos, lane);
+            pos.advance(pc.stages);
         }
         if (ok && valid && A.v_post_last) {
 #pragma unroll
-            for (int j = 0; j < V; ++j) A.v_post_last[n + j] = post_reset<RESET>(v[j], af[j], q[j]);
+            for (int j = 0; j < V; ++j) A.v_post_last[n + j] = post_reset<RESET>(v[j], af[j], q[NQ == 1 ? 0 : j]);
         }
         if (A.spike_count) {
-            const unsigned long long tot = warp_sum_u64((valid && ok) ? cnt.total() : 0ull);
+            const unsigned long long tot = warp_sum_u64((valid && ok) ? cnt.total(cfg) : 0ull);
             if (lane == 0 && tot) atomicAdd(A.spike_count, tot);
-        }
-    }
-    ring_finish(ring, pc.stages);
-}
-
-// ===========================================================================
-// fused reverse-time backward
-// ===========================================================================
-template <int SURR, int RESET, bool WA, int WS, int NW, int V>
-__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V, (WA || WS != 0 || SURR == EXB_SURR_GENERIC || SURR == EXB_SURR_PERIODIC_EXPONENTIAL || SURR == EXB_SURR_SINGLE_EXPONENTIAL)>::value)
-lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, const int tiles_m, const int nmaps,
-                   const PipeCfg pc)
-{
-    using G = TileGeom<NW, V>;
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    float *stages = reinterpret_cast<float *>(smem_raw);
-    const int tensor_floats = pc.tc * G::W;
-    const int stage_floats = nmaps * tensor_floats;
-    Ring *ring = reinterpret_cast<Ring *>(smem_raw + (size_t)pc.stages * stage_floats * sizeof(float));
-    ring_init(ring, pc.stages, NW);
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.x / tiles_m;
-    const int m0 = (blockIdx.x - b * tiles_m) * G::W;
-    const int T = (int)A.T;
-    const int nchunks = (T + pc.tc - 1) / pc.tc;
-    // stage layout: [grad_spikes][v_mem]([grad_v_mem])([surr])([input])
-    const bool has_gv = A.gv != nullptr;
-    const int i_sl = 2 + (has_gv ? 1 : 0);
-    const int i_x = i_sl + ((SURR == EXB_SURR_GENERIC) ? 1 : 0);
-
-    if (warp == NW) {
-        if (lane == 0) {
-            const CUtensorMap *mp[5] = {&maps.m[0], &maps.m[1], &maps.m[2], &maps.m[3], &maps.m[V]};
-            produce<NW, V>(ring, stages, mp, nmaps, nchunks, m0, b, pc, true);
-        }
-    } else {
-        const int c = threadIdx.x * V;
-        const int64_t m = (int64_t)m0 + c;
-        const bool valid = m < A.M;
-        const int64_t mm = valid ? m : 0;
-        const int64_t n = (int64_t)b * A.M + mm;
-        const SpikeCfg cfg = make_spike_cfg(A.maxs);
-        Neuron q[V];
-        SurrConst sc[V];
-        float cp[V], Rprev[V], f0[V], glast[V];
-        bool n0[V];
-        BwdState st[V];
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-            q[j] = A.np.load(b, mm + j, cfg);
-            sc[j] = surr_prepare<SURR>(q[j], A.p0, A.p1);
-            cp[j] = __fmul_rn(q[j].alpha, q[j].c);
-            st[j].R = 0.0f; st[j].ag = 0.0f; st[j].sg = 0.0f; st[j].vnext = 0.0f;
-            Rprev[j] = 0.0f; f0[j] = 0.0f; n0[j] = true;
-            glast[j] = A.g_last ? __ldg(A.g_last + n + j) : 0.0f;
-        }
-        const int64_t M = A.M;
-        float *gi_base = A.grad_input + ((int64_t)b * T) * M + mm;
-        const int col = tile_col_off<NW, V>(pc.tc, c);
-        bool ok = true;
-        for (int k = 0; k < nchunks; ++k) {
-            if (!wait_chunk(ring, k, pc.stages)) { ok = false; break; }
-            const float *stg = stages + (size_t)(k % pc.stages) * stage_floats + col;
-            const int chunk = nchunks - 1 - k;
-            const int tmax = min(pc.tc, T - chunk * pc.tc);
-            float *gi = gi_base + (int64_t)(chunk * pc.tc + tmax - 1) * M;
-#pragma unroll 2
-            for (int tt = tmax - 1; tt >= 0; --tt) {
-                const float *e = stg + tt * G::BW;
-                float go[V], vv[V];
-                float gv[V] = {}, sl[V] = {}, xx[V] = {};
-                lds_vec<V>(go, e);
-                lds_vec<V>(vv, e + tensor_floats);
-                if (has_gv) lds_vec<V>(gv, e + 2 * tensor_floats);
-                if (SURR == EXB_SURR_GENERIC) lds_vec<V>(sl, e + i_sl * tensor_floats);
-                if (WS == SCALE_GRAD_FROM_INPUT) lds_vec<V>(xx, e + i_x * tensor_floats);
-                if (A.g_last && chunk * pc.tc + tt == T - 1) {
-#pragma unroll
-                    for (int j = 0; j < V; ++j) fold_last_state_grad<RESET>(go[j], gv[j], glast[j], vv[j], q[j], cfg);
-                }
-                float r[V];
-#pragma unroll
-                for (int j = 0; j < V; ++j) {
-                    Rprev[j] = st[j].R;
-                    const float Rt = lif_bwd_step<SURR, RESET, WA, WS>(st[j], vv[j], go[j], gv[j], sl[j], xx[j], q[j], sc[j],
-                                                                      cp[j], cfg, f0[j], n0[j]);
-                    r[j] = __fmul_rn(q[j].scale, Rt);
-                }
-                if (valid) stv<V>(gi, r);
-                gi -= M;
-            }
-            release_chunk(ring, k, pc.stages, lane);
-        }
-        if (ok && valid) {
-#pragma unroll
-            for (int j = 0; j < V; ++j) {
-                if (A.grad_init) A.grad_init[n + j] = __fmul_rn(q[j].alpha, st[j].R);
-                const float vi = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
-                if (WA) A.grad_alpha[n + j] = alpha_grad_finish<RESET>(st[j], vi, Rprev[j], f0[j], n0[j]);
-                if (WS) A.grad_scale[n + j] = scale_grad_finish<WS>(st[j], vi, q[j]);
-            }
         }
     }
     ring_finish(ring, pc.stages);
@@ -338,9 +131,10 @@ leaky_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A,
         float *out = A.out + ((int64_t)b * T) * M + mm;
         const int col = tile_col_off<NW, V>(pc.tc, c);
         bool ok = true;
+        RingPos pos = {0, 0u};
         for (int k = 0; k < nchunks; ++k) {
-            if (!wait_chunk(ring, k, pc.stages)) { ok = false; break; }
-            const float *st = stages + (size_t)(k % pc.stages) * tensor_floats + col;
+            if (!wait_chunk(ring, pos)) { ok = false; break; }
+            const float *st = stages + (size_t)pos.s * tensor_floats + col;
             const int tmax = min(pc.tc, T - k * pc.tc);
 #pragma unroll 4
             for (int tt = 0; tt < tmax; ++tt) {
@@ -351,7 +145,8 @@ leaky_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A,
                 if (valid) stv<V>(out, v);
                 out += M;
             }
-            release_chunk(ring, k, pc.stages, lane);
+            release_chunk(ring, pos, lane);
+            pos.advance(pc.stages);
         }
         if (ok && valid && A.v_last) {
 #pragma unroll
@@ -405,9 +200,10 @@ leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A,
         float *gi_base = A.grad_input + ((int64_t)b * T) * M + mm;
         const int col = tile_col_off<NW, V>(pc.tc, c);
         bool ok = true;
+        RingPos pos = {0, 0u};
         for (int k = 0; k < nchunks; ++k) {
-            if (!wait_chunk(ring, k, pc.stages)) { ok = false; break; }
-            const float *stg = stages + (size_t)(k % pc.stages) * stage_floats + col;
+            if (!wait_chunk(ring, pos)) { ok = false; break; }
+            const float *stg = stages + (size_t)pos.s * stage_floats + col;
             const int chunk = nchunks - 1 - k;
             const int tmax = min(pc.tc, T - chunk * pc.tc);
             float *gi = gi_base + (int64_t)(chunk * pc.tc + tmax - 1) * M;
@@ -432,7 +228,8 @@ leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A,
                 if (valid) stv<V>(gi, r);
                 gi -= M;
             }
-            release_chunk(ring, k, pc.stages, lane);
+            release_chunk(ring, pos, lane);
+            pos.advance(pc.stages);
         }
         if (ok && valid) {
 #pragma unroll
@@ -450,87 +247,7 @@ leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A,
 #include "exb_leaky_scan.cuh"
 namespace exb {
 
-// ===========================================================================
-// host side
-// ===========================================================================
-static PFN_cuTensorMapEncodeTiled get_encode_fn()
-{
-    static PFN_cuTensorMapEncodeTiled fn = []() -> PFN_cuTensorMapEncodeTiled {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
-            qres != cudaDriverEntryPointSuccess)
-            return nullptr;
-        return reinterpret_cast<PFN_cuTensorMapEncodeTiled>(p);
-    }();
-    return fn;
-}
-
-bool make_btm_tensor_map(CUtensorMap *map, const float *base, int64_t B, int64_t T, int64_t M, int box_m, int box_t)
-{
-    PFN_cuTensorMapEncodeTiled enc = get_encode_fn();
-    if (!enc || !base) return false;
-    if ((reinterpret_cast<uintptr_t>(base) & 15u) || (M % 4) || M <= 0 || T <= 0 || B <= 0) return false;
-    if (M > (1ll << 31) || T > (1ll << 31) || B > (1ll << 31)) return false;
-    if ((double)T * (double)M * 4.0 >= 1.0e12) return false;    // stride limit is 2^40 bytes
-    cuuint64_t gdim[3] = {(cuuint64_t)M, (cuuint64_t)T, (cuuint64_t)B};
-    cuuint64_t gstr[2] = {(cuuint64_t)M * 4u, (cuuint64_t)T * (cuuint64_t)M * 4u};
-    cuuint32_t box[3] = {(cuuint32_t)box_m, (cuuint32_t)box_t, 1u};
-    cuuint32_t estr[3] = {1u, 1u, 1u};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(base), gdim, gstr, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
-}
-
-// Tile shape choice: wide tiles (512 neurons, 4+1 warps) when they alone fill the GPU,
-// narrow tiles (128 neurons, 1+1 warps, longer time chunks) otherwise.  The pipeline shape
-// (time steps per stage, stages) keeps one stage at about 8-16 KB.  EXB_TMA_TC / EXB_TMA_STAGES
-// in the environment override it (tuning aid).
-static bool use_wide(int64_t B, int64_t M)
-{
-    const int64_t wide_tiles = B * ((M + 511) / 512);
-    return wide_tiles >= 2 * 148;
-}
-constexpr int NWARPS = 4;   // consumer warps per CTA in both tile shapes
-
-static int env_int(const char *name, int dflt)
-{
-    const char *v = getenv(name);
-    return (v && *v) ? atoi(v) : dflt;
-}
-
-static PipeCfg pipe_cfg(bool wide, int nmaps)  // wide: 4 neurons per thread (W = 512), else 1 (W = 128)
-{
-    static const int env_tc = env_int("EXB_TMA_TC", 0);
-    static const int env_st = env_int("EXB_TMA_STAGES", 0);
-    PipeCfg pc;
-    const int w = wide ? 512 : 128;
-    // target ~8 KB per stage across all streamed tensors
-    int tc = (8 * 1024) / (w * 4 * nmaps);
-    if (tc < 2) tc = 2;
-    if (tc > 32) tc = 32;
-    pc.tc = tc;
-    pc.stages = 4;
-    if (env_tc > 0) pc.tc = env_tc;
-    if (env_st > 1 && env_st <= MAX_STAGES) pc.stages = env_st;
-    if (pc.tc > 256) pc.tc = 256;
-    return pc;
-}
-
-template <typename K>
-static cudaError_t set_smem(K kern, size_t bytes)
-{
-    if (bytes <= 48 * 1024) return cudaSuccess;
-    return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-}
-
-static bool eligible(int64_t B, int64_t T, int64_t M)
-{
-    return M % 4 == 0 && B * ((M + 127) / 128) <= 0x7fffffffll && T <= 0x7fffffffll;
-}
-
-template <int RESET, int NW, int V>
+template <int RESET, int NW, int V, bool UNI>
 static cudaError_t run_lif_fwd(const LifFwdArgs &a, cudaStream_t s, bool *used)
 {
     using G = TileGeom<NW, V>;
@@ -541,7 +258,7 @@ static cudaError_t run_lif_fwd(const LifFwdArgs &a, cudaStream_t s, bool *used)
     const int tiles_m = (int)((a.M + G::W - 1) / G::W);
     const size_t smem = tma_smem_bytes<NW, V>(1, pc);
     if (smem > 200 * 1024) return cudaSuccess;
-    auto kern = lif_fwd_tma_kernel<RESET, NW, V>;
+    auto kern = lif_fwd_tma_kernel<RESET, NW, V, UNI>;
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
     kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m, pc);
@@ -554,75 +271,15 @@ cudaError_t launch_lif_forward_tma(const LifFwdArgs &a, int reset_mode, cudaStre
     *used = false;
     if (!eligible(a.B, a.T, a.M) || !aligned16(a.spikes) || !aligned16(a.v_mem) || !aligned16(a.input)) return cudaSuccess;
     const bool wide = use_wide(a.B, a.M);
-    if (reset_mode == EXB_RESET_SUBTRACT)
-        return wide ? run_lif_fwd<EXB_RESET_SUBTRACT, NWARPS, 4>(a, s, used) : run_lif_fwd<EXB_RESET_SUBTRACT, NWARPS, 1>(a, s, used);
-    return wide ? run_lif_fwd<EXB_RESET_TO_VALUE, NWARPS, 4>(a, s, used) : run_lif_fwd<EXB_RESET_TO_VALUE, NWARPS, 1>(a, s, used);
-}
-
-template <int SURR, int RESET, bool WA, int WS, int NW, int V>
-static cudaError_t run_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
-{
-    using G = TileGeom<NW, V>;
-    TmaMaps maps;
-    const float *ptrs[5] = {a.go, a.v_mem, nullptr, nullptr, nullptr};
-    int nmaps = 2;
-    if (a.gv) ptrs[nmaps++] = a.gv;
-    if (SURR == EXB_SURR_GENERIC) ptrs[nmaps++] = a.surr;
-    if (WS == SCALE_GRAD_FROM_INPUT) ptrs[nmaps++] = a.input;
-    const PipeCfg pc = pipe_cfg(V == 4, nmaps);
-    for (int i = 0; i < nmaps; ++i)
-        if (!make_btm_tensor_map(&maps.m[i], ptrs[i], a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
-    for (int i = nmaps; i < 5; ++i) maps.m[i] = maps.m[0];
-    const int tiles_m = (int)((a.M + G::W - 1) / G::W);
-    const size_t smem = tma_smem_bytes<NW, V>(nmaps, pc);
-    if (smem > 200 * 1024) return cudaSuccess;
-    auto kern = lif_bwd_tma_kernel<SURR, RESET, WA, WS, NW, V>;
-    cudaError_t e = set_smem(kern, smem);
-    if (e != cudaSuccess) return e;
-    kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m, nmaps, pc);
-    *used = true;
-    return cudaPeekAtLastError();
-}
-
-template <int SURR, int RESET, bool WA, int WS>
-static cudaError_t pick_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
-{
-    return use_wide(a.B, a.M) ? run_lif_bwd<SURR, RESET, WA, WS, NWARPS, 4>(a, s, used)
-                              : run_lif_bwd<SURR, RESET, WA, WS, NWARPS, 1>(a, s, used);
-}
-
-template <int SURR, int RESET>
-static cudaError_t flags_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
-{
-    const bool wa = a.grad_alpha != nullptr;
-    const int ws = a.grad_scale ? (a.input ? SCALE_GRAD_FROM_INPUT : SCALE_GRAD_FROM_STATE) : SCALE_GRAD_NONE;
-    if (wa) {
-        if (ws == SCALE_GRAD_FROM_INPUT) return pick_lif_bwd<SURR, RESET, true, SCALE_GRAD_FROM_INPUT>(a, s, used);
-        if (ws == SCALE_GRAD_FROM_STATE) return pick_lif_bwd<SURR, RESET, true, SCALE_GRAD_FROM_STATE>(a, s, used);
-        return pick_lif_bwd<SURR, RESET, true, SCALE_GRAD_NONE>(a, s, used);
+    const bool uni = a.np.uniform();
+    if (reset_mode == EXB_RESET_SUBTRACT) {
+        if (!wide) return run_lif_fwd<EXB_RESET_SUBTRACT, NWARPS, 1, true>(a, s, used);
+        return uni ? run_lif_fwd<EXB_RESET_SUBTRACT, NWARPS, 4, true>(a, s, used)
+                   : run_lif_fwd<EXB_RESET_SUBTRACT, NWARPS, 4, false>(a, s, used);
     }
-    if (ws == SCALE_GRAD_FROM_INPUT) return pick_lif_bwd<SURR, RESET, false, SCALE_GRAD_FROM_INPUT>(a, s, used);
-    if (ws == SCALE_GRAD_FROM_STATE) return pick_lif_bwd<SURR, RESET, false, SCALE_GRAD_FROM_STATE>(a, s, used);
-    return pick_lif_bwd<SURR, RESET, false, SCALE_GRAD_NONE>(a, s, used);
-}
-
-template <int RESET>
-static cudaError_t surr_lif_bwd(const LifBwdArgs &a, int kind, cudaStream_t s, bool *used)
-{
-    switch (kind) {
-    case EXB_SURR_GENERIC: return flags_lif_bwd<EXB_SURR_GENERIC, RESET>(a, s, used);
-    case EXB_SURR_SINGLE_EXPONENTIAL: return flags_lif_bwd<EXB_SURR_SINGLE_EXPONENTIAL, RESET>(a, s, used);
-    case EXB_SURR_HEAVISIDE: return flags_lif_bwd<EXB_SURR_HEAVISIDE, RESET>(a, s, used);
-    default: return flags_lif_bwd<EXB_SURR_PERIODIC_EXPONENTIAL, RESET>(a, s, used);
-    }
-}
-
-cudaError_t launch_lif_backward_tma(const LifBwdArgs &a, int reset_mode, int surr_kind, cudaStream_t s, bool *used)
-{
-    *used = false;
-    if (!eligible(a.B, a.T, a.M) || !aligned16(a.grad_input)) return cudaSuccess;
-    return reset_mode == EXB_RESET_SUBTRACT ? surr_lif_bwd<EXB_RESET_SUBTRACT>(a, surr_kind, s, used)
-                                            : surr_lif_bwd<EXB_RESET_TO_VALUE>(a, surr_kind, s, used);
+    if (!wide) return run_lif_fwd<EXB_RESET_TO_VALUE, NWARPS, 1, true>(a, s, used);
+    return uni ? run_lif_fwd<EXB_RESET_TO_VALUE, NWARPS, 4, true>(a, s, used)
+               : run_lif_fwd<EXB_RESET_TO_VALUE, NWARPS, 4, false>(a, s, used);
 }
 
 template <int NW, int V>
