@@ -166,7 +166,8 @@ class ClockSampler:
 # kernel event timing: wraps the C-ABI calls with CUDA events on the launch stream
 # --------------------------------------------------------------------------
 class KernelTimer:
-    NAMES = ("lif_forward", "lif_backward", "leaky_forward", "leaky_backward")
+    NAMES = ("lif_forward", "lif_backward", "leaky_forward", "leaky_backward", "leaky_forward_scan",
+             "leaky_backward_scan", "lif_syn_forward", "lif_syn_backward")
 
     def __init__(self):
         from sinabs_exodus_b200 import _lib
@@ -185,9 +186,10 @@ class KernelTimer:
                 return orig(*args, **kwargs)
             s = torch.cuda.Event(enable_timing=True); e = torch.cuda.Event(enable_timing=True)
             s.record()                       # torch's current stream == the stream the kernel is launched on
-            orig(*args, **kwargs)
+            res = orig(*args, **kwargs)
             e.record()
             self.events[name].append((s, e))
+            return res
         return call
 
     def launches(self):
@@ -448,6 +450,9 @@ def run_ours(args, wl):
         # dominant kernel = largest total time; bytes per launch = bytes/nts of that pass * nts per launch
         per_kernel_bytes = {
             "lif_forward": 12, "lif_backward": 12, "leaky_forward": 8, "leaky_backward": 8,
+            "leaky_forward_scan": 8, "leaky_backward_scan": 8,
+            # fused LIF + synapse: read in, write i_syn/spikes/v_mem; read grad, v_mem, i_syn, write grad_in
+            "lif_syn_forward": 16, "lif_syn_backward": 16,
         }
         if wl["kind"] == "expleak":              # trainable tau: the alpha gradient reads the forward output
             per_kernel_bytes["leaky_backward"] = 12

@@ -150,6 +150,45 @@ int exb_leaky_backward(float *grad_input, float *grad_alpha, float *grad_init, f
                        int64_t B, int64_t T, int64_t M, int layout,
                        int device, void *stream);
 
+/* LIF layer with synaptic stage in one kernel per direction (time-major layout only, M % 4 == 0,
+ * 16-byte aligned tensors; otherwise EXB_ERR_UNSUPPORTED and the caller chains exb_leaky_* and
+ * exb_lif_*).  The reference runs the two stages as separate kernels with PyTorch passes in between
+ * (layers/lif.py:185-198, 200-258: leakyForward, x*alpha, (1-alpha)*i, lifForward).
+ *   i_t = alpha_syn*i_{t-1} + scale_syn*in_t ;  membrane step of exb_lif_forward on scale_mem*i_t
+ * Forward writes i_syn, spikes, v_mem (+ optional v_post_last[N], i_last[N], spike_count).
+ * Backward takes gradients w.r.t. spikes and optionally v_mem, v_post_last, i_syn, i_last, and
+ * writes grad_input, optional grad_v_init / grad_i_init, and -- all four or none -- the
+ * per-instance gradients w.r.t. alpha_mem, scale_mem, alpha_syn, scale_syn (these need `i_syn`;
+ * scale_syn must be non-zero: its gradient is rebuilt from i_t - alpha_syn*i_{t-1}). */
+int exb_lif_syn_forward(float *spikes, float *v_mem, float *i_syn, const float *input,
+                        const float *v_init, const float *i_init,
+                        const float *alpha_syn, int alpha_syn_mode, const float *scale_syn, int scale_syn_mode,
+                        const float *scale_mem, int scale_mem_mode,
+                        const float *alpha_mem, int alpha_mem_mode,
+                        const float *subtract, int subtract_mode,
+                        const float *theta, int theta_mode,
+                        const float *theta_low, int theta_low_mode,
+                        uint32_t max_spikes, int reset_mode,
+                        float *v_post_last, float *i_last, unsigned long long *spike_count,
+                        int64_t B, int64_t T, int64_t M, int device, void *stream);
+
+int exb_lif_syn_backward(float *grad_input,
+                         float *grad_alpha_mem, float *grad_scale_mem, float *grad_alpha_syn, float *grad_scale_syn,
+                         float *grad_v_init, float *grad_i_init,
+                         const float *grad_spikes, const float *grad_v_mem, const float *grad_v_last,
+                         const float *grad_i_syn, const float *grad_i_last,
+                         const float *v_mem, const float *i_syn, const float *surr,
+                         const float *v_init, const float *i_init,
+                         const float *alpha_syn, int alpha_syn_mode, const float *scale_syn, int scale_syn_mode,
+                         const float *scale_mem, int scale_mem_mode,
+                         const float *alpha_mem, int alpha_mem_mode,
+                         const float *subtract, int subtract_mode,
+                         const float *theta, int theta_mode,
+                         const float *theta_low, int theta_low_mode,
+                         uint32_t max_spikes, int reset_mode,
+                         int surrogate_kind, float surr_p0, float surr_p1,
+                         int64_t B, int64_t T, int64_t M, int device, void *stream);
+
 /* Time-parallel variants of the leaky integrator for long sequences with few neurons
  * (time-major layout only).  The reference has one thread per neuron walking through all of
  * T (cuda/leaky_kernels.h:41-56, 96-108), which leaves the GPU empty when N is small; here

@@ -22,7 +22,7 @@ from . import leaky, spike  # noqa: E402
 from . import layers  # noqa: E402
 from . import conversion  # noqa: E402
 from .leaky import LeakyIntegrator, LeakyIntegratorTM  # noqa: E402
-from .spike import IntegrateAndFire, IntegrateAndFireTM  # noqa: E402
+from .spike import IntegrateAndFire, IntegrateAndFireTM, LIFSynapticTM  # noqa: E402
 
 
 def install_as_sinabs_exodus() -> None:

@@ -39,7 +39,7 @@ EXPORTS = (
     "exb_version", "exb_last_error", "exb_status_string", "exb_device_status",
     "exb_lif_forward", "exb_lif_backward", "exb_leaky_forward", "exb_leaky_backward",
     "exb_leaky_scan_workspace_bytes", "exb_leaky_forward_scan", "exb_leaky_backward_scan",
-    "exb_leaky_forward_scan_static",
+    "exb_leaky_forward_scan_static", "exb_lif_syn_forward", "exb_lif_syn_backward",
 )
 
 
@@ -85,6 +85,11 @@ def load() -> ctypes.CDLL:
     lib.exb_leaky_forward_scan.argtypes = [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp] + scan_tail
     lib.exb_leaky_backward_scan.restype = _i
     lib.exb_leaky_backward_scan.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i] + scan_tail
+    syn_params = [_vp, _i] * 7
+    lib.exb_lif_syn_forward.restype = _i
+    lib.exb_lif_syn_forward.argtypes = [_vp] * 6 + syn_params + [_u32, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i, _vp]
+    lib.exb_lif_syn_backward.restype = _i
+    lib.exb_lif_syn_backward.argtypes = ([_vp] * 17 + syn_params + [_u32, _i, _i, _f, _f, _i64, _i64, _i64, _i, _vp])
     lib.exb_leaky_forward_scan_static.restype = _i
     lib.exb_leaky_forward_scan_static.argtypes = [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _i, _vp]
     _lib = lib
@@ -237,3 +242,43 @@ def leaky_forward_scan_static(out, inp, v_init, alpha: Tuple, in_scale: Tuple, v
                                               ptr(in_scale[0]), in_scale[1], ptr(v_last),
                                               B, T, M, dev.index, _stream(dev))
     _check(st, "exb_leaky_forward_scan_static")
+
+
+def _pm(spec):
+    return ptr(spec[0]), spec[1]
+
+
+def lif_syn_forward(spikes, v_mem, i_syn, inp, v_init, i_init, alpha_syn: Tuple, scale_syn: Tuple, scale_mem: Tuple,
+                    alpha_mem: Tuple, subtract: Tuple, theta: Tuple, theta_low: Tuple, max_spikes: Optional[int],
+                    reset_mode: int, v_post_last, i_last, spike_count, B: int, T: int, M: int) -> bool:
+    """``exb_lif_syn_forward``.  Returns False when the shape is not eligible for the fused kernel."""
+    dev = _require_cuda(spikes, v_mem, i_syn, inp, v_init, i_init, alpha_syn[0], scale_syn[0], scale_mem[0],
+                        alpha_mem[0], subtract[0], theta[0], theta_low[0], v_post_last, i_last)
+    ms = MAX_SPIKES_UNLIMITED if max_spikes is None else int(max_spikes)
+    st = load().exb_lif_syn_forward(
+        ptr(spikes), ptr(v_mem), ptr(i_syn), ptr(inp), ptr(v_init), ptr(i_init),
+        *_pm(alpha_syn), *_pm(scale_syn), *_pm(scale_mem), *_pm(alpha_mem), *_pm(subtract), *_pm(theta), *_pm(theta_low),
+        ms, reset_mode, ptr(v_post_last), ptr(i_last), ptr(spike_count), B, T, M, dev.index, _stream(dev))
+    if st == 4:
+        return False
+    _check(st, "exb_lif_syn_forward")
+    return True
+
+
+def lif_syn_backward(grad_input, grad_alpha_mem, grad_scale_mem, grad_alpha_syn, grad_scale_syn, grad_v_init,
+                     grad_i_init, grad_spikes, grad_v_mem, grad_v_last, grad_i_syn, grad_i_last, v_mem, i_syn, surr,
+                     v_init, i_init, alpha_syn: Tuple, scale_syn: Tuple, scale_mem: Tuple, alpha_mem: Tuple,
+                     subtract: Tuple, theta: Tuple, theta_low: Tuple, max_spikes: Optional[int], reset_mode: int,
+                     surr_kind: int, p0: float, p1: float, B: int, T: int, M: int) -> None:
+    dev = _require_cuda(grad_input, grad_alpha_mem, grad_scale_mem, grad_alpha_syn, grad_scale_syn, grad_v_init,
+                        grad_i_init, grad_spikes, grad_v_mem, grad_v_last, grad_i_syn, grad_i_last, v_mem, i_syn, surr,
+                        v_init, i_init, alpha_syn[0], scale_syn[0], scale_mem[0], alpha_mem[0], subtract[0], theta[0],
+                        theta_low[0])
+    ms = MAX_SPIKES_UNLIMITED if max_spikes is None else int(max_spikes)
+    st = load().exb_lif_syn_backward(
+        ptr(grad_input), ptr(grad_alpha_mem), ptr(grad_scale_mem), ptr(grad_alpha_syn), ptr(grad_scale_syn),
+        ptr(grad_v_init), ptr(grad_i_init), ptr(grad_spikes), ptr(grad_v_mem), ptr(grad_v_last), ptr(grad_i_syn),
+        ptr(grad_i_last), ptr(v_mem), ptr(i_syn), ptr(surr), ptr(v_init), ptr(i_init),
+        *_pm(alpha_syn), *_pm(scale_syn), *_pm(scale_mem), *_pm(alpha_mem), *_pm(subtract), *_pm(theta), *_pm(theta_low),
+        ms, reset_mode, surr_kind, float(p0), float(p1), B, T, M, dev.index, _stream(dev))
+    _check(st, "exb_lif_syn_backward")

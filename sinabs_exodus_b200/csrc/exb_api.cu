@@ -84,9 +84,11 @@ int exb_device_status(int device, void *stream)
     if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_device_status: cannot select device %d", device);
     unsigned int code = 0, code2 = 0;
     cudaError_t e = exb::read_device_status((cudaStream_t)stream, &code);
+    unsigned int code3 = 0;
     if (e == cudaSuccess) e = exb::read_device_status_lif_bwd((cudaStream_t)stream, &code2);
+    if (e == cudaSuccess) e = exb::read_device_status_lif_syn((cudaStream_t)stream, &code3);
     if (e != cudaSuccess) return fail(EXB_ERR_LAUNCH, "exb_device_status: %s", cudaGetErrorString(e));
-    if (!code) code = code2;
+    if (!code) code = code2 ? code2 : code3;
     if (code) return fail(EXB_ERR_TIMEOUT, "a bounded device-side wait ran out (code %u); results of the affected call are incomplete", code);
     return EXB_OK;
 }
@@ -333,6 +335,115 @@ int exb_leaky_forward_scan_static(float *out, const float *input, const float *v
     cudaError_t e = exb::launch_leaky_forward_scan_static(a, current, (cudaStream_t)stream, &used);
     if (e != cudaSuccess) return launch_status(e, "exb_leaky_forward_scan_static");
     if (!used) return fail(EXB_ERR_UNSUPPORTED, "exb_leaky_forward_scan_static: shape or alignment not eligible");
+    return EXB_OK;
+}
+
+int exb_lif_syn_forward(float *spikes, float *v_mem, float *i_syn, const float *input,
+                        const float *v_init, const float *i_init,
+                        const float *alpha_syn, int alpha_syn_mode, const float *scale_syn, int scale_syn_mode,
+                        const float *scale_mem, int scale_mem_mode,
+                        const float *alpha_mem, int alpha_mem_mode,
+                        const float *subtract, int subtract_mode,
+                        const float *theta, int theta_mode,
+                        const float *theta_low, int theta_low_mode,
+                        uint32_t max_spikes, int reset_mode,
+                        float *v_post_last, float *i_last, unsigned long long *spike_count,
+                        int64_t B, int64_t T, int64_t M, int device, void *stream)
+{
+    if (int st = check_geometry(B, T, M, EXB_LAYOUT_BTM)) return st;
+    if (!spikes || !v_mem || !i_syn || !input || !alpha_syn || !alpha_mem || !theta)
+        return fail(EXB_ERR_ARG, "exb_lif_syn_forward: spikes, v_mem, i_syn, input, alpha_syn, alpha_mem and theta are required");
+    if (!mode_ok(alpha_syn_mode) || !mode_ok(alpha_mem_mode) || !mode_ok(theta_mode) ||
+        (scale_syn && !mode_ok(scale_syn_mode)) || (scale_mem && !mode_ok(scale_mem_mode)) ||
+        (subtract && !mode_ok(subtract_mode)) || (theta_low && !mode_ok(theta_low_mode)))
+        return fail(EXB_ERR_ARG, "exb_lif_syn_forward: bad parameter mode");
+    if (reset_mode != EXB_RESET_SUBTRACT && reset_mode != EXB_RESET_TO_VALUE)
+        return fail(EXB_ERR_ARG, "exb_lif_syn_forward: bad reset mode %d", reset_mode);
+    if (reset_mode == EXB_RESET_TO_VALUE && !subtract)
+        return fail(EXB_ERR_ARG, "exb_lif_syn_forward: reset-to-value needs the value in `subtract`");
+    if (B == 0 || M == 0 || T == 0) return EXB_OK;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_lif_syn_forward: cannot select device %d", device);
+    exb::LifSynFwdArgs a;
+    a.spikes = spikes; a.v_mem = v_mem; a.i_syn = i_syn; a.input = input; a.v_init = v_init; a.i_init = i_init;
+    a.np.alpha = exb::make_param(alpha_mem, alpha_mem_mode, M);
+    a.np.c = exb::make_param(subtract, subtract_mode, M);
+    a.np.th = exb::make_param(theta, theta_mode, M);
+    a.np.lo = exb::make_param(theta_low, theta_low_mode, M);
+    a.np.scale = exb::make_param(scale_mem, scale_mem_mode, M);
+    a.alpha_syn = exb::make_param(alpha_syn, alpha_syn_mode, M);
+    a.scale_syn = exb::make_param(scale_syn, scale_syn_mode, M);
+    a.maxs = max_spikes;
+    a.v_post_last = v_post_last; a.i_last = i_last; a.spike_count = spike_count;
+    a.B = B; a.T = T; a.M = M;
+    bool used = false;
+    cudaError_t e = exb::launch_lif_syn_forward(a, reset_mode, (cudaStream_t)stream, &used);
+    if (e != cudaSuccess) return launch_status(e, "exb_lif_syn_forward");
+    if (!used) return fail(EXB_ERR_UNSUPPORTED, "exb_lif_syn_forward: shape or alignment not eligible (needs M %% 4 == 0 and 16-byte aligned tensors)");
+    return EXB_OK;
+}
+
+int exb_lif_syn_backward(float *grad_input,
+                         float *grad_alpha_mem, float *grad_scale_mem, float *grad_alpha_syn, float *grad_scale_syn,
+                         float *grad_v_init, float *grad_i_init,
+                         const float *grad_spikes, const float *grad_v_mem, const float *grad_v_last,
+                         const float *grad_i_syn, const float *grad_i_last,
+                         const float *v_mem, const float *i_syn, const float *surr,
+                         const float *v_init, const float *i_init,
+                         const float *alpha_syn, int alpha_syn_mode, const float *scale_syn, int scale_syn_mode,
+                         const float *scale_mem, int scale_mem_mode,
+                         const float *alpha_mem, int alpha_mem_mode,
+                         const float *subtract, int subtract_mode,
+                         const float *theta, int theta_mode,
+                         const float *theta_low, int theta_low_mode,
+                         uint32_t max_spikes, int reset_mode,
+                         int surrogate_kind, float surr_p0, float surr_p1,
+                         int64_t B, int64_t T, int64_t M, int device, void *stream)
+{
+    if (int st = check_geometry(B, T, M, EXB_LAYOUT_BTM)) return st;
+    if (!grad_input || !grad_spikes || !v_mem || !alpha_syn || !alpha_mem || !theta)
+        return fail(EXB_ERR_ARG, "exb_lif_syn_backward: grad_input, grad_spikes, v_mem, alpha_syn, alpha_mem and theta are required");
+    if (!mode_ok(alpha_syn_mode) || !mode_ok(alpha_mem_mode) || !mode_ok(theta_mode) ||
+        (scale_syn && !mode_ok(scale_syn_mode)) || (scale_mem && !mode_ok(scale_mem_mode)) ||
+        (subtract && !mode_ok(subtract_mode)) || (theta_low && !mode_ok(theta_low_mode)))
+        return fail(EXB_ERR_ARG, "exb_lif_syn_backward: bad parameter mode");
+    if (reset_mode != EXB_RESET_SUBTRACT && reset_mode != EXB_RESET_TO_VALUE)
+        return fail(EXB_ERR_ARG, "exb_lif_syn_backward: bad reset mode %d", reset_mode);
+    if (reset_mode == EXB_RESET_TO_VALUE && !subtract)
+        return fail(EXB_ERR_ARG, "exb_lif_syn_backward: reset-to-value needs the value in `subtract`");
+    if (surrogate_kind < EXB_SURR_GENERIC || surrogate_kind > EXB_SURR_PERIODIC_EXPONENTIAL)
+        return fail(EXB_ERR_ARG, "exb_lif_syn_backward: unknown surrogate kind %d", surrogate_kind);
+    if (surrogate_kind == EXB_SURR_GENERIC && !surr)
+        return fail(EXB_ERR_ARG, "exb_lif_syn_backward: the generic surrogate needs the `surr` tensor");
+    const int ngrads = (grad_alpha_mem != nullptr) + (grad_scale_mem != nullptr) + (grad_alpha_syn != nullptr) +
+                       (grad_scale_syn != nullptr);
+    if (ngrads != 0 && ngrads != 4)
+        return fail(EXB_ERR_ARG, "exb_lif_syn_backward: pass all four parameter-gradient outputs or none");
+    if (ngrads == 4 && !i_syn) return fail(EXB_ERR_ARG, "exb_lif_syn_backward: parameter gradients need `i_syn`");
+    if (B == 0 || M == 0 || T == 0) return EXB_OK;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_lif_syn_backward: cannot select device %d", device);
+    exb::LifSynBwdArgs a;
+    a.grad_input = grad_input;
+    a.grad_alpha_mem = grad_alpha_mem; a.grad_scale_mem = grad_scale_mem;
+    a.grad_alpha_syn = grad_alpha_syn; a.grad_scale_syn = grad_scale_syn;
+    a.grad_v_init = grad_v_init; a.grad_i_init = grad_i_init;
+    a.go = grad_spikes; a.gv = grad_v_mem; a.g_vlast = grad_v_last; a.g_isyn = grad_i_syn; a.g_ilast = grad_i_last;
+    a.v_mem = v_mem; a.i_syn = i_syn; a.surr = (surrogate_kind == EXB_SURR_GENERIC) ? surr : nullptr;
+    a.v_init = v_init; a.i_init = i_init;
+    a.np.alpha = exb::make_param(alpha_mem, alpha_mem_mode, M);
+    a.np.c = exb::make_param(subtract, subtract_mode, M);
+    a.np.th = exb::make_param(theta, theta_mode, M);
+    a.np.lo = exb::make_param(theta_low, theta_low_mode, M);
+    a.np.scale = exb::make_param(scale_mem, scale_mem_mode, M);
+    a.alpha_syn = exb::make_param(alpha_syn, alpha_syn_mode, M);
+    a.scale_syn = exb::make_param(scale_syn, scale_syn_mode, M);
+    a.maxs = max_spikes; a.p0 = surr_p0; a.p1 = surr_p1;
+    a.B = B; a.T = T; a.M = M;
+    bool used = false;
+    cudaError_t e = exb::launch_lif_syn_backward(a, reset_mode, surrogate_kind, (cudaStream_t)stream, &used);
+    if (e != cudaSuccess) return launch_status(e, "exb_lif_syn_backward");
+    if (!used) return fail(EXB_ERR_UNSUPPORTED, "exb_lif_syn_backward: shape or alignment not eligible");
     return EXB_OK;
 }
 

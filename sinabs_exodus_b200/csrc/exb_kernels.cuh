@@ -40,6 +40,35 @@ struct LeakyBwdArgs {
     int64_t B, T, M;
 };
 
+// LIF with synaptic stage, both stages in one kernel (time-major layout only).
+struct LifSynFwdArgs {
+    float *spikes, *v_mem, *i_syn;
+    const float *input, *v_init, *i_init;
+    NeuronParams np;               // membrane stage; np.scale multiplies i_syn
+    Param alpha_syn, scale_syn;    // synaptic stage; scale_syn multiplies the input
+    unsigned maxs;
+    float *v_post_last, *i_last;
+    unsigned long long *spike_count;
+    int64_t B, T, M;
+};
+
+struct LifSynBwdArgs {
+    float *grad_input;
+    float *grad_alpha_mem, *grad_scale_mem, *grad_alpha_syn, *grad_scale_syn;   // all four or none
+    float *grad_v_init, *grad_i_init;
+    const float *go, *gv, *g_vlast, *g_isyn, *g_ilast;
+    const float *v_mem, *i_syn, *surr, *v_init, *i_init;
+    NeuronParams np;
+    Param alpha_syn, scale_syn;
+    unsigned maxs;
+    float p0, p1;
+    int64_t B, T, M;
+};
+
+cudaError_t launch_lif_syn_forward(const LifSynFwdArgs &a, int reset_mode, cudaStream_t s, bool *used);
+cudaError_t launch_lif_syn_backward(const LifSynBwdArgs &a, int reset_mode, int surr_kind, cudaStream_t s, bool *used);
+cudaError_t read_device_status_lif_syn(cudaStream_t s, unsigned int *out);
+
 // Each launcher returns a cudaError_t from the launch (cudaPeekAtLastError).
 cudaError_t launch_lif_forward(const LifFwdArgs &a, int layout, int reset_mode, cudaStream_t s);
 cudaError_t launch_lif_backward(const LifBwdArgs &a, int layout, int reset_mode, int surr_kind, cudaStream_t s);

@@ -179,7 +179,7 @@ leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A,
 
     if (warp == NW) {
         if (lane == 0) {
-            const CUtensorMap *mp[5] = {&maps.m[0], &maps.m[1], &maps.m[2], &maps.m[3], &maps.m[V]};
+            const CUtensorMap *mp[5] = {&maps.m[0], &maps.m[1], &maps.m[2], &maps.m[3], &maps.m[4]};
             produce<NW, V>(ring, stages, mp, nmaps, nchunks, m0, b, pc, true);
         }
     } else {

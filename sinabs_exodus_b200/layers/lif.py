@@ -27,7 +27,7 @@ from ..compat.activation import (
 from ..compat.layers import LIF as LIFBase
 from ..compat.layers import SqueezeMixin
 from ..leaky import LeakyIntegratorTM
-from ..spike import IntegrateAndFireTM
+from ..spike import IntegrateAndFireTM, LIFSynapticTM, fused_synaptic_eligible
 
 __all__ = ["LIF", "LIFSqueeze"]
 
@@ -212,6 +212,9 @@ class LIF(LIFBase):
         trailing = tuple(trailing_dim)
         self.recordings = dict()
 
+        if self.tau_syn_calculated is not None and self.spike_fn is not None and fused_synaptic_eligible(x):
+            return self._forward_fused_synaptic(x, original_shape)
+
         if self.tau_syn_calculated is None:
             i_syn = x
         else:
@@ -229,6 +232,43 @@ class LIF(LIFBase):
             self.firing_rate = count[0].to(torch.float32) / output_full.numel()
         else:
             self.firing_rate = output_full.detach().sum() / output_full.numel()
+        return output_full
+
+    def _forward_fused_synaptic(self, x: torch.Tensor, original_shape):
+        """Synaptic and membrane stage in one kernel (same results as the two-stage route)."""
+        batch_size, time_steps, *trailing_dim = original_shape
+        trailing = tuple(trailing_dim)
+        dev = x.device
+        alpha_syn = _flat_param(self.alpha_syn_calculated, trailing, batch_size, dev)
+        alpha_mem = _flat_param(self.alpha_mem_calculated, trailing, batch_size, dev)
+        scale_mem = (1.0 - alpha_mem) if self.norm_input else None
+        threshold = _flat_param(self.spike_threshold, trailing, batch_size, dev)
+        min_v_mem = _flat_param(self.min_v_mem, trailing, batch_size, dev)
+        if isinstance(self.reset_fn, MembraneReset):
+            reset_mode = _lib.RESET_TO_VALUE
+            subtract = _flat_param(self.reset_fn.reset_value, trailing, batch_size, dev)
+        else:
+            reset_mode = _lib.RESET_SUBTRACT
+            subtract = _flat_param(self.reset_fn.subtract_value, trailing, batch_size, dev)
+        self._validate_once(alpha_mem, dev)
+        count = torch.zeros(1, dtype=torch.int64, device=dev)
+        spikes, v_pre, v_post_last, i_syn, i_last = LIFSynapticTM.apply(
+            x, alpha_syn, alpha_syn if self.decay_early else None, self.i_syn.reshape(-1), alpha_mem, scale_mem,
+            self.v_mem.reshape(-1), threshold, subtract, min_v_mem, self.surrogate_grad_fn,
+            self.max_num_spikes_per_bin, reset_mode, count)
+        self.i_syn = i_last.reshape(batch_size, *trailing)
+        self.v_mem = v_post_last.reshape(batch_size, *trailing)
+        if self.record_states:
+            self.recordings["i_syn"] = i_syn.reshape(original_shape)
+            c = threshold if subtract is None else subtract
+            c = c if c.numel() == 1 else (c.view(1, 1, -1) if c.numel() == v_pre.shape[2] else c.view(batch_size, 1, -1))
+            if reset_mode == _lib.RESET_SUBTRACT:
+                v_rec = v_pre - c * spikes
+            else:
+                v_rec = torch.where(spikes > 0, c.expand_as(v_pre), v_pre)
+            self.recordings["v_mem"] = v_rec.reshape(original_shape)
+        output_full = spikes.reshape(original_shape)
+        self.firing_rate = count[0].to(torch.float32) / output_full.numel()
         return output_full
 
     def __repr__(self):

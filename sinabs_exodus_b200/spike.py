@@ -230,3 +230,116 @@ class IntegrateAndFireTM(torch.autograd.Function):
     def backward(ctx, grad_spikes, grad_v_mem, grad_v_last):
         grad_input, grad_alpha, grad_init, grad_scale = _LifCore.backward(ctx, grad_spikes, grad_v_mem, grad_v_last)
         return grad_input, grad_alpha, grad_init, None, None, None, grad_scale, None, None, None, None, None
+
+
+def fused_synaptic_eligible(inp: torch.Tensor) -> bool:
+    """Whether ``LIFSynapticTM`` can take this (B, T, M) tensor: the fused kernels stage through TMA,
+    which needs M % 4 == 0 and 16-byte aligned, contiguous float32 storage."""
+    return (inp.ndim == 3 and inp.is_cuda and inp.dtype == torch.float32 and inp.is_contiguous()
+            and inp.shape[2] % 4 == 0 and inp.data_ptr() % 16 == 0 and inp.numel() > 0)
+
+
+class LIFSynapticTM(torch.autograd.Function):
+    """Synaptic leaky integrator and spiking membrane of a LIF layer as one kernel per direction.
+
+    ``apply(inp, alpha_syn, scale_syn, i_init, alpha_mem, scale_mem, v_init, threshold,
+    membrane_subtract, min_v_mem, surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count)
+    -> (spikes, v_mem, v_post_last, i_syn, i_last)`` on a time-major ``(B, T, M)`` tensor:
+
+        i_t = alpha_syn * i_{t-1} + scale_syn * inp_t
+        v_t, spikes_t = membrane step on scale_mem * i_t      (as ``IntegrateAndFireTM``)
+
+    Replaces the chain ``LeakyIntegrator`` -> ``(1 - alpha) * i_syn`` -> ``IntegrateAndFire`` of the
+    reference layer (``layers/lif.py:185-258``) and saves re-reading ``i_syn`` and ``inp``.
+    Parameters hold 1, M or B*M values; ``scale_syn`` / ``scale_mem`` may be None (= 1).
+    """
+
+    @staticmethod
+    def forward(ctx, inp, alpha_syn, scale_syn, i_init, alpha_mem, scale_mem, v_init, threshold, membrane_subtract,
+                min_v_mem, surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count):
+        if not fused_synaptic_eligible(inp):
+            raise ValueError("'inp' must be a contiguous float32 CUDA tensor (batch, time, neurons) with neurons % 4 == 0")
+        B, T, M = inp.shape
+        N = B * M
+        f = {k: _flat32(t) for k, t in dict(a_syn=alpha_syn, s_syn=scale_syn, a_mem=alpha_mem, s_mem=scale_mem,
+                                            th=threshold, c=membrane_subtract, lo=min_v_mem).items()}
+        modes = {k: _mode_of(t, M, N, k) for k, t in f.items()}
+        vi_f, ii_f = _flat32(v_init), _flat32(i_init)
+        spikes = torch.empty_like(inp); v_mem = torch.empty_like(inp); i_syn = torch.empty_like(inp)
+        v_post_last = torch.empty(N, dtype=torch.float32, device=inp.device)
+        i_last = torch.empty(N, dtype=torch.float32, device=inp.device)
+        spec = lambda k: (f[k], modes[k])
+        done = _lib.lif_syn_forward(spikes, v_mem, i_syn, inp, vi_f, ii_f, spec("a_syn"), spec("s_syn"), spec("s_mem"),
+                                    spec("a_mem"), spec("c"), spec("th"), spec("lo"), max_num_spikes_per_bin, reset_mode,
+                                    v_post_last, i_last, spike_count, B, T, M)
+        if not done:
+            raise _lib.ExodusLibraryError("exb_lif_syn_forward refused a shape that passed the eligibility check")
+        ctx.set_materialize_grads(False)
+        ctx.geometry = (B, T, M)
+        ctx.modes = modes
+        ctx.keys = [k for k in f if f[k] is not None]
+        ctx.surrogate_fn = surrogate_grad_fn
+        ctx.max_spikes = max_num_spikes_per_bin
+        ctx.reset_mode = reset_mode
+        ctx.param_shapes = {k: (None if t is None else t.shape) for k, t in
+                            dict(a_syn=alpha_syn, s_syn=scale_syn, a_mem=alpha_mem, s_mem=scale_mem).items()}
+        ctx.param_needs = {k: (t is not None and t.requires_grad) for k, t in
+                           dict(a_syn=alpha_syn, s_syn=scale_syn, a_mem=alpha_mem, s_mem=scale_mem).items()}
+        ctx.want_params = any(ctx.param_needs.values())
+        ctx.init_shapes = (None if v_init is None else v_init.shape, None if i_init is None else i_init.shape)
+        saved = [v_mem] + [f[k] for k in ctx.keys] + [t for t in (vi_f, ii_f) if t is not None]
+        ctx.has_init = (vi_f is not None, ii_f is not None)
+        if ctx.want_params:
+            saved.append(i_syn)
+        ctx.save_for_backward(*saved)
+        return spikes, v_mem, v_post_last, i_syn, i_last
+
+    @staticmethod
+    def backward(ctx, g_spikes, g_vmem, g_vlast, g_isyn, g_ilast):
+        B, T, M = ctx.geometry
+        N = B * M
+        saved = list(ctx.saved_tensors)
+        v_mem = saved.pop(0)
+        f = {k: None for k in ("a_syn", "s_syn", "a_mem", "s_mem", "th", "c", "lo")}
+        for k in ctx.keys:
+            f[k] = saved.pop(0)
+        vi_f = saved.pop(0) if ctx.has_init[0] else None
+        ii_f = saved.pop(0) if ctx.has_init[1] else None
+        i_syn = saved.pop(0) if ctx.want_params else None
+        modes = ctx.modes
+        dev = v_mem.device
+        if g_spikes is None:
+            g_spikes = torch.zeros_like(v_mem)
+        g_spikes = g_spikes.contiguous()
+        g_vmem = None if g_vmem is None else g_vmem.contiguous()
+        g_isyn = None if g_isyn is None else g_isyn.contiguous()
+        g_vlast = None if g_vlast is None else g_vlast.to(torch.float32).reshape(-1).contiguous()
+        g_ilast = None if g_ilast is None else g_ilast.to(torch.float32).reshape(-1).contiguous()
+        kind, p0, p1 = classify(ctx.surrogate_fn)
+        surr = None
+        if kind == _lib.SURR_GENERIC:
+            th = f["th"]
+            th_b = th if th.numel() == 1 else (th.view(1, 1, M) if modes["th"] == _lib.PARAM_PER_M else th.view(B, 1, M))
+            surr = ctx.surrogate_fn(v_mem, th_b).to(torch.float32).contiguous()
+        new = lambda: torch.empty(N, dtype=torch.float32, device=dev)
+        grad_input = torch.empty_like(v_mem)
+        ga_mem, gs_mem, ga_syn, gs_syn = (new(), new(), new(), new()) if ctx.want_params else (None,) * 4
+        gv0 = new() if ctx.init_shapes[0] is not None else None
+        gi0 = new() if ctx.init_shapes[1] is not None else None
+        spec = lambda k: (f[k], modes[k])
+        _lib.lif_syn_backward(grad_input, ga_mem, gs_mem, ga_syn, gs_syn, gv0, gi0, g_spikes, g_vmem, g_vlast, g_isyn,
+                              g_ilast, v_mem, i_syn, surr, vi_f, ii_f, spec("a_syn"), spec("s_syn"), spec("s_mem"),
+                              spec("a_mem"), spec("c"), spec("th"), spec("lo"), ctx.max_spikes, ctx.reset_mode,
+                              kind, p0, p1, B, T, M)
+
+        def red(per_instance, key):
+            if not ctx.param_needs[key]:
+                return None
+            return _reduce_to_param(per_instance, ctx.param_shapes[key], modes[key], B, M)
+
+        if gv0 is not None:
+            gv0 = gv0.reshape(ctx.init_shapes[0])
+        if gi0 is not None:
+            gi0 = gi0.reshape(ctx.init_shapes[1])
+        return (grad_input, red(ga_syn, "a_syn"), red(gs_syn, "s_syn"), gi0, red(ga_mem, "a_mem"), red(gs_mem, "s_mem"),
+                gv0, None, None, None, None, None, None, None)

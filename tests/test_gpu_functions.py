@@ -309,3 +309,44 @@ def test_layer_rejects_cpu_and_bad_config():
     bad = LIF(tau_mem=10.0, min_v_mem=2.0).cuda()
     with pytest.raises(ValueError):
         bad(torch.zeros(1, 4, 3, device="cuda:0"))
+
+
+@pytest.mark.parametrize("B,T,M", [(4, 40, 12), (300, 12, 516)])
+@pytest.mark.parametrize("train_alphas", [False, True])
+def test_fused_synaptic_layer_equals_two_stage(B, T, M, train_alphas, monkeypatch):
+    """The one-kernel LIF+synapse route gives the two-stage route's bits in the forward pass and its
+    gradients to rounding (narrow and wide tiles; per-neuron time constants)."""
+    import sinabs_exodus_b200.layers.lif as lif_mod
+    from sinabs_exodus_b200.layers import LIF
+    from sinabs_exodus_b200.compat.activation import SingleExponential
+    rng = np.random.default_rng(5)
+    tau_mem = torch.tensor(rng.uniform(10, 40, M).astype(np.float32))
+    x_np = (0.3 + 0.8 * rng.standard_normal((2, B, T, M))).astype(np.float32)
+    w = torch.tensor(rng.standard_normal((B, T, M)).astype(np.float32), device="cuda:0")
+
+    def run(fused):
+        if not fused:
+            monkeypatch.setattr(lif_mod, "fused_synaptic_eligible", lambda t: False)
+        layer = LIF(tau_mem=tau_mem.clone(), tau_syn=8.0, min_v_mem=-1.0, train_alphas=train_alphas,
+                    surrogate_grad_fn=SingleExponential(), record_states=True).cuda()
+        xs = [torch.tensor(x_np[e], device="cuda:0", requires_grad=True) for e in range(2)]
+        outs, loss = [], 0
+        for e in range(2):                     # second call starts from the carried states
+            out = layer(xs[e])
+            outs.append(out)
+            loss = loss + (out * w).sum() + 0.1 * layer.recordings["i_syn"].sum()
+        loss.backward()
+        monkeypatch.undo()
+        params = [p.grad.clone() for _, p in sorted(layer.named_parameters())]
+        return outs, [x.grad for x in xs], params, layer
+
+    o_f, g_f, p_f, l_f = run(True)
+    o_t, g_t, p_t, l_t = run(False)
+    for a, b in zip(o_f, o_t):
+        assert torch.equal(a, b)
+    assert torch.equal(l_f.v_mem, l_t.v_mem) and torch.equal(l_f.i_syn, l_t.i_syn)
+    assert torch.equal(l_f.recordings["v_mem"], l_t.recordings["v_mem"])
+    for a, b in zip(g_f, g_t):
+        assert rel_err(a.cpu().numpy(), b.cpu().numpy()) < TOL
+    for a, b in zip(p_f, p_t):
+        assert rel_err(a.cpu().numpy(), b.cpu().numpy()) < 1e-4

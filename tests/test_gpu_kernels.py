@@ -171,6 +171,33 @@ def test_in_scale_and_state_gradient(layout):
         assert rel_err(gs2, (R64 * cs["inp"].astype(np.float64)).sum(1)) < TOL
 
 
+@pytest.mark.parametrize("B,T,M", [(3, 40, 20), (300, 9, 516)])
+def test_backward_all_five_streams(B, T, M):
+    """Time-major backward with every optional tensor streamed at once: grad_v_mem, a caller-computed
+    surrogate, and the forward input for the scale gradient (narrow and wide TMA tiles)."""
+    from tests import _gpu
+    from sinabs_exodus_b200 import _lib
+    N = B * M
+    cs = lif_case(55, N, T, clamp=True)
+    cs["alpha"] = np.minimum(cs["alpha"], np.float32(0.97))
+    scale = (1.0 - cs["alpha"]).astype(np.float32)
+    scaled = (scale[:, None] * cs["inp"]).astype(np.float32)
+    s, v = orc.lif_forward(scaled, cs["v_init"], cs["alpha"], cs["subtract"], cs["theta"], cs["theta_low"])
+    rng = np.random.default_rng(3)
+    go = rng.standard_normal((N, T)).astype(np.float32)
+    gv = (0.3 * rng.standard_normal((N, T))).astype(np.float32)
+    surr = orc.surrogate_single_exponential(v, cs["theta"][:, None], 0.7, 1.3)
+    nc = (v > cs["theta_low"][:, None]).astype(np.float32)
+    g = (surr * go).astype(np.float32) + gv
+    vpost = (v - cs["subtract"][:, None] * s).astype(np.float32)
+    R64, ag64 = orc.lif_backward_f64(g, surr, nc, cs["alpha"], cs["subtract"], vpost, cs["v_init"])
+    gi, ga, g0, gs = _gpu.lif_backward(cs, v, go, B, M, 1, gv=gv, surr=surr, kind=_lib.SURR_GENERIC,
+                                       in_scale=scale, want_scale=True, want_alpha=True)
+    assert rel_err(gi, scale[:, None].astype(np.float64) * R64) < TOL
+    assert rel_err(ga, ag64) < TOL
+    assert rel_err(gs, (R64 * cs["inp"].astype(np.float64)).sum(1)) < TOL
+
+
 @pytest.mark.parametrize("layout", [0, 1])
 def test_reset_to_value_vs_bptt(layout):
     """Reset-to-value has no reference kernel; the checker is back-propagation through the time-stepped loop."""
