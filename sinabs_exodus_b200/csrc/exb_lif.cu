@@ -183,6 +183,26 @@ __device__ __forceinline__ void tile_load(float *tile, const float *src, int64_t
     }
 }
 
+// Asynchronous variant of tile_load: 4-byte cp.async copies straight into the padded tile, so the
+// next time chunk streams in while the current one is being processed (no registers held).
+__device__ __forceinline__ void tile_prefetch(float *tile, const float *src, int64_t T, int rows, int tc, int lane)
+{
+    if (lane < tc) {
+        const unsigned dst = (unsigned)__cvta_generic_to_shared(tile + lane);
+#pragma unroll 8
+        for (int r = 0; r < rows; ++r)
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + r * TSTR * 4), "l"(src + r * T + lane)
+                         : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+template <int PENDING>
+__device__ __forceinline__ void prefetch_wait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory");
+}
+
 __device__ __forceinline__ void tile_store(float *dst, const float *tile, int64_t T, int rows, int tc, int lane)
 {
     if (lane < tc) {
@@ -199,8 +219,8 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_fwd_nt_kernel(const LifFwdA
     const int64_t N = A.B * A.M, T = A.T;
     const int64_t n0 = (blockIdx.x * (int64_t)NT_WARPS + warp) * TILE;
     if (n0 >= N) return;   // whole warp leaves together
-    float *tx = smem + warp * (2 * TILE_FLOATS);
-    float *ts = tx + TILE_FLOATS;
+    float *tbuf = smem + warp * (3 * TILE_FLOATS);     // two input tiles (double buffer) + one spike tile
+    float *ts = tbuf + 2 * TILE_FLOATS;
     const int rows = (int)min((int64_t)TILE, N - n0);
     const bool valid = lane < rows;
     const int64_t n = valid ? n0 + lane : n0;
@@ -212,9 +232,18 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_fwd_nt_kernel(const LifFwdA
     SpikeTotal cnt;
     cnt.c32 = 0u; cnt.c64 = 0ull;
 
-    for (int64_t t0 = 0; t0 < T; t0 += TILE) {
+    tile_prefetch(tbuf, A.input + n0 * T, T, rows, (int)min((int64_t)TILE, T), lane);
+    int cur = 0;
+    for (int64_t t0 = 0; t0 < T; t0 += TILE, cur ^= 1) {
         const int tc = (int)min((int64_t)TILE, T - t0);
-        tile_load(tx, A.input + n0 * T + t0, T, rows, tc, lane);
+        float *tx = tbuf + cur * TILE_FLOATS;
+        if (t0 + TILE < T) {
+            tile_prefetch(tbuf + (cur ^ 1) * TILE_FLOATS, A.input + n0 * T + t0 + TILE, T, rows,
+                          (int)min((int64_t)TILE, T - t0 - TILE), lane);
+            prefetch_wait<1>();
+        } else {
+            prefetch_wait<0>();
+        }
         __syncwarp();
         if (valid) {
             for (int t = 0; t < tc; ++t) {
@@ -243,13 +272,11 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_nt_kernel(const LifBwdA
     const int64_t N = A.B * A.M, T = A.T;
     const int64_t n0 = (blockIdx.x * (int64_t)NT_WARPS + warp) * TILE;
     if (n0 >= N) return;
-    float *tg = smem + warp * (ntiles * TILE_FLOATS);   // grad_spikes in, grad_input out
-    float *tv = tg + TILE_FLOATS;
-    float *nxt = tv + TILE_FLOATS;
-    float *tgv = nullptr, *tsl = nullptr, *txi = nullptr;
-    if (A.gv) { tgv = nxt; nxt += TILE_FLOATS; }
-    if (SURR == EXB_SURR_GENERIC) { tsl = nxt; nxt += TILE_FLOATS; }
-    if (WS == SCALE_GRAD_FROM_INPUT) { txi = nxt; nxt += TILE_FLOATS; }
+    // per warp: two sets (double buffer) of `ntiles` input tiles; grad_input overwrites grad_spikes in place
+    float *wbase = smem + warp * (2 * ntiles * TILE_FLOATS);
+    const int i_gv = A.gv ? 2 : -1;
+    const int i_sl = (SURR == EXB_SURR_GENERIC) ? (2 + (A.gv ? 1 : 0)) : -1;
+    const int i_xi = (WS == SCALE_GRAD_FROM_INPUT) ? (ntiles - 1) : -1;
 
     const int rows = (int)min((int64_t)TILE, N - n0);
     const bool valid = lane < rows;
@@ -265,14 +292,45 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_nt_kernel(const LifBwdA
     bool nc0 = true;
     const float glast = (A.g_last && valid) ? __ldg(A.g_last + n) : 0.0f;
 
-    for (int64_t t0 = ((T - 1) / TILE) * TILE; t0 >= 0; t0 -= TILE) {
+    auto prefetch_set = [&](float *set, int64_t t0) {
         const int tc = (int)min((int64_t)TILE, T - t0);
         const int64_t off = n0 * T + t0;
-        tile_load(tg, A.go + off, T, rows, tc, lane);
-        tile_load(tv, A.v_mem + off, T, rows, tc, lane);
-        if (tgv) tile_load(tgv, A.gv + off, T, rows, tc, lane);
-        if (SURR == EXB_SURR_GENERIC) tile_load(tsl, A.surr + off, T, rows, tc, lane);
-        if (WS == SCALE_GRAD_FROM_INPUT) tile_load(txi, A.input + off, T, rows, tc, lane);
+        // one commit group per set: tile_prefetch commits after each tensor, the waits below count sets
+        if (lane < tc) {
+            const float *srcs[5] = {A.go + off, A.v_mem + off, i_gv >= 0 ? A.gv + off : nullptr,
+                                    i_sl >= 0 ? A.surr + off : nullptr, i_xi >= 0 ? A.input + off : nullptr};
+            const int slots[5] = {0, 1, i_gv, i_sl, i_xi};
+#pragma unroll
+            for (int k = 0; k < 5; ++k) {
+                if (slots[k] < 0) continue;
+                const unsigned dst = (unsigned)__cvta_generic_to_shared(set + slots[k] * TILE_FLOATS + lane);
+                const float *src = srcs[k] + lane;
+#pragma unroll 8
+                for (int r = 0; r < rows; ++r)
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + r * TSTR * 4), "l"(src + r * T)
+                                 : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    const int64_t t_first = ((T - 1) / TILE) * TILE;
+    prefetch_set(wbase, t_first);
+    int cur = 0;
+    for (int64_t t0 = t_first; t0 >= 0; t0 -= TILE, cur ^= 1) {
+        const int tc = (int)min((int64_t)TILE, T - t0);
+        const int64_t off = n0 * T + t0;
+        float *set = wbase + cur * (ntiles * TILE_FLOATS);
+        float *tg = set, *tv = set + TILE_FLOATS;
+        const float *tgv = i_gv >= 0 ? set + i_gv * TILE_FLOATS : nullptr;
+        const float *tsl = i_sl >= 0 ? set + i_sl * TILE_FLOATS : nullptr;
+        const float *txi = i_xi >= 0 ? set + i_xi * TILE_FLOATS : nullptr;
+        if (t0 >= TILE) {
+            prefetch_set(wbase + (cur ^ 1) * (ntiles * TILE_FLOATS), t0 - TILE);
+            prefetch_wait<1>();
+        } else {
+            prefetch_wait<0>();
+        }
         __syncwarp();
         if (valid) {
             for (int t = tc - 1; t >= 0; --t) {
@@ -323,7 +381,11 @@ static cudaError_t launch_fwd_t(const LifFwdArgs &a, int layout, cudaStream_t s)
     } else {
         const int64_t N = a.B * a.M;
         const int64_t warps = (N + TILE - 1) / TILE;
-        const size_t sm = NT_WARPS * 2 * TILE_FLOATS * sizeof(float);
+        const size_t sm = NT_WARPS * 3 * TILE_FLOATS * sizeof(float);
+        if (sm > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(lif_fwd_nt_kernel<RESET>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+            if (e != cudaSuccess) return e;
+        }
         lif_fwd_nt_kernel<RESET><<<(unsigned)((warps + NT_WARPS - 1) / NT_WARPS), NT_WARPS * 32, sm, s>>>(a);
     }
     return cudaPeekAtLastError();
@@ -355,7 +417,7 @@ static cudaError_t launch_bwd_t(const LifBwdArgs &a, int layout, cudaStream_t s)
         const int64_t N = a.B * a.M;
         const int64_t warps = (N + TILE - 1) / TILE;
         const int ntiles = 2 + (a.gv ? 1 : 0) + (SURR == EXB_SURR_GENERIC ? 1 : 0) + (WS == SCALE_GRAD_FROM_INPUT ? 1 : 0);
-        const size_t sm = (size_t)NT_WARPS * ntiles * TILE_FLOATS * sizeof(float);
+        const size_t sm = (size_t)NT_WARPS * 2 * ntiles * TILE_FLOATS * sizeof(float);
         auto kern = lif_bwd_nt_kernel<SURR, RESET, WA, WS>;
         if (sm > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
