@@ -463,8 +463,14 @@ def run_ours(args, wl):
             dom = max(kernels, key=lambda k: kernels[k]["avg_ms"] * kernels[k]["launches"])
             bts = per_kernel_bytes[dom] * nts_step
             ach = bts / (kernels[dom]["avg_ms"] * 1e-3) / 1e9
+            traffic = None
+            try:      # DRAM bytes per neuron-step from the committed ncu capture, scaled to this launch
+                with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+                    traffic = float(json.load(f)[name][dom]) * nts_step
+            except Exception:
+                traffic = None
             roof = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                    "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": bts,
+                    "traffic": traffic, "peak_source": peak_src, "algorithmic_bytes_per_launch": bts,
                     "avg_launch_ms": kernels[dom]["avg_ms"],
                     "all_kernels": {k: dict(v, gbs=per_kernel_bytes[k] * nts_step / (v["avg_ms"] * 1e-3) / 1e9)
                                     for k, v in kernels.items()}}

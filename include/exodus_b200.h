@@ -5,7 +5,8 @@
  * reference (cuda/bindings.cu:362-373).  Every entry point takes raw device
  * pointers and sizes, launches on the stream it is given, allocates nothing
  * and returns an int status (0 = EXB_OK).  The only state kept between calls
- * is one device status word (see exb_device_status).  No
+ * is a device status word per kernel family (see exb_device_status) and the
+ * built-in scratch array of exb_leaky_forward_scan_static.  No
  * exception crosses this boundary; exb_last_error() gives the text of the
  * calling thread's most recent failure.
  *
