@@ -18,7 +18,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 BUILD_DIR = os.path.join(HERE, "_build")
 REF_DIR = os.path.join(HERE, "_ref")
-REFERENCE_ROOT = os.environ.get("EXODUS_REFERENCE_ROOT", "/root/reference")
+# checkout of the reference project (read-only); override with EXODUS_REFERENCE_ROOT
+REFERENCE_ROOT = os.environ.get("EXODUS_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
 
 
 def _newer(target: str, *sources: str) -> bool:
