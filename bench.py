@@ -344,6 +344,29 @@ def run_ours(args, wl):
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
+
+    run_step = step
+    graph = None
+    if args.cuda_graph:
+        # Whole step (state reset, forward, backward) captured once and replayed: removes the per-step
+        # host work, which dominates when the kernels take only tens of microseconds.
+        if world > 1 and tc_params:
+            raise SystemExit("--cuda-graph is for single-process runs (the allreduce is issued from the host)")
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        torch.cuda.synchronize()
+        run_step = graph.replay
+        for _ in range(3):
+            run_step()
+        torch.cuda.synchronize()
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
@@ -356,7 +379,7 @@ def run_ours(args, wl):
     ev0 = torch.cuda.Event(enable_timing=True); ev1 = torch.cuda.Event(enable_timing=True)
     ev0.record()
     for _ in range(args.steps):
-        step()
+        run_step()
     ev1.record()
     torch.cuda.synchronize()
     timer.enabled = False
@@ -485,7 +508,8 @@ def run_ours(args, wl):
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"{name}: {wl['desc']}", "per_gpu_shape": list(shape),
                        "l2": f"each tensor is {nts_step * 4 / 1e6:.0f} MB (L2 is 126 MB); no flush between steps",
-                       "parallelism": f"batch-sharded x{world}", "api": "sinabs_exodus_b200.layers"},
+                       "parallelism": f"batch-sharded x{world}", "api": "sinabs_exodus_b200.layers",
+                       "cuda_graph": bool(args.cuda_graph)},
             "step_fraction_of_hbm_roofline": (step_bytes / (ms_total / args.steps * 1e-3) / 1e9) / peak,
             "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         }
@@ -502,6 +526,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch size (profiling small cases)")
+    ap.add_argument("--cuda-graph", action="store_true", help="capture the step in a CUDA graph and time replays")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=5)
