@@ -150,6 +150,8 @@ class ParamSpec(tuple):
 def lif_forward(spikes, v_mem, inp, v_init, in_scale: Tuple, alpha: Tuple, subtract: Tuple, theta: Tuple,
                 theta_low: Tuple, max_spikes: Optional[int], reset_mode: int, v_post_last, spike_count,
                 B: int, T: int, M: int, layout: int) -> None:
+    if B * T * M == 0:      # empty problem: nothing to launch (empty tensors have no storage to point at)
+        return
     dev = _require_cuda(spikes, v_mem, inp, v_init, in_scale[0], alpha[0], subtract[0], theta[0], theta_low[0],
                         v_post_last)
     ms = MAX_SPIKES_UNLIMITED if max_spikes is None else int(max_spikes)
@@ -166,6 +168,8 @@ def lif_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, gra
                  v_mem, surr, v_init, inp, in_scale: Tuple, alpha: Tuple, subtract: Tuple, theta: Tuple,
                  theta_low: Tuple, max_spikes: Optional[int], reset_mode: int,
                  surr_kind: int, p0: float, p1: float, B: int, T: int, M: int, layout: int) -> None:
+    if B * T * M == 0:      # empty problem: nothing to launch (empty tensors have no storage to point at)
+        return
     dev = _require_cuda(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, grad_v_mem, grad_v_last,
                         v_mem, surr, v_init, inp, in_scale[0], alpha[0], subtract[0], theta[0], theta_low[0])
     ms = MAX_SPIKES_UNLIMITED if max_spikes is None else int(max_spikes)
@@ -182,6 +186,8 @@ def lif_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, gra
 
 def leaky_forward(out, inp, v_init, alpha: Tuple, in_scale: Tuple, v_last, B: int, T: int, M: int,
                   layout: int) -> None:
+    if B * T * M == 0:      # empty problem: nothing to launch (empty tensors have no storage to point at)
+        return
     dev = _require_cuda(out, inp, v_init, alpha[0], in_scale[0], v_last)
     st = load().exb_leaky_forward(ptr(out), ptr(inp), ptr(v_init), ptr(alpha[0]), alpha[1],
                                   ptr(in_scale[0]), in_scale[1], ptr(v_last),
@@ -191,6 +197,8 @@ def leaky_forward(out, inp, v_init, alpha: Tuple, in_scale: Tuple, v_last, B: in
 
 def leaky_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad_v_last, out, inp, v_init,
                    alpha: Tuple, in_scale: Tuple, B: int, T: int, M: int, layout: int) -> None:
+    if B * T * M == 0:      # empty problem: nothing to launch (empty tensors have no storage to point at)
+        return
     dev = _require_cuda(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad_v_last, out, inp, v_init,
                         alpha[0], in_scale[0])
     st = load().exb_leaky_backward(ptr(grad_input), ptr(grad_alpha), ptr(grad_init), ptr(grad_scale),

@@ -132,7 +132,10 @@ class LIF(LIFBase):
         x = input_data
         if x.dtype != torch.float32:
             x = x.float()
-        x = x.reshape(batch_size, time_steps, -1)
+        neurons = 1
+        for d in trailing_dim:
+            neurons *= d
+        x = x.reshape(batch_size, time_steps, neurons)
         if not x.is_contiguous():
             x = x.contiguous()
         return x, (batch_size, time_steps, *trailing_dim)

@@ -38,8 +38,11 @@ class _LeakyCore:
         a_f, sc_f, vi_f = _flat32(alpha), _flat32(in_scale), _flat32(v_init)
         modes = dict(alpha=_mode_of(a_f, M, N, "alpha"), scale=_mode_of(sc_f, M, N, "in_scale"))
         out = torch.empty_like(inp)
-        v_last = torch.empty(N, dtype=torch.float32, device=inp.device)
-        ws = _scan_workspace(B, T, M, layout, inp.device)
+        if T == 0:      # nothing to integrate: the state passes through unchanged
+            v_last = vi_f.clone() if vi_f is not None else torch.zeros(N, dtype=torch.float32, device=inp.device)
+        else:
+            v_last = torch.empty(N, dtype=torch.float32, device=inp.device)
+        ws = _scan_workspace(B, T, M, layout, inp.device) if T > 0 else None
         if ws is not None:
             _lib.leaky_forward_scan(out, inp, vi_f, (a_f, modes["alpha"]), (sc_f, modes["scale"]), v_last, ws, B, T, M)
         else:
@@ -78,11 +81,12 @@ class _LeakyCore:
         grad_out = grad_out.contiguous()
         if grad_v_last is not None:
             grad_v_last = grad_v_last.to(torch.float32).reshape(-1).contiguous()
+        new = torch.zeros if T == 0 else torch.empty      # an empty sweep launches nothing
         grad_input = torch.empty_like(grad_out)
-        grad_init = torch.empty(N, dtype=torch.float32, device=dev) if ctx.v_init_shape is not None else None
-        ga = torch.empty(N, dtype=torch.float32, device=dev) if ctx.want_alpha else None
-        gs = torch.empty(N, dtype=torch.float32, device=dev) if ctx.want_scale else None
-        ws = _scan_workspace(B, T, M, layout, dev)
+        grad_init = new(N, dtype=torch.float32, device=dev) if ctx.v_init_shape is not None else None
+        ga = new(N, dtype=torch.float32, device=dev) if ctx.want_alpha else None
+        gs = new(N, dtype=torch.float32, device=dev) if ctx.want_scale else None
+        ws = _scan_workspace(B, T, M, layout, dev) if T > 0 else None
         if ws is not None:
             _lib.leaky_backward_scan(grad_input, ga, grad_init, gs, grad_out, grad_v_last, out, inp, vi_f,
                                      (a_f, ctx.modes["alpha"]), (sc_f, ctx.modes["scale"]), ws, B, T, M)

@@ -66,7 +66,10 @@ class _LifCore:
         vi_f = _flat32(v_init)
         spikes = torch.empty_like(inp)
         v_mem = torch.empty_like(inp)
-        v_post_last = torch.empty(N, dtype=torch.float32, device=inp.device)
+        if T == 0:      # nothing to integrate: the state passes through unchanged
+            v_post_last = vi_f.clone() if vi_f is not None else torch.zeros(N, dtype=torch.float32, device=inp.device)
+        else:
+            v_post_last = torch.empty(N, dtype=torch.float32, device=inp.device)
         _lib.lif_forward(spikes, v_mem, inp, vi_f, (sc_f, modes["scale"]), (a_f, modes["alpha"]),
                          (c_f, modes["subtract"]), (th_f, modes["theta"]), (lo_f, modes["lo"]),
                          max_spikes, reset_mode, v_post_last, spike_count, B, T, M, layout)
@@ -126,10 +129,11 @@ class _LifCore:
                     th_f.view(1, 1, M) if modes["theta"] == _lib.PARAM_PER_M else th_f.view(B, 1, M))
             surr = ctx.surrogate_fn(v_mem, th_b).to(torch.float32).contiguous()
 
+        new = torch.zeros if T == 0 else torch.empty      # an empty sweep launches nothing
         grad_input = torch.empty_like(v_mem)
-        grad_init = torch.empty(N, dtype=torch.float32, device=dev) if ctx.v_init_shape is not None else None
-        ga = torch.empty(N, dtype=torch.float32, device=dev) if ctx.want_alpha else None
-        gs = torch.empty(N, dtype=torch.float32, device=dev) if ctx.want_scale else None
+        grad_init = new(N, dtype=torch.float32, device=dev) if ctx.v_init_shape is not None else None
+        ga = new(N, dtype=torch.float32, device=dev) if ctx.want_alpha else None
+        gs = new(N, dtype=torch.float32, device=dev) if ctx.want_scale else None
         _lib.lif_backward(grad_input, ga, grad_init, gs, grad_spikes, grad_v_mem, grad_v_last, v_mem, surr, vi_f,
                           inp, (sc_f, modes["scale"]), (a_f, modes["alpha"]), (c_f, modes["subtract"]),
                           (th_f, modes["theta"]), (lo_f, modes["lo"]), ctx.max_spikes, ctx.reset_mode,

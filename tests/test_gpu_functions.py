@@ -350,3 +350,23 @@ def test_fused_synaptic_layer_equals_two_stage(B, T, M, train_alphas, monkeypatc
         assert rel_err(a.cpu().numpy(), b.cpu().numpy()) < TOL
     for a, b in zip(p_f, p_t):
         assert rel_err(a.cpu().numpy(), b.cpu().numpy()) < 1e-4
+
+
+def test_empty_inputs():
+    """No rows or no time steps: nothing is launched, shapes and states pass through."""
+    from sinabs_exodus_b200 import IntegrateAndFire, LeakyIntegrator
+    from sinabs_exodus_b200.layers import IAF, ExpLeak
+    from sinabs_exodus_b200.compat.activation import Heaviside
+    dev = "cuda:0"
+    a = torch.full((3,), 0.9, device=dev); z = torch.tensor([0.1, -0.2, 0.3], device=dev); th = torch.ones(3, device=dev)
+    x0 = torch.zeros(3, 0, device=dev, requires_grad=True)
+    s, v = IntegrateAndFire.apply(x0, a, z, th, th, None, Heaviside())
+    assert s.shape == v.shape == (3, 0)
+    (s.sum() + v.sum()).backward()
+    out = LeakyIntegrator.apply(x0, a, z)
+    assert out.shape == (3, 0)
+    e = torch.zeros(0, device=dev)
+    s, v = IntegrateAndFire.apply(torch.zeros(0, 7, device=dev), e, e, e, e, None, Heaviside())
+    assert s.shape == (0, 7)
+    assert IAF().to(dev)(torch.zeros(2, 0, 5, device=dev)).shape == (2, 0, 5)
+    assert ExpLeak(tau_mem=5.0).to(dev)(torch.zeros(0, 4, 5, device=dev)).shape == (0, 4, 5)
