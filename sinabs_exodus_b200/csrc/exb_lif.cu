@@ -168,34 +168,46 @@ __global__ void __launch_bounds__(256) lif_bwd_btm_kernel(const LifBwdArgs A)
 }
 
 // ===========================================================================
-// [N,T] layout: warp-private 32x32 tiles, padded to 33 columns
+// [N,T] layout: warp-private tiles of 32 rows (neurons) x 32 time steps, padded to 33 columns
 // ===========================================================================
+// A row of this layout starts wherever n*T*4 bytes falls, in general not on a 128-byte line.
+// Chunks cut at fixed time steps would then straddle lines: every 128-byte piece of a row would
+// touch five 32-byte sectors instead of four and write two of them partially (measured on B200:
+// 2.2 TB/s for T = 300 against 4.8 TB/s for line-aligned pieces).  So every row gets its own
+// chunk boundaries, on the 128-byte lines of the output tensor: with `a` the position of the
+// row's first element inside its line (in floats), chunk k of that row covers the time steps
+// [32k - a, 32k - a + 32) that fall inside [0, T).  The lanes of a warp own one row each during
+// the recurrence, which is sequential per row anyway, so the rows need not be in step.
 constexpr int TILE = 32;
 constexpr int TSTR = 33;
 constexpr int TILE_FLOATS = TILE * TSTR;
 constexpr int NT_WARPS = 4;
 
-__device__ __forceinline__ void tile_load(float *tile, const float *src, int64_t T, int rows, int tc, int lane)
+// Position (in floats) of element (n, 0) of an [N,T] tensor inside its 128-byte line.
+__device__ __forceinline__ int line_pos(const void *base, int64_t n, int64_t T)
 {
-    if (lane < tc) {
+    return (int)(((reinterpret_cast<uintptr_t>(base) >> 2) + (uint64_t)(n * T)) & (TILE - 1));
+}
+
+__device__ __forceinline__ int nt_chunks(int64_t T) { return (int)((T + 2 * TILE - 2) / TILE); }
+
+// Chunk k of the 32 rows from row n0 on: lane j moves element j of every row's chunk.  `a0` is
+// line_pos of row n0; `src` points at element (n0, 0).
+__device__ __forceinline__ void tile_prefetch(float *tile, const float *src, int64_t T, int rows, int k, int a0, int lane)
+{
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(tile + lane);
+    const int step = (int)(T & (TILE - 1));
+    int a = a0;
 #pragma unroll 8
-        for (int r = 0; r < rows; ++r) tile[r * TSTR + lane] = __ldcs(src + r * T + lane);
+    for (int r = 0; r < rows; ++r) {
+        const int64_t t = (int64_t)k * TILE - a + lane;
+        if (t >= 0 && t < T)
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + r * TSTR * 4), "l"(src + r * T + t) : "memory");
+        a = (a + step) & (TILE - 1);
     }
 }
 
-// Asynchronous variant of tile_load: 4-byte cp.async copies straight into the padded tile, so the
-// next time chunk streams in while the current one is being processed (no registers held).
-__device__ __forceinline__ void tile_prefetch(float *tile, const float *src, int64_t T, int rows, int tc, int lane)
-{
-    if (lane < tc) {
-        const unsigned dst = (unsigned)__cvta_generic_to_shared(tile + lane);
-#pragma unroll 8
-        for (int r = 0; r < rows; ++r)
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + r * TSTR * 4), "l"(src + r * T + lane)
-                         : "memory");
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-}
+__device__ __forceinline__ void prefetch_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 
 template <int PENDING>
 __device__ __forceinline__ void prefetch_wait()
@@ -203,11 +215,15 @@ __device__ __forceinline__ void prefetch_wait()
     asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory");
 }
 
-__device__ __forceinline__ void tile_store(float *dst, const float *tile, int64_t T, int rows, int tc, int lane)
+__device__ __forceinline__ void tile_store(float *dst, const float *tile, int64_t T, int rows, int k, int a0, int lane)
 {
-    if (lane < tc) {
+    const int step = (int)(T & (TILE - 1));
+    int a = a0;
 #pragma unroll 8
-        for (int r = 0; r < rows; ++r) __stcs(dst + r * T + lane, tile[r * TSTR + lane]);
+    for (int r = 0; r < rows; ++r) {
+        const int64_t t = (int64_t)k * TILE - a + lane;
+        if (t >= 0 && t < T) __stcs(dst + r * T + t, tile[r * TSTR + lane]);
+        a = (a + step) & (TILE - 1);
     }
 }
 
@@ -232,29 +248,36 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_fwd_nt_kernel(const LifFwdA
     SpikeTotal cnt;
     cnt.c32 = 0u; cnt.c64 = 0ull;
 
-    tile_prefetch(tbuf, A.input + n0 * T, T, rows, (int)min((int64_t)TILE, T), lane);
+    const int a0 = line_pos(A.spikes, n0, T);          // chunk boundaries follow the outputs' lines
+    const int a = line_pos(A.spikes, n, T);            // this lane's own row
+    const int nchunks = nt_chunks(T);
+    const float *src = A.input + n0 * T;
+    tile_prefetch(tbuf, src, T, rows, 0, a0, lane);
+    prefetch_commit();
     int cur = 0;
-    for (int64_t t0 = 0; t0 < T; t0 += TILE, cur ^= 1) {
-        const int tc = (int)min((int64_t)TILE, T - t0);
+    for (int k = 0; k < nchunks; ++k, cur ^= 1) {
         float *tx = tbuf + cur * TILE_FLOATS;
-        if (t0 + TILE < T) {
-            tile_prefetch(tbuf + (cur ^ 1) * TILE_FLOATS, A.input + n0 * T + t0 + TILE, T, rows,
-                          (int)min((int64_t)TILE, T - t0 - TILE), lane);
+        if (k + 1 < nchunks) {
+            tile_prefetch(tbuf + (cur ^ 1) * TILE_FLOATS, src, T, rows, k + 1, a0, lane);
+            prefetch_commit();
             prefetch_wait<1>();
         } else {
             prefetch_wait<0>();
         }
         __syncwarp();
         if (valid) {
-            for (int t = 0; t < tc; ++t) {
-                lif_step<RESET>(v, af, tx[lane * TSTR + t], q, cfg, cnt);
-                ts[lane * TSTR + t] = af;
-                tx[lane * TSTR + t] = v;
+            const int64_t tb = (int64_t)k * TILE - a;   // time step of column 0
+            const int j_lo = tb < 0 ? (int)-tb : 0;
+            const int j_hi = (int)min((int64_t)TILE, T - tb);
+            for (int j = j_lo; j < j_hi; ++j) {
+                lif_step<RESET>(v, af, tx[lane * TSTR + j], q, cfg, cnt);
+                ts[lane * TSTR + j] = af;
+                tx[lane * TSTR + j] = v;
             }
         }
         __syncwarp();
-        tile_store(A.spikes + n0 * T + t0, ts, T, rows, tc, lane);
-        tile_store(A.v_mem + n0 * T + t0, tx, T, rows, tc, lane);
+        tile_store(A.spikes + n0 * T, ts, T, rows, k, a0, lane);
+        tile_store(A.v_mem + n0 * T, tx, T, rows, k, a0, lane);
         __syncwarp();
     }
     if (A.v_post_last && valid) A.v_post_last[n] = post_reset<RESET>(v, af, q);
@@ -292,52 +315,48 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_nt_kernel(const LifBwdA
     bool nc0 = true;
     const float glast = (A.g_last && valid) ? __ldg(A.g_last + n) : 0.0f;
 
-    auto prefetch_set = [&](float *set, int64_t t0) {
-        const int tc = (int)min((int64_t)TILE, T - t0);
-        const int64_t off = n0 * T + t0;
-        // one commit group per set: tile_prefetch commits after each tensor, the waits below count sets
-        if (lane < tc) {
-            const float *srcs[5] = {A.go + off, A.v_mem + off, i_gv >= 0 ? A.gv + off : nullptr,
-                                    i_sl >= 0 ? A.surr + off : nullptr, i_xi >= 0 ? A.input + off : nullptr};
-            const int slots[5] = {0, 1, i_gv, i_sl, i_xi};
+    const int a0 = line_pos(A.grad_input, n0, T);      // chunk boundaries follow the output's lines
+    const int a = line_pos(A.grad_input, n, T);        // this lane's own row
+    const int nchunks = nt_chunks(T);
+    const int64_t off = n0 * T;
+
+    // one commit group per set of tiles: the waits below count sets
+    auto prefetch_set = [&](float *set, int k) {
+        const float *srcs[5] = {A.go + off, A.v_mem + off, i_gv >= 0 ? A.gv + off : nullptr,
+                                i_sl >= 0 ? A.surr + off : nullptr, i_xi >= 0 ? A.input + off : nullptr};
+        const int slots[5] = {0, 1, i_gv, i_sl, i_xi};
 #pragma unroll
-            for (int k = 0; k < 5; ++k) {
-                if (slots[k] < 0) continue;
-                const unsigned dst = (unsigned)__cvta_generic_to_shared(set + slots[k] * TILE_FLOATS + lane);
-                const float *src = srcs[k] + lane;
-#pragma unroll 8
-                for (int r = 0; r < rows; ++r)
-                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + r * TSTR * 4), "l"(src + r * T)
-                                 : "memory");
-            }
+        for (int i = 0; i < 5; ++i) {
+            if (slots[i] < 0) continue;
+            tile_prefetch(set + slots[i] * TILE_FLOATS, srcs[i], T, rows, k, a0, lane);
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
+        prefetch_commit();
     };
 
-    const int64_t t_first = ((T - 1) / TILE) * TILE;
-    prefetch_set(wbase, t_first);
+    prefetch_set(wbase, nchunks - 1);
     int cur = 0;
-    for (int64_t t0 = t_first; t0 >= 0; t0 -= TILE, cur ^= 1) {
-        const int tc = (int)min((int64_t)TILE, T - t0);
-        const int64_t off = n0 * T + t0;
+    for (int k = nchunks - 1; k >= 0; --k, cur ^= 1) {
         float *set = wbase + cur * (ntiles * TILE_FLOATS);
         float *tg = set, *tv = set + TILE_FLOATS;
         const float *tgv = i_gv >= 0 ? set + i_gv * TILE_FLOATS : nullptr;
         const float *tsl = i_sl >= 0 ? set + i_sl * TILE_FLOATS : nullptr;
         const float *txi = i_xi >= 0 ? set + i_xi * TILE_FLOATS : nullptr;
-        if (t0 >= TILE) {
-            prefetch_set(wbase + (cur ^ 1) * (ntiles * TILE_FLOATS), t0 - TILE);
+        if (k > 0) {
+            prefetch_set(wbase + (cur ^ 1) * (ntiles * TILE_FLOATS), k - 1);
             prefetch_wait<1>();
         } else {
             prefetch_wait<0>();
         }
         __syncwarp();
         if (valid) {
-            for (int t = tc - 1; t >= 0; --t) {
-                const int i = lane * TSTR + t;
+            const int64_t tb = (int64_t)k * TILE - a;   // time step of column 0
+            const int j_lo = tb < 0 ? (int)-tb : 0;
+            const int j_hi = (int)min((int64_t)TILE, T - tb);
+            for (int j = j_hi - 1; j >= j_lo; --j) {
+                const int i = lane * TSTR + j;
                 float go = tg[i], gv = tgv ? tgv[i] : 0.0f;
                 const float v = tv[i];
-                if (A.g_last && t0 + t == T - 1) fold_last_state_grad<RESET>(go, gv, glast, v, q, cfg);
+                if (A.g_last && tb + j == T - 1) fold_last_state_grad<RESET>(go, gv, glast, v, q, cfg);
                 Rprev = st.R;
                 const float Rt = lif_bwd_step<SURR, RESET, WA, WS>(st, v, go, gv, (SURR == EXB_SURR_GENERIC) ? tsl[i] : 0.0f,
                                                                   (WS == SCALE_GRAD_FROM_INPUT) ? txi[i] : 0.0f, q, sc, cp, cfg, f0, nc0);
@@ -345,7 +364,7 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_nt_kernel(const LifBwdA
             }
         }
         __syncwarp();
-        tile_store(A.grad_input + off, tg, T, rows, tc, lane);
+        tile_store(A.grad_input + off, tg, T, rows, k, a0, lane);
         __syncwarp();
     }
     if (valid) {
@@ -355,6 +374,10 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_nt_kernel(const LifBwdA
         if (WS) A.grad_scale[n] = scale_grad_finish<WS>(st, vi, q);
     }
 }
+
+}  // namespace exb
+#include "exb_lif_nt.cuh"
+namespace exb {
 
 // ===========================================================================
 // launchers
@@ -381,12 +404,15 @@ static cudaError_t launch_fwd_t(const LifFwdArgs &a, int layout, cudaStream_t s)
     } else {
         const int64_t N = a.B * a.M;
         const int64_t warps = (N + TILE - 1) / TILE;
-        const size_t sm = NT_WARPS * 3 * TILE_FLOATS * sizeof(float);
+        const unsigned grid = (unsigned)((warps + NT_WARPS - 1) / NT_WARPS);
+        const bool vec = ntv_eligible(a.T, a.spikes, {a.v_mem, a.input});
+        const size_t sm = (size_t)NT_WARPS * 3 * (vec ? NTV_TILE_FLOATS : TILE_FLOATS) * sizeof(float);
+        auto kern = vec ? lif_fwd_ntv_kernel<RESET> : lif_fwd_nt_kernel<RESET>;
         if (sm > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(lif_fwd_nt_kernel<RESET>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
             if (e != cudaSuccess) return e;
         }
-        lif_fwd_nt_kernel<RESET><<<(unsigned)((warps + NT_WARPS - 1) / NT_WARPS), NT_WARPS * 32, sm, s>>>(a);
+        kern<<<grid, NT_WARPS * 32, sm, s>>>(a);
     }
     return cudaPeekAtLastError();
 }
@@ -417,8 +443,9 @@ static cudaError_t launch_bwd_t(const LifBwdArgs &a, int layout, cudaStream_t s)
         const int64_t N = a.B * a.M;
         const int64_t warps = (N + TILE - 1) / TILE;
         const int ntiles = 2 + (a.gv ? 1 : 0) + (SURR == EXB_SURR_GENERIC ? 1 : 0) + (WS == SCALE_GRAD_FROM_INPUT ? 1 : 0);
-        const size_t sm = (size_t)NT_WARPS * 2 * ntiles * TILE_FLOATS * sizeof(float);
-        auto kern = lif_bwd_nt_kernel<SURR, RESET, WA, WS>;
+        const bool vec = ntv_eligible(a.T, a.grad_input, {a.go, a.v_mem, a.gv, a.surr, a.input});
+        const size_t sm = (size_t)NT_WARPS * 2 * ntiles * (vec ? NTV_TILE_FLOATS : TILE_FLOATS) * sizeof(float);
+        auto kern = vec ? lif_bwd_ntv_kernel<SURR, RESET, WA, WS> : lif_bwd_nt_kernel<SURR, RESET, WA, WS>;
         if (sm > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
             if (e != cudaSuccess) return e;

@@ -1,0 +1,288 @@
+// [N,T] layout, fast variant: 16-byte pieces between global and shared memory.
+//
+// A warp owns 32 rows (neurons) and walks time in chunks of 32 steps.  The chunk boundaries of
+// every row lie on the 128-byte lines of the output tensor (see line_pos in exb_lif.cu), so a
+// row's chunk is exactly one aligned line: eight 16-byte granules.  One warp instruction moves
+// four such lines (lane -> row it*4 + lane/8, granule lane%8), a quarter of the instructions
+// of the 4-byte variant, which was bound by instruction issue.
+//
+// Shared-memory tile: 32 rows x 32 floats, unpadded; granule g of row r is stored at granule
+// position g ^ (r & 7).  Both access patterns are then free of bank conflicts with 16-byte
+// accesses: the copy phases touch the eight granules of one row per quarter-warp, the
+// recurrence touches the same granule of eight consecutive rows per quarter-warp.
+//
+// Row heads and tails (time steps outside [0,T) inside a line belong to the neighbouring rows)
+// are moved element by element.  Needs every tensor's base address congruent to the output's
+// modulo 16 bytes and T < 2^31 - 64; the launcher falls back to the 4-byte variant otherwise.
+#pragma once
+
+namespace exb {
+
+constexpr int NTV_TILE_FLOATS = TILE * TILE;   // unpadded
+
+__device__ __forceinline__ int ntv_off(int r, int g) { return r * TILE + ((g ^ (r & 7)) << 2); }
+
+// Granule (row r, granule g) of chunk k: first time step and whether all four steps exist.
+struct NtvPiece {
+    int r, g, t0;
+    bool in_rows, whole;
+};
+
+__device__ __forceinline__ NtvPiece ntv_piece(int it, int lane, int k, int a0, int step, int rows, int T)
+{
+    NtvPiece p;
+    p.r = it * 4 + (lane >> 3);
+    p.g = lane & 7;
+    const int ar = (a0 + p.r * step) & (TILE - 1);
+    p.t0 = k * TILE - ar + 4 * p.g;
+    p.in_rows = p.r < rows;
+    p.whole = p.t0 >= 0 && p.t0 + 3 < T;
+    return p;
+}
+
+__device__ __forceinline__ void ntv_prefetch(float *tile, const float *src, int T, int rows, int k, int a0, int lane)
+{
+    const int step = T & (TILE - 1);
+    const unsigned base = (unsigned)__cvta_generic_to_shared(tile);
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const NtvPiece p = ntv_piece(it, lane, k, a0, step, rows, T);
+        if (!p.in_rows) continue;
+        const float *gp = src + (int64_t)p.r * T + p.t0;
+        const unsigned dst = base + 4u * (unsigned)ntv_off(p.r, p.g);
+        if (p.whole) {
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gp) : "memory");
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if ((unsigned)(p.t0 + e) < (unsigned)T)
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * e), "l"(gp + e) : "memory");
+        }
+    }
+}
+
+__device__ __forceinline__ void ntv_store(float *dst, const float *tile, int T, int rows, int k, int a0, int lane)
+{
+    const int step = T & (TILE - 1);
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const NtvPiece p = ntv_piece(it, lane, k, a0, step, rows, T);
+        if (!p.in_rows) continue;
+        float *gp = dst + (int64_t)p.r * T + p.t0;
+        const float4 val = *reinterpret_cast<const float4 *>(tile + ntv_off(p.r, p.g));
+        if (p.whole) {
+            __stcs(reinterpret_cast<float4 *>(gp), val);
+        } else {
+            const float e4[4] = {val.x, val.y, val.z, val.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if ((unsigned)(p.t0 + e) < (unsigned)T) __stcs(gp + e, e4[e]);
+        }
+    }
+}
+
+// Forward recurrence of one lane's row over one chunk.  GUARD: the chunk holds time steps
+// outside [0,T) for this row (first and last chunk only).
+template <int RESET, bool GUARD>
+__device__ __forceinline__ void ntv_fwd_chunk(float *tx, float *ts, int lane, int tb, int T, float &v, float &af,
+                                              const Neuron &q, const SpikeCfg &cfg, SpikeTotal &cnt)
+{
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const int o = ntv_off(lane, g);
+        const float4 x4 = *reinterpret_cast<const float4 *>(tx + o);
+        float x[4] = {x4.x, x4.y, x4.z, x4.w};
+        float s[4], u[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (!GUARD || (unsigned)(tb + 4 * g + e) < (unsigned)T) lif_step<RESET>(v, af, x[e], q, cfg, cnt);
+            s[e] = af;
+            u[e] = v;
+        }
+        *reinterpret_cast<float4 *>(ts + o) = make_float4(s[0], s[1], s[2], s[3]);
+        *reinterpret_cast<float4 *>(tx + o) = make_float4(u[0], u[1], u[2], u[3]);
+    }
+}
+
+template <int RESET>
+__global__ void __launch_bounds__(NT_WARPS * 32) lif_fwd_ntv_kernel(const LifFwdArgs A)
+{
+    extern __shared__ __align__(16) float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t N = A.B * A.M;
+    const int T = (int)A.T;
+    const int64_t n0 = (blockIdx.x * (int64_t)NT_WARPS + warp) * TILE;
+    if (n0 >= N) return;   // whole warp leaves together
+    float *tbuf = smem + warp * (3 * NTV_TILE_FLOATS);   // two input tiles (double buffer) + one spike tile
+    float *ts = tbuf + 2 * NTV_TILE_FLOATS;
+    const int rows = (int)min((int64_t)TILE, N - n0);
+    const bool valid = lane < rows;
+    const int64_t n = valid ? n0 + lane : n0;
+    const int64_t b = n / A.M, m = n - b * A.M;
+    const SpikeCfg cfg = make_spike_cfg(A.maxs);
+    const Neuron q = A.np.load(b, m, cfg);
+    float v = A.v_init ? __ldg(A.v_init + n) : 0.0f;
+    float af = 0.0f;
+    SpikeTotal cnt;
+    cnt.c32 = 0u; cnt.c64 = 0ull;
+
+    const int a0 = line_pos(A.spikes, n0, A.T);
+    const int a = line_pos(A.spikes, n, A.T);
+    const int nchunks = nt_chunks(A.T);
+    const float *src = A.input + n0 * A.T;
+    ntv_prefetch(tbuf, src, T, rows, 0, a0, lane);
+    prefetch_commit();
+    int cur = 0;
+    for (int k = 0; k < nchunks; ++k, cur ^= 1) {
+        float *tx = tbuf + cur * NTV_TILE_FLOATS;
+        if (k + 1 < nchunks) {
+            ntv_prefetch(tbuf + (cur ^ 1) * NTV_TILE_FLOATS, src, T, rows, k + 1, a0, lane);
+            prefetch_commit();
+            prefetch_wait<1>();
+        } else {
+            prefetch_wait<0>();
+        }
+        __syncwarp();
+        if (valid) {
+            const int tb = k * TILE - a;   // time step of column 0
+            if (tb >= 0 && tb + TILE <= T) ntv_fwd_chunk<RESET, false>(tx, ts, lane, tb, T, v, af, q, cfg, cnt);
+            else ntv_fwd_chunk<RESET, true>(tx, ts, lane, tb, T, v, af, q, cfg, cnt);
+        }
+        __syncwarp();
+        ntv_store(A.spikes + n0 * A.T, ts, T, rows, k, a0, lane);
+        ntv_store(A.v_mem + n0 * A.T, tx, T, rows, k, a0, lane);
+        __syncwarp();
+    }
+    if (A.v_post_last && valid) A.v_post_last[n] = post_reset<RESET>(v, af, q);
+    if (A.spike_count) {
+        const unsigned long long tot = warp_sum_u64(valid ? cnt.total(cfg) : 0ull);
+        if (lane == 0 && tot) atomicAdd(A.spike_count, tot);
+    }
+}
+
+// Reverse recurrence of one lane's row over one chunk; grad_input overwrites grad_spikes in place.
+template <int SURR, int RESET, bool WA, int WS, bool GUARD>
+__device__ __forceinline__ void ntv_bwd_chunk(float *tg, const float *tv, const float *tgv, const float *tsl,
+                                              const float *txi, int lane, int tb, int T, bool fold_last, float glast,
+                                              BwdState &st, float &Rprev, float &f0, bool &nc0, const Neuron &q,
+                                              const SurrConst &sc, float cp, const SpikeCfg &cfg)
+{
+#pragma unroll
+    for (int g = 7; g >= 0; --g) {
+        const int o = ntv_off(lane, g);
+        const float4 go4 = *reinterpret_cast<const float4 *>(tg + o);
+        const float4 v4 = *reinterpret_cast<const float4 *>(tv + o);
+        float4 gv4 = make_float4(0.f, 0.f, 0.f, 0.f), sl4 = gv4, xi4 = gv4;
+        if (tgv) gv4 = *reinterpret_cast<const float4 *>(tgv + o);
+        if (SURR == EXB_SURR_GENERIC) sl4 = *reinterpret_cast<const float4 *>(tsl + o);
+        if (WS == SCALE_GRAD_FROM_INPUT) xi4 = *reinterpret_cast<const float4 *>(txi + o);
+        float go[4] = {go4.x, go4.y, go4.z, go4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+        float gv[4] = {gv4.x, gv4.y, gv4.z, gv4.w}, sl[4] = {sl4.x, sl4.y, sl4.z, sl4.w};
+        float xi[4] = {xi4.x, xi4.y, xi4.z, xi4.w};
+        float r[4];
+#pragma unroll
+        for (int e = 3; e >= 0; --e) {
+            const int t = tb + 4 * g + e;
+            r[e] = 0.0f;
+            if (GUARD && (unsigned)t >= (unsigned)T) continue;
+            if (fold_last && t == T - 1) fold_last_state_grad<RESET>(go[e], gv[e], glast, vv[e], q, cfg);
+            Rprev = st.R;
+            const float Rt = lif_bwd_step<SURR, RESET, WA, WS>(st, vv[e], go[e], gv[e], sl[e], xi[e], q, sc, cp, cfg, f0, nc0);
+            r[e] = __fmul_rn(q.scale, Rt);
+        }
+        *reinterpret_cast<float4 *>(tg + o) = make_float4(r[0], r[1], r[2], r[3]);
+    }
+}
+
+template <int SURR, int RESET, bool WA, int WS>
+__global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_ntv_kernel(const LifBwdArgs A, int ntiles)
+{
+    extern __shared__ __align__(16) float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t N = A.B * A.M;
+    const int T = (int)A.T;
+    const int64_t n0 = (blockIdx.x * (int64_t)NT_WARPS + warp) * TILE;
+    if (n0 >= N) return;
+    // per warp: two sets (double buffer) of `ntiles` tiles
+    float *wbase = smem + warp * (2 * ntiles * NTV_TILE_FLOATS);
+    const int i_gv = A.gv ? 2 : -1;
+    const int i_sl = (SURR == EXB_SURR_GENERIC) ? (2 + (A.gv ? 1 : 0)) : -1;
+    const int i_xi = (WS == SCALE_GRAD_FROM_INPUT) ? (ntiles - 1) : -1;
+
+    const int rows = (int)min((int64_t)TILE, N - n0);
+    const bool valid = lane < rows;
+    const int64_t n = valid ? n0 + lane : n0;
+    const int64_t b = n / A.M, m = n - b * A.M;
+    const SpikeCfg cfg = make_spike_cfg(A.maxs);
+    const Neuron q = A.np.load(b, m, cfg);
+    const SurrConst sc = surr_prepare<SURR>(q, A.p0, A.p1);
+    const float cp = __fmul_rn(q.alpha, q.c);
+    BwdState st;
+    st.R = 0.0f; st.ag = 0.0f; st.sg = 0.0f; st.vnext = 0.0f;
+    float Rprev = 0.0f, f0 = 0.0f;
+    bool nc0 = true;
+    const float glast = (A.g_last && valid) ? __ldg(A.g_last + n) : 0.0f;
+    const bool fold_last = A.g_last != nullptr;
+
+    const int a0 = line_pos(A.grad_input, n0, A.T);
+    const int a = line_pos(A.grad_input, n, A.T);
+    const int nchunks = nt_chunks(A.T);
+    const int64_t off = n0 * A.T;
+
+    auto prefetch_set = [&](float *set, int k) {
+        ntv_prefetch(set, A.go + off, T, rows, k, a0, lane);
+        ntv_prefetch(set + NTV_TILE_FLOATS, A.v_mem + off, T, rows, k, a0, lane);
+        if (i_gv >= 0) ntv_prefetch(set + i_gv * NTV_TILE_FLOATS, A.gv + off, T, rows, k, a0, lane);
+        if (i_sl >= 0) ntv_prefetch(set + i_sl * NTV_TILE_FLOATS, A.surr + off, T, rows, k, a0, lane);
+        if (i_xi >= 0) ntv_prefetch(set + i_xi * NTV_TILE_FLOATS, A.input + off, T, rows, k, a0, lane);
+        prefetch_commit();
+    };
+
+    prefetch_set(wbase, nchunks - 1);
+    int cur = 0;
+    for (int k = nchunks - 1; k >= 0; --k, cur ^= 1) {
+        float *set = wbase + cur * (ntiles * NTV_TILE_FLOATS);
+        float *tg = set;
+        const float *tv = set + NTV_TILE_FLOATS;
+        const float *tgv = i_gv >= 0 ? set + i_gv * NTV_TILE_FLOATS : nullptr;
+        const float *tsl = i_sl >= 0 ? set + i_sl * NTV_TILE_FLOATS : nullptr;
+        const float *txi = i_xi >= 0 ? set + i_xi * NTV_TILE_FLOATS : nullptr;
+        if (k > 0) {
+            prefetch_set(wbase + (cur ^ 1) * (ntiles * NTV_TILE_FLOATS), k - 1);
+            prefetch_wait<1>();
+        } else {
+            prefetch_wait<0>();
+        }
+        __syncwarp();
+        if (valid) {
+            const int tb = k * TILE - a;   // time step of column 0
+            if (tb >= 0 && tb + TILE < T)  // strictly inside: no guards, and not the last time step
+                ntv_bwd_chunk<SURR, RESET, WA, WS, false>(tg, tv, tgv, tsl, txi, lane, tb, T, false, glast, st, Rprev, f0,
+                                                          nc0, q, sc, cp, cfg);
+            else
+                ntv_bwd_chunk<SURR, RESET, WA, WS, true>(tg, tv, tgv, tsl, txi, lane, tb, T, fold_last, glast, st, Rprev,
+                                                         f0, nc0, q, sc, cp, cfg);
+        }
+        __syncwarp();
+        ntv_store(A.grad_input + off, tg, T, rows, k, a0, lane);
+        __syncwarp();
+    }
+    if (valid) {
+        if (A.grad_init) A.grad_init[n] = __fmul_rn(q.alpha, st.R);
+        const float vi = A.v_init ? __ldg(A.v_init + n) : 0.0f;
+        if (WA) A.grad_alpha[n] = alpha_grad_finish<RESET>(st, vi, Rprev, f0, nc0);
+        if (WS) A.grad_scale[n] = scale_grad_finish<WS>(st, vi, q);
+    }
+}
+
+// All tensors share the output's position inside a 16-byte granule, and T fits the int arithmetic.
+static inline bool ntv_eligible(int64_t T, const void *ref, std::initializer_list<const void *> others)
+{
+    if (T > 0x7fffffffll - 64) return false;
+    const uintptr_t r = reinterpret_cast<uintptr_t>(ref) & 15u;
+    for (const void *p : others)
+        if (p && (reinterpret_cast<uintptr_t>(p) & 15u) != r) return false;
+    return true;
+}
+
+}  // namespace exb

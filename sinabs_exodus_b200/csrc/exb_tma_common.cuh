@@ -159,7 +159,9 @@ static bool make_btm_tensor_map(CUtensorMap *map, const float *base, int64_t B, 
 }
 
 // Tile shape choice: wide tiles (512 neurons, 4+1 warps) when they alone fill the GPU,
-// narrow tiles (128 neurons, 1+1 warps, longer time chunks) otherwise.  The pipeline shape
+// narrow tiles (128 neurons, 4+1 warps, longer time chunks) otherwise.  Tiles narrower than
+// 128 neurons were measured and are slower: their 128-byte rows reach about 4.9 TB/s where
+// 512-byte rows reach 6.1 TB/s, which costs more than the extra CTAs gain.  The pipeline shape
 // (time steps per stage, stages) keeps one stage at about 8-16 KB.  EXB_TMA_TC / EXB_TMA_STAGES
 // in the environment override it (tuning aid).
 static bool use_wide(int64_t B, int64_t M)

@@ -64,6 +64,39 @@ def test_integrate_and_fire_chained(surrogate, backward_var):
     assert rel_err(alpha.grad.cpu().numpy()[ok], ga64[ok]) < TOL
 
 
+@pytest.mark.parametrize("N,T", [(70, 300), (33, 75), (5, 1), (64, 31), (40, 97)])
+@pytest.mark.parametrize("shift", [0, 1, 4, 5, 8])
+def test_integrate_and_fire_unaligned_rows(N, T, shift):
+    """[N,T] rows that start anywhere inside a 128-byte line (T not a multiple of 32, base pointers
+    shifted by a few floats): forward bit-exact, gradients to rounding."""
+    from sinabs_exodus_b200 import IntegrateAndFire
+    from sinabs_exodus_b200.compat import activation as sa
+    cs = lif_case(N * 7 + T, N, T, clamp=True)
+    buf = torch.zeros(N * T + shift, device="cuda:0")
+    inp = buf[shift:].view(N, T)
+    inp.copy_(cu(cs["inp"]))
+    assert inp.data_ptr() % 128 == (4 * shift) % 128
+    inp.requires_grad_(True)
+    alpha = cu(cs["alpha"], True)
+    v0, theta, c, lo = cu(cs["v_init"]), cu(cs["theta"]), cu(cs["subtract"]), cu(cs["theta_low"])
+    s, vm = IntegrateAndFire.apply(inp, alpha, v0, theta, c, lo, sa.SingleExponential(), None)
+    s_ref, v_ref = orc.lif_forward(cs["inp"], cs["v_init"], cs["alpha"], cs["subtract"], cs["theta"], cs["theta_low"], None)
+    np.testing.assert_array_equal(s.detach().cpu().numpy(), s_ref)
+    np.testing.assert_array_equal(vm.detach().cpu().numpy(), v_ref)
+    rng = np.random.default_rng(N + T)
+    w_s = rng.standard_normal((N, T)).astype(np.float32); w_v = rng.standard_normal((N, T)).astype(np.float32)
+    gbuf = torch.zeros(N * T + shift, device="cuda:0")
+    gs = gbuf[shift:].view(N, T); gs.copy_(cu(w_s))
+    torch.autograd.backward([s, vm], [gs, cu(w_v)])
+    surr = orc.surrogate_single_exponential(v_ref, cs["theta"][:, None])
+    nc = (v_ref > cs["theta_low"][:, None]).astype(np.float32)
+    g = (surr * w_s).astype(np.float32) + w_v
+    vpost = (v_ref - cs["subtract"][:, None] * s_ref).astype(np.float32)
+    gi64, ga64 = orc.lif_backward_f64(g, surr, nc, cs["alpha"], cs["subtract"], vpost, cs["v_init"])
+    assert rel_err(inp.grad.cpu().numpy(), gi64) < TOL
+    assert rel_err(alpha.grad.cpu().numpy(), ga64) < 2 * TOL
+
+
 def test_integrate_and_fire_errors():
     from sinabs_exodus_b200 import IntegrateAndFire
     from sinabs_exodus_b200._lib import ExodusLibraryError
