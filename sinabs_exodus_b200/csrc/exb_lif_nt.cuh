@@ -13,7 +13,7 @@
 //
 // Row heads and tails (time steps outside [0,T) inside a line belong to the neighbouring rows)
 // are moved element by element.  Needs every tensor's base address congruent to the output's
-// modulo 16 bytes and T < 2^31 - 64; the launcher falls back to the 4-byte variant otherwise.
+// modulo 16 bytes and T <= 2^25; the launcher falls back to the 4-byte variant otherwise.
 #pragma once
 
 namespace exb {
@@ -22,61 +22,71 @@ constexpr int NTV_TILE_FLOATS = TILE * TILE;   // unpadded
 
 __device__ __forceinline__ int ntv_off(int r, int g) { return r * TILE + ((g ^ (r & 7)) << 2); }
 
-// Granule (row r, granule g) of chunk k: first time step and whether all four steps exist.
-struct NtvPiece {
-    int r, g, t0;
-    bool in_rows, whole;
+// What one lane moves in the copy phases: granule lane%8 of rows it*4 + lane/8, it = 0..7.
+// Everything that does not depend on the chunk is kept here, so a copy costs a handful of
+// instructions per granule: with kb = 32*k, the granule's first time step is kb + c[it] and its
+// element offset from the warp's first row is kb + off[it].
+struct NtvLane {
+    int c[8];      // 4*g - (position of the row's first element in its line); far negative for rows past the end
+    int off[8];    // r*T + c
+    int sm0, sm1;  // tile offset (floats) of this lane's granule for even / odd `it`, without the it*128 term
 };
 
-__device__ __forceinline__ NtvPiece ntv_piece(int it, int lane, int k, int a0, int step, int rows, int T)
+__device__ __forceinline__ NtvLane ntv_lane(int lane, int a0, int T, int rows)
 {
-    NtvPiece p;
-    p.r = it * 4 + (lane >> 3);
-    p.g = lane & 7;
-    const int ar = (a0 + p.r * step) & (TILE - 1);
-    p.t0 = k * TILE - ar + 4 * p.g;
-    p.in_rows = p.r < rows;
-    p.whole = p.t0 >= 0 && p.t0 + 3 < T;
-    return p;
-}
-
-__device__ __forceinline__ void ntv_prefetch(float *tile, const float *src, int T, int rows, int k, int a0, int lane)
-{
+    NtvLane L;
     const int step = T & (TILE - 1);
-    const unsigned base = (unsigned)__cvta_generic_to_shared(tile);
+    const int q = lane >> 3, g = lane & 7;
 #pragma unroll
     for (int it = 0; it < 8; ++it) {
-        const NtvPiece p = ntv_piece(it, lane, k, a0, step, rows, T);
-        if (!p.in_rows) continue;
-        const float *gp = src + (int64_t)p.r * T + p.t0;
-        const unsigned dst = base + 4u * (unsigned)ntv_off(p.r, p.g);
-        if (p.whole) {
+        const int r = it * 4 + q;
+        const int ar = (a0 + r * step) & (TILE - 1);
+        L.c[it] = (r < rows) ? 4 * g - ar : -(1 << 30);
+        L.off[it] = r * T + 4 * g - ar;
+    }
+    L.sm0 = q * TILE + ((g ^ q) << 2);
+    L.sm1 = q * TILE + ((g ^ (q | 4)) << 2);
+    return L;
+}
+
+__device__ __forceinline__ void ntv_prefetch(float *tile, const float *src, int T, int kb, const NtvLane &L)
+{
+    const unsigned base = (unsigned)__cvta_generic_to_shared(tile);
+    const unsigned tm3 = (unsigned)max(T - 3, 0);
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const int t0 = kb + L.c[it];
+        const float *gp = src + (kb + L.off[it]);
+        const unsigned dst = base + 4u * (unsigned)(((it & 1) ? L.sm1 : L.sm0) + it * 4 * TILE);
+        if ((unsigned)t0 < tm3) {
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gp) : "memory");
-        } else {
+        } else if (t0 > -4 && t0 < T) {
 #pragma unroll
             for (int e = 0; e < 4; ++e)
-                if ((unsigned)(p.t0 + e) < (unsigned)T)
+                if ((unsigned)(t0 + e) < (unsigned)T)
                     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * e), "l"(gp + e) : "memory");
         }
     }
 }
 
-__device__ __forceinline__ void ntv_store(float *dst, const float *tile, int T, int rows, int k, int a0, int lane)
+__device__ __forceinline__ void ntv_store(float *dst, const float *tile, int T, int kb, const NtvLane &L)
 {
-    const int step = T & (TILE - 1);
+    const unsigned tm3 = (unsigned)max(T - 3, 0);
+    float4 val[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it)
+        val[it] = *reinterpret_cast<const float4 *>(tile + ((it & 1) ? L.sm1 : L.sm0) + it * 4 * TILE);
 #pragma unroll
     for (int it = 0; it < 8; ++it) {
-        const NtvPiece p = ntv_piece(it, lane, k, a0, step, rows, T);
-        if (!p.in_rows) continue;
-        float *gp = dst + (int64_t)p.r * T + p.t0;
-        const float4 val = *reinterpret_cast<const float4 *>(tile + ntv_off(p.r, p.g));
-        if (p.whole) {
-            __stcs(reinterpret_cast<float4 *>(gp), val);
-        } else {
-            const float e4[4] = {val.x, val.y, val.z, val.w};
+        const int t0 = kb + L.c[it];
+        float *gp = dst + (kb + L.off[it]);
+        if ((unsigned)t0 < tm3) {
+            __stcs(reinterpret_cast<float4 *>(gp), val[it]);
+        } else if (t0 > -4 && t0 < T) {
+            const float e4[4] = {val[it].x, val[it].y, val[it].z, val[it].w};
 #pragma unroll
             for (int e = 0; e < 4; ++e)
-                if ((unsigned)(p.t0 + e) < (unsigned)T) __stcs(gp + e, e4[e]);
+                if ((unsigned)(t0 + e) < (unsigned)T) __stcs(gp + e, e4[e]);
         }
     }
 }
@@ -87,10 +97,14 @@ template <int RESET, bool GUARD>
 __device__ __forceinline__ void ntv_fwd_chunk(float *tx, float *ts, int lane, int tb, int T, float &v, float &af,
                                               const Neuron &q, const SpikeCfg &cfg, SpikeTotal &cnt)
 {
-#pragma unroll
+    // the next granule is read before this one's results are written: the compiler cannot tell that
+    // the two do not alias and would otherwise serialise a shared-memory round trip per granule
+    float4 xn = *reinterpret_cast<const float4 *>(tx + ntv_off(lane, 0));
+#pragma unroll(GUARD ? 1 : 8)   // the guarded variant runs twice per row: keep its code small
     for (int g = 0; g < 8; ++g) {
         const int o = ntv_off(lane, g);
-        const float4 x4 = *reinterpret_cast<const float4 *>(tx + o);
+        const float4 x4 = xn;
+        if (g < 7) xn = *reinterpret_cast<const float4 *>(tx + ntv_off(lane, g + 1));
         float x[4] = {x4.x, x4.y, x4.z, x4.w};
         float s[4], u[4];
 #pragma unroll
@@ -128,15 +142,16 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_fwd_ntv_kernel(const LifFwd
 
     const int a0 = line_pos(A.spikes, n0, A.T);
     const int a = line_pos(A.spikes, n, A.T);
+    const NtvLane L = ntv_lane(lane, a0, T, rows);
     const int nchunks = nt_chunks(A.T);
     const float *src = A.input + n0 * A.T;
-    ntv_prefetch(tbuf, src, T, rows, 0, a0, lane);
+    ntv_prefetch(tbuf, src, T, 0, L);
     prefetch_commit();
     int cur = 0;
     for (int k = 0; k < nchunks; ++k, cur ^= 1) {
         float *tx = tbuf + cur * NTV_TILE_FLOATS;
         if (k + 1 < nchunks) {
-            ntv_prefetch(tbuf + (cur ^ 1) * NTV_TILE_FLOATS, src, T, rows, k + 1, a0, lane);
+            ntv_prefetch(tbuf + (cur ^ 1) * NTV_TILE_FLOATS, src, T, (k + 1) * TILE, L);
             prefetch_commit();
             prefetch_wait<1>();
         } else {
@@ -149,8 +164,8 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_fwd_ntv_kernel(const LifFwd
             else ntv_fwd_chunk<RESET, true>(tx, ts, lane, tb, T, v, af, q, cfg, cnt);
         }
         __syncwarp();
-        ntv_store(A.spikes + n0 * A.T, ts, T, rows, k, a0, lane);
-        ntv_store(A.v_mem + n0 * A.T, tx, T, rows, k, a0, lane);
+        ntv_store(A.spikes + n0 * A.T, ts, T, k * TILE, L);
+        ntv_store(A.v_mem + n0 * A.T, tx, T, k * TILE, L);
         __syncwarp();
     }
     if (A.v_post_last && valid) A.v_post_last[n] = post_reset<RESET>(v, af, q);
@@ -167,15 +182,21 @@ __device__ __forceinline__ void ntv_bwd_chunk(float *tg, const float *tv, const 
                                               BwdState &st, float &Rprev, float &f0, bool &nc0, const Neuron &q,
                                               const SurrConst &sc, float cp, const SpikeCfg &cfg)
 {
+    // one granule ahead, for the same reason as in the forward chunk
+    float4 go_n = *reinterpret_cast<const float4 *>(tg + ntv_off(lane, 7));
+    float4 v_n = *reinterpret_cast<const float4 *>(tv + ntv_off(lane, 7));
 #pragma unroll
     for (int g = 7; g >= 0; --g) {
         const int o = ntv_off(lane, g);
-        const float4 go4 = *reinterpret_cast<const float4 *>(tg + o);
-        const float4 v4 = *reinterpret_cast<const float4 *>(tv + o);
+        const float4 go4 = go_n, v4 = v_n;
         float4 gv4 = make_float4(0.f, 0.f, 0.f, 0.f), sl4 = gv4, xi4 = gv4;
         if (tgv) gv4 = *reinterpret_cast<const float4 *>(tgv + o);
         if (SURR == EXB_SURR_GENERIC) sl4 = *reinterpret_cast<const float4 *>(tsl + o);
         if (WS == SCALE_GRAD_FROM_INPUT) xi4 = *reinterpret_cast<const float4 *>(txi + o);
+        if (g > 0) {
+            go_n = *reinterpret_cast<const float4 *>(tg + ntv_off(lane, g - 1));
+            v_n = *reinterpret_cast<const float4 *>(tv + ntv_off(lane, g - 1));
+        }
         float go[4] = {go4.x, go4.y, go4.z, go4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
         float gv[4] = {gv4.x, gv4.y, gv4.z, gv4.w}, sl[4] = {sl4.x, sl4.y, sl4.z, sl4.w};
         float xi[4] = {xi4.x, xi4.y, xi4.z, xi4.w};
@@ -226,15 +247,17 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_ntv_kernel(const LifBwd
 
     const int a0 = line_pos(A.grad_input, n0, A.T);
     const int a = line_pos(A.grad_input, n, A.T);
+    const NtvLane L = ntv_lane(lane, a0, T, rows);
     const int nchunks = nt_chunks(A.T);
     const int64_t off = n0 * A.T;
 
     auto prefetch_set = [&](float *set, int k) {
-        ntv_prefetch(set, A.go + off, T, rows, k, a0, lane);
-        ntv_prefetch(set + NTV_TILE_FLOATS, A.v_mem + off, T, rows, k, a0, lane);
-        if (i_gv >= 0) ntv_prefetch(set + i_gv * NTV_TILE_FLOATS, A.gv + off, T, rows, k, a0, lane);
-        if (i_sl >= 0) ntv_prefetch(set + i_sl * NTV_TILE_FLOATS, A.surr + off, T, rows, k, a0, lane);
-        if (i_xi >= 0) ntv_prefetch(set + i_xi * NTV_TILE_FLOATS, A.input + off, T, rows, k, a0, lane);
+        const int kb = k * TILE;
+        ntv_prefetch(set, A.go + off, T, kb, L);
+        ntv_prefetch(set + NTV_TILE_FLOATS, A.v_mem + off, T, kb, L);
+        if (i_gv >= 0) ntv_prefetch(set + i_gv * NTV_TILE_FLOATS, A.gv + off, T, kb, L);
+        if (i_sl >= 0) ntv_prefetch(set + i_sl * NTV_TILE_FLOATS, A.surr + off, T, kb, L);
+        if (i_xi >= 0) ntv_prefetch(set + i_xi * NTV_TILE_FLOATS, A.input + off, T, kb, L);
         prefetch_commit();
     };
 
@@ -264,7 +287,7 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_ntv_kernel(const LifBwd
                                                          f0, nc0, q, sc, cp, cfg);
         }
         __syncwarp();
-        ntv_store(A.grad_input + off, tg, T, rows, k, a0, lane);
+        ntv_store(A.grad_input + off, tg, T, k * TILE, L);
         __syncwarp();
     }
     if (valid) {
@@ -278,7 +301,7 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_ntv_kernel(const LifBwd
 // All tensors share the output's position inside a 16-byte granule, and T fits the int arithmetic.
 static inline bool ntv_eligible(int64_t T, const void *ref, std::initializer_list<const void *> others)
 {
-    if (T > 0x7fffffffll - 64) return false;
+    if (T > (1ll << 25)) return false;   // 32 rows of T floats are addressed with int offsets
     const uintptr_t r = reinterpret_cast<uintptr_t>(ref) & 15u;
     for (const void *p : others)
         if (p && (reinterpret_cast<uintptr_t>(p) & 15u) != r) return false;

@@ -64,7 +64,7 @@ def test_integrate_and_fire_chained(surrogate, backward_var):
     assert rel_err(alpha.grad.cpu().numpy()[ok], ga64[ok]) < TOL
 
 
-@pytest.mark.parametrize("N,T", [(70, 300), (33, 75), (5, 1), (64, 31), (40, 97)])
+@pytest.mark.parametrize("N,T", [(70, 300), (33, 75), (5, 1), (64, 31), (40, 97), (70, 68), (45, 132), (64, 100), (37, 64), (31, 60)])
 @pytest.mark.parametrize("shift", [0, 1, 4, 5, 8])
 def test_integrate_and_fire_unaligned_rows(N, T, shift):
     """[N,T] rows that start anywhere inside a 128-byte line (T not a multiple of 32, base pointers
