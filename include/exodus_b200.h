@@ -128,11 +128,14 @@ int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, flo
  * leakyForward (cuda/bindings.cu:163-193, kernel cuda/leaky_kernels.h:29-58).
  * in_scale (NULL = 1) is a per-neuron factor on the input that fuses the
  * layer's decay_early / norm_input multiplications (layers/lif.py:194-195,
- * 206-214).  v_last[N] (may be NULL) receives v_{T-1}. */
+ * 206-214).  v_last[N] (may be NULL) receives v_{T-1}.  out_sum (may be NULL)
+ * points at one double on the device, zeroed by the caller, to which the sum of
+ * all outputs is added: the layer's `output.sum() / numel` (layers/lif.py:305)
+ * without another pass over the output. */
 int exb_leaky_forward(float *out, const float *input, const float *v_init,
                       const float *alpha, int alpha_mode,
                       const float *in_scale, int in_scale_mode,
-                      float *v_last,
+                      float *v_last, double *out_sum,
                       int64_t B, int64_t T, int64_t M, int layout,
                       int device, void *stream);
 
@@ -205,7 +208,7 @@ int64_t exb_leaky_scan_workspace_bytes(int64_t B, int64_t T, int64_t M);
 int exb_leaky_forward_scan(float *out, const float *input, const float *v_init,
                            const float *alpha, int alpha_mode,
                            const float *in_scale, int in_scale_mode,
-                           float *v_last, void *workspace, int64_t workspace_bytes,
+                           float *v_last, double *out_sum, void *workspace, int64_t workspace_bytes,
                            int64_t B, int64_t T, int64_t M, int device, void *stream);
 
 int exb_leaky_backward_scan(float *grad_input, float *grad_alpha, float *grad_init, float *grad_scale,

@@ -74,7 +74,7 @@ def load() -> ctypes.CDLL:
                                      _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _i,
                                      _u32, _i, _i, _f, _f] + geometry
     lib.exb_leaky_forward.restype = _i
-    lib.exb_leaky_forward.argtypes = [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp] + geometry
+    lib.exb_leaky_forward.argtypes = [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _vp] + geometry
     lib.exb_leaky_backward.restype = _i
     lib.exb_leaky_backward.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                        _vp, _i, _vp, _i] + geometry
@@ -82,7 +82,7 @@ def load() -> ctypes.CDLL:
     lib.exb_leaky_scan_workspace_bytes.argtypes = [_i64, _i64, _i64]
     scan_tail = [_vp, _i64, _i64, _i64, _i64, _i, _vp]
     lib.exb_leaky_forward_scan.restype = _i
-    lib.exb_leaky_forward_scan.argtypes = [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp] + scan_tail
+    lib.exb_leaky_forward_scan.argtypes = [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _vp] + scan_tail
     lib.exb_leaky_backward_scan.restype = _i
     lib.exb_leaky_backward_scan.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i] + scan_tail
     syn_params = [_vp, _i] * 7
@@ -115,6 +115,15 @@ def device_status(device: Optional[torch.device] = None) -> None:
 
 def ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
+
+
+def _ptr_f64(t: Optional[torch.Tensor]):
+    """Address of a one-element float64 CUDA accumulator (or None)."""
+    if t is None:
+        return None
+    if not t.is_cuda or t.dtype != torch.float64 or t.numel() < 1:
+        raise ExodusLibraryError("the sum accumulator must be a float64 CUDA tensor with one element")
+    return t.data_ptr()
 
 
 def _require_cuda(*tensors: Optional[torch.Tensor]) -> torch.device:
@@ -185,12 +194,13 @@ def lif_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, gra
 
 
 def leaky_forward(out, inp, v_init, alpha: Tuple, in_scale: Tuple, v_last, B: int, T: int, M: int,
-                  layout: int) -> None:
+                  layout: int, out_sum=None) -> None:
+    """``out_sum``: optional float64 tensor of one element (zeroed by the caller) that receives sum(out)."""
     if B * T * M == 0:      # empty problem: nothing to launch (empty tensors have no storage to point at)
         return
     dev = _require_cuda(out, inp, v_init, alpha[0], in_scale[0], v_last)
     st = load().exb_leaky_forward(ptr(out), ptr(inp), ptr(v_init), ptr(alpha[0]), alpha[1],
-                                  ptr(in_scale[0]), in_scale[1], ptr(v_last),
+                                  ptr(in_scale[0]), in_scale[1], ptr(v_last), _ptr_f64(out_sum),
                                   B, T, M, layout, dev.index, _stream(dev))
     _check(st, "exb_leaky_forward")
 
@@ -214,10 +224,10 @@ def leaky_scan_workspace_bytes(B: int, T: int, M: int) -> int:
 
 
 def leaky_forward_scan(out, inp, v_init, alpha: Tuple, in_scale: Tuple, v_last, workspace, B: int, T: int,
-                       M: int) -> None:
+                       M: int, out_sum=None) -> None:
     dev = _require_cuda(out, inp, v_init, alpha[0], in_scale[0], v_last)
     st = load().exb_leaky_forward_scan(ptr(out), ptr(inp), ptr(v_init), ptr(alpha[0]), alpha[1],
-                                       ptr(in_scale[0]), in_scale[1], ptr(v_last),
+                                       ptr(in_scale[0]), in_scale[1], ptr(v_last), _ptr_f64(out_sum),
                                        workspace.data_ptr(), workspace.numel() * workspace.element_size(),
                                        B, T, M, dev.index, _stream(dev))
     _check(st, "exb_leaky_forward_scan")

@@ -184,7 +184,7 @@ int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, flo
 int exb_leaky_forward(float *out, const float *input, const float *v_init,
                       const float *alpha, int alpha_mode,
                       const float *in_scale, int in_scale_mode,
-                      float *v_last,
+                      float *v_last, double *out_sum,
                       int64_t B, int64_t T, int64_t M, int layout,
                       int device, void *stream)
 {
@@ -201,6 +201,7 @@ int exb_leaky_forward(float *out, const float *input, const float *v_init,
     a.alpha = exb::make_param(alpha, alpha_mode, M);
     a.scale = exb::make_param(in_scale, in_scale_mode, M);
     a.v_last = v_last;
+    a.out_sum = out_sum;
     a.B = B; a.T = T; a.M = M;
     return launch_status(exb::launch_leaky_forward(a, layout, (cudaStream_t)stream), "exb_leaky_forward");
 }
@@ -242,7 +243,7 @@ int64_t exb_leaky_scan_workspace_bytes(int64_t B, int64_t T, int64_t M)
 int exb_leaky_forward_scan(float *out, const float *input, const float *v_init,
                            const float *alpha, int alpha_mode,
                            const float *in_scale, int in_scale_mode,
-                           float *v_last, void *workspace, int64_t workspace_bytes,
+                           float *v_last, double *out_sum, void *workspace, int64_t workspace_bytes,
                            int64_t B, int64_t T, int64_t M, int device, void *stream)
 {
     if (int st = check_geometry(B, T, M, EXB_LAYOUT_BTM)) return st;
@@ -258,6 +259,7 @@ int exb_leaky_forward_scan(float *out, const float *input, const float *v_init,
     a.alpha = exb::make_param(alpha, alpha_mode, M);
     a.scale = exb::make_param(in_scale, in_scale_mode, M);
     a.v_last = v_last;
+    a.out_sum = out_sum;
     a.B = B; a.T = T; a.M = M;
     bool used = false;
     cudaError_t e = exb::launch_leaky_forward_scan(a, workspace, workspace_bytes, (cudaStream_t)stream, &used);
@@ -330,6 +332,7 @@ int exb_leaky_forward_scan_static(float *out, const float *input, const float *v
     a.alpha = exb::make_param(alpha, alpha_mode, M);
     a.scale = exb::make_param(in_scale, in_scale_mode, M);
     a.v_last = v_last;
+    a.out_sum = nullptr;
     a.B = B; a.T = T; a.M = M;
     bool used = false;
     cudaError_t e = exb::launch_leaky_forward_scan_static(a, current, (cudaStream_t)stream, &used);

@@ -30,6 +30,7 @@ struct LeakyFwdArgs {
     const float *input, *v_init;
     Param alpha, scale;
     float *v_last;
+    double *out_sum;   // optional: receives (atomically) the sum of all outputs
     int64_t B, T, M;
 };
 
@@ -101,6 +102,14 @@ __device__ __forceinline__ unsigned long long warp_sum_u64(unsigned long long x)
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
     return x;
+}
+
+// Sum over the warp of per-thread partial sums, added to *dst by lane 0 (all 32 lanes must call).
+__device__ __forceinline__ void warp_add_f64(double *dst, double x, int lane)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    if (lane == 0) atomicAdd(dst, x);
 }
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -22,12 +22,17 @@ template <int V, int U>
 __global__ void __launch_bounds__(256) leaky_fwd_btm_kernel(const LeakyFwdArgs A)
 {
     const int64_t MV = A.M / V;
-    const int64_t gid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-    if (gid >= A.B * MV) return;
+    int64_t gid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    const bool valid = gid < A.B * MV;
+    if (!valid) {
+        if (!A.out_sum) return;
+        gid = A.B * MV - 1;   // keeps the warp whole for the final reduction; stores are skipped
+    }
     const int64_t b = gid / MV;
     const int64_t m = (gid - b * MV) * V;
     const int64_t n = b * A.M + m;
     const int64_t T = A.T, M = A.M;
+    double total = 0.0;
     float al[V], sc[V], v[V];
 #pragma unroll
     for (int j = 0; j < V; ++j) {
@@ -47,6 +52,7 @@ __global__ void __launch_bounds__(256) leaky_fwd_btm_kernel(const LeakyFwdArgs A
         if (u < T) ldv<V>(xc[u], in + u * M);
     }
     for (int64_t t = 0; t < T; t += U) {
+        float part = 0.0f;
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int64_t tt = t + U + u;
@@ -57,19 +63,24 @@ __global__ void __launch_bounds__(256) leaky_fwd_btm_kernel(const LeakyFwdArgs A
             const int64_t tt = t + u;
             if (tt < T) {
 #pragma unroll
-                for (int j = 0; j < V; ++j) v[j] = __fmaf_rn(v[j], al[j], __fmul_rn(sc[j], xc[u][j]));
-                stv<V>(out + tt * M, v);
+                for (int j = 0; j < V; ++j) {
+                    v[j] = __fmaf_rn(v[j], al[j], __fmul_rn(sc[j], xc[u][j]));
+                    part += v[j];
+                }
+                if (valid) stv<V>(out + tt * M, v);
             }
         }
+        total += (double)part;
 #pragma unroll
         for (int u = 0; u < U; ++u)
 #pragma unroll
             for (int j = 0; j < V; ++j) xc[u][j] = xn[u][j];
     }
-    if (A.v_last) {
+    if (A.v_last && valid) {
 #pragma unroll
         for (int j = 0; j < V; ++j) A.v_last[n + j] = v[j];
     }
+    if (A.out_sum) warp_add_f64(A.out_sum, valid ? total : 0.0, threadIdx.x & 31);
 }
 
 template <int V, bool WA, bool WS, int U>
@@ -217,6 +228,7 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) leaky_fwd_nt_kernel(const Lea
     const float *rin = A.input + n * T;
     float *rout = A.out + n * T;
 
+    double total = 0.0;
     float x[E], xnext[E];
     load_seg<E>(x, rin, (int64_t)lane * E, T);
     for (int64_t t0 = 0; t0 < T; t0 += 32 * E) {
@@ -248,10 +260,18 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) leaky_fwd_nt_kernel(const Lea
             for (int e = 0; e < E; ++e)
                 if (t + e == T - 1) A.v_last[n] = res[e];
         }
+        if (A.out_sum) {
+            float part = 0.0f;
+#pragma unroll
+            for (int e = 0; e < E; ++e)
+                if (t + e < T) part += res[e];
+            total += (double)part;
+        }
         carry = __shfl_sync(0xffffffffu, o, 31);
 #pragma unroll
         for (int e = 0; e < E; ++e) x[e] = xnext[e];
     }
+    if (A.out_sum) warp_add_f64(A.out_sum, total, lane);
 }
 
 template <int E, bool WA, bool WS>

@@ -229,20 +229,26 @@ leaky_fwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A
             }
         }
         // ---- pass B: the real thing
+        double total = 0.0;
         float *out = A.out + ((int64_t)b * T + t0) * M + mm;
         for (int kb = 0; kb < nck && ok; ++kb, ++k) {
             if (!wait_chunk(ring, pos)) { ok = false; break; }
             const float *st = stages + (size_t)pos.s * tensor_floats + col;
             const int tmax = min(pc.tc, nsteps - kb * pc.tc);
+            float part = 0.0f;
 #pragma unroll 4
             for (int tt = 0; tt < tmax; ++tt) {
                 float xs[V];
                 lds_vec<V>(xs, st + tt * G::BW);
 #pragma unroll
-                for (int j = 0; j < V; ++j) v[j] = __fmaf_rn(v[j], al[j], __fmul_rn(sc[j], xs[j]));
+                for (int j = 0; j < V; ++j) {
+                    v[j] = __fmaf_rn(v[j], al[j], __fmul_rn(sc[j], xs[j]));
+                    part += v[j];
+                }
                 if (valid) stv<V>(out, v);
                 out += M;
             }
+            total += (double)part;
             release_chunk(ring, pos, lane);
             pos.advance(pc.stages);
         }
@@ -250,6 +256,7 @@ leaky_fwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A
 #pragma unroll
             for (int j = 0; j < V; ++j) A.v_last[n + j] = v[j];
         }
+        if (A.out_sum) warp_add_f64(A.out_sum, (ok && valid) ? total : 0.0, lane);
     }
     ring_finish(ring, pc.stages);
 }

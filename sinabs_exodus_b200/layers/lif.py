@@ -153,8 +153,9 @@ class LIF(LIFBase):
         if self.spike_fn is None:
             if self.decay_early:
                 scale = alpha_mem if scale is None else scale * alpha_mem
-            v_mem, v_last = LeakyIntegratorTM.apply(i_syn, alpha_mem, self.v_mem.reshape(-1), scale)
-            return v_mem, v_mem, v_last, None
+            total = torch.zeros(1, dtype=torch.float64, device=dev)
+            v_mem, v_last = LeakyIntegratorTM.apply(i_syn, alpha_mem, self.v_mem.reshape(-1), scale, total)
+            return v_mem, v_mem, v_last, total
 
         threshold = _flat_param(self.spike_threshold, trailing, batch, dev)
         min_v_mem = _flat_param(self.min_v_mem, trailing, batch, dev)
@@ -231,10 +232,9 @@ class LIF(LIFBase):
             self.recordings["v_mem"] = v_rec.reshape(original_shape)
         self.v_mem = v_last.reshape(batch_size, *trailing)
         output_full = output.reshape(original_shape)
-        if count is not None:
-            self.firing_rate = count[0].to(torch.float32) / output_full.numel()
-        else:
-            self.firing_rate = output_full.detach().sum() / output_full.numel()
+        # spike count (int64) or, for the non-spiking layer, the sum of the outputs (float64): both come
+        # out of the forward kernel, so the reference's `output.sum() / numel` pass is not needed
+        self.firing_rate = count[0].to(torch.float32) / max(output_full.numel(), 1)
         return output_full
 
     def _forward_fused_synaptic(self, x: torch.Tensor, original_shape):

@@ -33,7 +33,7 @@ def _scan_workspace(B: int, T: int, M: int, layout: int, device):
 
 class _LeakyCore:
     @staticmethod
-    def forward(ctx, inp, alpha, v_init, in_scale, B, T, M, layout):
+    def forward(ctx, inp, alpha, v_init, in_scale, B, T, M, layout, total=None):
         N = B * M
         a_f, sc_f, vi_f = _flat32(alpha), _flat32(in_scale), _flat32(v_init)
         modes = dict(alpha=_mode_of(a_f, M, N, "alpha"), scale=_mode_of(sc_f, M, N, "in_scale"))
@@ -44,9 +44,11 @@ class _LeakyCore:
             v_last = torch.empty(N, dtype=torch.float32, device=inp.device)
         ws = _scan_workspace(B, T, M, layout, inp.device) if T > 0 else None
         if ws is not None:
-            _lib.leaky_forward_scan(out, inp, vi_f, (a_f, modes["alpha"]), (sc_f, modes["scale"]), v_last, ws, B, T, M)
+            _lib.leaky_forward_scan(out, inp, vi_f, (a_f, modes["alpha"]), (sc_f, modes["scale"]), v_last, ws, B, T, M,
+                                    out_sum=total)
         else:
-            _lib.leaky_forward(out, inp, vi_f, (a_f, modes["alpha"]), (sc_f, modes["scale"]), v_last, B, T, M, layout)
+            _lib.leaky_forward(out, inp, vi_f, (a_f, modes["alpha"]), (sc_f, modes["scale"]), v_last, B, T, M, layout,
+                               out_sum=total)
         ctx.set_materialize_grads(False)
         ctx.geometry = (B, T, M, layout)
         ctx.modes = modes
@@ -132,13 +134,15 @@ class LeakyIntegrator(torch.autograd.Function):
 class LeakyIntegratorTM(torch.autograd.Function):
     """Leaky integrator on a time-major ``(B, T, M)`` tensor.
 
-    ``apply(inp, alpha, v_init, in_scale) -> (out, v_last)``; parameters hold 1, M or
-    B*M values.  ``v_last`` (B*M,) equals ``out[:, -1]`` and carries its own gradient,
-    so that keeping the state for the next call costs no full-size tensor.
+    ``apply(inp, alpha, v_init, in_scale, total=None) -> (out, v_last)``; parameters hold
+    1, M or B*M values.  ``v_last`` (B*M,) equals ``out[:, -1]`` and carries its own
+    gradient, so that keeping the state for the next call costs no full-size tensor.
+    ``total``: optional float64 tensor of one element, zeroed by the caller, to which the
+    kernel adds ``out.sum()`` (no gradient flows through it).
     """
 
     @staticmethod
-    def forward(ctx, inp, alpha, v_init, in_scale):
+    def forward(ctx, inp, alpha, v_init, in_scale, total=None):
         if inp.ndim != 3:
             raise ValueError("'inp' must be 3D, (batch, time, neurons)")
         if not inp.is_contiguous():
@@ -146,8 +150,8 @@ class LeakyIntegratorTM(torch.autograd.Function):
         B, T, M = inp.shape
         if v_init is not None and v_init.numel() != B * M:
             raise ValueError("'v_init' must hold one value per batch item and neuron")
-        return _LeakyCore.forward(ctx, inp, alpha, v_init, in_scale, B, T, M, _lib.LAYOUT_BTM)
+        return _LeakyCore.forward(ctx, inp, alpha, v_init, in_scale, B, T, M, _lib.LAYOUT_BTM, total)
 
     @staticmethod
     def backward(ctx, grad_out, grad_v_last):
-        return _LeakyCore.backward(ctx, grad_out, grad_v_last)
+        return _LeakyCore.backward(ctx, grad_out, grad_v_last) + (None,)

@@ -83,14 +83,23 @@ def lif_backward(cs, v_mem, go, B, M, layout, mode=_lib.PARAM_PER_N, gv=None, g_
     return from_dev(gi, B, M, layout), cpu(ga), cpu(g0), cpu(gs)
 
 
+def _check_total(total, out):
+    """The sum of the outputs that the forward kernel accumulates on the side."""
+    ref = out.double().sum().item()
+    scale = out.double().abs().sum().item() + 1e-30
+    assert abs(total.item() - ref) <= 1e-6 * scale, (total.item(), ref)
+
+
 def leaky_forward(inp, v_init, alpha, B, M, layout, mode=_lib.PARAM_PER_N, in_scale=None):
     N, T = inp.shape
     x = to_dev(inp, B, M, layout)
     out = torch.full_like(x, float("nan"))
     v_last = torch.empty(N, device=DEV)
+    total = torch.zeros(1, dtype=torch.float64, device=DEV)
     _lib.leaky_forward(out, x, vec(v_init), param(alpha, mode, B, M), param(in_scale, mode, B, M), v_last,
-                       B, T, M, layout)
+                       B, T, M, layout, out_sum=total)
     torch.cuda.synchronize()
+    _check_total(total, out)
     return from_dev(out, B, M, layout), v_last.cpu().numpy()
 
 
@@ -120,9 +129,11 @@ def leaky_forward_scan(inp, v_init, alpha, B, M, mode=_lib.PARAM_PER_N, in_scale
     x = to_dev(inp, B, M, _lib.LAYOUT_BTM)
     out = torch.full_like(x, float("nan"))
     v_last = torch.empty(N, device=DEV)
+    total = torch.zeros(1, dtype=torch.float64, device=DEV)
     _lib.leaky_forward_scan(out, x, vec(v_init), param(alpha, mode, B, M), param(in_scale, mode, B, M), v_last, ws,
-                            B, T, M)
+                            B, T, M, out_sum=total)
     torch.cuda.synchronize()
+    _check_total(total, out)
     return from_dev(out, B, M, _lib.LAYOUT_BTM), v_last.cpu().numpy()
 
 

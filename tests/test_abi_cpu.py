@@ -44,16 +44,16 @@ def test_argument_validation_without_gpu(lib):
     """Bad arguments are rejected before any CUDA call is made."""
     null = None
     one = ctypes.c_void_p(16)   # never dereferenced: validation fails first
-    st = lib.exb_leaky_forward(null, one, null, one, 0, null, 0, null, 1, 1, 1, 0, 0, null)
+    st = lib.exb_leaky_forward(null, one, null, one, 0, null, 0, null, null, 1, 1, 1, 0, 0, null)
     assert st == 1 and b"required" in lib.exb_last_error()
-    st = lib.exb_leaky_forward(one, one, null, one, 0, null, 0, null, -1, 1, 1, 0, 0, null)
+    st = lib.exb_leaky_forward(one, one, null, one, 0, null, 0, null, null, -1, 1, 1, 0, 0, null)
     assert st == 1 and b"negative" in lib.exb_last_error()
-    st = lib.exb_leaky_forward(one, one, null, one, 7, null, 0, null, 1, 1, 1, 0, 0, null)
+    st = lib.exb_leaky_forward(one, one, null, one, 7, null, 0, null, null, 1, 1, 1, 0, 0, null)
     assert st == 1 and b"mode" in lib.exb_last_error()
-    st = lib.exb_leaky_forward(one, one, null, one, 0, null, 0, null, 1, 1, 1, 9, 0, null)
+    st = lib.exb_leaky_forward(one, one, null, one, 0, null, 0, null, null, 1, 1, 1, 9, 0, null)
     assert st == 1 and b"layout" in lib.exb_last_error()
     # empty problems are a successful no-op
-    assert lib.exb_leaky_forward(one, one, null, one, 0, null, 0, null, 0, 5, 3, 0, 0, null) == 0
+    assert lib.exb_leaky_forward(one, one, null, one, 0, null, 0, null, null, 0, 5, 3, 0, 0, null) == 0
 
 
 def test_missing_library_is_loud(monkeypatch, tmp_path):

@@ -304,6 +304,19 @@ def test_layer_exp_leak(train_alphas, norm_input, decay_early):
         assert rel_err(out.detach().cpu().numpy(), want.detach().cpu().numpy()) < TOL
 
 
+def test_layer_exp_leak_firing_rate():
+    """`firing_rate` of the non-spiking layer is output.sum() / numel as in the reference layer
+    (layers/lif.py:305); here it comes out of the forward kernel, on both kernel routes."""
+    from sinabs_exodus_b200.layers import ExpLeak
+    for shape in [(3, 50, 40), (2, 3000, 8), (200, 20, 516)]:
+        torch.manual_seed(5)
+        layer = ExpLeak(tau_mem=20.0).to("cuda:0")
+        x = torch.randn(*shape, device="cuda:0") + 0.3
+        out = layer(x)
+        ref = out.double().sum().item() / out.numel()
+        assert abs(layer.firing_rate.item() - ref) <= 1e-5 * (out.double().abs().mean().item() + 1e-12)
+
+
 def test_layer_exp_leak_long_sequence_uses_scan():
     """Few neurons, long sequence: the layer routes through the time-parallel scan; same results."""
     from sinabs_exodus_b200 import _lib
