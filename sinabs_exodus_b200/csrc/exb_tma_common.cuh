@@ -118,6 +118,9 @@ __device__ __forceinline__ void lds_vec(float (&d)[V], const float *p)
     if (V == 4) {
         const float4 t = *reinterpret_cast<const float4 *>(p);
         d[0] = t.x; d[1] = t.y; d[2] = t.z; d[3] = t.w;
+    } else if (V == 2) {
+        const float2 t = *reinterpret_cast<const float2 *>(p);
+        d[0] = t.x; d[1] = t.y;
     } else {
 #pragma unroll
         for (int j = 0; j < V; ++j) d[j] = p[j];
@@ -161,7 +164,9 @@ static bool make_btm_tensor_map(CUtensorMap *map, const float *base, int64_t B, 
 // Tile shape choice: wide tiles (512 neurons, 4+1 warps) when they alone fill the GPU,
 // narrow tiles (128 neurons, 4+1 warps, longer time chunks) otherwise.  Tiles narrower than
 // 128 neurons were measured and are slower: their 128-byte rows reach about 4.9 TB/s where
-// 512-byte rows reach 6.1 TB/s, which costs more than the extra CTAs gain.  The pipeline shape
+// 512-byte rows reach 6.1 TB/s, which costs more than the extra CTAs gain.  A middle shape (256
+// neurons, 2 per thread) was measured on the fused synapse kernels: 14 % fewer instructions in the
+// backward but half the warps, and slower overall.  The pipeline shape
 // (time steps per stage, stages) keeps one stage at about 8-16 KB.  EXB_TMA_TC / EXB_TMA_STAGES
 // in the environment override it (tuning aid).
 static bool use_wide(int64_t B, int64_t M)
@@ -169,7 +174,7 @@ static bool use_wide(int64_t B, int64_t M)
     const int64_t wide_tiles = B * ((M + 511) / 512);
     return wide_tiles >= 2 * 148;
 }
-constexpr int NWARPS = 4;   // consumer warps per CTA in both tile shapes
+constexpr int NWARPS = 4;   // consumer warps per CTA in all tile shapes
 
 static int env_int(const char *name, int dflt)
 {
@@ -177,12 +182,11 @@ static int env_int(const char *name, int dflt)
     return (v && *v) ? atoi(v) : dflt;
 }
 
-static PipeCfg pipe_cfg(bool wide, int nmaps)  // wide: 4 neurons per thread (W = 512), else 1 (W = 128)
+static PipeCfg pipe_cfg(int w, int nmaps)  // w: neurons per tile (512, 256 or 128)
 {
     static const int env_tc = env_int("EXB_TMA_TC", 0);
     static const int env_st = env_int("EXB_TMA_STAGES", 0);
     PipeCfg pc;
-    const int w = wide ? 512 : 128;
     // target ~8 KB per stage across all streamed tensors
     int tc = (8 * 1024) / (w * 4 * nmaps);
     if (tc < 2) tc = 2;

@@ -116,8 +116,10 @@ lif_syn_fwd_tma_kernel(const __grid_constant__ TmaMaps6 maps, const LifSynFwdArg
 }
 
 // WG: parameter gradients wanted (streams i_syn as well).
+// The narrow tile with all four parameter gradients keeps about twenty values live per thread: at the
+// 48 registers of 8 CTAs per SM the compiler recomputes loop invariants in every step; 7 CTAs give 56.
 template <int SURR, int RESET, bool WG, int NW, int V, bool UNI>
-__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V, (V == 4)>::value)
+__global__ void __launch_bounds__((NW + 1) * 32, (V == 1 && WG) ? 7 : MinBlocks<NW, V, (V == 4)>::value)
 lif_syn_bwd_tma_kernel(const __grid_constant__ TmaMaps6 maps, const LifSynBwdArgs A, const int tiles_m, const int nmaps,
                        const PipeCfg pc)
 {
@@ -261,7 +263,7 @@ template <int RESET, int NW, int V, bool UNI>
 static cudaError_t run_syn_fwd(const LifSynFwdArgs &a, cudaStream_t s, bool *used)
 {
     using G = TileGeom<NW, V>;
-    const PipeCfg pc = pipe_cfg(V == 4, 1);
+    const PipeCfg pc = pipe_cfg(G::W, 1);
     TmaMaps6 maps;
     if (!make_btm_tensor_map(&maps.m[0], a.input, a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
     for (int i = 1; i < 6; ++i) maps.m[i] = maps.m[0];
@@ -305,7 +307,7 @@ static cudaError_t run_syn_bwd(const LifSynBwdArgs &a, cudaStream_t s, bool *use
     if (SURR == EXB_SURR_GENERIC) ptrs[nmaps++] = a.surr;
     if (WG) ptrs[nmaps++] = a.i_syn;
     if (a.g_isyn) ptrs[nmaps++] = a.g_isyn;
-    const PipeCfg pc = pipe_cfg(V == 4, nmaps);
+    const PipeCfg pc = pipe_cfg(G::W, nmaps);
     for (int i = 0; i < nmaps; ++i)
         if (!make_btm_tensor_map(&maps.m[i], ptrs[i], a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
     for (int i = nmaps; i < 6; ++i) maps.m[i] = maps.m[0];

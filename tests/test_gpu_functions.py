@@ -357,7 +357,7 @@ def test_layer_rejects_cpu_and_bad_config():
         bad(torch.zeros(1, 4, 3, device="cuda:0"))
 
 
-@pytest.mark.parametrize("B,T,M", [(4, 40, 12), (300, 12, 516)])
+@pytest.mark.parametrize("B,T,M", [(4, 40, 12), (300, 12, 516), (100, 9, 516)])
 @pytest.mark.parametrize("train_alphas", [False, True])
 def test_fused_synaptic_layer_equals_two_stage(B, T, M, train_alphas, monkeypatch):
     """The one-kernel LIF+synapse route gives the two-stage route's bits in the forward pass and its
