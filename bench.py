@@ -87,6 +87,38 @@ def make_layer(kind: str, neurons_shape, device):
     return layer.to(device)
 
 
+class FunctionArm(torch.nn.Module):
+    """The drop-in autograd Functions on the reference's own [N,T] layout (rows = batch x neurons), with the
+    workload's neuron model and no layer glue: `IntegrateAndFire.apply` / `LeakyIntegrator.apply`."""
+
+    def __init__(self, kind: str, rows: int, device):
+        super().__init__()
+        import math
+        from sinabs_exodus_b200.compat import activation as sa
+        if kind == "lif_syn":
+            raise SystemExit("--layout nt: the synaptic workload has no single [N,T] Function")
+        self.kind = kind
+        alpha = {"iaf": 1.0, "lif": math.exp(-1.0 / 20.0), "lif5": math.exp(-1.0 / 20.0),
+                 "expleak": math.exp(-1.0 / 50.0)}[kind]
+        self.alpha = torch.full((rows,), alpha, device=device)
+        self.v0 = torch.zeros(rows, device=device)
+        self.theta = torch.ones(rows, device=device)
+        self.low = torch.full((rows,), -1.0, device=device) if kind == "lif" else None
+        self.surrogate = {"iaf": sa.Heaviside(), "lif": sa.SingleExponential(grad_width=0.5),
+                          "lif5": sa.SingleExponential(), "expleak": None}[kind]
+
+    def reset_states(self):
+        pass
+
+    def forward(self, x):
+        import sinabs_exodus_b200 as ex
+        if self.kind == "expleak":
+            return ex.LeakyIntegrator.apply(x, self.alpha, self.v0)
+        spikes, _ = ex.IntegrateAndFire.apply(x, self.alpha, self.v0, self.theta, self.theta, self.low,
+                                              self.surrogate, None)
+        return spikes
+
+
 def make_input(name: str, shape, device, rank: int, batch=None):
     """Seeded synthetic input and upstream gradient with the configuration's value distribution."""
     seed = {"c1": 0, "c2": 1, "c3": 2, "c4": 3, "c5": 100}[name] + (rank if name != "c5" else rank)
@@ -327,6 +359,12 @@ def run_ours(args, wl):
     M = int(np.prod(shape[2:]))
     layer = make_layer(wl["kind"], shape[2:], dev)
     x, grad = make_input(name, shape, dev, rank)
+    if args.layout == "nt":
+        # same values, rows = (batch item, neuron), time contiguous
+        x = x.reshape(B, T, M).transpose(1, 2).reshape(B * M, T).contiguous()
+        grad = grad.reshape(B, T, M).transpose(1, 2).reshape(B * M, T).contiguous()
+        layer = FunctionArm(wl["kind"], B * M, dev)
+        args.no_e2e = True
     x.requires_grad_(True)
     tc_params = exd.time_constant_parameters(layer)
 
@@ -508,7 +546,9 @@ def run_ours(args, wl):
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"{name}: {wl['desc']}", "per_gpu_shape": list(shape),
                        "l2": f"each tensor is {nts_step * 4 / 1e6:.0f} MB (L2 is 126 MB); no flush between steps",
-                       "parallelism": f"batch-sharded x{world}", "api": "sinabs_exodus_b200.layers",
+                       "parallelism": f"batch-sharded x{world}",
+                       "api": "sinabs_exodus_b200.layers" if args.layout == "btm"
+                       else "IntegrateAndFire / LeakyIntegrator Functions on [N,T] (no layer glue)",
                        "cuda_graph": bool(args.cuda_graph)},
             "step_fraction_of_hbm_roofline": (step_bytes / (ms_total / args.steps * 1e-3) / 1e9) / peak,
             "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
@@ -526,6 +566,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch size (profiling small cases)")
+    ap.add_argument("--layout", default="btm", choices=["btm", "nt"],
+                    help="btm: the layers (time-major kernels); nt: the drop-in Functions on the reference's [N,T] layout")
     ap.add_argument("--cuda-graph", action="store_true", help="capture the step in a CUDA graph and time replays")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
