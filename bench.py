@@ -390,18 +390,9 @@ def run_ours(args, wl):
         # host work, which dominates when the kernels take only tens of microseconds.
         if world > 1 and tc_params:
             raise SystemExit("--cuda-graph is for single-process runs (the allreduce is issued from the host)")
-        side = torch.cuda.Stream(dev)
-        side.wait_stream(torch.cuda.current_stream(dev))
-        with torch.cuda.stream(side):
-            for _ in range(3):
-                step()
-        torch.cuda.current_stream(dev).wait_stream(side)
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step()
-        torch.cuda.synchronize()
-        run_step = graph.replay
+        graphed = ex.GraphedStep(layer, x, grad, carry_state=False, input_grad=True)
+        graph = graphed.graph
+        run_step = graphed.replay
         for _ in range(3):
             run_step()
         torch.cuda.synchronize()

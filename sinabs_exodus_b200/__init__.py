@@ -7,6 +7,9 @@ Public surface (same names as the reference's ``sinabs.exodus`` package):
 * ``leaky``       -- ``LeakyIntegrator`` autograd Function
 * ``conversion``  -- ``sinabs_to_exodus``, ``exodus_to_sinabs``, ``module_map``
 
+Beyond the reference: ``GraphedStep`` (``graphs``) captures a whole forward(+backward) step of a
+network of these layers in a CUDA graph.
+
 All computation runs in ``libexodus_b200.so`` (hand-written CUDA for sm_100a,
 C ABI in ``include/exodus_b200.h``).  There is no PyTorch or CPU fallback: a
 missing library or a CPU tensor raises.
@@ -21,6 +24,8 @@ from . import _lib  # noqa: E402
 from . import leaky, spike  # noqa: E402
 from . import layers  # noqa: E402
 from . import conversion  # noqa: E402
+from . import graphs  # noqa: E402
+from .graphs import GraphedStep  # noqa: E402
 from .leaky import LeakyIntegrator, LeakyIntegratorTM  # noqa: E402
 from .spike import IntegrateAndFire, IntegrateAndFireTM, LIFSynapticTM  # noqa: E402
 
