@@ -8,7 +8,7 @@ import torch
 
 from ..compat.activation import MembraneSubtract, MultiSpike, SingleExponential
 from ..compat.layers import SqueezeMixin
-from .lif import LIF
+from .lif import LIF, _scalar_constant
 
 __all__ = ["IAF", "IAFSqueeze"]
 
@@ -46,8 +46,8 @@ class IAF(LIF):
 
     @property
     def alpha_mem_calculated(self):
-        # created on the device (no host-to-device copy, which would stall the launch queue)
-        return torch.ones((), device=self.v_mem.device)
+        # made on the device, once (no host-to-device copy, which would stall the launch queue)
+        return _scalar_constant(1.0, self.v_mem.device).reshape(())
 
     @property
     def _param_dict(self) -> dict:

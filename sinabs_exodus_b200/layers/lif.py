@@ -40,6 +40,24 @@ def expand_to_1d_contiguous(value: Union[float, torch.Tensor], shape: Tuple[int]
     return torch.as_tensor(value).expand(shape).float().flatten().contiguous()
 
 
+_SCALARS: dict = {}
+
+
+def _scalar_constant(value: float, device) -> torch.Tensor:
+    """One-element tensor holding a Python number, made once per value and device (read-only).
+
+    A fill kernel instead of a host-to-device copy: the copy would wait for all queued work.  Tensors
+    made while a CUDA graph is being captured belong to that graph's memory pool and are not kept.
+    """
+    key = (value, str(device))
+    t = _SCALARS.get(key)
+    if t is None:
+        t = torch.full((1,), value, dtype=torch.float32, device=device)
+        if t.device.type != "cuda" or not torch.cuda.is_current_stream_capturing():
+            _SCALARS[key] = t
+    return t
+
+
 def _flat_param(value, trailing: Tuple[int, ...], batch: int, device) -> Optional[torch.Tensor]:
     """Bring a parameter to 1, M or B*M elements without breaking its autograd graph.
 
@@ -49,8 +67,7 @@ def _flat_param(value, trailing: Tuple[int, ...], batch: int, device) -> Optiona
     if value is None:
         return None
     if isinstance(value, (int, float)):
-        # A fill kernel instead of a host-to-device copy: the copy would wait for all queued work.
-        return torch.full((1,), float(value), dtype=torch.float32, device=device)
+        return _scalar_constant(float(value), device)
     t = value if isinstance(value, torch.Tensor) else torch.as_tensor(value, dtype=torch.float32)
     if t.device != torch.device(device) or t.dtype != torch.float32:
         t = t.to(device=device, dtype=torch.float32)
@@ -60,6 +77,38 @@ def _flat_param(value, trailing: Tuple[int, ...], batch: int, device) -> Optiona
         return t.expand(trailing).reshape(-1)
     except RuntimeError:
         return t.expand((batch, *trailing)).reshape(-1)
+
+
+class _DecayFromTau(torch.autograd.Function):
+    """``alpha = exp(-1/tau)`` and, on request, ``1 - alpha`` (the ``norm_input`` scale) as ONE autograd node.
+
+    Same values as the expression the layers are specified with (``torch.exp(-1.0 / tau)``); written as a
+    Function because the four small nodes it replaces, and their four backward nodes, cost more host time per
+    step than the neuron kernels of a small layer take to run.
+    """
+
+    @staticmethod
+    def forward(ctx, tau, with_complement: bool):
+        r = torch.reciprocal(tau)
+        alpha = torch.exp(r.neg())
+        ctx.set_materialize_grads(False)
+        ctx.save_for_backward(alpha, r)
+        if with_complement:
+            return alpha, 1.0 - alpha
+        return alpha, None
+
+    @staticmethod
+    def backward(ctx, grad_alpha, grad_complement):
+        alpha, r = ctx.saved_tensors
+        if grad_alpha is None and grad_complement is None:
+            return None, None
+        if grad_complement is None:
+            g = grad_alpha
+        elif grad_alpha is None:
+            g = grad_complement.neg()
+        else:
+            g = grad_alpha - grad_complement
+        return g * alpha * r * r, None      # d/dtau exp(-1/tau) = exp(-1/tau) / tau^2
 
 
 class LIF(LIFBase):
@@ -140,15 +189,30 @@ class LIF(LIFBase):
             x = x.contiguous()
         return x, (batch_size, time_steps, *trailing_dim)
 
+    def _membrane_decay(self):
+        """(alpha_mem, 1 - alpha_mem or None): the decay per step and the ``norm_input`` scale."""
+        tau = None if self.train_alphas else getattr(self, "tau_mem", None)
+        if isinstance(tau, torch.Tensor):
+            return _DecayFromTau.apply(tau, bool(self.norm_input))
+        alpha = self.alpha_mem_calculated
+        return alpha, ((1.0 - alpha) if self.norm_input else None)
+
+    def _synaptic_decay(self):
+        tau = None if self.train_alphas else getattr(self, "tau_syn", None)
+        if isinstance(tau, torch.Tensor):
+            return _DecayFromTau.apply(tau, False)[0]
+        return self.alpha_syn_calculated
+
     def _forward_synaptic(self, x: torch.Tensor, batch: int, trailing):
-        alpha_syn = _flat_param(self.alpha_syn_calculated, trailing, batch, x.device)
+        alpha_syn = _flat_param(self._synaptic_decay(), trailing, batch, x.device)
         return LeakyIntegratorTM.apply(
             x, alpha_syn, self.i_syn.reshape(-1), alpha_syn if self.decay_early else None)
 
     def _forward_membrane(self, i_syn: torch.Tensor, batch: int, trailing):
         dev = i_syn.device
-        alpha_mem = _flat_param(self.alpha_mem_calculated, trailing, batch, dev)
-        scale = (1.0 - alpha_mem) if self.norm_input else None
+        alpha_mem, scale = self._membrane_decay()
+        alpha_mem = _flat_param(alpha_mem, trailing, batch, dev)
+        scale = _flat_param(scale, trailing, batch, dev)
 
         if self.spike_fn is None:
             if self.decay_early:
@@ -216,10 +280,11 @@ class LIF(LIFBase):
         trailing = tuple(trailing_dim)
         self.recordings = dict()
 
-        if self.tau_syn_calculated is not None and self.spike_fn is not None and fused_synaptic_eligible(x):
+        has_synapse = getattr(self, "alpha_syn" if self.train_alphas else "tau_syn", None) is not None
+        if has_synapse and self.spike_fn is not None and fused_synaptic_eligible(x):
             return self._forward_fused_synaptic(x, original_shape)
 
-        if self.tau_syn_calculated is None:
+        if not has_synapse:
             i_syn = x
         else:
             i_syn, i_last = self._forward_synaptic(x, batch_size, trailing)
@@ -234,7 +299,7 @@ class LIF(LIFBase):
         output_full = output.reshape(original_shape)
         # spike count (int64) or, for the non-spiking layer, the sum of the outputs (float64): both come
         # out of the forward kernel, so the reference's `output.sum() / numel` pass is not needed
-        self.firing_rate = count[0].to(torch.float32) / max(output_full.numel(), 1)
+        self._set_rate_source(count, output_full.numel())
         return output_full
 
     def _forward_fused_synaptic(self, x: torch.Tensor, original_shape):
@@ -242,9 +307,10 @@ class LIF(LIFBase):
         batch_size, time_steps, *trailing_dim = original_shape
         trailing = tuple(trailing_dim)
         dev = x.device
-        alpha_syn = _flat_param(self.alpha_syn_calculated, trailing, batch_size, dev)
-        alpha_mem = _flat_param(self.alpha_mem_calculated, trailing, batch_size, dev)
-        scale_mem = (1.0 - alpha_mem) if self.norm_input else None
+        alpha_syn = _flat_param(self._synaptic_decay(), trailing, batch_size, dev)
+        alpha_mem, scale_mem = self._membrane_decay()
+        alpha_mem = _flat_param(alpha_mem, trailing, batch_size, dev)
+        scale_mem = _flat_param(scale_mem, trailing, batch_size, dev)
         threshold = _flat_param(self.spike_threshold, trailing, batch_size, dev)
         min_v_mem = _flat_param(self.min_v_mem, trailing, batch_size, dev)
         if isinstance(self.reset_fn, MembraneReset):
@@ -271,8 +337,29 @@ class LIF(LIFBase):
                 v_rec = torch.where(spikes > 0, c.expand_as(v_pre), v_pre)
             self.recordings["v_mem"] = v_rec.reshape(original_shape)
         output_full = spikes.reshape(original_shape)
-        self.firing_rate = count[0].to(torch.float32) / output_full.numel()
+        self._set_rate_source(count, output_full.numel())
         return output_full
+
+    # ``firing_rate`` (reference ``layers/lif.py:305``: mean of the output) is formed from the total that the
+    # forward kernel leaves on the device, when it is read: two tiny kernels less in every forward call.
+    _rate_source = None
+    _rate_value = None
+
+    def _set_rate_source(self, total: torch.Tensor, numel: int) -> None:
+        self._rate_source = (total, max(int(numel), 1))
+        self._rate_value = None
+
+    @property
+    def firing_rate(self):
+        if self._rate_value is None and self._rate_source is not None:
+            total, numel = self._rate_source
+            self._rate_value = total[0].to(torch.float32) / numel
+        return self._rate_value
+
+    @firing_rate.setter
+    def firing_rate(self, value) -> None:
+        self._rate_source = None
+        self._rate_value = value
 
     def __repr__(self):
         return "EXODUS " + super().__repr__()
