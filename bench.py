@@ -563,7 +563,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=5)
-    ap.add_argument("--e2e-microbatches", type=int, default=8)
+    ap.add_argument("--e2e-microbatches", type=int, default=16)
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the cpu_baseline leg")
     ap.add_argument("--cpu-seconds-reference", type=float, default=120.0, help="budget of --impl reference")
     args = ap.parse_args()
