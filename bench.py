@@ -310,6 +310,52 @@ def cpu_sample(name: str, wl: dict, budget_s: float, steps: int, warmup: int):
     return nts / dt, sample, cores, dt / steps * 1e3
 
 
+def cpu_c_kernels_sample(name: str, wl: dict, budget_s: float):
+    """Second CPU point: the C restatement of the reference's kernel loops (OpenMP over neurons), with the
+    Function glue of the reference in numpy, on an [N,T] sample of the workload.  None for the synaptic
+    workload (the reference has no single Function for it)."""
+    from oracle import oracle as orc
+    kind = wl["kind"]
+    if kind == "lif_syn":
+        return None
+    shape = wl["shape"]
+    T = shape[1]
+    rows_all = shape[0] * int(np.prod(shape[2:]))
+    rng = np.random.default_rng(0)
+
+    def run(rows):
+        if name == "c2":
+            x = (0.4 * rng.poisson(0.1, (rows, T))).astype(np.float32)
+        else:
+            mean, std = {"c1": (0.3, 0.5), "c3": (0.0, 1.0), "c5": (0.25, 0.5)}[name]
+            x = rng.normal(mean, std, (rows, T)).astype(np.float32)
+        go = np.ones((rows, T), np.float32) if name == "c1" else rng.standard_normal((rows, T)).astype(np.float32)
+        z = np.zeros(rows, np.float32)
+        one = np.ones(rows, np.float32)
+        t0 = time.perf_counter()
+        if kind == "expleak":
+            a = np.full(rows, np.exp(-1 / 50.0), np.float32)
+            out = orc.leaky_forward(x, z, a)
+            orc.leaky_integrator_backward(go, out, z, a, True)
+        else:
+            a = one if kind == "iaf" else np.full(rows, np.exp(-1 / 20.0), np.float32)
+            low = np.full(rows, -1.0, np.float32) if kind == "lif" else None
+            surr = {"iaf": lambda v, th: orc.surrogate_heaviside(v, th),
+                    "lif": lambda v, th: orc.surrogate_single_exponential(v, th, 0.5),
+                    "lif5": lambda v, th: orc.surrogate_single_exponential(v, th)}[kind]
+            spikes, v = orc.lif_forward(x, z, a, one, one, low, None)
+            orc.integrate_and_fire_backward(go, np.zeros_like(go), v, spikes, z, a, one, one, low, surr, kind != "iaf")
+        return time.perf_counter() - t0
+
+    rows = min(rows_all, 4096)
+    dt = min(run(rows), run(rows))
+    rows_fit = int(min(rows_all, max(rows, rows * (budget_s / 4.0) / dt)))
+    dt = run(rows_fit)
+    return {"value": rows_fit * T / dt, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
+            "sample": f"C restatement of the reference kernel loops (OpenMP) + numpy Function glue, forward+backward "
+                      f"on {rows_fit} rows x {T} steps of {name} in the reference's [N,T] layout"}
+
+
 # --------------------------------------------------------------------------
 def measured_peak_gbs():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -531,6 +577,10 @@ def run_ours(args, wl):
         if not args.no_cpu:
             v, sample, cores, _ = cpu_sample(name, wl, args.cpu_seconds, 3, 1)
             cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+            try:
+                cpu["c_kernels"] = cpu_c_kernels_sample(name, wl, 6.0)
+            except Exception as exc:      # the checker library is optional for this extra figure
+                cpu["c_kernels"] = {"unavailable": str(exc)[:200]}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
