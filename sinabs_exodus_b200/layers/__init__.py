@@ -1,5 +1,5 @@
-from .lif import LIF, LIFSqueeze
-from .iaf import IAF, IAFSqueeze
-from .exp_leak import ExpLeak, ExpLeakSqueeze
+"""The EXODUS layers: ``LIF`` and the variants derived from it."""
+from .lif import LIF
+from .variants import IAF, ExpLeak, ExpLeakSqueeze, IAFSqueeze, LIFSqueeze
 
 __all__ = ["LIF", "LIFSqueeze", "IAF", "IAFSqueeze", "ExpLeak", "ExpLeakSqueeze"]

@@ -25,11 +25,10 @@ from ..compat.activation import (
     SingleSpike,
 )
 from ..compat.layers import LIF as LIFBase
-from ..compat.layers import SqueezeMixin
 from ..leaky import LeakyIntegratorTM
 from ..spike import IntegrateAndFireTM, LIFSynapticTM, fused_synaptic_eligible
 
-__all__ = ["LIF", "LIFSqueeze"]
+__all__ = ["LIF"]
 
 
 def expand_to_1d_contiguous(value: Union[float, torch.Tensor], shape: Tuple[int]) -> torch.Tensor:
@@ -363,18 +362,3 @@ class LIF(LIFBase):
 
     def __repr__(self):
         return "EXODUS " + super().__repr__()
-
-
-class LIFSqueeze(LIF, SqueezeMixin):
-    """``LIF`` for 4D input (batch*time, channel, height, width)."""
-
-    def __init__(self, batch_size=None, num_timesteps=None, **kwargs):
-        super().__init__(**kwargs)
-        self.squeeze_init(batch_size, num_timesteps)
-
-    def forward(self, input_data: torch.Tensor) -> torch.Tensor:
-        return self.squeeze_forward(input_data, super().forward)
-
-    @property
-    def _param_dict(self) -> dict:
-        return self.squeeze_param_dict(super()._param_dict)
