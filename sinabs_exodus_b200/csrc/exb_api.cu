@@ -47,6 +47,8 @@ int check_geometry(int64_t B, int64_t T, int64_t M, int layout)
     if (layout != EXB_LAYOUT_NT && layout != EXB_LAYOUT_BTM) return fail(EXB_ERR_ARG, "unknown layout %d", layout);
     // Kernel grids are 1-D in units of 128..1024 neurons; keep far away from 2^31 blocks.
     if (B > 0 && M > 0 && (double)B * (double)M > 1.0e11) return fail(EXB_ERR_ARG, "B*M too large");
+    // Time steps are counted in int inside the kernels (2^31 steps of one neuron would be 8.6 GB per tensor).
+    if (T > 0x7fffffffll - 64) return fail(EXB_ERR_ARG, "T too large (%lld)", (long long)T);
     return EXB_OK;
 }
 

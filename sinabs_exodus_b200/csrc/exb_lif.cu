@@ -377,6 +377,7 @@ __global__ void __launch_bounds__(NT_WARPS * 32) lif_bwd_nt_kernel(const LifBwdA
 
 }  // namespace exb
 #include "exb_lif_nt.cuh"
+#include "exb_ring.cuh"
 namespace exb {
 
 // ===========================================================================
@@ -390,6 +391,28 @@ static inline bool can_vec4(int64_t M, std::initializer_list<const void *> ptrs)
     return true;
 }
 
+static inline bool can_vec2(int64_t M, std::initializer_list<const void *> ptrs)
+{
+    if (M % 2) return false;
+    for (const void *p : ptrs)
+        if (p && (reinterpret_cast<uintptr_t>(p) & 7u)) return false;
+    return true;
+}
+
+template <int V, typename K, typename Args>
+static cudaError_t launch_ring(K kern, const Args &a, int ntensors, cudaStream_t s)
+{
+    const int ng = ring_groups<V>(ntensors);
+    const size_t sm = ring_smem_bytes<V>(ntensors, ng);
+    if (sm > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+        if (e != cudaSuccess) return e;
+    }
+    const int64_t total = a.B * (a.M / V);
+    kern<<<(unsigned)((total + RING_THREADS - 1) / RING_THREADS), RING_THREADS, sm, s>>>(a, ng);
+    return cudaSuccess;
+}
+
 template <int RESET>
 static cudaError_t launch_fwd_t(const LifFwdArgs &a, int layout, cudaStream_t s)
 {
@@ -397,9 +420,12 @@ static cudaError_t launch_fwd_t(const LifFwdArgs &a, int layout, cudaStream_t s)
         if (can_vec4(a.M, {a.spikes, a.v_mem, a.input})) {
             const int64_t total = a.B * (a.M / 4);
             lif_fwd_btm_kernel<4, RESET, 4><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+        } else if (can_vec2(a.M, {a.spikes, a.v_mem, a.input})) {
+            cudaError_t e = launch_ring<2>(lif_fwd_btm_ring_kernel<2, RESET>, a, 1, s);
+            if (e != cudaSuccess) return e;
         } else {
-            const int64_t total = a.B * a.M;
-            lif_fwd_btm_kernel<1, RESET, 8><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+            cudaError_t e = launch_ring<1>(lif_fwd_btm_ring_kernel<1, RESET>, a, 1, s);
+            if (e != cudaSuccess) return e;
         }
     } else {
         const int64_t N = a.B * a.M;
@@ -436,8 +462,11 @@ static cudaError_t launch_bwd_t(const LifBwdArgs &a, int layout, cudaStream_t s)
             const int64_t total = a.B * (a.M / 4);
             lif_bwd_btm_kernel<4, SURR, RESET, WA, WS, 2><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
         } else {
-            const int64_t total = a.B * a.M;
-            lif_bwd_btm_kernel<1, SURR, RESET, WA, WS, 4><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+            const int nt = 2 + (a.gv ? 1 : 0) + (SURR == EXB_SURR_GENERIC ? 1 : 0) + (WS == SCALE_GRAD_FROM_INPUT ? 1 : 0);
+            cudaError_t e = can_vec2(a.M, {a.grad_input, a.go, a.gv, a.v_mem, a.surr, a.input})
+                                ? launch_ring<2>(lif_bwd_btm_ring_kernel<2, SURR, RESET, WA, WS>, a, nt, s)
+                                : launch_ring<1>(lif_bwd_btm_ring_kernel<1, SURR, RESET, WA, WS>, a, nt, s);
+            if (e != cudaSuccess) return e;
         }
     } else {
         const int64_t N = a.B * a.M;

@@ -16,6 +16,7 @@ TOL = 1e-5
 
 # the last two are wide enough (B * ceil(M/512) >= 296) for the 512-neuron TMA tiles
 SHAPES = [(1, 1, 1), (2, 3, 5), (3, 33, 37), (2, 64, 128), (1, 100, 257), (4, 31, 32), (2, 130, 36), (5, 7, 4),
+          (3, 50, 38), (4, 70, 6),            # M even but not a multiple of 4: two neurons per thread, 8-byte copies
           (300, 9, 516), (150, 21, 1024)]
 
 
