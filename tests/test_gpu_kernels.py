@@ -77,7 +77,8 @@ def _surrogates():
 
 
 @pytest.mark.parametrize("layout", [0, 1])
-@pytest.mark.parametrize("B,T,M", [(2, 3, 5), (3, 33, 37), (2, 64, 128), (1, 100, 257), (4, 31, 32), (1, 1, 3), (300, 9, 516)])
+@pytest.mark.parametrize("B,T,M", [(2, 3, 5), (3, 33, 37), (2, 64, 128), (1, 100, 257), (4, 31, 32), (1, 1, 3), (300, 9, 516),
+                                   (3, 50, 38), (2, 45, 6)])
 @pytest.mark.parametrize("surr_idx", [0, 1, 2, 3])
 def test_lif_backward_parity(layout, B, T, M, surr_idx):
     from tests import _gpu
@@ -172,7 +173,7 @@ def test_in_scale_and_state_gradient(layout):
         assert rel_err(gs2, (R64 * cs["inp"].astype(np.float64)).sum(1)) < TOL
 
 
-@pytest.mark.parametrize("B,T,M", [(3, 40, 20), (300, 9, 516)])
+@pytest.mark.parametrize("B,T,M", [(3, 40, 20), (300, 9, 516), (3, 40, 21), (2, 37, 22)])
 def test_backward_all_five_streams(B, T, M):
     """Time-major backward with every optional tensor streamed at once: grad_v_mem, a caller-computed
     surrogate, and the forward input for the scale gradient (narrow and wide TMA tiles)."""
