@@ -358,6 +358,10 @@ static inline bool all_aligned16(std::initializer_list<const void *> ptrs)
     return true;
 }
 
+}  // namespace exb
+#include "exb_ring.cuh"
+namespace exb {
+
 cudaError_t launch_leaky_forward(const LeakyFwdArgs &a, int layout, cudaStream_t s)
 {
     if (layout == EXB_LAYOUT_BTM && tma_enabled()) {
@@ -370,8 +374,9 @@ cudaError_t launch_leaky_forward(const LeakyFwdArgs &a, int layout, cudaStream_t
             const int64_t total = a.B * (a.M / 4);
             leaky_fwd_btm_kernel<4, 4><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
         } else {
-            const int64_t total = a.B * a.M;
-            leaky_fwd_btm_kernel<1, 8><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+            cudaError_t e = can_vec2(a.M, {a.out, a.input}) ? launch_ring<2>(leaky_fwd_btm_ring_kernel<2>, a, 1, s)
+                                                            : launch_ring<1>(leaky_fwd_btm_ring_kernel<1>, a, 1, s);
+            if (e != cudaSuccess) return e;
         }
     } else {
         const int64_t N = a.B * a.M;
@@ -392,8 +397,11 @@ static cudaError_t launch_leaky_bwd_t(const LeakyBwdArgs &a, int layout, cudaStr
             const int64_t total = a.B * (a.M / 4);
             leaky_bwd_btm_kernel<4, WA, WS, 4><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
         } else {
-            const int64_t total = a.B * a.M;
-            leaky_bwd_btm_kernel<1, WA, WS, 8><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+            const int nt = 1 + (WA ? 1 : 0) + (WS ? 1 : 0);
+            cudaError_t e = can_vec2(a.M, {a.grad_input, a.go, a.out, a.input})
+                                ? launch_ring<2>(leaky_bwd_btm_ring_kernel<2, WA, WS>, a, nt, s)
+                                : launch_ring<1>(leaky_bwd_btm_ring_kernel<1, WA, WS>, a, nt, s);
+            if (e != cudaSuccess) return e;
         }
     } else {
         const int64_t N = a.B * a.M;

@@ -391,28 +391,6 @@ static inline bool can_vec4(int64_t M, std::initializer_list<const void *> ptrs)
     return true;
 }
 
-static inline bool can_vec2(int64_t M, std::initializer_list<const void *> ptrs)
-{
-    if (M % 2) return false;
-    for (const void *p : ptrs)
-        if (p && (reinterpret_cast<uintptr_t>(p) & 7u)) return false;
-    return true;
-}
-
-template <int V, typename K, typename Args>
-static cudaError_t launch_ring(K kern, const Args &a, int ntensors, cudaStream_t s)
-{
-    const int ng = ring_groups<V>(ntensors);
-    const size_t sm = ring_smem_bytes<V>(ntensors, ng);
-    if (sm > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-        if (e != cudaSuccess) return e;
-    }
-    const int64_t total = a.B * (a.M / V);
-    kern<<<(unsigned)((total + RING_THREADS - 1) / RING_THREADS), RING_THREADS, sm, s>>>(a, ng);
-    return cudaSuccess;
-}
-
 template <int RESET>
 static cudaError_t launch_fwd_t(const LifFwdArgs &a, int layout, cudaStream_t s)
 {

@@ -12,6 +12,8 @@
 // flight per SM.
 #pragma once
 
+#include <initializer_list>
+
 namespace exb {
 
 constexpr int RING_G = 4;                    // time steps per commit group
@@ -246,6 +248,158 @@ __global__ void __launch_bounds__(RING_THREADS, 4) lif_bwd_btm_ring_kernel(const
     }
 }
 
+// ===========================================================================
+// leaky integrator, same pipelines
+// ===========================================================================
+template <int V>
+__global__ void __launch_bounds__(RING_THREADS, 4) leaky_fwd_btm_ring_kernel(const LeakyFwdArgs A, const int ng)
+{
+    extern __shared__ __align__(16) float ring_smem[];
+    const int64_t MV = A.M / V;
+    const int64_t total = A.B * MV;
+    int64_t gid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    const bool valid = gid < total;
+    if (!valid) gid = total - 1;   // keeps the warp whole for the final reduction; stores are skipped
+    const int64_t b = gid / MV;
+    const int64_t m = (gid - b * MV) * V;
+    const int64_t n = b * A.M + m;
+    const int64_t M = A.M;
+    const int Ti = (int)A.T;
+    float al[V], sc[V], v[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        al[j] = A.alpha.get(b, m + j, 1.0f);
+        sc[j] = A.scale.get(b, m + j, 1.0f);
+        v[j] = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
+    }
+    const int64_t base = (b * A.T) * M + m;
+    float *out = A.out + base;
+    float *mine = ring_smem + threadIdx.x * V;
+    const int mask = RING_G * ng - 1;
+    double total_out = 0.0;
+
+    int t_issue = 0;
+    const float *p_issue = A.input + base;
+    auto issue = [&]() {
+#pragma unroll
+        for (int u = 0; u < RING_G; ++u) {
+            if (t_issue < Ti) ring_copy<4 * V>(ring_slot<V>(mine, t_issue, mask), p_issue);
+            ++t_issue;
+            p_issue += M;
+        }
+        ring_commit();
+    };
+    for (int g = 0; g < ng - 1; ++g) issue();
+    for (int t0 = 0; t0 < Ti; t0 += RING_G) {
+        issue();
+        ring_wait(ng);
+        float part = 0.0f;
+#pragma unroll
+        for (int u = 0; u < RING_G; ++u) {
+            const int t = t0 + u;
+            if (t < Ti) {
+                float xs[V];
+                lds_small<V>(xs, ring_slot<V>(mine, t, mask));
+#pragma unroll
+                for (int j = 0; j < V; ++j) {
+                    v[j] = __fmaf_rn(v[j], al[j], __fmul_rn(sc[j], xs[j]));
+                    part += v[j];
+                }
+                if (valid) stv<V>(out, v);
+                out += M;
+            }
+        }
+        total_out += (double)part;
+    }
+    if (A.v_last && valid) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) A.v_last[n + j] = v[j];
+    }
+    if (A.out_sum) warp_add_f64(A.out_sum, valid ? total_out : 0.0, threadIdx.x & 31);
+}
+
+template <int V, bool WA, bool WS>
+__global__ void __launch_bounds__(RING_THREADS, 4) leaky_bwd_btm_ring_kernel(const LeakyBwdArgs A, const int ng)
+{
+    extern __shared__ __align__(16) float ring_smem[];
+    const int64_t MV = A.M / V;
+    const int64_t gid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (gid >= A.B * MV) return;
+    const int64_t b = gid / MV;
+    const int64_t m = (gid - b * MV) * V;
+    const int64_t n = b * A.M + m;
+    const int64_t T = A.T, M = A.M;
+    const int Ti = (int)T;
+    float al[V], sc[V], G[V], ag[V], sg[V], glast[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        al[j] = A.alpha.get(b, m + j, 1.0f);
+        sc[j] = A.scale.get(b, m + j, 1.0f);
+        G[j] = 0.0f; ag[j] = 0.0f; sg[j] = 0.0f;
+        glast[j] = A.g_last ? __ldg(A.g_last + n + j) : 0.0f;
+    }
+    const int64_t base = (b * T) * M + m;
+    const float *go = A.go + base;
+    const float *vo = WA ? A.out + base : nullptr;
+    const float *xin = WS ? A.input + base : nullptr;
+    float *gi = A.grad_input + base + (T - 1) * M;
+
+    const int mask = RING_G * ng - 1;
+    const int TENSOR = RING_G * ng * RING_THREADS * V;
+    float *r_go = ring_smem + threadIdx.x * V;
+    float *r_vo = r_go + TENSOR;
+    float *r_xi = r_vo + (WA ? TENSOR : 0);
+
+    int p_issue = 0;
+    int64_t off_issue = (T - 1) * M;
+    auto issue = [&]() {
+#pragma unroll
+        for (int u = 0; u < RING_G; ++u) {
+            if (p_issue < Ti) {
+                ring_copy<4 * V>(ring_slot<V>(r_go, p_issue, mask), go + off_issue);
+                if (WA) ring_copy<4 * V>(ring_slot<V>(r_vo, p_issue, mask), vo + off_issue);
+                if (WS) ring_copy<4 * V>(ring_slot<V>(r_xi, p_issue, mask), xin + off_issue);
+            }
+            ++p_issue;
+            off_issue -= M;
+        }
+        ring_commit();
+    };
+    for (int g = 0; g < ng - 1; ++g) issue();
+    for (int p0 = 0; p0 < Ti; p0 += RING_G) {
+        issue();
+        ring_wait(ng);
+#pragma unroll
+        for (int u = 0; u < RING_G; ++u) {
+            const int p = p0 + u;
+            if (p < Ti) {
+                float xgo[V];
+                float xo[V] = {}, xx[V] = {};
+                lds_small<V>(xgo, ring_slot<V>(r_go, p, mask));
+                if (WA) lds_small<V>(xo, ring_slot<V>(r_vo, p, mask));
+                if (WS) lds_small<V>(xx, ring_slot<V>(r_xi, p, mask));
+                float r[V];
+#pragma unroll
+                for (int j = 0; j < V; ++j) {
+                    if (p == 0) xgo[j] = __fadd_rn(xgo[j], glast[j]);
+                    if (WA) ag[j] = __fmaf_rn(G[j], xo[j], ag[j]);      // G_{t+1} * v_t
+                    G[j] = __fmaf_rn(G[j], al[j], xgo[j]);
+                    if (WS) sg[j] = __fmaf_rn(G[j], xx[j], sg[j]);
+                    r[j] = __fmul_rn(sc[j], G[j]);
+                }
+                stv<V>(gi, r);
+                gi -= M;
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        if (A.grad_init) A.grad_init[n + j] = __fmul_rn(al[j], G[j]);
+        if (WA) A.grad_alpha[n + j] = __fmaf_rn(G[j], A.v_init ? __ldg(A.v_init + n + j) : 0.0f, ag[j]);
+        if (WS) A.grad_scale[n + j] = sg[j];
+    }
+}
+
 // Groups per ring such that the rings of `ntensors` tensors take at most 64 KB per CTA.
 template <int V>
 static inline int ring_groups(int ntensors)
@@ -258,6 +412,28 @@ template <int V>
 static inline size_t ring_smem_bytes(int ntensors, int ng)
 {
     return (size_t)ntensors * RING_G * ng * RING_THREADS * V * sizeof(float);
+}
+
+static inline bool can_vec2(int64_t M, std::initializer_list<const void *> ptrs)
+{
+    if (M % 2) return false;
+    for (const void *p : ptrs)
+        if (p && (reinterpret_cast<uintptr_t>(p) & 7u)) return false;
+    return true;
+}
+
+template <int V, typename K, typename Args>
+static cudaError_t launch_ring(K kern, const Args &a, int ntensors, cudaStream_t s)
+{
+    const int ng = ring_groups<V>(ntensors);
+    const size_t sm = ring_smem_bytes<V>(ntensors, ng);
+    if (sm > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+        if (e != cudaSuccess) return e;
+    }
+    const int64_t total = a.B * (a.M / V);
+    kern<<<(unsigned)((total + RING_THREADS - 1) / RING_THREADS), RING_THREADS, sm, s>>>(a, ng);
+    return cudaSuccess;
 }
 
 }  // namespace exb

@@ -238,6 +238,7 @@ def test_reset_to_value_vs_bptt(layout):
 
 
 LEAKY_SHAPES = [(1, 1, 1), (2, 3, 5), (3, 33, 37), (2, 64, 128), (1, 300, 7), (2, 129, 4), (1, 1000, 3), (4, 128, 8),
+                (3, 60, 6), (2, 41, 38),             # M even, not a multiple of 4: two neurons per thread
                 (300, 11, 516), (140, 7, 644)]   # last two: 512-neuron and 128-neuron TMA tiles
 
 
