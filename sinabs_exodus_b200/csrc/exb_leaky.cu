@@ -3,8 +3,9 @@
 //     backward  G_t = alpha*G_{t+1} + grad_out_t,  grad_in_t = scale*G_t
 //               d/d alpha = sum_t G_t*v_{t-1},     d/d scale = sum_t G_t*in_t
 //
-// Time-major (B,T,M): one thread owns V adjacent neurons and walks through
-// time with the state in registers.
+// This file: the [N,T]-layout kernels and the launchers of both layouts.  The
+// time-major (B,T,M) kernels are in exb_tma_kernels.cu (TMA-staged, incl. the
+// time-parallel scan) and exb_ring.cuh (cp.async rings).
 //
 // [N,T]: the recurrence is linear, so one warp owns one neuron row and scans
 // it 32*E time steps at a time: every lane integrates E consecutive steps,
@@ -14,138 +15,6 @@
 #include "exb_kernels.cuh"
 
 namespace exb {
-
-// ===========================================================================
-// time-major
-// ===========================================================================
-template <int V, int U>
-__global__ void __launch_bounds__(256) leaky_fwd_btm_kernel(const LeakyFwdArgs A)
-{
-    const int64_t MV = A.M / V;
-    int64_t gid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-    const bool valid = gid < A.B * MV;
-    if (!valid) {
-        if (!A.out_sum) return;
-        gid = A.B * MV - 1;   // keeps the warp whole for the final reduction; stores are skipped
-    }
-    const int64_t b = gid / MV;
-    const int64_t m = (gid - b * MV) * V;
-    const int64_t n = b * A.M + m;
-    const int64_t T = A.T, M = A.M;
-    double total = 0.0;
-    float al[V], sc[V], v[V];
-#pragma unroll
-    for (int j = 0; j < V; ++j) {
-        al[j] = A.alpha.get(b, m + j, 1.0f);
-        sc[j] = A.scale.get(b, m + j, 1.0f);
-        v[j] = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
-    }
-    const int64_t base = (b * T) * M + m;
-    const float *in = A.input + base;
-    float *out = A.out + base;
-
-    float xc[U][V], xn[U][V];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-#pragma unroll
-        for (int j = 0; j < V; ++j) { xc[u][j] = 0.0f; xn[u][j] = 0.0f; }
-        if (u < T) ldv<V>(xc[u], in + u * M);
-    }
-    for (int64_t t = 0; t < T; t += U) {
-        float part = 0.0f;
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int64_t tt = t + U + u;
-            if (tt < T) ldv<V>(xn[u], in + tt * M);
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int64_t tt = t + u;
-            if (tt < T) {
-#pragma unroll
-                for (int j = 0; j < V; ++j) {
-                    v[j] = __fmaf_rn(v[j], al[j], __fmul_rn(sc[j], xc[u][j]));
-                    part += v[j];
-                }
-                if (valid) stv<V>(out + tt * M, v);
-            }
-        }
-        total += (double)part;
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-#pragma unroll
-            for (int j = 0; j < V; ++j) xc[u][j] = xn[u][j];
-    }
-    if (A.v_last && valid) {
-#pragma unroll
-        for (int j = 0; j < V; ++j) A.v_last[n + j] = v[j];
-    }
-    if (A.out_sum) warp_add_f64(A.out_sum, valid ? total : 0.0, threadIdx.x & 31);
-}
-
-template <int V, bool WA, bool WS, int U>
-__global__ void __launch_bounds__(256) leaky_bwd_btm_kernel(const LeakyBwdArgs A)
-{
-    const int64_t MV = A.M / V;
-    const int64_t gid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-    if (gid >= A.B * MV) return;
-    const int64_t b = gid / MV;
-    const int64_t m = (gid - b * MV) * V;
-    const int64_t n = b * A.M + m;
-    const int64_t T = A.T, M = A.M;
-    float al[V], sc[V], G[V], ag[V], sg[V];
-#pragma unroll
-    for (int j = 0; j < V; ++j) {
-        al[j] = A.alpha.get(b, m + j, 1.0f);
-        sc[j] = A.scale.get(b, m + j, 1.0f);
-        G[j] = 0.0f; ag[j] = 0.0f; sg[j] = 0.0f;
-    }
-    const int64_t base = (b * T) * M + m;
-    const float *go = A.go + base;
-    const float *vo = WA ? A.out + base : nullptr;
-    const float *xin = WS ? A.input + base : nullptr;
-    float *gi = A.grad_input + base;
-
-    for (int64_t t = T - 1; t >= 0; t -= U) {
-        float rgo[U][V], ro[U][V], rx[U][V];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int64_t tt = t - u;
-#pragma unroll
-            for (int j = 0; j < V; ++j) { rgo[u][j] = 0.0f; ro[u][j] = 0.0f; rx[u][j] = 0.0f; }
-            if (tt >= 0) {
-                ldv<V>(rgo[u], go + tt * M);
-                if (WA) ldv<V>(ro[u], vo + tt * M);
-                if (WS) ldv<V>(rx[u], xin + tt * M);
-            }
-        }
-        if (t == T - 1 && A.g_last) {
-#pragma unroll
-            for (int j = 0; j < V; ++j) rgo[0][j] = __fadd_rn(rgo[0][j], __ldg(A.g_last + n + j));
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int64_t tt = t - u;
-            if (tt >= 0) {
-                float r[V];
-#pragma unroll
-                for (int j = 0; j < V; ++j) {
-                    if (WA) ag[j] = __fmaf_rn(G[j], ro[u][j], ag[j]);      // G_{t+1} * v_t
-                    G[j] = __fmaf_rn(G[j], al[j], rgo[u][j]);
-                    if (WS) sg[j] = __fmaf_rn(G[j], rx[u][j], sg[j]);
-                    r[j] = __fmul_rn(sc[j], G[j]);
-                }
-                stv<V>(gi + tt * M, r);
-            }
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < V; ++j) {
-        if (A.grad_init) A.grad_init[n + j] = __fmul_rn(al[j], G[j]);
-        if (WA) A.grad_alpha[n + j] = __fmaf_rn(G[j], A.v_init ? __ldg(A.v_init + n + j) : 0.0f, ag[j]);
-        if (WS) A.grad_scale[n + j] = sg[j];
-    }
-}
 
 // ===========================================================================
 // [N,T]: warp-shuffle scan over time
@@ -371,8 +240,8 @@ cudaError_t launch_leaky_forward(const LeakyFwdArgs &a, int layout, cudaStream_t
     }
     if (layout == EXB_LAYOUT_BTM) {
         if (a.M % 4 == 0 && all_aligned16({a.out, a.input})) {
-            const int64_t total = a.B * (a.M / 4);
-            leaky_fwd_btm_kernel<4, 4><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+            cudaError_t e = launch_ring<4>(leaky_fwd_btm_ring_kernel<4>, a, 1, s);
+            if (e != cudaSuccess) return e;
         } else {
             cudaError_t e = can_vec2(a.M, {a.out, a.input}) ? launch_ring<2>(leaky_fwd_btm_ring_kernel<2>, a, 1, s)
                                                             : launch_ring<1>(leaky_fwd_btm_ring_kernel<1>, a, 1, s);
@@ -394,8 +263,8 @@ static cudaError_t launch_leaky_bwd_t(const LeakyBwdArgs &a, int layout, cudaStr
 {
     if (layout == EXB_LAYOUT_BTM) {
         if (a.M % 4 == 0 && all_aligned16({a.grad_input, a.go, a.out, a.input})) {
-            const int64_t total = a.B * (a.M / 4);
-            leaky_bwd_btm_kernel<4, WA, WS, 4><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+            cudaError_t e = launch_ring<4>(leaky_bwd_btm_ring_kernel<4, WA, WS>, a, 1 + (WA ? 1 : 0) + (WS ? 1 : 0), s);
+            if (e != cudaSuccess) return e;
         } else {
             const int nt = 1 + (WA ? 1 : 0) + (WS ? 1 : 0);
             cudaError_t e = can_vec2(a.M, {a.grad_input, a.go, a.out, a.input})

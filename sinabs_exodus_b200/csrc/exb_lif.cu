@@ -1,171 +1,18 @@
 // Spiking-neuron kernels: forward spike scan and fused reverse-time EXODUS
-// backward, for the time-major (B,T,M) layout and for the [N,T] layout.
+// backward.  This file holds the [N,T]-layout kernels and the launchers of both
+// layouts; the time-major (B,T,M) kernels are in exb_tma_*.cu (TMA-staged) and
+// exb_ring.cuh (cp.async rings, for shapes a TMA box cannot describe).
 //
-// Time-major kernels: one thread owns V (4 or 1) adjacent neurons of one batch
-// item and walks through time; at every step a warp touches one contiguous
-// 128*V-byte span per tensor.  The membrane state, spike count and all
-// gradients accumulators live in registers for the whole sweep.
+// In every kernel one thread owns a neuron (or a few adjacent ones) and walks
+// through time; the membrane state, spike count and all gradient accumulators
+// live in registers for the whole sweep.
 //
 // [N,T] kernels: one warp owns 32 neurons; 32x32 tiles are moved between
-// global memory (coalesced along time) and shared memory (padded, read along
-// neurons), so the same per-thread sweep runs on a transposed tile.
+// global memory (coalesced along time) and shared memory (read along neurons),
+// so the same per-thread sweep runs on a transposed tile.
 #include "exb_kernels.cuh"
 
 namespace exb {
-
-// ===========================================================================
-// time-major forward
-// ===========================================================================
-template <int V, int RESET, int U>
-__global__ void __launch_bounds__(256) lif_fwd_btm_kernel(const LifFwdArgs A)
-{
-    const int64_t MV = A.M / V;
-    const int64_t total = A.B * MV;
-    int64_t gid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-    const bool valid = gid < total;
-    if (!valid) gid = total - 1;   // keeps the warp whole for the final reduction; stores are skipped
-    const int64_t b = gid / MV;
-    const int64_t m = (gid - b * MV) * V;
-    const int64_t n = b * A.M + m;
-
-    const SpikeCfg cfg = make_spike_cfg(A.maxs);
-    Neuron q[V];
-    float v[V], af[V];
-#pragma unroll
-    for (int j = 0; j < V; ++j) {
-        q[j] = A.np.load(b, m + j, cfg);
-        v[j] = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
-        af[j] = 0.0f;
-    }
-    const int64_t base = (b * A.T) * A.M + m;
-    const float *in = A.input + base;
-    float *sp = A.spikes + base;
-    float *vm = A.v_mem + base;
-    const int64_t T = A.T, M = A.M;
-    SpikeTotal cnt;
-    cnt.c32 = 0u; cnt.c64 = 0ull;
-
-    float xc[U][V], xn[U][V];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-#pragma unroll
-        for (int j = 0; j < V; ++j) { xc[u][j] = 0.0f; xn[u][j] = 0.0f; }
-        if (u < T) ldv<V>(xc[u], in + u * M);
-    }
-    for (int64_t t = 0; t < T; t += U) {
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int64_t tt = t + U + u;
-            if (tt < T) ldv<V>(xn[u], in + tt * M);
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int64_t tt = t + u;
-            if (tt < T) {
-                lif_step_vec<RESET, V, V>(v, af, xc[u], q, cfg, cnt);
-                if (valid) {
-                    stv<V>(sp + tt * M, af);
-                    stv<V>(vm + tt * M, v);
-                }
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-#pragma unroll
-            for (int j = 0; j < V; ++j) xc[u][j] = xn[u][j];
-    }
-    if (A.v_post_last && valid) {
-#pragma unroll
-        for (int j = 0; j < V; ++j) A.v_post_last[n + j] = post_reset<RESET>(v[j], af[j], q[j]);
-    }
-    if (A.spike_count) {
-        const unsigned long long tot = warp_sum_u64(valid ? cnt.total(cfg) : 0ull);
-        if ((threadIdx.x & 31) == 0 && tot) atomicAdd(A.spike_count, tot);
-    }
-}
-
-// ===========================================================================
-// time-major backward
-// ===========================================================================
-template <int V, int SURR, int RESET, bool WA, int WS, int U>
-__global__ void __launch_bounds__(256) lif_bwd_btm_kernel(const LifBwdArgs A)
-{
-    const int64_t MV = A.M / V;
-    const int64_t total = A.B * MV;
-    const int64_t gid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-    if (gid >= total) return;
-    const int64_t b = gid / MV;
-    const int64_t m = (gid - b * MV) * V;
-    const int64_t n = b * A.M + m;
-    const int64_t T = A.T, M = A.M;
-
-    const SpikeCfg cfg = make_spike_cfg(A.maxs);
-    Neuron q[V];
-    SurrConst sc[V];
-    float cp[V];
-    BwdState st[V];
-    float Rprev[V], f0[V];
-    bool n0[V];
-#pragma unroll
-    for (int j = 0; j < V; ++j) {
-        q[j] = A.np.load(b, m + j, cfg);
-        sc[j] = surr_prepare<SURR>(q[j], A.p0, A.p1);
-        cp[j] = __fmul_rn(q[j].alpha, q[j].c);
-        st[j].R = 0.0f; st[j].ag = 0.0f; st[j].sg = 0.0f; st[j].vnext = 0.0f;
-        Rprev[j] = 0.0f; f0[j] = 0.0f; n0[j] = true;
-    }
-    const int64_t base = (b * T) * M + m;
-    const float *go = A.go + base;
-    const float *vm = A.v_mem + base;
-    const float *gv = A.gv ? A.gv + base : nullptr;
-    const float *sl = (SURR == EXB_SURR_GENERIC) ? A.surr + base : nullptr;
-    const float *xin = (WS == SCALE_GRAD_FROM_INPUT) ? A.input + base : nullptr;
-    float *gi = A.grad_input + base;
-
-    for (int64_t t = T - 1; t >= 0; t -= U) {
-        float rgo[U][V], rv[U][V], rgv[U][V], rsl[U][V], rx[U][V];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int64_t tt = t - u;
-#pragma unroll
-            for (int j = 0; j < V; ++j) { rgv[u][j] = 0.0f; rsl[u][j] = 0.0f; rx[u][j] = 0.0f; rgo[u][j] = 0.0f; rv[u][j] = 0.0f; }
-            if (tt >= 0) {
-                ldv<V>(rgo[u], go + tt * M);
-                ldv<V>(rv[u], vm + tt * M);
-                if (gv) ldv<V>(rgv[u], gv + tt * M);
-                if (SURR == EXB_SURR_GENERIC) ldv<V>(rsl[u], sl + tt * M);
-                if (WS == SCALE_GRAD_FROM_INPUT) ldv<V>(rx[u], xin + tt * M);
-            }
-        }
-        if (t == T - 1 && A.g_last) {
-#pragma unroll
-            for (int j = 0; j < V; ++j)
-                fold_last_state_grad<RESET>(rgo[0][j], rgv[0][j], __ldg(A.g_last + n + j), rv[0][j], q[j], cfg);
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int64_t tt = t - u;
-            if (tt >= 0) {
-                float r[V];
-#pragma unroll
-                for (int j = 0; j < V; ++j) {
-                    Rprev[j] = st[j].R;
-                    const float Rt = lif_bwd_step<SURR, RESET, WA, WS>(st[j], rv[u][j], rgo[u][j], rgv[u][j], rsl[u][j],
-                                                                      rx[u][j], q[j], sc[j], cp[j], cfg, f0[j], n0[j]);
-                    r[j] = __fmul_rn(q[j].scale, Rt);
-                }
-                stv<V>(gi + tt * M, r);
-            }
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < V; ++j) {
-        if (A.grad_init) A.grad_init[n + j] = __fmul_rn(q[j].alpha, st[j].R);
-        const float vi = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
-        if (WA) A.grad_alpha[n + j] = alpha_grad_finish<RESET>(st[j], vi, Rprev[j], f0[j], n0[j]);
-        if (WS) A.grad_scale[n + j] = scale_grad_finish<WS>(st[j], vi, q[j]);
-    }
-}
 
 // ===========================================================================
 // [N,T] layout: warp-private tiles of 32 rows (neurons) x 32 time steps, padded to 33 columns
@@ -396,8 +243,8 @@ static cudaError_t launch_fwd_t(const LifFwdArgs &a, int layout, cudaStream_t s)
 {
     if (layout == EXB_LAYOUT_BTM) {
         if (can_vec4(a.M, {a.spikes, a.v_mem, a.input})) {
-            const int64_t total = a.B * (a.M / 4);
-            lif_fwd_btm_kernel<4, RESET, 4><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+            cudaError_t e = launch_ring<4>(lif_fwd_btm_ring_kernel<4, RESET>, a, 1, s);
+            if (e != cudaSuccess) return e;
         } else if (can_vec2(a.M, {a.spikes, a.v_mem, a.input})) {
             cudaError_t e = launch_ring<2>(lif_fwd_btm_ring_kernel<2, RESET>, a, 1, s);
             if (e != cudaSuccess) return e;
@@ -437,8 +284,9 @@ static cudaError_t launch_bwd_t(const LifBwdArgs &a, int layout, cudaStream_t s)
 {
     if (layout == EXB_LAYOUT_BTM) {
         if (can_vec4(a.M, {a.grad_input, a.go, a.gv, a.v_mem, a.surr, a.input})) {
-            const int64_t total = a.B * (a.M / 4);
-            lif_bwd_btm_kernel<4, SURR, RESET, WA, WS, 2><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+            const int nt4 = 2 + (a.gv ? 1 : 0) + (SURR == EXB_SURR_GENERIC ? 1 : 0) + (WS == SCALE_GRAD_FROM_INPUT ? 1 : 0);
+            cudaError_t e = launch_ring<4>(lif_bwd_btm_ring_kernel<4, SURR, RESET, WA, WS>, a, nt4, s);
+            if (e != cudaSuccess) return e;
         } else {
             const int nt = 2 + (a.gv ? 1 : 0) + (SURR == EXB_SURR_GENERIC ? 1 : 0) + (WS == SCALE_GRAD_FROM_INPUT ? 1 : 0);
             cudaError_t e = can_vec2(a.M, {a.grad_input, a.go, a.gv, a.v_mem, a.surr, a.input})
