@@ -182,17 +182,41 @@ static int env_int(const char *name, int dflt)
     return (v && *v) ? atoi(v) : dflt;
 }
 
-static PipeCfg pipe_cfg(int w, int nmaps)  // w: neurons per tile (512, 256 or 128)
+static int sm_count()
+{
+    static const int n = []() {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+            return 148;
+        return v;
+    }();
+    return n;
+}
+
+// w: neurons per tile (512 or 128); nmaps: tensors streamed per stage; ctas: grid size.
+static PipeCfg pipe_cfg(int w, int nmaps, int64_t ctas)
 {
     static const int env_tc = env_int("EXB_TMA_TC", 0);
     static const int env_st = env_int("EXB_TMA_STAGES", 0);
     PipeCfg pc;
-    // target ~8 KB per stage across all streamed tensors
-    int tc = (8 * 1024) / (w * 4 * nmaps);
+    pc.stages = 4;
+    // ~8 KB per stage for one streamed tensor, ~16 KB for several (the backward kernels): with two
+    // tensors in 8 KB a wide stage holds only 2 time steps and the per-chunk work (barrier wait,
+    // release, loop set-up) weighs on every step.  Measured: c2 backward 0.682 -> 0.657 ms, c3 step
+    // 0.467 -> 0.445 ms.
+    int target = (nmaps >= 2) ? 16 * 1024 : 8 * 1024;
+    // A grid of a few CTAs per SM should be resident at once: a second, short wave costs more than
+    // longer stages gain (c4: 1024 CTAs, 7 per SM; with 3 resident the step took 0.60 instead of 0.53 ms).
+    const int64_t per_sm = (ctas + sm_count() - 1) / sm_count();
+    if (per_sm >= 1 && per_sm <= 8) {
+        const int budget = (224 * 1024) / (int)per_sm - 1280;      // shared memory of one CTA, ring bookkeeping off
+        if (target > budget / pc.stages) target = budget / pc.stages;
+    }
+    int tc = target / (w * 4 * nmaps);
     if (tc < 2) tc = 2;
     if (tc > 32) tc = 32;
     pc.tc = tc;
-    pc.stages = 4;
     if (env_tc > 0) pc.tc = env_tc;
     if (env_st > 1 && env_st <= MAX_STAGES) pc.stages = env_st;
     if (pc.tc > 256) pc.tc = 256;

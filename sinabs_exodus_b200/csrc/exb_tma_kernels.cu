@@ -258,7 +258,7 @@ template <int RESET, int NW, int V, bool UNI>
 static cudaError_t run_lif_fwd(const LifFwdArgs &a, cudaStream_t s, bool *used)
 {
     using G = TileGeom<NW, V>;
-    const PipeCfg pc = pipe_cfg(G::W, 1);
+    const PipeCfg pc = pipe_cfg(G::W, 1, a.B * ((a.M + G::W - 1) / G::W));
     TmaMaps maps;
     if (!make_btm_tensor_map(&maps.m[0], a.input, a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
     for (int i = 1; i < 5; ++i) maps.m[i] = maps.m[0];
@@ -293,7 +293,7 @@ template <int NW, int V>
 static cudaError_t run_leaky_fwd(const LeakyFwdArgs &a, cudaStream_t s, bool *used)
 {
     using G = TileGeom<NW, V>;
-    const PipeCfg pc = pipe_cfg(G::W, 1);
+    const PipeCfg pc = pipe_cfg(G::W, 1, a.B * ((a.M + G::W - 1) / G::W));
     TmaMaps maps;
     if (!make_btm_tensor_map(&maps.m[0], a.input, a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
     for (int i = 1; i < 5; ++i) maps.m[i] = maps.m[0];
@@ -324,7 +324,7 @@ static cudaError_t run_leaky_bwd(const LeakyBwdArgs &a, cudaStream_t s, bool *us
     int nmaps = 1;
     if (WA) ptrs[nmaps++] = a.out;
     if (WS) ptrs[nmaps++] = a.input;
-    const PipeCfg pc = pipe_cfg(G::W, nmaps);
+    const PipeCfg pc = pipe_cfg(G::W, nmaps, a.B * ((a.M + G::W - 1) / G::W));
     for (int i = 0; i < nmaps; ++i)
         if (!make_btm_tensor_map(&maps.m[i], ptrs[i], a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
     for (int i = nmaps; i < 5; ++i) maps.m[i] = maps.m[0];

@@ -124,7 +124,7 @@ static cudaError_t run_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
     if (a.gv) ptrs[nmaps++] = a.gv;
     if (SURR == EXB_SURR_GENERIC) ptrs[nmaps++] = a.surr;
     if (WS == SCALE_GRAD_FROM_INPUT) ptrs[nmaps++] = a.input;
-    const PipeCfg pc = pipe_cfg(G::W, nmaps);
+    const PipeCfg pc = pipe_cfg(G::W, nmaps, a.B * ((a.M + G::W - 1) / G::W));
     for (int i = 0; i < nmaps; ++i)
         if (!make_btm_tensor_map(&maps.m[i], ptrs[i], a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
     for (int i = nmaps; i < 5; ++i) maps.m[i] = maps.m[0];

@@ -263,7 +263,7 @@ template <int RESET, int NW, int V, bool UNI>
 static cudaError_t run_syn_fwd(const LifSynFwdArgs &a, cudaStream_t s, bool *used)
 {
     using G = TileGeom<NW, V>;
-    const PipeCfg pc = pipe_cfg(G::W, 1);
+    const PipeCfg pc = pipe_cfg(G::W, 1, a.B * ((a.M + G::W - 1) / G::W));
     TmaMaps6 maps;
     if (!make_btm_tensor_map(&maps.m[0], a.input, a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
     for (int i = 1; i < 6; ++i) maps.m[i] = maps.m[0];
@@ -307,7 +307,7 @@ static cudaError_t run_syn_bwd(const LifSynBwdArgs &a, cudaStream_t s, bool *use
     if (SURR == EXB_SURR_GENERIC) ptrs[nmaps++] = a.surr;
     if (WG) ptrs[nmaps++] = a.i_syn;
     if (a.g_isyn) ptrs[nmaps++] = a.g_isyn;
-    const PipeCfg pc = pipe_cfg(G::W, nmaps);
+    const PipeCfg pc = pipe_cfg(G::W, nmaps, a.B * ((a.M + G::W - 1) / G::W));
     for (int i = 0; i < nmaps; ++i)
         if (!make_btm_tensor_map(&maps.m[i], ptrs[i], a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
     for (int i = nmaps; i < 6; ++i) maps.m[i] = maps.m[0];
