@@ -123,3 +123,58 @@ def test_function_validation_on_cpu_tensors():
         LeakyIntegrator.apply(x.t(), a, z)
     with pytest.raises(_lib.ExodusLibraryError):
         LeakyIntegrator.apply(x, a, z)          # valid arguments, CPU tensors: no CPU implementation
+
+
+def test_decay_from_tau_matches_autograd():
+    """The one-node decay Function: same values and gradients as exp(-1/tau) and 1 - exp(-1/tau) through autograd."""
+    from sinabs_exodus_b200.layers.lif import _DecayFromTau
+    tau = torch.tensor([2.0, 10.0, 37.5], dtype=torch.float32, requires_grad=True)
+    w1, w2 = torch.tensor([0.3, -1.2, 2.0]), torch.tensor([1.5, 0.4, -0.7])
+    alpha, comp = _DecayFromTau.apply(tau, True)
+    torch.testing.assert_close(alpha, torch.exp(-1.0 / tau.detach()), rtol=0, atol=0)
+    torch.testing.assert_close(comp, 1.0 - torch.exp(-1.0 / tau.detach()), rtol=0, atol=0)
+    ((alpha * w1).sum() + (comp * w2).sum()).backward()
+    got = tau.grad.clone()
+    tau.grad = None
+    a = torch.exp(-1.0 / tau)
+    ((a * w1).sum() + ((1.0 - a) * w2).sum()).backward()
+    torch.testing.assert_close(got, tau.grad, rtol=1e-6, atol=1e-9)
+    # one output unused, and the variant without the complement
+    tau.grad = None
+    alpha, comp = _DecayFromTau.apply(tau, True)
+    comp.sum().backward()
+    torch.testing.assert_close(tau.grad, -(torch.exp(-1.0 / tau.detach()) / tau.detach() ** 2), rtol=1e-6, atol=1e-9)
+    alpha, none = _DecayFromTau.apply(tau, False)
+    assert none is None
+    assert torch.autograd.gradcheck(lambda t: _DecayFromTau.apply(t, True), (torch.tensor([3.0, 8.0], dtype=torch.float64,
+                                    requires_grad=True),))
+
+
+def test_scalar_constants_are_cached():
+    from sinabs_exodus_b200.layers.lif import _scalar_constant
+    a = _scalar_constant(0.75, "cpu")
+    assert a is _scalar_constant(0.75, "cpu") and a.item() == 0.75 and a.shape == (1,)
+    assert _scalar_constant(0.5, "cpu") is not a
+
+
+def test_firing_rate_is_formed_on_read():
+    layer = el.IAF()
+    assert layer.firing_rate is None
+    layer._set_rate_source(torch.tensor([30], dtype=torch.int64), 120)
+    assert abs(layer.firing_rate.item() - 0.25) < 1e-7
+    layer.firing_rate = torch.tensor(0.5)          # plain assignment still works (sinabs sets it that way)
+    assert layer.firing_rate.item() == 0.5
+
+
+def test_variant_layers_are_ordinary_classes():
+    import pickle
+    for cls, kwargs in ((el.IAFSqueeze, dict(batch_size=2, spike_threshold=0.5)),
+                        (el.ExpLeakSqueeze, dict(num_timesteps=5, tau_mem=12.0)),
+                        (el.LIFSqueeze, dict(batch_size=3, tau_mem=20.0, tau_syn=5.0))):
+        layer = cls(**kwargs)
+        assert repr(layer).startswith("EXODUS " + cls.__name__)
+        clone = pickle.loads(pickle.dumps(layer))
+        assert type(clone) is cls and clone.arg_dict.keys() == layer.arg_dict.keys()
+        rebuilt = cls(**layer.arg_dict)
+        assert type(rebuilt) is cls
+    assert "tau_mem" not in el.IAF().arg_dict and "spike_fn" not in el.ExpLeak(tau_mem=5.0).arg_dict
