@@ -590,7 +590,8 @@ def run_ours(args, wl):
                        "parallelism": f"batch-sharded x{world}",
                        "api": "sinabs_exodus_b200.layers" if args.layout == "btm"
                        else "IntegrateAndFire / LeakyIntegrator Functions on [N,T] (no layer glue)",
-                       "cuda_graph": bool(args.cuda_graph)},
+                       "cuda_graph": bool(args.cuda_graph),
+                       "autograd": "single-threaded" if args.single_thread_autograd else "default (backward on PyTorch's autograd thread)"},
             "step_fraction_of_hbm_roofline": (step_bytes / (ms_total / args.steps * 1e-3) / 1e9) / peak,
             "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         }
@@ -609,6 +610,9 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch size (profiling small cases)")
     ap.add_argument("--layout", default="btm", choices=["btm", "nt"],
                     help="btm: the layers (time-major kernels); nt: the drop-in Functions on the reference's [N,T] layout")
+    ap.add_argument("--single-thread-autograd", action="store_true",
+                    help="run backward in the calling thread (torch.autograd.set_multithreading_enabled(False)): "
+                         "saves the hand-over to PyTorch's autograd thread, 60-120 us per step, which shows on small problems")
     ap.add_argument("--cuda-graph", action="store_true", help="capture the step in a CUDA graph and time replays")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -625,6 +629,9 @@ def main():
         wl["desc"] += f" [batch overridden to {args.batch}]"
     if args.impl == "reference":
         run_reference(args, wl)
+    elif args.single_thread_autograd:
+        with torch.autograd.set_multithreading_enabled(False):
+            run_ours(args, wl)
     else:
         run_ours(args, wl)
 
