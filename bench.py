@@ -356,6 +356,36 @@ def cpu_c_kernels_sample(name: str, wl: dict, budget_s: float):
                       f"on {rows_fit} rows x {T} steps of {name} in the reference's [N,T] layout"}
 
 
+def stream_mix_ceilings(dev) -> dict:
+    """What plain streaming kernels reach on this GPU for the read/write mixes of the two passes: one read and two
+    writes per element (the forward: in -> spikes, v_mem) and two reads and one write (the backward: grad, v_mem ->
+    grad_in).  Calibration only, with library elementwise kernels on 512 MB tensors: `torch.frexp` (one fp32 in, one
+    fp32 and one int32 out) and `torch.add`.  DRAM turns around between reads and writes, so the ceiling of a mix is
+    not that of a copy; the kernels' GB/s should be read against these as well as against the copy peak."""
+    n = 1 << 27
+    a = torch.randn(n, device=dev)
+    b = torch.randn(n, device=dev)
+    o1 = torch.empty(n, device=dev)
+    o2 = torch.empty(n, device=dev, dtype=torch.int32)
+
+    def timed(fn, reps=20):
+        for _ in range(3):
+            fn()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / reps * 1e-3
+
+    t12 = timed(lambda: torch.frexp(a, out=(o1, o2)))
+    t21 = timed(lambda: torch.add(a, b, out=o1))
+    t11 = timed(lambda: o1.copy_(a))
+    return {"1r2w_gbs": 12.0 * n / t12 / 1e9, "2r1w_gbs": 12.0 * n / t21 / 1e9, "copy_gbs": 8.0 * n / t11 / 1e9,
+            "how": "torch.frexp / torch.add / copy_ on 2^27 fp32 elements, CUDA events, 20 repetitions"}
+
+
 # --------------------------------------------------------------------------
 def measured_peak_gbs():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -542,6 +572,12 @@ def run_ours(args, wl):
         del xh, gh, oh, gih, xd, gd
 
     clocks = sampler.stop() if sampler else None
+    mix = None
+    if rank == 0 and not args.no_mix:
+        try:
+            mix = stream_mix_ceilings(dev)
+        except Exception as exc:
+            mix = {"unavailable": str(exc)[:200]}
 
     if rank == 0:
         peak, peak_src = measured_peak_gbs()
@@ -593,7 +629,7 @@ def run_ours(args, wl):
                        "cuda_graph": bool(args.cuda_graph),
                        "autograd": "single-threaded" if args.single_thread_autograd else "default (backward on PyTorch's autograd thread)"},
             "step_fraction_of_hbm_roofline": (step_bytes / (ms_total / args.steps * 1e-3) / 1e9) / peak,
-            "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+            "roofline": roof, "stream_mix_ceilings": mix, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -615,6 +651,7 @@ def main():
                          "saves the hand-over to PyTorch's autograd thread, 60-120 us per step, which shows on small problems")
     ap.add_argument("--cuda-graph", action="store_true", help="capture the step in a CUDA graph and time replays")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-mix", action="store_true", help="skip the streaming-mix calibration (1 read : 2 writes, 2 : 1)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--e2e-microbatches", type=int, default=16)
