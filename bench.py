@@ -644,6 +644,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch size (profiling small cases)")
+    ap.add_argument("--shape", default=None,
+                    help="override the per-GPU input shape, e.g. 32,300,36991 (same layer and value distribution)")
     ap.add_argument("--layout", default="btm", choices=["btm", "nt"],
                     help="btm: the layers (time-major kernels); nt: the drop-in Functions on the reference's [N,T] layout")
     ap.add_argument("--single-thread-autograd", action="store_true",
@@ -661,6 +663,11 @@ def main():
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     wl = dict(WORKLOADS[args.workload])
+    if args.shape is not None:
+        wl["shape"] = tuple(int(v) for v in args.shape.split(","))
+        if len(wl["shape"]) < 3:
+            raise SystemExit("--shape needs at least batch,time,neurons")
+        wl["desc"] += f" [shape overridden to {wl['shape']}]"
     if args.batch is not None:
         wl["shape"] = (args.batch,) + tuple(wl["shape"][1:])
         wl["desc"] += f" [batch overridden to {args.batch}]"
