@@ -13,6 +13,7 @@ mask, gradient combination, ``lifBackward``, ``lifBackwardAlpha`` and
 """
 from __future__ import annotations
 
+import weakref
 from typing import Callable, Optional, Tuple
 
 import torch
@@ -156,6 +157,32 @@ def _validate_1d(t: torch.Tensor, name: str) -> None:
         raise ValueError(f"'{name}' has to be contiguous.")
 
 
+# Value checks of the reference Function (spike.py:183,190).  Each one reads a result back from the GPU,
+# which drains the launch queue, so the verdict is remembered for as long as the very same tensors (object
+# and version counter) come back: parameters checked once are not read back again on every call.
+_CHECKED: dict = {}
+
+
+def _check_values(alpha: torch.Tensor, threshold: torch.Tensor, min_v_mem: Optional[torch.Tensor]) -> None:
+    tensors = [t for t in (alpha, threshold, min_v_mem) if t is not None]
+    key = tuple(id(t) for t in tensors)
+    seen = _CHECKED.get(key)
+    if seen is not None and all(r() is t and ver == t._version for (r, ver), t in zip(seen, tensors)):
+        return      # the same live tensors, unmodified since they passed
+    bad_alpha = ((alpha < 0) | (alpha > 1)).any()
+    if min_v_mem is not None:
+        bad_alpha, bad_low = torch.stack((bad_alpha, (threshold <= min_v_mem).any())).tolist()   # one read-back
+    else:
+        bad_alpha, bad_low = bool(bad_alpha), False
+    if bad_alpha:
+        raise ValueError("'alpha' must be between 0 and 1.")
+    if bad_low:
+        raise ValueError("`threshold` must be greater than `min_v_mem`.")
+    if len(_CHECKED) >= 256:
+        _CHECKED.clear()
+    _CHECKED[key] = [(weakref.ref(t), t._version) for t in tensors]
+
+
 class IntegrateAndFire(torch.autograd.Function):
     """Drop-in for the reference ``IntegrateAndFire`` (``[N, T]`` tensors, per-row parameters).
 
@@ -178,12 +205,9 @@ class IntegrateAndFire(torch.autograd.Function):
         _validate_1d(membrane_subtract, "membrane_subtract")
         _validate_1d(v_mem_init, "v_mem_init")
         _validate_1d(threshold, "threshold")
-        if (alpha < 0).any() or (alpha > 1).any():
-            raise ValueError("'alpha' must be between 0 and 1.")
         if apply_min_v_mem:
             _validate_1d(min_v_mem, "min_v_mem")
-            if (threshold <= min_v_mem).any():
-                raise ValueError("`threshold` must be greater than `min_v_mem`.")
+        _check_values(alpha, threshold, min_v_mem)
         N, T = inp.shape
         for t, name in ((alpha, "alpha"), (membrane_subtract, "membrane_subtract"),
                         (v_mem_init, "v_mem_init"), (threshold, "threshold")):

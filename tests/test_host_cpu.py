@@ -178,3 +178,22 @@ def test_variant_layers_are_ordinary_classes():
         rebuilt = cls(**layer.arg_dict)
         assert type(rebuilt) is cls
     assert "tau_mem" not in el.IAF().arg_dict and "spike_fn" not in el.ExpLeak(tau_mem=5.0).arg_dict
+
+
+def test_value_checks_are_remembered_per_tensor():
+    """The alpha / threshold checks read back from the device once per (live tensor, version), not per call,
+    and still fire when a tensor is modified in place or replaced by another one."""
+    from sinabs_exodus_b200.spike import _CHECKED, _check_values
+    a, th, lo = torch.rand(6), torch.ones(6), -torch.ones(6)
+    _check_values(a, th, lo)
+    entries = len(_CHECKED)
+    _check_values(a, th, lo)
+    assert len(_CHECKED) == entries
+    a.mul_(5.0)                                   # same object, new version
+    with pytest.raises(ValueError):
+        _check_values(a, th, lo)
+    for _ in range(4):                            # short-lived tensors may reuse ids: never trusted blindly
+        with pytest.raises(ValueError):
+            _check_values(torch.full((6,), 1.5), th, None)
+    with pytest.raises(ValueError):
+        _check_values(torch.rand(6), th, torch.full((6,), 2.0))
