@@ -94,6 +94,23 @@ int exb_lif_forward(float *spikes, float *v_mem, const float *input, const float
                     int64_t B, int64_t T, int64_t M, int layout,
                     int device, void *stream);
 
+/* exb_lif_forward that also records the membrane potential AFTER each step's reset:
+ * v_post[b,t,m] = v_mem - subtract * spikes (EXB_RESET_SUBTRACT; product rounded first, as
+ * the layer's PyTorch expression layers/lif.py:256 does) or the reset value where a spike
+ * occurred (EXB_RESET_TO_VALUE).  It is what a layer with record_states stores
+ * (layers/lif.py:299-300); written by the same launch, 4 more bytes per neuron-step instead
+ * of a read-read-write pass.  Time-major layout only (EXB_ERR_UNSUPPORTED otherwise). */
+int exb_lif_forward_record(float *spikes, float *v_mem, float *v_post, const float *input, const float *v_init,
+                           const float *in_scale, int in_scale_mode,
+                           const float *alpha, int alpha_mode,
+                           const float *subtract, int subtract_mode,
+                           const float *theta, int theta_mode,
+                           const float *theta_low, int theta_low_mode,
+                           uint32_t max_spikes, int reset_mode,
+                           float *v_post_last, unsigned long long *spike_count,
+                           int64_t B, int64_t T, int64_t M, int layout,
+                           int device, void *stream);
+
 /* Fused reverse-time EXODUS backward.  Replaces lifBackward + lifBackwardAlpha
  * (cuda/bindings.cu:72-158, kernels cuda/lif_kernels.h:122-168, 199-246) and
  * the tensor glue of IntegrateAndFire.backward (sinabs/exodus/spike.py:251-289):

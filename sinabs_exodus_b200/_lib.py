@@ -37,7 +37,7 @@ _lib: Optional[ctypes.CDLL] = None
 
 EXPORTS = (
     "exb_version", "exb_last_error", "exb_status_string", "exb_device_status",
-    "exb_lif_forward", "exb_lif_backward", "exb_leaky_forward", "exb_leaky_backward",
+    "exb_lif_forward", "exb_lif_forward_record", "exb_lif_backward", "exb_leaky_forward", "exb_leaky_backward",
     "exb_leaky_scan_workspace_bytes", "exb_leaky_forward_scan", "exb_leaky_backward_scan",
     "exb_leaky_forward_scan_static", "exb_lif_syn_forward", "exb_lif_syn_backward",
 )
@@ -67,6 +67,10 @@ def load() -> ctypes.CDLL:
     lib.exb_lif_forward.argtypes = [_vp, _vp, _vp, _vp,
                                     _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _i,
                                     _u32, _i, _vp, _vp] + geometry
+    lib.exb_lif_forward_record.restype = _i
+    lib.exb_lif_forward_record.argtypes = [_vp, _vp, _vp, _vp, _vp,
+                                           _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _i,
+                                           _u32, _i, _vp, _vp] + geometry
     lib.exb_lif_backward.restype = _i
     lib.exb_lif_backward.argtypes = [_vp, _vp, _vp, _vp,
                                      _vp, _vp, _vp,
@@ -158,19 +162,24 @@ class ParamSpec(tuple):
 
 def lif_forward(spikes, v_mem, inp, v_init, in_scale: Tuple, alpha: Tuple, subtract: Tuple, theta: Tuple,
                 theta_low: Tuple, max_spikes: Optional[int], reset_mode: int, v_post_last, spike_count,
-                B: int, T: int, M: int, layout: int) -> None:
+                B: int, T: int, M: int, layout: int, v_post=None) -> None:
+    """``v_post``: optional tensor like ``v_mem`` that receives the potential after each step's reset
+    (time-major layout only)."""
     if B * T * M == 0:      # empty problem: nothing to launch (empty tensors have no storage to point at)
         return
     dev = _require_cuda(spikes, v_mem, inp, v_init, in_scale[0], alpha[0], subtract[0], theta[0], theta_low[0],
-                        v_post_last)
+                        v_post_last, v_post)
     ms = MAX_SPIKES_UNLIMITED if max_spikes is None else int(max_spikes)
-    st = load().exb_lif_forward(
-        ptr(spikes), ptr(v_mem), ptr(inp), ptr(v_init),
-        ptr(in_scale[0]), in_scale[1], ptr(alpha[0]), alpha[1], ptr(subtract[0]), subtract[1],
-        ptr(theta[0]), theta[1], ptr(theta_low[0]), theta_low[1],
-        ms, reset_mode, ptr(v_post_last), ptr(spike_count),
-        B, T, M, layout, dev.index, _stream(dev))
-    _check(st, "exb_lif_forward")
+    tail = (ptr(in_scale[0]), in_scale[1], ptr(alpha[0]), alpha[1], ptr(subtract[0]), subtract[1],
+            ptr(theta[0]), theta[1], ptr(theta_low[0]), theta_low[1],
+            ms, reset_mode, ptr(v_post_last), ptr(spike_count),
+            B, T, M, layout, dev.index, _stream(dev))
+    if v_post is None:
+        st = load().exb_lif_forward(ptr(spikes), ptr(v_mem), ptr(inp), ptr(v_init), *tail)
+        _check(st, "exb_lif_forward")
+    else:
+        st = load().exb_lif_forward_record(ptr(spikes), ptr(v_mem), ptr(v_post), ptr(inp), ptr(v_init), *tail)
+        _check(st, "exb_lif_forward_record")
 
 
 def lif_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, grad_v_mem, grad_v_last,

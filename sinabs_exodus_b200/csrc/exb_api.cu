@@ -95,7 +95,9 @@ int exb_device_status(int device, void *stream)
     return EXB_OK;
 }
 
-int exb_lif_forward(float *spikes, float *v_mem, const float *input, const float *v_init,
+}  // extern "C"
+
+static int lif_forward_impl(const char *who, float *spikes, float *v_mem, float *v_post, const float *input, const float *v_init,
                     const float *in_scale, int in_scale_mode,
                     const float *alpha, int alpha_mode,
                     const float *subtract, int subtract_mode,
@@ -107,18 +109,20 @@ int exb_lif_forward(float *spikes, float *v_mem, const float *input, const float
                     int device, void *stream)
 {
     if (int st = check_geometry(B, T, M, layout)) return st;
-    if (!spikes || !v_mem || !input) return fail(EXB_ERR_ARG, "exb_lif_forward: spikes, v_mem and input are required");
-    if (!alpha || !theta) return fail(EXB_ERR_ARG, "exb_lif_forward: alpha and theta are required");
+    if (!spikes || !v_mem || !input) return fail(EXB_ERR_ARG, "%s: spikes, v_mem and input are required", who);
+    if (!alpha || !theta) return fail(EXB_ERR_ARG, "%s: alpha and theta are required", who);
     if (!mode_ok(alpha_mode) || !mode_ok(theta_mode) || (subtract && !mode_ok(subtract_mode)) ||
         (theta_low && !mode_ok(theta_low_mode)) || (in_scale && !mode_ok(in_scale_mode)))
-        return fail(EXB_ERR_ARG, "exb_lif_forward: bad parameter mode");
+        return fail(EXB_ERR_ARG, "%s: bad parameter mode", who);
     if (reset_mode != EXB_RESET_SUBTRACT && reset_mode != EXB_RESET_TO_VALUE)
-        return fail(EXB_ERR_ARG, "exb_lif_forward: bad reset mode %d", reset_mode);
+        return fail(EXB_ERR_ARG, "%s: bad reset mode %d", who, reset_mode);
     if (reset_mode == EXB_RESET_TO_VALUE && !subtract)
-        return fail(EXB_ERR_ARG, "exb_lif_forward: reset-to-value needs the value in `subtract`");
+        return fail(EXB_ERR_ARG, "%s: reset-to-value needs the value in `subtract`", who);
+    if (v_post && layout != EXB_LAYOUT_BTM)
+        return fail(EXB_ERR_UNSUPPORTED, "%s: the post-reset record is written by the time-major kernels only", who);
     if (B == 0 || M == 0 || T == 0) return EXB_OK;
     DeviceGuard guard(device);
-    if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_lif_forward: cannot select device %d", device);
+    if (!guard.ok) return fail(EXB_ERR_DEVICE, "%s: cannot select device %d", who, device);
 
     exb::LifFwdArgs a;
     a.spikes = spikes; a.v_mem = v_mem; a.input = input; a.v_init = v_init;
@@ -128,9 +132,44 @@ int exb_lif_forward(float *spikes, float *v_mem, const float *input, const float
     a.np.lo = exb::make_param(theta_low, theta_low_mode, M);
     a.np.scale = exb::make_param(in_scale, in_scale_mode, M);
     a.maxs = max_spikes;
-    a.v_post_last = v_post_last; a.spike_count = spike_count;
+    a.v_post_last = v_post_last; a.spike_count = spike_count; a.v_post = v_post;
     a.B = B; a.T = T; a.M = M;
-    return launch_status(exb::launch_lif_forward(a, layout, reset_mode, (cudaStream_t)stream), "exb_lif_forward");
+    return launch_status(exb::launch_lif_forward(a, layout, reset_mode, (cudaStream_t)stream), who);
+}
+
+extern "C" {
+
+int exb_lif_forward(float *spikes, float *v_mem, const float *input, const float *v_init,
+                    const float *in_scale, int in_scale_mode,
+                    const float *alpha, int alpha_mode,
+                    const float *subtract, int subtract_mode,
+                    const float *theta, int theta_mode,
+                    const float *theta_low, int theta_low_mode,
+                    uint32_t max_spikes, int reset_mode,
+                    float *v_post_last, unsigned long long *spike_count,
+                    int64_t B, int64_t T, int64_t M, int layout,
+                    int device, void *stream)
+{
+    return lif_forward_impl("exb_lif_forward", spikes, v_mem, nullptr, input, v_init, in_scale, in_scale_mode, alpha,
+                            alpha_mode, subtract, subtract_mode, theta, theta_mode, theta_low, theta_low_mode,
+                            max_spikes, reset_mode, v_post_last, spike_count, B, T, M, layout, device, stream);
+}
+
+int exb_lif_forward_record(float *spikes, float *v_mem, float *v_post, const float *input, const float *v_init,
+                           const float *in_scale, int in_scale_mode,
+                           const float *alpha, int alpha_mode,
+                           const float *subtract, int subtract_mode,
+                           const float *theta, int theta_mode,
+                           const float *theta_low, int theta_low_mode,
+                           uint32_t max_spikes, int reset_mode,
+                           float *v_post_last, unsigned long long *spike_count,
+                           int64_t B, int64_t T, int64_t M, int layout,
+                           int device, void *stream)
+{
+    if (!v_post) return fail(EXB_ERR_ARG, "exb_lif_forward_record: v_post is required (use exb_lif_forward without it)");
+    return lif_forward_impl("exb_lif_forward_record", spikes, v_mem, v_post, input, v_init, in_scale, in_scale_mode,
+                            alpha, alpha_mode, subtract, subtract_mode, theta, theta_mode, theta_low, theta_low_mode,
+                            max_spikes, reset_mode, v_post_last, spike_count, B, T, M, layout, device, stream);
 }
 
 int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, float *grad_scale,

@@ -13,6 +13,7 @@ struct LifFwdArgs {
     unsigned maxs;
     float *v_post_last;
     unsigned long long *spike_count;
+    float *v_post;     // optional full record of the potential after each step's reset (time-major kernels only)
     int64_t B, T, M;
 };
 

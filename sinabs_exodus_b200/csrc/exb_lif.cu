@@ -242,10 +242,10 @@ template <int RESET>
 static cudaError_t launch_fwd_t(const LifFwdArgs &a, int layout, cudaStream_t s)
 {
     if (layout == EXB_LAYOUT_BTM) {
-        if (can_vec4(a.M, {a.spikes, a.v_mem, a.input})) {
+        if (can_vec4(a.M, {a.spikes, a.v_mem, a.input, a.v_post})) {
             cudaError_t e = launch_ring<4>(lif_fwd_btm_ring_kernel<4, RESET>, a, 1, s);
             if (e != cudaSuccess) return e;
-        } else if (can_vec2(a.M, {a.spikes, a.v_mem, a.input})) {
+        } else if (can_vec2(a.M, {a.spikes, a.v_mem, a.input, a.v_post})) {
             cudaError_t e = launch_ring<2>(lif_fwd_btm_ring_kernel<2, RESET>, a, 1, s);
             if (e != cudaSuccess) return e;
         } else {

@@ -166,6 +166,15 @@ __device__ __forceinline__ float post_reset(float v, float af, const Neuron &q)
     return (af != 0.0f) ? q.c : v;
 }
 
+// The same for the recorded potential (layers/lif.py:256 of the reference: `v_mem - subtract * spikes`,
+// formed by PyTorch with a rounded product): two roundings, so that a recording equals the reference's bit for bit.
+template <int RESET>
+__device__ __forceinline__ float recorded_post(float v, float af, const Neuron &q)
+{
+    if (RESET == EXB_RESET_SUBTRACT) return __fsub_rn(v, __fmul_rn(q.c, af));
+    return (af != 0.0f) ? q.c : v;
+}
+
 // Surrogate-gradient constants of one neuron.
 struct SurrConst {
     float k0, k1, k2;

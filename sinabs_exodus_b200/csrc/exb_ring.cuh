@@ -92,6 +92,7 @@ __global__ void __launch_bounds__(RING_THREADS, 4) lif_fwd_btm_ring_kernel(const
     const float *in = A.input + base;
     float *sp = A.spikes + base;
     float *vm = A.v_mem + base;
+    float *rec = A.v_post ? A.v_post + base : nullptr;      // optional record of the potential after each reset
     SpikeTotal cnt;
     cnt.c32 = 0u; cnt.c64 = 0ull;
     float *mine = ring_smem + threadIdx.x * V;
@@ -125,9 +126,16 @@ __global__ void __launch_bounds__(RING_THREADS, 4) lif_fwd_btm_ring_kernel(const
                 if (valid) {
                     stv<V>(sp, af);
                     stv<V>(vm, v);
+                    if (rec) {
+                        float vp[V];
+#pragma unroll
+                        for (int j = 0; j < V; ++j) vp[j] = recorded_post<RESET>(v[j], af[j], q[j]);
+                        stv<V>(rec, vp);
+                    }
                 }
                 sp += M;
                 vm += M;
+                if (rec) rec += M;
             }
         }
     }

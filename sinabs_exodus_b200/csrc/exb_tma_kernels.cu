@@ -10,7 +10,8 @@ namespace exb {
 // ===========================================================================
 // spike scan forward
 // ===========================================================================
-template <int RESET, int NW, int V, bool UNI>
+// REC: also write the potential after each step's reset (the layers' `record_states`).
+template <int RESET, int NW, int V, bool UNI, bool REC>
 __global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V, (V == 4 && !UNI)>::value)
 lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, const int tiles_m, const PipeCfg pc)
 {
@@ -52,6 +53,7 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
         const int64_t base = ((int64_t)b * T) * A.M + mm;
         float *sp = A.spikes + base;
         float *vm = A.v_mem + base;
+        float *rec = REC ? A.v_post + base : nullptr;
         const int64_t M = A.M;
         const int col = tile_col_off<NW, V>(pc.tc, c);
         SpikeTotal cnt;
@@ -70,9 +72,16 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
                 if (valid) {
                     stv<V>(sp, af);
                     stv<V>(vm, v);
+                    if (REC) {
+                        float vp[V];
+#pragma unroll
+                        for (int j = 0; j < V; ++j) vp[j] = recorded_post<RESET>(v[j], af[j], q[NQ == 1 ? 0 : j]);
+                        stv<V>(rec, vp);
+                    }
                 }
                 sp += M;
                 vm += M;
+                if (REC) rec += M;
             }
             release_chunk(ring, pos, lane);
             pos.advance(pc.stages);
@@ -265,7 +274,7 @@ static cudaError_t run_lif_fwd(const LifFwdArgs &a, cudaStream_t s, bool *used)
     const int tiles_m = (int)((a.M + G::W - 1) / G::W);
     const size_t smem = tma_smem_bytes<NW, V>(1, pc);
     if (smem > 200 * 1024) return cudaSuccess;
-    auto kern = lif_fwd_tma_kernel<RESET, NW, V, UNI>;
+    auto kern = a.v_post ? lif_fwd_tma_kernel<RESET, NW, V, UNI, true> : lif_fwd_tma_kernel<RESET, NW, V, UNI, false>;
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
     kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m, pc);
@@ -276,7 +285,9 @@ static cudaError_t run_lif_fwd(const LifFwdArgs &a, cudaStream_t s, bool *used)
 cudaError_t launch_lif_forward_tma(const LifFwdArgs &a, int reset_mode, cudaStream_t s, bool *used)
 {
     *used = false;
-    if (!eligible(a.B, a.T, a.M) || !aligned16(a.spikes) || !aligned16(a.v_mem) || !aligned16(a.input)) return cudaSuccess;
+    if (!eligible(a.B, a.T, a.M) || !aligned16(a.spikes) || !aligned16(a.v_mem) || !aligned16(a.input) ||
+        (a.v_post && !aligned16(a.v_post)))
+        return cudaSuccess;
     const bool wide = use_wide(a.B, a.M);
     const bool uni = a.np.uniform();
     if (reset_mode == EXB_RESET_SUBTRACT) {

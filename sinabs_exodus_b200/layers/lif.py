@@ -230,19 +230,21 @@ class LIF(LIFBase):
             subtract = _flat_param(self.reset_fn.subtract_value, trailing, batch, dev)
         self._validate_once(alpha_mem, dev)
         count = torch.zeros(1, dtype=torch.int64, device=dev)
+        # With autograd off the recorded potential is a plain side output of the forward launch; with autograd on
+        # it stays the reference's differentiable expression (layers/lif.py:256), so that a loss on a recording works.
+        fused_record = self.record_states and not torch.is_grad_enabled()
+        v_rec = torch.empty_like(i_syn) if fused_record else None
         spikes, v_pre, v_post_last = IntegrateAndFireTM.apply(
             i_syn, alpha_mem, self.v_mem.reshape(-1), threshold, subtract, min_v_mem, scale,
             self.surrogate_grad_fn, self.max_num_spikes_per_bin, reset_mode, count,
-            scale is not None and getattr(self, "_scale_nonzero", False))
-        if self.record_states:
+            scale is not None and getattr(self, "_scale_nonzero", False), v_rec)
+        if self.record_states and not fused_record:
             c = threshold if subtract is None else subtract
             c = c if c.numel() == 1 else (c.view(1, 1, -1) if c.numel() == v_pre.shape[2] else c.view(batch, 1, -1))
             if reset_mode == _lib.RESET_SUBTRACT:
                 v_rec = v_pre - c * spikes
             else:
                 v_rec = torch.where(spikes > 0, c.expand_as(v_pre), v_pre)
-        else:
-            v_rec = None
         return spikes, v_rec, v_post_last, count
 
     def _validate_once(self, alpha_mem: torch.Tensor, dev) -> None:

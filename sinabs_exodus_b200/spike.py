@@ -57,7 +57,7 @@ class _LifCore:
 
     @staticmethod
     def forward(ctx, inp, alpha, v_init, theta, subtract, min_v_mem, in_scale, surrogate_fn, max_spikes,
-                reset_mode, spike_count, B, T, M, layout, scale_grad_from_state=False):
+                reset_mode, spike_count, B, T, M, layout, scale_grad_from_state=False, record=None):
         N = B * M
         a_f, th_f, c_f, lo_f, sc_f = map(_flat32, (alpha, theta, subtract, min_v_mem, in_scale))
         modes = dict(
@@ -73,7 +73,7 @@ class _LifCore:
             v_post_last = torch.empty(N, dtype=torch.float32, device=inp.device)
         _lib.lif_forward(spikes, v_mem, inp, vi_f, (sc_f, modes["scale"]), (a_f, modes["alpha"]),
                          (c_f, modes["subtract"]), (th_f, modes["theta"]), (lo_f, modes["lo"]),
-                         max_spikes, reset_mode, v_post_last, spike_count, B, T, M, layout)
+                         max_spikes, reset_mode, v_post_last, spike_count, B, T, M, layout, v_post=record)
         ctx.set_materialize_grads(False)
         ctx.geometry = (B, T, M, layout)
         ctx.modes = modes
@@ -237,12 +237,14 @@ class IntegrateAndFireTM(torch.autograd.Function):
     is an optional zero-initialised int64 tensor of one element that receives the
     total number of spikes.  ``scale_grad_from_state=True`` makes the backward rebuild the
     gradient w.r.t. ``in_scale`` from the saved membrane potential instead of keeping and re-reading
-    the input; the caller guarantees that no scale is zero.
+    the input; the caller guarantees that no scale is zero.  ``record``: optional tensor like ``inp`` that
+    the same launch fills with the potential after each step's reset (a plain side output, no gradient).
     """
 
     @staticmethod
     def forward(ctx, inp, alpha, v_init, threshold, membrane_subtract, min_v_mem, in_scale,
-                surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count, scale_grad_from_state=False):
+                surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count, scale_grad_from_state=False,
+                record=None):
         if inp.ndim != 3:
             raise ValueError("'inp' must be 3D, (batch, time, neurons)")
         if not inp.is_contiguous():
@@ -252,12 +254,12 @@ class IntegrateAndFireTM(torch.autograd.Function):
             raise ValueError("'v_init' must hold one value per batch item and neuron")
         return _LifCore.forward(ctx, inp, alpha, v_init, threshold, membrane_subtract, min_v_mem, in_scale,
                                 surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count,
-                                B, T, M, _lib.LAYOUT_BTM, scale_grad_from_state)
+                                B, T, M, _lib.LAYOUT_BTM, scale_grad_from_state, record)
 
     @staticmethod
     def backward(ctx, grad_spikes, grad_v_mem, grad_v_last):
         grad_input, grad_alpha, grad_init, grad_scale = _LifCore.backward(ctx, grad_spikes, grad_v_mem, grad_v_last)
-        return grad_input, grad_alpha, grad_init, None, None, None, grad_scale, None, None, None, None, None
+        return grad_input, grad_alpha, grad_init, None, None, None, grad_scale, None, None, None, None, None, None
 
 
 def fused_synaptic_eligible(inp: torch.Tensor) -> bool:

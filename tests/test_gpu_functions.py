@@ -476,3 +476,20 @@ def test_graphed_step_carries_state():
     for c, w in zip(chunks, want):
         torch.testing.assert_close(step(c), w, rtol=0, atol=0)
     torch.testing.assert_close(stateful[0].v_mem, v_want, rtol=0, atol=0)
+
+
+def test_layer_recordings_fused_under_no_grad():
+    """record_states: with autograd off the recording is a side output of the forward launch; it equals the
+    differentiable expression used with autograd on, bit for bit."""
+    from sinabs_exodus_b200.layers import LIF
+    torch.manual_seed(2)
+    x = 0.4 + 0.6 * torch.randn(3, 40, 24, device="cuda:0")
+    for kwargs in (dict(tau_mem=15.0, min_v_mem=-0.5), dict(tau_mem=15.0, tau_syn=6.0)):
+        a = LIF(record_states=True, **kwargs).to("cuda:0")
+        b = LIF(record_states=True, **kwargs).to("cuda:0")
+        out_a = a(x.clone().requires_grad_(True))
+        with torch.no_grad():
+            out_b = b(x)
+        torch.testing.assert_close(out_a.detach(), out_b, rtol=0, atol=0)
+        torch.testing.assert_close(a.recordings["v_mem"].detach(), b.recordings["v_mem"], rtol=0, atol=0)
+        assert a.recordings["v_mem"].requires_grad and not b.recordings["v_mem"].requires_grad

@@ -377,3 +377,32 @@ def test_device_status_clean():
     """After all the launches above no bounded device-side wait has run out."""
     from sinabs_exodus_b200 import _lib
     _lib.device_status()
+
+
+@pytest.mark.parametrize("B,T,M", [(3, 33, 37), (2, 40, 38), (2, 64, 128), (300, 9, 516)])
+@pytest.mark.parametrize("reset_mode", [0, 1])
+def test_forward_record_of_post_reset_potential(B, T, M, reset_mode):
+    """exb_lif_forward_record: the extra output equals v_mem - subtract * spikes (two roundings, as PyTorch
+    forms it) or the reset value where a spike occurred; spikes and v_mem are those of exb_lif_forward.
+    Shapes cover the cp.async rings (4- and 8-byte pieces) and both TMA tile widths."""
+    import torch
+    from sinabs_exodus_b200 import _lib
+    from tests import _gpu
+    cs = _tile_case(40 + M, B, T, M, _lib.PARAM_PER_N, clamp=True)
+    N = B * M
+    x = _gpu.to_dev(cs["inp"], B, M, _lib.LAYOUT_BTM)
+    spikes, v_mem, rec = (torch.full_like(x, float("nan")) for _ in range(3))
+    par = lambda k: _gpu.param(cs[k], _lib.PARAM_PER_N, B, M)
+    _lib.lif_forward(spikes, v_mem, x, _gpu.vec(cs["v_init"]), (None, 0), par("alpha"), par("subtract"), par("theta"),
+                     par("theta_low"), None, reset_mode, None, None, B, T, M, _lib.LAYOUT_BTM, v_post=rec)
+    s2, v2 = torch.full_like(x, float("nan")), torch.full_like(x, float("nan"))
+    _lib.lif_forward(s2, v2, x, _gpu.vec(cs["v_init"]), (None, 0), par("alpha"), par("subtract"), par("theta"),
+                     par("theta_low"), None, reset_mode, None, None, B, T, M, _lib.LAYOUT_BTM)
+    torch.cuda.synchronize()
+    assert torch.equal(spikes, s2) and torch.equal(v_mem, v2)
+    c = torch.as_tensor(cs["subtract"], device=x.device).view(B, 1, M)
+    want = v_mem - c * spikes if reset_mode == _lib.RESET_SUBTRACT else torch.where(spikes > 0, c.expand_as(v_mem), v_mem)
+    assert torch.equal(rec, want)
+    with pytest.raises(_lib.ExodusLibraryError):      # the [N,T] kernels do not write it
+        _lib.lif_forward(spikes, v_mem, x, _gpu.vec(cs["v_init"]), (None, 0), par("alpha"), par("subtract"),
+                         par("theta"), par("theta_low"), None, reset_mode, None, None, 1, T, N, _lib.LAYOUT_NT, v_post=rec)
