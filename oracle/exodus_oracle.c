@@ -256,3 +256,126 @@ void orc_leaky_backward_f64(double *input_grad, double *alpha_grad /* nullable *
         }
     }
 }
+
+/* ========================================================================
+ * Extensions beyond the reference kernels (still test infrastructure).
+ *
+ * orc_lif_forward_ext: lifForwardKernel (cuda/lif_kernels.h:58-91) with the two
+ * options the B200 library adds to that step:
+ *   in_scale  (nullable) multiplies the input per neuron; the product is rounded
+ *             on its own and then enters the fused multiply-add, which is what a
+ *             separate PyTorch multiplication in front of lifForward gives
+ *             (sinabs/exodus/layers/lif.py:206-209);
+ *   reset_to_value != 0   replaces "v -= act * subtract" (lif_kernels.h:63) by
+ *             "v = subtract[n] where act > 0" -- not a reference mode: the
+ *             reference layer rejects every reset but MembraneSubtract
+ *             (sinabs/exodus/layers/lif.py:136-143).
+ * ====================================================================== */
+void orc_lif_forward_ext(float *spikes, float *vmem, const float *input,
+                         const float *v_init, const float *alpha, const float *subtract,
+                         const float *theta, const float *theta_low, int apply_theta_low,
+                         uint32_t max_spikes, const float *in_scale /* nullable */,
+                         int reset_to_value, int64_t N, int64_t T)
+{
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < N; ++n) {
+        float v = v_init[n];
+        uint32_t act = 0;
+        const float sc = in_scale ? in_scale[n] : 1.0f;
+        for (int64_t t = 0; t < T; ++t) {
+            if (reset_to_value) { if (act) v = subtract[n]; }
+            else v = orc_fma(-(float)act, subtract[n], v);
+            volatile float x = sc * input[n * T + t];
+            v = orc_fma(v, alpha[n], x);
+            if (apply_theta_low && v < theta_low[n]) v = theta_low[n];
+            if (v >= theta[n]) act = orc_min_u32(orc_f2u_sat(v / theta[n]), max_spikes);
+            else act = 0;
+            spikes[n * T + t] = (float)act;
+            vmem[n * T + t] = v;
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------
+ * Float64 adjoint of a LIF layer with synaptic stage, i.e. of the chain the
+ * reference layer runs as leakyForward -> x*alpha -> (1-alpha)*i -> lifForward
+ * (sinabs/exodus/layers/lif.py:185-258):
+ *     i_t = a_s*i_{t-1} + s_s*x_t
+ *     v_t = clip( a_m*post(v_{t-1}) + s_m*i_t ),  post = v - c*spikes  (or the
+ *           reset value where a spike occurred when reset_to_value != 0)
+ * linearised at the given v_mem / spikes / i_syn (the values the forward
+ * produced), with ds/dv := surr (given, double).  Reverse sweep:
+ *     g_t = surr_t*go_t + gv_t                       (spike.py:266)
+ *     R_t = n_t*(g_t + f_t*R_{t+1}),  f_t = a_m*(1 - c*surr_t)   [subtract]
+ *                                     f_t = a_m*[spikes_t == 0]  [reset to value]
+ *     G_t = a_s*G_{t+1} + s_m*R_t + gis_t,   grad_x_t = s_s*G_t
+ * A gradient on the state after the last reset enters through the last step's
+ * go/gv (v_post = v - c*spikes; reset to value: passes only where no spike).
+ * Parameter gradients per neuron instance: a_m: sum_t R_t*post_{t-1} (+ the
+ * reference's first-step term, lif_kernels.h:219-238, subtract mode only),
+ * s_m: sum_t R_t*i_t, a_s: sum_t G_t*i_{t-1}, s_s: sum_t G_t*x_t.
+ * Every [N] / [N,T] argument is double; nullable ones are marked.
+ * ---------------------------------------------------------------------- */
+void orc_lif_syn_backward_f64(double *grad_input,
+                              double *grad_alpha_mem, double *grad_scale_mem,      /* nullable */
+                              double *grad_alpha_syn, double *grad_scale_syn,      /* nullable */
+                              double *grad_v_init, double *grad_i_init,            /* nullable */
+                              const double *grad_spikes, const double *grad_v_mem /* nullable */,
+                              const double *grad_v_last /* nullable */, const double *grad_i_syn /* nullable */,
+                              const double *grad_i_last /* nullable */,
+                              const double *v_mem, const double *spikes, const double *i_syn,
+                              const double *input, const double *surr,
+                              const double *v_init, const double *i_init,
+                              const double *alpha_syn, const double *scale_syn,
+                              const double *scale_mem, const double *alpha_mem,
+                              const double *subtract, const double *theta_low /* nullable */,
+                              int reset_to_value, int64_t N, int64_t T)
+{
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < N; ++n) {
+        const int64_t row = n * T;
+        const double am = alpha_mem[n], sm = scale_mem[n], as = alpha_syn[n], ss = scale_syn[n], c = subtract[n];
+        double R = 0.0, G = 0.0, R1 = 0.0, f0 = 0.0;
+        double gam = 0.0, gsm = 0.0, gas = 0.0, gss = 0.0;
+        for (int64_t t = T - 1; t >= 0; --t) {
+            const double v = v_mem[row + t], a = spikes[row + t], s = surr[row + t];
+            double go = grad_spikes[row + t];
+            double gv = grad_v_mem ? grad_v_mem[row + t] : 0.0;
+            double gis = grad_i_syn ? grad_i_syn[row + t] : 0.0;
+            if (t == T - 1) {
+                if (grad_v_last) {
+                    if (reset_to_value) gv += (a != 0.0) ? 0.0 : grad_v_last[n];
+                    else { go -= c * grad_v_last[n]; gv += grad_v_last[n]; }
+                }
+                if (grad_i_last) gis += grad_i_last[n];
+            }
+            const double nt = (theta_low && !(v > theta_low[n])) ? 0.0 : 1.0;
+            const double f = reset_to_value ? ((a != 0.0) ? 0.0 : am) : am * (1.0 - c * s);
+            R1 = R;
+            R = nt * (s * go + gv + f * R);
+            if (t == 0) f0 = f;
+            double post_prev, i_prev;
+            if (t > 0) {
+                const double vp = v_mem[row + t - 1], ap = spikes[row + t - 1];
+                post_prev = reset_to_value ? ((ap != 0.0) ? c : vp) : vp - c * ap;
+                i_prev = i_syn[row + t - 1];
+            } else {
+                post_prev = v_init[n];
+                i_prev = i_init[n];
+            }
+            gam += R * post_prev;
+            if (t == 0 && !reset_to_value && nt == 0.0) gam += v_init[n] * f0 * R1;
+            gsm += R * i_syn[row + t];
+            G = as * G + sm * R + gis;
+            gas += G * i_prev;
+            gss += G * input[row + t];
+            grad_input[row + t] = ss * G;
+        }
+        if (grad_alpha_mem) grad_alpha_mem[n] = gam;
+        if (grad_scale_mem) grad_scale_mem[n] = gsm;
+        if (grad_alpha_syn) grad_alpha_syn[n] = gas;
+        if (grad_scale_syn) grad_scale_syn[n] = gss;
+        if (grad_v_init) grad_v_init[n] = am * R;
+        if (grad_i_init) grad_i_init[n] = as * G;
+    }
+}

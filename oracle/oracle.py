@@ -158,6 +158,78 @@ def leaky_backward_f64(output_grad, alpha, inp=None, v_init=None):
     return gi, ag
 
 
+def lif_forward_ext(inp, v_init, alpha, subtract, theta, theta_low=None, max_spikes=None, in_scale=None,
+                    reset_to_value=False):
+    """cuda/lif_kernels.h:40-93 plus the two options of the B200 library: a per-neuron input scale (its product
+    with the input is rounded before the fused multiply-add, as a separate PyTorch multiplication in front of
+    the kernel gives, layers/lif.py:206-209) and "reset to `subtract` where a spike occurred" instead of
+    "subtract per spike" (not a reference mode).  Returns (spikes, v_mem)."""
+    inp = _f32(inp); N, T = inp.shape
+    v_init, alpha, subtract, theta = map(_f32, (v_init, alpha, subtract, theta))
+    apply_low = theta_low is not None
+    tl = _f32(theta_low) if apply_low else np.zeros(N, np.float32)
+    sc = None if in_scale is None else _f32(in_scale)
+    spikes = np.empty_like(inp); vmem = np.empty_like(inp)
+    ms = 0xFFFFFFFF if max_spikes is None else int(max_spikes)
+    _load().orc_lif_forward_ext(_p(spikes), _p(vmem), _p(inp), _p(v_init), _p(alpha), _p(subtract), _p(theta),
+                                _p(tl), ctypes.c_int(int(apply_low)), ctypes.c_uint32(ms), _p(sc),
+                                ctypes.c_int(int(bool(reset_to_value))), ctypes.c_int64(N), ctypes.c_int64(T))
+    return spikes, vmem
+
+
+def _f64(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float64)
+
+
+def lif_syn_backward_f64(grad_spikes, v_mem, spikes, i_syn, inp, surr, v_init, i_init, alpha_syn, scale_syn,
+                         scale_mem, alpha_mem, subtract, theta_low=None, reset_to_value=False, grad_v_mem=None,
+                         grad_v_last=None, grad_i_syn=None, grad_i_last=None):
+    """Float64 adjoint of the layer chain leaky -> scale -> spike step (layers/lif.py:185-258) linearised at the
+    given forward results; see orc_lif_syn_backward_f64.  All per-neuron arguments hold N values.
+
+    Returns dict(grad_input, grad_alpha_mem, grad_scale_mem, grad_alpha_syn, grad_scale_syn, grad_v_init,
+    grad_i_init), float64.
+    """
+    v_mem = _f64(v_mem); N, T = v_mem.shape
+    full = lambda a: None if a is None else _f64(a)
+    per_n = lambda a: _f64(np.broadcast_to(np.asarray(a, np.float64), (N,)))
+    args = dict(go=_f64(grad_spikes), gv=full(grad_v_mem), gvl=None if grad_v_last is None else per_n(grad_v_last),
+                gis=full(grad_i_syn), gil=None if grad_i_last is None else per_n(grad_i_last),
+                v=v_mem, a=_f64(spikes), i=_f64(i_syn), x=_f64(inp), s=_f64(surr),
+                v0=per_n(v_init), i0=per_n(i_init), as_=per_n(alpha_syn), ss=per_n(scale_syn), sm=per_n(scale_mem),
+                am=per_n(alpha_mem), c=per_n(subtract), lo=None if theta_low is None else per_n(theta_low))
+    out = {k: np.empty(N, np.float64) for k in ("grad_alpha_mem", "grad_scale_mem", "grad_alpha_syn", "grad_scale_syn",
+                                                "grad_v_init", "grad_i_init")}
+    out["grad_input"] = np.empty((N, T), np.float64)
+    d = lambda a: _p(a, _f64p)
+    _load().orc_lif_syn_backward_f64(
+        d(out["grad_input"]), d(out["grad_alpha_mem"]), d(out["grad_scale_mem"]), d(out["grad_alpha_syn"]),
+        d(out["grad_scale_syn"]), d(out["grad_v_init"]), d(out["grad_i_init"]),
+        d(args["go"]), d(args["gv"]), d(args["gvl"]), d(args["gis"]), d(args["gil"]),
+        d(args["v"]), d(args["a"]), d(args["i"]), d(args["x"]), d(args["s"]), d(args["v0"]), d(args["i0"]),
+        d(args["as_"]), d(args["ss"]), d(args["sm"]), d(args["am"]), d(args["c"]), d(args["lo"]),
+        ctypes.c_int(int(bool(reset_to_value))), ctypes.c_int64(N), ctypes.c_int64(T))
+    return out
+
+
+def surrogate_f64(kind: str, v, theta, p0, p1=1.0):
+    """The three closed-form surrogates evaluated in float64 (ground truth for the fused kernels).
+    kind: "single_exponential" (p0 = grad_width, p1 = grad_scale), "heaviside" (p0 = window),
+    "periodic_exponential" (p0 = grad_width, p1 = grad_scale)."""
+    v = np.asarray(v, np.float64); th = np.asarray(theta, np.float64)
+    if kind == "single_exponential":
+        w = th * p0
+        return p1 / w * np.exp(-np.abs(v - th) / w)
+    if kind == "heaviside":
+        return (v >= th - p0).astype(np.float64) / th
+    if kind == "periodic_exponential":
+        half = th / 2.0
+        u = v - half
+        w = np.where(v >= th, u - np.floor(u / th), u)
+        return p1 * np.exp(-np.abs(w - half) / p0) / th
+    raise ValueError(kind)
+
+
 # --------------------------------------------------------------------------
 # surrogate gradients (this project's definitions; float32 numpy)
 # --------------------------------------------------------------------------

@@ -156,3 +156,48 @@ def leaky_backward_scan(go, alpha, B, M, mode=_lib.PARAM_PER_N, out=None, inp=No
     torch.cuda.synchronize()
     cpu = lambda t: None if t is None else t.cpu().numpy()
     return from_dev(gi, B, M, L), cpu(ga), cpu(g0), cpu(gs)
+
+
+def lif_syn_forward(inp, v_init, i_init, a_syn, s_syn, s_mem, a_mem, subtract, theta, theta_low, B, M,
+                    mode=_lib.PARAM_PER_N, max_spikes=None, reset_mode=_lib.RESET_SUBTRACT):
+    """exb_lif_syn_forward on an [N,T] problem (time-major on the device).  Per-neuron arguments hold N values
+    consistent with `mode`.  Returns (spikes, v_mem, i_syn) as [N,T], v_post_last, i_last, spike count; None when
+    the library says the shape is not eligible for the fused kernel."""
+    N, T = inp.shape
+    L = _lib.LAYOUT_BTM
+    x = to_dev(inp, B, M, L)
+    spikes = torch.full_like(x, float("nan")); v_mem = torch.full_like(x, float("nan")); i_syn = torch.full_like(x, float("nan"))
+    v_post = torch.full((N,), float("nan"), device=DEV); i_last = torch.full((N,), float("nan"), device=DEV)
+    count = torch.zeros(1, dtype=torch.int64, device=DEV)
+    ok = _lib.lif_syn_forward(spikes, v_mem, i_syn, x, vec(v_init), vec(i_init), param(a_syn, mode, B, M),
+                              param(s_syn, mode, B, M), param(s_mem, mode, B, M), param(a_mem, mode, B, M),
+                              param(subtract, mode, B, M), param(theta, mode, B, M), param(theta_low, mode, B, M),
+                              max_spikes, reset_mode, v_post, i_last, count, B, T, M)
+    if not ok:
+        return None
+    torch.cuda.synchronize()
+    return (from_dev(spikes, B, M, L), from_dev(v_mem, B, M, L), from_dev(i_syn, B, M, L), v_post.cpu().numpy(),
+            i_last.cpu().numpy(), int(count.item()))
+
+
+def lif_syn_backward(go, v_mem, i_syn, v_init, i_init, a_syn, s_syn, s_mem, a_mem, subtract, theta, theta_low, B, M,
+                     mode=_lib.PARAM_PER_N, max_spikes=None, reset_mode=_lib.RESET_SUBTRACT, kind=_lib.SURR_GENERIC,
+                     p0=0.0, p1=0.0, surr=None, gv=None, g_vlast=None, g_isyn=None, g_ilast=None, want_params=True,
+                     want_init=True):
+    """exb_lif_syn_backward; [N,T] numpy in and out.  Returns dict of numpy arrays (absent outputs are None)."""
+    N, T = v_mem.shape
+    L = _lib.LAYOUT_BTM
+    nan_n = lambda: torch.full((N,), float("nan"), device=DEV)
+    gi = torch.full((B, T, M), float("nan"), device=DEV)
+    gam, gsm, gas, gss = (nan_n(), nan_n(), nan_n(), nan_n()) if want_params else (None,) * 4
+    gv0, gi0 = (nan_n(), nan_n()) if want_init else (None, None)
+    _lib.lif_syn_backward(gi, gam, gsm, gas, gss, gv0, gi0, to_dev(go, B, M, L), to_dev(gv, B, M, L), vec(g_vlast),
+                          to_dev(g_isyn, B, M, L), vec(g_ilast), to_dev(v_mem, B, M, L),
+                          to_dev(i_syn, B, M, L) if want_params else None, to_dev(surr, B, M, L), vec(v_init),
+                          vec(i_init), param(a_syn, mode, B, M), param(s_syn, mode, B, M), param(s_mem, mode, B, M),
+                          param(a_mem, mode, B, M), param(subtract, mode, B, M), param(theta, mode, B, M),
+                          param(theta_low, mode, B, M), max_spikes, reset_mode, kind, p0, p1, B, T, M)
+    torch.cuda.synchronize()
+    cpu = lambda t: None if t is None else t.cpu().numpy()
+    return dict(grad_input=from_dev(gi, B, M, L), grad_alpha_mem=cpu(gam), grad_scale_mem=cpu(gsm),
+                grad_alpha_syn=cpu(gas), grad_scale_syn=cpu(gss), grad_v_init=cpu(gv0), grad_i_init=cpu(gi0))

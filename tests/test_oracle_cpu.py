@@ -170,3 +170,88 @@ def test_golden_vectors(path):
         np.testing.assert_array_equal(orc.leaky_backward(g["go"], g["alpha"]), g["ref_grad_input"])
         ag = orc.leaky_backward_alpha(g["go"], g["ref_out"], g["v_init"], g["alpha"])
         assert rel_err(ag, g["ref_grad_alpha"]) < 1e-6
+
+
+def test_forward_ext_reduces_to_reference_forward():
+    """Without a scale and with the subtract reset the extended forward is the reference forward bit for bit; with a
+    scale it equals the reference forward on the pre-multiplied input (a separate rounded product)."""
+    cs = lif_case(5, N=40, T=60, clamp=True)
+    s0, v0 = orc.lif_forward(cs["inp"], cs["v_init"], cs["alpha"], cs["subtract"], cs["theta"], cs["theta_low"], 3)
+    s1, v1 = orc.lif_forward_ext(cs["inp"], cs["v_init"], cs["alpha"], cs["subtract"], cs["theta"], cs["theta_low"], 3)
+    np.testing.assert_array_equal(s0, s1); np.testing.assert_array_equal(v0, v1)
+    sc = np.random.default_rng(1).uniform(0.1, 2.0, 40).astype(np.float32)
+    s2, v2 = orc.lif_forward_ext(cs["inp"], cs["v_init"], cs["alpha"], cs["subtract"], cs["theta"], None, None, in_scale=sc)
+    s3, v3 = orc.lif_forward((sc[:, None] * cs["inp"]).astype(np.float32), cs["v_init"], cs["alpha"], cs["subtract"], cs["theta"])
+    np.testing.assert_array_equal(s2, s3); np.testing.assert_array_equal(v2, v3)
+
+
+def test_forward_ext_reset_to_value_by_hand():
+    x = np.array([[1.5, 0.2, 2.4, 0.1]], np.float32)
+    one = np.ones(1, np.float32)
+    s, v = orc.lif_forward_ext(x, np.zeros(1, np.float32), 0.5 * one, 0.25 * one, one, reset_to_value=True)
+    # t0: 1.5 -> spike, reset to .25; t1: .25*.5+.2=.325; t2: .325*.5+2.4=2.5625 -> 2 spikes, reset; t3: .25*.5+.1
+    np.testing.assert_array_equal(s, [[1, 0, 2, 0]])
+    np.testing.assert_allclose(v, [[1.5, 0.325, 2.5625, 0.225]], rtol=1e-6)
+
+
+@pytest.mark.parametrize("reset_to_value", [False, True])
+@pytest.mark.parametrize("surrogate", ["single_exponential", "heaviside", "periodic_exponential"])
+def test_synaptic_adjoint_f64_equals_bptt(reset_to_value, surrogate):
+    """The float64 adjoint of the two-stage layer chain (synapse -> scale -> spiking membrane) equals
+    back-propagation through the time-stepped loop in float64: input gradient, both initial states and all four
+    parameter gradients, with gradients arriving on spikes, v_mem, i_syn and on both final states."""
+    import torch
+    from oracle.torch_loop import lif_loop
+    from sinabs_exodus_b200.compat import activation as sa
+
+    fn, p0 = {"single_exponential": (sa.SingleExponential(0.7, 1.3), 0.7), "heaviside": (sa.Heaviside(0.6), 0.6),
+              "periodic_exponential": (sa.PeriodicExponential(0.4, 0.9), 0.4)}[surrogate]
+    p1 = getattr(fn, "grad_scale", 1.0)
+    rng = np.random.default_rng(17)
+    B, T, M = 2, 40, 7
+    dt = torch.float64
+    x = torch.tensor(1.5 + 4.0 * rng.standard_normal((B, T, M)), dtype=dt, requires_grad=True)
+    a_mem = torch.tensor(rng.uniform(0.4, 0.9, M), dtype=dt, requires_grad=True)
+    a_syn = torch.tensor(rng.uniform(0.5, 0.95, M), dtype=dt, requires_grad=True)
+    v0 = torch.tensor(rng.uniform(-0.3, 0.3, (B, M)), dtype=dt, requires_grad=True)
+    i0 = torch.tensor(rng.uniform(-0.3, 0.3, (B, M)), dtype=dt, requires_grad=True)
+    theta = torch.tensor(rng.uniform(0.5, 1.1, M), dtype=dt)
+    c = torch.tensor(rng.uniform(0.2, 0.5, M), dtype=dt)
+    lo = torch.tensor(-rng.uniform(0.1, 0.4, M), dtype=dt)
+    res = lif_loop(x, a_mem, v0, theta, c, lo, fn, 2, reset_value=None, alpha_syn=a_syn, i_syn_init=i0,
+                   norm_input=True, decay_early=True) if not reset_to_value else None
+    if reset_to_value:
+        # per-neuron reset values are not an option of the loop: use one value
+        c = torch.full((M,), 0.15, dtype=dt)
+        res = lif_loop(x, a_mem, v0, theta, None, lo, fn, 2, reset_value=0.15, alpha_syn=a_syn, i_syn_init=i0,
+                       norm_input=True, decay_early=True)
+    w = {k: torch.tensor(rng.standard_normal((B, T, M)), dtype=dt) for k in ("s", "v", "i")}
+    wl = {k: torch.tensor(rng.standard_normal((B, M)), dtype=dt) for k in ("v", "i")}
+    loss = ((res["spikes"] * w["s"]).sum() + (res["v_mem_pre"] * w["v"]).sum() + (res["i_syn"] * w["i"]).sum()
+            + (res["v_last"] * wl["v"]).sum() + (res["i_last"] * wl["i"]).sum())
+    loss.backward()
+
+    nt = lambda t: t.detach().permute(0, 2, 1).reshape(B * M, T).numpy()       # (B,T,M) -> [N,T]
+    per_n = lambda t: np.tile(t.detach().numpy(), B)                           # (M,) -> (N,)
+    v = nt(res["v_mem_pre"])
+    surr = orc.surrogate_f64(surrogate, v, per_n(theta)[:, None], p0, p1)
+    got = orc.lif_syn_backward_f64(
+        nt(w["s"]), v, nt(res["spikes"]), nt(res["i_syn"]), nt(x), surr, v0.detach().reshape(-1).numpy(),
+        i0.detach().reshape(-1).numpy(), per_n(a_syn), per_n(a_syn), per_n(1.0 - a_mem), per_n(a_mem), per_n(c),
+        per_n(lo), reset_to_value, grad_v_mem=nt(w["v"]), grad_v_last=wl["v"].reshape(-1).numpy(),
+        grad_i_syn=nt(w["i"]), grad_i_last=wl["i"].reshape(-1).numpy())
+    assert (nt(res["spikes"]) > 1).any() and (v <= per_n(lo)[:, None]).any()
+    tol = 1e-10
+    assert rel_err(got["grad_input"], nt(x.grad)) < tol
+    assert rel_err(got["grad_v_init"], v0.grad.reshape(-1).numpy()) < tol
+    assert rel_err(got["grad_i_init"], i0.grad.reshape(-1).numpy()) < tol
+    # parameters: alpha_mem enters as decay and, through norm_input, as scale 1 - alpha_mem; alpha_syn as decay
+    # and, through decay_early, as the input scale.  Rows whose first step is clipped carry the reference's extra
+    # first-step term, which back-propagation through the loop does not have: leave those neurons out.
+    first_clipped = (v[:, 0] <= per_n(lo)).reshape(B, M).any(0)
+    ok = ~first_clipped
+    g_am = (got["grad_alpha_mem"] - got["grad_scale_mem"]).reshape(B, M).sum(0)
+    g_as = (got["grad_alpha_syn"] + got["grad_scale_syn"]).reshape(B, M).sum(0)
+    assert ok.any()
+    assert rel_err(g_am[ok], a_mem.grad.numpy()[ok]) < tol
+    assert rel_err(g_as, a_syn.grad.numpy()) < tol
