@@ -67,11 +67,23 @@ const char *exb_status_string(int status);
 
 /* Kernels that stage data through TMA wait on shared-memory barriers; every such
  * wait is bounded.  If one ever runs out, the kernel records it in a device
- * status word and returns normally.  exb_device_status waits for `stream`,
+ * status word, writes NaN to the per-neuron results of the affected neurons
+ * (final states, initial-state and parameter gradients, the output sum) and
+ * returns normally.  exb_device_status waits for `stream`,
  * returns EXB_ERR_TIMEOUT if that happened since the last query (and clears the
  * word), EXB_OK otherwise.  No counterpart in the reference, whose kernels
  * never wait (cuda/lif_kernels.h, cuda/leaky_kernels.h). */
 int exb_device_status(int device, void *stream);
+
+/* Sets, on `device`, how many polls a bounded wait may take before it gives up (0 = the default,
+ * 2^22, several seconds), and a diagnostic switch: with withhold_scan_flags != 0 the segments of
+ * the time-parallel leaky scan (exb_leaky_*_scan*) do not raise their ready flags, so every
+ * dependent segment's wait runs out.  That is how the give-up path can be exercised without any
+ * fault: the kernel returns normally, exb_device_status reports EXB_ERR_TIMEOUT once, and the
+ * per-neuron results the wait belonged to (final states, parameter gradients, output sum) are
+ * NaN.  Applies to kernels launched afterwards; call it with (device, 0, 0) to restore the defaults.
+ * Synchronous (a constant upload); not for the steady state.  No counterpart in the reference. */
+int exb_set_wait_limit(int device, uint32_t polls, int withhold_scan_flags);
 
 /* Forward spike scan.  Replaces lifForward (cuda/bindings.cu:14-70, kernel
  * cuda/lif_kernels.h:40-93).  Per neuron and step:
@@ -252,7 +264,9 @@ int exb_leaky_backward_scan(float *grad_input, float *grad_alpha, float *grad_in
  *    is rejected with EXB_ERR_ARG and a message that says how much was needed; shapes the scan
  *    does not apply to give EXB_ERR_UNSUPPORTED, as with exb_leaky_forward_scan;
  *  - the first call on each device looks up the array's device address (once per device, with
- *    that device current); make that first call before any stream capture begins;
+ *    that device current) and, like the first call of any entry point, makes the CUDA runtime load
+ *    the kernel; make that first call before any stream capture begins and before the point from
+ *    which the host may no longer allocate;
  *  - all calls on a device share the one array, and it keeps what the previous call left in it.
  *    Each call clears the part that must start from zero (work ticket and ready flags) on
  *    `stream` ahead of its kernel, so calls issued one after another on a stream are fine.  Two
@@ -260,6 +274,8 @@ int exb_leaky_backward_scan(float *grad_input, float *grad_alpha, float *grad_in
  *    would use the same flags and aggregates and corrupt each other: do not overlap them.
  * Arguments and results are those of exb_leaky_forward_scan without the workspace pair. */
 #define EXB_STATIC_SCRATCH_BYTES (1u << 20)
+/* The size the loaded library was built with (for bindings that cannot see this header). */
+int64_t exb_static_scratch_bytes(void);
 int exb_leaky_forward_scan_static(float *out, const float *input, const float *v_init,
                                   const float *alpha, int alpha_mode,
                                   const float *in_scale, int in_scale_mode,

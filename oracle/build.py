@@ -18,8 +18,10 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 BUILD_DIR = os.path.join(HERE, "_build")
 REF_DIR = os.path.join(HERE, "_ref")
-# checkout of the reference project (read-only); override with EXODUS_REFERENCE_ROOT
-REFERENCE_ROOT = os.environ.get("EXODUS_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+# Checkout of the reference project (read-only): the EXODUS_REFERENCE_ROOT environment variable, else a
+# directory named `reference` beside this repository.  Absent -> the reference kernels are simply not built.
+REFERENCE_ROOT = os.environ.get("EXODUS_REFERENCE_ROOT",
+                                os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 
 
 def _newer(target: str, *sources: str) -> bool:

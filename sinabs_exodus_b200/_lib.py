@@ -36,10 +36,10 @@ _f = ctypes.c_float
 _lib: Optional[ctypes.CDLL] = None
 
 EXPORTS = (
-    "exb_version", "exb_last_error", "exb_status_string", "exb_device_status",
+    "exb_version", "exb_last_error", "exb_status_string", "exb_device_status", "exb_set_wait_limit",
     "exb_lif_forward", "exb_lif_forward_record", "exb_lif_backward", "exb_leaky_forward", "exb_leaky_backward",
     "exb_leaky_scan_workspace_bytes", "exb_leaky_forward_scan", "exb_leaky_backward_scan",
-    "exb_leaky_forward_scan_static", "exb_lif_syn_forward", "exb_lif_syn_backward",
+    "exb_leaky_forward_scan_static", "exb_static_scratch_bytes", "exb_lif_syn_forward", "exb_lif_syn_backward",
 )
 
 
@@ -62,6 +62,8 @@ def load() -> ctypes.CDLL:
     lib.exb_status_string.argtypes = [_i]
     lib.exb_device_status.restype = _i
     lib.exb_device_status.argtypes = [_i, _vp]
+    lib.exb_set_wait_limit.restype = _i
+    lib.exb_set_wait_limit.argtypes = [_i, _u32, _i]
     geometry = [_i64, _i64, _i64, _i, _i, _vp]
     lib.exb_lif_forward.restype = _i
     lib.exb_lif_forward.argtypes = [_vp, _vp, _vp, _vp,
@@ -94,6 +96,8 @@ def load() -> ctypes.CDLL:
     lib.exb_lif_syn_forward.argtypes = [_vp] * 6 + syn_params + [_u32, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i, _vp]
     lib.exb_lif_syn_backward.restype = _i
     lib.exb_lif_syn_backward.argtypes = ([_vp] * 17 + syn_params + [_u32, _i, _i, _f, _f, _i64, _i64, _i64, _i, _vp])
+    lib.exb_static_scratch_bytes.restype = _i64
+    lib.exb_static_scratch_bytes.argtypes = []
     lib.exb_leaky_forward_scan_static.restype = _i
     lib.exb_leaky_forward_scan_static.argtypes = [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _i, _vp]
     _lib = lib
@@ -111,10 +115,35 @@ def _check(status: int, what: str) -> None:
             f"{what} failed: {lib.exb_status_string(status).decode()} -- {lib.exb_last_error().decode()}")
 
 
+# Opt-in: query the device status after every launch.  Each query waits for the stream, so this is for
+# debugging and for hosts that prefer a loud failure to speed; off unless EXODUS_B200_CHECK_STATUS=1 or
+# set_status_checks(True).  Without it a wait that ran out shows as NaN in the layer state and in the
+# per-neuron gradients, and in device_status() whenever the caller polls it.
+_check_every_call = os.environ.get("EXODUS_B200_CHECK_STATUS", "0") == "1"
+
+
+def set_status_checks(enabled: bool) -> None:
+    """Poll ``exb_device_status`` after every kernel launch (synchronises the stream each time)."""
+    global _check_every_call
+    _check_every_call = bool(enabled)
+
+
+def _after_launch(dev: torch.device) -> None:
+    if _check_every_call and not torch.cuda.is_current_stream_capturing():
+        device_status(dev)
+
+
 def device_status(device: Optional[torch.device] = None) -> None:
     """Wait for the current stream of ``device`` and raise if a bounded device-side wait ran out."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     _check(load().exb_device_status(dev.index, _stream(dev)), "exb_device_status")
+
+
+def set_wait_limit(polls: int = 0, withhold_scan_flags: bool = False, device: Optional[torch.device] = None) -> None:
+    """``exb_set_wait_limit``: poll limit of the kernels' bounded waits (0 = default) and the diagnostic switch
+    that keeps the time-parallel scan's ready flags down (so that its waits run out)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    _check(load().exb_set_wait_limit(dev.index, int(polls), int(bool(withhold_scan_flags))), "exb_set_wait_limit")
 
 
 def ptr(t: Optional[torch.Tensor]):
@@ -177,9 +206,11 @@ def lif_forward(spikes, v_mem, inp, v_init, in_scale: Tuple, alpha: Tuple, subtr
     if v_post is None:
         st = load().exb_lif_forward(ptr(spikes), ptr(v_mem), ptr(inp), ptr(v_init), *tail)
         _check(st, "exb_lif_forward")
+        _after_launch(dev)
     else:
         st = load().exb_lif_forward_record(ptr(spikes), ptr(v_mem), ptr(v_post), ptr(inp), ptr(v_init), *tail)
         _check(st, "exb_lif_forward_record")
+        _after_launch(dev)
 
 
 def lif_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, grad_v_mem, grad_v_last,
@@ -200,6 +231,7 @@ def lif_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, gra
         ms, reset_mode, surr_kind, float(p0), float(p1),
         B, T, M, layout, dev.index, _stream(dev))
     _check(st, "exb_lif_backward")
+    _after_launch(dev)
 
 
 def leaky_forward(out, inp, v_init, alpha: Tuple, in_scale: Tuple, v_last, B: int, T: int, M: int,
@@ -212,6 +244,7 @@ def leaky_forward(out, inp, v_init, alpha: Tuple, in_scale: Tuple, v_last, B: in
                                   ptr(in_scale[0]), in_scale[1], ptr(v_last), _ptr_f64(out_sum),
                                   B, T, M, layout, dev.index, _stream(dev))
     _check(st, "exb_leaky_forward")
+    _after_launch(dev)
 
 
 def leaky_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad_v_last, out, inp, v_init,
@@ -225,6 +258,7 @@ def leaky_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad
                                    ptr(alpha[0]), alpha[1], ptr(in_scale[0]), in_scale[1],
                                    B, T, M, layout, dev.index, _stream(dev))
     _check(st, "exb_leaky_backward")
+    _after_launch(dev)
 
 
 def leaky_scan_workspace_bytes(B: int, T: int, M: int) -> int:
@@ -240,6 +274,7 @@ def leaky_forward_scan(out, inp, v_init, alpha: Tuple, in_scale: Tuple, v_last, 
                                        workspace.data_ptr(), workspace.numel() * workspace.element_size(),
                                        B, T, M, dev.index, _stream(dev))
     _check(st, "exb_leaky_forward_scan")
+    _after_launch(dev)
 
 
 def leaky_backward_scan(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad_v_last, out, inp, v_init,
@@ -252,9 +287,18 @@ def leaky_backward_scan(grad_input, grad_alpha, grad_init, grad_scale, grad_out,
                                         workspace.data_ptr(), workspace.numel() * workspace.element_size(),
                                         B, T, M, dev.index, _stream(dev))
     _check(st, "exb_leaky_backward_scan")
+    _after_launch(dev)
 
 
-STATIC_SCRATCH_BYTES = 1 << 20
+def static_scratch_bytes() -> int:
+    """Size of the library's built-in scratch array (``EXB_STATIC_SCRATCH_BYTES``), asked from the library."""
+    return int(load().exb_static_scratch_bytes())
+
+
+def __getattr__(name: str):
+    if name == "STATIC_SCRATCH_BYTES":      # kept as a module attribute; the value lives in the library
+        return static_scratch_bytes()
+    raise AttributeError(name)
 
 
 def leaky_forward_scan_static(out, inp, v_init, alpha: Tuple, in_scale: Tuple, v_last, B: int, T: int, M: int) -> None:
@@ -269,6 +313,7 @@ def leaky_forward_scan_static(out, inp, v_init, alpha: Tuple, in_scale: Tuple, v
                                               ptr(in_scale[0]), in_scale[1], ptr(v_last),
                                               B, T, M, dev.index, _stream(dev))
     _check(st, "exb_leaky_forward_scan_static")
+    _after_launch(dev)
 
 
 def _pm(spec):
@@ -289,6 +334,7 @@ def lif_syn_forward(spikes, v_mem, i_syn, inp, v_init, i_init, alpha_syn: Tuple,
     if st == 4:
         return False
     _check(st, "exb_lif_syn_forward")
+    _after_launch(dev)
     return True
 
 
@@ -309,3 +355,4 @@ def lif_syn_backward(grad_input, grad_alpha_mem, grad_scale_mem, grad_alpha_syn,
         *_pm(alpha_syn), *_pm(scale_syn), *_pm(scale_mem), *_pm(alpha_mem), *_pm(subtract), *_pm(theta), *_pm(theta_low),
         ms, reset_mode, surr_kind, float(p0), float(p1), B, T, M, dev.index, _stream(dev))
     _check(st, "exb_lif_syn_backward")
+    _after_launch(dev)

@@ -1,6 +1,8 @@
 // C-ABI front end: argument validation, device selection, dispatch.
-// Nothing here allocates device memory or keeps state between calls; the only
-// per-thread state is the text of the last error.
+// Nothing here allocates device memory.  State kept between calls: the text of the calling
+// thread's last error (host); per device, the status words and the poll limit of the bounded
+// waits, and the built-in scratch array of exb_leaky_forward_scan_static (all in the kernel
+// translation units).
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -52,6 +54,19 @@ int check_geometry(int64_t B, int64_t T, int64_t M, int layout)
     return EXB_OK;
 }
 
+// Every tensor and vector is float32 (or wider, for the counters): an address that is not a multiple of 4
+// cannot be one, and the kernels would fault on it.
+template <typename... P>
+bool all_aligned4(const P *...ptrs)
+{
+    return (((reinterpret_cast<uintptr_t>(static_cast<const void *>(ptrs)) & 3u) == 0) && ...);
+}
+
+int misaligned(const char *who)
+{
+    return fail(EXB_ERR_ALIGN, "%s: every tensor must be aligned to its element size (float32: 4 bytes; counters: 8)", who);
+}
+
 int launch_status(cudaError_t e, const char *what)
 {
     if (e == cudaSuccess) return EXB_OK;
@@ -95,6 +110,17 @@ int exb_device_status(int device, void *stream)
     return EXB_OK;
 }
 
+int exb_set_wait_limit(int device, uint32_t polls, int withhold_scan_flags)
+{
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_set_wait_limit: cannot select device %d", device);
+    cudaError_t e = exb::set_wait_limit(polls, withhold_scan_flags != 0);
+    if (e == cudaSuccess) e = exb::set_wait_limit_lif_bwd(polls);
+    if (e == cudaSuccess) e = exb::set_wait_limit_lif_syn(polls);
+    if (e != cudaSuccess) return fail(EXB_ERR_LAUNCH, "exb_set_wait_limit: %s", cudaGetErrorString(e));
+    return EXB_OK;
+}
+
 }  // extern "C"
 
 static int lif_forward_impl(const char *who, float *spikes, float *v_mem, float *v_post, const float *input, const float *v_init,
@@ -120,6 +146,9 @@ static int lif_forward_impl(const char *who, float *spikes, float *v_mem, float 
         return fail(EXB_ERR_ARG, "%s: reset-to-value needs the value in `subtract`", who);
     if (v_post && layout != EXB_LAYOUT_BTM)
         return fail(EXB_ERR_UNSUPPORTED, "%s: the post-reset record is written by the time-major kernels only", who);
+    if (!all_aligned4(spikes, v_mem, v_post, input, v_init, in_scale, alpha, subtract, theta, theta_low, v_post_last) ||
+        (reinterpret_cast<uintptr_t>(spike_count) & 7u))
+        return misaligned(who);
     if (B == 0 || M == 0 || T == 0) return EXB_OK;
     DeviceGuard guard(device);
     if (!guard.ok) return fail(EXB_ERR_DEVICE, "%s: cannot select device %d", who, device);
@@ -202,6 +231,9 @@ int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, flo
         return fail(EXB_ERR_ARG, "exb_lif_backward: the generic surrogate needs the `surr` tensor");
     if (grad_scale && !input && !in_scale)
         return fail(EXB_ERR_ARG, "exb_lif_backward: grad_scale without `input` is rebuilt from v_mem and needs in_scale");
+    if (!all_aligned4(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, grad_v_mem, grad_v_last, v_mem, surr,
+                      v_init, input, in_scale, alpha, subtract, theta, theta_low))
+        return misaligned("exb_lif_backward");
     if (B == 0 || M == 0 || T == 0) return EXB_OK;
     DeviceGuard guard(device);
     if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_lif_backward: cannot select device %d", device);
@@ -233,6 +265,8 @@ int exb_leaky_forward(float *out, const float *input, const float *v_init,
     if (!out || !input || !alpha) return fail(EXB_ERR_ARG, "exb_leaky_forward: out, input and alpha are required");
     if (!mode_ok(alpha_mode) || (in_scale && !mode_ok(in_scale_mode)))
         return fail(EXB_ERR_ARG, "exb_leaky_forward: bad parameter mode");
+    if (!all_aligned4(out, input, v_init, alpha, in_scale, v_last) || (reinterpret_cast<uintptr_t>(out_sum) & 7u))
+        return misaligned("exb_leaky_forward");
     if (B == 0 || M == 0 || T == 0) return EXB_OK;
     DeviceGuard guard(device);
     if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_leaky_forward: cannot select device %d", device);
@@ -262,6 +296,8 @@ int exb_leaky_backward(float *grad_input, float *grad_alpha, float *grad_init, f
         return fail(EXB_ERR_ARG, "exb_leaky_backward: bad parameter mode");
     if (grad_alpha && !out) return fail(EXB_ERR_ARG, "exb_leaky_backward: grad_alpha needs `out`");
     if (grad_scale && !input) return fail(EXB_ERR_ARG, "exb_leaky_backward: grad_scale needs `input`");
+    if (!all_aligned4(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad_v_last, out, input, v_init, alpha, in_scale))
+        return misaligned("exb_leaky_backward");
     if (B == 0 || M == 0 || T == 0) return EXB_OK;
     DeviceGuard guard(device);
     if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_leaky_backward: cannot select device %d", device);
@@ -292,6 +328,8 @@ int exb_leaky_forward_scan(float *out, const float *input, const float *v_init,
     if (!mode_ok(alpha_mode) || (in_scale && !mode_ok(in_scale_mode)))
         return fail(EXB_ERR_ARG, "exb_leaky_forward_scan: bad parameter mode");
     if (!workspace) return fail(EXB_ERR_ARG, "exb_leaky_forward_scan: workspace is required");
+    if (!all_aligned4(out, input, v_init, alpha, in_scale, v_last) || (reinterpret_cast<uintptr_t>(out_sum) & 7u))
+        return misaligned("exb_leaky_forward_scan");
     if (B == 0 || M == 0 || T == 0) return EXB_OK;
     DeviceGuard guard(device);
     if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_leaky_forward_scan: cannot select device %d", device);
@@ -325,6 +363,8 @@ int exb_leaky_backward_scan(float *grad_input, float *grad_alpha, float *grad_in
     if (grad_alpha && !out) return fail(EXB_ERR_ARG, "exb_leaky_backward_scan: grad_alpha needs `out`");
     if (grad_scale && !input) return fail(EXB_ERR_ARG, "exb_leaky_backward_scan: grad_scale needs `input`");
     if (!workspace) return fail(EXB_ERR_ARG, "exb_leaky_backward_scan: workspace is required");
+    if (!all_aligned4(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad_v_last, out, input, v_init, alpha, in_scale))
+        return misaligned("exb_leaky_backward_scan");
     if (B == 0 || M == 0 || T == 0) return EXB_OK;
     DeviceGuard guard(device);
     if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_leaky_backward_scan: cannot select device %d", device);
@@ -341,6 +381,8 @@ int exb_leaky_backward_scan(float *grad_input, float *grad_alpha, float *grad_in
     return EXB_OK;
 }
 
+int64_t exb_static_scratch_bytes(void) { return (int64_t)exb::leaky_scan_static_capacity(); }
+
 // Time-parallel leaky forward for callers that cannot supply scratch memory (see the header).
 // Nothing is allocated here or below: the workspace is a fixed array inside the library.
 int exb_leaky_forward_scan_static(float *out, const float *input, const float *v_init,
@@ -354,6 +396,7 @@ int exb_leaky_forward_scan_static(float *out, const float *input, const float *v
         return fail(EXB_ERR_ARG, "exb_leaky_forward_scan_static: out, input and alpha are required");
     if (!mode_ok(alpha_mode) || (in_scale && !mode_ok(in_scale_mode)))
         return fail(EXB_ERR_ARG, "exb_leaky_forward_scan_static: bad parameter mode");
+    if (!all_aligned4(out, input, v_init, alpha, in_scale, v_last)) return misaligned("exb_leaky_forward_scan_static");
     if (B == 0 || M == 0 || T == 0) return EXB_OK;
     const int64_t need = exb::leaky_scan_workspace_bytes(B, T, M);
     if (need == 0)
@@ -405,6 +448,9 @@ int exb_lif_syn_forward(float *spikes, float *v_mem, float *i_syn, const float *
         return fail(EXB_ERR_ARG, "exb_lif_syn_forward: bad reset mode %d", reset_mode);
     if (reset_mode == EXB_RESET_TO_VALUE && !subtract)
         return fail(EXB_ERR_ARG, "exb_lif_syn_forward: reset-to-value needs the value in `subtract`");
+    if (!all_aligned4(spikes, v_mem, i_syn, input, v_init, i_init, alpha_syn, scale_syn, scale_mem, alpha_mem, subtract,
+                      theta, theta_low, v_post_last, i_last) || (reinterpret_cast<uintptr_t>(spike_count) & 7u))
+        return misaligned("exb_lif_syn_forward");
     if (B == 0 || M == 0 || T == 0) return EXB_OK;
     DeviceGuard guard(device);
     if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_lif_syn_forward: cannot select device %d", device);
@@ -464,6 +510,10 @@ int exb_lif_syn_backward(float *grad_input,
     if (ngrads != 0 && ngrads != 4)
         return fail(EXB_ERR_ARG, "exb_lif_syn_backward: pass all four parameter-gradient outputs or none");
     if (ngrads == 4 && !i_syn) return fail(EXB_ERR_ARG, "exb_lif_syn_backward: parameter gradients need `i_syn`");
+    if (!all_aligned4(grad_input, grad_alpha_mem, grad_scale_mem, grad_alpha_syn, grad_scale_syn, grad_v_init, grad_i_init,
+                      grad_spikes, grad_v_mem, grad_v_last, grad_i_syn, grad_i_last, v_mem, i_syn, surr, v_init, i_init,
+                      alpha_syn, scale_syn, scale_mem, alpha_mem, subtract, theta, theta_low))
+        return misaligned("exb_lif_syn_backward");
     if (B == 0 || M == 0 || T == 0) return EXB_OK;
     DeviceGuard guard(device);
     if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_lif_syn_backward: cannot select device %d", device);

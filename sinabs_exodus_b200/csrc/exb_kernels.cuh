@@ -94,6 +94,11 @@ cudaError_t launch_leaky_backward_scan(const LeakyBwdArgs &a, void *workspace, i
 size_t leaky_scan_static_capacity();
 cudaError_t launch_leaky_forward_scan_static(const LeakyFwdArgs &a, int device, cudaStream_t s, bool *used);
 cudaError_t read_device_status(cudaStream_t s, unsigned int *out);
+// Poll limit of the bounded waits (0 = default) on the current device, one setter per translation unit with
+// such waits; the first also sets the diagnostic switch that keeps the time-parallel scan's ready flags down.
+cudaError_t set_wait_limit(unsigned int polls, bool withhold_scan_flags);
+cudaError_t set_wait_limit_lif_bwd(unsigned int polls);
+cudaError_t set_wait_limit_lif_syn(unsigned int polls);
 cudaError_t read_device_status_lif_bwd(cudaStream_t s, unsigned int *out);
 // EXB_DISABLE_TMA=1 in the environment forces the plain-load kernels (debugging aid).
 bool tma_enabled();

@@ -59,12 +59,19 @@ __device__ __forceinline__ void st_release(unsigned int *p, unsigned int v)
     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// Diagnostic switch (exb_set_wait_limit): when non-zero no segment raises its ready flag, so every
+// dependent segment's bounded wait runs out.  It exists so that the give-up path (status word, NaN
+// poisoning, orderly return) can be exercised without any fault; it is 0 unless a test sets it.
+static __constant__ unsigned int c_exb_scan_withhold_flags = 0u;
+
 // Bounded spin on a ready flag written by another CTA of the same launch.
 __device__ __forceinline__ bool wait_flag(const unsigned int *p)
 {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-        if (ld_acquire(p) != 0u) return true;
+    if (ld_acquire(p) != 0u) return true;
+    const uint32_t limit = c_exb_wait_limit;
+    for (uint32_t i = 1; i < limit; ++i) {
         __nanosleep(64);
+        if (ld_acquire(p) != 0u) return true;
     }
     return false;
 }
@@ -139,7 +146,7 @@ __device__ __forceinline__ void publish_aggregate(const ScanWs &ws, Ring *ring, 
     }
     __threadfence();
     consumer_barrier(NW * 32);      // reached by every consumer thread, whatever `ok` is
-    if (threadIdx.x == 0 && !ring->aborted) st_release(ws.flags + slot, 1u);
+    if (threadIdx.x == 0 && !ring->aborted && c_exb_scan_withhold_flags == 0u) st_release(ws.flags + slot, 1u);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -252,11 +259,13 @@ leaky_fwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A
             release_chunk(ring, pos, lane);
             pos.advance(pc.stages);
         }
-        if (ok && valid && last_seg && A.v_last) {
+        // The last segment depends on every other one: if any wait ran out, its own did too, and the
+        // state it leaves is NaN so that the failure cannot go unnoticed downstream.
+        if (valid && last_seg && A.v_last) {
 #pragma unroll
-            for (int j = 0; j < V; ++j) A.v_last[n + j] = v[j];
+            for (int j = 0; j < V; ++j) A.v_last[n + j] = ok ? v[j] : NAN;
         }
-        if (A.out_sum) warp_add_f64(A.out_sum, (ok && valid) ? total : 0.0, lane);
+        if (A.out_sum) warp_add_f64(A.out_sum, valid ? (ok ? total : (double)NAN) : 0.0, lane);
     }
     ring_finish(ring, pc.stages);
 }
@@ -394,9 +403,10 @@ leaky_bwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A
             release_chunk(ring, pos, lane);
             pos.advance(pc.stages);
         }
-        if (ok && valid) {
+        if (valid) {
 #pragma unroll
             for (int j = 0; j < V; ++j) {
+                if (!ok) { ag[j] = NAN; sgr[j] = NAN; Gv[j] = NAN; }      // gave up: poison what depends on this segment
                 if (first_in_time) {
                     if (A.grad_init) A.grad_init[n + j] = __fmul_rn(al[j], Gv[j]);
                     if (WA) ag[j] = __fmaf_rn(Gv[j], A.v_init ? __ldg(A.v_init + n + j) : 0.0f, ag[j]);

@@ -9,9 +9,10 @@
 // the number of resident threads, so small problems and the last partial wave
 // of large ones still keep HBM busy.
 //
-// Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the kernel
-// records a code in a device status word (read by exb_device_status), stops
-// issuing work, waits -- again bounded -- for its own copies in flight, and
+// Every wait on an mbarrier is bounded: after a limit of polls (WAIT_LIMIT unless
+// exb_set_wait_limit changed it) the kernel records a code in a device status
+// word (read by exb_device_status), stops issuing work, poisons its per-neuron
+// results with NaN, waits -- again bounded -- for its own copies in flight, and
 // returns normally.  No multicast loads are used anywhere.
 #pragma once
 
@@ -29,6 +30,10 @@ static __device__ unsigned int g_exb_status = 0;
 enum { EXB_STATUS_FULL_WAIT = 1, EXB_STATUS_EMPTY_WAIT = 2, EXB_STATUS_DRAIN_WAIT = 3, EXB_STATUS_LOOKBACK_WAIT = 4 };
 
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+// Polls a wait may take before it gives up.  One copy per translation unit, like the status word;
+// exb_set_wait_limit writes all of them.  The drain at the end of a kernel always uses WAIT_LIMIT.
+static __constant__ unsigned int c_exb_wait_limit = WAIT_LIMIT;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {
@@ -56,21 +61,44 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
                  : "memory");
 }
 
-// Bounded wait for the completion of the phase with the given parity.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0u;
+}
+
+// Bounded wait for the completion of the phase with the given parity.  The limit is read only
+// when the first poll fails.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
 {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (ok) return true;
-    }
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint32_t limit = c_exb_wait_limit;
+    for (uint32_t i = 1; i < limit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
     return false;
+}
+
+// The same with the compile-time limit: for the drain of a kernel that gave up, which must outlast
+// its own copies in flight whatever limit the host has set.
+__device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity)
+{
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+// Host side: set this translation unit's copy of the limit on the current device (0 = default).
+static inline cudaError_t set_wait_limit_here(unsigned int polls)
+{
+    const unsigned int v = polls ? polls : WAIT_LIMIT;
+    return cudaMemcpyToSymbol(c_exb_wait_limit, &v, sizeof(v));
 }
 
 __device__ __forceinline__ void report_timeout(unsigned int code) { atomicCAS(&g_exb_status, 0u, code); }
@@ -125,7 +153,7 @@ __device__ __forceinline__ void ring_finish(Ring *r, int stages)
         for (int s = 0; s < stages; ++s) {
             int k = issued - 1;
             while (k >= 0 && (k % stages) != s) --k;
-            if (k >= 0 && !mbar_wait(smem_u32(&r->full[s]), (uint32_t)((k / stages) & 1)))
+            if (k >= 0 && !mbar_wait_drain(smem_u32(&r->full[s]), (uint32_t)((k / stages) & 1)))
                 report_timeout(EXB_STATUS_DRAIN_WAIT);
         }
     }

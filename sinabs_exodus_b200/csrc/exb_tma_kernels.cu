@@ -86,9 +86,9 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
             release_chunk(ring, pos, lane);
             pos.advance(pc.stages);
         }
-        if (ok && valid && A.v_post_last) {
+        if (valid && A.v_post_last) {      // NaN when a wait ran out: the failure must not pass for a state
 #pragma unroll
-            for (int j = 0; j < V; ++j) A.v_post_last[n + j] = post_reset<RESET>(v[j], af[j], q[NQ == 1 ? 0 : j]);
+            for (int j = 0; j < V; ++j) A.v_post_last[n + j] = ok ? post_reset<RESET>(v[j], af[j], q[NQ == 1 ? 0 : j]) : NAN;
         }
         if (A.spike_count) {
             const unsigned long long tot = warp_sum_u64((valid && ok) ? cnt.total(cfg) : 0ull);
@@ -163,11 +163,11 @@ leaky_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A,
             release_chunk(ring, pos, lane);
             pos.advance(pc.stages);
         }
-        if (ok && valid && A.v_last) {
+        if (valid && A.v_last) {
 #pragma unroll
-            for (int j = 0; j < V; ++j) A.v_last[n + j] = v[j];
+            for (int j = 0; j < V; ++j) A.v_last[n + j] = ok ? v[j] : NAN;
         }
-        if (A.out_sum) warp_add_f64(A.out_sum, (ok && valid) ? total : 0.0, lane);
+        if (A.out_sum) warp_add_f64(A.out_sum, valid ? (ok ? total : (double)NAN) : 0.0, lane);
     }
     ring_finish(ring, pc.stages);
 }
@@ -247,9 +247,10 @@ leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A,
             release_chunk(ring, pos, lane);
             pos.advance(pc.stages);
         }
-        if (ok && valid) {
+        if (valid) {
 #pragma unroll
             for (int j = 0; j < V; ++j) {
+                if (!ok) { G_[j] = NAN; ag[j] = NAN; sg[j] = NAN; }      // a wait ran out: poison the results
                 if (A.grad_init) A.grad_init[n + j] = __fmul_rn(al[j], G_[j]);
                 if (WA) A.grad_alpha[n + j] = __fmaf_rn(G_[j], A.v_init ? __ldg(A.v_init + n + j) : 0.0f, ag[j]);
                 if (WS) A.grad_scale[n + j] = sg[j];
@@ -494,8 +495,9 @@ cudaError_t launch_leaky_backward_scan(const LeakyBwdArgs &a, void *workspace, i
 // fragment a nearly full GPU) is exactly what such hosts forbid.  For them the scan's scratch
 // lives in this fixed array, part of the library image: every GPU that loads the library
 // holds these bytes until the process exits.
-constexpr size_t STATIC_SCRATCH_BYTES = 1u << 20;   // 1 MiB: covers every shape with up to ~1300 (tile, segment) pairs
-static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+// EXB_STATIC_SCRATCH_BYTES (1 MiB, set in the public header) covers every shape with up to ~1300 (tile, segment) pairs.
+static __device__ __align__(256) unsigned char g_static_scratch[EXB_STATIC_SCRATCH_BYTES];
+static_assert(sizeof(g_static_scratch) == EXB_STATIC_SCRATCH_BYTES, "the array is what the header promises");
 
 // Device address of the array on `device`, which must be the current device.  In host code the
 // array's name is only a handle; the address a kernel can use comes from cudaGetSymbolAddress.
@@ -517,7 +519,7 @@ static cudaError_t static_scratch_address(int device, void **out)
     return cudaSuccess;
 }
 
-size_t leaky_scan_static_capacity() { return STATIC_SCRATCH_BYTES; }
+size_t leaky_scan_static_capacity() { return sizeof(g_static_scratch); }
 
 // Same launch as launch_leaky_forward_scan, with the library's own array as the workspace.
 // `device` is the current device.  The launcher clears the ticket and the ready flags at the
@@ -529,7 +531,7 @@ cudaError_t launch_leaky_forward_scan_static(const LeakyFwdArgs &a, int device, 
     void *scratch = nullptr;
     cudaError_t e = static_scratch_address(device, &scratch);
     if (e != cudaSuccess) return e;
-    return launch_leaky_forward_scan(a, scratch, (int64_t)STATIC_SCRATCH_BYTES, s, used);
+    return launch_leaky_forward_scan(a, scratch, (int64_t)sizeof(g_static_scratch), s, used);
 }
 
 bool tma_enabled()
@@ -539,6 +541,16 @@ bool tma_enabled()
         return !(v && v[0] == '1');
     }();
     return on;
+}
+
+// Sets the poll limit of the bounded waits of this translation unit on the current device (0 = default) and
+// the diagnostic switch that keeps the scan's ready flags down.
+cudaError_t set_wait_limit(unsigned int polls, bool withhold_scan_flags)
+{
+    cudaError_t e = set_wait_limit_here(polls);
+    if (e != cudaSuccess) return e;
+    const unsigned int w = withhold_scan_flags ? 1u : 0u;
+    return cudaMemcpyToSymbol(c_exb_scan_withhold_flags, &w, sizeof(w));
 }
 
 // Reads and clears the status word of the current device (synchronises `stream`).

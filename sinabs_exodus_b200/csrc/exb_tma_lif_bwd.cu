@@ -100,10 +100,11 @@ lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, con
             release_chunk(ring, pos, lane);
             pos.advance(pc.stages);
         }
-        if (ok && valid) {
+        if (valid) {
 #pragma unroll
             for (int j = 0; j < V; ++j) {
                 const Neuron &qj = q[NQ == 1 ? 0 : j];
+                if (!ok) { st[j].R = NAN; st[j].ag = NAN; st[j].sg = NAN; }      // a wait ran out: poison the results
                 if (A.grad_init) A.grad_init[n + j] = __fmul_rn(qj.alpha, st[j].R);
                 const float vi = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
                 if (WA) A.grad_alpha[n + j] = alpha_grad_finish<RESET>(st[j], vi, Rprev[j], f0[j], n0[j]);
@@ -180,6 +181,8 @@ cudaError_t launch_lif_backward_tma(const LifBwdArgs &a, int reset_mode, int sur
     return reset_mode == EXB_RESET_SUBTRACT ? surr_lif_bwd<EXB_RESET_SUBTRACT>(a, surr_kind, s, used)
                                             : surr_lif_bwd<EXB_RESET_TO_VALUE>(a, surr_kind, s, used);
 }
+
+cudaError_t set_wait_limit_lif_bwd(unsigned int polls) { return set_wait_limit_here(polls); }
 
 // Status word of this translation unit (see read_device_status).
 cudaError_t read_device_status_lif_bwd(cudaStream_t s, unsigned int *out)

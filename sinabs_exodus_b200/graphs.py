@@ -47,7 +47,12 @@ class GraphedStep:
 
     What is captured is what ran during the capture: shapes, layer options and the set of
     parameters that require gradients are frozen; parameter *values* are read at replay time, so
-    an optimizer that updates them in place works between replays.
+    an optimizer that updates them in place works between replays.  Frozen too are the decisions the
+    layers take from parameter values on the host: the value checks (0 <= alpha <= 1, threshold >
+    min_v_mem) ran during the warm-up and are not repeated by a replay, and so did the choice of how
+    the ``norm_input`` scale gradient is formed (rebuilt from the membrane potential while
+    1 - alpha >= 0.01, from the input otherwise).  An optimizer that can move a time constant across
+    those limits should re-capture.
     """
 
     def __init__(self, module: nn.Module, example_input: torch.Tensor, example_grad: Optional[torch.Tensor] = None,
@@ -98,6 +103,14 @@ class GraphedStep:
         if not self.carry_state:
             for m in self._stateful:
                 m.reset_states()
+        elif self.training_step:
+            # Truncated back-propagation: the states come from the previous step, whose graph is gone.  Cut them
+            # here, layer by layer; `module.zero_grad()` below only reaches a layer's own override when `module`
+            # is that layer (nn.Module.zero_grad walks parameters, not the children's methods).
+            for m in self._stateful:
+                for name, buf in list(m.named_buffers(recurse=False)):
+                    if buf.requires_grad or buf.grad_fn is not None:
+                        m.register_buffer(name, buf.detach())
         if not self.training_step:
             with torch.no_grad():
                 return self.module(self.static_input)

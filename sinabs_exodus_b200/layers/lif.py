@@ -11,6 +11,7 @@ pass (``:256``) and ``sum()/numel()`` pass (``:305``) have no counterpart here.
 """
 from __future__ import annotations
 
+import weakref
 from typing import Callable, Optional, Tuple, Union
 
 import torch
@@ -263,9 +264,13 @@ class LIF(LIFBase):
             bad, near_one = torch.stack((bad, near_one)).tolist()      # one read-back for both
             if bad:
                 raise ValueError("'alpha' must be between 0 and 1.")
-            # 1 - alpha is the input scale under norm_input.  While it is at least 0.01 the backward
-            # rebuilds the scale gradient from v_mem (relative error ~ulp(v)/(scale*x), far below
-            # 1e-5) and need not keep or re-read the input; closer to zero it reads the input.
+            # 1 - alpha is the input scale under norm_input.  While it is at least 0.01 the backward rebuilds
+            # the scale gradient from v_mem and need not keep or re-read the input; closer to zero it reads
+            # the input.  The rebuilt term scale*x_t = v_t - alpha*vpost_{t-1} carries the rounding of v_t, at
+            # most ulp(v_t)/2: an error of R_t*ulp(v_t)/(2*scale) per step with random sign, against the
+            # R_t*vpost_{t-1} of the alpha gradient that it is combined with into the tau gradient, i.e.
+            # 6e-8/scale <= 6e-6 of that per step before averaging over steps and neurons.  The decision is
+            # taken from the parameter values seen here and is part of what a CUDA-graph capture freezes.
             self._scale_nonzero = not near_one
             if self.min_v_mem is not None:
                 th = torch.as_tensor(self.spike_threshold, dtype=torch.float32, device=dev)
@@ -300,7 +305,7 @@ class LIF(LIFBase):
         output_full = output.reshape(original_shape)
         # spike count (int64) or, for the non-spiking layer, the sum of the outputs (float64): both come
         # out of the forward kernel, so the reference's `output.sum() / numel` pass is not needed
-        self._set_rate_source(count, output_full.numel())
+        self._set_rate_source(count, output_full.numel(), output_full)
         return output_full
 
     def _forward_fused_synaptic(self, x: torch.Tensor, original_shape):
@@ -338,28 +343,38 @@ class LIF(LIFBase):
                 v_rec = torch.where(spikes > 0, c.expand_as(v_pre), v_pre)
             self.recordings["v_mem"] = v_rec.reshape(original_shape)
         output_full = spikes.reshape(original_shape)
-        self._set_rate_source(count, output_full.numel())
+        self._set_rate_source(count, output_full.numel(), output_full)
         return output_full
 
-    # ``firing_rate`` (reference ``layers/lif.py:305``: mean of the output) is formed from the total that the
-    # forward kernel leaves on the device, when it is read: two tiny kernels less in every forward call.
+    # ``firing_rate`` (reference ``layers/lif.py:305``: mean of the output) is formed when it is read.  While the
+    # caller still holds the output of a forward pass made with autograd on, it is the reference's differentiable
+    # expression ``output.sum() / numel`` (a loss term on the rate gets its gradient); otherwise -- inference, or
+    # the output already dropped -- it comes from the total that the forward kernel left on the device, which
+    # costs no pass over the output and carries no graph.
     _rate_source = None
     _rate_value = None
+    _rate_output = None
 
-    def _set_rate_source(self, total: torch.Tensor, numel: int) -> None:
+    def _set_rate_source(self, total: torch.Tensor, numel: int, output: Optional[torch.Tensor] = None) -> None:
         self._rate_source = (total, max(int(numel), 1))
         self._rate_value = None
+        self._rate_output = weakref.ref(output) if (output is not None and output.requires_grad) else None
 
     @property
     def firing_rate(self):
         if self._rate_value is None and self._rate_source is not None:
             total, numel = self._rate_source
-            self._rate_value = total[0].to(torch.float32) / numel
+            out = self._rate_output() if self._rate_output is not None else None
+            if out is not None and torch.is_grad_enabled():
+                self._rate_value = out.sum() / numel
+            else:
+                self._rate_value = total[0].to(torch.float32) / numel
         return self._rate_value
 
     @firing_rate.setter
     def firing_rate(self, value) -> None:
         self._rate_source = None
+        self._rate_output = None
         self._rate_value = value
 
     def __repr__(self):

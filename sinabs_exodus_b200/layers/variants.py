@@ -9,6 +9,7 @@ forms are produced by one class factory.
 from __future__ import annotations
 
 import math
+import weakref
 from typing import Callable, Optional, Union
 
 import torch
@@ -77,7 +78,10 @@ def _squeezed(base: type, name: str) -> type:
         self.squeeze_init(batch_size, num_timesteps)
 
     def forward(self, input_data: torch.Tensor) -> torch.Tensor:
-        return self.squeeze_forward(input_data, lambda x: base.forward(self, x))
+        out = self.squeeze_forward(input_data, lambda x: base.forward(self, x))
+        if out.requires_grad:      # the tensor the caller holds is the flattened one: firing_rate differentiates through it
+            self._rate_output = weakref.ref(out)
+        return out
 
     def _param_dict(self) -> dict:
         return self.squeeze_param_dict(base._param_dict.fget(self))

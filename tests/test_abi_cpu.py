@@ -62,3 +62,25 @@ def test_missing_library_is_loud(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(_lib.ExodusLibraryError):
         _lib.load()
+
+
+def test_misaligned_pointers_are_rejected(lib):
+    """A float32 tensor cannot start at an address that is not a multiple of 4: EXB_ERR_ALIGN, before any launch."""
+    null = None
+    ok, odd = ctypes.c_void_p(64), ctypes.c_void_p(66)
+    st = lib.exb_leaky_forward(ok, odd, null, ok, 0, null, 0, null, null, 1, 1, 1, 0, 0, null)
+    assert st == 2 and b"aligned" in lib.exb_last_error()
+    assert lib.exb_status_string(2) == b"misaligned pointer"
+    st = lib.exb_leaky_forward(ok, ok, null, ok, 0, null, 0, null, ctypes.c_void_p(68), 1, 1, 1, 0, 0, null)
+    assert st == 2      # the float64 sum accumulator needs 8 bytes
+
+
+def test_static_scratch_size_has_one_source(lib):
+    """The size of the built-in scratch array is set in the public header; the library reports the value it was
+    built with and the Python constant is that report."""
+    from sinabs_exodus_b200 import _lib
+    text = open(os.path.join(ROOT, "include", "exodus_b200.h")).read()
+    m = re.search(r"#define\s+EXB_STATIC_SCRATCH_BYTES\s+\((\d+)u\s*<<\s*(\d+)\)", text)
+    assert m and _lib.STATIC_SCRATCH_BYTES == lib.exb_static_scratch_bytes() == int(m.group(1)) << int(m.group(2)) == 1 << 20
+    src = open(os.path.join(ROOT, "sinabs_exodus_b200", "csrc", "exb_tma_kernels.cu")).read()
+    assert "g_static_scratch[EXB_STATIC_SCRATCH_BYTES]" in src and "1u << 20" not in src

@@ -534,6 +534,64 @@ def test_graphed_step_carries_state():
     torch.testing.assert_close(stateful[0].v_mem, v_want, rtol=0, atol=0)
 
 
+def test_graphed_step_truncated_bptt_on_a_container():
+    """carry_state=True with an upstream gradient (truncated back-propagation through time) on a Sequential of two
+    stateful layers: every replay continues from the detached state of the previous one and gives the outputs and
+    parameter gradients of the eager loop that detaches the states between chunks."""
+    from sinabs_exodus_b200 import GraphedStep
+    B, T, M, H = 3, 20, 16, 32
+    net = _two_layer_net(M, H)
+    g = torch.Generator(device="cuda:0").manual_seed(9)
+    chunks = [torch.randn(B, T, M, device="cuda:0", generator=g) for _ in range(4)]
+    gos = [torch.randn(B, T, M, device="cuda:0", generator=g) for _ in range(4)]
+    stateful = [m for m in net.modules() if hasattr(m, "reset_states")]
+    for m in stateful:
+        m.reset_states()
+    want = []
+    for c, go in zip(chunks, gos):
+        for m in stateful:
+            m.zero_grad()                      # the layers' own zero_grad detaches their states
+        net.zero_grad(set_to_none=True)
+        out = net(c)
+        out.backward(go)
+        want.append((out.detach().clone(), [p.grad.clone() for p in net.parameters()]))
+    v_want = stateful[0].v_mem.detach().clone()
+    step = GraphedStep(net, chunks[0], gos[0], carry_state=True)      # used to raise in its second warm-up step
+    for m in stateful:
+        for name, buf in m.named_buffers(recurse=False):
+            buf.zero_()
+    for (out_w, gp_w), c, go in zip(want, chunks, gos):
+        out = step(c, go)
+        torch.testing.assert_close(out, out_w, rtol=0, atol=0)
+        for p, gw in zip(net.parameters(), gp_w):
+            torch.testing.assert_close(p.grad, gw, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(stateful[0].v_mem, v_want, rtol=0, atol=0)
+
+
+def test_firing_rate_is_differentiable_while_output_is_held():
+    """`firing_rate` as the reference sets it (layers/lif.py:305, mean of the output with its graph): a loss on the
+    rate reaches the input while the caller holds the output; under no_grad it is a plain number from the kernel's count."""
+    from sinabs_exodus_b200.layers import LIF
+    torch.manual_seed(4)
+    layer = LIF(tau_mem=10.0).to("cuda:0")
+    x = (0.5 + torch.randn(3, 25, 16, device="cuda:0")).requires_grad_(True)
+    out = layer(x)
+    rate = layer.firing_rate
+    assert rate.requires_grad
+    rate.backward()
+    g_rate = x.grad.clone()
+    assert g_rate.abs().sum() > 0
+    layer.zero_grad(); layer.reset_states(); x.grad = None
+    out = layer(x)
+    out.mean().backward()
+    torch.testing.assert_close(x.grad, g_rate, rtol=1e-5, atol=1e-9)
+    with torch.no_grad():
+        layer.reset_states()
+        out2 = layer(x)
+    assert not layer.firing_rate.requires_grad
+    torch.testing.assert_close(layer.firing_rate, out2.mean(), rtol=1e-6, atol=0)
+
+
 def test_layer_recordings_fused_under_no_grad():
     """record_states: with autograd off the recording is a side output of the forward launch; it equals the
     differentiable expression used with autograd on, bit for bit."""

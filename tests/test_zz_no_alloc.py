@@ -74,3 +74,28 @@ def test_static_scratch_rejects_oversized_and_inapplicable_shapes():
     x2 = torch.zeros(1, 40, 128, device=DEV)
     with pytest.raises(_lib.ExodusLibraryError, match="does not apply"):
         _lib.leaky_forward_scan_static(torch.empty_like(x2), x2, None, (a, _lib.PARAM_SCALAR), (None, 0), None, 1, 40, 128)
+
+
+def test_static_scratch_call_takes_no_device_memory():
+    """What the entry point promises: once the first call on the device has been made (it looks up the array and
+    makes the runtime load the kernel), a call takes no device memory at all.  Free device memory as the driver
+    reports it is the same before and after a call on preallocated tensors."""
+    from sinabs_exodus_b200 import _lib
+    B, T, M = 2, 2048, 64
+    x, alpha, v0 = _problem(5, B, T, M)
+    out = torch.empty_like(x); v_last = torch.empty(B * M, device=DEV)
+    args = (out, x, v0, (alpha, _lib.PARAM_PER_N), (None, 0), v_last, B, T, M)
+    _lib.leaky_forward_scan_static(*args)          # first call: set-up happens here
+    torch.cuda.synchronize()
+    unchanged = False
+    for _ in range(3):                             # the figure is device-wide; allow for an unrelated blip
+        free_before, _total = torch.cuda.mem_get_info()
+        _lib.leaky_forward_scan_static(*args)
+        torch.cuda.synchronize()
+        free_after, _total = torch.cuda.mem_get_info()
+        if free_after == free_before:
+            unchanged = True
+            break
+    assert unchanged, (free_before, free_after)
+    want, _ = _with_workspace(x, alpha, v0)
+    torch.testing.assert_close(out, want, rtol=TOL, atol=TOL)
