@@ -1,23 +1,31 @@
 """Benchmark of the neuron hot path: neuron-timesteps per second, forward + backward.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5] [--impl ours|reference]
 
-One "step" is one forward + backward pass of one layer over one batch of
-synthetic input (the configurations of BASELINE.json; default ``c2``, the IAF
-layer on conv feature maps).  With N > 1 the script is launched by torchrun, one
-rank per GPU; every rank owns its own batch shard of the same size (weak scaling)
-and the only collective is the allreduce of time-constant gradients (``c4``).
+One "step" is one forward + backward pass of one layer over one batch of synthetic input.  The
+headline workload is ``c5``, the largest configuration that fits one GPU: a LIF layer on
+``(32, 500, 64, 64, 64)`` per GPU (16.8 GB per tensor); ``c1`` .. ``c4`` are the other configurations
+and are measured in the same run as short extra legs.  With N > 1 the script is launched by torchrun,
+one rank per GPU; every rank owns its own batch shard of the same size (weak scaling) and the only
+collective is the allreduce of time-constant gradients.
 
 Rank 0 prints ONE JSON line:
-* ``value``        whole-job neuron-timesteps/s with inputs resident in HBM, device-timed
-                   (CUDA events, max over ranks)
-* ``roofline``     the dominant kernel's algorithmic bytes / its event-timed duration
-                   against the measured HBM copy bandwidth
-* ``e2e``          the same metric through the public layer API with pinned HOST buffers:
-                   input and upstream gradient copied in, spikes and input gradient copied out,
-                   every step, inside the timed region
-* ``cpu_baseline`` a time-stepped PyTorch layer loop (the stand-in for sinabs' CPU layers,
-                   which are not installed) on the host cores, on a bounded sample
+* ``value``           whole-job neuron-timesteps/s with inputs resident in HBM, device-timed
+                      (CUDA events, max over ranks)
+* ``roofline``        the dominant kernel's algorithmic bytes / its event-timed duration against
+                      the measured HBM copy bandwidth
+* ``e2e``             the same metric through the public layer API with pinned HOST buffers: input
+                      and upstream gradient copied in, spikes and input gradient copied out, every
+                      step, inside the timed region (streamed through a fixed pinned staging ring)
+* ``other_configs``   the other configurations, device-timed, each with its dominant kernel and
+                      fraction of the copy peak; with N > 1 the synaptic configuration includes the
+                      allreduce of its time-constant gradients, timed separately as well
+* ``reference_cuda``  the reference project's own CUDA kernels (built from its sources into the
+                      checker directory, when present) with the tensor glue of its autograd
+                      Functions, on a batch slice of the same seeded input
+* ``cpu_baseline``    a time-stepped PyTorch layer loop (the stand-in for the CPU layers of the
+                      package the reference plugs into, which is not installed) on the host cores,
+                      on a fixed sample
 
 ``--impl reference`` times that CPU loop alone, on the same workload definition.
 """
@@ -44,7 +52,7 @@ UNIT = "nts/s"
 
 
 # --------------------------------------------------------------------------
-# workloads (BASELINE.json configs; shapes are per GPU)
+# workloads (shapes are per GPU)
 # --------------------------------------------------------------------------
 WORKLOADS = {
     "c1": dict(desc="LIF tau_mem=20 thr=1 subtract MultiSpike SingleExponential(0.5) min_v_mem=-1, "
@@ -279,25 +287,19 @@ def cpu_step(name: str, kind: str, x: torch.Tensor, grad: torch.Tensor):
     return xr.grad
 
 
-def cpu_sample(name: str, wl: dict, budget_s: float, steps: int, warmup: int):
-    """Times `steps` CPU steps on a batch/neuron sample sized to fit `budget_s` in total.
-    Returns (nts_per_s, sample description, cores, ms_per_step)."""
+# Fixed sample of each workload for the CPU legs: (batch items, neurons) of the workload's own time length.
+# Sized for a few seconds per step on 16 host cores; the same in every run.
+CPU_SAMPLE = {"c1": (8, 128), "c2": (8, 36992), "c3": (16, 512), "c4": (16, 1024), "c5": (1, 65536)}
+
+
+def cpu_sample(name: str, wl: dict, steps: int, warmup: int):
+    """Times `steps` CPU steps on the workload's fixed sample.  Returns (nts_per_s, sample description, cores, ms_per_step)."""
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     shape = wl["shape"]
-    B, T = shape[0], shape[1]
-    M = int(np.prod(shape[2:]))
-    # calibrate on a small neuron slice of one batch item
-    m0 = min(M, 4096)
-    x, g = make_input(name, (1, T, m0), "cpu", 0)
-    t0 = time.perf_counter(); cpu_step(name, wl["kind"], x, g); dt = time.perf_counter() - t0
-    t0 = time.perf_counter(); cpu_step(name, wl["kind"], x, g); dt = min(dt, time.perf_counter() - t0)
-    rate = T * m0 / dt                                    # nts/s at small size (pessimistic for large)
-    per_step = budget_s / max(1, steps + warmup)
-    want = max(T * m0, rate * per_step)                   # nts per step that fit the budget
-    neurons = int(min(B * M, max(m0, want // T)))
-    b = max(1, min(B, neurons // M)) if neurons >= M else 1
-    m = M if neurons >= M else max(1, neurons)
+    T = shape[1]
+    b, m = CPU_SAMPLE[name]
+    b = min(b, shape[0]); m = min(m, int(np.prod(shape[2:])))
     x, g = make_input(name, (b, T, m), "cpu", 0)
     for _ in range(warmup):
         cpu_step(name, wl["kind"], x, g)
@@ -306,7 +308,8 @@ def cpu_sample(name: str, wl: dict, budget_s: float, steps: int, warmup: int):
         cpu_step(name, wl["kind"], x, g)
     dt = time.perf_counter() - t0
     nts = b * m * T * steps
-    sample = f"{steps} fwd+bwd steps of a time-stepped PyTorch loop on batch {b} x {m} neurons x {T} steps of {name}"
+    sample = (f"{steps} fwd+bwd steps of a time-stepped PyTorch loop on a fixed sample of {name}: "
+              f"batch {b} x {m} neurons x {T} steps")
     return nts / dt, sample, cores, dt / steps * 1e3
 
 
@@ -396,16 +399,25 @@ def measured_peak_gbs():
         return 6650.0, "fallback (earlier pool measurement)"
 
 
+def config_dict(name: str, wl: dict, world: int) -> dict:
+    """The `config` object of the JSON line; the same for both arms."""
+    shape = wl["shape"]
+    nts = int(np.prod(shape))
+    return {"workload": f"{name}: {wl['desc']}", "per_gpu_shape": list(shape),
+            "l2": f"each tensor is {nts * 4 / 1e6:.0f} MB (L2 is 126 MB); no flush between steps",
+            "parallelism": f"batch-sharded x{world}"}
+
+
 def run_reference(args, wl):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    value, sample, cores, ms = cpu_sample(args.workload, wl, args.cpu_seconds_reference, args.steps, args.warmup)
+    value, sample, cores, ms = cpu_sample(args.workload, wl, args.steps, args.warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: {wl['desc']}", "note": "CPU arm runs a bounded sample per step"},
+        "config": config_dict(args.workload, wl, args.gpus),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -413,10 +425,292 @@ def run_reference(args, wl):
     print(json.dumps(line), flush=True)
 
 
+def kernel_bytes(kind: str) -> dict:
+    """Algorithmic bytes per neuron-step of each entry point for a workload kind."""
+    b = {"lif_forward": 12, "lif_backward": 12, "leaky_forward": 8, "leaky_backward": 8,
+         "leaky_forward_scan": 8, "leaky_backward_scan": 8,
+         # fused LIF + synapse: read in, write i_syn/spikes/v_mem; read grad, v_mem, i_syn, write grad_in
+         "lif_syn_forward": 16, "lif_syn_backward": 16}
+    if kind == "expleak":              # trainable tau: the alpha gradient reads the forward output
+        b["leaky_backward"] = 12
+        b["leaky_backward_scan"] = 12
+    if kind == "lif_syn":              # two-stage route: alpha gradient reads i_syn, decay_early scale gradient reads the input
+        b["leaky_backward"] = 16
+    return b
+
+
+def roofline_of(name: str, kind: str, kernels: dict, nts_step: int, peak: float, peak_src: str):
+    """Roofline object for the dominant kernel (largest total time) of a timed region."""
+    if not kernels:
+        return None
+    per = kernel_bytes(kind)
+    dom = max(kernels, key=lambda k: kernels[k]["avg_ms"] * kernels[k]["launches"])
+    bts = per[dom] * nts_step
+    ach = bts / (kernels[dom]["avg_ms"] * 1e-3) / 1e9
+    traffic = None
+    try:      # DRAM bytes per neuron-step from the committed ncu capture of a small case, scaled to this launch
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            traffic = float(json.load(f)[name][dom]) * nts_step
+    except Exception:
+        traffic = None
+    return {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+            "traffic": traffic, "peak_source": peak_src, "algorithmic_bytes_per_launch": bts,
+            "avg_launch_ms": kernels[dom]["avg_ms"],
+            "all_kernels": {k: dict(v, gbs=per[k] * nts_step / (v["avg_ms"] * 1e-3) / 1e9) for k, v in kernels.items()}}
+
+
+class Workload:
+    """Layer, resident input and upstream gradient of one configuration on this rank's GPU."""
+
+    def __init__(self, name: str, wl: dict, dev, rank: int, layout: str = "btm"):
+        import sinabs_exodus_b200 as ex
+        from sinabs_exodus_b200 import distributed as exd
+        self.name, self.wl, self.dev = name, wl, dev
+        shape = wl["shape"]
+        self.B, self.T = shape[0], shape[1]
+        self.M = int(np.prod(shape[2:]))
+        self.nts = self.B * self.T * self.M
+        self.layer = make_layer(wl["kind"], shape[2:], dev)
+        x, grad = make_input(name, shape, dev, rank)
+        if layout == "nt":      # same values, rows = (batch item, neuron), time contiguous
+            B, T, M = self.B, self.T, self.M
+            x = x.reshape(B, T, M).transpose(1, 2).reshape(B * M, T).contiguous()
+            grad = grad.reshape(B, T, M).transpose(1, 2).reshape(B * M, T).contiguous()
+            self.layer = FunctionArm(wl["kind"], B * M, dev)
+        self.x = x.requires_grad_(True)
+        self.grad = grad
+        self.tc_params = exd.time_constant_parameters(self.layer)
+        self.collective_events = []
+
+    def step(self, world: int = 1, time_collective: bool = False):
+        from sinabs_exodus_b200 import distributed as exd
+        self.layer.zero_grad(set_to_none=True)
+        self.x.grad = None
+        self.layer.reset_states()
+        out = self.layer(self.x)
+        out.backward(self.grad)
+        if world > 1 and self.tc_params:
+            if time_collective:
+                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+                e0.record()
+                exd.allreduce_gradients(self.tc_params)
+                e1.record()
+                self.collective_events.append((e0, e1))
+            else:
+                exd.allreduce_gradients(self.tc_params)
+        return out
+
+
+def timed_steps(fn, steps: int, world: int, dev):
+    """K calls of fn between barrier + synchronize on both sides, CUDA events, max over ranks.  Returns ms in total."""
+    import torch.distributed as dist
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev0 = torch.cuda.Event(enable_timing=True); ev1 = torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(steps):
+        fn()
+    ev1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def measure_other(name: str, timer: KernelTimer, dev, rank: int, world: int, steps: int, warmup: int, peak: float,
+                  peak_src: str):
+    """Short device-timed run of another configuration (eager layer API; c1 also as one CUDA graph)."""
+    import sinabs_exodus_b200 as ex
+    wl = dict(WORKLOADS[name])
+    w = Workload(name, wl, dev, rank)
+    for _ in range(warmup):
+        w.step(world)
+    torch.cuda.synchronize()
+    timer.reset()
+    timer.enabled = True
+    ms = timed_steps(lambda: w.step(world, time_collective=True), steps, world, dev)
+    timer.enabled = False
+    kernels = timer.summary()
+    launches = timer.launches()
+    step_bytes = (wl["bytes_fwd"] + wl["bytes_bwd"]) * w.nts
+    res = {"workload": f"{name}: {wl['desc']}", "per_gpu_shape": list(wl["shape"]), "steps": steps, "warmup": warmup,
+           "ms_per_step": ms / steps, "value": w.nts * world * steps / (ms * 1e-3), "unit": UNIT,
+           "launches_per_step": launches / steps,
+           "step_fraction_of_hbm_roofline": (step_bytes / (ms / steps * 1e-3) / 1e9) / peak,
+           "roofline": roofline_of(name, wl["kind"], kernels, w.nts, peak, peak_src)}
+    if w.collective_events:
+        c_ms = [a.elapsed_time(b) for a, b in w.collective_events]
+        res["collective"] = {"what": "sum-allreduce of the time-constant gradients (NCCL, one flat buffer), inside the timed region",
+                             "floats": int(sum(p.numel() for p in w.tc_params)), "avg_ms": sum(c_ms) / len(c_ms),
+                             "calls": len(c_ms)}
+    if name in ("c1", "c3", "c4") and not (world > 1 and w.tc_params):
+        # the same step captured once as a CUDA graph: what is left when the per-step host work is taken out
+        try:
+            graphed = ex.GraphedStep(w.layer, w.x.detach(), w.grad, carry_state=False, input_grad=True)
+            for _ in range(3):
+                graphed.replay()
+            gms = timed_steps(graphed.replay, steps, world, dev)
+            res["cuda_graph"] = {"ms_per_step": gms / steps, "value": w.nts * world * steps / (gms * 1e-3),
+                                 "step_fraction_of_hbm_roofline": (step_bytes / (gms / steps * 1e-3) / 1e9) / peak}
+            del graphed
+        except Exception as exc:
+            res["cuda_graph"] = {"unavailable": str(exc)[:200]}
+    del w
+    torch.cuda.empty_cache()
+    return res
+
+
+# Batch items of each workload given to the reference's kernels (its backward is O(T^2) per neuron and its
+# Function glue keeps about ten [N,T] tensors alive).
+REFERENCE_CUDA_BATCH = {"c2": 8, "c3": 64, "c5": 4}
+
+
+def reference_cuda(name: str, wl: dict, dev, reps: int = 3):
+    """The reference project's own CUDA kernels (oracle/_ref, built from its sources where they are present) with
+    the tensor glue of its autograd Functions (sinabs/exodus/spike.py:193-289, leaky.py:43-72), forward + backward
+    in its [N,T] layout, on a batch slice of the workload's seeded input.  A baseline, never the product path."""
+    from oracle import ref_gpu
+    from sinabs_exodus_b200.compat import activation as sa
+    if not ref_gpu.available():
+        return {"unavailable": "the reference kernels are not built here (no reference checkout at build time)"}
+    if name not in REFERENCE_CUDA_BATCH:
+        return {"unavailable": "the reference has no kernel for this configuration (reset to zero; fused synapse)"
+                if name == "c4" else "not measured"}
+    kind = wl["kind"]
+    shape = wl["shape"]
+    B = min(REFERENCE_CUDA_BATCH[name], shape[0])
+    T = shape[1]
+    M = int(np.prod(shape[2:]))
+    N = B * M
+    x, go = make_input(name, shape, dev, 0, batch=B)
+    to_nt = lambda t: t.reshape(B, T, M).transpose(1, 2).reshape(N, T).contiguous()
+    x, go = to_nt(x), to_nt(go)
+    z = torch.zeros(N, device=dev); one = torch.ones(N, device=dev)
+    note = ""
+    if kind == "expleak":
+        alpha = torch.full((N,), float(np.exp(-1 / 50.0)), device=dev)
+
+        def step():
+            out = ref_gpu.leaky_forward(x, z, alpha)
+            ref_gpu.leaky_backward(go, alpha, out, z)          # tau is trainable: alpha gradient included
+    else:
+        if kind == "iaf":
+            alpha, fn, low = one, sa.Heaviside(), None
+        else:
+            a = float(np.exp(-1 / 20.0))
+            alpha = torch.full((N,), a, device=dev)
+            x = (1.0 - a) * x                                  # layers/lif.py:206-209 (norm_input), done by the layer
+            fn = sa.SingleExponential(0.5) if kind == "lif" else sa.SingleExponential()
+            low = -one if kind == "lif" else None
+            note = "; input pre-multiplied by 1 - alpha as the reference layer's norm_input does"
+        gv = torch.zeros_like(go)
+
+        def step():
+            s, v = ref_gpu.lif_forward(x, z, alpha, one, one, low)
+            ref_gpu.integrate_and_fire_backward(go, gv, v, s, z, alpha, one, one, low, fn, kind != "iaf")
+    step()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    return {"value": N * T / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "batch": B, "rows": N, "steps_timed": reps,
+            "what": "reference CUDA kernels (lifForward/lifBackward/lifBackwardAlpha or leakyForward/leakyBackward/"
+                    "leakyBackwardAlpha, compiled for sm_100a from the reference sources) + the PyTorch glue of the "
+                    f"reference Functions, [N,T] layout, batch {B} of {name}" + note}
+
+
+def run_e2e(w: Workload, world: int, args, timer: KernelTimer):
+    """The metric through the public layer API with pinned host buffers.  Every step copies the whole input and the
+    whole upstream gradient from host memory and the whole output and input gradient back, in micro-batches of batch
+    items through a FIXED pinned staging ring (a few slots per direction, reused round robin: every byte still crosses
+    the bus every step, but a rank pins a few GB instead of four full tensors).  Copy-in of micro-batch i+1, the layer
+    call on i and the copy-out of i-1 run on three streams."""
+    from sinabs_exodus_b200 import distributed as exd
+    import torch.distributed as dist
+    dev = w.dev
+    shape = w.wl["shape"]
+    B = w.B
+    item_bytes = w.T * w.M * 4
+    # micro-batches of whole batch items, about 128 MB per tensor each (one item if an item is larger)
+    per_mb = max(1, min(B, int((128 << 20) // item_bytes)))
+    nmb = (B + per_mb - 1) // per_mb
+    if args.e2e_microbatches:
+        nmb = max(1, min(args.e2e_microbatches, B))
+    bounds = [exd.shard_bounds(B, i, nmb) for i in range(nmb)]
+    mb_items = max(hi - lo for lo, hi in bounds)
+    host_slots = max(2, min(nmb, args.e2e_host_slots))
+    dev_slots = max(2, min(nmb, 3))
+    mb_shape = (mb_items,) + tuple(shape[1:])
+    pin = lambda: torch.empty(mb_shape, pin_memory=True)
+    xh = [pin() for _ in range(host_slots)]; gh = [pin() for _ in range(host_slots)]
+    oh = [pin() for _ in range(host_slots)]; gih = [pin() for _ in range(host_slots)]
+    gen = torch.Generator().manual_seed(1234)
+    for t in xh:
+        t.copy_(w.x.detach()[:mb_items].reshape(mb_shape) if w.x.shape[0] >= mb_items else torch.randn(mb_shape, generator=gen))
+    for t in gh:
+        t.copy_(w.grad[:mb_items].reshape(mb_shape))
+    xd = [torch.empty(mb_shape, device=dev, requires_grad=True) for _ in range(dev_slots)]
+    gd = [torch.empty(mb_shape, device=dev) for _ in range(dev_slots)]
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    s_main = torch.cuda.current_stream(dev)
+    layer = w.layer
+    done = [None] * dev_slots          # event: the layer call that used device slot s has finished
+
+    def e2e_step():
+        layer.zero_grad(set_to_none=True)
+        s_in.wait_stream(s_out)             # host slots of the previous step are free again
+        for i, (lo, hi) in enumerate(bounds):
+            n = hi - lo
+            ds, hs = i % dev_slots, i % host_slots
+            with torch.cuda.stream(s_in), torch.no_grad():
+                if done[ds] is not None:
+                    s_in.wait_event(done[ds])
+                xd[ds].grad = None
+                xd[ds][:n].copy_(xh[hs][:n], non_blocking=True)
+                gd[ds][:n].copy_(gh[hs][:n], non_blocking=True)
+                ev = torch.cuda.Event(); ev.record(s_in)
+            s_main.wait_event(ev)
+            layer.reset_states()
+            xin = xd[ds] if n == mb_items else xd[ds][:n]
+            out = layer(xin)
+            out.backward(gd[ds][:n])
+            gin = xd[ds].grad
+            ev2 = torch.cuda.Event(); ev2.record(s_main)
+            done[ds] = ev2
+            s_out.wait_event(ev2)
+            with torch.cuda.stream(s_out):
+                oh[hs][:n].copy_(out.detach(), non_blocking=True)
+                gih[hs][:n].copy_(gin[:n], non_blocking=True)
+            out.record_stream(s_out); gin.record_stream(s_out)
+        if world > 1 and w.tc_params:
+            exd.allreduce_gradients(w.tc_params)
+        s_main.wait_stream(s_out)           # the step ends when its results are in host memory
+
+    k_e2e = max(3, min(args.steps, args.e2e_steps))
+    for _ in range(2):
+        e2e_step()
+    ms = timed_steps(e2e_step, k_e2e, world, dev)
+    bytes_t = w.nts * 4
+    pinned = 4 * host_slots * int(np.prod(mb_shape)) * 4
+    return {"value": w.nts * world * k_e2e / (ms * 1e-3), "unit": UNIT,
+            "h2d_bytes_per_step": 2 * bytes_t, "d2h_bytes_per_step": 2 * bytes_t, "steps": k_e2e,
+            "ms_per_step": ms / k_e2e, "microbatches": nmb, "pinned_staging_bytes": pinned,
+            "what": "layer forward+backward; input and upstream gradient copied from pinned host memory, "
+                    "spikes/output and input gradient copied back, every step; the batch is streamed in "
+                    "micro-batches through a fixed pinned staging ring so that copy-in, kernels and copy-out overlap"}
+
+
 def run_ours(args, wl):
     import torch.distributed as dist
     import sinabs_exodus_b200 as ex
-    from sinabs_exodus_b200 import distributed as exd
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -428,46 +722,24 @@ def run_ours(args, wl):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     ex._lib.load()
+    peak, peak_src = measured_peak_gbs()
 
     name = args.workload
-    shape = wl["shape"]
-    B, T = shape[0], shape[1]
-    M = int(np.prod(shape[2:]))
-    layer = make_layer(wl["kind"], shape[2:], dev)
-    x, grad = make_input(name, shape, dev, rank)
+    w = Workload(name, wl, dev, rank, args.layout)
     if args.layout == "nt":
-        # same values, rows = (batch item, neuron), time contiguous
-        x = x.reshape(B, T, M).transpose(1, 2).reshape(B * M, T).contiguous()
-        grad = grad.reshape(B, T, M).transpose(1, 2).reshape(B * M, T).contiguous()
-        layer = FunctionArm(wl["kind"], B * M, dev)
         args.no_e2e = True
-    x.requires_grad_(True)
-    tc_params = exd.time_constant_parameters(layer)
-
-    def step():
-        layer.zero_grad(set_to_none=True)
-        x.grad = None
-        layer.reset_states()
-        out = layer(x)
-        out.backward(grad)
-        if world > 1 and tc_params:
-            exd.allreduce_gradients(tc_params)
-        return out
-
     timer = KernelTimer()
     for _ in range(args.warmup):
-        step()
+        w.step(world)
     torch.cuda.synchronize()
 
-    run_step = step
-    graph = None
+    run_step = lambda: w.step(world)
     if args.cuda_graph:
         # Whole step (state reset, forward, backward) captured once and replayed: removes the per-step
         # host work, which dominates when the kernels take only tens of microseconds.
-        if world > 1 and tc_params:
+        if world > 1 and w.tc_params:
             raise SystemExit("--cuda-graph is for single-process runs (the allreduce is issued from the host)")
-        graphed = ex.GraphedStep(layer, x, grad, carry_state=False, input_grad=True)
-        graph = graphed.graph
+        graphed = ex.GraphedStep(w.layer, w.x.detach(), w.grad, carry_state=False, input_grad=True)
         run_step = graphed.replay
         for _ in range(3):
             run_step()
@@ -477,159 +749,74 @@ def run_ours(args, wl):
         sampler.start()
 
     # ---- timed region: K steps, device-timed, barrier + synchronize on both sides
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
     timer.enabled = True
-    ev0 = torch.cuda.Event(enable_timing=True); ev1 = torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for _ in range(args.steps):
-        run_step()
-    ev1.record()
-    torch.cuda.synchronize()
+    ms_total = timed_steps(run_step, args.steps, world, dev)
     timer.enabled = False
-    if world > 1:
-        dist.barrier()
-    ms_total = ev0.elapsed_time(ev1)
-    t = torch.tensor([ms_total], device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total = float(t.item())
     launches = timer.launches()
     kernels = timer.summary()
-    nts_step = B * T * M
-    value = nts_step * world * args.steps / (ms_total * 1e-3)
+    value = w.nts * world * args.steps / (ms_total * 1e-3)
 
     # ---- end to end with host buffers (public layer API; copies inside the timed region)
     e2e = None
     if not args.no_e2e:
         timer.reset()
-        xh = torch.empty(shape, pin_memory=True); xh.copy_(x.detach())
-        gh = torch.empty(shape, pin_memory=True); gh.copy_(grad)
-        oh = torch.empty(shape, pin_memory=True); gih = torch.empty(shape, pin_memory=True)
-        # The batch is streamed in micro-batches (batch items are independent): the copy-in of item
-        # group i+1, the layer call on group i and the copy-out of group i-1 run on three streams, so
-        # both PCIe directions and the kernels overlap.  Every byte still crosses the bus every step.
-        nmb = max(1, min(args.e2e_microbatches, B))
-        bounds = [exd.shard_bounds(B, i, nmb) for i in range(nmb)]
-        xd = [torch.empty((hi - lo,) + tuple(shape[1:]), device=dev, requires_grad=True) for lo, hi in bounds]
-        gd = [torch.empty((hi - lo,) + tuple(shape[1:]), device=dev) for lo, hi in bounds]
-        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-        s_main = torch.cuda.current_stream(dev)
-
-        def e2e_step():
-            keep = []
-            layer.zero_grad(set_to_none=True)
-            ev_in = []
-            s_in.wait_stream(s_main)            # device buffers of the previous step are free again
-            with torch.cuda.stream(s_in), torch.no_grad():
-                for i, (lo, hi) in enumerate(bounds):
-                    xd[i].grad = None
-                    xd[i].copy_(xh[lo:hi], non_blocking=True)
-                    gd[i].copy_(gh[lo:hi], non_blocking=True)
-                    ev = torch.cuda.Event(); ev.record(s_in); ev_in.append(ev)
-            for i, (lo, hi) in enumerate(bounds):
-                s_main.wait_event(ev_in[i])
-                layer.reset_states()
-                out = layer(xd[i])
-                out.backward(gd[i])
-                ev = torch.cuda.Event(); ev.record(s_main)
-                s_out.wait_event(ev)
-                with torch.cuda.stream(s_out):
-                    oh[lo:hi].copy_(out.detach(), non_blocking=True)
-                    gih[lo:hi].copy_(xd[i].grad, non_blocking=True)
-                keep.append((out, xd[i].grad))
-            if world > 1 and tc_params:
-                exd.allreduce_gradients(tc_params)
-            s_main.wait_stream(s_out)           # the step ends when its results are in host memory
-            return keep
-
-        k_e2e = max(3, min(args.steps, args.e2e_steps))
-        for _ in range(2):
-            e2e_step()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(k_e2e):
-            e2e_step()
-        e1.record()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        te = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        if world > 1:
-            dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        bytes_t = nts_step * 4
-        e2e = {"value": nts_step * world * k_e2e / (float(te.item()) * 1e-3), "unit": UNIT,
-               "h2d_bytes_per_step": 2 * bytes_t, "d2h_bytes_per_step": 2 * bytes_t, "steps": k_e2e,
-               "ms_per_step": float(te.item()) / k_e2e,
-               "microbatches": nmb,
-               "what": "layer forward+backward; input and upstream gradient copied from pinned host memory, "
-                       "spikes/output and input gradient copied back, every step; the batch is streamed in "
-                       "micro-batches so that copy-in, kernels and copy-out overlap"}
-        del xh, gh, oh, gih, xd, gd
-
+        e2e = run_e2e(w, world, args, timer)
     clocks = sampler.stop() if sampler else None
-    mix = None
-    if rank == 0 and not args.no_mix:
-        try:
-            mix = stream_mix_ceilings(dev)
-        except Exception as exc:
-            mix = {"unavailable": str(exc)[:200]}
 
+    roof = roofline_of(name, wl["kind"], kernels, w.nts, peak, peak_src) if rank == 0 else None
+    step_bytes = (wl["bytes_fwd"] + wl["bytes_bwd"]) * w.nts
+    nts_step = w.nts
+    del w
+    torch.cuda.empty_cache()
+
+    # ---- the other configurations, device-timed (every rank takes part: c4 has a collective)
+    others = None
+    if not args.no_others:
+        others = {}
+        for other in ("c1", "c2", "c3", "c4", "c5"):
+            if other == name or (other == "c5" and name != "c5"):
+                continue
+            try:
+                others[other] = measure_other(other, timer, dev, rank, world, args.other_steps, 3, peak, peak_src)
+            except Exception as exc:      # an extra leg must not take the headline down
+                others[other] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
+                torch.cuda.empty_cache()
+
+    mix = ref_cuda = cpu = None
     if rank == 0:
-        peak, peak_src = measured_peak_gbs()
-        # dominant kernel = largest total time; bytes per launch = bytes/nts of that pass * nts per launch
-        per_kernel_bytes = {
-            "lif_forward": 12, "lif_backward": 12, "leaky_forward": 8, "leaky_backward": 8,
-            "leaky_forward_scan": 8, "leaky_backward_scan": 8,
-            # fused LIF + synapse: read in, write i_syn/spikes/v_mem; read grad, v_mem, i_syn, write grad_in
-            "lif_syn_forward": 16, "lif_syn_backward": 16,
-        }
-        if wl["kind"] == "expleak":              # trainable tau: the alpha gradient reads the forward output
-            per_kernel_bytes["leaky_backward"] = 12
-        if wl["kind"] == "lif_syn":              # alpha gradient reads i_syn, decay_early scale gradient reads the input
-            per_kernel_bytes["leaky_backward"] = 16
-        roof = None
-        if kernels:
-            dom = max(kernels, key=lambda k: kernels[k]["avg_ms"] * kernels[k]["launches"])
-            bts = per_kernel_bytes[dom] * nts_step
-            ach = bts / (kernels[dom]["avg_ms"] * 1e-3) / 1e9
-            traffic = None
-            try:      # DRAM bytes per neuron-step from the committed ncu capture, scaled to this launch
-                with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
-                    traffic = float(json.load(f)[name][dom]) * nts_step
-            except Exception:
-                traffic = None
-            roof = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                    "traffic": traffic, "peak_source": peak_src, "algorithmic_bytes_per_launch": bts,
-                    "avg_launch_ms": kernels[dom]["avg_ms"],
-                    "all_kernels": {k: dict(v, gbs=per_kernel_bytes[k] * nts_step / (v["avg_ms"] * 1e-3) / 1e9)
-                                    for k, v in kernels.items()}}
-        step_bytes = (wl["bytes_fwd"] + wl["bytes_bwd"]) * nts_step
-        cpu = None
-        if not args.no_cpu:
-            v, sample, cores, _ = cpu_sample(name, wl, args.cpu_seconds, 3, 1)
+        if not args.no_mix:
+            try:
+                mix = stream_mix_ceilings(dev)
+            except Exception as exc:
+                mix = {"unavailable": str(exc)[:200]}
+        if world == 1 and not args.no_reference_cuda:
+            ref_cuda = {}
+            for n in dict.fromkeys([name, "c2", "c3"]):
+                try:
+                    ref_cuda[n] = reference_cuda(n, dict(WORKLOADS[n]) if n != name else wl, dev)
+                except Exception as exc:
+                    ref_cuda[n] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
+                torch.cuda.empty_cache()
+        if world == 1 and not args.no_cpu:
+            v, sample, cores, _ = cpu_sample(name, wl, 3, 1)
             cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
             try:
                 cpu["c_kernels"] = cpu_c_kernels_sample(name, wl, 6.0)
             except Exception as exc:      # the checker library is optional for this extra figure
                 cpu["c_kernels"] = {"unavailable": str(exc)[:200]}
+        config = config_dict(name, wl, world)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{name}: {wl['desc']}", "per_gpu_shape": list(shape),
-                       "l2": f"each tensor is {nts_step * 4 / 1e6:.0f} MB (L2 is 126 MB); no flush between steps",
-                       "parallelism": f"batch-sharded x{world}",
-                       "api": "sinabs_exodus_b200.layers" if args.layout == "btm"
-                       else "IntegrateAndFire / LeakyIntegrator Functions on [N,T] (no layer glue)",
-                       "cuda_graph": bool(args.cuda_graph),
-                       "autograd": "single-threaded" if args.single_thread_autograd else "default (backward on PyTorch's autograd thread)"},
+            "config": config,
+            "run": {"api": "sinabs_exodus_b200.layers" if args.layout == "btm"
+                    else "IntegrateAndFire / LeakyIntegrator Functions on [N,T] (no layer glue)",
+                    "cuda_graph": bool(args.cuda_graph),
+                    "autograd": "single-threaded" if args.single_thread_autograd else "default (backward on PyTorch's autograd thread)"},
             "step_fraction_of_hbm_roofline": (step_bytes / (ms_total / args.steps * 1e-3) / 1e9) / peak,
-            "roofline": roof, "stream_mix_ceilings": mix, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+            "roofline": roof, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+            "cpu_baseline": cpu, "other_configs": others, "reference_cuda": ref_cuda, "stream_mix_ceilings": mix,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -639,10 +826,10 @@ def run_ours(args, wl):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch size (profiling small cases)")
     ap.add_argument("--shape", default=None,
                     help="override the per-GPU input shape, e.g. 32,300,36991 (same layer and value distribution)")
@@ -655,11 +842,16 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-mix", action="store_true", help="skip the streaming-mix calibration (1 read : 2 writes, 2 : 1)")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-others", action="store_true", help="skip the short runs of the other configurations")
+    ap.add_argument("--no-reference-cuda", action="store_true", help="skip timing the reference project's CUDA kernels")
+    ap.add_argument("--lean", action="store_true", help="headline timing only (profiling): no e2e, mix, cpu, others, reference")
+    ap.add_argument("--other-steps", type=int, default=10)
     ap.add_argument("--e2e-steps", type=int, default=5)
-    ap.add_argument("--e2e-microbatches", type=int, default=16)
-    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the cpu_baseline leg")
-    ap.add_argument("--cpu-seconds-reference", type=float, default=120.0, help="budget of --impl reference")
+    ap.add_argument("--e2e-microbatches", type=int, default=0, help="0: micro-batches of about 128 MB per tensor")
+    ap.add_argument("--e2e-host-slots", type=int, default=2, help="pinned staging slots per direction and tensor")
     args = ap.parse_args()
+    if args.lean:
+        args.no_e2e = args.no_mix = args.no_cpu = args.no_others = args.no_reference_cuda = True
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     wl = dict(WORKLOADS[args.workload])
