@@ -123,6 +123,24 @@ int exb_lif_forward_record(float *spikes, float *v_mem, float *v_post, const flo
                            int64_t B, int64_t T, int64_t M, int layout,
                            int device, void *stream);
 
+/* exb_lif_forward with the spike raster as one byte per neuron-step instead of a float32.  The reference stores
+ * the count as float (cuda/lif_kernels.h:87 `static_cast<float>(activation)`) and hands that raster to the next
+ * layer (layers/lif.py:296-297); a consumer that can take bytes saves 3 of the forward's 12 bytes per neuron-step.
+ * Counts above 255 are stored as 255: with max_spikes > 255 (EXB_MAX_SPIKES_UNLIMITED included) the caller must say
+ * that this is acceptable (saturate != 0), else EXB_ERR_ARG; the membrane always resets by the true count, and
+ * spike_count receives the true total.  v_mem may be NULL: a forward pass that is neither differentiated nor
+ * recorded needs only the spikes (5 bytes per neuron-step in all).  Time-major layout, M % 4 == 0 and 16-byte
+ * aligned tensors only; otherwise EXB_ERR_UNSUPPORTED and the caller uses exb_lif_forward. */
+int exb_lif_forward_u8(uint8_t *spikes, float *v_mem, const float *input, const float *v_init,
+                       const float *in_scale, int in_scale_mode,
+                       const float *alpha, int alpha_mode,
+                       const float *subtract, int subtract_mode,
+                       const float *theta, int theta_mode,
+                       const float *theta_low, int theta_low_mode,
+                       uint32_t max_spikes, int reset_mode, int saturate,
+                       float *v_post_last, unsigned long long *spike_count,
+                       int64_t B, int64_t T, int64_t M, int device, void *stream);
+
 /* Fused reverse-time EXODUS backward.  Replaces lifBackward + lifBackwardAlpha
  * (cuda/bindings.cu:72-158, kernels cuda/lif_kernels.h:122-168, 199-246) and
  * the tensor glue of IntegrateAndFire.backward (sinabs/exodus/spike.py:251-289):
@@ -204,6 +222,20 @@ int exb_lif_syn_forward(float *spikes, float *v_mem, float *i_syn, const float *
                         uint32_t max_spikes, int reset_mode,
                         float *v_post_last, float *i_last, unsigned long long *spike_count,
                         int64_t B, int64_t T, int64_t M, int device, void *stream);
+
+/* exb_lif_syn_forward with the byte raster of exb_lif_forward_u8 (same saturation rule).  v_mem and i_syn may both
+ * be NULL (inference: only the spikes and the final states are written, 5 bytes per neuron-step instead of 16). */
+int exb_lif_syn_forward_u8(uint8_t *spikes, float *v_mem, float *i_syn, const float *input,
+                           const float *v_init, const float *i_init,
+                           const float *alpha_syn, int alpha_syn_mode, const float *scale_syn, int scale_syn_mode,
+                           const float *scale_mem, int scale_mem_mode,
+                           const float *alpha_mem, int alpha_mem_mode,
+                           const float *subtract, int subtract_mode,
+                           const float *theta, int theta_mode,
+                           const float *theta_low, int theta_low_mode,
+                           uint32_t max_spikes, int reset_mode, int saturate,
+                           float *v_post_last, float *i_last, unsigned long long *spike_count,
+                           int64_t B, int64_t T, int64_t M, int device, void *stream);
 
 int exb_lif_syn_backward(float *grad_input,
                          float *grad_alpha_mem, float *grad_scale_mem, float *grad_alpha_syn, float *grad_scale_syn,

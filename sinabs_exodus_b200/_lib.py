@@ -37,7 +37,7 @@ _lib: Optional[ctypes.CDLL] = None
 
 EXPORTS = (
     "exb_version", "exb_last_error", "exb_status_string", "exb_device_status", "exb_set_wait_limit",
-    "exb_lif_forward", "exb_lif_forward_record", "exb_lif_backward", "exb_leaky_forward", "exb_leaky_backward",
+    "exb_lif_forward", "exb_lif_forward_record", "exb_lif_forward_u8", "exb_lif_syn_forward_u8", "exb_lif_backward", "exb_leaky_forward", "exb_leaky_backward",
     "exb_leaky_scan_workspace_bytes", "exb_leaky_forward_scan", "exb_leaky_backward_scan",
     "exb_leaky_forward_scan_static", "exb_static_scratch_bytes", "exb_lif_syn_forward", "exb_lif_syn_backward",
 )
@@ -73,6 +73,10 @@ def load() -> ctypes.CDLL:
     lib.exb_lif_forward_record.argtypes = [_vp, _vp, _vp, _vp, _vp,
                                            _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _i,
                                            _u32, _i, _vp, _vp] + geometry
+    lib.exb_lif_forward_u8.restype = _i
+    lib.exb_lif_forward_u8.argtypes = [_vp, _vp, _vp, _vp,
+                                       _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _i,
+                                       _u32, _i, _i, _vp, _vp, _i64, _i64, _i64, _i, _vp]
     lib.exb_lif_backward.restype = _i
     lib.exb_lif_backward.argtypes = [_vp, _vp, _vp, _vp,
                                      _vp, _vp, _vp,
@@ -94,6 +98,8 @@ def load() -> ctypes.CDLL:
     syn_params = [_vp, _i] * 7
     lib.exb_lif_syn_forward.restype = _i
     lib.exb_lif_syn_forward.argtypes = [_vp] * 6 + syn_params + [_u32, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i, _vp]
+    lib.exb_lif_syn_forward_u8.restype = _i
+    lib.exb_lif_syn_forward_u8.argtypes = [_vp] * 6 + syn_params + [_u32, _i, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i, _vp]
     lib.exb_lif_syn_backward.restype = _i
     lib.exb_lif_syn_backward.argtypes = ([_vp] * 17 + syn_params + [_u32, _i, _i, _f, _f, _i64, _i64, _i64, _i, _vp])
     lib.exb_static_scratch_bytes.restype = _i64
@@ -211,6 +217,32 @@ def lif_forward(spikes, v_mem, inp, v_init, in_scale: Tuple, alpha: Tuple, subtr
         st = load().exb_lif_forward_record(ptr(spikes), ptr(v_mem), ptr(v_post), ptr(inp), ptr(v_init), *tail)
         _check(st, "exb_lif_forward_record")
         _after_launch(dev)
+
+
+def _require_u8(t: torch.Tensor) -> None:
+    if not t.is_cuda or t.dtype != torch.uint8 or not t.is_contiguous():
+        raise ExodusLibraryError("the compact spike raster must be a contiguous uint8 CUDA tensor")
+
+
+def lif_forward_u8(spikes_u8, v_mem, inp, v_init, in_scale: Tuple, alpha: Tuple, subtract: Tuple, theta: Tuple,
+                   theta_low: Tuple, max_spikes: Optional[int], reset_mode: int, saturate: bool, v_post_last, spike_count,
+                   B: int, T: int, M: int) -> bool:
+    """``exb_lif_forward_u8``: spikes as one byte per neuron-step (``v_mem`` may be None).  Returns False when the
+    shape is not eligible (the caller then uses :func:`lif_forward`)."""
+    if B * T * M == 0:
+        return True
+    _require_u8(spikes_u8)
+    dev = _require_cuda(v_mem, inp, v_init, in_scale[0], alpha[0], subtract[0], theta[0], theta_low[0], v_post_last)
+    ms = MAX_SPIKES_UNLIMITED if max_spikes is None else int(max_spikes)
+    st = load().exb_lif_forward_u8(
+        ptr(spikes_u8), ptr(v_mem), ptr(inp), ptr(v_init), ptr(in_scale[0]), in_scale[1], ptr(alpha[0]), alpha[1],
+        ptr(subtract[0]), subtract[1], ptr(theta[0]), theta[1], ptr(theta_low[0]), theta_low[1],
+        ms, reset_mode, int(bool(saturate)), ptr(v_post_last), ptr(spike_count), B, T, M, dev.index, _stream(dev))
+    if st == 4:
+        return False
+    _check(st, "exb_lif_forward_u8")
+    _after_launch(dev)
+    return True
 
 
 def lif_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, grad_v_mem, grad_v_last,
@@ -334,6 +366,27 @@ def lif_syn_forward(spikes, v_mem, i_syn, inp, v_init, i_init, alpha_syn: Tuple,
     if st == 4:
         return False
     _check(st, "exb_lif_syn_forward")
+    _after_launch(dev)
+    return True
+
+
+def lif_syn_forward_u8(spikes_u8, v_mem, i_syn, inp, v_init, i_init, alpha_syn: Tuple, scale_syn: Tuple, scale_mem: Tuple,
+                       alpha_mem: Tuple, subtract: Tuple, theta: Tuple, theta_low: Tuple, max_spikes: Optional[int],
+                       reset_mode: int, saturate: bool, v_post_last, i_last, spike_count, B: int, T: int, M: int) -> bool:
+    """``exb_lif_syn_forward_u8`` (``v_mem`` and ``i_syn`` both given or both None).  False when not eligible."""
+    if B * T * M == 0:
+        return True
+    _require_u8(spikes_u8)
+    dev = _require_cuda(v_mem, i_syn, inp, v_init, i_init, alpha_syn[0], scale_syn[0], scale_mem[0], alpha_mem[0],
+                        subtract[0], theta[0], theta_low[0], v_post_last, i_last)
+    ms = MAX_SPIKES_UNLIMITED if max_spikes is None else int(max_spikes)
+    st = load().exb_lif_syn_forward_u8(
+        ptr(spikes_u8), ptr(v_mem), ptr(i_syn), ptr(inp), ptr(v_init), ptr(i_init),
+        *_pm(alpha_syn), *_pm(scale_syn), *_pm(scale_mem), *_pm(alpha_mem), *_pm(subtract), *_pm(theta), *_pm(theta_low),
+        ms, reset_mode, int(bool(saturate)), ptr(v_post_last), ptr(i_last), ptr(spike_count), B, T, M, dev.index, _stream(dev))
+    if st == 4:
+        return False
+    _check(st, "exb_lif_syn_forward_u8")
     _after_launch(dev)
     return True
 

@@ -123,7 +123,7 @@ int exb_set_wait_limit(int device, uint32_t polls, int withhold_scan_flags)
 
 }  // extern "C"
 
-static int lif_forward_impl(const char *who, float *spikes, float *v_mem, float *v_post, const float *input, const float *v_init,
+static int lif_forward_impl(const char *who, float *spikes, uint8_t *spikes_u8, float *v_mem, float *v_post, const float *input, const float *v_init,
                     const float *in_scale, int in_scale_mode,
                     const float *alpha, int alpha_mode,
                     const float *subtract, int subtract_mode,
@@ -135,7 +135,12 @@ static int lif_forward_impl(const char *who, float *spikes, float *v_mem, float 
                     int device, void *stream)
 {
     if (int st = check_geometry(B, T, M, layout)) return st;
-    if (!spikes || !v_mem || !input) return fail(EXB_ERR_ARG, "%s: spikes, v_mem and input are required", who);
+    if (spikes_u8) {
+        if (!input) return fail(EXB_ERR_ARG, "%s: spikes and input are required", who);
+        if (layout != EXB_LAYOUT_BTM) return fail(EXB_ERR_UNSUPPORTED, "%s: the compact raster is written by the time-major kernels only", who);
+    } else if (!spikes || !v_mem || !input) {
+        return fail(EXB_ERR_ARG, "%s: spikes, v_mem and input are required", who);
+    }
     if (!alpha || !theta) return fail(EXB_ERR_ARG, "%s: alpha and theta are required", who);
     if (!mode_ok(alpha_mode) || !mode_ok(theta_mode) || (subtract && !mode_ok(subtract_mode)) ||
         (theta_low && !mode_ok(theta_low_mode)) || (in_scale && !mode_ok(in_scale_mode)))
@@ -162,7 +167,15 @@ static int lif_forward_impl(const char *who, float *spikes, float *v_mem, float 
     a.np.scale = exb::make_param(in_scale, in_scale_mode, M);
     a.maxs = max_spikes;
     a.v_post_last = v_post_last; a.spike_count = spike_count; a.v_post = v_post;
+    a.spikes_u8 = spikes_u8;
     a.B = B; a.T = T; a.M = M;
+    if (spikes_u8) {
+        bool used = false;
+        cudaError_t e = exb::tma_enabled() ? exb::launch_lif_forward_tma(a, reset_mode, (cudaStream_t)stream, &used) : cudaSuccess;
+        if (e != cudaSuccess) return launch_status(e, who);
+        if (!used) return fail(EXB_ERR_UNSUPPORTED, "%s: shape or alignment not eligible (needs M %% 4 == 0 and 16-byte aligned tensors)", who);
+        return EXB_OK;
+    }
     return launch_status(exb::launch_lif_forward(a, layout, reset_mode, (cudaStream_t)stream), who);
 }
 
@@ -179,7 +192,7 @@ int exb_lif_forward(float *spikes, float *v_mem, const float *input, const float
                     int64_t B, int64_t T, int64_t M, int layout,
                     int device, void *stream)
 {
-    return lif_forward_impl("exb_lif_forward", spikes, v_mem, nullptr, input, v_init, in_scale, in_scale_mode, alpha,
+    return lif_forward_impl("exb_lif_forward", spikes, nullptr, v_mem, nullptr, input, v_init, in_scale, in_scale_mode, alpha,
                             alpha_mode, subtract, subtract_mode, theta, theta_mode, theta_low, theta_low_mode,
                             max_spikes, reset_mode, v_post_last, spike_count, B, T, M, layout, device, stream);
 }
@@ -196,9 +209,28 @@ int exb_lif_forward_record(float *spikes, float *v_mem, float *v_post, const flo
                            int device, void *stream)
 {
     if (!v_post) return fail(EXB_ERR_ARG, "exb_lif_forward_record: v_post is required (use exb_lif_forward without it)");
-    return lif_forward_impl("exb_lif_forward_record", spikes, v_mem, v_post, input, v_init, in_scale, in_scale_mode,
+    return lif_forward_impl("exb_lif_forward_record", spikes, nullptr, v_mem, v_post, input, v_init, in_scale, in_scale_mode,
                             alpha, alpha_mode, subtract, subtract_mode, theta, theta_mode, theta_low, theta_low_mode,
                             max_spikes, reset_mode, v_post_last, spike_count, B, T, M, layout, device, stream);
+}
+
+int exb_lif_forward_u8(uint8_t *spikes, float *v_mem, const float *input, const float *v_init,
+                       const float *in_scale, int in_scale_mode,
+                       const float *alpha, int alpha_mode,
+                       const float *subtract, int subtract_mode,
+                       const float *theta, int theta_mode,
+                       const float *theta_low, int theta_low_mode,
+                       uint32_t max_spikes, int reset_mode, int saturate,
+                       float *v_post_last, unsigned long long *spike_count,
+                       int64_t B, int64_t T, int64_t M, int device, void *stream)
+{
+    if (!spikes) return fail(EXB_ERR_ARG, "exb_lif_forward_u8: spikes is required");
+    if (max_spikes > 255u && !saturate)
+        return fail(EXB_ERR_ARG, "exb_lif_forward_u8: more than 255 spikes per step are possible (max_spikes = %u); "
+                    "pass saturate != 0 to store min(count, 255)", max_spikes);
+    return lif_forward_impl("exb_lif_forward_u8", nullptr, spikes, v_mem, nullptr, input, v_init, in_scale, in_scale_mode,
+                            alpha, alpha_mode, subtract, subtract_mode, theta, theta_mode, theta_low, theta_low_mode,
+                            max_spikes, reset_mode, v_post_last, spike_count, B, T, M, EXB_LAYOUT_BTM, device, stream);
 }
 
 int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, float *grad_scale,
@@ -425,7 +457,9 @@ int exb_leaky_forward_scan_static(float *out, const float *input, const float *v
     return EXB_OK;
 }
 
-int exb_lif_syn_forward(float *spikes, float *v_mem, float *i_syn, const float *input,
+}  // extern "C"
+
+static int lif_syn_forward_impl(const char *who, float *spikes, uint8_t *spikes_u8, float *v_mem, float *i_syn, const float *input,
                         const float *v_init, const float *i_init,
                         const float *alpha_syn, int alpha_syn_mode, const float *scale_syn, int scale_syn_mode,
                         const float *scale_mem, int scale_mem_mode,
@@ -438,7 +472,12 @@ int exb_lif_syn_forward(float *spikes, float *v_mem, float *i_syn, const float *
                         int64_t B, int64_t T, int64_t M, int device, void *stream)
 {
     if (int st = check_geometry(B, T, M, EXB_LAYOUT_BTM)) return st;
-    if (!spikes || !v_mem || !i_syn || !input || !alpha_syn || !alpha_mem || !theta)
+    if (spikes_u8) {
+        if (!input || !alpha_syn || !alpha_mem || !theta)
+            return fail(EXB_ERR_ARG, "%s: spikes, input, alpha_syn, alpha_mem and theta are required", who);
+        if ((v_mem != nullptr) != (i_syn != nullptr))
+            return fail(EXB_ERR_ARG, "%s: pass both v_mem and i_syn or neither", who);
+    } else if (!spikes || !v_mem || !i_syn || !input || !alpha_syn || !alpha_mem || !theta)
         return fail(EXB_ERR_ARG, "exb_lif_syn_forward: spikes, v_mem, i_syn, input, alpha_syn, alpha_mem and theta are required");
     if (!mode_ok(alpha_syn_mode) || !mode_ok(alpha_mem_mode) || !mode_ok(theta_mode) ||
         (scale_syn && !mode_ok(scale_syn_mode)) || (scale_mem && !mode_ok(scale_mem_mode)) ||
@@ -465,12 +504,55 @@ int exb_lif_syn_forward(float *spikes, float *v_mem, float *i_syn, const float *
     a.scale_syn = exb::make_param(scale_syn, scale_syn_mode, M);
     a.maxs = max_spikes;
     a.v_post_last = v_post_last; a.i_last = i_last; a.spike_count = spike_count;
+    a.spikes_u8 = spikes_u8;
     a.B = B; a.T = T; a.M = M;
     bool used = false;
     cudaError_t e = exb::launch_lif_syn_forward(a, reset_mode, (cudaStream_t)stream, &used);
     if (e != cudaSuccess) return launch_status(e, "exb_lif_syn_forward");
     if (!used) return fail(EXB_ERR_UNSUPPORTED, "exb_lif_syn_forward: shape or alignment not eligible (needs M %% 4 == 0 and 16-byte aligned tensors)");
     return EXB_OK;
+}
+
+extern "C" {
+
+int exb_lif_syn_forward(float *spikes, float *v_mem, float *i_syn, const float *input,
+                        const float *v_init, const float *i_init,
+                        const float *alpha_syn, int alpha_syn_mode, const float *scale_syn, int scale_syn_mode,
+                        const float *scale_mem, int scale_mem_mode,
+                        const float *alpha_mem, int alpha_mem_mode,
+                        const float *subtract, int subtract_mode,
+                        const float *theta, int theta_mode,
+                        const float *theta_low, int theta_low_mode,
+                        uint32_t max_spikes, int reset_mode,
+                        float *v_post_last, float *i_last, unsigned long long *spike_count,
+                        int64_t B, int64_t T, int64_t M, int device, void *stream)
+{
+    return lif_syn_forward_impl("exb_lif_syn_forward", spikes, nullptr, v_mem, i_syn, input, v_init, i_init, alpha_syn,
+                                alpha_syn_mode, scale_syn, scale_syn_mode, scale_mem, scale_mem_mode, alpha_mem,
+                                alpha_mem_mode, subtract, subtract_mode, theta, theta_mode, theta_low, theta_low_mode,
+                                max_spikes, reset_mode, v_post_last, i_last, spike_count, B, T, M, device, stream);
+}
+
+int exb_lif_syn_forward_u8(uint8_t *spikes, float *v_mem, float *i_syn, const float *input,
+                           const float *v_init, const float *i_init,
+                           const float *alpha_syn, int alpha_syn_mode, const float *scale_syn, int scale_syn_mode,
+                           const float *scale_mem, int scale_mem_mode,
+                           const float *alpha_mem, int alpha_mem_mode,
+                           const float *subtract, int subtract_mode,
+                           const float *theta, int theta_mode,
+                           const float *theta_low, int theta_low_mode,
+                           uint32_t max_spikes, int reset_mode, int saturate,
+                           float *v_post_last, float *i_last, unsigned long long *spike_count,
+                           int64_t B, int64_t T, int64_t M, int device, void *stream)
+{
+    if (!spikes) return fail(EXB_ERR_ARG, "exb_lif_syn_forward_u8: spikes is required");
+    if (max_spikes > 255u && !saturate)
+        return fail(EXB_ERR_ARG, "exb_lif_syn_forward_u8: more than 255 spikes per step are possible (max_spikes = %u); "
+                    "pass saturate != 0 to store min(count, 255)", max_spikes);
+    return lif_syn_forward_impl("exb_lif_syn_forward_u8", nullptr, spikes, v_mem, i_syn, input, v_init, i_init, alpha_syn,
+                                alpha_syn_mode, scale_syn, scale_syn_mode, scale_mem, scale_mem_mode, alpha_mem,
+                                alpha_mem_mode, subtract, subtract_mode, theta, theta_mode, theta_low, theta_low_mode,
+                                max_spikes, reset_mode, v_post_last, i_last, spike_count, B, T, M, device, stream);
 }
 
 int exb_lif_syn_backward(float *grad_input,

@@ -14,6 +14,7 @@ struct LifFwdArgs {
     float *v_post_last;
     unsigned long long *spike_count;
     float *v_post;     // optional full record of the potential after each step's reset (time-major kernels only)
+    uint8_t *spikes_u8 = nullptr;   // compact raster instead of `spikes` (TMA-staged kernels only; v_mem may then be null)
     int64_t B, T, M;
 };
 
@@ -51,6 +52,7 @@ struct LifSynFwdArgs {
     unsigned maxs;
     float *v_post_last, *i_last;
     unsigned long long *spike_count;
+    uint8_t *spikes_u8 = nullptr;   // compact raster instead of `spikes`; v_mem and i_syn may then be null
     int64_t B, T, M;
 };
 

@@ -359,4 +359,23 @@ __device__ __forceinline__ void stv(float *p, const float (&d)[V])
     }
 }
 
+// Spike counts of one thread's V adjacent neurons to the output raster: float32 as the reference stores them
+// (cuda/lif_kernels.h:87), or one byte each, saturating at 255 (the compact raster; V = 4 -> one 32-bit store).
+template <int V>
+__device__ __forceinline__ void st_spikes(float *p, const float (&af)[V]) { stv<V>(p, af); }
+
+template <int V>
+__device__ __forceinline__ void st_spikes(uint8_t *p, const float (&af)[V])
+{
+    unsigned b[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) b[j] = min(__float2uint_rz(af[j]), 255u);
+    if (V == 4) {
+        __stcs(reinterpret_cast<unsigned *>(p), b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24));
+    } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) __stcs(p + j, (uint8_t)b[j]);
+    }
+}
+
 }  // namespace exb

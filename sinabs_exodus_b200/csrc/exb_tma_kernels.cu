@@ -4,6 +4,7 @@
 #include "exb_tma_common.cuh"
 
 #include <mutex>
+#include <type_traits>
 
 namespace exb {
 
@@ -11,7 +12,9 @@ namespace exb {
 // spike scan forward
 // ===========================================================================
 // REC: also write the potential after each step's reset (the layers' `record_states`).
-template <int RESET, int NW, int V, bool UNI, bool REC>
+// ST: element type of the spike raster (float, or uint8_t for the compact raster); WV: write v_mem (a forward
+// pass that nobody differentiates or records needs only the spikes).
+template <int RESET, int NW, int V, bool UNI, bool REC, typename ST, bool WV>
 __global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V, (V == 4 && !UNI)>::value)
 lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, const int tiles_m, const PipeCfg pc)
 {
@@ -51,8 +54,8 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
             af[j] = 0.0f;
         }
         const int64_t base = ((int64_t)b * T) * A.M + mm;
-        float *sp = A.spikes + base;
-        float *vm = A.v_mem + base;
+        ST *sp = (std::is_same<ST, float>::value ? reinterpret_cast<ST *>(A.spikes) : reinterpret_cast<ST *>(A.spikes_u8)) + base;
+        float *vm = WV ? A.v_mem + base : nullptr;
         float *rec = REC ? A.v_post + base : nullptr;
         const int64_t M = A.M;
         const int col = tile_col_off<NW, V>(pc.tc, c);
@@ -70,8 +73,8 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
                 lds_vec<V>(xs, st + tt * G::BW);
                 lif_step_vec<RESET, V, NQ>(v, af, xs, q, cfg, cnt);
                 if (valid) {
-                    stv<V>(sp, af);
-                    stv<V>(vm, v);
+                    st_spikes<V>(sp, af);
+                    if (WV) stv<V>(vm, v);
                     if (REC) {
                         float vp[V];
 #pragma unroll
@@ -80,7 +83,7 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
                     }
                 }
                 sp += M;
-                vm += M;
+                if (WV) vm += M;
                 if (REC) rec += M;
             }
             release_chunk(ring, pos, lane);
@@ -275,7 +278,10 @@ static cudaError_t run_lif_fwd(const LifFwdArgs &a, cudaStream_t s, bool *used)
     const int tiles_m = (int)((a.M + G::W - 1) / G::W);
     const size_t smem = tma_smem_bytes<NW, V>(1, pc);
     if (smem > 200 * 1024) return cudaSuccess;
-    auto kern = a.v_post ? lif_fwd_tma_kernel<RESET, NW, V, UNI, true> : lif_fwd_tma_kernel<RESET, NW, V, UNI, false>;
+    auto kern = a.spikes_u8 ? (a.v_mem ? lif_fwd_tma_kernel<RESET, NW, V, UNI, false, uint8_t, true>
+                                       : lif_fwd_tma_kernel<RESET, NW, V, UNI, false, uint8_t, false>)
+                : a.v_post  ? lif_fwd_tma_kernel<RESET, NW, V, UNI, true, float, true>
+                            : lif_fwd_tma_kernel<RESET, NW, V, UNI, false, float, true>;
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
     kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m, pc);
@@ -286,9 +292,12 @@ static cudaError_t run_lif_fwd(const LifFwdArgs &a, cudaStream_t s, bool *used)
 cudaError_t launch_lif_forward_tma(const LifFwdArgs &a, int reset_mode, cudaStream_t s, bool *used)
 {
     *used = false;
-    if (!eligible(a.B, a.T, a.M) || !aligned16(a.spikes) || !aligned16(a.v_mem) || !aligned16(a.input) ||
-        (a.v_post && !aligned16(a.v_post)))
+    if (!eligible(a.B, a.T, a.M) || !aligned16(a.input) || (a.v_post && !aligned16(a.v_post))) return cudaSuccess;
+    if (a.spikes_u8) {      // compact raster: no float raster, v_mem optional, no post-reset record
+        if (!aligned16(a.spikes_u8) || (a.v_mem && !aligned16(a.v_mem)) || a.v_post) return cudaSuccess;
+    } else if (!aligned16(a.spikes) || !aligned16(a.v_mem)) {
         return cudaSuccess;
+    }
     const bool wide = use_wide(a.B, a.M);
     const bool uni = a.np.uniform();
     if (reset_mode == EXB_RESET_SUBTRACT) {

@@ -38,7 +38,9 @@ struct SynGeom {
     static constexpr int TF = TC * G::W;      // floats of one tensor in one stage
 };
 
-template <int RESET, int NW, int V, bool UNI, int TC>
+// ST: element type of the spike raster (float, or uint8_t for the compact raster); WS: write v_mem and i_syn
+// (a forward pass that nobody differentiates or records needs only the spikes).
+template <int RESET, int NW, int V, bool UNI, int TC, typename ST, bool WS>
 __global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V, (V == 4)>::value)
 lif_syn_fwd_tma_kernel(const __grid_constant__ TmaMaps6 maps, const LifSynFwdArgs A, const int tiles_m, const int nstages)
 {
@@ -87,9 +89,9 @@ lif_syn_fwd_tma_kernel(const __grid_constant__ TmaMaps6 maps, const LifSynFwdArg
         // Element offsets inside one batch item fit 32 bits (the launcher checks T*M < 2^31): one 32-bit offset
         // per step serves all three outputs, each address one widening multiply-add from its base.
         const int64_t base = ((int64_t)b * T) * A.M + mm;
-        float *const is_b = A.i_syn + base;
-        float *const sp_b = A.spikes + base;
-        float *const vm_b = A.v_mem + base;
+        float *const is_b = WS ? A.i_syn + base : nullptr;
+        ST *const sp_b = (std::is_same<ST, float>::value ? reinterpret_cast<ST *>(A.spikes) : reinterpret_cast<ST *>(A.spikes_u8)) + base;
+        float *const vm_b = WS ? A.v_mem + base : nullptr;
         const int Mi = (int)A.M;
         const int col = tile_col_off<NW, V>(TC, c);
         SpikeTotal cnt;
@@ -107,9 +109,9 @@ lif_syn_fwd_tma_kernel(const __grid_constant__ TmaMaps6 maps, const LifSynFwdArg
             }
             lif_step_vec<RESET, V, NQ>(v, af, isyn, q, cfg, cnt);
             if (valid) {
-                stv<V>(is_b + o, isyn);
-                stv<V>(sp_b + o, af);
-                stv<V>(vm_b + o, v);
+                if (WS) stv<V>(is_b + o, isyn);
+                st_spikes<V>(sp_b + o, af);
+                if (WS) stv<V>(vm_b + o, v);
             }
         };
 
@@ -351,11 +353,15 @@ static int syn_stages(size_t stage_bytes, int64_t ctas)
 }
 
 // Time steps per stage: the larger of the two compiled values whose ring still has 4 stages (3 at least).
-// EXB_TMA_TC in the environment forces one of them (tuning aid).
+// EXB_SYN_FWD_TC / EXB_SYN_BWD_TC (else EXB_TMA_TC) in the environment force one of them (tuning aid).
 template <int TC_BIG, int TC_SMALL>
-static int syn_pick_tc(int w, int nmaps, int64_t ctas)
+static int syn_pick_tc(int w, int nmaps, int64_t ctas, bool backward)
 {
-    static const int env_tc = env_int("EXB_TMA_TC", 0);
+    static const int env_any = env_int("EXB_TMA_TC", 0);
+    static const int env_fwd = env_int("EXB_SYN_FWD_TC", 0);
+    static const int env_bwd = env_int("EXB_SYN_BWD_TC", 0);
+    const int env_dir = backward ? env_bwd : env_fwd;
+    const int env_tc = env_dir ? env_dir : env_any;
     if (env_tc == TC_BIG || env_tc == TC_SMALL) return env_tc;
     const size_t big = (size_t)TC_BIG * w * 4 * nmaps;
     if (big <= 16 * 1024 && syn_stages(big, ctas) >= 4) return TC_BIG;
@@ -375,7 +381,9 @@ static cudaError_t run_syn_fwd(const LifSynFwdArgs &a, cudaStream_t s, bool *use
     for (int i = 1; i < 6; ++i) maps.m[i] = maps.m[0];
     const PipeCfg pc = {TC, nstages};
     const size_t smem = tma_smem_bytes<NW, V>(1, pc);
-    auto kern = lif_syn_fwd_tma_kernel<RESET, NW, V, UNI, TC>;
+    auto kern = a.spikes_u8 ? (a.v_mem ? lif_syn_fwd_tma_kernel<RESET, NW, V, UNI, TC, uint8_t, true>
+                                       : lif_syn_fwd_tma_kernel<RESET, NW, V, UNI, TC, uint8_t, false>)
+                            : lif_syn_fwd_tma_kernel<RESET, NW, V, UNI, TC, float, true>;
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
     kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m, nstages);
@@ -387,10 +395,10 @@ template <int RESET>
 static cudaError_t pick_syn_fwd(const LifSynFwdArgs &a, cudaStream_t s, bool *used)
 {
     if (!use_wide(a.B, a.M)) {
-        const int tc = syn_pick_tc<16, 8>(128, 1, a.B * ((a.M + 127) / 128));
+        const int tc = syn_pick_tc<16, 8>(128, 1, a.B * ((a.M + 127) / 128), false);
         return tc == 16 ? run_syn_fwd<RESET, NWARPS, 1, true, 16>(a, s, used) : run_syn_fwd<RESET, NWARPS, 1, true, 8>(a, s, used);
     }
-    const int tc = syn_pick_tc<4, 2>(512, 1, a.B * ((a.M + 511) / 512));
+    const int tc = syn_pick_tc<4, 2>(512, 1, a.B * ((a.M + 511) / 512), false);
     if (syn_uniform(a.np, a.alpha_syn, a.scale_syn))
         return tc == 4 ? run_syn_fwd<RESET, NWARPS, 4, true, 4>(a, s, used) : run_syn_fwd<RESET, NWARPS, 4, true, 2>(a, s, used);
     return tc == 4 ? run_syn_fwd<RESET, NWARPS, 4, false, 4>(a, s, used) : run_syn_fwd<RESET, NWARPS, 4, false, 2>(a, s, used);
@@ -399,9 +407,13 @@ static cudaError_t pick_syn_fwd(const LifSynFwdArgs &a, cudaStream_t s, bool *us
 cudaError_t launch_lif_syn_forward(const LifSynFwdArgs &a, int reset_mode, cudaStream_t s, bool *used)
 {
     *used = false;
-    if (!eligible(a.B, a.T, a.M) || !aligned16(a.spikes) || !aligned16(a.v_mem) || !aligned16(a.i_syn) ||
-        !aligned16(a.input) || a.T * a.M >= (1ll << 31))
+    if (!eligible(a.B, a.T, a.M) || !aligned16(a.input) || a.T * a.M >= (1ll << 31)) return cudaSuccess;
+    if (a.spikes_u8) {      // compact raster: v_mem and i_syn are written together or not at all
+        if (!aligned16(a.spikes_u8) || (a.v_mem != nullptr) != (a.i_syn != nullptr)) return cudaSuccess;
+        if (a.v_mem && (!aligned16(a.v_mem) || !aligned16(a.i_syn))) return cudaSuccess;
+    } else if (!aligned16(a.spikes) || !aligned16(a.v_mem) || !aligned16(a.i_syn)) {
         return cudaSuccess;
+    }
     return reset_mode == EXB_RESET_SUBTRACT ? pick_syn_fwd<EXB_RESET_SUBTRACT>(a, s, used)
                                             : pick_syn_fwd<EXB_RESET_TO_VALUE>(a, s, used);
 }
@@ -439,11 +451,11 @@ static cudaError_t pick_syn_bwd(const LifSynBwdArgs &a, cudaStream_t s, bool *us
 {
     const int nmaps = 2 + (SURR == EXB_SURR_GENERIC ? 1 : 0) + (WG ? 1 : 0) + (a.gv ? 1 : 0) + (a.g_isyn ? 1 : 0);
     if (!use_wide(a.B, a.M)) {
-        const int tc = syn_pick_tc<8, 4>(128, nmaps, a.B * ((a.M + 127) / 128));
+        const int tc = syn_pick_tc<8, 4>(128, nmaps, a.B * ((a.M + 127) / 128), true);
         return tc == 8 ? run_syn_bwd<SURR, RESET, WG, EXTRA, NWARPS, 1, true, 8>(a, s, used)
                        : run_syn_bwd<SURR, RESET, WG, EXTRA, NWARPS, 1, true, 4>(a, s, used);
     }
-    const int tc = syn_pick_tc<4, 2>(512, nmaps, a.B * ((a.M + 511) / 512));
+    const int tc = syn_pick_tc<4, 2>(512, nmaps, a.B * ((a.M + 511) / 512), true);
     if (syn_uniform(a.np, a.alpha_syn, a.scale_syn))
         return tc == 4 ? run_syn_bwd<SURR, RESET, WG, EXTRA, NWARPS, 4, true, 4>(a, s, used)
                        : run_syn_bwd<SURR, RESET, WG, EXTRA, NWARPS, 4, true, 2>(a, s, used);

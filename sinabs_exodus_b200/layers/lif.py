@@ -27,7 +27,7 @@ from ..compat.activation import (
 )
 from ..compat.layers import LIF as LIFBase
 from ..leaky import LeakyIntegratorTM
-from ..spike import IntegrateAndFireTM, LIFSynapticTM, fused_synaptic_eligible
+from ..spike import IntegrateAndFireTM, LIFSynapticTM, _flat32, _mode_of, fused_synaptic_eligible
 
 __all__ = ["LIF"]
 
@@ -248,6 +248,99 @@ class LIF(LIFBase):
                 v_rec = torch.where(spikes > 0, c.expand_as(v_pre), v_pre)
         return spikes, v_rec, v_post_last, count
 
+    # ------------------------------------------------------------------
+    # compact spike output (inference)
+    _spike_dtype = torch.float32
+    _spike_saturate = False
+
+    def set_spike_output(self, dtype: torch.dtype = torch.float32, saturate: bool = False) -> "LIF":
+        """Choose the element type of the layer's output raster.
+
+        ``torch.float32`` (default) is the reference's format.  ``torch.uint8`` makes the forward kernel write one
+        byte per neuron and step (3 of the forward's 12 bytes per neuron-step less on the way to a consumer that can
+        take bytes) and, unless ``record_states`` is set, skip the membrane-potential tensor altogether.  Integer
+        tensors carry no gradient, so this is for forward passes that are not differentiated: calling the layer with
+        autograd recording raises.  Counts above 255 are stored as 255; with a spike function that allows more
+        (``MultiSpike``, ``MaxSpike(k > 255)``) that must be accepted explicitly with ``saturate=True``.  The layer's
+        state and ``firing_rate`` always use the true counts.
+        """
+        if dtype not in (torch.float32, torch.uint8):
+            raise ValueError("spike output must be torch.float32 or torch.uint8")
+        if dtype == torch.uint8:
+            if self.spike_fn is None:
+                raise ValueError("a non-spiking layer has no spike raster")
+            k = self.max_num_spikes_per_bin
+            if (k is None or k > 255) and not saturate:
+                raise ValueError("this spike function can emit more than 255 spikes per step; pass saturate=True to "
+                                 "store min(count, 255)")
+        self._spike_dtype = dtype
+        self._spike_saturate = bool(saturate)
+        return self
+
+    def _forward_compact(self, x: torch.Tensor, original_shape, has_synapse: bool):
+        """Forward with the byte raster: straight to the library, no autograd node."""
+        if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in self.parameters())):
+            raise ValueError("the uint8 spike output carries no gradient: call the layer under torch.no_grad() "
+                             "(or set_spike_output(torch.float32) for training)")
+        batch, time_steps, *trailing_dim = original_shape
+        trailing = tuple(trailing_dim)
+        dev = x.device
+        B, T, M = x.shape
+        N = B * M
+        alpha_mem, scale_mem = self._membrane_decay()
+        flat = lambda v: _flat32(_flat_param(v, trailing, batch, dev))
+        a_mem, s_mem = flat(alpha_mem), flat(scale_mem)
+        th, lo = flat(self.spike_threshold), flat(self.min_v_mem)
+        if isinstance(self.reset_fn, MembraneReset):
+            reset_mode, c = _lib.RESET_TO_VALUE, flat(self.reset_fn.reset_value)
+        else:
+            reset_mode, c = _lib.RESET_SUBTRACT, flat(self.reset_fn.subtract_value)
+        self._validate_once(a_mem, dev)
+        spec = lambda t, name: (t, _mode_of(t, M, N, name))
+        spikes = torch.empty((B, T, M), dtype=torch.uint8, device=dev)
+        keep = bool(self.record_states)
+        v_mem = torch.empty_like(x) if keep else None
+        v_post_last = torch.empty(N, dtype=torch.float32, device=dev)
+        count = torch.zeros(1, dtype=torch.int64, device=dev)
+        v0 = self.v_mem.reshape(-1).to(torch.float32).contiguous()
+        i_syn = None
+        if has_synapse:
+            a_syn = flat(self._synaptic_decay())
+            i_syn = torch.empty_like(x) if keep else None
+            i_last = torch.empty(N, dtype=torch.float32, device=dev)
+            i0 = self.i_syn.reshape(-1).to(torch.float32).contiguous()
+            done = _lib.lif_syn_forward_u8(
+                spikes, v_mem, i_syn, x, v0, i0, spec(a_syn, "alpha_syn"),
+                spec(a_syn if self.decay_early else None, "scale_syn"), spec(s_mem, "scale_mem"), spec(a_mem, "alpha_mem"),
+                spec(c, "subtract"), spec(th, "threshold"), spec(lo, "min_v_mem"), self.max_num_spikes_per_bin,
+                reset_mode, self._spike_saturate, v_post_last, i_last, count, B, T, M)
+        else:
+            done = _lib.lif_forward_u8(
+                spikes, v_mem, x, v0, spec(s_mem, "in_scale"), spec(a_mem, "alpha"), spec(c, "subtract"),
+                spec(th, "threshold"), spec(lo, "min_v_mem"), self.max_num_spikes_per_bin, reset_mode,
+                self._spike_saturate, v_post_last, count, B, T, M)
+        if not done:
+            return None        # shape the byte kernels do not take: the caller converts the float raster
+        if has_synapse:
+            self.i_syn = i_last.reshape(batch, *trailing)
+        self.v_mem = v_post_last.reshape(batch, *trailing)
+        if keep:
+            if i_syn is not None:
+                self.recordings["i_syn"] = i_syn.reshape(original_shape)
+            bc = lambda t: t if t.numel() == 1 else (t.view(1, 1, -1) if t.numel() == M else t.view(B, 1, -1))
+            thb, cb = bc(th), bc(th if c is None else c)
+            if reset_mode == _lib.RESET_SUBTRACT:       # true counts for the recording: rebuilt from v_mem, not from the bytes
+                k = torch.where(v_mem >= thb, torch.div(v_mem, thb).trunc(), torch.zeros_like(v_mem))
+                if self.max_num_spikes_per_bin is not None:
+                    k = k.clamp(max=float(self.max_num_spikes_per_bin))
+                v_rec = v_mem - cb * k
+            else:
+                v_rec = torch.where(spikes > 0, cb.expand_as(v_mem), v_mem)
+            self.recordings["v_mem"] = v_rec.reshape(original_shape)
+        out = spikes.reshape(original_shape)
+        self._set_rate_source(count, out.numel())
+        return out
+
     def _validate_once(self, alpha_mem: torch.Tensor, dev) -> None:
         """Value checks of the reference Function (``spike.py:183,190``): 0 <= alpha <= 1 and
         threshold > min_v_mem.  Each check reads a result back from the GPU, which stalls the
@@ -287,6 +380,18 @@ class LIF(LIFBase):
         self.recordings = dict()
 
         has_synapse = getattr(self, "alpha_syn" if self.train_alphas else "tau_syn", None) is not None
+        if self._spike_dtype == torch.uint8 and self.spike_fn is not None:
+            out = self._forward_compact(x, original_shape, has_synapse) if time_steps > 0 and x.numel() > 0 else None
+            if out is not None:
+                return out
+            # shapes the byte kernels do not take (neurons % 4 != 0, unaligned storage): float raster, converted
+            with torch.no_grad():
+                self._spike_dtype = torch.float32
+                try:
+                    out = self.forward(input_data)
+                finally:
+                    self._spike_dtype = torch.uint8
+            return out.clamp(max=255.0).to(torch.uint8)
         if has_synapse and self.spike_fn is not None and fused_synaptic_eligible(x):
             return self._forward_fused_synaptic(x, original_shape)
 

@@ -216,7 +216,7 @@ def test_layer_lif_sparse_input_long_tau():
     B, T, M = 16, 300, 256
     N = B * M
     g = torch.Generator().manual_seed(11)
-    x_cpu = 4.0 * torch.poisson(torch.full((B, T, M), 0.1), generator=g)
+    x_cpu = 20.0 * torch.poisson(torch.full((B, T, M), 0.1), generator=g)
     go_cpu = torch.randn(B, T, M, generator=g)
     nt = lambda t: t.detach().cpu().permute(0, 2, 1).reshape(N, T).numpy()
     for tau0, from_state in ((90.0, True), (150.0, False)):
@@ -547,15 +547,19 @@ def test_graphed_step_truncated_bptt_on_a_container():
     stateful = [m for m in net.modules() if hasattr(m, "reset_states")]
     for m in stateful:
         m.reset_states()
-    want = []
-    for c, go in zip(chunks, gos):
+
+    def eager(c, go):
         for m in stateful:
             m.zero_grad()                      # the layers' own zero_grad detaches their states
         net.zero_grad(set_to_none=True)
         out = net(c)
         out.backward(go)
-        want.append((out.detach().clone(), [p.grad.clone() for p in net.parameters()]))
+        return out.detach().clone(), [p.grad.clone() for p in net.parameters()]
+
+    want = [eager(c, go) for c, go in zip(chunks, gos)]
     v_want = stateful[0].v_mem.detach().clone()
+    for m in stateful:
+        m.zero_grad()                          # nothing of the eager graphs is left alive when the capture starts
     step = GraphedStep(net, chunks[0], gos[0], carry_state=True)      # used to raise in its second warm-up step
     for m in stateful:
         for name, buf in m.named_buffers(recurse=False):
