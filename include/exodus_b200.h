@@ -42,7 +42,16 @@ enum { EXB_OK = 0, EXB_ERR_ARG = 1, EXB_ERR_ALIGN = 2, EXB_ERR_LAUNCH = 3, EXB_E
        EXB_ERR_DEVICE = 5, EXB_ERR_TIMEOUT = 6 };
 
 enum { EXB_LAYOUT_NT = 0, EXB_LAYOUT_BTM = 1 };
-enum { EXB_PARAM_SCALAR = 0, EXB_PARAM_PER_M = 1, EXB_PARAM_PER_N = 2 };
+enum { EXB_PARAM_SCALAR = 0, EXB_PARAM_PER_M = 1, EXB_PARAM_PER_N = 2, EXB_PARAM_SHAPE_MASK = 3 };
+
+/* Bits that may be OR-ed into a mode to let the kernels derive the decay and the input scale of a stage from
+ * what a layer actually owns, so that the small tensor operations of the reference layer around its kernels
+ * (layers/lif.py:188,194-195,204-214: exp(-1/tau), 1 - alpha, x * alpha) need no launches of their own:
+ *   on an alpha argument  EXB_PARAM_IS_TAU           the values are time constants; alpha = exp(-1/tau)
+ *   on a scale argument   EXB_SCALE_ONE_MINUS_ALPHA  the scale is 1 - alpha of the same stage (pointer must be NULL)
+ *                         EXB_SCALE_TIMES_ALPHA      the scale (given, 1 - alpha, or 1) is multiplied by alpha
+ * The roundings are those of the PyTorch expressions they replace. */
+enum { EXB_PARAM_IS_TAU = 0x10, EXB_SCALE_ONE_MINUS_ALPHA = 0x20, EXB_SCALE_TIMES_ALPHA = 0x40 };
 
 /* What happens to the membrane after a step that emitted spikes.
  * SUBTRACT: v <- v - a*c       (the reference's only mode, cuda/lif_kernels.h:63)
@@ -157,7 +166,13 @@ int exb_lif_forward_u8(uint8_t *spikes, float *v_mem, const float *input, const 
  * With `input` (the forward's unscaled input) given, that sum reads it.  With
  * input == NULL it is rebuilt from v_mem alone, using
  * scale*in_t = v_t - alpha*vpost_{t-1} wherever R_t != 0, at no extra memory
- * traffic; this needs every scale to be non-zero. */
+ * traffic; this needs every scale to be non-zero.
+ * acc_decay (may be NULL; time-major TMA-eligible shapes only, else EXB_ERR_UNSUPPORTED): float64
+ * accumulator with the SHAPE OF THE ALPHA ARGUMENT (1, M or B*M values), zeroed by the caller, to which
+ * the kernel adds the gradient with respect to the values passed as `alpha` -- alpha or, with
+ * EXB_PARAM_IS_TAU, tau -- including the part that reaches them through a scale derived from alpha
+ * (EXB_SCALE_* bits).  It replaces grad_alpha / grad_scale (both must then be NULL) and the reduction
+ * over the batch and the chain rule that the reference leaves to autograd (layers/lif.py:43-44,204). */
 int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, float *grad_scale,
                      const float *grad_spikes, const float *grad_v_mem, const float *grad_v_last,
                      const float *v_mem, const float *surr, const float *v_init, const float *input,
@@ -167,9 +182,15 @@ int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, flo
                      const float *theta, int theta_mode,
                      const float *theta_low, int theta_low_mode,
                      uint32_t max_spikes, int reset_mode,
-                     int surrogate_kind, float surr_p0, float surr_p1,
+                     int surrogate_kind, float surr_p0, float surr_p1, double *acc_decay,
                      int64_t B, int64_t T, int64_t M, int layout,
                      int device, void *stream);
+
+/* Converts float64 accumulators that the backward entry points filled (acc_decay) to the float32 gradient
+ * tensor `out` and clears them, so that the same accumulator serves the next backward pass:
+ * out[i] = (float) acc[i]; acc[i] = 0, for i < n.  One small launch.  No counterpart in the reference, which
+ * leaves the reduction to autograd's expand-backward (layers/lif.py:43-44). */
+int exb_acc_finish(float *out, double *acc, int64_t n, int device, void *stream);
 
 /* Leaky integrator forward, v_t = alpha*v_{t-1} + scale*in_t.  Replaces
  * leakyForward (cuda/bindings.cu:163-193, kernel cuda/leaky_kernels.h:29-58).
@@ -192,12 +213,13 @@ int exb_leaky_forward(float *out, const float *input, const float *v_init,
  * is added to grad_out at t = T-1.  grad_init[N] (may be NULL) = alpha*G_0.
  * grad_alpha[N] (may be NULL) = sum_t G_t * out_{t-1}, out_{-1} = v_init; it
  * needs `out` (the forward result).  grad_scale[N] (may be NULL) =
- * sum_t G_t * in_t needs `input`. */
+ * sum_t G_t * in_t needs `input`.  acc_decay: as for exb_lif_backward (needs `out`, and `input` when the
+ * scale is derived from alpha). */
 int exb_leaky_backward(float *grad_input, float *grad_alpha, float *grad_init, float *grad_scale,
                        const float *grad_out, const float *grad_v_last,
                        const float *out, const float *input, const float *v_init,
                        const float *alpha, int alpha_mode,
-                       const float *in_scale, int in_scale_mode,
+                       const float *in_scale, int in_scale_mode, double *acc_decay,
                        int64_t B, int64_t T, int64_t M, int layout,
                        int device, void *stream);
 
@@ -210,7 +232,9 @@ int exb_leaky_backward(float *grad_input, float *grad_alpha, float *grad_init, f
  * Backward takes gradients w.r.t. spikes and optionally v_mem, v_post_last, i_syn, i_last, and
  * writes grad_input, optional grad_v_init / grad_i_init, and -- all four or none -- the
  * per-instance gradients w.r.t. alpha_mem, scale_mem, alpha_syn, scale_syn (these need `i_syn`;
- * scale_syn must be non-zero: its gradient is rebuilt from i_t - alpha_syn*i_{t-1}). */
+ * scale_syn must be non-zero: its gradient is rebuilt from i_t - alpha_syn*i_{t-1}).
+ * acc_decay_mem / acc_decay_syn (both or neither; they replace the four per-instance outputs): float64
+ * accumulators shaped like alpha_mem / alpha_syn, as acc_decay of exb_lif_backward, one per stage. */
 int exb_lif_syn_forward(float *spikes, float *v_mem, float *i_syn, const float *input,
                         const float *v_init, const float *i_init,
                         const float *alpha_syn, int alpha_syn_mode, const float *scale_syn, int scale_syn_mode,
@@ -252,6 +276,7 @@ int exb_lif_syn_backward(float *grad_input,
                          const float *theta_low, int theta_low_mode,
                          uint32_t max_spikes, int reset_mode,
                          int surrogate_kind, float surr_p0, float surr_p1,
+                         double *acc_decay_mem, double *acc_decay_syn,
                          int64_t B, int64_t T, int64_t M, int device, void *stream);
 
 /* Time-parallel variants of the leaky integrator for long sequences with few neurons
@@ -263,21 +288,24 @@ int exb_lif_syn_backward(float *grad_input,
  * splitting is not applicable (short T, M % 4 != 0); the scan entry points then return
  * EXB_ERR_UNSUPPORTED and the caller uses exb_leaky_forward / exb_leaky_backward.  Arguments
  * and results are those of the plain entry points; results agree to rounding (the carry
- * across segments is folded in a different order). */
+ * across segments is folded in a different order).
+ * workspace_clean != 0: the caller guarantees that the workspace is in the state a scan call leaves it in
+ * (all zero at first, and every call that ran to its end restores that), so the entry point need not clear
+ * it first; with 0 the entry point clears what must start from zero on `stream` before the kernel. */
 int64_t exb_leaky_scan_workspace_bytes(int64_t B, int64_t T, int64_t M);
 
 int exb_leaky_forward_scan(float *out, const float *input, const float *v_init,
                            const float *alpha, int alpha_mode,
                            const float *in_scale, int in_scale_mode,
-                           float *v_last, double *out_sum, void *workspace, int64_t workspace_bytes,
+                           float *v_last, double *out_sum, void *workspace, int64_t workspace_bytes, int workspace_clean,
                            int64_t B, int64_t T, int64_t M, int device, void *stream);
 
 int exb_leaky_backward_scan(float *grad_input, float *grad_alpha, float *grad_init, float *grad_scale,
                             const float *grad_out, const float *grad_v_last,
                             const float *out, const float *input, const float *v_init,
                             const float *alpha, int alpha_mode,
-                            const float *in_scale, int in_scale_mode,
-                            void *workspace, int64_t workspace_bytes,
+                            const float *in_scale, int in_scale_mode, double *acc_decay,
+                            void *workspace, int64_t workspace_bytes, int workspace_clean,
                             int64_t B, int64_t T, int64_t M, int device, void *stream);
 
 /* exb_leaky_forward_scan for callers that have no scratch memory to give.  No counterpart in

@@ -19,6 +19,10 @@ LAYOUT_BTM = 1
 PARAM_SCALAR = 0
 PARAM_PER_M = 1
 PARAM_PER_N = 2
+PARAM_SHAPE_MASK = 3
+PARAM_IS_TAU = 0x10                # on a decay argument: the values are time constants, alpha = exp(-1/tau)
+SCALE_ONE_MINUS_ALPHA = 0x20       # on a scale argument (pointer None): scale = 1 - alpha of the same stage
+SCALE_TIMES_ALPHA = 0x40           # on a scale argument: the scale is multiplied by alpha
 RESET_SUBTRACT = 0
 RESET_TO_VALUE = 1
 SURR_GENERIC = 0
@@ -36,7 +40,7 @@ _f = ctypes.c_float
 _lib: Optional[ctypes.CDLL] = None
 
 EXPORTS = (
-    "exb_version", "exb_last_error", "exb_status_string", "exb_device_status", "exb_set_wait_limit",
+    "exb_version", "exb_last_error", "exb_status_string", "exb_device_status", "exb_set_wait_limit", "exb_acc_finish",
     "exb_lif_forward", "exb_lif_forward_record", "exb_lif_forward_u8", "exb_lif_syn_forward_u8", "exb_lif_backward", "exb_leaky_forward", "exb_leaky_backward",
     "exb_leaky_scan_workspace_bytes", "exb_leaky_forward_scan", "exb_leaky_backward_scan",
     "exb_leaky_forward_scan_static", "exb_static_scratch_bytes", "exb_lif_syn_forward", "exb_lif_syn_backward",
@@ -82,26 +86,28 @@ def load() -> ctypes.CDLL:
                                      _vp, _vp, _vp,
                                      _vp, _vp, _vp, _vp,
                                      _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _i,
-                                     _u32, _i, _i, _f, _f] + geometry
+                                     _u32, _i, _i, _f, _f, _vp] + geometry
+    lib.exb_acc_finish.restype = _i
+    lib.exb_acc_finish.argtypes = [_vp, _vp, _i64, _i, _vp]
     lib.exb_leaky_forward.restype = _i
     lib.exb_leaky_forward.argtypes = [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _vp] + geometry
     lib.exb_leaky_backward.restype = _i
     lib.exb_leaky_backward.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
-                                       _vp, _i, _vp, _i] + geometry
+                                       _vp, _i, _vp, _i, _vp] + geometry
     lib.exb_leaky_scan_workspace_bytes.restype = _i64
     lib.exb_leaky_scan_workspace_bytes.argtypes = [_i64, _i64, _i64]
-    scan_tail = [_vp, _i64, _i64, _i64, _i64, _i, _vp]
+    scan_tail = [_vp, _i64, _i, _i64, _i64, _i64, _i, _vp]
     lib.exb_leaky_forward_scan.restype = _i
     lib.exb_leaky_forward_scan.argtypes = [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _vp] + scan_tail
     lib.exb_leaky_backward_scan.restype = _i
-    lib.exb_leaky_backward_scan.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i] + scan_tail
+    lib.exb_leaky_backward_scan.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp] + scan_tail
     syn_params = [_vp, _i] * 7
     lib.exb_lif_syn_forward.restype = _i
     lib.exb_lif_syn_forward.argtypes = [_vp] * 6 + syn_params + [_u32, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i, _vp]
     lib.exb_lif_syn_forward_u8.restype = _i
     lib.exb_lif_syn_forward_u8.argtypes = [_vp] * 6 + syn_params + [_u32, _i, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i, _vp]
     lib.exb_lif_syn_backward.restype = _i
-    lib.exb_lif_syn_backward.argtypes = ([_vp] * 17 + syn_params + [_u32, _i, _i, _f, _f, _i64, _i64, _i64, _i, _vp])
+    lib.exb_lif_syn_backward.argtypes = ([_vp] * 17 + syn_params + [_u32, _i, _i, _f, _f, _vp, _vp, _i64, _i64, _i64, _i, _vp])
     lib.exb_static_scratch_bytes.restype = _i64
     lib.exb_static_scratch_bytes.argtypes = []
     lib.exb_leaky_forward_scan_static.restype = _i
@@ -248,9 +254,11 @@ def lif_forward_u8(spikes_u8, v_mem, inp, v_init, in_scale: Tuple, alpha: Tuple,
 def lif_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, grad_v_mem, grad_v_last,
                  v_mem, surr, v_init, inp, in_scale: Tuple, alpha: Tuple, subtract: Tuple, theta: Tuple,
                  theta_low: Tuple, max_spikes: Optional[int], reset_mode: int,
-                 surr_kind: int, p0: float, p1: float, B: int, T: int, M: int, layout: int) -> None:
+                 surr_kind: int, p0: float, p1: float, B: int, T: int, M: int, layout: int, acc_decay=None) -> bool:
+    """``acc_decay``: float64 accumulator shaped like the alpha argument (see the header).  Returns False when it was
+    given and the shape is not one the reducing kernels take (nothing was launched)."""
     if B * T * M == 0:      # empty problem: nothing to launch (empty tensors have no storage to point at)
-        return
+        return True
     dev = _require_cuda(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, grad_v_mem, grad_v_last,
                         v_mem, surr, v_init, inp, in_scale[0], alpha[0], subtract[0], theta[0], theta_low[0])
     ms = MAX_SPIKES_UNLIMITED if max_spikes is None else int(max_spikes)
@@ -260,10 +268,25 @@ def lif_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, gra
         ptr(v_mem), ptr(surr), ptr(v_init), ptr(inp),
         ptr(in_scale[0]), in_scale[1], ptr(alpha[0]), alpha[1], ptr(subtract[0]), subtract[1],
         ptr(theta[0]), theta[1], ptr(theta_low[0]), theta_low[1],
-        ms, reset_mode, surr_kind, float(p0), float(p1),
+        ms, reset_mode, surr_kind, float(p0), float(p1), _ptr_f64(acc_decay),
         B, T, M, layout, dev.index, _stream(dev))
+    if st == 4 and acc_decay is not None:
+        return False
     _check(st, "exb_lif_backward")
     _after_launch(dev)
+    return True
+
+
+def acc_finish(out: torch.Tensor, acc: torch.Tensor) -> None:
+    """``exb_acc_finish``: ``out[i] = float(acc[i]); acc[i] = 0`` (float64 accumulators -> float32 gradients)."""
+    n = out.numel()
+    if n == 0:
+        return
+    if not (out.is_cuda and out.dtype == torch.float32 and out.is_contiguous() and acc.is_cuda
+            and acc.dtype == torch.float64 and acc.is_contiguous() and acc.numel() >= n):
+        raise ExodusLibraryError("acc_finish needs a contiguous float32 output and a float64 accumulator of at least its size")
+    dev = out.device
+    _check(load().exb_acc_finish(out.data_ptr(), acc.data_ptr(), n, dev.index, _stream(dev)), "exb_acc_finish")
 
 
 def leaky_forward(out, inp, v_init, alpha: Tuple, in_scale: Tuple, v_last, B: int, T: int, M: int,
@@ -280,17 +303,20 @@ def leaky_forward(out, inp, v_init, alpha: Tuple, in_scale: Tuple, v_last, B: in
 
 
 def leaky_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad_v_last, out, inp, v_init,
-                   alpha: Tuple, in_scale: Tuple, B: int, T: int, M: int, layout: int) -> None:
+                   alpha: Tuple, in_scale: Tuple, B: int, T: int, M: int, layout: int, acc_decay=None) -> bool:
     if B * T * M == 0:      # empty problem: nothing to launch (empty tensors have no storage to point at)
-        return
+        return True
     dev = _require_cuda(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad_v_last, out, inp, v_init,
                         alpha[0], in_scale[0])
     st = load().exb_leaky_backward(ptr(grad_input), ptr(grad_alpha), ptr(grad_init), ptr(grad_scale),
                                    ptr(grad_out), ptr(grad_v_last), ptr(out), ptr(inp), ptr(v_init),
-                                   ptr(alpha[0]), alpha[1], ptr(in_scale[0]), in_scale[1],
+                                   ptr(alpha[0]), alpha[1], ptr(in_scale[0]), in_scale[1], _ptr_f64(acc_decay),
                                    B, T, M, layout, dev.index, _stream(dev))
+    if st == 4 and acc_decay is not None:
+        return False
     _check(st, "exb_leaky_backward")
     _after_launch(dev)
+    return True
 
 
 def leaky_scan_workspace_bytes(B: int, T: int, M: int) -> int:
@@ -299,24 +325,25 @@ def leaky_scan_workspace_bytes(B: int, T: int, M: int) -> int:
 
 
 def leaky_forward_scan(out, inp, v_init, alpha: Tuple, in_scale: Tuple, v_last, workspace, B: int, T: int,
-                       M: int, out_sum=None) -> None:
+                       M: int, out_sum=None, clean: bool = False) -> None:
     dev = _require_cuda(out, inp, v_init, alpha[0], in_scale[0], v_last)
     st = load().exb_leaky_forward_scan(ptr(out), ptr(inp), ptr(v_init), ptr(alpha[0]), alpha[1],
                                        ptr(in_scale[0]), in_scale[1], ptr(v_last), _ptr_f64(out_sum),
-                                       workspace.data_ptr(), workspace.numel() * workspace.element_size(),
+                                       workspace.data_ptr(), workspace.numel() * workspace.element_size(), int(clean),
                                        B, T, M, dev.index, _stream(dev))
     _check(st, "exb_leaky_forward_scan")
     _after_launch(dev)
 
 
 def leaky_backward_scan(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad_v_last, out, inp, v_init,
-                        alpha: Tuple, in_scale: Tuple, workspace, B: int, T: int, M: int) -> None:
+                        alpha: Tuple, in_scale: Tuple, workspace, B: int, T: int, M: int, acc_decay=None,
+                        clean: bool = False) -> None:
     dev = _require_cuda(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad_v_last, out, inp, v_init,
                         alpha[0], in_scale[0])
     st = load().exb_leaky_backward_scan(ptr(grad_input), ptr(grad_alpha), ptr(grad_init), ptr(grad_scale),
                                         ptr(grad_out), ptr(grad_v_last), ptr(out), ptr(inp), ptr(v_init),
-                                        ptr(alpha[0]), alpha[1], ptr(in_scale[0]), in_scale[1],
-                                        workspace.data_ptr(), workspace.numel() * workspace.element_size(),
+                                        ptr(alpha[0]), alpha[1], ptr(in_scale[0]), in_scale[1], _ptr_f64(acc_decay),
+                                        workspace.data_ptr(), workspace.numel() * workspace.element_size(), int(clean),
                                         B, T, M, dev.index, _stream(dev))
     _check(st, "exb_leaky_backward_scan")
     _after_launch(dev)
@@ -395,7 +422,8 @@ def lif_syn_backward(grad_input, grad_alpha_mem, grad_scale_mem, grad_alpha_syn,
                      grad_i_init, grad_spikes, grad_v_mem, grad_v_last, grad_i_syn, grad_i_last, v_mem, i_syn, surr,
                      v_init, i_init, alpha_syn: Tuple, scale_syn: Tuple, scale_mem: Tuple, alpha_mem: Tuple,
                      subtract: Tuple, theta: Tuple, theta_low: Tuple, max_spikes: Optional[int], reset_mode: int,
-                     surr_kind: int, p0: float, p1: float, B: int, T: int, M: int) -> None:
+                     surr_kind: int, p0: float, p1: float, B: int, T: int, M: int, acc_decay_mem=None,
+                     acc_decay_syn=None) -> None:
     dev = _require_cuda(grad_input, grad_alpha_mem, grad_scale_mem, grad_alpha_syn, grad_scale_syn, grad_v_init,
                         grad_i_init, grad_spikes, grad_v_mem, grad_v_last, grad_i_syn, grad_i_last, v_mem, i_syn, surr,
                         v_init, i_init, alpha_syn[0], scale_syn[0], scale_mem[0], alpha_mem[0], subtract[0], theta[0],
@@ -406,6 +434,7 @@ def lif_syn_backward(grad_input, grad_alpha_mem, grad_scale_mem, grad_alpha_syn,
         ptr(grad_v_init), ptr(grad_i_init), ptr(grad_spikes), ptr(grad_v_mem), ptr(grad_v_last), ptr(grad_i_syn),
         ptr(grad_i_last), ptr(v_mem), ptr(i_syn), ptr(surr), ptr(v_init), ptr(i_init),
         *_pm(alpha_syn), *_pm(scale_syn), *_pm(scale_mem), *_pm(alpha_mem), *_pm(subtract), *_pm(theta), *_pm(theta_low),
-        ms, reset_mode, surr_kind, float(p0), float(p1), B, T, M, dev.index, _stream(dev))
+        ms, reset_mode, surr_kind, float(p0), float(p1), _ptr_f64(acc_decay_mem), _ptr_f64(acc_decay_syn),
+        B, T, M, dev.index, _stream(dev))
     _check(st, "exb_lif_syn_backward")
     _after_launch(dev)

@@ -41,7 +41,24 @@ struct DeviceGuard {
     }
 };
 
-bool mode_ok(int mode) { return mode == EXB_PARAM_SCALAR || mode == EXB_PARAM_PER_M || mode == EXB_PARAM_PER_N; }
+// Shape in the low bits; the derived-parameter bits only where they mean something: IS_TAU on a decay
+// argument, the SCALE bits on a scale argument.
+bool mode_ok(int mode, int allowed_flags = 0)
+{
+    const int shape = mode & EXB_PARAM_SHAPE_MASK;
+    return (mode & ~(EXB_PARAM_SHAPE_MASK | allowed_flags)) == 0 &&
+           (shape == EXB_PARAM_SCALAR || shape == EXB_PARAM_PER_M || shape == EXB_PARAM_PER_N);
+}
+constexpr int DECAY_FLAGS = EXB_PARAM_IS_TAU;
+constexpr int SCALE_FLAGS = EXB_SCALE_ONE_MINUS_ALPHA | EXB_SCALE_TIMES_ALPHA;
+
+// A scale that is 1 - alpha has no values of its own.
+bool scale_arg_ok(const float *scale, int mode)
+{
+    if (!scale && !(mode & SCALE_FLAGS)) return true;      // absent
+    if (!mode_ok(mode, SCALE_FLAGS)) return false;
+    return !((mode & EXB_SCALE_ONE_MINUS_ALPHA) && scale);
+}
 
 int check_geometry(int64_t B, int64_t T, int64_t M, int layout)
 {
@@ -142,8 +159,8 @@ static int lif_forward_impl(const char *who, float *spikes, uint8_t *spikes_u8, 
         return fail(EXB_ERR_ARG, "%s: spikes, v_mem and input are required", who);
     }
     if (!alpha || !theta) return fail(EXB_ERR_ARG, "%s: alpha and theta are required", who);
-    if (!mode_ok(alpha_mode) || !mode_ok(theta_mode) || (subtract && !mode_ok(subtract_mode)) ||
-        (theta_low && !mode_ok(theta_low_mode)) || (in_scale && !mode_ok(in_scale_mode)))
+    if (!mode_ok(alpha_mode, DECAY_FLAGS) || !mode_ok(theta_mode) || (subtract && !mode_ok(subtract_mode)) ||
+        (theta_low && !mode_ok(theta_low_mode)) || !scale_arg_ok(in_scale, in_scale_mode))
         return fail(EXB_ERR_ARG, "%s: bad parameter mode", who);
     if (reset_mode != EXB_RESET_SUBTRACT && reset_mode != EXB_RESET_TO_VALUE)
         return fail(EXB_ERR_ARG, "%s: bad reset mode %d", who, reset_mode);
@@ -242,7 +259,7 @@ int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, flo
                      const float *theta, int theta_mode,
                      const float *theta_low, int theta_low_mode,
                      uint32_t max_spikes, int reset_mode,
-                     int surrogate_kind, float surr_p0, float surr_p1,
+                     int surrogate_kind, float surr_p0, float surr_p1, double *acc_decay,
                      int64_t B, int64_t T, int64_t M, int layout,
                      int device, void *stream)
 {
@@ -250,9 +267,13 @@ int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, flo
     if (!grad_input || !grad_spikes || !v_mem)
         return fail(EXB_ERR_ARG, "exb_lif_backward: grad_input, grad_spikes and v_mem are required");
     if (!alpha || !theta) return fail(EXB_ERR_ARG, "exb_lif_backward: alpha and theta are required");
-    if (!mode_ok(alpha_mode) || !mode_ok(theta_mode) || (subtract && !mode_ok(subtract_mode)) ||
-        (theta_low && !mode_ok(theta_low_mode)) || (in_scale && !mode_ok(in_scale_mode)))
+    if (!mode_ok(alpha_mode, DECAY_FLAGS) || !mode_ok(theta_mode) || (subtract && !mode_ok(subtract_mode)) ||
+        (theta_low && !mode_ok(theta_low_mode)) || !scale_arg_ok(in_scale, in_scale_mode))
         return fail(EXB_ERR_ARG, "exb_lif_backward: bad parameter mode");
+    const bool scale_derived = (in_scale_mode & SCALE_FLAGS) != 0;
+    if (acc_decay && (grad_alpha || grad_scale))
+        return fail(EXB_ERR_ARG, "exb_lif_backward: acc_decay replaces grad_alpha and grad_scale; pass NULL for those");
+    if (acc_decay && (reinterpret_cast<uintptr_t>(acc_decay) & 7u)) return misaligned("exb_lif_backward");
     if (reset_mode != EXB_RESET_SUBTRACT && reset_mode != EXB_RESET_TO_VALUE)
         return fail(EXB_ERR_ARG, "exb_lif_backward: bad reset mode %d", reset_mode);
     if (reset_mode == EXB_RESET_TO_VALUE && !subtract)
@@ -261,7 +282,7 @@ int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, flo
         return fail(EXB_ERR_ARG, "exb_lif_backward: unknown surrogate kind %d", surrogate_kind);
     if (surrogate_kind == EXB_SURR_GENERIC && !surr)
         return fail(EXB_ERR_ARG, "exb_lif_backward: the generic surrogate needs the `surr` tensor");
-    if (grad_scale && !input && !in_scale)
+    if (grad_scale && !input && !in_scale && !scale_derived)
         return fail(EXB_ERR_ARG, "exb_lif_backward: grad_scale without `input` is rebuilt from v_mem and needs in_scale");
     if (!all_aligned4(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, grad_v_mem, grad_v_last, v_mem, surr,
                       v_init, input, in_scale, alpha, subtract, theta, theta_low))
@@ -281,9 +302,13 @@ int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, flo
     a.np.lo = exb::make_param(theta_low, theta_low_mode, M);
     a.np.scale = exb::make_param(in_scale, in_scale_mode, M);
     a.maxs = max_spikes; a.p0 = surr_p0; a.p1 = surr_p1;
+    a.acc_decay = acc_decay;
     a.B = B; a.T = T; a.M = M;
-    return launch_status(exb::launch_lif_backward(a, layout, reset_mode, surrogate_kind, (cudaStream_t)stream),
-                         "exb_lif_backward");
+    const cudaError_t e = exb::launch_lif_backward(a, layout, reset_mode, surrogate_kind, (cudaStream_t)stream);
+    if (e == cudaErrorNotSupported)
+        return fail(EXB_ERR_UNSUPPORTED, "exb_lif_backward: acc_decay needs a shape the TMA-staged kernels take "
+                    "(time-major, M %% 4 == 0, 16-byte aligned tensors)");
+    return launch_status(e, "exb_lif_backward");
 }
 
 int exb_leaky_forward(float *out, const float *input, const float *v_init,
@@ -295,7 +320,7 @@ int exb_leaky_forward(float *out, const float *input, const float *v_init,
 {
     if (int st = check_geometry(B, T, M, layout)) return st;
     if (!out || !input || !alpha) return fail(EXB_ERR_ARG, "exb_leaky_forward: out, input and alpha are required");
-    if (!mode_ok(alpha_mode) || (in_scale && !mode_ok(in_scale_mode)))
+    if (!mode_ok(alpha_mode, DECAY_FLAGS) || !scale_arg_ok(in_scale, in_scale_mode))
         return fail(EXB_ERR_ARG, "exb_leaky_forward: bad parameter mode");
     if (!all_aligned4(out, input, v_init, alpha, in_scale, v_last) || (reinterpret_cast<uintptr_t>(out_sum) & 7u))
         return misaligned("exb_leaky_forward");
@@ -317,17 +342,21 @@ int exb_leaky_backward(float *grad_input, float *grad_alpha, float *grad_init, f
                        const float *grad_out, const float *grad_v_last,
                        const float *out, const float *input, const float *v_init,
                        const float *alpha, int alpha_mode,
-                       const float *in_scale, int in_scale_mode,
+                       const float *in_scale, int in_scale_mode, double *acc_decay,
                        int64_t B, int64_t T, int64_t M, int layout,
                        int device, void *stream)
 {
     if (int st = check_geometry(B, T, M, layout)) return st;
     if (!grad_input || !grad_out || !alpha)
         return fail(EXB_ERR_ARG, "exb_leaky_backward: grad_input, grad_out and alpha are required");
-    if (!mode_ok(alpha_mode) || (in_scale && !mode_ok(in_scale_mode)))
+    if (!mode_ok(alpha_mode, DECAY_FLAGS) || !scale_arg_ok(in_scale, in_scale_mode))
         return fail(EXB_ERR_ARG, "exb_leaky_backward: bad parameter mode");
-    if (grad_alpha && !out) return fail(EXB_ERR_ARG, "exb_leaky_backward: grad_alpha needs `out`");
-    if (grad_scale && !input) return fail(EXB_ERR_ARG, "exb_leaky_backward: grad_scale needs `input`");
+    if ((grad_alpha || acc_decay) && !out) return fail(EXB_ERR_ARG, "exb_leaky_backward: the alpha gradient needs `out`");
+    if ((grad_scale || (acc_decay && (in_scale_mode & SCALE_FLAGS))) && !input)
+        return fail(EXB_ERR_ARG, "exb_leaky_backward: the scale gradient needs `input`");
+    if (acc_decay && (grad_alpha || grad_scale))
+        return fail(EXB_ERR_ARG, "exb_leaky_backward: acc_decay replaces grad_alpha and grad_scale; pass NULL for those");
+    if (acc_decay && (reinterpret_cast<uintptr_t>(acc_decay) & 7u)) return misaligned("exb_leaky_backward");
     if (!all_aligned4(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad_v_last, out, input, v_init, alpha, in_scale))
         return misaligned("exb_leaky_backward");
     if (B == 0 || M == 0 || T == 0) return EXB_OK;
@@ -339,8 +368,13 @@ int exb_leaky_backward(float *grad_input, float *grad_alpha, float *grad_init, f
     a.go = grad_out; a.g_last = grad_v_last; a.out = out; a.input = input; a.v_init = v_init;
     a.alpha = exb::make_param(alpha, alpha_mode, M);
     a.scale = exb::make_param(in_scale, in_scale_mode, M);
+    a.acc_decay = acc_decay;
     a.B = B; a.T = T; a.M = M;
-    return launch_status(exb::launch_leaky_backward(a, layout, (cudaStream_t)stream), "exb_leaky_backward");
+    const cudaError_t e = exb::launch_leaky_backward(a, layout, (cudaStream_t)stream);
+    if (e == cudaErrorNotSupported)
+        return fail(EXB_ERR_UNSUPPORTED, "exb_leaky_backward: acc_decay needs a shape the TMA-staged kernels take "
+                    "(time-major, M %% 4 == 0, 16-byte aligned tensors)");
+    return launch_status(e, "exb_leaky_backward");
 }
 
 int64_t exb_leaky_scan_workspace_bytes(int64_t B, int64_t T, int64_t M)
@@ -352,12 +386,12 @@ int64_t exb_leaky_scan_workspace_bytes(int64_t B, int64_t T, int64_t M)
 int exb_leaky_forward_scan(float *out, const float *input, const float *v_init,
                            const float *alpha, int alpha_mode,
                            const float *in_scale, int in_scale_mode,
-                           float *v_last, double *out_sum, void *workspace, int64_t workspace_bytes,
+                           float *v_last, double *out_sum, void *workspace, int64_t workspace_bytes, int workspace_clean,
                            int64_t B, int64_t T, int64_t M, int device, void *stream)
 {
     if (int st = check_geometry(B, T, M, EXB_LAYOUT_BTM)) return st;
     if (!out || !input || !alpha) return fail(EXB_ERR_ARG, "exb_leaky_forward_scan: out, input and alpha are required");
-    if (!mode_ok(alpha_mode) || (in_scale && !mode_ok(in_scale_mode)))
+    if (!mode_ok(alpha_mode, DECAY_FLAGS) || !scale_arg_ok(in_scale, in_scale_mode))
         return fail(EXB_ERR_ARG, "exb_leaky_forward_scan: bad parameter mode");
     if (!workspace) return fail(EXB_ERR_ARG, "exb_leaky_forward_scan: workspace is required");
     if (!all_aligned4(out, input, v_init, alpha, in_scale, v_last) || (reinterpret_cast<uintptr_t>(out_sum) & 7u))
@@ -373,7 +407,7 @@ int exb_leaky_forward_scan(float *out, const float *input, const float *v_init,
     a.out_sum = out_sum;
     a.B = B; a.T = T; a.M = M;
     bool used = false;
-    cudaError_t e = exb::launch_leaky_forward_scan(a, workspace, workspace_bytes, (cudaStream_t)stream, &used);
+    cudaError_t e = exb::launch_leaky_forward_scan(a, workspace, workspace_bytes, workspace_clean != 0, (cudaStream_t)stream, &used);
     if (e != cudaSuccess) return launch_status(e, "exb_leaky_forward_scan");
     if (!used) return fail(EXB_ERR_UNSUPPORTED, "exb_leaky_forward_scan: shape, alignment or workspace not eligible");
     return EXB_OK;
@@ -383,17 +417,21 @@ int exb_leaky_backward_scan(float *grad_input, float *grad_alpha, float *grad_in
                             const float *grad_out, const float *grad_v_last,
                             const float *out, const float *input, const float *v_init,
                             const float *alpha, int alpha_mode,
-                            const float *in_scale, int in_scale_mode,
-                            void *workspace, int64_t workspace_bytes,
+                            const float *in_scale, int in_scale_mode, double *acc_decay,
+                            void *workspace, int64_t workspace_bytes, int workspace_clean,
                             int64_t B, int64_t T, int64_t M, int device, void *stream)
 {
     if (int st = check_geometry(B, T, M, EXB_LAYOUT_BTM)) return st;
     if (!grad_input || !grad_out || !alpha)
         return fail(EXB_ERR_ARG, "exb_leaky_backward_scan: grad_input, grad_out and alpha are required");
-    if (!mode_ok(alpha_mode) || (in_scale && !mode_ok(in_scale_mode)))
+    if (!mode_ok(alpha_mode, DECAY_FLAGS) || !scale_arg_ok(in_scale, in_scale_mode))
         return fail(EXB_ERR_ARG, "exb_leaky_backward_scan: bad parameter mode");
-    if (grad_alpha && !out) return fail(EXB_ERR_ARG, "exb_leaky_backward_scan: grad_alpha needs `out`");
-    if (grad_scale && !input) return fail(EXB_ERR_ARG, "exb_leaky_backward_scan: grad_scale needs `input`");
+    if ((grad_alpha || acc_decay) && !out) return fail(EXB_ERR_ARG, "exb_leaky_backward_scan: the alpha gradient needs `out`");
+    if ((grad_scale || (acc_decay && (in_scale_mode & SCALE_FLAGS))) && !input)
+        return fail(EXB_ERR_ARG, "exb_leaky_backward_scan: the scale gradient needs `input`");
+    if (acc_decay && (grad_alpha || grad_scale))
+        return fail(EXB_ERR_ARG, "exb_leaky_backward_scan: acc_decay replaces grad_alpha and grad_scale; pass NULL for those");
+    if (acc_decay && (reinterpret_cast<uintptr_t>(acc_decay) & 7u)) return misaligned("exb_leaky_backward_scan");
     if (!workspace) return fail(EXB_ERR_ARG, "exb_leaky_backward_scan: workspace is required");
     if (!all_aligned4(grad_input, grad_alpha, grad_init, grad_scale, grad_out, grad_v_last, out, input, v_init, alpha, in_scale))
         return misaligned("exb_leaky_backward_scan");
@@ -405,12 +443,24 @@ int exb_leaky_backward_scan(float *grad_input, float *grad_alpha, float *grad_in
     a.go = grad_out; a.g_last = grad_v_last; a.out = out; a.input = input; a.v_init = v_init;
     a.alpha = exb::make_param(alpha, alpha_mode, M);
     a.scale = exb::make_param(in_scale, in_scale_mode, M);
+    a.acc_decay = acc_decay;
     a.B = B; a.T = T; a.M = M;
     bool used = false;
-    cudaError_t e = exb::launch_leaky_backward_scan(a, workspace, workspace_bytes, (cudaStream_t)stream, &used);
+    cudaError_t e = exb::launch_leaky_backward_scan(a, workspace, workspace_bytes, workspace_clean != 0, (cudaStream_t)stream, &used);
     if (e != cudaSuccess) return launch_status(e, "exb_leaky_backward_scan");
     if (!used) return fail(EXB_ERR_UNSUPPORTED, "exb_leaky_backward_scan: shape, alignment or workspace not eligible");
     return EXB_OK;
+}
+
+int exb_acc_finish(float *out, double *acc, int64_t n, int device, void *stream)
+{
+    if (n < 0) return fail(EXB_ERR_ARG, "exb_acc_finish: negative size");
+    if (n == 0) return EXB_OK;
+    if (!out || !acc) return fail(EXB_ERR_ARG, "exb_acc_finish: out and acc are required");
+    if ((reinterpret_cast<uintptr_t>(out) & 3u) || (reinterpret_cast<uintptr_t>(acc) & 7u)) return misaligned("exb_acc_finish");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_acc_finish: cannot select device %d", device);
+    return launch_status(exb::launch_acc_finish(out, acc, n, (cudaStream_t)stream), "exb_acc_finish");
 }
 
 int64_t exb_static_scratch_bytes(void) { return (int64_t)exb::leaky_scan_static_capacity(); }
@@ -426,7 +476,7 @@ int exb_leaky_forward_scan_static(float *out, const float *input, const float *v
     if (int st = check_geometry(B, T, M, EXB_LAYOUT_BTM)) return st;
     if (!out || !input || !alpha)
         return fail(EXB_ERR_ARG, "exb_leaky_forward_scan_static: out, input and alpha are required");
-    if (!mode_ok(alpha_mode) || (in_scale && !mode_ok(in_scale_mode)))
+    if (!mode_ok(alpha_mode, DECAY_FLAGS) || !scale_arg_ok(in_scale, in_scale_mode))
         return fail(EXB_ERR_ARG, "exb_leaky_forward_scan_static: bad parameter mode");
     if (!all_aligned4(out, input, v_init, alpha, in_scale, v_last)) return misaligned("exb_leaky_forward_scan_static");
     if (B == 0 || M == 0 || T == 0) return EXB_OK;
@@ -479,8 +529,8 @@ static int lif_syn_forward_impl(const char *who, float *spikes, uint8_t *spikes_
             return fail(EXB_ERR_ARG, "%s: pass both v_mem and i_syn or neither", who);
     } else if (!spikes || !v_mem || !i_syn || !input || !alpha_syn || !alpha_mem || !theta)
         return fail(EXB_ERR_ARG, "exb_lif_syn_forward: spikes, v_mem, i_syn, input, alpha_syn, alpha_mem and theta are required");
-    if (!mode_ok(alpha_syn_mode) || !mode_ok(alpha_mem_mode) || !mode_ok(theta_mode) ||
-        (scale_syn && !mode_ok(scale_syn_mode)) || (scale_mem && !mode_ok(scale_mem_mode)) ||
+    if (!mode_ok(alpha_syn_mode, DECAY_FLAGS) || !mode_ok(alpha_mem_mode, DECAY_FLAGS) || !mode_ok(theta_mode) ||
+        !scale_arg_ok(scale_syn, scale_syn_mode) || !scale_arg_ok(scale_mem, scale_mem_mode) ||
         (subtract && !mode_ok(subtract_mode)) || (theta_low && !mode_ok(theta_low_mode)))
         return fail(EXB_ERR_ARG, "exb_lif_syn_forward: bad parameter mode");
     if (reset_mode != EXB_RESET_SUBTRACT && reset_mode != EXB_RESET_TO_VALUE)
@@ -570,13 +620,14 @@ int exb_lif_syn_backward(float *grad_input,
                          const float *theta_low, int theta_low_mode,
                          uint32_t max_spikes, int reset_mode,
                          int surrogate_kind, float surr_p0, float surr_p1,
+                         double *acc_decay_mem, double *acc_decay_syn,
                          int64_t B, int64_t T, int64_t M, int device, void *stream)
 {
     if (int st = check_geometry(B, T, M, EXB_LAYOUT_BTM)) return st;
     if (!grad_input || !grad_spikes || !v_mem || !alpha_syn || !alpha_mem || !theta)
         return fail(EXB_ERR_ARG, "exb_lif_syn_backward: grad_input, grad_spikes, v_mem, alpha_syn, alpha_mem and theta are required");
-    if (!mode_ok(alpha_syn_mode) || !mode_ok(alpha_mem_mode) || !mode_ok(theta_mode) ||
-        (scale_syn && !mode_ok(scale_syn_mode)) || (scale_mem && !mode_ok(scale_mem_mode)) ||
+    if (!mode_ok(alpha_syn_mode, DECAY_FLAGS) || !mode_ok(alpha_mem_mode, DECAY_FLAGS) || !mode_ok(theta_mode) ||
+        !scale_arg_ok(scale_syn, scale_syn_mode) || !scale_arg_ok(scale_mem, scale_mem_mode) ||
         (subtract && !mode_ok(subtract_mode)) || (theta_low && !mode_ok(theta_low_mode)))
         return fail(EXB_ERR_ARG, "exb_lif_syn_backward: bad parameter mode");
     if (reset_mode != EXB_RESET_SUBTRACT && reset_mode != EXB_RESET_TO_VALUE)
@@ -591,7 +642,13 @@ int exb_lif_syn_backward(float *grad_input,
                        (grad_scale_syn != nullptr);
     if (ngrads != 0 && ngrads != 4)
         return fail(EXB_ERR_ARG, "exb_lif_syn_backward: pass all four parameter-gradient outputs or none");
-    if (ngrads == 4 && !i_syn) return fail(EXB_ERR_ARG, "exb_lif_syn_backward: parameter gradients need `i_syn`");
+    if ((acc_decay_mem != nullptr) != (acc_decay_syn != nullptr))
+        return fail(EXB_ERR_ARG, "exb_lif_syn_backward: pass both acc_decay_mem and acc_decay_syn or neither");
+    if (acc_decay_mem && ngrads != 0)
+        return fail(EXB_ERR_ARG, "exb_lif_syn_backward: the accumulators replace the four per-instance outputs; pass NULL for those");
+    if (acc_decay_mem && ((reinterpret_cast<uintptr_t>(acc_decay_mem) | reinterpret_cast<uintptr_t>(acc_decay_syn)) & 7u))
+        return misaligned("exb_lif_syn_backward");
+    if ((ngrads == 4 || acc_decay_mem) && !i_syn) return fail(EXB_ERR_ARG, "exb_lif_syn_backward: parameter gradients need `i_syn`");
     if (!all_aligned4(grad_input, grad_alpha_mem, grad_scale_mem, grad_alpha_syn, grad_scale_syn, grad_v_init, grad_i_init,
                       grad_spikes, grad_v_mem, grad_v_last, grad_i_syn, grad_i_last, v_mem, i_syn, surr, v_init, i_init,
                       alpha_syn, scale_syn, scale_mem, alpha_mem, subtract, theta, theta_low))
@@ -615,6 +672,7 @@ int exb_lif_syn_backward(float *grad_input,
     a.alpha_syn = exb::make_param(alpha_syn, alpha_syn_mode, M);
     a.scale_syn = exb::make_param(scale_syn, scale_syn_mode, M);
     a.maxs = max_spikes; a.p0 = surr_p0; a.p1 = surr_p1;
+    a.acc_decay_mem = acc_decay_mem; a.acc_decay_syn = acc_decay_syn;
     a.B = B; a.T = T; a.M = M;
     bool used = false;
     cudaError_t e = exb::launch_lif_syn_backward(a, reset_mode, surrogate_kind, (cudaStream_t)stream, &used);

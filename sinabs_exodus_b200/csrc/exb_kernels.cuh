@@ -19,6 +19,9 @@ struct LifFwdArgs {
 };
 
 struct LifBwdArgs {
+    // Parameter-shaped float64 accumulator for the gradient w.r.t. the decay values the caller passed (alpha or
+    // tau), scale derived from alpha included; replaces grad_alpha / grad_scale.  TMA-staged kernels only.
+    double *acc_decay = nullptr;
     float *grad_input, *grad_alpha, *grad_init, *grad_scale;
     const float *go, *gv, *g_last, *v_mem, *surr, *v_init, *input;
     NeuronParams np;
@@ -37,6 +40,7 @@ struct LeakyFwdArgs {
 };
 
 struct LeakyBwdArgs {
+    double *acc_decay = nullptr;      // as in LifBwdArgs
     float *grad_input, *grad_alpha, *grad_init, *grad_scale;
     const float *go, *g_last, *out, *input, *v_init;
     Param alpha, scale;
@@ -57,6 +61,7 @@ struct LifSynFwdArgs {
 };
 
 struct LifSynBwdArgs {
+    double *acc_decay_mem = nullptr, *acc_decay_syn = nullptr;      // both or neither; replace the four per-instance outputs
     float *grad_input;
     float *grad_alpha_mem, *grad_scale_mem, *grad_alpha_syn, *grad_scale_syn;   // all four or none
     float *grad_v_init, *grad_i_init;
@@ -88,10 +93,13 @@ cudaError_t launch_leaky_backward_tma(const LeakyBwdArgs &a, cudaStream_t s, boo
 // Time-parallel leaky integrator (time-major layout): the time axis is cut into segments that
 // run in different CTAs.  Needs caller-provided scratch memory of leaky_scan_workspace_bytes().
 int64_t leaky_scan_workspace_bytes(int64_t B, int64_t T, int64_t M);
-cudaError_t launch_leaky_forward_scan(const LeakyFwdArgs &a, void *workspace, int64_t workspace_bytes, cudaStream_t s,
-                                      bool *used);
-cudaError_t launch_leaky_backward_scan(const LeakyBwdArgs &a, void *workspace, int64_t workspace_bytes, cudaStream_t s,
-                                       bool *used);
+// `clean`: the workspace is known to be in the all-zero state a completed scan leaves it in (no memset needed).
+cudaError_t launch_leaky_forward_scan(const LeakyFwdArgs &a, void *workspace, int64_t workspace_bytes, bool clean,
+                                      cudaStream_t s, bool *used);
+cudaError_t launch_leaky_backward_scan(const LeakyBwdArgs &a, void *workspace, int64_t workspace_bytes, bool clean,
+                                       cudaStream_t s, bool *used);
+// out[i] = (float) acc[i]; acc[i] = 0.
+cudaError_t launch_acc_finish(float *out, double *acc, int64_t n, cudaStream_t s);
 // Forward scan on the library's own fixed scratch array (no caller workspace).
 size_t leaky_scan_static_capacity();
 cudaError_t launch_leaky_forward_scan_static(const LeakyFwdArgs &a, int device, cudaStream_t s, bool *used);

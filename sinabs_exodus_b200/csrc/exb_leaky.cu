@@ -91,8 +91,9 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) leaky_fwd_nt_kernel(const Lea
     const int64_t N = A.B * A.M, T = A.T;
     if (n >= N) return;
     const int64_t b = n / A.M, m = n - b * A.M;
-    const ScanPowers p = scan_powers<E>(A.alpha.get(b, m, 1.0f), lane);
-    const float sc = A.scale.get(b, m, 1.0f);
+    const float alpha_nm = decay_of(A.alpha, b, m);
+    const ScanPowers p = scan_powers<E>(alpha_nm, lane);
+    const float sc = scale_of(A.scale, alpha_nm, b, m);
     float carry = A.v_init ? __ldg(A.v_init + n) : 0.0f;
     const float *rin = A.input + n * T;
     float *rout = A.out + n * T;
@@ -151,8 +152,9 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) leaky_bwd_nt_kernel(const Lea
     const int64_t N = A.B * A.M, T = A.T;
     if (n >= N) return;
     const int64_t b = n / A.M, m = n - b * A.M;
-    const ScanPowers p = scan_powers<E>(A.alpha.get(b, m, 1.0f), lane);
-    const float sc = A.scale.get(b, m, 1.0f);
+    const float alpha_nm = decay_of(A.alpha, b, m);
+    const ScanPowers p = scan_powers<E>(alpha_nm, lane);
+    const float sc = scale_of(A.scale, alpha_nm, b, m);
     const float vinit = A.v_init ? __ldg(A.v_init + n) : 0.0f;
     const float glast = A.g_last ? __ldg(A.g_last + n) : 0.0f;
     const float *rgo = A.go + n * T;
@@ -290,6 +292,7 @@ cudaError_t launch_leaky_backward(const LeakyBwdArgs &a, int layout, cudaStream_
         cudaError_t e = launch_leaky_backward_tma(a, s, &used);
         if (e != cudaSuccess || used) return e;
     }
+    if (a.acc_decay) return cudaErrorNotSupported;      // only the TMA-staged kernels reduce in the kernel
     const bool wa = a.grad_alpha != nullptr, ws = a.grad_scale != nullptr;
     if (wa && ws) return launch_leaky_bwd_t<true, true>(a, layout, s);
     if (wa) return launch_leaky_bwd_t<true, false>(a, layout, s);

@@ -27,8 +27,12 @@ constexpr int SCAN_MAX_SEGMENTS = 64;
 
 // Scratch memory layout (all offsets in 4-byte words):
 //   [0]                       ticket counter
+//   [1]                       number of CTAs that have finished
 //   [16 .. 16+ntiles*nseg)    ready flags
 //   [agg_off ..)              aggregates, ntiles*nseg*W floats
+// The counters and flags must be zero when a launch starts.  The CTA that finishes last puts them back to
+// zero, so a workspace that was zero once stays usable launch after launch without a memset in between
+// (launches that share it must be ordered on one stream).
 struct ScanWs {
     unsigned int *ticket;
     unsigned int *flags;
@@ -86,6 +90,24 @@ __device__ __forceinline__ float pow_int(float alpha, int n)
         n >>= 1;
     }
     return (float)r;
+}
+
+// Called by every thread of the CTA at the very end of a scan kernel (after ring_finish): the last CTA of the
+// grid to get here clears the ticket, the finish counter and the ready flags for the next launch.  Everybody
+// who read a flag has finished by then, since they count themselves in only after their last read.
+__device__ __forceinline__ void scan_workspace_release(const ScanWs &ws, Ring *ring, int nflags)
+{
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned int done = atomicAdd(ws.ticket + 1, 1u);
+        ring->ticket = (done + 1u == gridDim.x) ? 1u : 0u;
+    }
+    __syncthreads();
+    if (ring->ticket) {
+        for (int i = threadIdx.x; i < nflags; i += blockDim.x) ws.flags[i] = 0u;
+        if (threadIdx.x == 0) { ws.ticket[0] = 0u; ws.ticket[1] = 0u; }
+    }
 }
 
 __device__ __forceinline__ void consumer_barrier(int nthreads)
@@ -190,8 +212,8 @@ leaky_fwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A
         float al[V], sc[V], v[V];
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-            al[j] = A.alpha.get(b, mm + j, 1.0f);
-            sc[j] = A.scale.get(b, mm + j, 1.0f);
+            al[j] = decay_of(A.alpha, b, mm + j);
+            sc[j] = scale_of(A.scale, al[j], b, mm + j);
             v[j] = 0.0f;
         }
         const int64_t M = A.M;
@@ -268,6 +290,7 @@ leaky_fwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A
         if (A.out_sum) warp_add_f64(A.out_sum, valid ? (ok ? total : (double)NAN) : 0.0, lane);
     }
     ring_finish(ring, pc.stages);
+    scan_workspace_release(ws, ring, sg.ntiles * sg.nseg);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -276,7 +299,7 @@ leaky_fwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A
 template <int NW, int V>
 __global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V>::value)
 leaky_bwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A, const int tiles_m, const int nmaps,
-                      const PipeCfg pc, const ScanGeom sg, const ScanWs ws)
+                      const PipeCfg pc, const ScanGeom sg, const ScanWs ws, const bool WA, const bool WS)
 {
     using G = TileGeom<NW, V>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -300,7 +323,6 @@ leaky_bwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A
     const int nck = (nsteps + pc.tc - 1) / pc.tc;
     const bool first_in_time = (q == 0);
     const int nA = first_in_time ? 0 : nck;   // the segment at t = 0 is last in scan order
-    const bool WA = A.grad_alpha != nullptr, WS = A.grad_scale != nullptr;
     const int i_x = WA ? 2 : 1;
 
     if (warp == NW) {
@@ -317,8 +339,8 @@ leaky_bwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A
         float al[V], sc[V], Gv[V], glast[V];
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-            al[j] = A.alpha.get(b, mm + j, 1.0f);
-            sc[j] = A.scale.get(b, mm + j, 1.0f);
+            al[j] = decay_of(A.alpha, b, mm + j);
+            sc[j] = scale_of(A.scale, al[j], b, mm + j);
             Gv[j] = 0.0f;
             glast[j] = A.g_last ? __ldg(A.g_last + n + j) : 0.0f;
         }
@@ -403,20 +425,28 @@ leaky_bwd_scan_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A
             release_chunk(ring, pos, lane);
             pos.advance(pc.stages);
         }
-        if (valid) {
+        float gdecay[V];
 #pragma unroll
-            for (int j = 0; j < V; ++j) {
+        for (int j = 0; j < V; ++j) {
+            gdecay[j] = 0.0f;
+            if (valid) {
                 if (!ok) { ag[j] = NAN; sgr[j] = NAN; Gv[j] = NAN; }      // gave up: poison what depends on this segment
                 if (first_in_time) {
                     if (A.grad_init) A.grad_init[n + j] = __fmul_rn(al[j], Gv[j]);
                     if (WA) ag[j] = __fmaf_rn(Gv[j], A.v_init ? __ldg(A.v_init + n + j) : 0.0f, ag[j]);
                 }
-                if (WA) atomicAdd(A.grad_alpha + n + j, ag[j]);
-                if (WS) atomicAdd(A.grad_scale + n + j, sgr[j]);
+                if (A.acc_decay) {      // this segment's share; the chain rule is linear in it
+                    gdecay[j] = decay_param_grad(ag[j], sgr[j], A.alpha, A.scale, al[j], b, mm + j);
+                } else {
+                    if (WA) atomicAdd(A.grad_alpha + n + j, ag[j]);
+                    if (WS) atomicAdd(A.grad_scale + n + j, sgr[j]);
+                }
             }
         }
+        if (A.acc_decay) acc_param_grad<V>(A.acc_decay, A.alpha, gdecay, valid, b, mm, lane);
     }
     ring_finish(ring, pc.stages);
+    scan_workspace_release(ws, ring, sg.ntiles * sg.nseg);
 }
 
 }  // namespace exb

@@ -343,6 +343,7 @@ cudaError_t launch_lif_backward(const LifBwdArgs &a, int layout, int reset_mode,
         cudaError_t e = launch_lif_backward_tma(a, reset_mode, surr_kind, s, &used);
         if (e != cudaSuccess || used) return e;
     }
+    if (a.acc_decay) return cudaErrorNotSupported;      // only the TMA-staged kernels reduce in the kernel
     return reset_mode == EXB_RESET_SUBTRACT ? launch_bwd_surr<EXB_RESET_SUBTRACT>(a, layout, surr_kind, s)
                                             : launch_bwd_surr<EXB_RESET_TO_VALUE>(a, layout, surr_kind, s);
 }

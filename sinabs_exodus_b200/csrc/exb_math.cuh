@@ -14,9 +14,11 @@ namespace exb {
 
 // A per-neuron parameter that is not expanded by the caller:
 // value(b, m) = p[b*sb + m*sm]; scalar (0,0), per-m (0,1), per-n (M,1).
+// `flags` are the EXB_PARAM_IS_TAU / EXB_SCALE_* bits of the mode the caller passed.
 struct Param {
     const float *p;
     int64_t sb, sm;
+    int flags;
     __device__ __forceinline__ float get(int64_t b, int64_t m, float dflt) const
     {
         return p ? __ldg(p + b * sb + m * sm) : dflt;
@@ -27,9 +29,71 @@ __host__ inline Param make_param(const float *p, int mode, int64_t M)
 {
     Param r;
     r.p = p;
+    r.flags = mode & ~EXB_PARAM_SHAPE_MASK;
+    mode &= EXB_PARAM_SHAPE_MASK;
     r.sb = (mode == EXB_PARAM_PER_N) ? M : 0;
     r.sm = (mode == EXB_PARAM_SCALAR) ? 0 : 1;
     return r;
+}
+
+// Decay per step from the value the caller passed: alpha itself, or exp(-1/tau) with EXB_PARAM_IS_TAU
+// (correctly rounded reciprocal, exact negation, expf: the roundings of `torch.exp(-1.0 / tau)`).
+__device__ __forceinline__ float decay_of(const Param &a, int64_t b, int64_t m)
+{
+    const float x = a.get(b, m, 1.0f);
+    return (a.flags & EXB_PARAM_IS_TAU) ? expf(-__frcp_rn(x)) : x;
+}
+
+// Input scale: the given value (1 when there is none), replaced by 1 - alpha with EXB_SCALE_ONE_MINUS_ALPHA and then
+// multiplied by alpha with EXB_SCALE_TIMES_ALPHA (the layers' norm_input and decay_early factors,
+// layers/lif.py:194-195,206-214 of the reference, formed with the same roundings as the PyTorch expressions there).
+__device__ __forceinline__ float scale_of(const Param &s, float alpha, int64_t b, int64_t m)
+{
+    float v = s.get(b, m, 1.0f);
+    if (s.flags & EXB_SCALE_ONE_MINUS_ALPHA) v = __fsub_rn(1.0f, alpha);
+    if (s.flags & EXB_SCALE_TIMES_ALPHA) v = __fmul_rn(v, alpha);
+    return v;
+}
+
+// Gradient w.r.t. the value the caller passed for the decay, from the gradient w.r.t. alpha (ga) and, when the scale
+// is derived from alpha, the gradient w.r.t. the scale (gs): d scale / d alpha is -1, +1 or 1 - 2*alpha; with
+// EXB_PARAM_IS_TAU the chain rule through alpha = exp(-1/tau) multiplies by alpha / tau^2.  Linear in (ga, gs), so
+// partial sums may be folded one by one.
+__device__ __forceinline__ float decay_param_grad(float ga, float gs, const Param &a, const Param &s, float alpha,
+                                                  int64_t b, int64_t m)
+{
+    float g = ga;
+    const bool om = (s.flags & EXB_SCALE_ONE_MINUS_ALPHA) != 0, ta = (s.flags & EXB_SCALE_TIMES_ALPHA) != 0;
+    if (om && ta) g = __fmaf_rn(__fmaf_rn(-2.0f, alpha, 1.0f), gs, g);
+    else if (om) g = __fsub_rn(g, gs);
+    else if (ta) g = __fmaf_rn(s.get(b, m, 1.0f), gs, g);
+    if (a.flags & EXB_PARAM_IS_TAU) {
+        const float r = __frcp_rn(a.get(b, m, 1.0f));
+        g = __fmul_rn(__fmul_rn(__fmul_rn(g, alpha), r), r);
+    }
+    return g;
+}
+
+// Adds one thread's V per-neuron gradient values to a float64 accumulator that has the shape of the parameter
+// `p` (1, M or B*M values).  Every lane of the warp must call.  One value: warp sum and one atomic per warp; M
+// values: one atomic per neuron (the batch items meet there); B*M values: nobody else writes the slot.
+template <int V>
+__device__ __forceinline__ void acc_param_grad(double *acc, const Param &p, const float (&val)[V], bool valid, int64_t b,
+                                               int64_t m, int lane)
+{
+    if (p.sb == 0 && p.sm == 0) {
+        double s = 0.0;
+        if (valid) {
+#pragma unroll
+            for (int j = 0; j < V; ++j) s += (double)val[j];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) atomicAdd(acc, s);
+    } else if (valid) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) atomicAdd(acc + b * p.sb + (m + j) * p.sm, (double)val[j]);
+    }
 }
 
 // Limit on the number of spikes per step, in the forms the step needs.
@@ -71,7 +135,7 @@ struct NeuronParams {
     __device__ __forceinline__ Neuron load(int64_t b, int64_t m, const SpikeCfg &cfg) const
     {
         Neuron q;
-        q.alpha = alpha.get(b, m, 1.0f);
+        q.alpha = decay_of(alpha, b, m);
         q.th = th.get(b, m, 1.0f);
         q.c = c.get(b, m, q.th);
         // For a positive threshold and th <= v < 2*th the correctly rounded quotient v/th lies in
@@ -79,7 +143,7 @@ struct NeuronParams {
         // never needed.  A non-positive threshold always takes the exact path.
         q.th2 = (q.th > 0.0f) ? ((cfg.maxs <= 1u) ? INFINITY : __fadd_rn(q.th, q.th)) : q.th;
         q.lo = lo.get(b, m, -INFINITY);
-        q.scale = scale.get(b, m, 1.0f);
+        q.scale = scale_of(scale, q.alpha, b, m);
         return q;
     }
 };

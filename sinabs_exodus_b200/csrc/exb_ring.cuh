@@ -276,8 +276,8 @@ __global__ void __launch_bounds__(RING_THREADS, 4) leaky_fwd_btm_ring_kernel(con
     float al[V], sc[V], v[V];
 #pragma unroll
     for (int j = 0; j < V; ++j) {
-        al[j] = A.alpha.get(b, m + j, 1.0f);
-        sc[j] = A.scale.get(b, m + j, 1.0f);
+        al[j] = decay_of(A.alpha, b, m + j);
+        sc[j] = scale_of(A.scale, al[j], b, m + j);
         v[j] = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
     }
     const int64_t base = (b * A.T) * M + m;
@@ -341,8 +341,8 @@ __global__ void __launch_bounds__(RING_THREADS, 4) leaky_bwd_btm_ring_kernel(con
     float al[V], sc[V], G[V], ag[V], sg[V], glast[V];
 #pragma unroll
     for (int j = 0; j < V; ++j) {
-        al[j] = A.alpha.get(b, m + j, 1.0f);
-        sc[j] = A.scale.get(b, m + j, 1.0f);
+        al[j] = decay_of(A.alpha, b, m + j);
+        sc[j] = scale_of(A.scale, al[j], b, m + j);
         G[j] = 0.0f; ag[j] = 0.0f; sg[j] = 0.0f;
         glast[j] = A.g_last ? __ldg(A.g_last + n + j) : 0.0f;
     }

@@ -135,8 +135,8 @@ leaky_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyFwdArgs A,
         float al[V], sc[V], v[V];
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-            al[j] = A.alpha.get(b, mm + j, 1.0f);
-            sc[j] = A.scale.get(b, mm + j, 1.0f);
+            al[j] = decay_of(A.alpha, b, mm + j);
+            sc[j] = scale_of(A.scale, al[j], b, mm + j);
             v[j] = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
         }
         const int64_t M = A.M;
@@ -210,8 +210,8 @@ leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A,
         float al[V], sc[V], G_[V], ag[V], sg[V], glast[V];
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-            al[j] = A.alpha.get(b, mm + j, 1.0f);
-            sc[j] = A.scale.get(b, mm + j, 1.0f);
+            al[j] = decay_of(A.alpha, b, mm + j);
+            sc[j] = scale_of(A.scale, al[j], b, mm + j);
             G_[j] = 0.0f; ag[j] = 0.0f; sg[j] = 0.0f;
             glast[j] = A.g_last ? __ldg(A.g_last + n + j) : 0.0f;
         }
@@ -250,15 +250,23 @@ leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A,
             release_chunk(ring, pos, lane);
             pos.advance(pc.stages);
         }
-        if (valid) {
+        float gdecay[V];
 #pragma unroll
-            for (int j = 0; j < V; ++j) {
+        for (int j = 0; j < V; ++j) {
+            gdecay[j] = 0.0f;
+            if (valid) {
                 if (!ok) { G_[j] = NAN; ag[j] = NAN; sg[j] = NAN; }      // a wait ran out: poison the results
                 if (A.grad_init) A.grad_init[n + j] = __fmul_rn(al[j], G_[j]);
-                if (WA) A.grad_alpha[n + j] = __fmaf_rn(G_[j], A.v_init ? __ldg(A.v_init + n + j) : 0.0f, ag[j]);
-                if (WS) A.grad_scale[n + j] = sg[j];
+                const float ga = WA ? __fmaf_rn(G_[j], A.v_init ? __ldg(A.v_init + n + j) : 0.0f, ag[j]) : 0.0f;
+                if (A.acc_decay) {
+                    gdecay[j] = decay_param_grad(ga, sg[j], A.alpha, A.scale, al[j], b, mm + j);
+                } else {
+                    if (WA) A.grad_alpha[n + j] = ga;
+                    if (WS) A.grad_scale[n + j] = sg[j];
+                }
             }
         }
+        if (A.acc_decay) acc_param_grad<V>(A.acc_decay, A.alpha, gdecay, valid, b, mm, lane);
     }
     ring_finish(ring, pc.stages);
 }
@@ -370,7 +378,9 @@ cudaError_t launch_leaky_backward_tma(const LeakyBwdArgs &a, cudaStream_t s, boo
 {
     *used = false;
     if (!eligible(a.B, a.T, a.M) || !aligned16(a.grad_input)) return cudaSuccess;
-    const bool wa = a.grad_alpha != nullptr, ws = a.grad_scale != nullptr;
+    const bool derived = (a.scale.flags & (EXB_SCALE_ONE_MINUS_ALPHA | EXB_SCALE_TIMES_ALPHA)) != 0;
+    const bool wa = a.grad_alpha != nullptr || a.acc_decay != nullptr;
+    const bool ws = a.grad_scale != nullptr || (a.acc_decay != nullptr && derived);
     if (wa && ws) return pick_leaky_bwd<true, true>(a, s, used);
     if (wa) return pick_leaky_bwd<true, false>(a, s, used);
     if (ws) return pick_leaky_bwd<false, true>(a, s, used);
@@ -434,8 +444,8 @@ static bool scan_workspace(void *workspace, int64_t bytes, const ScanGeom &sg, S
     return true;
 }
 
-cudaError_t launch_leaky_forward_scan(const LeakyFwdArgs &a, void *workspace, int64_t workspace_bytes, cudaStream_t s,
-                                      bool *used)
+cudaError_t launch_leaky_forward_scan(const LeakyFwdArgs &a, void *workspace, int64_t workspace_bytes, bool clean,
+                                      cudaStream_t s, bool *used)
 {
     using G = TileGeom<NWARPS, SCAN_V>;
     *used = false;
@@ -454,23 +464,26 @@ cudaError_t launch_leaky_forward_scan(const LeakyFwdArgs &a, void *workspace, in
     auto kern = leaky_fwd_scan_kernel<NWARPS, SCAN_V>;
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
-    e = cudaMemsetAsync(workspace, 0, zero_bytes, s);
+    if (!clean) e = cudaMemsetAsync(workspace, 0, zero_bytes, s);
     if (e != cudaSuccess) return e;
     kern<<<(unsigned)((int64_t)sg.ntiles * sg.nseg), (NWARPS + 1) * 32, smem, s>>>(maps, a, tiles_m, pc, sg, ws);
     *used = true;
     return cudaPeekAtLastError();
 }
 
-cudaError_t launch_leaky_backward_scan(const LeakyBwdArgs &a, void *workspace, int64_t workspace_bytes, cudaStream_t s,
-                                       bool *used)
+cudaError_t launch_leaky_backward_scan(const LeakyBwdArgs &a, void *workspace, int64_t workspace_bytes, bool clean,
+                                       cudaStream_t s, bool *used)
 {
     using G = TileGeom<NWARPS, SCAN_V>;
     *used = false;
     if (!aligned16(a.grad_input)) return cudaSuccess;
+    const bool derived = (a.scale.flags & (EXB_SCALE_ONE_MINUS_ALPHA | EXB_SCALE_TIMES_ALPHA)) != 0;
+    const bool wa = a.grad_alpha != nullptr || a.acc_decay != nullptr;
+    const bool ws_ = a.grad_scale != nullptr || (a.acc_decay != nullptr && derived);
     const float *ptrs[5] = {a.go, nullptr, nullptr, nullptr, nullptr};
     int nmaps = 1;
-    if (a.grad_alpha) ptrs[nmaps++] = a.out;
-    if (a.grad_scale) ptrs[nmaps++] = a.input;
+    if (wa) ptrs[nmaps++] = a.out;
+    if (ws_) ptrs[nmaps++] = a.input;
     PipeCfg pc;
     ScanGeom sg;
     int tiles_m;
@@ -486,12 +499,12 @@ cudaError_t launch_leaky_backward_scan(const LeakyBwdArgs &a, void *workspace, i
     auto kern = leaky_bwd_scan_kernel<NWARPS, SCAN_V>;
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
-    e = cudaMemsetAsync(workspace, 0, zero_bytes, s);
+    if (!clean) e = cudaMemsetAsync(workspace, 0, zero_bytes, s);
     const size_t nbytes = (size_t)(a.B * a.M) * sizeof(float);
     if (e == cudaSuccess && a.grad_alpha) e = cudaMemsetAsync(a.grad_alpha, 0, nbytes, s);
     if (e == cudaSuccess && a.grad_scale) e = cudaMemsetAsync(a.grad_scale, 0, nbytes, s);
     if (e != cudaSuccess) return e;
-    kern<<<(unsigned)((int64_t)sg.ntiles * sg.nseg), (NWARPS + 1) * 32, smem, s>>>(maps, a, tiles_m, nmaps, pc, sg, ws);
+    kern<<<(unsigned)((int64_t)sg.ntiles * sg.nseg), (NWARPS + 1) * 32, smem, s>>>(maps, a, tiles_m, nmaps, pc, sg, ws, wa, ws_);
     *used = true;
     return cudaPeekAtLastError();
 }
@@ -540,7 +553,24 @@ cudaError_t launch_leaky_forward_scan_static(const LeakyFwdArgs &a, int device, 
     void *scratch = nullptr;
     cudaError_t e = static_scratch_address(device, &scratch);
     if (e != cudaSuccess) return e;
-    return launch_leaky_forward_scan(a, scratch, (int64_t)sizeof(g_static_scratch), s, used);
+    return launch_leaky_forward_scan(a, scratch, (int64_t)sizeof(g_static_scratch), false, s, used);
+}
+
+// out[i] = (float) acc[i]; acc[i] = 0
+__global__ void acc_finish_kernel(float *out, double *acc, int64_t n)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        out[i] = (float)acc[i];
+        acc[i] = 0.0;
+    }
+}
+
+cudaError_t launch_acc_finish(float *out, double *acc, int64_t n, cudaStream_t s)
+{
+    if (n <= 0) return cudaSuccess;
+    acc_finish_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(out, acc, n);
+    return cudaPeekAtLastError();
 }
 
 bool tma_enabled()

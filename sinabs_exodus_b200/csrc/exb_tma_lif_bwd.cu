@@ -100,17 +100,26 @@ lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, con
             release_chunk(ring, pos, lane);
             pos.advance(pc.stages);
         }
-        if (valid) {
+        float gdecay[V];
 #pragma unroll
-            for (int j = 0; j < V; ++j) {
-                const Neuron &qj = q[NQ == 1 ? 0 : j];
+        for (int j = 0; j < V; ++j) {
+            const Neuron &qj = q[NQ == 1 ? 0 : j];
+            gdecay[j] = 0.0f;
+            if (valid) {
                 if (!ok) { st[j].R = NAN; st[j].ag = NAN; st[j].sg = NAN; }      // a wait ran out: poison the results
                 if (A.grad_init) A.grad_init[n + j] = __fmul_rn(qj.alpha, st[j].R);
                 const float vi = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
-                if (WA) A.grad_alpha[n + j] = alpha_grad_finish<RESET>(st[j], vi, Rprev[j], f0[j], n0[j]);
-                if (WS) A.grad_scale[n + j] = scale_grad_finish<WS>(st[j], vi, qj);
+                const float ga = WA ? alpha_grad_finish<RESET>(st[j], vi, Rprev[j], f0[j], n0[j]) : 0.0f;
+                const float gs = WS ? scale_grad_finish<WS>(st[j], vi, qj) : 0.0f;
+                if (A.acc_decay) {
+                    gdecay[j] = decay_param_grad(ga, gs, A.np.alpha, A.np.scale, qj.alpha, b, mm + j);
+                } else {
+                    if (WA) A.grad_alpha[n + j] = ga;
+                    if (WS) A.grad_scale[n + j] = gs;
+                }
             }
         }
+        if (A.acc_decay) acc_param_grad<V>(A.acc_decay, A.np.alpha, gdecay, valid, b, mm, lane);
     }
     ring_finish(ring, pc.stages);
 }
@@ -151,8 +160,11 @@ static cudaError_t pick_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
 template <int SURR, int RESET>
 static cudaError_t flags_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
 {
-    const bool wa = a.grad_alpha != nullptr;
-    const int ws = a.grad_scale ? (a.input ? SCALE_GRAD_FROM_INPUT : SCALE_GRAD_FROM_STATE) : SCALE_GRAD_NONE;
+    // With an accumulator the alpha gradient is always wanted, and the scale gradient when the scale derives from alpha.
+    const bool derived = (a.np.scale.flags & (EXB_SCALE_ONE_MINUS_ALPHA | EXB_SCALE_TIMES_ALPHA)) != 0;
+    const bool wa = a.grad_alpha != nullptr || a.acc_decay != nullptr;
+    const bool want_scale = a.grad_scale != nullptr || (a.acc_decay != nullptr && derived);
+    const int ws = want_scale ? (a.input ? SCALE_GRAD_FROM_INPUT : SCALE_GRAD_FROM_STATE) : SCALE_GRAD_NONE;
     if (wa) {
         if (ws == SCALE_GRAD_FROM_INPUT) return pick_lif_bwd<SURR, RESET, true, SCALE_GRAD_FROM_INPUT>(a, s, used);
         if (ws == SCALE_GRAD_FROM_STATE) return pick_lif_bwd<SURR, RESET, true, SCALE_GRAD_FROM_STATE>(a, s, used);

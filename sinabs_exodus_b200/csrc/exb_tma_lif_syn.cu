@@ -77,8 +77,8 @@ lif_syn_fwd_tma_kernel(const __grid_constant__ TmaMaps6 maps, const LifSynFwdArg
 #pragma unroll
         for (int j = 0; j < NQ; ++j) {
             q[j] = A.np.load(b, mm + j, cfg);
-            as[j] = A.alpha_syn.get(b, mm + j, 1.0f);
-            ss[j] = A.scale_syn.get(b, mm + j, 1.0f);
+            as[j] = decay_of(A.alpha_syn, b, mm + j);
+            ss[j] = scale_of(A.scale_syn, as[j], b, mm + j);
         }
 #pragma unroll
         for (int j = 0; j < V; ++j) {
@@ -224,8 +224,8 @@ lif_syn_bwd_tma_kernel(const __grid_constant__ TmaMaps6 maps, const LifSynBwdArg
             q[j] = A.np.load(b, mm + j, cfg);
             sc[j] = surr_prepare<SURR>(q[j], A.p0, A.p1);
             cp[j] = __fmul_rn(q[j].alpha, q[j].c);
-            as[j] = A.alpha_syn.get(b, mm + j, 1.0f);
-            ss[j] = A.scale_syn.get(b, mm + j, 1.0f);
+            as[j] = decay_of(A.alpha_syn, b, mm + j);
+            ss[j] = scale_of(A.scale_syn, as[j], b, mm + j);
         }
 #pragma unroll
         for (int j = 0; j < V; ++j) {
@@ -304,10 +304,12 @@ lif_syn_bwd_tma_kernel(const __grid_constant__ TmaMaps6 maps, const LifSynBwdArg
             release_chunk(ring, pos, lane);
             pos.advance(nstages);
         }
-        if (valid) {
+        float gd_mem[V], gd_syn[V];
 #pragma unroll
-            for (int j = 0; j < V; ++j) {
-                const int jq = (NQ == 1) ? 0 : j;
+        for (int j = 0; j < V; ++j) {
+            const int jq = (NQ == 1) ? 0 : j;
+            gd_mem[j] = 0.0f; gd_syn[j] = 0.0f;
+            if (valid) {
                 const float vi = A.v_init ? __ldg(A.v_init + n + j) : 0.0f;
                 const float ii = A.i_init ? __ldg(A.i_init + n + j) : 0.0f;
                 if (!ok) {      // a wait ran out: poison the per-neuron results
@@ -316,13 +318,25 @@ lif_syn_bwd_tma_kernel(const __grid_constant__ TmaMaps6 maps, const LifSynBwdArg
                 if (A.grad_v_init) A.grad_v_init[n + j] = __fmul_rn(q[jq].alpha, S.st[j].R);
                 if (A.grad_i_init) A.grad_i_init[n + j] = __fmul_rn(as[jq], S.Gs[j]);
                 if (WG) {
-                    A.grad_alpha_mem[n + j] = alpha_grad_finish<RESET>(S.st[j], vi, R1[j], f0[j], n0[j]);
-                    A.grad_scale_mem[n + j] = S.st[j].sg;
-                    A.grad_alpha_syn[n + j] = __fmaf_rn(S.Gs[j], ii, S.ag_syn[j]);
-                    A.grad_scale_syn[n + j] =
-                        __fdiv_rn(__fmaf_rn(S.Gs[j], __fmaf_rn(-as[jq], ii, S.inext[j]), S.sg_syn[j]), ss[jq]);
+                    const float ga_mem = alpha_grad_finish<RESET>(S.st[j], vi, R1[j], f0[j], n0[j]);
+                    const float gs_mem = S.st[j].sg;
+                    const float ga_syn = __fmaf_rn(S.Gs[j], ii, S.ag_syn[j]);
+                    const float gs_syn = __fdiv_rn(__fmaf_rn(S.Gs[j], __fmaf_rn(-as[jq], ii, S.inext[j]), S.sg_syn[j]), ss[jq]);
+                    if (A.acc_decay_mem) {
+                        gd_mem[j] = decay_param_grad(ga_mem, gs_mem, A.np.alpha, A.np.scale, q[jq].alpha, b, mm + j);
+                        gd_syn[j] = decay_param_grad(ga_syn, gs_syn, A.alpha_syn, A.scale_syn, as[jq], b, mm + j);
+                    } else {
+                        A.grad_alpha_mem[n + j] = ga_mem;
+                        A.grad_scale_mem[n + j] = gs_mem;
+                        A.grad_alpha_syn[n + j] = ga_syn;
+                        A.grad_scale_syn[n + j] = gs_syn;
+                    }
                 }
             }
+        }
+        if (WG && A.acc_decay_mem) {
+            acc_param_grad<V>(A.acc_decay_mem, A.np.alpha, gd_mem, valid, b, mm, lane);
+            acc_param_grad<V>(A.acc_decay_syn, A.alpha_syn, gd_syn, valid, b, mm, lane);
         }
     }
     ring_finish(ring, nstages);
@@ -352,11 +366,15 @@ static int syn_stages(size_t stage_bytes, int64_t ctas)
     return s;
 }
 
-// Time steps per stage: the larger of the two compiled values whose ring still has 4 stages (3 at least).
+// Time steps per stage: the larger of the two compiled values whose ring still has `min_stages` stages.  The forward
+// streams one tensor and likes a deep ring; the backward streams two to five and does more per chunk, and measured
+// faster with twice the steps per stage on two stages than with half of them on five (synaptic layer, 128 x 500 x
+// 1024: 200 us against 235 us), because the work per chunk (barrier wait, release, pointer set-up) halves.
 // EXB_SYN_FWD_TC / EXB_SYN_BWD_TC (else EXB_TMA_TC) in the environment force one of them (tuning aid).
 template <int TC_BIG, int TC_SMALL>
 static int syn_pick_tc(int w, int nmaps, int64_t ctas, bool backward)
 {
+    const int min_stages = backward ? 2 : 4;
     static const int env_any = env_int("EXB_TMA_TC", 0);
     static const int env_fwd = env_int("EXB_SYN_FWD_TC", 0);
     static const int env_bwd = env_int("EXB_SYN_BWD_TC", 0);
@@ -364,7 +382,7 @@ static int syn_pick_tc(int w, int nmaps, int64_t ctas, bool backward)
     const int env_tc = env_dir ? env_dir : env_any;
     if (env_tc == TC_BIG || env_tc == TC_SMALL) return env_tc;
     const size_t big = (size_t)TC_BIG * w * 4 * nmaps;
-    if (big <= 16 * 1024 && syn_stages(big, ctas) >= 4) return TC_BIG;
+    if (big <= 16 * 1024 && syn_stages(big, ctas) >= min_stages) return TC_BIG;
     return TC_SMALL;
 }
 
@@ -467,7 +485,7 @@ template <int SURR, int RESET>
 static cudaError_t flags_syn_bwd(const LifSynBwdArgs &a, cudaStream_t s, bool *used)
 {
     const bool extra = a.gv != nullptr || a.g_isyn != nullptr;
-    if (a.grad_alpha_mem)
+    if (a.grad_alpha_mem || a.acc_decay_mem)
         return extra ? pick_syn_bwd<SURR, RESET, true, true>(a, s, used) : pick_syn_bwd<SURR, RESET, true, false>(a, s, used);
     return extra ? pick_syn_bwd<SURR, RESET, false, true>(a, s, used) : pick_syn_bwd<SURR, RESET, false, false>(a, s, used);
 }

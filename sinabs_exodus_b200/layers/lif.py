@@ -27,7 +27,7 @@ from ..compat.activation import (
 )
 from ..compat.layers import LIF as LIFBase
 from ..leaky import LeakyIntegratorTM
-from ..spike import IntegrateAndFireTM, LIFSynapticTM, _flat32, _mode_of, fused_synaptic_eligible
+from ..spike import IntegrateAndFireTM, LIFSynapticTM, _flat32, _mode_of, acc_eligible, fused_synaptic_eligible
 
 __all__ = ["LIF"]
 
@@ -156,6 +156,28 @@ class LIF(LIFBase):
         )
         self.decay_early = decay_early
 
+    def reset_states(self, randomize: bool = False, value_ranges=None) -> None:
+        """Reset the states to zero (or, with ``randomize``, as the base class does).
+
+        A plain reset installs a zero tensor that the layer keeps for this purpose instead of filling a new one on
+        every call (one launch less per step for loops that reset between samples).  The forward pass never writes
+        into its initial state, so the tensor stays zero; should anybody have modified it in place since it was
+        installed (its version counter tells), a fresh one is made.
+        """
+        if randomize or not self.is_state_initialised():
+            return super().reset_states(randomize=randomize, value_ranges=value_ranges)
+        cache = self.__dict__.setdefault("_zero_states", {})
+        for name, buf in list(self.named_buffers(recurse=False)):
+            hit = cache.get(name)
+            if hit is None or hit[0].shape != buf.shape or hit[0].device != buf.device or hit[0]._version != hit[1] \
+                    or (hit[0].is_cuda and torch.cuda.is_current_stream_capturing()):
+                z = torch.zeros_like(buf.detach())
+                if not (z.is_cuda and torch.cuda.is_current_stream_capturing()):
+                    cache[name] = (z, z._version)
+            else:
+                z = hit[0]
+            self.register_buffer(name, z)
+
     def _parse_activation_fn(self, spike_fn, reset_fn):
         if spike_fn is None:
             return
@@ -203,22 +225,45 @@ class LIF(LIFBase):
             return _DecayFromTau.apply(tau, False)[0]
         return self.alpha_syn_calculated
 
+    def _decay_source(self, which: str):
+        """``(tensor, flags)`` for the decay of the membrane (``"mem"``) or synapse (``"syn"``) stage: what the layer
+        owns -- the time constant (``PARAM_IS_TAU``: the kernels form ``exp(-1/tau)`` themselves, and their backward
+        returns the gradient w.r.t. tau) or, with ``train_alphas`` or a layer without leak, alpha itself."""
+        if not self.train_alphas:
+            tau = getattr(self, "tau_" + which, None)
+            if isinstance(tau, torch.Tensor):
+                return tau, _lib.PARAM_IS_TAU
+        return getattr(self, f"alpha_{which}_calculated"), 0
+
+    @staticmethod
+    def _aux(n_acc: int, dev) -> torch.Tensor:
+        """One zeroed float64 buffer per call: element 0 is the forward kernel's total (spike count, read as int64,
+        or the output sum), the rest are the accumulators the backward kernel reduces parameter gradients into."""
+        return torch.zeros(1 + n_acc, dtype=torch.float64, device=dev)
+
     def _forward_synaptic(self, x: torch.Tensor, batch: int, trailing):
-        alpha_syn = _flat_param(self._synaptic_decay(), trailing, batch, x.device)
-        return LeakyIntegratorTM.apply(
-            x, alpha_syn, self.i_syn.reshape(-1), alpha_syn if self.decay_early else None)
+        raw, dflags = self._decay_source("syn")
+        raw = _flat_param(raw, trailing, batch, x.device)
+        acc = None
+        if raw.requires_grad and torch.is_grad_enabled() and acc_eligible(x):
+            acc = torch.zeros(raw.numel(), dtype=torch.float64, device=x.device)
+        return LeakyIntegratorTM.apply(x, raw, self.i_syn.reshape(-1), None, None, dflags,
+                                       _lib.SCALE_TIMES_ALPHA if self.decay_early else 0, acc)
 
     def _forward_membrane(self, i_syn: torch.Tensor, batch: int, trailing):
         dev = i_syn.device
-        alpha_mem, scale = self._membrane_decay()
-        alpha_mem = _flat_param(alpha_mem, trailing, batch, dev)
-        scale = _flat_param(scale, trailing, batch, dev)
+        raw, dflags = self._decay_source("mem")
+        raw = _flat_param(raw, trailing, batch, dev)
+        sflags = _lib.SCALE_ONE_MINUS_ALPHA if self.norm_input else 0
+        use_acc = raw.requires_grad and torch.is_grad_enabled() and acc_eligible(i_syn)
+        aux = self._aux(raw.numel() if use_acc else 0, dev)
+        acc = aux[1:] if use_acc else None
 
         if self.spike_fn is None:
             if self.decay_early:
-                scale = alpha_mem if scale is None else scale * alpha_mem
-            total = torch.zeros(1, dtype=torch.float64, device=dev)
-            v_mem, v_last = LeakyIntegratorTM.apply(i_syn, alpha_mem, self.v_mem.reshape(-1), scale, total)
+                sflags |= _lib.SCALE_TIMES_ALPHA
+            total = aux[:1]
+            v_mem, v_last = LeakyIntegratorTM.apply(i_syn, raw, self.v_mem.reshape(-1), None, total, dflags, sflags, acc)
             return v_mem, v_mem, v_last, total
 
         threshold = _flat_param(self.spike_threshold, trailing, batch, dev)
@@ -229,16 +274,16 @@ class LIF(LIFBase):
         else:
             reset_mode = _lib.RESET_SUBTRACT
             subtract = _flat_param(self.reset_fn.subtract_value, trailing, batch, dev)
-        self._validate_once(alpha_mem, dev)
-        count = torch.zeros(1, dtype=torch.int64, device=dev)
+        self._validate_once(dev)
+        count = aux[:1].view(torch.int64)
         # With autograd off the recorded potential is a plain side output of the forward launch; with autograd on
         # it stays the reference's differentiable expression (layers/lif.py:256), so that a loss on a recording works.
         fused_record = self.record_states and not torch.is_grad_enabled()
         v_rec = torch.empty_like(i_syn) if fused_record else None
         spikes, v_pre, v_post_last = IntegrateAndFireTM.apply(
-            i_syn, alpha_mem, self.v_mem.reshape(-1), threshold, subtract, min_v_mem, scale,
+            i_syn, raw, self.v_mem.reshape(-1), threshold, subtract, min_v_mem, None,
             self.surrogate_grad_fn, self.max_num_spikes_per_bin, reset_mode, count,
-            scale is not None and getattr(self, "_scale_nonzero", False), v_rec)
+            bool(sflags) and getattr(self, "_scale_nonzero", False), v_rec, dflags, sflags, acc)
         if self.record_states and not fused_record:
             c = threshold if subtract is None else subtract
             c = c if c.numel() == 1 else (c.view(1, 1, -1) if c.numel() == v_pre.shape[2] else c.view(batch, 1, -1))
@@ -287,16 +332,17 @@ class LIF(LIFBase):
         dev = x.device
         B, T, M = x.shape
         N = B * M
-        alpha_mem, scale_mem = self._membrane_decay()
         flat = lambda v: _flat32(_flat_param(v, trailing, batch, dev))
-        a_mem, s_mem = flat(alpha_mem), flat(scale_mem)
+        raw_mem, dmem = self._decay_source("mem")
+        a_mem = flat(raw_mem)
+        smem_flags = _lib.SCALE_ONE_MINUS_ALPHA if self.norm_input else 0
         th, lo = flat(self.spike_threshold), flat(self.min_v_mem)
         if isinstance(self.reset_fn, MembraneReset):
             reset_mode, c = _lib.RESET_TO_VALUE, flat(self.reset_fn.reset_value)
         else:
             reset_mode, c = _lib.RESET_SUBTRACT, flat(self.reset_fn.subtract_value)
-        self._validate_once(a_mem, dev)
-        spec = lambda t, name: (t, _mode_of(t, M, N, name))
+        self._validate_once(dev)
+        spec = lambda t, name, flags=0: (t, _mode_of(t, M, N, name) | flags)
         spikes = torch.empty((B, T, M), dtype=torch.uint8, device=dev)
         keep = bool(self.record_states)
         v_mem = torch.empty_like(x) if keep else None
@@ -305,18 +351,20 @@ class LIF(LIFBase):
         v0 = self.v_mem.reshape(-1).to(torch.float32).contiguous()
         i_syn = None
         if has_synapse:
-            a_syn = flat(self._synaptic_decay())
+            raw_syn, dsyn = self._decay_source("syn")
+            a_syn = flat(raw_syn)
             i_syn = torch.empty_like(x) if keep else None
             i_last = torch.empty(N, dtype=torch.float32, device=dev)
             i0 = self.i_syn.reshape(-1).to(torch.float32).contiguous()
             done = _lib.lif_syn_forward_u8(
-                spikes, v_mem, i_syn, x, v0, i0, spec(a_syn, "alpha_syn"),
-                spec(a_syn if self.decay_early else None, "scale_syn"), spec(s_mem, "scale_mem"), spec(a_mem, "alpha_mem"),
+                spikes, v_mem, i_syn, x, v0, i0, spec(a_syn, "alpha_syn", dsyn),
+                spec(None, "scale_syn", _lib.SCALE_TIMES_ALPHA if self.decay_early else 0),
+                spec(None, "scale_mem", smem_flags), spec(a_mem, "alpha_mem", dmem),
                 spec(c, "subtract"), spec(th, "threshold"), spec(lo, "min_v_mem"), self.max_num_spikes_per_bin,
                 reset_mode, self._spike_saturate, v_post_last, i_last, count, B, T, M)
         else:
             done = _lib.lif_forward_u8(
-                spikes, v_mem, x, v0, spec(s_mem, "in_scale"), spec(a_mem, "alpha"), spec(c, "subtract"),
+                spikes, v_mem, x, v0, spec(None, "in_scale", smem_flags), spec(a_mem, "alpha", dmem), spec(c, "subtract"),
                 spec(th, "threshold"), spec(lo, "min_v_mem"), self.max_num_spikes_per_bin, reset_mode,
                 self._spike_saturate, v_post_last, count, B, T, M)
         if not done:
@@ -341,7 +389,7 @@ class LIF(LIFBase):
         self._set_rate_source(count, out.numel())
         return out
 
-    def _validate_once(self, alpha_mem: torch.Tensor, dev) -> None:
+    def _validate_once(self, dev) -> None:
         """Value checks of the reference Function (``spike.py:183,190``): 0 <= alpha <= 1 and
         threshold > min_v_mem.  Each check reads a result back from the GPU, which stalls the
         launch queue, so the outcome is remembered until one of the inputs changes."""
@@ -352,7 +400,7 @@ class LIF(LIFBase):
         if getattr(self, "_validated_key", None) == key:
             return
         with torch.no_grad():
-            a = alpha_mem.detach()
+            a = torch.as_tensor(self._membrane_decay()[0]).detach().to(dev)
             bad, near_one = (((a < 0) | (a > 1)).any(), (a > 0.99).any())
             bad, near_one = torch.stack((bad, near_one)).tolist()      # one read-back for both
             if bad:
@@ -418,10 +466,15 @@ class LIF(LIFBase):
         batch_size, time_steps, *trailing_dim = original_shape
         trailing = tuple(trailing_dim)
         dev = x.device
-        alpha_syn = _flat_param(self._synaptic_decay(), trailing, batch_size, dev)
-        alpha_mem, scale_mem = self._membrane_decay()
-        alpha_mem = _flat_param(alpha_mem, trailing, batch_size, dev)
-        scale_mem = _flat_param(scale_mem, trailing, batch_size, dev)
+        raw_syn, dsyn = self._decay_source("syn")
+        raw_mem, dmem = self._decay_source("mem")
+        raw_syn = _flat_param(raw_syn, trailing, batch_size, dev)
+        raw_mem = _flat_param(raw_mem, trailing, batch_size, dev)
+        flags = (dsyn, _lib.SCALE_TIMES_ALPHA if self.decay_early else 0,
+                 dmem, _lib.SCALE_ONE_MINUS_ALPHA if self.norm_input else 0)
+        use_acc = (raw_syn.requires_grad or raw_mem.requires_grad) and torch.is_grad_enabled()
+        aux = self._aux(raw_mem.numel() + raw_syn.numel() if use_acc else 0, dev)
+        acc = (aux[1:1 + raw_mem.numel()], aux[1 + raw_mem.numel():]) if use_acc else None
         threshold = _flat_param(self.spike_threshold, trailing, batch_size, dev)
         min_v_mem = _flat_param(self.min_v_mem, trailing, batch_size, dev)
         if isinstance(self.reset_fn, MembraneReset):
@@ -430,12 +483,12 @@ class LIF(LIFBase):
         else:
             reset_mode = _lib.RESET_SUBTRACT
             subtract = _flat_param(self.reset_fn.subtract_value, trailing, batch_size, dev)
-        self._validate_once(alpha_mem, dev)
-        count = torch.zeros(1, dtype=torch.int64, device=dev)
+        self._validate_once(dev)
+        count = aux[:1].view(torch.int64)
         spikes, v_pre, v_post_last, i_syn, i_last = LIFSynapticTM.apply(
-            x, alpha_syn, alpha_syn if self.decay_early else None, self.i_syn.reshape(-1), alpha_mem, scale_mem,
+            x, raw_syn, None, self.i_syn.reshape(-1), raw_mem, None,
             self.v_mem.reshape(-1), threshold, subtract, min_v_mem, self.surrogate_grad_fn,
-            self.max_num_spikes_per_bin, reset_mode, count)
+            self.max_num_spikes_per_bin, reset_mode, count, flags, acc)
         self.i_syn = i_last.reshape(batch_size, *trailing)
         self.v_mem = v_post_last.reshape(batch_size, *trailing)
         if self.record_states:

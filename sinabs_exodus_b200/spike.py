@@ -13,6 +13,7 @@ mask, gradient combination, ``lifBackward``, ``lifBackwardAlpha`` and
 """
 from __future__ import annotations
 
+import os
 import weakref
 from typing import Callable, Optional, Tuple
 
@@ -46,6 +47,36 @@ def _reduce_to_param(per_instance: torch.Tensor, shape, mode: int, B: int, M: in
     return g.reshape(shape)
 
 
+def _fold_decay_grad(ga: torch.Tensor, gs: Optional[torch.Tensor], raw: torch.Tensor, decay_flags: int,
+                     scale_flags: int, given_scale: Optional[torch.Tensor]) -> torch.Tensor:
+    """PyTorch form of what the kernels' float64 accumulator holds, for shapes the reducing kernels do not take:
+    the gradient w.r.t. the decay values as passed (alpha, or tau with ``PARAM_IS_TAU``) from the per-instance
+    gradients w.r.t. alpha (``ga``) and w.r.t. a scale derived from alpha (``gs``), already reduced to the
+    parameter's shape."""
+    alpha = torch.exp(-torch.reciprocal(raw)) if decay_flags & _lib.PARAM_IS_TAU else raw
+    g = ga
+    if gs is not None:
+        om, ta = scale_flags & _lib.SCALE_ONE_MINUS_ALPHA, scale_flags & _lib.SCALE_TIMES_ALPHA
+        if om and ta:
+            g = g + (1.0 - 2.0 * alpha) * gs
+        elif om:
+            g = g - gs
+        elif ta:
+            g = g + (gs if given_scale is None else given_scale * gs)
+    if decay_flags & _lib.PARAM_IS_TAU:
+        r = torch.reciprocal(raw)
+        g = g * alpha * r * r
+    return g
+
+
+def acc_eligible(inp: torch.Tensor) -> bool:
+    """Whether the backward kernels that reduce parameter gradients in the kernel take this (B, T, M) tensor (the
+    TMA-staged family: neurons % 4 == 0, 16-byte aligned contiguous float32 storage)."""
+    return (inp.ndim == 3 and inp.is_cuda and inp.dtype == torch.float32 and inp.is_contiguous()
+            and inp.shape[2] % 4 == 0 and inp.data_ptr() % 16 == 0 and inp.numel() > 0
+            and inp.shape[1] * inp.shape[2] < 2 ** 31 and os.environ.get("EXB_DISABLE_TMA", "0") != "1")
+
+
 def _flat32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     if t is None:
         return None
@@ -57,13 +88,19 @@ class _LifCore:
 
     @staticmethod
     def forward(ctx, inp, alpha, v_init, theta, subtract, min_v_mem, in_scale, surrogate_fn, max_spikes,
-                reset_mode, spike_count, B, T, M, layout, scale_grad_from_state=False, record=None):
+                reset_mode, spike_count, B, T, M, layout, scale_grad_from_state=False, record=None,
+                decay_flags=0, scale_flags=0, acc=None):
+        """``decay_flags`` / ``scale_flags``: ``PARAM_IS_TAU`` and ``SCALE_*`` bits for the alpha and scale arguments
+        (the kernels then derive alpha = exp(-1/tau) and the scale from alpha; the gradient returned for ``alpha`` is
+        the one w.r.t. the values passed, scale part included).  ``acc``: zeroed float64 tensor shaped like the
+        flattened ``alpha`` that the backward kernel reduces that gradient into (no per-instance vector, no
+        reduction or chain-rule launches)."""
         N = B * M
         a_f, th_f, c_f, lo_f, sc_f = map(_flat32, (alpha, theta, subtract, min_v_mem, in_scale))
         modes = dict(
-            alpha=_mode_of(a_f, M, N, "alpha"), theta=_mode_of(th_f, M, N, "threshold"),
+            alpha=_mode_of(a_f, M, N, "alpha") | decay_flags, theta=_mode_of(th_f, M, N, "threshold"),
             subtract=_mode_of(c_f, M, N, "membrane_subtract"), lo=_mode_of(lo_f, M, N, "min_v_mem"),
-            scale=_mode_of(sc_f, M, N, "in_scale"))
+            scale=_mode_of(sc_f, M, N, "in_scale") | scale_flags)
         vi_f = _flat32(v_init)
         spikes = torch.empty_like(inp)
         v_mem = torch.empty_like(inp)
@@ -81,7 +118,11 @@ class _LifCore:
         ctx.max_spikes = max_spikes
         ctx.reset_mode = reset_mode
         ctx.want_alpha = alpha is not None and alpha.requires_grad
-        ctx.want_scale = in_scale is not None and in_scale.requires_grad
+        ctx.scale_derived = bool(scale_flags)
+        # a scale derived from alpha sends its gradient to alpha; a separate scale tensor gets its own
+        ctx.want_scale = (in_scale is not None and in_scale.requires_grad) or (ctx.scale_derived and ctx.want_alpha)
+        ctx.flags = (decay_flags, scale_flags)
+        ctx.acc = acc if (ctx.want_alpha and acc is not None and not (in_scale is not None and in_scale.requires_grad)) else None
         # The scale gradient either reads the forward input again or is rebuilt from v_mem alone
         # (no extra tensor kept alive or streamed); the latter needs every scale to be non-zero.
         ctx.save_input = ctx.want_scale and not scale_grad_from_state
@@ -133,18 +174,30 @@ class _LifCore:
         new = torch.zeros if T == 0 else torch.empty      # an empty sweep launches nothing
         grad_input = torch.empty_like(v_mem)
         grad_init = new(N, dtype=torch.float32, device=dev) if ctx.v_init_shape is not None else None
-        ga = new(N, dtype=torch.float32, device=dev) if ctx.want_alpha else None
-        gs = new(N, dtype=torch.float32, device=dev) if ctx.want_scale else None
-        _lib.lif_backward(grad_input, ga, grad_init, gs, grad_spikes, grad_v_mem, grad_v_last, v_mem, surr, vi_f,
-                          inp, (sc_f, modes["scale"]), (a_f, modes["alpha"]), (c_f, modes["subtract"]),
-                          (th_f, modes["theta"]), (lo_f, modes["lo"]), ctx.max_spikes, ctx.reset_mode,
-                          kind, p0, p1, B, T, M, layout)
-        grad_alpha = None
-        if ctx.want_alpha:
-            grad_alpha = _reduce_to_param(ga, ctx.alpha_shape, modes["alpha"], B, M)
-        grad_scale = None
-        if ctx.want_scale:
-            grad_scale = _reduce_to_param(gs, ctx.scale_shape, modes["scale"], B, M)
+        args = (grad_spikes, grad_v_mem, grad_v_last, v_mem, surr, vi_f, inp, (sc_f, modes["scale"]),
+                (a_f, modes["alpha"]), (c_f, modes["subtract"]), (th_f, modes["theta"]), (lo_f, modes["lo"]),
+                ctx.max_spikes, ctx.reset_mode, kind, p0, p1, B, T, M, layout)
+        decay_flags, scale_flags = ctx.flags
+        shape_mode = modes["alpha"] & _lib.PARAM_SHAPE_MASK
+        if ctx.acc is not None and T > 0 and _lib.lif_backward(grad_input, None, grad_init, None, *args, acc_decay=ctx.acc):
+            # reduced over the batch, chain rule applied, in the kernel; one small launch converts and clears
+            grad_alpha = torch.empty(a_f.numel(), dtype=torch.float32, device=dev)
+            _lib.acc_finish(grad_alpha, ctx.acc)
+            grad_alpha = grad_alpha.reshape(ctx.alpha_shape)
+            grad_scale = None
+        else:
+            ga = new(N, dtype=torch.float32, device=dev) if ctx.want_alpha else None
+            gs = new(N, dtype=torch.float32, device=dev) if ctx.want_scale else None
+            _lib.lif_backward(grad_input, ga, grad_init, gs, *args)
+            grad_alpha = grad_scale = None
+            if ctx.want_alpha:
+                grad_alpha = _reduce_to_param(ga, ctx.alpha_shape, shape_mode, B, M)
+            if ctx.want_scale and not ctx.scale_derived:
+                grad_scale = _reduce_to_param(gs, ctx.scale_shape, modes["scale"] & _lib.PARAM_SHAPE_MASK, B, M)
+            if ctx.want_alpha and (decay_flags or ctx.scale_derived):
+                gs_p = _reduce_to_param(gs, ctx.alpha_shape, shape_mode, B, M) if ctx.scale_derived else None
+                grad_alpha = _fold_decay_grad(grad_alpha, gs_p, a_f.reshape(ctx.alpha_shape), decay_flags, scale_flags,
+                                              None if sc_f is None else sc_f.reshape(-1))
         if grad_init is not None:
             grad_init = grad_init.reshape(ctx.v_init_shape)
         return grad_input, grad_alpha, grad_init, grad_scale
@@ -244,7 +297,7 @@ class IntegrateAndFireTM(torch.autograd.Function):
     @staticmethod
     def forward(ctx, inp, alpha, v_init, threshold, membrane_subtract, min_v_mem, in_scale,
                 surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count, scale_grad_from_state=False,
-                record=None):
+                record=None, decay_flags=0, scale_flags=0, acc=None):
         if inp.ndim != 3:
             raise ValueError("'inp' must be 3D, (batch, time, neurons)")
         if not inp.is_contiguous():
@@ -254,12 +307,13 @@ class IntegrateAndFireTM(torch.autograd.Function):
             raise ValueError("'v_init' must hold one value per batch item and neuron")
         return _LifCore.forward(ctx, inp, alpha, v_init, threshold, membrane_subtract, min_v_mem, in_scale,
                                 surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count,
-                                B, T, M, _lib.LAYOUT_BTM, scale_grad_from_state, record)
+                                B, T, M, _lib.LAYOUT_BTM, scale_grad_from_state, record, decay_flags, scale_flags, acc)
 
     @staticmethod
     def backward(ctx, grad_spikes, grad_v_mem, grad_v_last):
         grad_input, grad_alpha, grad_init, grad_scale = _LifCore.backward(ctx, grad_spikes, grad_v_mem, grad_v_last)
-        return grad_input, grad_alpha, grad_init, None, None, None, grad_scale, None, None, None, None, None, None
+        return (grad_input, grad_alpha, grad_init, None, None, None, grad_scale, None, None, None, None, None, None,
+                None, None, None)
 
 
 def fused_synaptic_eligible(inp: torch.Tensor) -> bool:
@@ -286,7 +340,12 @@ class LIFSynapticTM(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, inp, alpha_syn, scale_syn, i_init, alpha_mem, scale_mem, v_init, threshold, membrane_subtract,
-                min_v_mem, surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count):
+                min_v_mem, surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count, flags=(0, 0, 0, 0),
+                acc=None):
+        """``flags``: (decay_syn, scale_syn, decay_mem, scale_mem) bits (``PARAM_IS_TAU``, ``SCALE_*``) for the four
+        parameter arguments.  ``acc``: (acc_mem, acc_syn), zeroed float64 tensors shaped like the flattened
+        ``alpha_mem`` / ``alpha_syn``, into which the backward kernel reduces the gradients w.r.t. the values passed
+        for the two decays (scale parts included) when neither scale is a tensor of its own."""
         if not fused_synaptic_eligible(inp):
             raise ValueError("'inp' must be a contiguous float32 CUDA tensor (batch, time, neurons) with neurons % 4 == 0")
         B, T, M = inp.shape
@@ -294,6 +353,7 @@ class LIFSynapticTM(torch.autograd.Function):
         f = {k: _flat32(t) for k, t in dict(a_syn=alpha_syn, s_syn=scale_syn, a_mem=alpha_mem, s_mem=scale_mem,
                                             th=threshold, c=membrane_subtract, lo=min_v_mem).items()}
         modes = {k: _mode_of(t, M, N, k) for k, t in f.items()}
+        modes["a_syn"] |= flags[0]; modes["s_syn"] |= flags[1]; modes["a_mem"] |= flags[2]; modes["s_mem"] |= flags[3]
         vi_f, ii_f = _flat32(v_init), _flat32(i_init)
         spikes = torch.empty_like(inp); v_mem = torch.empty_like(inp); i_syn = torch.empty_like(inp)
         v_post_last = torch.empty(N, dtype=torch.float32, device=inp.device)
@@ -316,6 +376,9 @@ class LIFSynapticTM(torch.autograd.Function):
         ctx.param_needs = {k: (t is not None and t.requires_grad) for k, t in
                            dict(a_syn=alpha_syn, s_syn=scale_syn, a_mem=alpha_mem, s_mem=scale_mem).items()}
         ctx.want_params = any(ctx.param_needs.values())
+        ctx.flags = flags
+        own_scale = (scale_syn is not None) or (scale_mem is not None)
+        ctx.acc = acc if (acc is not None and ctx.want_params and not own_scale) else None
         ctx.init_shapes = (None if v_init is None else v_init.shape, None if i_init is None else i_init.shape)
         saved = [v_mem] + [f[k] for k in ctx.keys] + [t for t in (vi_f, ii_f) if t is not None]
         ctx.has_init = (vi_f is not None, ii_f is not None)
@@ -353,23 +416,47 @@ class LIFSynapticTM(torch.autograd.Function):
             surr = ctx.surrogate_fn(v_mem, th_b).to(torch.float32).contiguous()
         new = lambda: torch.empty(N, dtype=torch.float32, device=dev)
         grad_input = torch.empty_like(v_mem)
-        ga_mem, gs_mem, ga_syn, gs_syn = (new(), new(), new(), new()) if ctx.want_params else (None,) * 4
         gv0 = new() if ctx.init_shapes[0] is not None else None
         gi0 = new() if ctx.init_shapes[1] is not None else None
         spec = lambda k: (f[k], modes[k])
-        _lib.lif_syn_backward(grad_input, ga_mem, gs_mem, ga_syn, gs_syn, gv0, gi0, g_spikes, g_vmem, g_vlast, g_isyn,
-                              g_ilast, v_mem, i_syn, surr, vi_f, ii_f, spec("a_syn"), spec("s_syn"), spec("s_mem"),
-                              spec("a_mem"), spec("c"), spec("th"), spec("lo"), ctx.max_spikes, ctx.reset_mode,
-                              kind, p0, p1, B, T, M)
-
-        def red(per_instance, key):
-            if not ctx.param_needs[key]:
-                return None
-            return _reduce_to_param(per_instance, ctx.param_shapes[key], modes[key], B, M)
-
+        tail = (gv0, gi0, g_spikes, g_vmem, g_vlast, g_isyn, g_ilast, v_mem, i_syn, surr, vi_f, ii_f, spec("a_syn"),
+                spec("s_syn"), spec("s_mem"), spec("a_mem"), spec("c"), spec("th"), spec("lo"), ctx.max_spikes,
+                ctx.reset_mode, kind, p0, p1, B, T, M)
         if gv0 is not None:
             gv0 = gv0.reshape(ctx.init_shapes[0])
         if gi0 is not None:
             gi0 = gi0.reshape(ctx.init_shapes[1])
+        if ctx.acc is not None:
+            # both decays' gradients reduced over the batch, with their scale parts and chain rules, in the kernel
+            _lib.lif_syn_backward(grad_input, None, None, None, None, *tail, acc_decay_mem=ctx.acc[0], acc_decay_syn=ctx.acc[1])
+            g_mem = torch.empty(f["a_mem"].numel(), dtype=torch.float32, device=dev)
+            g_syn = torch.empty(f["a_syn"].numel(), dtype=torch.float32, device=dev)
+            _lib.acc_finish(g_mem, ctx.acc[0])
+            _lib.acc_finish(g_syn, ctx.acc[1])
+            return (grad_input, g_syn.reshape(ctx.param_shapes["a_syn"]) if ctx.param_needs["a_syn"] else None, None, gi0,
+                    g_mem.reshape(ctx.param_shapes["a_mem"]) if ctx.param_needs["a_mem"] else None, None, gv0,
+                    None, None, None, None, None, None, None, None, None)
+        ga_mem, gs_mem, ga_syn, gs_syn = (new(), new(), new(), new()) if ctx.want_params else (None,) * 4
+        _lib.lif_syn_backward(grad_input, ga_mem, gs_mem, ga_syn, gs_syn, *tail)
+
+        def red(per_instance, key):
+            if not ctx.param_needs[key]:
+                return None
+            return _reduce_to_param(per_instance, ctx.param_shapes[key], modes[key] & _lib.PARAM_SHAPE_MASK, B, M)
+
+        if any(ctx.flags):
+            # derived decays / scales on a shape-independent route: fold with PyTorch what the kernel left per instance
+            def fold(key_a, key_s, decay_flags, scale_flags, ga, gs):
+                if not ctx.param_needs[key_a]:
+                    return None
+                shape, mode = ctx.param_shapes[key_a], modes[key_a] & _lib.PARAM_SHAPE_MASK
+                g = _reduce_to_param(ga, shape, mode, B, M)
+                gs_p = _reduce_to_param(gs, shape, mode, B, M) if scale_flags else None
+                return _fold_decay_grad(g, gs_p, f[key_a].reshape(shape), decay_flags, scale_flags, None)
+            fl = ctx.flags
+            return (grad_input, fold("a_syn", "s_syn", fl[0], fl[1], ga_syn, gs_syn), None if fl[1] else red(gs_syn, "s_syn"),
+                    gi0, fold("a_mem", "s_mem", fl[2], fl[3], ga_mem, gs_mem), None if fl[3] else red(gs_mem, "s_mem"),
+                    gv0, None, None, None, None, None, None, None, None, None)
+
         return (grad_input, red(ga_syn, "a_syn"), red(gs_syn, "s_syn"), gi0, red(ga_mem, "a_mem"), red(gs_mem, "s_mem"),
-                gv0, None, None, None, None, None, None, None)
+                gv0, None, None, None, None, None, None, None, None, None)
