@@ -58,11 +58,13 @@ def _scalar_constant(value: float, device) -> torch.Tensor:
     return t
 
 
-def _flat_param(value, trailing: Tuple[int, ...], batch: int, device) -> Optional[torch.Tensor]:
+def _flat_param(value, trailing: Tuple[int, ...], batch: int, device, perm=None) -> Optional[torch.Tensor]:
     """Bring a parameter to 1, M or B*M elements without breaking its autograd graph.
 
     A value that broadcasts against the neuron dimensions becomes M elements, one
     that needs the batch dimension too becomes B*M, a single value stays single.
+    ``perm``: order in which the neuron dimensions lie in the input's memory (None = as given); the
+    flattened parameter follows the same order.
     """
     if value is None:
         return None
@@ -74,9 +76,14 @@ def _flat_param(value, trailing: Tuple[int, ...], batch: int, device) -> Optiona
     if t.numel() == 1:
         return t.reshape(1)
     try:
-        return t.expand(trailing).reshape(-1)
+        t = t.expand(trailing)
+        lead = 0
     except RuntimeError:
-        return t.expand((batch, *trailing)).reshape(-1)
+        t = t.expand((batch, *trailing))
+        lead = 1
+    if perm is not None:
+        t = t.permute(*range(lead), *[lead + d for d in perm])
+    return t.reshape(-1)
 
 
 class _DecayFromTau(torch.autograd.Function):
@@ -206,6 +213,18 @@ class LIF(LIFBase):
         neurons = 1
         for d in trailing_dim:
             neurons *= d
+        # Neurons are independent, so the order in which they lie in memory is as good as any: an input whose
+        # neuron dimensions are stored in another order (a `channels_last` feature map from a convolution in front
+        # of a Squeeze layer, say) is used where it lies, with parameters, states and outputs following that order,
+        # instead of being copied into the row-major order first.
+        self._perm = None
+        if len(trailing_dim) > 1 and not x.is_contiguous():
+            order = sorted(range(len(trailing_dim)), key=lambda d: (-x.stride(2 + d), d))
+            if order != list(range(len(trailing_dim))):
+                xp = x.permute(0, 1, *[2 + d for d in order])
+                if xp.is_contiguous():
+                    self._perm = tuple(order)
+                    x = xp
         x = x.reshape(batch_size, time_steps, neurons)
         if not x.is_contiguous():
             x = x.contiguous()
@@ -225,6 +244,23 @@ class LIF(LIFBase):
             return _DecayFromTau.apply(tau, False)[0]
         return self.alpha_syn_calculated
 
+    _perm = None      # order of the neuron dimensions in the current input's memory (None: as declared)
+
+    def _state_flat(self, state: torch.Tensor) -> torch.Tensor:
+        """A (batch, *neurons) state as the flat vector the kernels index, neurons in the input's memory order."""
+        if self._perm is not None and state.dim() == 1 + len(self._perm):
+            state = state.permute(0, *[1 + d for d in self._perm])
+        return state.reshape(-1)
+
+    def _unflatten(self, t: torch.Tensor, lead: Tuple[int, ...], trailing: Tuple[int, ...]) -> torch.Tensor:
+        """(*lead, M) in the kernels' neuron order -> (*lead, *trailing) in the declared order; a view either way, so an
+        output computed on a `channels_last` input comes back in `channels_last` memory."""
+        if self._perm is None:
+            return t.reshape(*lead, *trailing)
+        t = t.reshape(*lead, *[trailing[d] for d in self._perm])
+        inverse = sorted(range(len(self._perm)), key=lambda i: self._perm[i])
+        return t.permute(*range(len(lead)), *[len(lead) + i for i in inverse])
+
     def _decay_source(self, which: str):
         """``(tensor, flags)`` for the decay of the membrane (``"mem"``) or synapse (``"syn"``) stage: what the layer
         owns -- the time constant (``PARAM_IS_TAU``: the kernels form ``exp(-1/tau)`` themselves, and their backward
@@ -243,17 +279,17 @@ class LIF(LIFBase):
 
     def _forward_synaptic(self, x: torch.Tensor, batch: int, trailing):
         raw, dflags = self._decay_source("syn")
-        raw = _flat_param(raw, trailing, batch, x.device)
+        raw = _flat_param(raw, trailing, batch, x.device, self._perm)
         acc = None
         if raw.requires_grad and torch.is_grad_enabled() and acc_eligible(x):
             acc = torch.zeros(raw.numel(), dtype=torch.float64, device=x.device)
-        return LeakyIntegratorTM.apply(x, raw, self.i_syn.reshape(-1), None, None, dflags,
+        return LeakyIntegratorTM.apply(x, raw, self._state_flat(self.i_syn), None, None, dflags,
                                        _lib.SCALE_TIMES_ALPHA if self.decay_early else 0, acc)
 
     def _forward_membrane(self, i_syn: torch.Tensor, batch: int, trailing):
         dev = i_syn.device
         raw, dflags = self._decay_source("mem")
-        raw = _flat_param(raw, trailing, batch, dev)
+        raw = _flat_param(raw, trailing, batch, dev, self._perm)
         sflags = _lib.SCALE_ONE_MINUS_ALPHA if self.norm_input else 0
         use_acc = raw.requires_grad and torch.is_grad_enabled() and acc_eligible(i_syn)
         aux = self._aux(raw.numel() if use_acc else 0, dev)
@@ -263,17 +299,17 @@ class LIF(LIFBase):
             if self.decay_early:
                 sflags |= _lib.SCALE_TIMES_ALPHA
             total = aux[:1]
-            v_mem, v_last = LeakyIntegratorTM.apply(i_syn, raw, self.v_mem.reshape(-1), None, total, dflags, sflags, acc)
+            v_mem, v_last = LeakyIntegratorTM.apply(i_syn, raw, self._state_flat(self.v_mem), None, total, dflags, sflags, acc)
             return v_mem, v_mem, v_last, total
 
-        threshold = _flat_param(self.spike_threshold, trailing, batch, dev)
-        min_v_mem = _flat_param(self.min_v_mem, trailing, batch, dev)
+        threshold = _flat_param(self.spike_threshold, trailing, batch, dev, self._perm)
+        min_v_mem = _flat_param(self.min_v_mem, trailing, batch, dev, self._perm)
         if isinstance(self.reset_fn, MembraneReset):
             reset_mode = _lib.RESET_TO_VALUE
-            subtract = _flat_param(self.reset_fn.reset_value, trailing, batch, dev)
+            subtract = _flat_param(self.reset_fn.reset_value, trailing, batch, dev, self._perm)
         else:
             reset_mode = _lib.RESET_SUBTRACT
-            subtract = _flat_param(self.reset_fn.subtract_value, trailing, batch, dev)
+            subtract = _flat_param(self.reset_fn.subtract_value, trailing, batch, dev, self._perm)
         self._validate_once(dev)
         count = aux[:1].view(torch.int64)
         # With autograd off the recorded potential is a plain side output of the forward launch; with autograd on
@@ -281,7 +317,7 @@ class LIF(LIFBase):
         fused_record = self.record_states and not torch.is_grad_enabled()
         v_rec = torch.empty_like(i_syn) if fused_record else None
         spikes, v_pre, v_post_last = IntegrateAndFireTM.apply(
-            i_syn, raw, self.v_mem.reshape(-1), threshold, subtract, min_v_mem, None,
+            i_syn, raw, self._state_flat(self.v_mem), threshold, subtract, min_v_mem, None,
             self.surrogate_grad_fn, self.max_num_spikes_per_bin, reset_mode, count,
             bool(sflags) and getattr(self, "_scale_nonzero", False), v_rec, dflags, sflags, acc)
         if self.record_states and not fused_record:
@@ -332,7 +368,7 @@ class LIF(LIFBase):
         dev = x.device
         B, T, M = x.shape
         N = B * M
-        flat = lambda v: _flat32(_flat_param(v, trailing, batch, dev))
+        flat = lambda v: _flat32(_flat_param(v, trailing, batch, dev, self._perm))
         raw_mem, dmem = self._decay_source("mem")
         a_mem = flat(raw_mem)
         smem_flags = _lib.SCALE_ONE_MINUS_ALPHA if self.norm_input else 0
@@ -348,14 +384,14 @@ class LIF(LIFBase):
         v_mem = torch.empty_like(x) if keep else None
         v_post_last = torch.empty(N, dtype=torch.float32, device=dev)
         count = torch.zeros(1, dtype=torch.int64, device=dev)
-        v0 = self.v_mem.reshape(-1).to(torch.float32).contiguous()
+        v0 = self._state_flat(self.v_mem).to(torch.float32).contiguous()
         i_syn = None
         if has_synapse:
             raw_syn, dsyn = self._decay_source("syn")
             a_syn = flat(raw_syn)
             i_syn = torch.empty_like(x) if keep else None
             i_last = torch.empty(N, dtype=torch.float32, device=dev)
-            i0 = self.i_syn.reshape(-1).to(torch.float32).contiguous()
+            i0 = self._state_flat(self.i_syn).to(torch.float32).contiguous()
             done = _lib.lif_syn_forward_u8(
                 spikes, v_mem, i_syn, x, v0, i0, spec(a_syn, "alpha_syn", dsyn),
                 spec(None, "scale_syn", _lib.SCALE_TIMES_ALPHA if self.decay_early else 0),
@@ -370,11 +406,11 @@ class LIF(LIFBase):
         if not done:
             return None        # shape the byte kernels do not take: the caller converts the float raster
         if has_synapse:
-            self.i_syn = i_last.reshape(batch, *trailing)
-        self.v_mem = v_post_last.reshape(batch, *trailing)
+            self.i_syn = self._unflatten(i_last, (batch,), trailing)
+        self.v_mem = self._unflatten(v_post_last, (batch,), trailing)
         if keep:
             if i_syn is not None:
-                self.recordings["i_syn"] = i_syn.reshape(original_shape)
+                self.recordings["i_syn"] = self._unflatten(i_syn, tuple(original_shape[:2]), tuple(original_shape[2:]))
             bc = lambda t: t if t.numel() == 1 else (t.view(1, 1, -1) if t.numel() == M else t.view(B, 1, -1))
             thb, cb = bc(th), bc(th if c is None else c)
             if reset_mode == _lib.RESET_SUBTRACT:       # true counts for the recording: rebuilt from v_mem, not from the bytes
@@ -384,8 +420,8 @@ class LIF(LIFBase):
                 v_rec = v_mem - cb * k
             else:
                 v_rec = torch.where(spikes > 0, cb.expand_as(v_mem), v_mem)
-            self.recordings["v_mem"] = v_rec.reshape(original_shape)
-        out = spikes.reshape(original_shape)
+            self.recordings["v_mem"] = self._unflatten(v_rec, tuple(original_shape[:2]), tuple(original_shape[2:]))
+        out = self._unflatten(spikes, tuple(original_shape[:2]), tuple(original_shape[2:]))
         self._set_rate_source(count, out.numel())
         return out
 
@@ -447,15 +483,15 @@ class LIF(LIFBase):
             i_syn = x
         else:
             i_syn, i_last = self._forward_synaptic(x, batch_size, trailing)
-            self.i_syn = i_last.reshape(batch_size, *trailing)
+            self.i_syn = self._unflatten(i_last, (batch_size,), trailing)
             if self.record_states:
-                self.recordings["i_syn"] = i_syn.reshape(original_shape)
+                self.recordings["i_syn"] = self._unflatten(i_syn, tuple(original_shape[:2]), tuple(original_shape[2:]))
 
         output, v_rec, v_last, count = self._forward_membrane(i_syn, batch_size, trailing)
         if self.record_states:
-            self.recordings["v_mem"] = v_rec.reshape(original_shape)
-        self.v_mem = v_last.reshape(batch_size, *trailing)
-        output_full = output.reshape(original_shape)
+            self.recordings["v_mem"] = self._unflatten(v_rec, tuple(original_shape[:2]), tuple(original_shape[2:]))
+        self.v_mem = self._unflatten(v_last, (batch_size,), trailing)
+        output_full = self._unflatten(output, tuple(original_shape[:2]), tuple(original_shape[2:]))
         # spike count (int64) or, for the non-spiking layer, the sum of the outputs (float64): both come
         # out of the forward kernel, so the reference's `output.sum() / numel` pass is not needed
         self._set_rate_source(count, output_full.numel(), output_full)
@@ -468,39 +504,39 @@ class LIF(LIFBase):
         dev = x.device
         raw_syn, dsyn = self._decay_source("syn")
         raw_mem, dmem = self._decay_source("mem")
-        raw_syn = _flat_param(raw_syn, trailing, batch_size, dev)
-        raw_mem = _flat_param(raw_mem, trailing, batch_size, dev)
+        raw_syn = _flat_param(raw_syn, trailing, batch_size, dev, self._perm)
+        raw_mem = _flat_param(raw_mem, trailing, batch_size, dev, self._perm)
         flags = (dsyn, _lib.SCALE_TIMES_ALPHA if self.decay_early else 0,
                  dmem, _lib.SCALE_ONE_MINUS_ALPHA if self.norm_input else 0)
         use_acc = (raw_syn.requires_grad or raw_mem.requires_grad) and torch.is_grad_enabled()
         aux = self._aux(raw_mem.numel() + raw_syn.numel() if use_acc else 0, dev)
         acc = (aux[1:1 + raw_mem.numel()], aux[1 + raw_mem.numel():]) if use_acc else None
-        threshold = _flat_param(self.spike_threshold, trailing, batch_size, dev)
-        min_v_mem = _flat_param(self.min_v_mem, trailing, batch_size, dev)
+        threshold = _flat_param(self.spike_threshold, trailing, batch_size, dev, self._perm)
+        min_v_mem = _flat_param(self.min_v_mem, trailing, batch_size, dev, self._perm)
         if isinstance(self.reset_fn, MembraneReset):
             reset_mode = _lib.RESET_TO_VALUE
-            subtract = _flat_param(self.reset_fn.reset_value, trailing, batch_size, dev)
+            subtract = _flat_param(self.reset_fn.reset_value, trailing, batch_size, dev, self._perm)
         else:
             reset_mode = _lib.RESET_SUBTRACT
-            subtract = _flat_param(self.reset_fn.subtract_value, trailing, batch_size, dev)
+            subtract = _flat_param(self.reset_fn.subtract_value, trailing, batch_size, dev, self._perm)
         self._validate_once(dev)
         count = aux[:1].view(torch.int64)
         spikes, v_pre, v_post_last, i_syn, i_last = LIFSynapticTM.apply(
-            x, raw_syn, None, self.i_syn.reshape(-1), raw_mem, None,
-            self.v_mem.reshape(-1), threshold, subtract, min_v_mem, self.surrogate_grad_fn,
+            x, raw_syn, None, self._state_flat(self.i_syn), raw_mem, None,
+            self._state_flat(self.v_mem), threshold, subtract, min_v_mem, self.surrogate_grad_fn,
             self.max_num_spikes_per_bin, reset_mode, count, flags, acc)
-        self.i_syn = i_last.reshape(batch_size, *trailing)
-        self.v_mem = v_post_last.reshape(batch_size, *trailing)
+        self.i_syn = self._unflatten(i_last, (batch_size,), trailing)
+        self.v_mem = self._unflatten(v_post_last, (batch_size,), trailing)
         if self.record_states:
-            self.recordings["i_syn"] = i_syn.reshape(original_shape)
+            self.recordings["i_syn"] = self._unflatten(i_syn, tuple(original_shape[:2]), tuple(original_shape[2:]))
             c = threshold if subtract is None else subtract
             c = c if c.numel() == 1 else (c.view(1, 1, -1) if c.numel() == v_pre.shape[2] else c.view(batch_size, 1, -1))
             if reset_mode == _lib.RESET_SUBTRACT:
                 v_rec = v_pre - c * spikes
             else:
                 v_rec = torch.where(spikes > 0, c.expand_as(v_pre), v_pre)
-            self.recordings["v_mem"] = v_rec.reshape(original_shape)
-        output_full = spikes.reshape(original_shape)
+            self.recordings["v_mem"] = self._unflatten(v_rec, tuple(original_shape[:2]), tuple(original_shape[2:]))
+        output_full = self._unflatten(spikes, tuple(original_shape[:2]), tuple(original_shape[2:]))
         self._set_rate_source(count, output_full.numel(), output_full)
         return output_full
 

@@ -611,3 +611,47 @@ def test_layer_recordings_fused_under_no_grad():
         torch.testing.assert_close(out_a.detach(), out_b, rtol=0, atol=0)
         torch.testing.assert_close(a.recordings["v_mem"].detach(), b.recordings["v_mem"], rtol=0, atol=0)
         assert a.recordings["v_mem"].requires_grad and not b.recordings["v_mem"].requires_grad
+
+
+@pytest.mark.parametrize("per_channel_tau", [False, True])
+def test_channels_last_input_is_used_where_it_lies(per_channel_tau, monkeypatch):
+    """A `channels_last` feature map (what a cuDNN convolution in that memory format hands to the Squeeze layer after
+    it, reference layers/iaf.py:96-112): the kernels read it in place -- no copy into row-major order -- and the output
+    comes back in `channels_last` memory; values, states and gradients are those of the row-major route."""
+    from sinabs_exodus_b200 import _lib
+    from sinabs_exodus_b200.layers import LIFSqueeze
+    B, T, C, H, W = 2, 12, 8, 5, 6
+    torch.manual_seed(5)
+    conv = torch.nn.Conv2d(3, C, 3, padding=1).to("cuda:0").to(memory_format=torch.channels_last)
+    frames = torch.randn(B * T, 3, H, W, device="cuda:0").to(memory_format=torch.channels_last)
+    tau = (10.0 + 20.0 * torch.rand(C, 1, 1)) if per_channel_tau else 15.0
+    make = lambda: LIFSqueeze(batch_size=B, tau_mem=tau, min_v_mem=-1.0, record_states=True).to("cuda:0")
+    seen = []
+    real = _lib.lif_forward
+    monkeypatch.setattr(_lib, "lif_forward", lambda spikes, v_mem, inp, *a, **k: (seen.append(inp.data_ptr()), real(spikes, v_mem, inp, *a, **k))[1])
+
+    def run(layer, as_is):
+        conv.zero_grad()
+        y = 3.0 * conv(frames)
+        assert y.is_contiguous(memory_format=torch.channels_last) and not y.is_contiguous()
+        y_in = y if as_is else y.contiguous()
+        outs = []
+        for _ in range(2):                       # the second call starts from the carried state
+            outs.append(layer(y_in))
+        w = torch.arange(outs[0].numel(), device="cuda:0", dtype=torch.float32).reshape(outs[0].shape).cos()
+        ((outs[0] + outs[1]) * w).sum().backward()
+        grads = [p.grad.clone() for p in list(conv.parameters()) + list(layer.parameters())]
+        return y, outs, grads
+
+    a, b = make(), make()
+    y, outs_a, grads_a = run(a, True)
+    assert seen[0] == y.data_ptr()                                    # the kernel got the convolution's own memory
+    assert outs_a[0].is_contiguous(memory_format=torch.channels_last)
+    _, outs_b, grads_b = run(b, False)
+    for oa, ob in zip(outs_a, outs_b):
+        torch.testing.assert_close(oa, ob, rtol=0, atol=0)
+    torch.testing.assert_close(a.v_mem, b.v_mem, rtol=0, atol=0)
+    torch.testing.assert_close(a.recordings["v_mem"], b.recordings["v_mem"], rtol=0, atol=0)
+    assert outs_a[0].sum() > 0
+    for ga, gb in zip(grads_a, grads_b):
+        torch.testing.assert_close(ga, gb, rtol=1e-4, atol=1e-5)
