@@ -192,6 +192,19 @@ int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, flo
  * leaves the reduction to autograd's expand-backward (layers/lif.py:43-44). */
 int exb_acc_finish(float *out, double *acc, int64_t n, int device, void *stream);
 
+/* One-shot sum-allreduce of a small float vector between the GPUs of one node, for the time-constant
+ * gradients that batch-sharded ranks exchange once per step (a few KB: launch latency, not bandwidth).
+ * `buffers` and `signals` are device arrays of `world` addresses: buffers[p] is rank p's data area of
+ * 2*n floats, signals[p] its signal area of 2*world uint32 (zero before the first call), both mapped into
+ * this process (CUDA peer / fabric mapping, e.g. PyTorch symmetric memory).  Every rank calls with the same
+ * n and the same epoch, which starts at 1 and grows by 1 per call.  One CTA: publishes `in` in the own area,
+ * signals every peer, waits -- bounded, see exb_set_wait_limit -- for every peer's signal, and adds all
+ * ranks' vectors in rank order with plain peer loads, so all ranks get the same bits in `out`.  If a peer
+ * does not arrive in time, `out` is NaN and exb_device_status reports EXB_ERR_TIMEOUT.  No counterpart in
+ * the reference (which is single-GPU); the library's default exchange is an NCCL allreduce. */
+int exb_allreduce_oneshot(float *out, const float *in, const uint64_t *buffers, const uint64_t *signals,
+                          int rank, int world, int64_t n, uint32_t epoch, int device, void *stream);
+
 /* Leaky integrator forward, v_t = alpha*v_{t-1} + scale*in_t.  Replaces
  * leakyForward (cuda/bindings.cu:163-193, kernel cuda/leaky_kernels.h:29-58).
  * in_scale (NULL = 1) is a per-neuron factor on the input that fuses the

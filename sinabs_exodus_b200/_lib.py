@@ -40,7 +40,7 @@ _f = ctypes.c_float
 _lib: Optional[ctypes.CDLL] = None
 
 EXPORTS = (
-    "exb_version", "exb_last_error", "exb_status_string", "exb_device_status", "exb_set_wait_limit", "exb_acc_finish",
+    "exb_version", "exb_last_error", "exb_status_string", "exb_device_status", "exb_set_wait_limit", "exb_acc_finish", "exb_allreduce_oneshot",
     "exb_lif_forward", "exb_lif_forward_record", "exb_lif_forward_u8", "exb_lif_syn_forward_u8", "exb_lif_backward", "exb_leaky_forward", "exb_leaky_backward",
     "exb_leaky_scan_workspace_bytes", "exb_leaky_forward_scan", "exb_leaky_backward_scan",
     "exb_leaky_forward_scan_static", "exb_static_scratch_bytes", "exb_lif_syn_forward", "exb_lif_syn_backward",
@@ -87,6 +87,8 @@ def load() -> ctypes.CDLL:
                                      _vp, _vp, _vp, _vp,
                                      _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _i,
                                      _u32, _i, _i, _f, _f, _vp] + geometry
+    lib.exb_allreduce_oneshot.restype = _i
+    lib.exb_allreduce_oneshot.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i64, _u32, _i, _vp]
     lib.exb_acc_finish.restype = _i
     lib.exb_acc_finish.argtypes = [_vp, _vp, _i64, _i, _vp]
     lib.exb_leaky_forward.restype = _i
@@ -190,7 +192,15 @@ def _require_cuda(*tensors: Optional[torch.Tensor]) -> torch.device:
     return dev
 
 
+try:      # raw handle of the current stream without building a Stream object (a few microseconds per call less)
+    _raw_stream = torch._C._cuda_getCurrentRawStream
+except AttributeError:      # pragma: no cover - older PyTorch
+    _raw_stream = None
+
+
 def _stream(dev: torch.device):
+    if _raw_stream is not None:
+        return _raw_stream(dev.index)
     return torch.cuda.current_stream(dev).cuda_stream
 
 
@@ -275,6 +285,18 @@ def lif_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, gra
     _check(st, "exb_lif_backward")
     _after_launch(dev)
     return True
+
+
+def allreduce_oneshot(out: torch.Tensor, inp: torch.Tensor, buffers: torch.Tensor, signals: torch.Tensor, rank: int,
+                      world: int, epoch: int) -> None:
+    """``exb_allreduce_oneshot``; ``buffers`` / ``signals``: int64 CUDA tensors holding the ``world`` peer addresses."""
+    dev = _require_cuda(out, inp)
+    n = inp.numel()
+    if out.numel() != n or not (out.is_contiguous() and inp.is_contiguous()):
+        raise ExodusLibraryError("allreduce_oneshot needs contiguous float32 vectors of equal length")
+    st = load().exb_allreduce_oneshot(out.data_ptr(), inp.data_ptr(), buffers.data_ptr(), signals.data_ptr(), rank, world,
+                                      n, epoch, dev.index, _stream(dev))
+    _check(st, "exb_allreduce_oneshot")
 
 
 def acc_finish(out: torch.Tensor, acc: torch.Tensor) -> None:

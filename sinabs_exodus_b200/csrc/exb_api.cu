@@ -463,6 +463,23 @@ int exb_acc_finish(float *out, double *acc, int64_t n, int device, void *stream)
     return launch_status(exb::launch_acc_finish(out, acc, n, (cudaStream_t)stream), "exb_acc_finish");
 }
 
+int exb_allreduce_oneshot(float *out, const float *in, const uint64_t *buffers, const uint64_t *signals,
+                          int rank, int world, int64_t n, uint32_t epoch, int device, void *stream)
+{
+    if (!out || !in || !buffers || !signals) return fail(EXB_ERR_ARG, "exb_allreduce_oneshot: out, in, buffers and signals are required");
+    if (world < 1 || world > 16 || rank < 0 || rank >= world)
+        return fail(EXB_ERR_ARG, "exb_allreduce_oneshot: rank %d of %d (at most 16 ranks)", rank, world);
+    if (n <= 0 || n > (1 << 24)) return fail(EXB_ERR_ARG, "exb_allreduce_oneshot: n must be in 1 .. 2^24");
+    if (epoch == 0) return fail(EXB_ERR_ARG, "exb_allreduce_oneshot: epochs start at 1 (the signal words start at 0)");
+    if (!all_aligned4(out, in) || (reinterpret_cast<uintptr_t>(buffers) & 7u) || (reinterpret_cast<uintptr_t>(signals) & 7u))
+        return misaligned("exb_allreduce_oneshot");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_allreduce_oneshot: cannot select device %d", device);
+    return launch_status(exb::launch_allreduce_oneshot(out, in, reinterpret_cast<const unsigned long long *>(buffers),
+                                                       reinterpret_cast<const unsigned long long *>(signals), rank, world, n,
+                                                       epoch, (cudaStream_t)stream), "exb_allreduce_oneshot");
+}
+
 int64_t exb_static_scratch_bytes(void) { return (int64_t)exb::leaky_scan_static_capacity(); }
 
 // Time-parallel leaky forward for callers that cannot supply scratch memory (see the header).

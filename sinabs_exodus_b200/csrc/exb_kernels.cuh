@@ -98,6 +98,10 @@ cudaError_t launch_leaky_forward_scan(const LeakyFwdArgs &a, void *workspace, in
                                       cudaStream_t s, bool *used);
 cudaError_t launch_leaky_backward_scan(const LeakyBwdArgs &a, void *workspace, int64_t workspace_bytes, bool clean,
                                        cudaStream_t s, bool *used);
+// One-shot sum-allreduce of a small vector over peer-mapped memory (one CTA per rank; see exb_tma_kernels.cu).
+cudaError_t launch_allreduce_oneshot(float *out, const float *in, const unsigned long long *buffers,
+                                     const unsigned long long *signals, int rank, int world, int64_t n, unsigned int epoch,
+                                     cudaStream_t s);
 // out[i] = (float) acc[i]; acc[i] = 0.
 cudaError_t launch_acc_finish(float *out, double *acc, int64_t n, cudaStream_t s);
 // Forward scan on the library's own fixed scratch array (no caller workspace).

@@ -27,7 +27,8 @@ namespace exb {
 // exb_device_status looks at all of them.
 static __device__ unsigned int g_exb_status = 0;
 
-enum { EXB_STATUS_FULL_WAIT = 1, EXB_STATUS_EMPTY_WAIT = 2, EXB_STATUS_DRAIN_WAIT = 3, EXB_STATUS_LOOKBACK_WAIT = 4 };
+enum { EXB_STATUS_FULL_WAIT = 1, EXB_STATUS_EMPTY_WAIT = 2, EXB_STATUS_DRAIN_WAIT = 3, EXB_STATUS_LOOKBACK_WAIT = 4,
+       EXB_STATUS_PEER_WAIT = 5 };
 
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 

@@ -573,6 +573,88 @@ cudaError_t launch_acc_finish(float *out, double *acc, int64_t n, cudaStream_t s
     return cudaPeekAtLastError();
 }
 
+// ---- one-shot sum-allreduce of a small vector over peer memory --------------------------------------------
+// For the few KB of time-constant gradients that batch-sharded ranks exchange once per step.  Every rank owns a
+// slot pair (two parities) in a buffer that all ranks of the node have mapped (NVLink peer access), and a row of
+// signal words per parity.  One CTA per rank: copy the local partial into the own slot, make it visible
+// system-wide, store the call's epoch into every peer's signal row, wait (bounded) for every peer's epoch, then
+// read all ranks' slots with plain peer loads and add them in rank order, so that every rank obtains the same
+// bits.  Two parities are enough: a rank can only enter call k+2, which reuses the slots of call k, after every
+// peer has signalled call k+1, which a peer does after it finished reading call k.  No multimem, no TMA.
+__device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *p)
+{
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ float ld_relaxed_sys(const float *p)
+{
+    float v;
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+
+constexpr int ONESHOT_MAX_RANKS = 16;
+
+__global__ void __launch_bounds__(256) allreduce_oneshot_kernel(float *out, const float *in, const unsigned long long *buffers,
+                                                                const unsigned long long *signals, int rank, int world,
+                                                                int n, unsigned int epoch)
+{
+    __shared__ int s_ok;
+    const int parity = (int)(epoch & 1u);
+    float *mine = reinterpret_cast<float *>(buffers[rank]) + (size_t)parity * n;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) mine[i] = in[i];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < world) {
+        const int p = threadIdx.x;
+        // announce: "rank `rank` has published call `epoch`" in peer p's row
+        st_release_sys(reinterpret_cast<unsigned int *>(signals[p]) + parity * world + rank, epoch);
+        // and wait for p's announcement in the own row
+        const unsigned int *flag = reinterpret_cast<const unsigned int *>(signals[rank]) + parity * world + p;
+        bool arrived = ld_acquire_sys(flag) == epoch;
+        const uint32_t limit = c_exb_wait_limit;
+        for (uint32_t i = 1; !arrived && i < limit; ++i) {
+            __nanosleep(100);
+            arrived = ld_acquire_sys(flag) == epoch;
+        }
+        if (!arrived) {
+            report_timeout(EXB_STATUS_PEER_WAIT);
+            s_ok = 0;
+        }
+    }
+    __syncthreads();
+    const bool ok = s_ok != 0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float acc = 0.0f;
+        if (ok) {
+            for (int p = 0; p < world; ++p)
+                acc = __fadd_rn(acc, ld_relaxed_sys(reinterpret_cast<const float *>(buffers[p]) + (size_t)parity * n + i));
+        } else {
+            acc = NAN;      // a peer never arrived: the sum is not known
+        }
+        out[i] = acc;
+    }
+}
+
+cudaError_t launch_allreduce_oneshot(float *out, const float *in, const unsigned long long *buffers,
+                                     const unsigned long long *signals, int rank, int world, int64_t n, unsigned int epoch,
+                                     cudaStream_t s)
+{
+    if (world < 1 || world > ONESHOT_MAX_RANKS || rank < 0 || rank >= world || n <= 0 || n > (1 << 24))
+        return cudaErrorInvalidValue;
+    allreduce_oneshot_kernel<<<1, 256, 0, s>>>(out, in, buffers, signals, rank, world, (int)n, epoch);
+    return cudaPeekAtLastError();
+}
+
 bool tma_enabled()
 {
     static const bool on = []() {

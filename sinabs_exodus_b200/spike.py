@@ -78,8 +78,12 @@ def acc_eligible(inp: torch.Tensor) -> bool:
 
 
 def _flat32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """Detached flat float32 view (or copy) of a parameter, as the library takes it.  The common cases -- a constant
+    that is already such a vector, a flat float32 parameter -- cost no or one tensor operation."""
     if t is None:
         return None
+    if t.dtype == torch.float32 and t.dim() == 1 and t.is_contiguous():
+        return t.detach() if t.requires_grad else t
     return t.detach().to(torch.float32).reshape(-1).contiguous()
 
 

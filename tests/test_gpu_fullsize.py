@@ -265,7 +265,7 @@ def test_config5_lif_full_size(norm_input):
     zeros, ones = np.zeros(R, np.float32), np.ones(R, np.float32)
     s_ref, v_ref = orc.lif_forward_ext(xin, zeros, a, ones, ones, None, None, in_scale=sc)
     np.testing.assert_array_equal(_sample_rows(out.detach(), rb, rm), s_ref)
-    assert norm_input or (s_ref > 1).mean() > 0.5
+    assert norm_input or ((s_ref > 1).any() and s_ref.mean() > 0.1)
     surr = orc.surrogate_f64("single_exponential", v_ref, 1.0, 0.5, 1.0)
     g_rows = surr * _sample_rows(go, rb, rm).astype(np.float64)
     gi64, _ = orc.lif_backward_f64(g_rows.astype(np.float32), surr.astype(np.float32), np.ones_like(v_ref), a, ones)
