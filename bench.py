@@ -547,6 +547,22 @@ def measure_other(name: str, timer: KernelTimer, dev, rank: int, world: int, ste
         res["collective"] = {"what": "sum-allreduce of the time-constant gradients (NCCL, one flat buffer), inside the timed region",
                              "floats": int(sum(p.numel() for p in w.tc_params)), "avg_ms": sum(c_ms) / len(c_ms),
                              "calls": len(c_ms)}
+        # the same exchange as one kernel per rank over peer-mapped memory (exb_allreduce_oneshot), timed alone
+        try:
+            from sinabs_exodus_b200.distributed import OneShotAllReduce
+            one = OneShotAllReduce(int(sum(p.numel() for p in w.tc_params)), dev)
+            for _ in range(3):
+                one.allreduce_gradients(w.tc_params)
+            evs = []
+            for _ in range(10):
+                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+                e0.record(); one.allreduce_gradients(w.tc_params); e1.record()
+                evs.append((e0, e1))
+            torch.cuda.synchronize()
+            res["collective"]["one_shot_avg_ms"] = sum(a.elapsed_time(b) for a, b in evs) / len(evs)
+            ex._lib.device_status(dev)
+        except Exception as exc:
+            res["collective"]["one_shot_unavailable"] = f"{type(exc).__name__}: {str(exc)[:160]}"
     if name in ("c1", "c3", "c4") and not (world > 1 and w.tc_params):
         # the same step captured once as a CUDA graph: what is left when the per-step host work is taken out
         try:

@@ -41,7 +41,7 @@ struct SynGeom {
 // ST: element type of the spike raster (float, or uint8_t for the compact raster); WS: write v_mem and i_syn
 // (a forward pass that nobody differentiates or records needs only the spikes).
 template <int RESET, int NW, int V, bool UNI, int TC, typename ST, bool WS>
-__global__ void __launch_bounds__((NW + 1) * 32, (NW == 8) ? 4 : MinBlocks<NW, V, (V == 4)>::value)
+__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V, (V == 4)>::value)
 lif_syn_fwd_tma_kernel(const __grid_constant__ TmaMaps6 maps, const LifSynFwdArgs A, const int tiles_m, const int nstages)
 {
     using G = TileGeom<NW, V>;
@@ -413,11 +413,6 @@ template <int RESET>
 static cudaError_t pick_syn_fwd(const LifSynFwdArgs &a, cudaStream_t s, bool *used)
 {
     if (!use_wide(a.B, a.M)) {
-        static const int env_nw = env_int("EXB_SYN_FWD_NW", 0);
-        if (env_nw == 8 && a.M % 256 == 0) {      // tuning aid: eight consumer warps, 256-neuron tiles (1 KB rows)
-            const int tc8 = syn_pick_tc<16, 8>(256, 1, a.B * ((a.M + 255) / 256), false);
-            return tc8 == 16 ? run_syn_fwd<RESET, 8, 1, true, 16>(a, s, used) : run_syn_fwd<RESET, 8, 1, true, 8>(a, s, used);
-        }
         const int tc = syn_pick_tc<16, 8>(128, 1, a.B * ((a.M + 127) / 128), false);
         return tc == 16 ? run_syn_fwd<RESET, NWARPS, 1, true, 16>(a, s, used) : run_syn_fwd<RESET, NWARPS, 1, true, 8>(a, s, used);
     }

@@ -625,7 +625,7 @@ def test_channels_last_input_is_used_where_it_lies(per_channel_tau, monkeypatch)
     conv = torch.nn.Conv2d(3, C, 3, padding=1).to("cuda:0").to(memory_format=torch.channels_last)
     frames = torch.randn(B * T, 3, H, W, device="cuda:0").to(memory_format=torch.channels_last)
     tau = (10.0 + 20.0 * torch.rand(C, 1, 1)) if per_channel_tau else 15.0
-    make = lambda: LIFSqueeze(batch_size=B, tau_mem=tau, min_v_mem=-1.0, record_states=True).to("cuda:0")
+    make = lambda: LIFSqueeze(batch_size=B, tau_mem=tau, min_v_mem=-1.0, record_states=True, norm_input=False).to("cuda:0")
     seen = []
     real = _lib.lif_forward
     monkeypatch.setattr(_lib, "lif_forward", lambda spikes, v_mem, inp, *a, **k: (seen.append(inp.data_ptr()), real(spikes, v_mem, inp, *a, **k))[1])
