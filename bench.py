@@ -547,19 +547,28 @@ def measure_other(name: str, timer: KernelTimer, dev, rank: int, world: int, ste
         res["collective"] = {"what": "sum-allreduce of the time-constant gradients (NCCL, one flat buffer), inside the timed region",
                              "floats": int(sum(p.numel() for p in w.tc_params)), "avg_ms": sum(c_ms) / len(c_ms),
                              "calls": len(c_ms)}
-        # the same exchange as one kernel per rank over peer-mapped memory (exb_allreduce_oneshot), timed alone
-        try:
-            from sinabs_exodus_b200.distributed import OneShotAllReduce
-            one = OneShotAllReduce(int(sum(p.numel() for p in w.tc_params)), dev)
+        # The exchange alone, GPU otherwise idle, both ways on equal footing (these small calls are bound by their
+        # host path, which is what they cost a step that is itself host-bound): the NCCL route of
+        # distributed.allreduce_gradients (flatten, collective, scatter) and the one-kernel route over peer-mapped
+        # memory (exb_allreduce_oneshot).
+        def alone(fn, reps=20):
             for _ in range(3):
-                one.allreduce_gradients(w.tc_params)
-            evs = []
-            for _ in range(10):
-                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-                e0.record(); one.allreduce_gradients(w.tc_params); e1.record()
-                evs.append((e0, e1))
+                fn()
             torch.cuda.synchronize()
-            res["collective"]["one_shot_avg_ms"] = sum(a.elapsed_time(b) for a, b in evs) / len(evs)
+            import torch.distributed as dist
+            dist.barrier()
+            e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / reps
+        from sinabs_exodus_b200 import distributed as exd
+        res["collective"]["nccl_alone_avg_ms"] = alone(lambda: exd.allreduce_gradients(w.tc_params))
+        try:
+            one = exd.OneShotAllReduce(int(sum(p.numel() for p in w.tc_params)), dev)
+            res["collective"]["one_shot_alone_avg_ms"] = alone(lambda: one.allreduce_gradients(w.tc_params))
             ex._lib.device_status(dev)
         except Exception as exc:
             res["collective"]["one_shot_unavailable"] = f"{type(exc).__name__}: {str(exc)[:160]}"
