@@ -88,6 +88,8 @@ cudaError_t launch_leaky_backward(const LeakyBwdArgs &a, int layout, cudaStream_
 // when false (shape or alignment not eligible) the caller takes the plain-load kernel.
 cudaError_t launch_lif_forward_tma(const LifFwdArgs &a, int reset_mode, cudaStream_t s, bool *used);
 cudaError_t launch_lif_backward_tma(const LifBwdArgs &a, int reset_mode, int surr_kind, cudaStream_t s, bool *used);
+// [N,T] layout forward through 2-D TMA boxes (T % 4 == 0, T >= 64, 16-byte aligned tensors).
+cudaError_t launch_lif_forward_nt_tma(const LifFwdArgs &a, int reset_mode, cudaStream_t s, bool *used);
 cudaError_t launch_leaky_forward_tma(const LeakyFwdArgs &a, cudaStream_t s, bool *used);
 cudaError_t launch_leaky_backward_tma(const LeakyBwdArgs &a, cudaStream_t s, bool *used);
 // Time-parallel leaky integrator (time-major layout): the time axis is cut into segments that

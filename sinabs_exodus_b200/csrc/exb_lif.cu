@@ -275,6 +275,11 @@ cudaError_t launch_lif_forward(const LifFwdArgs &a, int layout, int reset_mode, 
         cudaError_t e = launch_lif_forward_tma(a, reset_mode, s, &used);
         if (e != cudaSuccess || used) return e;
     }
+    if (layout == EXB_LAYOUT_NT && tma_enabled()) {
+        bool used = false;
+        cudaError_t e = launch_lif_forward_nt_tma(a, reset_mode, s, &used);
+        if (e != cudaSuccess || used) return e;
+    }
     return reset_mode == EXB_RESET_SUBTRACT ? launch_fwd_t<EXB_RESET_SUBTRACT>(a, layout, s)
                                             : launch_fwd_t<EXB_RESET_TO_VALUE>(a, layout, s);
 }

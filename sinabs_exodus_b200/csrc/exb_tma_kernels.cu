@@ -273,6 +273,7 @@ leaky_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LeakyBwdArgs A,
 
 }  // namespace exb
 #include "exb_leaky_scan.cuh"
+#include "exb_lif_nt_tma.cuh"
 namespace exb {
 
 template <int RESET, int NW, int V, bool UNI>
