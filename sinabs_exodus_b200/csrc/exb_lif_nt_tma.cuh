@@ -1,29 +1,36 @@
 // [N,T] layout, TMA-staged forward spike scan.
 //
 // The [N,T] layout (the reference's: one row per neuron, time contiguous) asks each neuron's thread
-// for consecutive time steps of its own row.  The cp.async variant (exb_lif_nt.cuh) moves 128-byte
-// pieces per row and chunk; pieces that short cost DRAM efficiency (a plain copy with that pattern
-// stays below 5 TB/s).  Here a CTA owns 128 rows and walks time in chunks of 64 steps: 256 bytes per
-// row and chunk, moved by TMA as 2-D boxes of [32 time steps x 32 rows] with the 128-byte swizzle, which
-// is exactly the bank-conflict-free tile the lanes want (granule g of row r at position g ^ (r & 7)).
+// for consecutive time steps of its own row.  Here a CTA owns 128 rows and walks time in chunks of 32 (or
+// 64) steps, moved by TMA as 2-D boxes of [32 time steps x 32 rows] with the 128-byte swizzle, which is
+// exactly the bank-conflict-free tile the lanes want (granule g of row r at position g ^ (r & 7)).
 // A producer warp streams the input boxes through a ring of stages (mbarriers, bounded waits); the four
 // consumer warps -- lane = row -- run the recurrence over the 64 steps of a stage, overwrite the stage
 // with the membrane potential and fill a spike tile beside it, and hand both to TMA stores (bulk async
 // group), which clip at the tensor's edges.  A row need not start on any boundary: chunk boundaries are
 // at fixed time steps, the hardware splits the boxes into sectors.
 //
-// Needs T % 4 == 0 (a row pitch that is a multiple of 16 bytes), 16-byte aligned tensors and T >= 64;
-// anything else takes the cp.async variants.  Included by exb_tma_kernels.cu (shares its status word).
+// Chunk boundaries are at fixed time steps for all rows, so this only pays when every row starts on a
+// 128-byte line (T % 32 == 0 and 128-byte aligned tensors): then each box row is one whole line.  Measured
+// on 1 183 744 rows: T = 320: 5.96 TB/s against 5.36 for the cp.async variant; T = 300 (rows start at any
+// multiple of 16 bytes, every piece ends in partial sectors): 4.12 against 4.47 -- those shapes keep the
+// cp.async variant, whose chunks follow each row's own lines.  Stages of 32 steps, four of them (80 KB per
+// CTA, two CTAs per SM) measured best: 64 steps x 2 stages 5.81 TB/s, 32 x 6 (one CTA per SM) 3.75.
+// Included by exb_tma_kernels.cu (shares its status word).
 #pragma once
 
 namespace exb {
 
 constexpr int NTT_WARPS = 4;           // consumer warps per CTA
 constexpr int NTT_ROWS = NTT_WARPS * 32;   // rows per CTA (lane = row)
-constexpr int NTT_TC = 64;             // time steps per stage
 constexpr int NTT_BOX_T = 32;          // time steps per box (128 bytes: the swizzle span)
 constexpr int NTT_TILE = 32 * NTT_BOX_T;               // floats of one [32 rows x 32 steps] box
-constexpr int NTT_STAGE = NTT_WARPS * (NTT_TC / NTT_BOX_T) * NTT_TILE;   // floats of one stage (8 boxes, 32 KB)
+// TC: time steps per stage (32 or 64); a stage holds NTT_WARPS * TC/32 boxes (16 or 32 KB)
+template <int TC>
+struct NttGeom {
+    static constexpr int BOXES_T = TC / NTT_BOX_T;
+    static constexpr int STAGE = NTT_WARPS * BOXES_T * NTT_TILE;
+};
 
 struct NttMaps {
     CUtensorMap in, spikes, v_mem;
@@ -50,10 +57,11 @@ __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bu
 // makes this thread's shared-memory writes visible to the async (TMA) proxy
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-template <int RESET>
-__global__ void __launch_bounds__((NTT_WARPS + 1) * 32, 1)
+template <int RESET, int NTT_TC>
+__global__ void __launch_bounds__((NTT_WARPS + 1) * 32, 2)
 lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, const int nstages)
 {
+    constexpr int NTT_STAGE = NttGeom<NTT_TC>::STAGE;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the swizzle works on 1 KB atoms: every box must start on one
     float *stages = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
@@ -66,7 +74,7 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
     const int T = (int)A.T;
     const int64_t n0 = (int64_t)blockIdx.x * NTT_ROWS;
     const int nchunks = (T + NTT_TC - 1) / NTT_TC;
-    constexpr int BOXES_T = NTT_TC / NTT_BOX_T;      // 2
+    constexpr int BOXES_T = NttGeom<NTT_TC>::BOXES_T;
 
     if (warp == NTT_WARPS) {
         if (lane == 0) {
@@ -169,8 +177,8 @@ static bool make_nt_tensor_map(CUtensorMap *map, const float *base, int64_t N, i
 {
     PFN_cuTensorMapEncodeTiled enc = get_encode_fn();
     if (!enc || !base) return false;
-    if ((reinterpret_cast<uintptr_t>(base) & 15u) || (T % 4) || T < NTT_TC || N <= 0) return false;
-    if (T > (1ll << 31) - NTT_TC || N > (1ll << 31) - NTT_ROWS) return false;
+    if ((reinterpret_cast<uintptr_t>(base) & 127u) || (T % 32) || T < 64 || N <= 0) return false;
+    if (T > (1ll << 31) - 64 || N > (1ll << 31) - NTT_ROWS) return false;
     cuuint64_t gdim[2] = {(cuuint64_t)T, (cuuint64_t)N};
     cuuint64_t gstr[1] = {(cuuint64_t)T * 4u};
     cuuint32_t box[2] = {(cuuint32_t)NTT_BOX_T, 32u};
@@ -194,10 +202,14 @@ cudaError_t launch_lif_forward_nt_tma(const LifFwdArgs &a, int reset_mode, cudaS
     const int64_t ctas = (N + NTT_ROWS - 1) / NTT_ROWS;
     if (ctas > 0x7fffffffll) return cudaSuccess;
     static const int env_st = env_int("EXB_NT_TMA_STAGES", 0);
-    const int nstages = (env_st >= 2 && env_st <= 5) ? env_st : 4;
-    const size_t smem = (size_t)(nstages + 1) * NTT_STAGE * sizeof(float) + sizeof(Ring) + 1024 + 128;
-    auto kern = reset_mode == EXB_RESET_SUBTRACT ? lif_fwd_nt_tma_kernel<EXB_RESET_SUBTRACT>
-                                                 : lif_fwd_nt_tma_kernel<EXB_RESET_TO_VALUE>;
+    static const int env_tc = env_int("EXB_NT_TMA_TC", 0);
+    const int tc = (env_tc == 64) ? 64 : 32;
+    const int nstages = (env_st >= 2 && env_st <= 6) ? env_st : (tc == 32 ? 4 : 2);
+    const size_t stage_bytes = (size_t)(tc == 32 ? NttGeom<32>::STAGE : NttGeom<64>::STAGE) * sizeof(float);
+    const size_t smem = (size_t)(nstages + 1) * stage_bytes + sizeof(Ring) + 1024 + 128;
+    const bool sub = reset_mode == EXB_RESET_SUBTRACT;
+    auto kern = tc == 32 ? (sub ? lif_fwd_nt_tma_kernel<EXB_RESET_SUBTRACT, 32> : lif_fwd_nt_tma_kernel<EXB_RESET_TO_VALUE, 32>)
+                         : (sub ? lif_fwd_nt_tma_kernel<EXB_RESET_SUBTRACT, 64> : lif_fwd_nt_tma_kernel<EXB_RESET_TO_VALUE, 64>);
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
     kern<<<(unsigned)ctas, (NTT_WARPS + 1) * 32, smem, s>>>(maps, a, nstages);

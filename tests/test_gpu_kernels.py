@@ -52,6 +52,27 @@ def test_lif_forward_bit_exact(layout, B, T, M, mode):
         np.testing.assert_allclose(v_post, want_post, rtol=1e-6, atol=1e-6)
 
 
+@pytest.mark.parametrize("N,T", [(333, 96), (128, 64), (1000, 160), (31, 4000)])
+@pytest.mark.parametrize("reset_mode", [0, 1])
+def test_lif_forward_nt_line_aligned_rows(N, T, reset_mode):
+    """[N,T] layout with T % 32 == 0: every row starts on a 128-byte line, which is the shape the TMA-staged [N,T]
+    forward takes (2-D boxes, TMA stores that clip at the tensor's edges; rows and time steps that do not fill the
+    last boxes).  Bit-exact against the checker, for both reset modes."""
+    from tests import _gpu
+    from sinabs_exodus_b200 import _lib
+    for clamp, max_spikes in ((True, None), (False, 1)):
+        cs = _tile_case(7 + N + T, 1, T, N, 2, clamp=clamp)
+        if reset_mode == 1:
+            cs["subtract"] = (0.25 * cs["theta"]).astype(np.float32)
+        s_ref, v_ref = orc.lif_forward_ext(cs["inp"], cs["v_init"], cs["alpha"], cs["subtract"], cs["theta"],
+                                           cs["theta_low"], max_spikes, reset_to_value=bool(reset_mode))
+        s, v, v_post, count = _gpu.lif_forward(cs, 1, N, _lib.LAYOUT_NT, 2, max_spikes, reset_mode=reset_mode)
+        np.testing.assert_array_equal(v, v_ref)
+        np.testing.assert_array_equal(s, s_ref)
+        assert count == int(s_ref.sum())
+        assert s_ref.sum() > 0
+
+
 def test_lif_forward_defaults_and_strong_input():
     """subtract omitted (= threshold), no v_init, many spikes per step."""
     from tests import _gpu
