@@ -167,8 +167,9 @@ static bool make_btm_tensor_map(CUtensorMap *map, const float *base, int64_t B, 
 // 512-byte rows reach 6.1 TB/s, which costs more than the extra CTAs gain.  A middle shape (256
 // neurons, 2 per thread) was measured on the fused synapse kernels: 14 % fewer instructions in the
 // backward but half the warps, and slower overall.  The pipeline shape
-// (time steps per stage, stages) keeps one stage at about 8-16 KB.  EXB_TMA_TC / EXB_TMA_STAGES
-// in the environment override it (tuning aid).
+// (time steps per stage, stages) keeps one stage at about 8-16 KB (the wide spiking forward on large grids
+// takes longer stages, see run_lif_fwd).  EXB_TMA_TC / EXB_TMA_STAGES in the environment override it for every
+// kernel, EXB_LIF_FWD_TC / EXB_LIF_FWD_STAGES for the spiking forward alone (tuning aids).
 static bool use_wide(int64_t B, int64_t M)
 {
     const int64_t wide_tiles = B * ((M + 511) / 512);
