@@ -209,14 +209,19 @@ class KernelTimer:
     NAMES = ("lif_forward", "lif_backward", "leaky_forward", "leaky_backward", "leaky_forward_scan",
              "leaky_backward_scan", "lif_syn_forward", "lif_syn_backward")
 
+    COUNTED = ("acc_finish", "allreduce_oneshot")     # small kernels of the library: counted, not timed
+
     def __init__(self):
         from sinabs_exodus_b200 import _lib
         self.lib = _lib
-        self.orig = {n: getattr(_lib, n) for n in self.NAMES}
+        self.orig = {n: getattr(_lib, n) for n in self.NAMES + self.COUNTED}
         self.events = {n: [] for n in self.NAMES}
+        self.counted = 0
         self.enabled = False
         for n in self.NAMES:
             setattr(_lib, n, self._wrap(n))
+        for n in self.COUNTED:
+            setattr(_lib, n, self._count(n))
 
     def _wrap(self, name):
         orig = self.orig[name]
@@ -232,8 +237,17 @@ class KernelTimer:
             return res
         return call
 
+    def _count(self, name):
+        orig = self.orig[name]
+
+        def call(*args, **kwargs):
+            if self.enabled:
+                self.counted += 1
+            return orig(*args, **kwargs)
+        return call
+
     def launches(self):
-        return sum(len(v) for v in self.events.values())
+        return sum(len(v) for v in self.events.values()) + self.counted
 
     def summary(self):
         out = {}
@@ -245,6 +259,7 @@ class KernelTimer:
 
     def reset(self):
         self.events = {n: [] for n in self.NAMES}
+        self.counted = 0
 
 
 # --------------------------------------------------------------------------
