@@ -1,52 +1,45 @@
 // [N,T] layout, TMA-staged forward spike scan.
 //
 // The [N,T] layout (the reference's: one row per neuron, time contiguous) asks each neuron's thread
-// for consecutive time steps of its own row.  Here a CTA owns 128 rows and walks time in chunks of 32 (or
-// 64) steps, moved by TMA as 2-D boxes of [32 time steps x 32 rows] with the 128-byte swizzle, which is
-// exactly the bank-conflict-free tile the lanes want (granule g of row r at position g ^ (r & 7)).
+// for consecutive time steps of its own row.  Here a CTA owns 128 rows and walks time in chunks of 32
+// steps, moved by TMA as boxes of 128-byte row pieces with the 128-byte swizzle, which is exactly the
+// bank-conflict-free tile the threads want (granule g of shared-memory row s at position g ^ (s & 7)).
 // A producer warp streams the input boxes through a ring of stages (mbarriers, bounded waits); the four
-// consumer warps -- lane = row -- run the recurrence over the 64 steps of a stage, overwrite the stage
-// with the membrane potential and fill a spike tile beside it, and hand both to TMA stores (bulk async
-// group), which clip at the tensor's edges.  A row need not start on any boundary: chunk boundaries are
-// at fixed time steps, the hardware splits the boxes into sectors.
+// consumer warps -- one thread per row -- run the recurrence over the 32 steps of a stage, overwrite the
+// stage with the membrane potential and fill a spike tile beside it, and hand both to TMA stores (bulk
+// async group), which clip at the end of a row.
 //
-// Chunk boundaries are at fixed time steps for all rows, so this only pays when every row starts on a
-// 128-byte line (T % 32 == 0 and 128-byte aligned tensors): then each box row is one whole line.  Measured
-// on 1 183 744 rows: T = 320: 5.96 TB/s against 5.36 for the cp.async variant; T = 300 (rows start at any
-// multiple of 16 bytes, every piece ends in partial sectors): 4.12 against 4.47 -- those shapes keep the
-// cp.async variant, whose chunks follow each row's own lines.  Stages of 32 steps, four of them (80 KB per
-// CTA, two CTAs per SM) measured best: 64 steps x 2 stages 5.81 TB/s, 32 x 6 (one CTA per SM) 3.75.
+// Row classes.  A box row should be one whole 128-byte line of global memory, or every piece ends in
+// partial sectors (measured at T = 300 with boxes cut at fixed time steps: 4.12 TB/s against 4.47 for the
+// cp.async variant, whose chunks follow each row's own lines).  Row n starts n*T floats into the tensor,
+// so its position inside a line repeats with period p = 32 / gcd(T mod 32, 32) rows (p <= 8 when
+// T % 4 == 0).  The tensor is therefore described to TMA as [N/p][p][T]: a box of [32 steps x 1 class x
+// RB rows] takes rows of ONE class j (rows j, j+p, j+2p, ...), which all start at the same position a_j
+// inside their lines, and is placed at time coordinate 32k - a_j: every box row is then one line.  The
+// classes of a CTA are at different time steps inside a chunk; that does not matter, a row's recurrence
+// is its own.  A load may start at a negative time coordinate (the fill is ignored), a store may not: the
+// first chunk of a class with a_j > 0 is stored by the threads themselves.  T % 32 == 0 is the case p = 1.
+//
+// Stages of 32 steps, four of them (80 KB per CTA, two CTAs per SM) measured best at T = 320: 5.96 TB/s
+// (cp.async variant 5.36); 64 steps x 2 stages 5.81, 32 x 6 (one CTA per SM) 3.75.
 // Included by exb_tma_kernels.cu (shares its status word).
 #pragma once
 
 namespace exb {
 
-constexpr int NTT_WARPS = 4;           // consumer warps per CTA
-constexpr int NTT_ROWS = NTT_WARPS * 32;   // rows per CTA (lane = row)
-constexpr int NTT_BOX_T = 32;          // time steps per box (128 bytes: the swizzle span)
-constexpr int NTT_TILE = 32 * NTT_BOX_T;               // floats of one [32 rows x 32 steps] box
-// TC: time steps per stage (32 or 64); a stage holds NTT_WARPS * TC/32 boxes (16 or 32 KB)
-template <int TC>
-struct NttGeom {
-    static constexpr int BOXES_T = TC / NTT_BOX_T;
-    static constexpr int STAGE = NTT_WARPS * BOXES_T * NTT_TILE;
-};
+constexpr int NTT_WARPS = 4;               // consumer warps per CTA
+constexpr int NTT_ROWS = NTT_WARPS * 32;   // rows per CTA (one thread per row)
+constexpr int NTT_BOX_T = 32;              // time steps per box (128 bytes: the swizzle span)
+constexpr int NTT_STAGE = NTT_ROWS * NTT_BOX_T;   // floats of one stage: 128 rows x 32 steps (16 KB)
 
 struct NttMaps {
     CUtensorMap in, spikes, v_mem;
 };
 
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar)
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, int x, int y, int z, uint32_t src)
 {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
-                 : "memory");
-}
-
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, uint32_t src)
-{
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(src)
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(src)
                  : "memory");
 }
 
@@ -57,11 +50,14 @@ __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bu
 // makes this thread's shared-memory writes visible to the async (TMA) proxy
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-template <int RESET, int NTT_TC>
+// lp: log2 of the number of row classes p; a_base: position (floats) of row 0 inside its 128-byte line,
+// the same for the three tensors.  Shared-memory row s of a stage holds row n0 + j + p*i with
+// j = s / R, i = s % R, R = 128 / p: the boxes of one class lie one after the other.
+template <int RESET>
 __global__ void __launch_bounds__((NTT_WARPS + 1) * 32, 2)
-lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, const int nstages)
+lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, const int nstages, const int lp,
+                      const int a_base)
 {
-    constexpr int NTT_STAGE = NttGeom<NTT_TC>::STAGE;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the swizzle works on 1 KB atoms: every box must start on one
     float *stages = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
@@ -73,8 +69,15 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
     const int64_t N = A.B * A.M;
     const int T = (int)A.T;
     const int64_t n0 = (int64_t)blockIdx.x * NTT_ROWS;
-    const int nchunks = (T + NTT_TC - 1) / NTT_TC;
-    constexpr int BOXES_T = NttGeom<NTT_TC>::BOXES_T;
+    const int lR = 7 - lp;                       // log2 of the rows per class in a CTA
+    const int R = 1 << lR;
+    const int RB = R < 32 ? R : 32;              // rows per box
+    const int i0 = (int)(n0 >> lp);              // first row of every class of this CTA, in class rows
+    const int Tm = T & 31;
+    auto line_pos_of = [&](int j) { return (a_base + j * Tm) & 31; };   // n0 * T is a multiple of 32
+    int a_max = 0;
+    for (int j = 0; j < (1 << lp); ++j) a_max = max(a_max, line_pos_of(j));
+    const int nchunks = (T + a_max + NTT_BOX_T - 1) / NTT_BOX_T;
 
     if (warp == NTT_WARPS) {
         if (lane == 0) {
@@ -90,18 +93,21 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
                 const uint32_t bar = smem_u32(&ring->full[s]);
                 mbar_arrive_expect_tx(bar, (uint32_t)(NTT_STAGE * sizeof(float)));
                 float *dst = stages + (size_t)s * NTT_STAGE;
-#pragma unroll
-                for (int w = 0; w < NTT_WARPS; ++w)
-#pragma unroll
-                    for (int j = 0; j < BOXES_T; ++j)      // boxes beyond the tensor are filled with zeros and still count
-                        tma_load_2d(smem_u32(dst + (w * BOXES_T + j) * NTT_TILE), &maps.in, k * NTT_TC + j * NTT_BOX_T,
-                                    (int)(n0 + w * 32), bar);
+                // boxes (or parts) outside the tensor are filled with zeros and still count as bytes
+                for (int s0 = 0; s0 < NTT_ROWS; s0 += RB) {
+                    const int j = s0 >> lR;
+                    tma_load_3d(smem_u32(dst + s0 * NTT_BOX_T), &maps.in, k * NTT_BOX_T - line_pos_of(j), j,
+                                i0 + (s0 & (R - 1)), bar);
+                }
                 if (++s == nstages) { s = 0; par ^= 1u; }
             }
             ring->issued = k;
         }
     } else {
-        const int64_t n = n0 + warp * 32 + lane;
+        const int srow = warp * 32 + lane;                 // this thread's row in the stage
+        const int cls = srow >> lR;
+        const int a = line_pos_of(cls);
+        const int64_t n = n0 + cls + ((int64_t)(srow & (R - 1)) << lp);
         const bool valid = n < N;
         const int64_t nn = valid ? n : 0;
         const int64_t b = nn / A.M, m = nn - b * A.M;
@@ -111,48 +117,54 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
         float af = 0.0f;
         SpikeTotal cnt;
         cnt.c32 = 0u; cnt.c64 = 0ull;
-        const int row_off = lane * NTT_BOX_T;          // this lane's row inside a box
+        const int row_off = lane * NTT_BOX_T;          // this thread's row inside its warp's quarter of a stage
         const int sw = lane & 7;
-        float *my_spk = spk + warp * BOXES_T * NTT_TILE;
+        float *my_spk = spk + warp * 32 * NTT_BOX_T;
         bool ok = true;
         RingPos pos = {0, 0u};
         for (int k = 0; k < nchunks; ++k) {
             if (!wait_chunk(ring, pos)) { ok = false; break; }
-            float *st = stages + (size_t)pos.s * NTT_STAGE + warp * BOXES_T * NTT_TILE;
-            const int t0 = k * NTT_TC;
-            const bool full = t0 + NTT_TC <= T;
+            float *st = stages + (size_t)pos.s * NTT_STAGE + warp * 32 * NTT_BOX_T;
+            const int tb = k * NTT_BOX_T - a;          // time step of this row's column 0
+            const bool full = tb >= 0 && tb + NTT_BOX_T <= T;
+            const bool head = tb < 0;                  // first chunk of a class whose rows start inside a line
+            float *tx = st + row_off;
+            float *ts = my_spk + row_off;
+            float *gs = A.spikes + nn * T + tb;        // used by head chunks only
+            float *gv = A.v_mem + nn * T + tb;
+            // the next granule is read before this one's results are written (no shared-memory round trip per granule)
+            float4 xn = *reinterpret_cast<const float4 *>(tx + ((0 ^ sw) << 2));
 #pragma unroll
-            for (int j = 0; j < BOXES_T; ++j) {
-                float *tx = st + j * NTT_TILE + row_off;
-                float *ts = my_spk + j * NTT_TILE + row_off;
-                // the next granule is read before this one's results are written (no shared-memory round trip per granule)
-                float4 xn = *reinterpret_cast<const float4 *>(tx + ((0 ^ sw) << 2));
+            for (int g = 0; g < 8; ++g) {
+                const int o = (g ^ sw) << 2;
+                const float4 x4 = xn;
+                if (g < 7) xn = *reinterpret_cast<const float4 *>(tx + (((g + 1) ^ sw) << 2));
+                float x[4] = {x4.x, x4.y, x4.z, x4.w};
+                float s4[4], u4[4];
 #pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    const int o = (g ^ sw) << 2;
-                    const float4 x4 = xn;
-                    if (g < 7) xn = *reinterpret_cast<const float4 *>(tx + (((g + 1) ^ sw) << 2));
-                    float x[4] = {x4.x, x4.y, x4.z, x4.w};
-                    float s4[4], u4[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        if (full || t0 + j * NTT_BOX_T + 4 * g + e < T) lif_step<RESET>(v, af, x[e], q, cfg, cnt);
-                        s4[e] = af;
-                        u4[e] = v;
-                    }
+                for (int e = 0; e < 4; ++e) {
+                    if (full || (unsigned)(tb + 4 * g + e) < (unsigned)T) lif_step<RESET>(v, af, x[e], q, cfg, cnt);
+                    s4[e] = af;
+                    u4[e] = v;
+                }
+                if (!head) {
                     *reinterpret_cast<float4 *>(ts + o) = make_float4(s4[0], s4[1], s4[2], s4[3]);
                     *reinterpret_cast<float4 *>(tx + o) = make_float4(u4[0], u4[1], u4[2], u4[3]);
+                } else if (valid && tb + 4 * g >= 0) {   // a is a multiple of 4: a granule is inside the row or outside
+                    __stcs(reinterpret_cast<float4 *>(gs + 4 * g), make_float4(s4[0], s4[1], s4[2], s4[3]));
+                    __stcs(reinterpret_cast<float4 *>(gv + 4 * g), make_float4(u4[0], u4[1], u4[2], u4[3]));
                 }
             }
             fence_async_smem();
             __syncwarp();
             if (lane == 0) {
-#pragma unroll
-                for (int j = 0; j < BOXES_T; ++j) {
-                    const int x = t0 + j * NTT_BOX_T;
-                    if (x < T) {      // a box that starts beyond the end of time has nothing to store
-                        tma_store_2d(&maps.spikes, x, (int)(n0 + warp * 32), smem_u32(my_spk + j * NTT_TILE));
-                        tma_store_2d(&maps.v_mem, x, (int)(n0 + warp * 32), smem_u32(st + j * NTT_TILE));
+                for (int s0 = warp * 32; s0 < warp * 32 + 32; s0 += RB) {
+                    const int j = s0 >> lR;
+                    const int x = k * NTT_BOX_T - line_pos_of(j);
+                    if (x >= 0 && x < T) {      // negative: stored by the threads above; beyond the end: nothing to store
+                        const int off = (s0 - warp * 32) * NTT_BOX_T;
+                        tma_store_3d(&maps.spikes, x, j, i0 + (s0 & (R - 1)), smem_u32(my_spk + off));
+                        tma_store_3d(&maps.v_mem, x, j, i0 + (s0 & (R - 1)), smem_u32(st + off));
                     }
                 }
                 tma_store_commit();
@@ -172,18 +184,31 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
     ring_finish(ring, nstages);
 }
 
-// 2-D map of an [N,T] tensor: x = time (contiguous), y = row; boxes of [32 x 32] with the 128-byte swizzle.
-static bool make_nt_tensor_map(CUtensorMap *map, const float *base, int64_t N, int64_t T)
+// Number of row classes of an [N,T] tensor (see above), as log2; -1 when rows do not start on 16-byte boundaries.
+static int nt_class_log2(int64_t T)
+{
+    if (T % 4) return -1;
+    const int tm = (int)(T & 31);
+    if (tm == 0) return 0;
+    if (tm % 16 == 0) return 1;
+    if (tm % 8 == 0) return 2;
+    return 3;
+}
+
+// 3-D map of an [N,T] tensor seen as [N/p][p][T]: x = time (contiguous), y = class, z = row of the class;
+// boxes of [32 x 1 x rb] with the 128-byte swizzle.
+static bool make_nt_tensor_map(CUtensorMap *map, const float *base, int64_t N, int64_t T, int lp, int rb)
 {
     PFN_cuTensorMapEncodeTiled enc = get_encode_fn();
     if (!enc || !base) return false;
-    if ((reinterpret_cast<uintptr_t>(base) & 127u) || (T % 32) || T < 64 || N <= 0) return false;
+    const int64_t p = 1ll << lp;
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) || (T % 4) || T < 64 || N <= 0 || (N % p)) return false;
     if (T > (1ll << 31) - 64 || N > (1ll << 31) - NTT_ROWS) return false;
-    cuuint64_t gdim[2] = {(cuuint64_t)T, (cuuint64_t)N};
-    cuuint64_t gstr[1] = {(cuuint64_t)T * 4u};
-    cuuint32_t box[2] = {(cuuint32_t)NTT_BOX_T, 32u};
-    cuuint32_t estr[2] = {1u, 1u};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), gdim, gstr, box, estr,
+    cuuint64_t gdim[3] = {(cuuint64_t)T, (cuuint64_t)p, (cuuint64_t)(N / p)};
+    cuuint64_t gstr[2] = {(cuuint64_t)T * 4u, (cuuint64_t)(T * p) * 4u};
+    cuuint32_t box[3] = {(cuuint32_t)NTT_BOX_T, 1u, (cuuint32_t)rb};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(base), gdim, gstr, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
@@ -193,26 +218,32 @@ cudaError_t launch_lif_forward_nt_tma(const LifFwdArgs &a, int reset_mode, cudaS
 {
     *used = false;
     static const bool off = env_int("EXB_DISABLE_NT_TMA", 0) == 1;
+    static const bool classes_off = env_int("EXB_NT_TMA_CLASSES", 1) == 0;    // tuning aid: T % 32 == 0 only
     if (off || a.v_post || a.spikes_u8) return cudaSuccess;
     const int64_t N = a.B * a.M;
+    const int lp = nt_class_log2(a.T);
+    if (lp < 0 || (lp > 0 && classes_off)) return cudaSuccess;
+    // the three tensors must agree on where a row starts inside its line
+    const uintptr_t pos = reinterpret_cast<uintptr_t>(a.input) & 127u;
+    if ((reinterpret_cast<uintptr_t>(a.spikes) & 127u) != pos || (reinterpret_cast<uintptr_t>(a.v_mem) & 127u) != pos)
+        return cudaSuccess;
+    if (classes_off && pos) return cudaSuccess;
+    const int rows_per_class = NTT_ROWS >> lp;
+    const int rb = rows_per_class < 32 ? rows_per_class : 32;
     NttMaps maps;
-    if (!make_nt_tensor_map(&maps.in, a.input, N, a.T) || !make_nt_tensor_map(&maps.spikes, a.spikes, N, a.T) ||
-        !make_nt_tensor_map(&maps.v_mem, a.v_mem, N, a.T))
+    if (!make_nt_tensor_map(&maps.in, a.input, N, a.T, lp, rb) || !make_nt_tensor_map(&maps.spikes, a.spikes, N, a.T, lp, rb) ||
+        !make_nt_tensor_map(&maps.v_mem, a.v_mem, N, a.T, lp, rb))
         return cudaSuccess;
     const int64_t ctas = (N + NTT_ROWS - 1) / NTT_ROWS;
     if (ctas > 0x7fffffffll) return cudaSuccess;
     static const int env_st = env_int("EXB_NT_TMA_STAGES", 0);
-    static const int env_tc = env_int("EXB_NT_TMA_TC", 0);
-    const int tc = (env_tc == 64) ? 64 : 32;
-    const int nstages = (env_st >= 2 && env_st <= 6) ? env_st : (tc == 32 ? 4 : 2);
-    const size_t stage_bytes = (size_t)(tc == 32 ? NttGeom<32>::STAGE : NttGeom<64>::STAGE) * sizeof(float);
-    const size_t smem = (size_t)(nstages + 1) * stage_bytes + sizeof(Ring) + 1024 + 128;
-    const bool sub = reset_mode == EXB_RESET_SUBTRACT;
-    auto kern = tc == 32 ? (sub ? lif_fwd_nt_tma_kernel<EXB_RESET_SUBTRACT, 32> : lif_fwd_nt_tma_kernel<EXB_RESET_TO_VALUE, 32>)
-                         : (sub ? lif_fwd_nt_tma_kernel<EXB_RESET_SUBTRACT, 64> : lif_fwd_nt_tma_kernel<EXB_RESET_TO_VALUE, 64>);
+    const int nstages = (env_st >= 2 && env_st <= 6) ? env_st : 4;
+    const size_t smem = (size_t)(nstages + 1) * NTT_STAGE * sizeof(float) + sizeof(Ring) + 1024 + 128;
+    auto kern = reset_mode == EXB_RESET_SUBTRACT ? lif_fwd_nt_tma_kernel<EXB_RESET_SUBTRACT>
+                                                 : lif_fwd_nt_tma_kernel<EXB_RESET_TO_VALUE>;
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
-    kern<<<(unsigned)ctas, (NTT_WARPS + 1) * 32, smem, s>>>(maps, a, nstages);
+    kern<<<(unsigned)ctas, (NTT_WARPS + 1) * 32, smem, s>>>(maps, a, nstages, lp, (int)(pos >> 2));
     *used = true;
     return cudaPeekAtLastError();
 }

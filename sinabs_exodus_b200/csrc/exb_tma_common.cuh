@@ -224,6 +224,19 @@ static PipeCfg pipe_cfg(int w, int nmaps, int64_t ctas)
     return pc;
 }
 
+// Forward kernels (one tensor in, one or two out) on wide tiles and a grid of many waves: two stages of 32 time
+// steps (128 KB, so one CTA per SM).  These kernels write at least as much as they read, and they are fastest when
+// each SM has 64-128 KB of loads in flight and four to eight warps storing.  Measured on 8 x 500 x 262144, spiking
+// forward alone: 2.055 ms with 4 steps x 4 stages (six CTAs per SM, 192 KB in flight), 2.03 with 8 x 4 (three
+// CTAs), 1.99 with 24 x 2 (two CTAs, 192 KB), 1.937 with 32 x 2, 1.936 with 8 x 4 when padded to one CTA per SM,
+// 2.117 with 4 x 4 padded to one CTA per SM (32 KB in flight: too little); 32 x 300 x 36992: 0.700 -> 0.669 ms.
+// The backward kernels (two or more tensors in, more arithmetic per step) want the opposite: 1.9 -> 3.1 ms with
+// one CTA per SM.  One CTA per SM needs many waves, or the last one leaves SMs idle.
+static void long_stages_for_wide_forward(PipeCfg &pc, int v, int64_t ctas, int64_t T)
+{
+    if (v == 4 && ctas >= 8 * (int64_t)sm_count() && T >= 128) { pc.tc = 32; pc.stages = 2; }
+}
+
 template <typename K>
 static cudaError_t set_smem(K kern, size_t bytes)
 {

@@ -282,14 +282,7 @@ static cudaError_t run_lif_fwd(const LifFwdArgs &a, cudaStream_t s, bool *used)
     using G = TileGeom<NW, V>;
     const int64_t ctas = a.B * ((a.M + G::W - 1) / G::W);
     PipeCfg pc = pipe_cfg(G::W, 1, ctas);
-    // Wide tiles on a grid of many waves: two stages of 32 time steps (128 KB, so one CTA per SM).  This kernel
-    // writes two bytes for every byte it reads, and it is fastest when each SM has 64-128 KB of loads in flight
-    // and four to eight warps storing: measured on 32 x 500 x 262144 (forward alone, 8 batch items) 2.055 ms with
-    // 4 steps x 4 stages (six CTAs per SM, 192 KB in flight), 2.03 with 8 x 4 (three CTAs), 1.99 with 24 x 2
-    // (two CTAs, 192 KB), 1.937 with 32 x 2, 1.936 with 8 x 4 when padded to one CTA per SM, 2.117 with
-    // 4 x 4 padded to one CTA per SM (32 KB in flight: too little); 32 x 300 x 36992: 0.700 -> 0.669 ms.
-    // One CTA per SM needs many waves, or the last one leaves SMs idle.
-    if (V == 4 && ctas >= 8 * (int64_t)sm_count() && a.T >= 128) { pc.tc = 32; pc.stages = 2; }
+    long_stages_for_wide_forward(pc, V, ctas, a.T);
     static const int env_tc = env_int("EXB_LIF_FWD_TC", 0), env_st = env_int("EXB_LIF_FWD_STAGES", 0);
     if (env_tc > 0 && env_tc <= 256) pc.tc = env_tc;
     if (env_st > 1 && env_st <= MAX_STAGES) pc.stages = env_st;
@@ -335,7 +328,9 @@ template <int NW, int V>
 static cudaError_t run_leaky_fwd(const LeakyFwdArgs &a, cudaStream_t s, bool *used)
 {
     using G = TileGeom<NW, V>;
-    const PipeCfg pc = pipe_cfg(G::W, 1, a.B * ((a.M + G::W - 1) / G::W));
+    const int64_t ctas = a.B * ((a.M + G::W - 1) / G::W);
+    PipeCfg pc = pipe_cfg(G::W, 1, ctas);
+    long_stages_for_wide_forward(pc, V, ctas, a.T);      // 8 x 500 x 262144: 1.301 -> 1.262 ms
     TmaMaps maps;
     if (!make_btm_tensor_map(&maps.m[0], a.input, a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
     for (int i = 1; i < 5; ++i) maps.m[i] = maps.m[0];

@@ -49,16 +49,33 @@ def vec(a):
 
 
 def lif_forward(cs, B, M, layout, mode=_lib.PARAM_PER_N, max_spikes=None, reset_mode=_lib.RESET_SUBTRACT,
-                in_scale=None, want_count=True):
+                in_scale=None, want_count=True, elem_offset=0):
+    """``elem_offset`` ([N,T] layout): the three tensors start that many floats into their allocations, which are
+    filled with a sentinel around them; the sentinel must survive the call."""
     N, T = cs["inp"].shape
     x = to_dev(cs["inp"], B, M, layout)
-    spikes = torch.full_like(x, float("nan")); v_mem = torch.full_like(x, float("nan"))
+    guards = []
+    if elem_offset:
+        assert layout == _lib.LAYOUT_NT
+        def carve(fill):
+            buf = torch.full((elem_offset + N * T + 64,), -12345.0, device=DEV)
+            guards.append(buf)
+            view = buf[elem_offset:elem_offset + N * T].view(N, T)
+            view.fill_(fill)
+            return view
+        xs = carve(0.0); xs.copy_(x); x = xs
+        spikes = carve(float("nan")); v_mem = carve(float("nan"))
+    else:
+        spikes = torch.full_like(x, float("nan")); v_mem = torch.full_like(x, float("nan"))
     v_post = torch.empty(N, device=DEV)
     count = torch.zeros(1, dtype=torch.int64, device=DEV) if want_count else None
     _lib.lif_forward(spikes, v_mem, x, vec(cs["v_init"]), param(in_scale, mode, B, M), param(cs["alpha"], mode, B, M),
                      param(cs["subtract"], mode, B, M), param(cs["theta"], mode, B, M),
                      param(cs["theta_low"], mode, B, M), max_spikes, reset_mode, v_post, count, B, T, M, layout)
     torch.cuda.synchronize()
+    for buf in guards:
+        assert bool((buf[:elem_offset] == -12345.0).all()) and bool((buf[elem_offset + N * T:] == -12345.0).all()), \
+            "the kernel wrote outside its tensors"
     return (from_dev(spikes, B, M, layout), from_dev(v_mem, B, M, layout), v_post.cpu().numpy(),
             int(count.item()) if want_count else None)
 

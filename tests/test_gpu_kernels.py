@@ -52,12 +52,19 @@ def test_lif_forward_bit_exact(layout, B, T, M, mode):
         np.testing.assert_allclose(v_post, want_post, rtol=1e-6, atol=1e-6)
 
 
-@pytest.mark.parametrize("N,T", [(333, 96), (128, 64), (1000, 160), (31, 4000)])
+# T % 32 == 0: one row class; 16 / 8 / 4 mod 32: two / four / eight classes; N multiples of the class count that
+# do not fill the last CTA, a single CTA, and many CTAs
+NT_TMA_SHAPES = [(333, 96), (128, 64), (1000, 160), (31, 4000),
+                 (334, 112), (130, 80), (1000, 72), (132, 104), (1000, 300), (136, 68), (8, 100), (2312, 300), (64, 1004)]
+
+
+@pytest.mark.parametrize("N,T", NT_TMA_SHAPES)
 @pytest.mark.parametrize("reset_mode", [0, 1])
-def test_lif_forward_nt_line_aligned_rows(N, T, reset_mode):
-    """[N,T] layout with T % 32 == 0: every row starts on a 128-byte line, which is the shape the TMA-staged [N,T]
-    forward takes (2-D boxes, TMA stores that clip at the tensor's edges; rows and time steps that do not fill the
-    last boxes).  Bit-exact against the checker, for both reset modes."""
+def test_lif_forward_nt_tma_row_classes(N, T, reset_mode):
+    """[N,T] layout with T % 4 == 0, the shapes the TMA-staged [N,T] forward takes: rows are grouped into classes that
+    start at the same position inside a 128-byte line (one class when T % 32 == 0, up to eight otherwise), boxes of a
+    class are placed on its lines, the first partial chunk of a class is stored by the threads, TMA stores clip at the
+    ends of rows and of the tensor.  Bit-exact against the checker, for both reset modes."""
     from tests import _gpu
     from sinabs_exodus_b200 import _lib
     for clamp, max_spikes in ((True, None), (False, 1)):
@@ -71,6 +78,22 @@ def test_lif_forward_nt_line_aligned_rows(N, T, reset_mode):
         np.testing.assert_array_equal(s, s_ref)
         assert count == int(s_ref.sum())
         assert s_ref.sum() > 0
+
+
+@pytest.mark.parametrize("N,T", [(264, 300), (200, 96), (132, 104), (7, 300)])
+@pytest.mark.parametrize("elem_offset", [4, 12, 32, 3])
+def test_lif_forward_nt_tensors_inside_an_allocation(N, T, elem_offset):
+    """The same with tensors that start 16, 48, 128 or 12 bytes into their allocations (a view into a larger buffer):
+    every row then starts somewhere else inside its line; nothing outside the tensors may be written.  (7 rows: not a
+    multiple of the eight classes; 12 bytes: not a 16-byte boundary -- both leave the TMA path.)"""
+    from tests import _gpu
+    from sinabs_exodus_b200 import _lib
+    cs = _tile_case(11 + N + T + elem_offset, 1, T, N, 2, clamp=True)
+    s_ref, v_ref = orc.lif_forward(cs["inp"], cs["v_init"], cs["alpha"], cs["subtract"], cs["theta"], cs["theta_low"], None)
+    s, v, v_post, count = _gpu.lif_forward(cs, 1, N, _lib.LAYOUT_NT, 2, None, elem_offset=elem_offset)
+    np.testing.assert_array_equal(v, v_ref)
+    np.testing.assert_array_equal(s, s_ref)
+    assert count == int(s_ref.sum())
 
 
 def test_lif_forward_defaults_and_strong_input():
