@@ -36,6 +36,20 @@ struct NttMaps {
     CUtensorMap in, spikes, v_mem;
 };
 
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, uint32_t src)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(src)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, int x, int y, int z, uint32_t src)
 {
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
@@ -53,11 +67,15 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 // lp: log2 of the number of row classes p; a_base: position (floats) of row 0 inside its 128-byte line,
 // the same for the three tensors.  Shared-memory row s of a stage holds row n0 + j + p*i with
 // j = s / R, i = s % R, R = 128 / p: the boxes of one class lie one after the other.
-template <int RESET>
+// CLS = false: one class whose rows start on lines (T % 32 == 0, 128-byte aligned tensors); the maps are then
+// plain 2-D [N][T] maps with boxes of [32 x 32] and nothing below depends on lp or a_base.
+template <int RESET, bool CLS>
 __global__ void __launch_bounds__((NTT_WARPS + 1) * 32, 2)
-lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, const int nstages, const int lp,
-                      const int a_base)
+lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, const int nstages, const int lp_arg,
+                      const int a_base_arg)
 {
+    const int lp = CLS ? lp_arg : 0;
+    const int a_base = CLS ? a_base_arg : 0;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the swizzle works on 1 KB atoms: every box must start on one
     float *stages = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
@@ -94,10 +112,16 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
                 mbar_arrive_expect_tx(bar, (uint32_t)(NTT_STAGE * sizeof(float)));
                 float *dst = stages + (size_t)s * NTT_STAGE;
                 // boxes (or parts) outside the tensor are filled with zeros and still count as bytes
-                for (int s0 = 0; s0 < NTT_ROWS; s0 += RB) {
-                    const int j = s0 >> lR;
-                    tma_load_3d(smem_u32(dst + s0 * NTT_BOX_T), &maps.in, k * NTT_BOX_T - line_pos_of(j), j,
-                                i0 + (s0 & (R - 1)), bar);
+                if (CLS) {
+                    for (int s0 = 0; s0 < NTT_ROWS; s0 += RB) {
+                        const int j = s0 >> lR;
+                        tma_load_3d(smem_u32(dst + s0 * NTT_BOX_T), &maps.in, k * NTT_BOX_T - line_pos_of(j), j,
+                                    i0 + (s0 & (R - 1)), bar);
+                    }
+                } else {
+#pragma unroll
+                    for (int w = 0; w < NTT_WARPS; ++w)
+                        tma_load_2d(smem_u32(dst + w * 32 * NTT_BOX_T), &maps.in, k * NTT_BOX_T, (int)(n0 + w * 32), bar);
                 }
                 if (++s == nstages) { s = 0; par ^= 1u; }
             }
@@ -127,45 +151,66 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
             float *st = stages + (size_t)pos.s * NTT_STAGE + warp * 32 * NTT_BOX_T;
             const int tb = k * NTT_BOX_T - a;          // time step of this row's column 0
             const bool full = tb >= 0 && tb + NTT_BOX_T <= T;
-            const bool head = tb < 0;                  // first chunk of a class whose rows start inside a line
             float *tx = st + row_off;
             float *ts = my_spk + row_off;
-            float *gs = A.spikes + nn * T + tb;        // used by head chunks only
-            float *gv = A.v_mem + nn * T + tb;
-            // the next granule is read before this one's results are written (no shared-memory round trip per granule)
-            float4 xn = *reinterpret_cast<const float4 *>(tx + ((0 ^ sw) << 2));
+            if (CLS && tb < 0) {
+                // First chunk of a class whose rows start inside a line: the steps before the row's start are fill,
+                // and a TMA store may not start at a negative coordinate, so the thread stores its own results.
+                // a is a multiple of 4: a granule is inside the row or outside.
+                float *gs = A.spikes + nn * T + tb;
+                float *gv = A.v_mem + nn * T + tb;
+#pragma unroll 1
+                for (int g = a >> 2; g < 8; ++g) {
+                    const float4 x4 = *reinterpret_cast<const float4 *>(tx + ((g ^ sw) << 2));
+                    float x[4] = {x4.x, x4.y, x4.z, x4.w};
+                    float s4[4], u4[4];
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                const int o = (g ^ sw) << 2;
-                const float4 x4 = xn;
-                if (g < 7) xn = *reinterpret_cast<const float4 *>(tx + (((g + 1) ^ sw) << 2));
-                float x[4] = {x4.x, x4.y, x4.z, x4.w};
-                float s4[4], u4[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    if (full || (unsigned)(tb + 4 * g + e) < (unsigned)T) lif_step<RESET>(v, af, x[e], q, cfg, cnt);
-                    s4[e] = af;
-                    u4[e] = v;
+                    for (int e = 0; e < 4; ++e) {
+                        lif_step<RESET>(v, af, x[e], q, cfg, cnt);
+                        s4[e] = af;
+                        u4[e] = v;
+                    }
+                    if (valid) {
+                        __stcs(reinterpret_cast<float4 *>(gs + 4 * g), make_float4(s4[0], s4[1], s4[2], s4[3]));
+                        __stcs(reinterpret_cast<float4 *>(gv + 4 * g), make_float4(u4[0], u4[1], u4[2], u4[3]));
+                    }
                 }
-                if (!head) {
+            } else {
+                // the next granule is read before this one's results are written (no shared-memory round trip per granule)
+                float4 xn = *reinterpret_cast<const float4 *>(tx + ((0 ^ sw) << 2));
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const int o = (g ^ sw) << 2;
+                    const float4 x4 = xn;
+                    if (g < 7) xn = *reinterpret_cast<const float4 *>(tx + (((g + 1) ^ sw) << 2));
+                    float x[4] = {x4.x, x4.y, x4.z, x4.w};
+                    float s4[4], u4[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        if (full || tb + 4 * g + e < T) lif_step<RESET>(v, af, x[e], q, cfg, cnt);
+                        s4[e] = af;
+                        u4[e] = v;
+                    }
                     *reinterpret_cast<float4 *>(ts + o) = make_float4(s4[0], s4[1], s4[2], s4[3]);
                     *reinterpret_cast<float4 *>(tx + o) = make_float4(u4[0], u4[1], u4[2], u4[3]);
-                } else if (valid && tb + 4 * g >= 0) {   // a is a multiple of 4: a granule is inside the row or outside
-                    __stcs(reinterpret_cast<float4 *>(gs + 4 * g), make_float4(s4[0], s4[1], s4[2], s4[3]));
-                    __stcs(reinterpret_cast<float4 *>(gv + 4 * g), make_float4(u4[0], u4[1], u4[2], u4[3]));
                 }
             }
             fence_async_smem();
             __syncwarp();
             if (lane == 0) {
-                for (int s0 = warp * 32; s0 < warp * 32 + 32; s0 += RB) {
-                    const int j = s0 >> lR;
-                    const int x = k * NTT_BOX_T - line_pos_of(j);
-                    if (x >= 0 && x < T) {      // negative: stored by the threads above; beyond the end: nothing to store
-                        const int off = (s0 - warp * 32) * NTT_BOX_T;
-                        tma_store_3d(&maps.spikes, x, j, i0 + (s0 & (R - 1)), smem_u32(my_spk + off));
-                        tma_store_3d(&maps.v_mem, x, j, i0 + (s0 & (R - 1)), smem_u32(st + off));
+                if (CLS) {
+                    for (int s0 = warp * 32; s0 < warp * 32 + 32; s0 += RB) {
+                        const int j = s0 >> lR;
+                        const int x = k * NTT_BOX_T - line_pos_of(j);
+                        if (x >= 0 && x < T) {      // negative: stored by the threads above; beyond the end: nothing to store
+                            const int off = (s0 - warp * 32) * NTT_BOX_T;
+                            tma_store_3d(&maps.spikes, x, j, i0 + (s0 & (R - 1)), smem_u32(my_spk + off));
+                            tma_store_3d(&maps.v_mem, x, j, i0 + (s0 & (R - 1)), smem_u32(st + off));
+                        }
                     }
+                } else {
+                    tma_store_2d(&maps.spikes, k * NTT_BOX_T, (int)(n0 + warp * 32), smem_u32(my_spk));
+                    tma_store_2d(&maps.v_mem, k * NTT_BOX_T, (int)(n0 + warp * 32), smem_u32(st));
                 }
                 tma_store_commit();
                 tma_store_wait_read();      // the stage and the spike tile may be overwritten from here on
@@ -197,13 +242,22 @@ static int nt_class_log2(int64_t T)
 
 // 3-D map of an [N,T] tensor seen as [N/p][p][T]: x = time (contiguous), y = class, z = row of the class;
 // boxes of [32 x 1 x rb] with the 128-byte swizzle.
-static bool make_nt_tensor_map(CUtensorMap *map, const float *base, int64_t N, int64_t T, int lp, int rb)
+static bool make_nt_tensor_map(CUtensorMap *map, const float *base, int64_t N, int64_t T, int lp, int rb, bool classes)
 {
     PFN_cuTensorMapEncodeTiled enc = get_encode_fn();
     if (!enc || !base) return false;
     const int64_t p = 1ll << lp;
     if ((reinterpret_cast<uintptr_t>(base) & 15u) || (T % 4) || T < 64 || N <= 0 || (N % p)) return false;
     if (T > (1ll << 31) - 64 || N > (1ll << 31) - NTT_ROWS) return false;
+    if (!classes) {      // plain [N][T], boxes of [32 x 32]
+        cuuint64_t gdim[2] = {(cuuint64_t)T, (cuuint64_t)N};
+        cuuint64_t gstr[1] = {(cuuint64_t)T * 4u};
+        cuuint32_t box[2] = {(cuuint32_t)NTT_BOX_T, 32u};
+        cuuint32_t estr[2] = {1u, 1u};
+        return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), gdim, gstr, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
     cuuint64_t gdim[3] = {(cuuint64_t)T, (cuuint64_t)p, (cuuint64_t)(N / p)};
     cuuint64_t gstr[2] = {(cuuint64_t)T * 4u, (cuuint64_t)(T * p) * 4u};
     cuuint32_t box[3] = {(cuuint32_t)NTT_BOX_T, 1u, (cuuint32_t)rb};
@@ -218,29 +272,33 @@ cudaError_t launch_lif_forward_nt_tma(const LifFwdArgs &a, int reset_mode, cudaS
 {
     *used = false;
     static const bool off = env_int("EXB_DISABLE_NT_TMA", 0) == 1;
-    static const bool classes_off = env_int("EXB_NT_TMA_CLASSES", 1) == 0;    // tuning aid: T % 32 == 0 only
+    // tuning aids: 0 = only shapes with one class on lines (T % 32 == 0); 2 = the class code for those too
+    static const int classes_mode = env_int("EXB_NT_TMA_CLASSES", 1);
     if (off || a.v_post || a.spikes_u8) return cudaSuccess;
     const int64_t N = a.B * a.M;
     const int lp = nt_class_log2(a.T);
-    if (lp < 0 || (lp > 0 && classes_off)) return cudaSuccess;
+    if (lp < 0) return cudaSuccess;
     // the three tensors must agree on where a row starts inside its line
     const uintptr_t pos = reinterpret_cast<uintptr_t>(a.input) & 127u;
     if ((reinterpret_cast<uintptr_t>(a.spikes) & 127u) != pos || (reinterpret_cast<uintptr_t>(a.v_mem) & 127u) != pos)
         return cudaSuccess;
-    if (classes_off && pos) return cudaSuccess;
+    const bool classes = lp > 0 || pos != 0 || classes_mode == 2;
+    if (classes && classes_mode == 0) return cudaSuccess;
     const int rows_per_class = NTT_ROWS >> lp;
     const int rb = rows_per_class < 32 ? rows_per_class : 32;
     NttMaps maps;
-    if (!make_nt_tensor_map(&maps.in, a.input, N, a.T, lp, rb) || !make_nt_tensor_map(&maps.spikes, a.spikes, N, a.T, lp, rb) ||
-        !make_nt_tensor_map(&maps.v_mem, a.v_mem, N, a.T, lp, rb))
+    if (!make_nt_tensor_map(&maps.in, a.input, N, a.T, lp, rb, classes) ||
+        !make_nt_tensor_map(&maps.spikes, a.spikes, N, a.T, lp, rb, classes) ||
+        !make_nt_tensor_map(&maps.v_mem, a.v_mem, N, a.T, lp, rb, classes))
         return cudaSuccess;
     const int64_t ctas = (N + NTT_ROWS - 1) / NTT_ROWS;
     if (ctas > 0x7fffffffll) return cudaSuccess;
     static const int env_st = env_int("EXB_NT_TMA_STAGES", 0);
     const int nstages = (env_st >= 2 && env_st <= 6) ? env_st : 4;
     const size_t smem = (size_t)(nstages + 1) * NTT_STAGE * sizeof(float) + sizeof(Ring) + 1024 + 128;
-    auto kern = reset_mode == EXB_RESET_SUBTRACT ? lif_fwd_nt_tma_kernel<EXB_RESET_SUBTRACT>
-                                                 : lif_fwd_nt_tma_kernel<EXB_RESET_TO_VALUE>;
+    const bool sub = reset_mode == EXB_RESET_SUBTRACT;
+    auto kern = classes ? (sub ? lif_fwd_nt_tma_kernel<EXB_RESET_SUBTRACT, true> : lif_fwd_nt_tma_kernel<EXB_RESET_TO_VALUE, true>)
+                        : (sub ? lif_fwd_nt_tma_kernel<EXB_RESET_SUBTRACT, false> : lif_fwd_nt_tma_kernel<EXB_RESET_TO_VALUE, false>);
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
     kern<<<(unsigned)ctas, (NTT_WARPS + 1) * 32, smem, s>>>(maps, a, nstages, lp, (int)(pos >> 2));
