@@ -64,6 +64,33 @@ __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bu
 // makes this thread's shared-memory writes visible to the async (TMA) proxy
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// Recurrence of one thread's row over the 32 steps of a stage row: reads the input granules of `tx`, leaves the
+// membrane potential there and the spikes in `ts`.  GUARD: the row ends inside this chunk (steps >= T are skipped).
+// The two cases are separate code so that the common one carries no per-step predicate.
+template <int RESET, bool GUARD>
+__device__ __forceinline__ void ntt_chunk(float *tx, float *ts, int sw, int tb, int T, float &v, float &af,
+                                          const Neuron &q, const SpikeCfg &cfg, SpikeTotal &cnt)
+{
+    // the next granule is read before this one's results are written (no shared-memory round trip per granule)
+    float4 xn = *reinterpret_cast<const float4 *>(tx + ((0 ^ sw) << 2));
+#pragma unroll(GUARD ? 1 : 8)
+    for (int g = 0; g < 8; ++g) {
+        const int o = (g ^ sw) << 2;
+        const float4 x4 = xn;
+        if (g < 7) xn = *reinterpret_cast<const float4 *>(tx + (((g + 1) ^ sw) << 2));
+        float x[4] = {x4.x, x4.y, x4.z, x4.w};
+        float s4[4], u4[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (!GUARD || tb + 4 * g + e < T) lif_step<RESET>(v, af, x[e], q, cfg, cnt);
+            s4[e] = af;
+            u4[e] = v;
+        }
+        *reinterpret_cast<float4 *>(ts + o) = make_float4(s4[0], s4[1], s4[2], s4[3]);
+        *reinterpret_cast<float4 *>(tx + o) = make_float4(u4[0], u4[1], u4[2], u4[3]);
+    }
+}
+
 // lp: log2 of the number of row classes p; a_base: position (floats) of row 0 inside its 128-byte line,
 // the same for the three tensors.  Shared-memory row s of a stage holds row n0 + j + p*i with
 // j = s / R, i = s % R, R = 128 / p: the boxes of one class lie one after the other.
@@ -129,9 +156,9 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
         }
     } else {
         const int srow = warp * 32 + lane;                 // this thread's row in the stage
-        const int cls = srow >> lR;
-        const int a = line_pos_of(cls);
-        const int64_t n = n0 + cls + ((int64_t)(srow & (R - 1)) << lp);
+        const int cls = CLS ? srow >> lR : 0;
+        const int a = CLS ? line_pos_of(cls) : 0;
+        const int64_t n = CLS ? n0 + cls + ((int64_t)(srow & (R - 1)) << lp) : n0 + srow;
         const bool valid = n < N;
         const int64_t nn = valid ? n : 0;
         const int64_t b = nn / A.M, m = nn - b * A.M;
@@ -150,7 +177,6 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
             if (!wait_chunk(ring, pos)) { ok = false; break; }
             float *st = stages + (size_t)pos.s * NTT_STAGE + warp * 32 * NTT_BOX_T;
             const int tb = k * NTT_BOX_T - a;          // time step of this row's column 0
-            const bool full = tb >= 0 && tb + NTT_BOX_T <= T;
             float *tx = st + row_off;
             float *ts = my_spk + row_off;
             if (CLS && tb < 0) {
@@ -175,25 +201,10 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
                         __stcs(reinterpret_cast<float4 *>(gv + 4 * g), make_float4(u4[0], u4[1], u4[2], u4[3]));
                     }
                 }
+            } else if (tb + NTT_BOX_T <= T) {
+                ntt_chunk<RESET, false>(tx, ts, sw, tb, T, v, af, q, cfg, cnt);
             } else {
-                // the next granule is read before this one's results are written (no shared-memory round trip per granule)
-                float4 xn = *reinterpret_cast<const float4 *>(tx + ((0 ^ sw) << 2));
-#pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    const int o = (g ^ sw) << 2;
-                    const float4 x4 = xn;
-                    if (g < 7) xn = *reinterpret_cast<const float4 *>(tx + (((g + 1) ^ sw) << 2));
-                    float x[4] = {x4.x, x4.y, x4.z, x4.w};
-                    float s4[4], u4[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        if (full || tb + 4 * g + e < T) lif_step<RESET>(v, af, x[e], q, cfg, cnt);
-                        s4[e] = af;
-                        u4[e] = v;
-                    }
-                    *reinterpret_cast<float4 *>(ts + o) = make_float4(s4[0], s4[1], s4[2], s4[3]);
-                    *reinterpret_cast<float4 *>(tx + o) = make_float4(u4[0], u4[1], u4[2], u4[3]);
-                }
+                ntt_chunk<RESET, true>(tx, ts, sw, tb, T, v, af, q, cfg, cnt);
             }
             fence_async_smem();
             __syncwarp();
