@@ -20,8 +20,11 @@
 // is its own.  A load may start at a negative time coordinate (the fill is ignored), a store may not: the
 // first chunk of a class with a_j > 0 is stored by the threads themselves.  T % 32 == 0 is the case p = 1.
 //
-// Stages of 32 steps, four of them (80 KB per CTA, two CTAs per SM) measured best at T = 320: 5.96 TB/s
-// (cp.async variant 5.36); 64 steps x 2 stages 5.81, 32 x 6 (one CTA per SM) 3.75.
+// Stages of 32 steps, four of them (80 KB per CTA, two CTAs per SM) measured best at T = 320: 5.97 TB/s
+// (cp.async variant 5.36); 64 steps x 2 stages 5.81, 32 x 6 (one CTA per SM) 3.75.  Measured on 1 183 744 rows
+// with classes: T = 304 (two classes) 5.52 TB/s against 5.10 for the cp.async variant, T = 300 (eight classes,
+// 16-row boxes, 11 chunk rounds for 9.4 chunks of data) 4.73 against 4.46; the class code on T = 320 costs 2.6 %
+// against the plain 2-D variant, which is why that one is kept.
 // Included by exb_tma_kernels.cu (shares its status word).
 #pragma once
 
