@@ -13,12 +13,12 @@
 // partial sectors (measured at T = 300 with boxes cut at fixed time steps: 4.12 TB/s against 4.47 for the
 // cp.async variant, whose chunks follow each row's own lines).  Row n starts n*T floats into the tensor,
 // so its position inside a line repeats with period p = 32 / gcd(T mod 32, 32) rows (p <= 8 when
-// T % 4 == 0).  The tensor is therefore described to TMA as [N/p][p][T]: a box of [32 steps x 1 class x
-// RB rows] takes rows of ONE class j (rows j, j+p, j+2p, ...), which all start at the same position a_j
-// inside their lines, and is placed at time coordinate 32k - a_j: every box row is then one line.  The
-// classes of a CTA are at different time steps inside a chunk; that does not matter, a row's recurrence
-// is its own.  A load may start at a negative time coordinate (the fill is ignored), a store may not: the
-// first chunk of a class with a_j > 0 is stored by the threads themselves.  T % 32 == 0 is the case p = 1.
+// T % 4 == 0).  The tensor is therefore described to TMA as [N/p][p][T], and a CTA owns 128 rows of ONE
+// class j (rows j, j+p, j+2p, ...): they all start at the same position a_j inside their lines, a box of
+// [32 steps x 1 class x 32 rows] placed at time coordinate 32k - a_j consists of whole lines, and the CTA
+// needs exactly ceil((T + a_j) / 32) chunks.  A load may start at a negative time coordinate (the fill is
+// ignored), a store may not: the first chunk of a class with a_j > 0 is stored by the warps themselves.
+// T % 32 == 0 is the case p = 1.
 //
 // Stages of 32 steps, four of them (80 KB per CTA, two CTAs per SM) measured best at T = 320: 5.97 TB/s
 // (cp.async variant 5.36); 64 steps x 2 stages 5.81, 32 x 6 (one CTA per SM) 3.75.  Measured on 1 183 744 rows
@@ -94,18 +94,16 @@ __device__ __forceinline__ void ntt_chunk(float *tx, float *ts, int sw, int tb, 
     }
 }
 
-// lp: log2 of the number of row classes p; a_base: position (floats) of row 0 inside its 128-byte line,
-// the same for the three tensors.  Shared-memory row s of a stage holds row n0 + j + p*i with
-// j = s / R, i = s % R, R = 128 / p: the boxes of one class lie one after the other.
-// CLS = false: one class whose rows start on lines (T % 32 == 0, 128-byte aligned tensors); the maps are then
-// plain 2-D [N][T] maps with boxes of [32 x 32] and nothing below depends on lp or a_base.
+// lp: log2 of the number of row classes p; a_base: position (floats) of row 0 inside its 128-byte line, the same
+// for the three tensors.  CLS: a CTA owns 128 rows of ONE class j = blockIdx.x % p (rows j + p*i, i from
+// 128 * (blockIdx.x / p) on): its rows all start `a` floats into their lines, so the whole CTA walks the same time
+// window per chunk and needs exactly ceil((T + a) / 32) chunks.  CLS = false: rows start on lines (T % 32 == 0,
+// 128-byte aligned tensors); the maps are plain 2-D [N][T] maps and a CTA owns 128 consecutive rows.
 template <int RESET, bool CLS>
 __global__ void __launch_bounds__((NTT_WARPS + 1) * 32, 2)
-lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, const int nstages, const int lp_arg,
-                      const int a_base_arg)
+lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, const int nstages, const int lp,
+                      const int a_base)
 {
-    const int lp = CLS ? lp_arg : 0;
-    const int a_base = CLS ? a_base_arg : 0;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the swizzle works on 1 KB atoms: every box must start on one
     float *stages = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
@@ -116,16 +114,11 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t N = A.B * A.M;
     const int T = (int)A.T;
-    const int64_t n0 = (int64_t)blockIdx.x * NTT_ROWS;
-    const int lR = 7 - lp;                       // log2 of the rows per class in a CTA
-    const int R = 1 << lR;
-    const int RB = R < 32 ? R : 32;              // rows per box
-    const int i0 = (int)(n0 >> lp);              // first row of every class of this CTA, in class rows
-    const int Tm = T & 31;
-    auto line_pos_of = [&](int j) { return (a_base + j * Tm) & 31; };   // n0 * T is a multiple of 32
-    int a_max = 0;
-    for (int j = 0; j < (1 << lp); ++j) a_max = max(a_max, line_pos_of(j));
-    const int nchunks = (T + a_max + NTT_BOX_T - 1) / NTT_BOX_T;
+    const int cls = CLS ? (int)(blockIdx.x & ((1u << lp) - 1u)) : 0;        // this CTA's class
+    const int blk = CLS ? (int)(blockIdx.x >> lp) : (int)blockIdx.x;        // its block of 128 rows of that class
+    const int a = CLS ? (a_base + cls * (T & 31)) & 31 : 0;                  // (j + p*i) * T = j * T modulo 32 floats
+    const int r0 = blk * NTT_ROWS;                                           // first row, counted inside the class
+    const int nchunks = (T + a + NTT_BOX_T - 1) / NTT_BOX_T;
 
     if (warp == NTT_WARPS) {
         if (lane == 0) {
@@ -142,26 +135,18 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
                 mbar_arrive_expect_tx(bar, (uint32_t)(NTT_STAGE * sizeof(float)));
                 float *dst = stages + (size_t)s * NTT_STAGE;
                 // boxes (or parts) outside the tensor are filled with zeros and still count as bytes
-                if (CLS) {
-                    for (int s0 = 0; s0 < NTT_ROWS; s0 += RB) {
-                        const int j = s0 >> lR;
-                        tma_load_3d(smem_u32(dst + s0 * NTT_BOX_T), &maps.in, k * NTT_BOX_T - line_pos_of(j), j,
-                                    i0 + (s0 & (R - 1)), bar);
-                    }
-                } else {
 #pragma unroll
-                    for (int w = 0; w < NTT_WARPS; ++w)
-                        tma_load_2d(smem_u32(dst + w * 32 * NTT_BOX_T), &maps.in, k * NTT_BOX_T, (int)(n0 + w * 32), bar);
+                for (int w = 0; w < NTT_WARPS; ++w) {
+                    if (CLS) tma_load_3d(smem_u32(dst + w * 32 * NTT_BOX_T), &maps.in, k * NTT_BOX_T - a, cls, r0 + w * 32, bar);
+                    else tma_load_2d(smem_u32(dst + w * 32 * NTT_BOX_T), &maps.in, k * NTT_BOX_T, r0 + w * 32, bar);
                 }
                 if (++s == nstages) { s = 0; par ^= 1u; }
             }
             ring->issued = k;
         }
     } else {
-        const int srow = warp * 32 + lane;                 // this thread's row in the stage
-        const int cls = CLS ? srow >> lR : 0;
-        const int a = CLS ? line_pos_of(cls) : 0;
-        const int64_t n = CLS ? n0 + cls + ((int64_t)(srow & (R - 1)) << lp) : n0 + srow;
+        const int64_t row = (int64_t)r0 + warp * 32 + lane;            // inside the class
+        const int64_t n = CLS ? cls + (row << lp) : row;
         const bool valid = n < N;
         const int64_t nn = valid ? n : 0;
         const int64_t b = nn / A.M, m = nn - b * A.M;
@@ -179,18 +164,17 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
         for (int k = 0; k < nchunks; ++k) {
             if (!wait_chunk(ring, pos)) { ok = false; break; }
             float *st = stages + (size_t)pos.s * NTT_STAGE + warp * 32 * NTT_BOX_T;
-            const int tb = k * NTT_BOX_T - a;          // time step of this row's column 0
+            const int tb = k * NTT_BOX_T - a;          // time step of column 0 (the same for the whole CTA)
             float *tx = st + row_off;
             float *ts = my_spk + row_off;
-            if (CLS && tb < 0) {
-                // First chunk of a class whose rows start inside a line: the steps before the row's start are fill,
-                // and a TMA store may not start at a negative coordinate, so the thread stores its own results.
-                // a is a multiple of 4: a granule is inside the row or outside.
-                float *gs = A.spikes + nn * T + tb;
-                float *gv = A.v_mem + nn * T + tb;
+            const bool head = CLS && tb < 0;
+            if (head) {
+                // First chunk of a class whose rows start inside a line: the granules before the row's start are
+                // fill (a is a multiple of 4: a granule is inside the row or outside).
 #pragma unroll 1
                 for (int g = a >> 2; g < 8; ++g) {
-                    const float4 x4 = *reinterpret_cast<const float4 *>(tx + ((g ^ sw) << 2));
+                    const int o = (g ^ sw) << 2;
+                    const float4 x4 = *reinterpret_cast<const float4 *>(tx + o);
                     float x[4] = {x4.x, x4.y, x4.z, x4.w};
                     float s4[4], u4[4];
 #pragma unroll
@@ -199,38 +183,55 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
                         s4[e] = af;
                         u4[e] = v;
                     }
-                    if (valid) {
-                        __stcs(reinterpret_cast<float4 *>(gs + 4 * g), make_float4(s4[0], s4[1], s4[2], s4[3]));
-                        __stcs(reinterpret_cast<float4 *>(gv + 4 * g), make_float4(u4[0], u4[1], u4[2], u4[3]));
-                    }
+                    *reinterpret_cast<float4 *>(ts + o) = make_float4(s4[0], s4[1], s4[2], s4[3]);
+                    *reinterpret_cast<float4 *>(tx + o) = make_float4(u4[0], u4[1], u4[2], u4[3]);
                 }
             } else if (tb + NTT_BOX_T <= T) {
                 ntt_chunk<RESET, false>(tx, ts, sw, tb, T, v, af, q, cfg, cnt);
             } else {
                 ntt_chunk<RESET, true>(tx, ts, sw, tb, T, v, af, q, cfg, cnt);
             }
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-                if (CLS) {
-                    for (int s0 = warp * 32; s0 < warp * 32 + 32; s0 += RB) {
-                        const int j = s0 >> lR;
-                        const int x = k * NTT_BOX_T - line_pos_of(j);
-                        if (x >= 0 && x < T) {      // negative: stored by the threads above; beyond the end: nothing to store
-                            const int off = (s0 - warp * 32) * NTT_BOX_T;
-                            tma_store_3d(&maps.spikes, x, j, i0 + (s0 & (R - 1)), smem_u32(my_spk + off));
-                            tma_store_3d(&maps.v_mem, x, j, i0 + (s0 & (R - 1)), smem_u32(st + off));
+            if (head) {
+                // A TMA store may not start at a negative coordinate: the warp stores the granules of this chunk
+                // itself, a quarter-warp per row (lane -> row it*4 + lane/8, granule lane%8).
+                __syncwarp();
+                const int g = lane & 7, q4 = lane >> 3;
+                if (g >= (a >> 2)) {
+#pragma unroll 1
+                    for (int it = 0; it < 8; ++it) {
+                        const int r = it * 4 + q4;
+                        const int64_t rn = (int64_t)r0 + warp * 32 + r;
+                        const int64_t gn = cls + (rn << lp);
+                        if (gn < N) {
+                            const int o = r * NTT_BOX_T + ((g ^ (r & 7)) << 2);
+                            const int64_t go = gn * T + tb + 4 * g;
+                            __stcs(reinterpret_cast<float4 *>(A.spikes + go), *reinterpret_cast<const float4 *>(my_spk + o));
+                            __stcs(reinterpret_cast<float4 *>(A.v_mem + go), *reinterpret_cast<const float4 *>(st + o));
                         }
                     }
-                } else {
-                    tma_store_2d(&maps.spikes, k * NTT_BOX_T, (int)(n0 + warp * 32), smem_u32(my_spk));
-                    tma_store_2d(&maps.v_mem, k * NTT_BOX_T, (int)(n0 + warp * 32), smem_u32(st));
                 }
-                tma_store_commit();
-                tma_store_wait_read();      // the stage and the spike tile may be overwritten from here on
-                mbar_arrive(smem_u32(&ring->empty[pos.s]));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ring->empty[pos.s]));
+            } else {
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    const int x = k * NTT_BOX_T - a;
+                    if (x < T) {      // beyond the end of the rows: nothing to store
+                        if (CLS) {
+                            tma_store_3d(&maps.spikes, x, cls, r0 + warp * 32, smem_u32(my_spk));
+                            tma_store_3d(&maps.v_mem, x, cls, r0 + warp * 32, smem_u32(st));
+                        } else {
+                            tma_store_2d(&maps.spikes, x, r0 + warp * 32, smem_u32(my_spk));
+                            tma_store_2d(&maps.v_mem, x, r0 + warp * 32, smem_u32(st));
+                        }
+                    }
+                    tma_store_commit();
+                    tma_store_wait_read();      // the stage and the spike tile may be overwritten from here on
+                    mbar_arrive(smem_u32(&ring->empty[pos.s]));
+                }
+                __syncwarp();
             }
-            __syncwarp();
             pos.advance(nstages);
         }
         if (lane == 0) tma_store_wait_all();
@@ -298,14 +299,14 @@ cudaError_t launch_lif_forward_nt_tma(const LifFwdArgs &a, int reset_mode, cudaS
         return cudaSuccess;
     const bool classes = lp > 0 || pos != 0 || classes_mode == 2;
     if (classes && classes_mode == 0) return cudaSuccess;
-    const int rows_per_class = NTT_ROWS >> lp;
-    const int rb = rows_per_class < 32 ? rows_per_class : 32;
+    const int rb = 32;
     NttMaps maps;
     if (!make_nt_tensor_map(&maps.in, a.input, N, a.T, lp, rb, classes) ||
         !make_nt_tensor_map(&maps.spikes, a.spikes, N, a.T, lp, rb, classes) ||
         !make_nt_tensor_map(&maps.v_mem, a.v_mem, N, a.T, lp, rb, classes))
         return cudaSuccess;
-    const int64_t ctas = (N + NTT_ROWS - 1) / NTT_ROWS;
+    // one class per CTA: p classes x blocks of 128 rows of a class (the class index varies fastest)
+    const int64_t ctas = classes ? (((N >> lp) + NTT_ROWS - 1) / NTT_ROWS) << lp : (N + NTT_ROWS - 1) / NTT_ROWS;
     if (ctas > 0x7fffffffll) return cudaSuccess;
     static const int env_st = env_int("EXB_NT_TMA_STAGES", 0);
     const int nstages = (env_st >= 2 && env_st <= 6) ? env_st : 4;
