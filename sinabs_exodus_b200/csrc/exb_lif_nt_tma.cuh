@@ -20,11 +20,11 @@
 // ignored), a store may not: the first chunk of a class with a_j > 0 is stored by the warps themselves.
 // T % 32 == 0 is the case p = 1.
 //
-// Stages of 32 steps, four of them (80 KB per CTA, two CTAs per SM) measured best at T = 320: 5.97 TB/s
-// (cp.async variant 5.36); 64 steps x 2 stages 5.81, 32 x 6 (one CTA per SM) 3.75.  Measured on 1 183 744 rows
-// with classes: T = 304 (two classes) 5.52 TB/s against 5.10 for the cp.async variant, T = 300 (eight classes,
-// 16-row boxes, 11 chunk rounds for 9.4 chunks of data) 4.73 against 4.46; the class code on T = 320 costs 2.6 %
-// against the plain 2-D variant, which is why that one is kept.
+// Stages of 32 steps, four of them (80 KB per CTA, two CTAs per SM) measured best at T = 320: 5.95 TB/s
+// (cp.async variant 5.36); 64 steps x 2 stages 5.81, 32 x 6 (one CTA per SM) 3.75.  On 1 183 744 rows:
+// T = 304 (two classes) 5.62 TB/s against 5.10 for the cp.async variant, T = 300 (eight classes) 5.21 against
+// 4.46.  (CTAs that mix the classes -- 16-row boxes, every CTA as many chunks as its latest class -- reached
+// 4.73 at T = 300; plain 2-D boxes for T % 32 == 0 are no faster than this code with one class.)
 // Included by exb_tma_kernels.cu (shares its status word).
 #pragma once
 
@@ -38,20 +38,6 @@ constexpr int NTT_STAGE = NTT_ROWS * NTT_BOX_T;   // floats of one stage: 128 ro
 struct NttMaps {
     CUtensorMap in, spikes, v_mem;
 };
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar)
-{
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
-                 : "memory");
-}
-
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, uint32_t src)
-{
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(src)
-                 : "memory");
-}
 
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, int x, int y, int z, uint32_t src)
 {
@@ -95,11 +81,10 @@ __device__ __forceinline__ void ntt_chunk(float *tx, float *ts, int sw, int tb, 
 }
 
 // lp: log2 of the number of row classes p; a_base: position (floats) of row 0 inside its 128-byte line, the same
-// for the three tensors.  CLS: a CTA owns 128 rows of ONE class j = blockIdx.x % p (rows j + p*i, i from
+// for the three tensors.  A CTA owns 128 rows of ONE class j = blockIdx.x % p (rows j + p*i, i from
 // 128 * (blockIdx.x / p) on): its rows all start `a` floats into their lines, so the whole CTA walks the same time
-// window per chunk and needs exactly ceil((T + a) / 32) chunks.  CLS = false: rows start on lines (T % 32 == 0,
-// 128-byte aligned tensors); the maps are plain 2-D [N][T] maps and a CTA owns 128 consecutive rows.
-template <int RESET, bool CLS>
+// window per chunk and needs exactly ceil((T + a) / 32) chunks.
+template <int RESET>
 __global__ void __launch_bounds__((NTT_WARPS + 1) * 32, 2)
 lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, const int nstages, const int lp,
                       const int a_base)
@@ -114,9 +99,9 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t N = A.B * A.M;
     const int T = (int)A.T;
-    const int cls = CLS ? (int)(blockIdx.x & ((1u << lp) - 1u)) : 0;        // this CTA's class
-    const int blk = CLS ? (int)(blockIdx.x >> lp) : (int)blockIdx.x;        // its block of 128 rows of that class
-    const int a = CLS ? (a_base + cls * (T & 31)) & 31 : 0;                  // (j + p*i) * T = j * T modulo 32 floats
+    const int cls = (int)(blockIdx.x & ((1u << lp) - 1u));        // this CTA's class
+    const int blk = (int)(blockIdx.x >> lp);                      // its block of 128 rows of that class
+    const int a = (a_base + cls * (T & 31)) & 31;                 // (j + p*i) * T = j * T modulo 32 floats
     const int r0 = blk * NTT_ROWS;                                           // first row, counted inside the class
     const int nchunks = (T + a + NTT_BOX_T - 1) / NTT_BOX_T;
 
@@ -136,17 +121,15 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
                 float *dst = stages + (size_t)s * NTT_STAGE;
                 // boxes (or parts) outside the tensor are filled with zeros and still count as bytes
 #pragma unroll
-                for (int w = 0; w < NTT_WARPS; ++w) {
-                    if (CLS) tma_load_3d(smem_u32(dst + w * 32 * NTT_BOX_T), &maps.in, k * NTT_BOX_T - a, cls, r0 + w * 32, bar);
-                    else tma_load_2d(smem_u32(dst + w * 32 * NTT_BOX_T), &maps.in, k * NTT_BOX_T, r0 + w * 32, bar);
-                }
+                for (int w = 0; w < NTT_WARPS; ++w)
+                    tma_load_3d(smem_u32(dst + w * 32 * NTT_BOX_T), &maps.in, k * NTT_BOX_T - a, cls, r0 + w * 32, bar);
                 if (++s == nstages) { s = 0; par ^= 1u; }
             }
             ring->issued = k;
         }
     } else {
         const int64_t row = (int64_t)r0 + warp * 32 + lane;            // inside the class
-        const int64_t n = CLS ? cls + (row << lp) : row;
+        const int64_t n = cls + (row << lp);
         const bool valid = n < N;
         const int64_t nn = valid ? n : 0;
         const int64_t b = nn / A.M, m = nn - b * A.M;
@@ -167,7 +150,7 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
             const int tb = k * NTT_BOX_T - a;          // time step of column 0 (the same for the whole CTA)
             float *tx = st + row_off;
             float *ts = my_spk + row_off;
-            const bool head = CLS && tb < 0;
+            const bool head = tb < 0;
             if (head) {
                 // First chunk of a class whose rows start inside a line: the granules before the row's start are
                 // fill (a is a multiple of 4: a granule is inside the row or outside).
@@ -218,13 +201,8 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
                 if (lane == 0) {
                     const int x = k * NTT_BOX_T - a;
                     if (x < T) {      // beyond the end of the rows: nothing to store
-                        if (CLS) {
-                            tma_store_3d(&maps.spikes, x, cls, r0 + warp * 32, smem_u32(my_spk));
-                            tma_store_3d(&maps.v_mem, x, cls, r0 + warp * 32, smem_u32(st));
-                        } else {
-                            tma_store_2d(&maps.spikes, x, r0 + warp * 32, smem_u32(my_spk));
-                            tma_store_2d(&maps.v_mem, x, r0 + warp * 32, smem_u32(st));
-                        }
+                        tma_store_3d(&maps.spikes, x, cls, r0 + warp * 32, smem_u32(my_spk));
+                        tma_store_3d(&maps.v_mem, x, cls, r0 + warp * 32, smem_u32(st));
                     }
                     tma_store_commit();
                     tma_store_wait_read();      // the stage and the spike tile may be overwritten from here on
@@ -256,26 +234,17 @@ static int nt_class_log2(int64_t T)
 }
 
 // 3-D map of an [N,T] tensor seen as [N/p][p][T]: x = time (contiguous), y = class, z = row of the class;
-// boxes of [32 x 1 x rb] with the 128-byte swizzle.
-static bool make_nt_tensor_map(CUtensorMap *map, const float *base, int64_t N, int64_t T, int lp, int rb, bool classes)
+// boxes of [32 x 1 x 32] with the 128-byte swizzle.
+static bool make_nt_tensor_map(CUtensorMap *map, const float *base, int64_t N, int64_t T, int lp)
 {
     PFN_cuTensorMapEncodeTiled enc = get_encode_fn();
     if (!enc || !base) return false;
     const int64_t p = 1ll << lp;
     if ((reinterpret_cast<uintptr_t>(base) & 15u) || (T % 4) || T < 64 || N <= 0 || (N % p)) return false;
     if (T > (1ll << 31) - 64 || N > (1ll << 31) - NTT_ROWS) return false;
-    if (!classes) {      // plain [N][T], boxes of [32 x 32]
-        cuuint64_t gdim[2] = {(cuuint64_t)T, (cuuint64_t)N};
-        cuuint64_t gstr[1] = {(cuuint64_t)T * 4u};
-        cuuint32_t box[2] = {(cuuint32_t)NTT_BOX_T, 32u};
-        cuuint32_t estr[2] = {1u, 1u};
-        return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), gdim, gstr, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-    }
     cuuint64_t gdim[3] = {(cuuint64_t)T, (cuuint64_t)p, (cuuint64_t)(N / p)};
     cuuint64_t gstr[2] = {(cuuint64_t)T * 4u, (cuuint64_t)(T * p) * 4u};
-    cuuint32_t box[3] = {(cuuint32_t)NTT_BOX_T, 1u, (cuuint32_t)rb};
+    cuuint32_t box[3] = {(cuuint32_t)NTT_BOX_T, 1u, 32u};
     cuuint32_t estr[3] = {1u, 1u, 1u};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(base), gdim, gstr, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -287,8 +256,6 @@ cudaError_t launch_lif_forward_nt_tma(const LifFwdArgs &a, int reset_mode, cudaS
 {
     *used = false;
     static const bool off = env_int("EXB_DISABLE_NT_TMA", 0) == 1;
-    // tuning aids: 0 = only shapes with one class on lines (T % 32 == 0); 2 = the class code for those too
-    static const int classes_mode = env_int("EXB_NT_TMA_CLASSES", 1);
     if (off || a.v_post || a.spikes_u8) return cudaSuccess;
     const int64_t N = a.B * a.M;
     const int lp = nt_class_log2(a.T);
@@ -297,23 +264,18 @@ cudaError_t launch_lif_forward_nt_tma(const LifFwdArgs &a, int reset_mode, cudaS
     const uintptr_t pos = reinterpret_cast<uintptr_t>(a.input) & 127u;
     if ((reinterpret_cast<uintptr_t>(a.spikes) & 127u) != pos || (reinterpret_cast<uintptr_t>(a.v_mem) & 127u) != pos)
         return cudaSuccess;
-    const bool classes = lp > 0 || pos != 0 || classes_mode == 2;
-    if (classes && classes_mode == 0) return cudaSuccess;
-    const int rb = 32;
     NttMaps maps;
-    if (!make_nt_tensor_map(&maps.in, a.input, N, a.T, lp, rb, classes) ||
-        !make_nt_tensor_map(&maps.spikes, a.spikes, N, a.T, lp, rb, classes) ||
-        !make_nt_tensor_map(&maps.v_mem, a.v_mem, N, a.T, lp, rb, classes))
+    if (!make_nt_tensor_map(&maps.in, a.input, N, a.T, lp) || !make_nt_tensor_map(&maps.spikes, a.spikes, N, a.T, lp) ||
+        !make_nt_tensor_map(&maps.v_mem, a.v_mem, N, a.T, lp))
         return cudaSuccess;
     // one class per CTA: p classes x blocks of 128 rows of a class (the class index varies fastest)
-    const int64_t ctas = classes ? (((N >> lp) + NTT_ROWS - 1) / NTT_ROWS) << lp : (N + NTT_ROWS - 1) / NTT_ROWS;
+    const int64_t ctas = (((N >> lp) + NTT_ROWS - 1) / NTT_ROWS) << lp;
     if (ctas > 0x7fffffffll) return cudaSuccess;
     static const int env_st = env_int("EXB_NT_TMA_STAGES", 0);
     const int nstages = (env_st >= 2 && env_st <= 6) ? env_st : 4;
     const size_t smem = (size_t)(nstages + 1) * NTT_STAGE * sizeof(float) + sizeof(Ring) + 1024 + 128;
-    const bool sub = reset_mode == EXB_RESET_SUBTRACT;
-    auto kern = classes ? (sub ? lif_fwd_nt_tma_kernel<EXB_RESET_SUBTRACT, true> : lif_fwd_nt_tma_kernel<EXB_RESET_TO_VALUE, true>)
-                        : (sub ? lif_fwd_nt_tma_kernel<EXB_RESET_SUBTRACT, false> : lif_fwd_nt_tma_kernel<EXB_RESET_TO_VALUE, false>);
+    auto kern = reset_mode == EXB_RESET_SUBTRACT ? lif_fwd_nt_tma_kernel<EXB_RESET_SUBTRACT>
+                                                 : lif_fwd_nt_tma_kernel<EXB_RESET_TO_VALUE>;
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
     kern<<<(unsigned)ctas, (NTT_WARPS + 1) * 32, smem, s>>>(maps, a, nstages, lp, (int)(pos >> 2));
