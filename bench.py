@@ -545,16 +545,26 @@ def measure_other(name: str, timer: KernelTimer, dev, rank: int, world: int, ste
     for _ in range(warmup):
         w.step(world)
     torch.cuda.synchronize()
+    # Step time first, with nothing else on the stream: sub-millisecond steps are bound by the host's launch path, and
+    # the two event records around every kernel of the second pass would add to exactly that.  Such steps are also
+    # timed over more repetitions.
+    small = w.nts < (1 << 28)
+    ksteps = steps
+    if small:
+        steps = max(steps, 50)
+        for _ in range(10):
+            w.step(world)
+    ms = timed_steps(lambda: w.step(world), steps, world, dev)
     timer.reset()
     timer.enabled = True
-    ms = timed_steps(lambda: w.step(world, time_collective=True), steps, world, dev)
+    timed_steps(lambda: w.step(world, time_collective=True), ksteps, world, dev)
     timer.enabled = False
     kernels = timer.summary()
     launches = timer.launches()
     step_bytes = (wl["bytes_fwd"] + wl["bytes_bwd"]) * w.nts
     res = {"workload": f"{name}: {wl['desc']}", "per_gpu_shape": list(wl["shape"]), "steps": steps, "warmup": warmup,
            "ms_per_step": ms / steps, "value": w.nts * world * steps / (ms * 1e-3), "unit": UNIT,
-           "launches_per_step": launches / steps,
+           "launches_per_step": launches / ksteps,
            "step_fraction_of_hbm_roofline": (step_bytes / (ms / steps * 1e-3) / 1e9) / peak,
            "roofline": roofline_of(name, wl["kind"], kernels, w.nts, peak, peak_src)}
     if w.collective_events:
@@ -587,6 +597,17 @@ def measure_other(name: str, timer: KernelTimer, dev, rank: int, world: int, ste
             ex._lib.device_status(dev)
         except Exception as exc:
             res["collective"]["one_shot_unavailable"] = f"{type(exc).__name__}: {str(exc)[:160]}"
+    if name == "c1":
+        # backward in the calling thread: no hand-over to PyTorch's autograd thread
+        prev = torch.autograd.is_multithreading_enabled()
+        torch.autograd.set_multithreading_enabled(False)
+        try:
+            for _ in range(10):
+                w.step(world)
+            sms = timed_steps(lambda: w.step(world), steps, world, dev)
+            res["single_thread_autograd"] = {"ms_per_step": sms / steps, "value": w.nts * world * steps / (sms * 1e-3)}
+        finally:
+            torch.autograd.set_multithreading_enabled(prev)
     if name in ("c1", "c3", "c4") and not (world > 1 and w.tc_params):
         # the same step captured once as a CUDA graph: what is left when the per-step host work is taken out
         try:

@@ -127,8 +127,10 @@ else:
 
         def zero_grad(self, set_to_none: bool = True) -> None:
             # Cut the graph that the states carry from one forward call to the next.
-            for name, buf in list(self.named_buffers()):
-                self.register_buffer(name, buf.detach())
+            bufs = self._buffers      # the layer has no submodules
+            for name, buf in bufs.items():
+                if buf is not None and (buf.grad_fn is not None or buf.requires_grad):
+                    bufs[name] = buf.detach()
             super().zero_grad(set_to_none)
 
         # -- construction arguments -------------------------------------------

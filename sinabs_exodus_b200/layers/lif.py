@@ -163,6 +163,10 @@ class LIF(LIFBase):
         )
         self.decay_early = decay_early
 
+    def _set_state(self, name: str, value: torch.Tensor) -> None:
+        # what ``self.<name> = value`` does for a registered buffer, without nn.Module.__setattr__'s searches
+        self._buffers[name] = value
+
     def reset_states(self, randomize: bool = False, value_ranges=None) -> None:
         """Reset the states to zero (or, with ``randomize``, as the base class does).
 
@@ -174,7 +178,8 @@ class LIF(LIFBase):
         if randomize or not self.is_state_initialised():
             return super().reset_states(randomize=randomize, value_ranges=value_ranges)
         cache = self.__dict__.setdefault("_zero_states", {})
-        for name, buf in list(self.named_buffers(recurse=False)):
+        bufs = self._buffers
+        for name, buf in bufs.items():
             hit = cache.get(name)
             if hit is None or hit[0].shape != buf.shape or hit[0].device != buf.device or hit[0]._version != hit[1] \
                     or (hit[0].is_cuda and torch.cuda.is_current_stream_capturing()):
@@ -183,7 +188,7 @@ class LIF(LIFBase):
                     cache[name] = (z, z._version)
             else:
                 z = hit[0]
-            self.register_buffer(name, z)
+            bufs[name] = z
 
     def _parse_activation_fn(self, spike_fn, reset_fn):
         if spike_fn is None:
@@ -406,8 +411,8 @@ class LIF(LIFBase):
         if not done:
             return None        # shape the byte kernels do not take: the caller converts the float raster
         if has_synapse:
-            self.i_syn = self._unflatten(i_last, (batch,), trailing)
-        self.v_mem = self._unflatten(v_post_last, (batch,), trailing)
+            self._set_state("i_syn", self._unflatten(i_last, (batch,), trailing))
+        self._set_state("v_mem", self._unflatten(v_post_last, (batch,), trailing))
         if keep:
             if i_syn is not None:
                 self.recordings["i_syn"] = self._unflatten(i_syn, tuple(original_shape[:2]), tuple(original_shape[2:]))
@@ -454,14 +459,14 @@ class LIF(LIFBase):
                 lo = torch.as_tensor(self.min_v_mem, dtype=torch.float32, device=dev)
                 if bool((th <= lo).any()):
                     raise ValueError("`threshold` must be greater than `min_v_mem`.")
-        self._validated_key = key
+        self.__dict__["_validated_key"] = key
 
     def forward(self, input_data: torch.Tensor):
         """``input_data``: (batch, time, ...) on a CUDA device.  Returns a tensor of the same shape."""
         x, original_shape = self._prepare_input(input_data)
         batch_size, time_steps, *trailing_dim = original_shape
         trailing = tuple(trailing_dim)
-        self.recordings = dict()
+        self.__dict__["recordings"] = dict()
 
         has_synapse = getattr(self, "alpha_syn" if self.train_alphas else "tau_syn", None) is not None
         if self._spike_dtype == torch.uint8 and self.spike_fn is not None:
@@ -483,14 +488,14 @@ class LIF(LIFBase):
             i_syn = x
         else:
             i_syn, i_last = self._forward_synaptic(x, batch_size, trailing)
-            self.i_syn = self._unflatten(i_last, (batch_size,), trailing)
+            self._set_state("i_syn", self._unflatten(i_last, (batch_size,), trailing))
             if self.record_states:
                 self.recordings["i_syn"] = self._unflatten(i_syn, tuple(original_shape[:2]), tuple(original_shape[2:]))
 
         output, v_rec, v_last, count = self._forward_membrane(i_syn, batch_size, trailing)
         if self.record_states:
             self.recordings["v_mem"] = self._unflatten(v_rec, tuple(original_shape[:2]), tuple(original_shape[2:]))
-        self.v_mem = self._unflatten(v_last, (batch_size,), trailing)
+        self._set_state("v_mem", self._unflatten(v_last, (batch_size,), trailing))
         output_full = self._unflatten(output, tuple(original_shape[:2]), tuple(original_shape[2:]))
         # spike count (int64) or, for the non-spiking layer, the sum of the outputs (float64): both come
         # out of the forward kernel, so the reference's `output.sum() / numel` pass is not needed
@@ -525,8 +530,8 @@ class LIF(LIFBase):
             x, raw_syn, None, self._state_flat(self.i_syn), raw_mem, None,
             self._state_flat(self.v_mem), threshold, subtract, min_v_mem, self.surrogate_grad_fn,
             self.max_num_spikes_per_bin, reset_mode, count, flags, acc)
-        self.i_syn = self._unflatten(i_last, (batch_size,), trailing)
-        self.v_mem = self._unflatten(v_post_last, (batch_size,), trailing)
+        self._set_state("i_syn", self._unflatten(i_last, (batch_size,), trailing))
+        self._set_state("v_mem", self._unflatten(v_post_last, (batch_size,), trailing))
         if self.record_states:
             self.recordings["i_syn"] = self._unflatten(i_syn, tuple(original_shape[:2]), tuple(original_shape[2:]))
             c = threshold if subtract is None else subtract
@@ -550,9 +555,10 @@ class LIF(LIFBase):
     _rate_output = None
 
     def _set_rate_source(self, total: torch.Tensor, numel: int, output: Optional[torch.Tensor] = None) -> None:
-        self._rate_source = (total, max(int(numel), 1))
-        self._rate_value = None
-        self._rate_output = weakref.ref(output) if (output is not None and output.requires_grad) else None
+        d = self.__dict__          # plain attributes: no need for nn.Module.__setattr__
+        d["_rate_source"] = (total, max(int(numel), 1))
+        d["_rate_value"] = None
+        d["_rate_output"] = weakref.ref(output) if (output is not None and output.requires_grad) else None
 
     @property
     def firing_rate(self):
