@@ -810,10 +810,20 @@ def run_ours(args, wl):
         sampler.start()
 
     # ---- timed region: K steps, device-timed, barrier + synchronize on both sides
-    timer.enabled = True
-    ms_total = timed_steps(run_step, args.steps, world, dev)
-    timer.enabled = False
-    launches = timer.launches()
+    if w.nts >= (1 << 28):
+        timer.enabled = True
+        ms_total = timed_steps(run_step, args.steps, world, dev)
+        timer.enabled = False
+        launches = timer.launches()
+    else:
+        # A sub-millisecond step is bound by the host's launch path: the two event records around every kernel
+        # would add to exactly that, so the kernels are timed in a second pass of the same steps and the launch
+        # count of that pass stands for the timed one (the same calls are made).
+        ms_total = timed_steps(run_step, args.steps, world, dev)
+        timer.enabled = True
+        timed_steps(run_step, args.steps, world, dev)
+        timer.enabled = False
+        launches = timer.launches()
     kernels = timer.summary()
     value = w.nts * world * args.steps / (ms_total * 1e-3)
 
