@@ -118,11 +118,12 @@ int exb_device_status(int device, void *stream)
     if (!guard.ok) return fail(EXB_ERR_DEVICE, "exb_device_status: cannot select device %d", device);
     unsigned int code = 0, code2 = 0;
     cudaError_t e = exb::read_device_status((cudaStream_t)stream, &code);
-    unsigned int code3 = 0;
+    unsigned int code3 = 0, code4 = 0;
     if (e == cudaSuccess) e = exb::read_device_status_lif_bwd((cudaStream_t)stream, &code2);
     if (e == cudaSuccess) e = exb::read_device_status_lif_syn((cudaStream_t)stream, &code3);
+    if (e == cudaSuccess) e = exb::read_device_status_lif_nt_bwd((cudaStream_t)stream, &code4);
     if (e != cudaSuccess) return fail(EXB_ERR_LAUNCH, "exb_device_status: %s", cudaGetErrorString(e));
-    if (!code) code = code2 ? code2 : code3;
+    if (!code) code = code2 ? code2 : (code3 ? code3 : code4);
     if (code) return fail(EXB_ERR_TIMEOUT, "a bounded device-side wait ran out (code %u); results of the affected call are incomplete", code);
     return EXB_OK;
 }
@@ -134,6 +135,7 @@ int exb_set_wait_limit(int device, uint32_t polls, int withhold_scan_flags)
     cudaError_t e = exb::set_wait_limit(polls, withhold_scan_flags != 0);
     if (e == cudaSuccess) e = exb::set_wait_limit_lif_bwd(polls);
     if (e == cudaSuccess) e = exb::set_wait_limit_lif_syn(polls);
+    if (e == cudaSuccess) e = exb::set_wait_limit_lif_nt_bwd(polls);
     if (e != cudaSuccess) return fail(EXB_ERR_LAUNCH, "exb_set_wait_limit: %s", cudaGetErrorString(e));
     return EXB_OK;
 }

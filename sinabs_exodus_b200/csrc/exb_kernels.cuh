@@ -88,8 +88,10 @@ cudaError_t launch_leaky_backward(const LeakyBwdArgs &a, int layout, cudaStream_
 // when false (shape or alignment not eligible) the caller takes the plain-load kernel.
 cudaError_t launch_lif_forward_tma(const LifFwdArgs &a, int reset_mode, cudaStream_t s, bool *used);
 cudaError_t launch_lif_backward_tma(const LifBwdArgs &a, int reset_mode, int surr_kind, cudaStream_t s, bool *used);
-// [N,T] layout forward through 2-D TMA boxes (T % 4 == 0, T >= 64, 16-byte aligned tensors).
+// [N,T] layout through TMA boxes of one row class (T % 4 == 0, T >= 64, N a multiple of the class count, tensors
+// at the same 16-byte aligned position inside a 128-byte line).
 cudaError_t launch_lif_forward_nt_tma(const LifFwdArgs &a, int reset_mode, cudaStream_t s, bool *used);
+cudaError_t launch_lif_backward_nt_tma(const LifBwdArgs &a, int reset_mode, int surr_kind, cudaStream_t s, bool *used);
 cudaError_t launch_leaky_forward_tma(const LeakyFwdArgs &a, cudaStream_t s, bool *used);
 cudaError_t launch_leaky_backward_tma(const LeakyBwdArgs &a, cudaStream_t s, bool *used);
 // Time-parallel leaky integrator (time-major layout): the time axis is cut into segments that
@@ -115,7 +117,9 @@ cudaError_t read_device_status(cudaStream_t s, unsigned int *out);
 cudaError_t set_wait_limit(unsigned int polls, bool withhold_scan_flags);
 cudaError_t set_wait_limit_lif_bwd(unsigned int polls);
 cudaError_t set_wait_limit_lif_syn(unsigned int polls);
+cudaError_t set_wait_limit_lif_nt_bwd(unsigned int polls);
 cudaError_t read_device_status_lif_bwd(cudaStream_t s, unsigned int *out);
+cudaError_t read_device_status_lif_nt_bwd(cudaStream_t s, unsigned int *out);
 // EXB_DISABLE_TMA=1 in the environment forces the plain-load kernels (debugging aid).
 bool tma_enabled();
 

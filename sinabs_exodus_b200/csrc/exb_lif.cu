@@ -11,6 +11,7 @@
 // global memory (coalesced along time) and shared memory (read along neurons),
 // so the same per-thread sweep runs on a transposed tile.
 #include "exb_kernels.cuh"
+#include "exb_lif_nt_chunk.cuh"
 
 namespace exb {
 
@@ -25,7 +26,6 @@ namespace exb {
 // row's first element inside its line (in floats), chunk k of that row covers the time steps
 // [32k - a, 32k - a + 32) that fall inside [0, T).  The lanes of a warp own one row each during
 // the recurrence, which is sequential per row anyway, so the rows need not be in step.
-constexpr int TILE = 32;
 constexpr int TSTR = 33;
 constexpr int TILE_FLOATS = TILE * TSTR;
 constexpr int NT_WARPS = 4;
@@ -348,7 +348,12 @@ cudaError_t launch_lif_backward(const LifBwdArgs &a, int layout, int reset_mode,
         cudaError_t e = launch_lif_backward_tma(a, reset_mode, surr_kind, s, &used);
         if (e != cudaSuccess || used) return e;
     }
-    if (a.acc_decay) return cudaErrorNotSupported;      // only the TMA-staged kernels reduce in the kernel
+    if (a.acc_decay) return cudaErrorNotSupported;      // only the time-major TMA-staged kernels reduce in the kernel
+    if (layout == EXB_LAYOUT_NT && tma_enabled()) {
+        bool used = false;
+        cudaError_t e = launch_lif_backward_nt_tma(a, reset_mode, surr_kind, s, &used);
+        if (e != cudaSuccess || used) return e;
+    }
     return reset_mode == EXB_RESET_SUBTRACT ? launch_bwd_surr<EXB_RESET_SUBTRACT>(a, layout, surr_kind, s)
                                             : launch_bwd_surr<EXB_RESET_TO_VALUE>(a, layout, surr_kind, s);
 }

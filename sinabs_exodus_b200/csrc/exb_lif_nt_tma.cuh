@@ -28,30 +28,13 @@
 // Included by exb_tma_kernels.cu (shares its status word).
 #pragma once
 
-namespace exb {
+#include "exb_nt_tma_common.cuh"
 
-constexpr int NTT_WARPS = 4;               // consumer warps per CTA
-constexpr int NTT_ROWS = NTT_WARPS * 32;   // rows per CTA (one thread per row)
-constexpr int NTT_BOX_T = 32;              // time steps per box (128 bytes: the swizzle span)
-constexpr int NTT_STAGE = NTT_ROWS * NTT_BOX_T;   // floats of one stage: 128 rows x 32 steps (16 KB)
+namespace exb {
 
 struct NttMaps {
     CUtensorMap in, spikes, v_mem;
 };
-
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, int x, int y, int z, uint32_t src)
-{
-    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
-                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(src)
-                 : "memory");
-}
-
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// all stores of this thread's groups have finished READING shared memory (the data may still be on its way to DRAM)
-__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-// makes this thread's shared-memory writes visible to the async (TMA) proxy
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // Recurrence of one thread's row over the 32 steps of a stage row: reads the input granules of `tx`, leaves the
 // membrane potential there and the spikes in `ts`.  GUARD: the row ends inside this chunk (steps >= T are skipped).
@@ -220,36 +203,6 @@ lif_fwd_nt_tma_kernel(const __grid_constant__ NttMaps maps, const LifFwdArgs A, 
         }
     }
     ring_finish(ring, nstages);
-}
-
-// Number of row classes of an [N,T] tensor (see above), as log2; -1 when rows do not start on 16-byte boundaries.
-static int nt_class_log2(int64_t T)
-{
-    if (T % 4) return -1;
-    const int tm = (int)(T & 31);
-    if (tm == 0) return 0;
-    if (tm % 16 == 0) return 1;
-    if (tm % 8 == 0) return 2;
-    return 3;
-}
-
-// 3-D map of an [N,T] tensor seen as [N/p][p][T]: x = time (contiguous), y = class, z = row of the class;
-// boxes of [32 x 1 x 32] with the 128-byte swizzle.
-static bool make_nt_tensor_map(CUtensorMap *map, const float *base, int64_t N, int64_t T, int lp)
-{
-    PFN_cuTensorMapEncodeTiled enc = get_encode_fn();
-    if (!enc || !base) return false;
-    const int64_t p = 1ll << lp;
-    if ((reinterpret_cast<uintptr_t>(base) & 15u) || (T % 4) || T < 64 || N <= 0 || (N % p)) return false;
-    if (T > (1ll << 31) - 64 || N > (1ll << 31) - NTT_ROWS) return false;
-    cuuint64_t gdim[3] = {(cuuint64_t)T, (cuuint64_t)p, (cuuint64_t)(N / p)};
-    cuuint64_t gstr[2] = {(cuuint64_t)T * 4u, (cuuint64_t)(T * p) * 4u};
-    cuuint32_t box[3] = {(cuuint32_t)NTT_BOX_T, 1u, 32u};
-    cuuint32_t estr[3] = {1u, 1u, 1u};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(base), gdim, gstr, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
 }
 
 cudaError_t launch_lif_forward_nt_tma(const LifFwdArgs &a, int reset_mode, cudaStream_t s, bool *used)

@@ -156,6 +156,72 @@ def test_lif_backward_parity(layout, B, T, M, surr_idx):
         assert ga_b is None
 
 
+@pytest.mark.parametrize("N,T", [(264, 300), (200, 96), (136, 104), (1000, 72), (8, 100), (64, 1004), (128, 64)])
+@pytest.mark.parametrize("surr_idx", [0, 1, 2, 3])
+def test_lif_backward_nt_tma_row_classes(N, T, surr_idx):
+    """[N,T] layout with T % 4 == 0, the shapes the TMA-staged [N,T] backward takes (one, two, four or eight row
+    classes; rows that do not fill the last CTA of a class; a first chunk that the warps store themselves): input,
+    alpha and initial-state gradients against the float64 form and the float32 restatement of the reference loops,
+    with and without a gradient on v_mem, with and without the alpha gradient."""
+    from tests import _gpu
+    name, kind, p0, p1, fn = _surrogates()[surr_idx]
+    for clamp, max_spikes, with_gv in ((True, None, True), (False, 2, False)):
+        cs = lif_case(500 + T + N, N, T, clamp=clamp)
+        s, v = orc.lif_forward(cs["inp"], cs["v_init"], cs["alpha"], cs["subtract"], cs["theta"], cs["theta_low"],
+                               max_spikes)
+        rng = np.random.default_rng(T * 5 + N)
+        go = rng.standard_normal((N, T)).astype(np.float32)
+        gv = (0.3 * rng.standard_normal((N, T))).astype(np.float32) if with_gv else None
+        gi32, ga32, g032 = orc.integrate_and_fire_backward(
+            go, gv if with_gv else np.zeros_like(go), v, s, cs["v_init"], cs["alpha"], cs["subtract"], cs["theta"],
+            cs["theta_low"], fn, True)
+        surr = fn(v, cs["theta"][:, None])
+        nc = (v > cs["theta_low"][:, None]).astype(np.float32) if clamp else np.ones_like(v)
+        g = (surr * go).astype(np.float32) + (gv if with_gv else 0)
+        vpost = (v - cs["subtract"][:, None] * s).astype(np.float32)
+        gi64, ga64 = orc.lif_backward_f64(g, surr, nc, cs["alpha"], cs["subtract"], vpost, cs["v_init"])
+        gi, ga, g0, _ = _gpu.lif_backward(cs, v, go, 1, N, 0, gv=gv, surr=surr if kind == 0 else None,
+                                          kind=kind, p0=p0, p1=p1, max_spikes=max_spikes, want_alpha=True)
+        assert np.isfinite(gi).all()
+        assert rel_err(gi, gi64) < TOL, name
+        assert rel_err(gi, gi32) < 2 * TOL, name
+        assert rel_err(ga, ga64) < TOL, name
+        assert rel_err(g0, cs["alpha"].astype(np.float64) * gi64[:, 0]) < TOL, name
+        gi_b, ga_b, _, _ = _gpu.lif_backward(cs, v, go, 1, N, 0, gv=gv, surr=surr if kind == 0 else None,
+                                             kind=kind, p0=p0, p1=p1, max_spikes=max_spikes, want_alpha=False)
+        np.testing.assert_array_equal(gi_b, gi)
+        assert ga_b is None
+
+
+@pytest.mark.parametrize("N,T", [(264, 300), (136, 104), (128, 64)])
+def test_lif_backward_nt_tma_scale_and_state_gradient(N, T):
+    """The same kernels with a fused input scale (its gradient from the input tensor and rebuilt from v_mem) and a
+    gradient arriving on the post-reset last state."""
+    from tests import _gpu
+    from sinabs_exodus_b200 import _lib
+    cs = lif_case(79 + N, N, T, clamp=True)
+    cs["alpha"] = np.minimum(cs["alpha"], np.float32(0.97))
+    scale = (1.0 - cs["alpha"]).astype(np.float32)
+    scaled = dict(cs, inp=(scale[:, None] * cs["inp"]).astype(np.float32))
+    s_ref, v_ref = orc.lif_forward(scaled["inp"], cs["v_init"], cs["alpha"], cs["subtract"], cs["theta"], cs["theta_low"])
+    rng = np.random.default_rng(9 + T)
+    go = rng.standard_normal((N, T)).astype(np.float32)
+    G = rng.standard_normal(N).astype(np.float32)
+    fn = lambda vv, th: orc.surrogate_single_exponential(vv, th)
+    go2 = go.copy(); go2[:, -1] -= cs["subtract"] * G
+    gv2 = np.zeros_like(go); gv2[:, -1] += G
+    surr = fn(v_ref, cs["theta"][:, None])
+    nc = (v_ref > cs["theta_low"][:, None]).astype(np.float32)
+    g = (surr * go2).astype(np.float32) + gv2
+    R64, _ = orc.lif_backward_f64(g, surr, nc, cs["alpha"], cs["subtract"])
+    for from_state in (False, True):
+        gi, _, g0, gs = _gpu.lif_backward(cs, v_ref, go, 1, N, 0, g_last=G, kind=_lib.SURR_SINGLE_EXPONENTIAL,
+                                          p0=0.5, p1=1.0, in_scale=scale, want_scale=True, scale_from_state=from_state)
+        assert rel_err(gi, scale[:, None].astype(np.float64) * R64) < TOL
+        assert rel_err(gs, (R64 * cs["inp"].astype(np.float64)).sum(1)) < TOL
+        assert rel_err(g0, cs["alpha"].astype(np.float64) * R64[:, 0]) < TOL
+
+
 def test_first_step_clip_term_gpu():
     """Rows that start clipped with a non-zero initial state (reference cuda/lif_kernels.h:219-238)."""
     from tests import _gpu
