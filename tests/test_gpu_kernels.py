@@ -311,14 +311,14 @@ def test_backward_all_five_streams(B, T, M):
 
 
 @pytest.mark.parametrize("layout", [0, 1])
-def test_reset_to_value_vs_bptt(layout):
+@pytest.mark.parametrize("B,T,M", [(2, 30, 9), (2, 68, 8)])      # the second: TMA-staged kernels in both layouts
+def test_reset_to_value_vs_bptt(layout, B, T, M):
     """Reset-to-value has no reference kernel; the checker is back-propagation through the time-stepped loop."""
     import torch
     from oracle.torch_loop import lif_loop
     from sinabs_exodus_b200 import _lib
     from sinabs_exodus_b200.compat.activation import SingleExponential
     from tests import _gpu
-    B, T, M = 2, 30, 9
     N = B * M
     cs = lif_case(13, N, T, clamp=True)
     cs["subtract"] = np.full(N, 0.1, np.float32)      # the reset value
