@@ -370,7 +370,8 @@ static int syn_stages(size_t stage_bytes, int64_t ctas)
 // streams one tensor and likes a deep ring; the backward streams two to five and does more per chunk, and measured
 // faster with twice the steps per stage on two stages than with half of them on five (synaptic layer, 128 x 500 x
 // 1024: 200 us against 235 us), because the work per chunk (barrier wait, release, pointer set-up) halves.
-// EXB_SYN_FWD_TC / EXB_SYN_BWD_TC (else EXB_TMA_TC) in the environment force one of them (tuning aid).
+// EXB_SYN_FWD_TC / EXB_SYN_BWD_TC (else EXB_TMA_TC) in the environment force one of them, EXB_SYN_FWD_STAGES the
+// forward's stage count (tuning aids).
 template <int TC_BIG, int TC_SMALL>
 static int syn_pick_tc(int w, int nmaps, int64_t ctas, bool backward)
 {
@@ -392,7 +393,13 @@ static cudaError_t run_syn_fwd(const LifSynFwdArgs &a, cudaStream_t s, bool *use
     using G = TileGeom<NW, V>;
     const int tiles_m = (int)((a.M + G::W - 1) / G::W);
     const size_t stage_bytes = (size_t)TC * G::W * 4;
-    const int nstages = syn_stages(stage_bytes, a.B * tiles_m);
+    int nstages = syn_stages(stage_bytes, a.B * tiles_m);
+    // With four or more CTAs resident per SM they are the parallelism; a deep ring on top only adds loads in flight
+    // that compete with this kernel's stores (three tensors out for one in).  128 x 500 x 1024, whole step replayed
+    // as a CUDA graph: 8 steps x 6 stages 0.3892 ms, 8 x 3 0.3827, 8 x 2 0.3782, 4 x 6 0.3880.
+    if (a.B * tiles_m >= 4 * (int64_t)sm_count() && nstages > 2) nstages = 2;
+    static const int env_fst = env_int("EXB_SYN_FWD_STAGES", 0);
+    if (env_fst > 1 && env_fst <= MAX_STAGES) nstages = env_fst;
     if (nstages < 2) return cudaSuccess;
     TmaMaps6 maps;
     if (!make_btm_tensor_map(&maps.m[0], a.input, a.B, a.T, a.M, G::BW, TC)) return cudaSuccess;
