@@ -186,6 +186,41 @@ int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, flo
                      int64_t B, int64_t T, int64_t M, int layout,
                      int device, void *stream);
 
+/* Forward and backward of a training step that never materialises v_mem.  No counterpart in the reference, whose
+ * forward always writes v_mem and whose backward reads it (cuda/lif_kernels.h:88, sinabs/exodus/spike.py:200,246).
+ * exb_lif_forward_ckpt is exb_lif_forward with, instead of v_mem, the state that enters every EXB_CKPT_EVERY-th
+ * step: ckpt[b, j, m] = post-reset potential before step j * EXB_CKPT_EVERY (the initial state for j = 0), a
+ * [B][ceil(T / EXB_CKPT_EVERY)][M] tensor, one eighth of v_mem.  exb_lif_backward_ckpt is exb_lif_backward with
+ * (input, ckpt) in place of v_mem: for every chunk of EXB_CKPT_EVERY steps it repeats the forward recurrence from
+ * the chunk's checkpoint with the forward kernel's own step arithmetic, which yields v_mem bit for bit, and then
+ * runs the reverse recurrence on it, so all gradients equal those of exb_lif_backward on the v_mem that
+ * exb_lif_forward writes.  The forward then moves 8.5 instead of 12 bytes per neuron-step, the backward 12.5
+ * instead of 12, and 7/8 of v_mem's memory is never allocated.  Not available: a gradient arriving on v_mem, the
+ * generic surrogate (both need the tensor), the [N,T] layout.  `input` is the forward's unscaled input; the scale
+ * gradient is always rebuilt from the state (needs non-zero scales).  Time-major layout, M % 4 == 0 and 16-byte
+ * aligned tensors only; otherwise EXB_ERR_UNSUPPORTED and the caller uses the v_mem pair. */
+#define EXB_CKPT_EVERY 8
+int exb_lif_forward_ckpt(float *spikes, float *ckpt, const float *input, const float *v_init,
+                         const float *in_scale, int in_scale_mode,
+                         const float *alpha, int alpha_mode,
+                         const float *subtract, int subtract_mode,
+                         const float *theta, int theta_mode,
+                         const float *theta_low, int theta_low_mode,
+                         uint32_t max_spikes, int reset_mode,
+                         float *v_post_last, unsigned long long *spike_count,
+                         int64_t B, int64_t T, int64_t M, int device, void *stream);
+int exb_lif_backward_ckpt(float *grad_input, float *grad_alpha, float *grad_init, float *grad_scale,
+                          const float *grad_spikes, const float *grad_v_last,
+                          const float *input, const float *ckpt, const float *v_init,
+                          const float *in_scale, int in_scale_mode,
+                          const float *alpha, int alpha_mode,
+                          const float *subtract, int subtract_mode,
+                          const float *theta, int theta_mode,
+                          const float *theta_low, int theta_low_mode,
+                          uint32_t max_spikes, int reset_mode,
+                          int surrogate_kind, float surr_p0, float surr_p1, double *acc_decay,
+                          int64_t B, int64_t T, int64_t M, int device, void *stream);
+
 /* Converts float64 accumulators that the backward entry points filled (acc_decay) to the float32 gradient
  * tensor `out` and clears them, so that the same accumulator serves the next backward pass:
  * out[i] = (float) acc[i]; acc[i] = 0, for i < n.  One small launch.  No counterpart in the reference, which

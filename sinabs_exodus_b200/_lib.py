@@ -41,7 +41,7 @@ _lib: Optional[ctypes.CDLL] = None
 
 EXPORTS = (
     "exb_version", "exb_last_error", "exb_status_string", "exb_device_status", "exb_set_wait_limit", "exb_acc_finish", "exb_allreduce_oneshot",
-    "exb_lif_forward", "exb_lif_forward_record", "exb_lif_forward_u8", "exb_lif_syn_forward_u8", "exb_lif_backward", "exb_leaky_forward", "exb_leaky_backward",
+    "exb_lif_forward", "exb_lif_forward_record", "exb_lif_forward_u8", "exb_lif_syn_forward_u8", "exb_lif_backward", "exb_lif_forward_ckpt", "exb_lif_backward_ckpt", "exb_leaky_forward", "exb_leaky_backward",
     "exb_leaky_scan_workspace_bytes", "exb_leaky_forward_scan", "exb_leaky_backward_scan",
     "exb_leaky_forward_scan_static", "exb_static_scratch_bytes", "exb_lif_syn_forward", "exb_lif_syn_backward",
 )
@@ -81,6 +81,16 @@ def load() -> ctypes.CDLL:
     lib.exb_lif_forward_u8.argtypes = [_vp, _vp, _vp, _vp,
                                        _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _i,
                                        _u32, _i, _i, _vp, _vp, _i64, _i64, _i64, _i, _vp]
+    lib.exb_lif_forward_ckpt.restype = _i
+    lib.exb_lif_forward_ckpt.argtypes = [_vp, _vp, _vp, _vp,
+                                         _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _i,
+                                         _u32, _i, _vp, _vp, _i64, _i64, _i64, _i, _vp]
+    lib.exb_lif_backward_ckpt.restype = _i
+    lib.exb_lif_backward_ckpt.argtypes = [_vp, _vp, _vp, _vp,
+                                          _vp, _vp,
+                                          _vp, _vp, _vp,
+                                          _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _i,
+                                          _u32, _i, _i, _f, _f, _vp, _i64, _i64, _i64, _i, _vp]
     lib.exb_lif_backward.restype = _i
     lib.exb_lif_backward.argtypes = [_vp, _vp, _vp, _vp,
                                      _vp, _vp, _vp,
@@ -285,6 +295,57 @@ def lif_backward(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, gra
     _check(st, "exb_lif_backward")
     _after_launch(dev)
     return True
+
+
+CKPT_EVERY = 8      # EXB_CKPT_EVERY of the header
+
+
+def ckpt_shape(B: int, T: int, M: int) -> Tuple[int, int, int]:
+    """Shape of the checkpoint tensor of :func:`lif_forward_ckpt`."""
+    return (B, (T + CKPT_EVERY - 1) // CKPT_EVERY, M)
+
+
+def lif_forward_ckpt(spikes, ckpt, inp, v_init, in_scale: Tuple, alpha: Tuple, subtract: Tuple, theta: Tuple,
+                     theta_low: Tuple, max_spikes: Optional[int], reset_mode: int, v_post_last, spike_count,
+                     B: int, T: int, M: int) -> bool:
+    """``exb_lif_forward_ckpt``: spikes and, instead of ``v_mem``, the state entering every ``CKPT_EVERY``-th step
+    (``ckpt``: float32 tensor of :func:`ckpt_shape`).  Returns False when the shape is not eligible (the caller then
+    uses :func:`lif_forward`)."""
+    if B * T * M == 0:
+        return False
+    dev = _require_cuda(spikes, ckpt, inp, v_init, in_scale[0], alpha[0], subtract[0], theta[0], theta_low[0], v_post_last)
+    if tuple(ckpt.shape) != ckpt_shape(B, T, M) or not ckpt.is_contiguous():
+        raise ExodusLibraryError(f"ckpt must be a contiguous float32 tensor of shape {ckpt_shape(B, T, M)}")
+    ms = MAX_SPIKES_UNLIMITED if max_spikes is None else int(max_spikes)
+    st = load().exb_lif_forward_ckpt(
+        ptr(spikes), ptr(ckpt), ptr(inp), ptr(v_init), ptr(in_scale[0]), in_scale[1], ptr(alpha[0]), alpha[1],
+        ptr(subtract[0]), subtract[1], ptr(theta[0]), theta[1], ptr(theta_low[0]), theta_low[1],
+        ms, reset_mode, ptr(v_post_last), ptr(spike_count), B, T, M, dev.index, _stream(dev))
+    if st == 4:
+        return False
+    _check(st, "exb_lif_forward_ckpt")
+    _after_launch(dev)
+    return True
+
+
+def lif_backward_ckpt(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, grad_v_last, inp, ckpt, v_init,
+                      in_scale: Tuple, alpha: Tuple, subtract: Tuple, theta: Tuple, theta_low: Tuple,
+                      max_spikes: Optional[int], reset_mode: int, surr_kind: int, p0: float, p1: float,
+                      B: int, T: int, M: int, acc_decay=None) -> None:
+    """``exb_lif_backward_ckpt``: the backward pass of :func:`lif_forward_ckpt` (same shapes are eligible)."""
+    if B * T * M == 0:
+        return
+    dev = _require_cuda(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, grad_v_last, inp, ckpt, v_init,
+                        in_scale[0], alpha[0], subtract[0], theta[0], theta_low[0])
+    ms = MAX_SPIKES_UNLIMITED if max_spikes is None else int(max_spikes)
+    st = load().exb_lif_backward_ckpt(
+        ptr(grad_input), ptr(grad_alpha), ptr(grad_init), ptr(grad_scale), ptr(grad_spikes), ptr(grad_v_last),
+        ptr(inp), ptr(ckpt), ptr(v_init),
+        ptr(in_scale[0]), in_scale[1], ptr(alpha[0]), alpha[1], ptr(subtract[0]), subtract[1],
+        ptr(theta[0]), theta[1], ptr(theta_low[0]), theta_low[1],
+        ms, reset_mode, surr_kind, float(p0), float(p1), _ptr_f64(acc_decay), B, T, M, dev.index, _stream(dev))
+    _check(st, "exb_lif_backward_ckpt")
+    _after_launch(dev)
 
 
 def allreduce_oneshot(out: torch.Tensor, inp: torch.Tensor, buffers: torch.Tensor, signals: torch.Tensor, rank: int,

@@ -121,9 +121,11 @@ int exb_device_status(int device, void *stream)
     unsigned int code3 = 0, code4 = 0;
     if (e == cudaSuccess) e = exb::read_device_status_lif_bwd((cudaStream_t)stream, &code2);
     if (e == cudaSuccess) e = exb::read_device_status_lif_syn((cudaStream_t)stream, &code3);
+    unsigned int code5 = 0;
     if (e == cudaSuccess) e = exb::read_device_status_lif_nt_bwd((cudaStream_t)stream, &code4);
+    if (e == cudaSuccess) e = exb::read_device_status_lif_bwd_rec((cudaStream_t)stream, &code5);
     if (e != cudaSuccess) return fail(EXB_ERR_LAUNCH, "exb_device_status: %s", cudaGetErrorString(e));
-    if (!code) code = code2 ? code2 : (code3 ? code3 : code4);
+    if (!code) code = code2 ? code2 : (code3 ? code3 : (code4 ? code4 : code5));
     if (code) return fail(EXB_ERR_TIMEOUT, "a bounded device-side wait ran out (code %u); results of the affected call are incomplete", code);
     return EXB_OK;
 }
@@ -136,6 +138,7 @@ int exb_set_wait_limit(int device, uint32_t polls, int withhold_scan_flags)
     if (e == cudaSuccess) e = exb::set_wait_limit_lif_bwd(polls);
     if (e == cudaSuccess) e = exb::set_wait_limit_lif_syn(polls);
     if (e == cudaSuccess) e = exb::set_wait_limit_lif_nt_bwd(polls);
+    if (e == cudaSuccess) e = exb::set_wait_limit_lif_bwd_rec(polls);
     if (e != cudaSuccess) return fail(EXB_ERR_LAUNCH, "exb_set_wait_limit: %s", cudaGetErrorString(e));
     return EXB_OK;
 }
@@ -151,10 +154,12 @@ static int lif_forward_impl(const char *who, float *spikes, uint8_t *spikes_u8, 
                     uint32_t max_spikes, int reset_mode,
                     float *v_post_last, unsigned long long *spike_count,
                     int64_t B, int64_t T, int64_t M, int layout,
-                    int device, void *stream)
+                    int device, void *stream, float *ckpt = nullptr)
 {
     if (int st = check_geometry(B, T, M, layout)) return st;
-    if (spikes_u8) {
+    if (ckpt) {
+        if (!spikes || !input) return fail(EXB_ERR_ARG, "%s: spikes, ckpt and input are required", who);
+    } else if (spikes_u8) {
         if (!input) return fail(EXB_ERR_ARG, "%s: spikes and input are required", who);
         if (layout != EXB_LAYOUT_BTM) return fail(EXB_ERR_UNSUPPORTED, "%s: the compact raster is written by the time-major kernels only", who);
     } else if (!spikes || !v_mem || !input) {
@@ -170,7 +175,7 @@ static int lif_forward_impl(const char *who, float *spikes, uint8_t *spikes_u8, 
         return fail(EXB_ERR_ARG, "%s: reset-to-value needs the value in `subtract`", who);
     if (v_post && layout != EXB_LAYOUT_BTM)
         return fail(EXB_ERR_UNSUPPORTED, "%s: the post-reset record is written by the time-major kernels only", who);
-    if (!all_aligned4(spikes, v_mem, v_post, input, v_init, in_scale, alpha, subtract, theta, theta_low, v_post_last) ||
+    if (!all_aligned4(spikes, v_mem, v_post, input, v_init, in_scale, alpha, subtract, theta, theta_low, v_post_last, ckpt) ||
         (reinterpret_cast<uintptr_t>(spike_count) & 7u))
         return misaligned(who);
     if (B == 0 || M == 0 || T == 0) return EXB_OK;
@@ -187,8 +192,9 @@ static int lif_forward_impl(const char *who, float *spikes, uint8_t *spikes_u8, 
     a.maxs = max_spikes;
     a.v_post_last = v_post_last; a.spike_count = spike_count; a.v_post = v_post;
     a.spikes_u8 = spikes_u8;
+    a.ckpt = ckpt;
     a.B = B; a.T = T; a.M = M;
-    if (spikes_u8) {
+    if (spikes_u8 || ckpt) {
         bool used = false;
         cudaError_t e = exb::tma_enabled() ? exb::launch_lif_forward_tma(a, reset_mode, (cudaStream_t)stream, &used) : cudaSuccess;
         if (e != cudaSuccess) return launch_status(e, who);
@@ -250,6 +256,82 @@ int exb_lif_forward_u8(uint8_t *spikes, float *v_mem, const float *input, const 
     return lif_forward_impl("exb_lif_forward_u8", nullptr, spikes, v_mem, nullptr, input, v_init, in_scale, in_scale_mode,
                             alpha, alpha_mode, subtract, subtract_mode, theta, theta_mode, theta_low, theta_low_mode,
                             max_spikes, reset_mode, v_post_last, spike_count, B, T, M, EXB_LAYOUT_BTM, device, stream);
+}
+
+int exb_lif_forward_ckpt(float *spikes, float *ckpt, const float *input, const float *v_init,
+                         const float *in_scale, int in_scale_mode,
+                         const float *alpha, int alpha_mode,
+                         const float *subtract, int subtract_mode,
+                         const float *theta, int theta_mode,
+                         const float *theta_low, int theta_low_mode,
+                         uint32_t max_spikes, int reset_mode,
+                         float *v_post_last, unsigned long long *spike_count,
+                         int64_t B, int64_t T, int64_t M, int device, void *stream)
+{
+    if (!ckpt) return fail(EXB_ERR_ARG, "exb_lif_forward_ckpt: ckpt is required (use exb_lif_forward without it)");
+    return lif_forward_impl("exb_lif_forward_ckpt", spikes, nullptr, nullptr, nullptr, input, v_init, in_scale, in_scale_mode,
+                            alpha, alpha_mode, subtract, subtract_mode, theta, theta_mode, theta_low, theta_low_mode,
+                            max_spikes, reset_mode, v_post_last, spike_count, B, T, M, EXB_LAYOUT_BTM, device, stream, ckpt);
+}
+
+int exb_lif_backward_ckpt(float *grad_input, float *grad_alpha, float *grad_init, float *grad_scale,
+                          const float *grad_spikes, const float *grad_v_last,
+                          const float *input, const float *ckpt, const float *v_init,
+                          const float *in_scale, int in_scale_mode,
+                          const float *alpha, int alpha_mode,
+                          const float *subtract, int subtract_mode,
+                          const float *theta, int theta_mode,
+                          const float *theta_low, int theta_low_mode,
+                          uint32_t max_spikes, int reset_mode,
+                          int surrogate_kind, float surr_p0, float surr_p1, double *acc_decay,
+                          int64_t B, int64_t T, int64_t M, int device, void *stream)
+{
+    const char *who = "exb_lif_backward_ckpt";
+    if (int st = check_geometry(B, T, M, EXB_LAYOUT_BTM)) return st;
+    if (!grad_input || !grad_spikes || !input || !ckpt)
+        return fail(EXB_ERR_ARG, "%s: grad_input, grad_spikes, input and ckpt are required", who);
+    if (!alpha || !theta) return fail(EXB_ERR_ARG, "%s: alpha and theta are required", who);
+    if (!mode_ok(alpha_mode, DECAY_FLAGS) || !mode_ok(theta_mode) || (subtract && !mode_ok(subtract_mode)) ||
+        (theta_low && !mode_ok(theta_low_mode)) || !scale_arg_ok(in_scale, in_scale_mode))
+        return fail(EXB_ERR_ARG, "%s: bad parameter mode", who);
+    if (acc_decay && (grad_alpha || grad_scale))
+        return fail(EXB_ERR_ARG, "%s: acc_decay replaces grad_alpha and grad_scale; pass NULL for those", who);
+    if (acc_decay && (reinterpret_cast<uintptr_t>(acc_decay) & 7u)) return misaligned(who);
+    if (reset_mode != EXB_RESET_SUBTRACT && reset_mode != EXB_RESET_TO_VALUE)
+        return fail(EXB_ERR_ARG, "%s: bad reset mode %d", who, reset_mode);
+    if (reset_mode == EXB_RESET_TO_VALUE && !subtract)
+        return fail(EXB_ERR_ARG, "%s: reset-to-value needs the value in `subtract`", who);
+    if (surrogate_kind <= EXB_SURR_GENERIC || surrogate_kind > EXB_SURR_PERIODIC_EXPONENTIAL)
+        return fail(EXB_ERR_ARG, "%s: needs one of the built-in surrogates (kind %d given): the generic one is a function "
+                    "of a v_mem tensor that this pass never materialises", who, surrogate_kind);
+    const bool scale_derived = (in_scale_mode & SCALE_FLAGS) != 0;
+    if (grad_scale && !in_scale && !scale_derived)
+        return fail(EXB_ERR_ARG, "%s: grad_scale is rebuilt from the state and needs in_scale", who);
+    if (!all_aligned4(grad_input, grad_alpha, grad_init, grad_scale, grad_spikes, grad_v_last, input, ckpt, v_init, in_scale,
+                      alpha, subtract, theta, theta_low))
+        return misaligned(who);
+    if (B == 0 || M == 0 || T == 0) return EXB_OK;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(EXB_ERR_DEVICE, "%s: cannot select device %d", who, device);
+
+    exb::LifBwdArgs a;
+    a.grad_input = grad_input; a.grad_alpha = grad_alpha; a.grad_init = grad_init; a.grad_scale = grad_scale;
+    a.go = grad_spikes; a.gv = nullptr; a.g_last = grad_v_last; a.v_mem = nullptr; a.surr = nullptr;
+    a.v_init = v_init; a.input = input; a.ckpt = ckpt;
+    a.np.alpha = exb::make_param(alpha, alpha_mode, M);
+    a.np.c = exb::make_param(subtract, subtract_mode, M);
+    a.np.th = exb::make_param(theta, theta_mode, M);
+    a.np.lo = exb::make_param(theta_low, theta_low_mode, M);
+    a.np.scale = exb::make_param(in_scale, in_scale_mode, M);
+    a.maxs = max_spikes; a.p0 = surr_p0; a.p1 = surr_p1;
+    a.acc_decay = acc_decay;
+    a.B = B; a.T = T; a.M = M;
+    bool used = false;
+    cudaError_t e = exb::tma_enabled() ? exb::launch_lif_backward_ckpt_tma(a, reset_mode, surrogate_kind, (cudaStream_t)stream, &used)
+                                       : cudaSuccess;
+    if (e != cudaSuccess) return launch_status(e, who);
+    if (!used) return fail(EXB_ERR_UNSUPPORTED, "%s: shape or alignment not eligible (needs M %% 4 == 0 and 16-byte aligned tensors)", who);
+    return EXB_OK;
 }
 
 int exb_lif_backward(float *grad_input, float *grad_alpha, float *grad_init, float *grad_scale,

@@ -15,6 +15,9 @@ struct LifFwdArgs {
     unsigned long long *spike_count;
     float *v_post;     // optional full record of the potential after each step's reset (time-major kernels only)
     uint8_t *spikes_u8 = nullptr;   // compact raster instead of `spikes` (TMA-staged kernels only; v_mem may then be null)
+    // Checkpoints instead of v_mem (TMA-staged time-major kernels only): the state entering every
+    // EXB_CKPT_EVERY-th step, [B][ceil(T / EXB_CKPT_EVERY)][M]; the backward rebuilds v_mem from them and the input.
+    float *ckpt = nullptr;
     int64_t B, T, M;
 };
 
@@ -24,6 +27,7 @@ struct LifBwdArgs {
     double *acc_decay = nullptr;
     float *grad_input, *grad_alpha, *grad_init, *grad_scale;
     const float *go, *gv, *g_last, *v_mem, *surr, *v_init, *input;
+    const float *ckpt = nullptr;      // with `input` and without `v_mem`: v_mem is rebuilt chunk by chunk (see LifFwdArgs)
     NeuronParams np;
     unsigned maxs;
     float p0, p1;
@@ -88,6 +92,8 @@ cudaError_t launch_leaky_backward(const LeakyBwdArgs &a, int layout, cudaStream_
 // when false (shape or alignment not eligible) the caller takes the plain-load kernel.
 cudaError_t launch_lif_forward_tma(const LifFwdArgs &a, int reset_mode, cudaStream_t s, bool *used);
 cudaError_t launch_lif_backward_tma(const LifBwdArgs &a, int reset_mode, int surr_kind, cudaStream_t s, bool *used);
+// The same with v_mem rebuilt from a.ckpt and a.input (a.v_mem, a.gv, a.surr must be null).
+cudaError_t launch_lif_backward_ckpt_tma(const LifBwdArgs &a, int reset_mode, int surr_kind, cudaStream_t s, bool *used);
 // [N,T] layout through TMA boxes of one row class (T % 4 == 0, T >= 64, N a multiple of the class count, tensors
 // at the same 16-byte aligned position inside a 128-byte line).
 cudaError_t launch_lif_forward_nt_tma(const LifFwdArgs &a, int reset_mode, cudaStream_t s, bool *used);
@@ -120,6 +126,8 @@ cudaError_t set_wait_limit_lif_syn(unsigned int polls);
 cudaError_t set_wait_limit_lif_nt_bwd(unsigned int polls);
 cudaError_t read_device_status_lif_bwd(cudaStream_t s, unsigned int *out);
 cudaError_t read_device_status_lif_nt_bwd(cudaStream_t s, unsigned int *out);
+cudaError_t set_wait_limit_lif_bwd_rec(unsigned int polls);
+cudaError_t read_device_status_lif_bwd_rec(cudaStream_t s, unsigned int *out);
 // EXB_DISABLE_TMA=1 in the environment forces the plain-load kernels (debugging aid).
 bool tma_enabled();
 

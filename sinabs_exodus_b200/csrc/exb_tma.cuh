@@ -114,6 +114,9 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
         : "memory");
 }
 
+// Orders this thread's shared-memory writes before later accesses of the async (TMA) proxy to the same bytes.
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 __device__ __forceinline__ float4 lds128(const float *p) { return *reinterpret_cast<const float4 *>(p); }
 
 // Ring of up to MAX_STAGES stages with one "full" (bytes landed) and one "empty" (all

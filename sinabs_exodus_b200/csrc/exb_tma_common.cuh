@@ -127,6 +127,33 @@ __device__ __forceinline__ void lds_vec(float (&d)[V], const float *p)
     }
 }
 
+// The same to a stage (a consumer thread overwriting its own columns).
+template <int V>
+__device__ __forceinline__ void sts_vec(float *p, const float (&d)[V])
+{
+    if (V == 4) *reinterpret_cast<float4 *>(p) = make_float4(d[0], d[1], d[2], d[3]);
+    else if (V == 2) *reinterpret_cast<float2 *>(p) = make_float2(d[0], d[1]);
+    else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) p[j] = d[j];
+    }
+}
+
+// V floats of one consumer thread from global memory (read-only path); p is aligned to V floats.
+template <int V>
+__device__ __forceinline__ void ldg_vec(float (&d)[V], const float *p)
+{
+    if (V == 4) {
+        const float4 t = __ldg(reinterpret_cast<const float4 *>(p));
+        d[0] = t.x; d[1] = t.y; d[2] = t.z; d[3] = t.w;
+    } else if (V == 2) {
+        const float2 t = __ldg(reinterpret_cast<const float2 *>(p));
+        d[0] = t.x; d[1] = t.y;
+    } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) d[j] = __ldg(p + j);
+    }
+}
 
 // ===========================================================================
 // host side

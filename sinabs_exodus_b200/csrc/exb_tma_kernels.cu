@@ -14,7 +14,9 @@ namespace exb {
 // REC: also write the potential after each step's reset (the layers' `record_states`).
 // ST: element type of the spike raster (float, or uint8_t for the compact raster); WV: write v_mem (a forward
 // pass that nobody differentiates or records needs only the spikes).
-template <int RESET, int NW, int V, bool UNI, bool REC, typename ST, bool WV>
+// CK: write the state that enters every EXB_CKPT_EVERY-th step (post-reset potential; the initial state at step 0)
+// to A.ckpt, for a backward pass that rebuilds v_mem instead of reading it.
+template <int RESET, int NW, int V, bool UNI, bool REC, typename ST, bool WV, bool CK = false>
 __global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V, (V == 4 && !UNI)>::value)
 lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, const int tiles_m, const PipeCfg pc)
 {
@@ -57,6 +59,7 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
         ST *sp = (std::is_same<ST, float>::value ? reinterpret_cast<ST *>(A.spikes) : reinterpret_cast<ST *>(A.spikes_u8)) + base;
         float *vm = WV ? A.v_mem + base : nullptr;
         float *rec = REC ? A.v_post + base : nullptr;
+        float *ck = CK ? A.ckpt + ((int64_t)b * ((T + EXB_CKPT_EVERY - 1) / EXB_CKPT_EVERY)) * A.M + mm : nullptr;
         const int64_t M = A.M;
         const int col = tile_col_off<NW, V>(pc.tc, c);
         SpikeTotal cnt;
@@ -71,6 +74,15 @@ lif_fwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifFwdArgs A, con
             for (int tt = 0; tt < tmax; ++tt) {
                 float xs[V];
                 lds_vec<V>(xs, st + tt * G::BW);
+                if (CK && ((k * pc.tc + tt) & (EXB_CKPT_EVERY - 1)) == 0) {
+                    if (valid) {
+                        float vs[V];
+#pragma unroll
+                        for (int j = 0; j < V; ++j) vs[j] = post_reset<RESET>(v[j], af[j], q[NQ == 1 ? 0 : j]);
+                        stv<V>(ck, vs);
+                    }
+                    ck += M;
+                }
                 lif_step_vec<RESET, V, NQ>(v, af, xs, q, cfg, cnt);
                 if (valid) {
                     st_spikes<V>(sp, af);
@@ -294,6 +306,7 @@ static cudaError_t run_lif_fwd(const LifFwdArgs &a, cudaStream_t s, bool *used)
     if (smem > 200 * 1024) return cudaSuccess;
     auto kern = a.spikes_u8 ? (a.v_mem ? lif_fwd_tma_kernel<RESET, NW, V, UNI, false, uint8_t, true>
                                        : lif_fwd_tma_kernel<RESET, NW, V, UNI, false, uint8_t, false>)
+                : a.ckpt    ? lif_fwd_tma_kernel<RESET, NW, V, UNI, false, float, false, true>
                 : a.v_post  ? lif_fwd_tma_kernel<RESET, NW, V, UNI, true, float, true>
                             : lif_fwd_tma_kernel<RESET, NW, V, UNI, false, float, true>;
     cudaError_t e = set_smem(kern, smem);
@@ -308,7 +321,9 @@ cudaError_t launch_lif_forward_tma(const LifFwdArgs &a, int reset_mode, cudaStre
     *used = false;
     if (!eligible(a.B, a.T, a.M) || !aligned16(a.input) || (a.v_post && !aligned16(a.v_post))) return cudaSuccess;
     if (a.spikes_u8) {      // compact raster: no float raster, v_mem optional, no post-reset record
-        if (!aligned16(a.spikes_u8) || (a.v_mem && !aligned16(a.v_mem)) || a.v_post) return cudaSuccess;
+        if (!aligned16(a.spikes_u8) || (a.v_mem && !aligned16(a.v_mem)) || a.v_post || a.ckpt) return cudaSuccess;
+    } else if (a.ckpt) {    // checkpoints instead of v_mem
+        if (!aligned16(a.spikes) || !aligned16(a.ckpt) || a.v_mem || a.v_post) return cudaSuccess;
     } else if (!aligned16(a.spikes) || !aligned16(a.v_mem)) {
         return cudaSuccess;
     }

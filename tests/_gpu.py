@@ -100,6 +100,43 @@ def lif_backward(cs, v_mem, go, B, M, layout, mode=_lib.PARAM_PER_N, gv=None, g_
     return from_dev(gi, B, M, layout), cpu(ga), cpu(g0), cpu(gs)
 
 
+def lif_forward_ckpt(cs, B, M, mode=_lib.PARAM_PER_N, max_spikes=None, reset_mode=_lib.RESET_SUBTRACT, in_scale=None):
+    """exb_lif_forward_ckpt on the time-major layout.  Returns (spikes [N,T], ckpt [N, ceil(T/8)], v_post_last, count,
+    device tensors (x, ckpt) for the backward) or None when the shape is not eligible."""
+    N, T = cs["inp"].shape
+    x = to_dev(cs["inp"], B, M, _lib.LAYOUT_BTM)
+    spikes = torch.full_like(x, float("nan"))
+    ckpt = torch.full(_lib.ckpt_shape(B, T, M), float("nan"), device=DEV)
+    v_post = torch.empty(N, device=DEV)
+    count = torch.zeros(1, dtype=torch.int64, device=DEV)
+    ok = _lib.lif_forward_ckpt(spikes, ckpt, x, vec(cs["v_init"]), param(in_scale, mode, B, M), param(cs["alpha"], mode, B, M),
+                               param(cs["subtract"], mode, B, M), param(cs["theta"], mode, B, M),
+                               param(cs["theta_low"], mode, B, M), max_spikes, reset_mode, v_post, count, B, T, M)
+    if not ok:
+        return None
+    torch.cuda.synchronize()
+    return (from_dev(spikes, B, M, _lib.LAYOUT_BTM), from_dev(ckpt, B, M, _lib.LAYOUT_BTM), v_post.cpu().numpy(),
+            int(count.item()), (x, ckpt))
+
+
+def lif_backward_ckpt(cs, dev_tensors, go, B, M, mode=_lib.PARAM_PER_N, g_last=None, kind=_lib.SURR_SINGLE_EXPONENTIAL,
+                      p0=0.5, p1=1.0, max_spikes=None, reset_mode=_lib.RESET_SUBTRACT, want_alpha=False, in_scale=None,
+                      want_scale=False, want_init=True):
+    x, ckpt = dev_tensors
+    N, T = go.shape
+    gi = torch.full_like(x, float("nan"))
+    ga = torch.empty(N, device=DEV) if want_alpha else None
+    g0 = torch.empty(N, device=DEV) if want_init else None
+    gs = torch.empty(N, device=DEV) if want_scale else None
+    _lib.lif_backward_ckpt(gi, ga, g0, gs, to_dev(go, B, M, _lib.LAYOUT_BTM), vec(g_last), x, ckpt, vec(cs["v_init"]),
+                           param(in_scale, mode, B, M), param(cs["alpha"], mode, B, M), param(cs["subtract"], mode, B, M),
+                           param(cs["theta"], mode, B, M), param(cs["theta_low"], mode, B, M), max_spikes, reset_mode,
+                           kind, p0, p1, B, T, M)
+    torch.cuda.synchronize()
+    cpu = lambda t: None if t is None else t.cpu().numpy()
+    return from_dev(gi, B, M, _lib.LAYOUT_BTM), cpu(ga), cpu(g0), cpu(gs)
+
+
 def _check_total(total, out):
     """The sum of the outputs that the forward kernel accumulates on the side."""
     ref = out.double().sum().item()

@@ -1,0 +1,119 @@
+"""The training pair that never materialises v_mem (``exb_lif_forward_ckpt`` / ``exb_lif_backward_ckpt``), through
+the C ABI.  Needs a GPU.
+
+The forward must give the spikes of the checker bit for bit and checkpoints that equal the checker's post-reset
+potential at every eighth step; the backward rebuilds v_mem with the forward's own arithmetic, so its gradients must
+equal those of ``exb_lif_backward`` on the materialised v_mem BIT FOR BIT, whatever the tile shape and pipeline.
+"""
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from tests._cases import lif_case
+
+pytestmark = pytest.mark.gpu
+
+# narrow tiles, ragged in time and neurons, fewer steps than one checkpoint interval, wide tiles (last two)
+SHAPES = [(3, 50, 36), (2, 64, 128), (1, 100, 260), (4, 7, 8), (2, 8, 4), (5, 17, 132), (300, 21, 516), (150, 40, 1024)]
+
+
+def _case(seed, B, T, M, mode, clamp):
+    from sinabs_exodus_b200 import _lib
+    N = B * M
+    cs = lif_case(seed, N, T, clamp=clamp)
+    for k in ("alpha", "theta", "subtract", "theta_low"):
+        if cs[k] is None:
+            continue
+        if mode == _lib.PARAM_SCALAR:
+            cs[k] = np.full(N, cs[k][0], np.float32)
+        elif mode == _lib.PARAM_PER_M:
+            cs[k] = np.tile(cs[k][:M], B)
+    return cs
+
+
+@pytest.mark.parametrize("B,T,M", SHAPES)
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("reset_mode", [0, 1])
+def test_checkpointed_pair_equals_the_materialised_one(B, T, M, mode, reset_mode):
+    from sinabs_exodus_b200 import _lib
+    from tests import _gpu
+    for clamp, max_spikes, kind, p0, p1 in ((True, None, _lib.SURR_SINGLE_EXPONENTIAL, 0.5, 1.0),
+                                            (False, 1, _lib.SURR_PERIODIC_EXPONENTIAL, 0.5, 1.0),
+                                            (True, 2, _lib.SURR_HEAVISIDE, 0.6, 0.0)):
+        cs = _case(40 + B + T + M, B, T, M, mode, clamp)
+        if reset_mode == 1:
+            cs["subtract"] = (0.25 * cs["theta"]).astype(np.float32)
+        N = B * M
+        s_ref, v_ref = orc.lif_forward_ext(cs["inp"], cs["v_init"], cs["alpha"], cs["subtract"], cs["theta"],
+                                           cs["theta_low"], max_spikes, reset_to_value=bool(reset_mode))
+        res = _gpu.lif_forward_ckpt(cs, B, M, mode, max_spikes, reset_mode=reset_mode)
+        assert res is not None
+        s, ckpt, v_post, count, dev_tensors = res
+        np.testing.assert_array_equal(s, s_ref)
+        assert count == int(s_ref.sum())
+        # the state that enters step 8j: the initial state, or the potential of step 8j-1 after its reset
+        if reset_mode == 0:
+            post = (v_ref.astype(np.float64) - cs["subtract"].astype(np.float64)[:, None] * s_ref).astype(np.float32)
+        else:
+            post = np.where(s_ref > 0, cs["subtract"][:, None], v_ref).astype(np.float32)
+        want = np.concatenate([cs["v_init"][:, None], post[:, 7::8]], axis=1)[:, :ckpt.shape[1]]
+        np.testing.assert_array_equal(ckpt, want)
+        np.testing.assert_array_equal(v_post, post[:, -1])
+
+        _, v_gpu, _, _ = _gpu.lif_forward(cs, B, M, _lib.LAYOUT_BTM, mode, max_spikes, reset_mode=reset_mode)
+        rng = np.random.default_rng(B * 31 + T)
+        go = rng.standard_normal((N, T)).astype(np.float32)
+        G = rng.standard_normal(N).astype(np.float32)
+        for want_alpha in (True, False):
+            a = _gpu.lif_backward(cs, v_gpu, go, B, M, _lib.LAYOUT_BTM, mode=mode, g_last=G, kind=kind, p0=p0, p1=p1,
+                                  max_spikes=max_spikes, reset_mode=reset_mode, want_alpha=want_alpha)
+            b = _gpu.lif_backward_ckpt(cs, dev_tensors, go, B, M, mode=mode, g_last=G, kind=kind, p0=p0, p1=p1,
+                                       max_spikes=max_spikes, reset_mode=reset_mode, want_alpha=want_alpha)
+            for x, y in zip(a[:3], b[:3]):
+                if x is None:
+                    assert y is None
+                else:
+                    assert np.isfinite(y).all()
+                    np.testing.assert_array_equal(y, x)
+
+
+@pytest.mark.parametrize("B,T,M", [(3, 40, 20), (300, 21, 516)])
+def test_checkpointed_pair_with_input_scale(B, T, M):
+    """Fused input scale and its gradient (rebuilt from the state in both routes)."""
+    from sinabs_exodus_b200 import _lib
+    from tests import _gpu
+    N = B * M
+    cs = lif_case(77, N, T, clamp=True)
+    cs["alpha"] = np.minimum(cs["alpha"], np.float32(0.97))
+    scale = (1.0 - cs["alpha"]).astype(np.float32)
+    scaled = dict(cs, inp=(scale[:, None] * cs["inp"]).astype(np.float32))
+    s_ref, v_ref = orc.lif_forward(scaled["inp"], cs["v_init"], cs["alpha"], cs["subtract"], cs["theta"], cs["theta_low"])
+    res = _gpu.lif_forward_ckpt(cs, B, M, 2, in_scale=scale)
+    assert res is not None
+    s, ckpt, v_post, count, dev_tensors = res
+    np.testing.assert_array_equal(s, s_ref)
+    go = np.random.default_rng(9).standard_normal((N, T)).astype(np.float32)
+    G = np.random.default_rng(10).standard_normal(N).astype(np.float32)
+    a = _gpu.lif_backward(cs, v_ref, go, B, M, _lib.LAYOUT_BTM, g_last=G, kind=_lib.SURR_SINGLE_EXPONENTIAL, p0=0.5, p1=1.0,
+                          in_scale=scale, want_scale=True, scale_from_state=True, want_alpha=True)
+    b = _gpu.lif_backward_ckpt(cs, dev_tensors, go, B, M, g_last=G, in_scale=scale, want_scale=True, want_alpha=True)
+    for x, y in zip(a, b):
+        np.testing.assert_array_equal(y, x)
+
+
+def test_checkpointed_pair_refuses_what_it_cannot_do():
+    import torch
+    from sinabs_exodus_b200 import _lib
+    from tests import _gpu
+    cs = lif_case(3, 2 * 6, 20, clamp=True)          # 6 neurons: not a multiple of 4
+    assert _gpu.lif_forward_ckpt(cs, 2, 6) is None
+    cs = lif_case(3, 2 * 8, 20, clamp=True)
+    res = _gpu.lif_forward_ckpt(cs, 2, 8)
+    go = np.ones((16, 20), np.float32)
+    with pytest.raises(_lib.ExodusLibraryError, match="built-in surrogates"):
+        _gpu.lif_backward_ckpt(cs, res[4], go, 2, 8, kind=_lib.SURR_GENERIC)
+    bad = torch.empty(2, 2, 8, device="cuda:0")
+    with pytest.raises(_lib.ExodusLibraryError, match="ckpt must be"):
+        _lib.lif_forward_ckpt(torch.empty(2, 20, 8, device="cuda:0"), bad, torch.empty(2, 20, 8, device="cuda:0"), None,
+                              (None, 0), (torch.ones(1, device="cuda:0"), 0), (None, 0), (torch.ones(1, device="cuda:0"), 0),
+                              (None, 0), None, 0, None, None, 2, 20, 8)
