@@ -207,7 +207,7 @@ class ClockSampler:
 # --------------------------------------------------------------------------
 class KernelTimer:
     NAMES = ("lif_forward", "lif_backward", "leaky_forward", "leaky_backward", "leaky_forward_scan",
-             "leaky_backward_scan", "lif_syn_forward", "lif_syn_backward")
+             "leaky_backward_scan", "lif_syn_forward", "lif_syn_backward", "lif_forward_ckpt", "lif_backward_ckpt")
 
     COUNTED = ("acc_finish", "allreduce_oneshot")     # small kernels of the library: counted, not timed
 
@@ -445,7 +445,9 @@ def kernel_bytes(kind: str) -> dict:
     b = {"lif_forward": 12, "lif_backward": 12, "leaky_forward": 8, "leaky_backward": 8,
          "leaky_forward_scan": 8, "leaky_backward_scan": 8,
          # fused LIF + synapse: read in, write i_syn/spikes/v_mem; read grad, v_mem, i_syn, write grad_in
-         "lif_syn_forward": 16, "lif_syn_backward": 16}
+         "lif_syn_forward": 16, "lif_syn_backward": 16,
+         # checkpointed pair: read in, write spikes + 1/8 state; read grad, in, 1/8 state, write grad_in
+         "lif_forward_ckpt": 8.5, "lif_backward_ckpt": 12.5}
     if kind == "expleak":              # trainable tau: the alpha gradient reads the forward output
         b["leaky_backward"] = 12
         b["leaky_backward_scan"] = 12
@@ -789,6 +791,8 @@ def run_ours(args, wl):
     w = Workload(name, wl, dev, rank, args.layout)
     if args.layout == "nt":
         args.no_e2e = True
+    if args.recompute:
+        w.layer.set_backward_recompute(True)
     timer = KernelTimer()
     for _ in range(args.warmup):
         w.step(world)
@@ -834,6 +838,32 @@ def run_ours(args, wl):
     if args.cuda_graph:
         launches = launches_per_step * args.steps      # replays do not pass through the wrappers
     value = w.nts * world * args.steps / (ms_total * 1e-3)
+
+    # ---- the same step without the v_mem tensor (layer.set_backward_recompute): extra key, not the headline
+    recompute = None
+    if (not args.lean and not args.cuda_graph and args.layout == "btm" and wl["kind"] in ("lif", "iaf")
+            and hasattr(w.layer, "set_backward_recompute")):
+        w.layer.set_backward_recompute(True)
+        try:
+            for _ in range(3):
+                w.step(world)
+            timer.reset()
+            timer.enabled = True
+            rsteps = max(3, min(args.steps, 10))
+            rms = timed_steps(run_step, rsteps, world, dev)
+            timer.enabled = False
+            rk = timer.summary()
+            per = kernel_bytes(wl["kind"])
+            recompute = {
+                "what": "layer.set_backward_recompute(True): the forward writes spikes and one checkpoint of the state per "
+                        "8 steps instead of v_mem, the backward rebuilds v_mem from the input and the checkpoints "
+                        "(bit-identical gradients); 8.5 + 12.5 = 21 bytes per neuron-step instead of 24",
+                "steps": rsteps, "ms_per_step": rms / rsteps, "value": w.nts * world * rsteps / (rms * 1e-3), "unit": UNIT,
+                "kernels": {k: dict(v, gbs=per[k] * w.nts / (v["avg_ms"] * 1e-3) / 1e9,
+                                    bytes_per_neuron_step=per[k]) for k, v in rk.items()}}
+        finally:
+            w.layer.set_backward_recompute(False)
+            timer.reset()
 
     # ---- end to end with host buffers (public layer API; copies inside the timed region)
     e2e = None
@@ -894,7 +924,7 @@ def run_ours(args, wl):
                     "cuda_graph": bool(args.cuda_graph),
                     "autograd": "single-threaded" if args.single_thread_autograd else "default (backward on PyTorch's autograd thread)"},
             "step_fraction_of_hbm_roofline": (step_bytes / (ms_total / args.steps * 1e-3) / 1e9) / peak,
-            "roofline": roof, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+            "roofline": roof, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "recompute": recompute,
             "cpu_baseline": cpu, "other_configs": others, "reference_cuda": ref_cuda, "stream_mix_ceilings": mix,
         }
         print(json.dumps(line), flush=True)
@@ -918,6 +948,9 @@ def main():
                     help="run backward in the calling thread (torch.autograd.set_multithreading_enabled(False)): "
                          "saves the hand-over to PyTorch's autograd thread, 60-120 us per step, which shows on small problems")
     ap.add_argument("--cuda-graph", action="store_true", help="capture the step in a CUDA graph and time replays")
+    ap.add_argument("--recompute", action="store_true",
+                    help="time the step with layer.set_backward_recompute(True) as the main measurement (profiling aid; "
+                         "the default run reports it as the extra key `recompute`)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-mix", action="store_true", help="skip the streaming-mix calibration (1 read : 2 writes, 2 : 1)")
     ap.add_argument("--no-cpu", action="store_true")
@@ -929,6 +962,8 @@ def main():
     ap.add_argument("--e2e-microbatches", type=int, default=0, help="0: micro-batches of about 128 MB per tensor")
     ap.add_argument("--e2e-host-slots", type=int, default=2, help="pinned staging slots per direction and tensor")
     args = ap.parse_args()
+    if args.recompute:
+        args.lean = True
     if args.lean:
         args.no_e2e = args.no_mix = args.no_cpu = args.no_others = args.no_reference_cuda = True
     if args.warmup < 3 and args.impl == "ours":

@@ -93,12 +93,15 @@ class _LifCore:
     @staticmethod
     def forward(ctx, inp, alpha, v_init, theta, subtract, min_v_mem, in_scale, surrogate_fn, max_spikes,
                 reset_mode, spike_count, B, T, M, layout, scale_grad_from_state=False, record=None,
-                decay_flags=0, scale_flags=0, acc=None):
+                decay_flags=0, scale_flags=0, acc=None, recompute=False):
         """``decay_flags`` / ``scale_flags``: ``PARAM_IS_TAU`` and ``SCALE_*`` bits for the alpha and scale arguments
         (the kernels then derive alpha = exp(-1/tau) and the scale from alpha; the gradient returned for ``alpha`` is
         the one w.r.t. the values passed, scale part included).  ``acc``: zeroed float64 tensor shaped like the
         flattened ``alpha`` that the backward kernel reduces that gradient into (no per-instance vector, no
-        reduction or chain-rule launches)."""
+        reduction or chain-rule launches).  ``recompute`` (time-major layout, built-in surrogates, no ``record``): keep
+        the input and one checkpoint of the state per ``CKPT_EVERY`` steps instead of ``v_mem``; the backward kernel
+        rebuilds ``v_mem`` bit for bit.  The second result is then ``None``.  Shapes the checkpointing kernels do not
+        take fall back to the ordinary pair."""
         N = B * M
         a_f, th_f, c_f, lo_f, sc_f = map(_flat32, (alpha, theta, subtract, min_v_mem, in_scale))
         modes = dict(
@@ -107,14 +110,25 @@ class _LifCore:
             scale=_mode_of(sc_f, M, N, "in_scale") | scale_flags)
         vi_f = _flat32(v_init)
         spikes = torch.empty_like(inp)
-        v_mem = torch.empty_like(inp)
         if T == 0:      # nothing to integrate: the state passes through unchanged
             v_post_last = vi_f.clone() if vi_f is not None else torch.zeros(N, dtype=torch.float32, device=inp.device)
         else:
             v_post_last = torch.empty(N, dtype=torch.float32, device=inp.device)
-        _lib.lif_forward(spikes, v_mem, inp, vi_f, (sc_f, modes["scale"]), (a_f, modes["alpha"]),
-                         (c_f, modes["subtract"]), (th_f, modes["theta"]), (lo_f, modes["lo"]),
-                         max_spikes, reset_mode, v_post_last, spike_count, B, T, M, layout, v_post=record)
+        ckpt = None
+        if (recompute and layout == _lib.LAYOUT_BTM and record is None and acc_eligible(inp)
+                and classify(surrogate_fn)[0] != _lib.SURR_GENERIC):
+            ckpt = torch.empty(_lib.ckpt_shape(B, T, M), dtype=torch.float32, device=inp.device)
+            if not _lib.lif_forward_ckpt(spikes, ckpt, inp, vi_f, (sc_f, modes["scale"]), (a_f, modes["alpha"]),
+                                         (c_f, modes["subtract"]), (th_f, modes["theta"]), (lo_f, modes["lo"]),
+                                         max_spikes, reset_mode, v_post_last, spike_count, B, T, M):
+                ckpt = None
+        if ckpt is None:
+            v_mem = torch.empty_like(inp)
+            _lib.lif_forward(spikes, v_mem, inp, vi_f, (sc_f, modes["scale"]), (a_f, modes["alpha"]),
+                             (c_f, modes["subtract"]), (th_f, modes["theta"]), (lo_f, modes["lo"]),
+                             max_spikes, reset_mode, v_post_last, spike_count, B, T, M, layout, v_post=record)
+        else:
+            v_mem = None
         ctx.set_materialize_grads(False)
         ctx.geometry = (B, T, M, layout)
         ctx.modes = modes
@@ -129,12 +143,13 @@ class _LifCore:
         ctx.acc = acc if (ctx.want_alpha and acc is not None and not (in_scale is not None and in_scale.requires_grad)) else None
         # The scale gradient either reads the forward input again or is rebuilt from v_mem alone
         # (no extra tensor kept alive or streamed); the latter needs every scale to be non-zero.
-        ctx.save_input = ctx.want_scale and not scale_grad_from_state
+        ctx.save_input = (ctx.want_scale and not scale_grad_from_state) or ckpt is not None
+        ctx.recompute = ckpt is not None
         ctx.alpha_shape = None if alpha is None else alpha.shape
         ctx.scale_shape = None if in_scale is None else in_scale.shape
         ctx.v_init_shape = None if v_init is None else v_init.shape
         ctx.has = tuple(t is not None for t in (c_f, lo_f, sc_f, vi_f))
-        saved = [v_mem, a_f, th_f]
+        saved = [ckpt if ckpt is not None else v_mem, a_f, th_f]
         saved += [t for t in (c_f, lo_f, sc_f, vi_f) if t is not None]
         if ctx.save_input:
             saved.append(inp)
@@ -155,6 +170,8 @@ class _LifCore:
         inp = rest.pop(0) if ctx.save_input else None
         modes = ctx.modes
         dev = v_mem.device
+        if ctx.recompute:
+            return _LifCore._backward_recompute(ctx, grad_spikes, grad_v_last, v_mem, inp, a_f, th_f, c_f, lo_f, sc_f, vi_f)
 
         if grad_spikes is None:
             grad_spikes = torch.zeros_like(v_mem)
@@ -205,6 +222,49 @@ class _LifCore:
         if grad_init is not None:
             grad_init = grad_init.reshape(ctx.v_init_shape)
         return grad_input, grad_alpha, grad_init, grad_scale
+
+
+def _backward_recompute(ctx, grad_spikes, grad_v_last, ckpt, inp, a_f, th_f, c_f, lo_f, sc_f, vi_f):
+    """Backward of a forward pass made with ``recompute``: ``exb_lif_backward_ckpt`` on (input, checkpoints)."""
+    B, T, M, _ = ctx.geometry
+    N = B * M
+    modes = ctx.modes
+    dev = inp.device
+    grad_spikes = torch.zeros_like(inp) if grad_spikes is None else grad_spikes.contiguous()
+    if grad_v_last is not None:
+        grad_v_last = grad_v_last.to(torch.float32).reshape(-1).contiguous()
+    kind, p0, p1 = classify(ctx.surrogate_fn)
+    grad_input = torch.empty_like(inp)
+    grad_init = torch.empty(N, dtype=torch.float32, device=dev) if ctx.v_init_shape is not None else None
+    tail = (grad_spikes, grad_v_last, inp, ckpt, vi_f, (sc_f, modes["scale"]), (a_f, modes["alpha"]),
+            (c_f, modes["subtract"]), (th_f, modes["theta"]), (lo_f, modes["lo"]), ctx.max_spikes, ctx.reset_mode,
+            kind, p0, p1, B, T, M)
+    decay_flags, scale_flags = ctx.flags
+    shape_mode = modes["alpha"] & _lib.PARAM_SHAPE_MASK
+    grad_alpha = grad_scale = None
+    if ctx.acc is not None:
+        _lib.lif_backward_ckpt(grad_input, None, grad_init, None, *tail, acc_decay=ctx.acc)
+        grad_alpha = torch.empty(a_f.numel(), dtype=torch.float32, device=dev)
+        _lib.acc_finish(grad_alpha, ctx.acc)
+        grad_alpha = grad_alpha.reshape(ctx.alpha_shape)
+    else:
+        ga = torch.empty(N, dtype=torch.float32, device=dev) if ctx.want_alpha else None
+        gs = torch.empty(N, dtype=torch.float32, device=dev) if ctx.want_scale else None
+        _lib.lif_backward_ckpt(grad_input, ga, grad_init, gs, *tail)
+        if ctx.want_alpha:
+            grad_alpha = _reduce_to_param(ga, ctx.alpha_shape, shape_mode, B, M)
+        if ctx.want_scale and not ctx.scale_derived:
+            grad_scale = _reduce_to_param(gs, ctx.scale_shape, modes["scale"] & _lib.PARAM_SHAPE_MASK, B, M)
+        if ctx.want_alpha and (decay_flags or ctx.scale_derived):
+            gs_p = _reduce_to_param(gs, ctx.alpha_shape, shape_mode, B, M) if ctx.scale_derived else None
+            grad_alpha = _fold_decay_grad(grad_alpha, gs_p, a_f.reshape(ctx.alpha_shape), decay_flags, scale_flags,
+                                          None if sc_f is None else sc_f.reshape(-1))
+    if grad_init is not None:
+        grad_init = grad_init.reshape(ctx.v_init_shape)
+    return grad_input, grad_alpha, grad_init, grad_scale
+
+
+_LifCore._backward_recompute = staticmethod(_backward_recompute)
 
 
 def _validate_1d(t: torch.Tensor, name: str) -> None:
@@ -296,12 +356,13 @@ class IntegrateAndFireTM(torch.autograd.Function):
     gradient w.r.t. ``in_scale`` from the saved membrane potential instead of keeping and re-reading
     the input; the caller guarantees that no scale is zero.  ``record``: optional tensor like ``inp`` that
     the same launch fills with the potential after each step's reset (a plain side output, no gradient).
+    ``recompute=True``: ``v_mem`` is not materialised (second result ``None``); see ``_LifCore.forward``.
     """
 
     @staticmethod
     def forward(ctx, inp, alpha, v_init, threshold, membrane_subtract, min_v_mem, in_scale,
                 surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count, scale_grad_from_state=False,
-                record=None, decay_flags=0, scale_flags=0, acc=None):
+                record=None, decay_flags=0, scale_flags=0, acc=None, recompute=False):
         if inp.ndim != 3:
             raise ValueError("'inp' must be 3D, (batch, time, neurons)")
         if not inp.is_contiguous():
@@ -311,13 +372,14 @@ class IntegrateAndFireTM(torch.autograd.Function):
             raise ValueError("'v_init' must hold one value per batch item and neuron")
         return _LifCore.forward(ctx, inp, alpha, v_init, threshold, membrane_subtract, min_v_mem, in_scale,
                                 surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count,
-                                B, T, M, _lib.LAYOUT_BTM, scale_grad_from_state, record, decay_flags, scale_flags, acc)
+                                B, T, M, _lib.LAYOUT_BTM, scale_grad_from_state, record, decay_flags, scale_flags, acc,
+                                recompute)
 
     @staticmethod
     def backward(ctx, grad_spikes, grad_v_mem, grad_v_last):
         grad_input, grad_alpha, grad_init, grad_scale = _LifCore.backward(ctx, grad_spikes, grad_v_mem, grad_v_last)
         return (grad_input, grad_alpha, grad_init, None, None, None, grad_scale, None, None, None, None, None, None,
-                None, None, None)
+                None, None, None, None)
 
 
 def fused_synaptic_eligible(inp: torch.Tensor) -> bool:

@@ -117,3 +117,55 @@ def test_checkpointed_pair_refuses_what_it_cannot_do():
         _lib.lif_forward_ckpt(torch.empty(2, 20, 8, device="cuda:0"), bad, torch.empty(2, 20, 8, device="cuda:0"), None,
                               (None, 0), (torch.ones(1, device="cuda:0"), 0), (None, 0), (torch.ones(1, device="cuda:0"), 0),
                               (None, 0), None, 0, None, None, 2, 20, 8)
+
+
+@pytest.mark.parametrize("norm_input", [True, False])
+@pytest.mark.parametrize("shape", [(8, 100, 128), (3, 37, 4, 6, 6), (300, 12, 516)])
+def test_layer_with_backward_recompute_equals_the_layer_without(shape, norm_input):
+    """``layer.set_backward_recompute(True)``: same spikes, same state, bit-identical input gradient; the tau gradient
+    comes out of the same per-neuron values through an atomic reduction, so it is compared to 1e-6."""
+    import torch
+    import sinabs_exodus_b200 as ex
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(5)
+    x = (0.6 * torch.randn(shape, device=dev, generator=g) + 0.3)
+    if norm_input:
+        x = 4.0 * x
+    grad = torch.randn(shape, device=dev, generator=g)
+    results = []
+    for recompute in (False, True):
+        layer = ex.layers.LIF(tau_mem=20.0, min_v_mem=-1.0, norm_input=norm_input).to(dev)
+        layer.set_backward_recompute(recompute)
+        xin = x.clone().requires_grad_(True)
+        before = torch.cuda.memory_allocated()
+        out = layer(xin)
+        held = torch.cuda.memory_allocated() - before
+        out.backward(grad)
+        results.append((out.detach(), xin.grad, layer.tau_mem.grad.clone(), layer.v_mem.detach().clone(), held,
+                        float(layer.firing_rate)))
+    a, b = results
+    assert a[0].sum() > 0
+    torch.testing.assert_close(b[0], a[0], rtol=0, atol=0)
+    torch.testing.assert_close(b[1], a[1], rtol=0, atol=0)
+    torch.testing.assert_close(b[2], a[2], rtol=1e-6, atol=0)
+    torch.testing.assert_close(b[3], a[3], rtol=0, atol=0)
+    assert b[5] == a[5]
+    if x.numel() * 4 > (1 << 20):
+        assert b[4] < a[4] - 0.8 * x.numel() * 4      # most of a v_mem-sized tensor less is held after the forward
+
+
+def test_layer_with_backward_recompute_falls_back():
+    """Recorded states, a surrogate the kernels do not know and neuron counts the TMA kernels do not take run as before."""
+    import torch
+    import sinabs_exodus_b200 as ex
+    dev = "cuda:0"
+    x = torch.rand(2, 30, 10, device=dev) * 2
+    for kw in (dict(record_states=True), dict(surrogate_grad_fn=lambda v, th: torch.exp(-(v - th).abs())), dict()):
+        layer = ex.layers.LIF(tau_mem=10.0, norm_input=False, **kw).to(dev)
+        ref = ex.layers.LIF(tau_mem=10.0, norm_input=False, **kw).to(dev)
+        layer.set_backward_recompute(True)
+        xa = x.clone().requires_grad_(True); xb = x.clone().requires_grad_(True)
+        layer(xa).sum().backward(); ref(xb).sum().backward()
+        torch.testing.assert_close(xa.grad, xb.grad, rtol=0, atol=0)
+        if kw.get("record_states"):
+            assert "v_mem" in layer.recordings
