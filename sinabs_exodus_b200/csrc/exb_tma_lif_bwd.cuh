@@ -14,7 +14,7 @@ namespace exb {
 // chunk length) with the forward kernel's own step function, in place over the input tile -- bit for bit the tensor
 // the forward pass would have written.  A step then moves 4 bytes per neuron less in the forward pass.
 template <int SURR, int RESET, bool WA, int WS, int NW, int V, bool UNI, bool REC>
-__global__ void __launch_bounds__((NW + 1) * 32, MinBlocks<NW, V, (V == 4 && (REC || !UNI || WA || WS != 0 || SURR == EXB_SURR_PERIODIC_EXPONENTIAL))>::value)
+__global__ void __launch_bounds__((NW + 1) * 32, (REC && V == 4) ? 3 : MinBlocks<NW, V, (V == 4 && (!UNI || WA || WS != 0 || SURR == EXB_SURR_PERIODIC_EXPONENTIAL))>::value)
 lif_bwd_tma_kernel(const __grid_constant__ TmaMaps maps, const LifBwdArgs A, const int tiles_m, const int nmaps,
                    const PipeCfg pc)
 {
@@ -167,9 +167,11 @@ static cudaError_t run_lif_bwd(const LifBwdArgs &a, cudaStream_t s, bool *used)
         if (WS == SCALE_GRAD_FROM_INPUT) ptrs[nmaps++] = a.input;
     }
     PipeCfg pc = pipe_cfg(G::W, nmaps, a.B * ((a.M + G::W - 1) / G::W));
-    if (REC) {      // a chunk starts where a checkpoint was taken; wide tiles: 3 stages of 32 KB, two CTAs per SM
+    if (REC) {      // a chunk starts where a checkpoint was taken; wide tiles: 2 stages of 32 KB, three CTAs per SM
+        static const int env_st = env_int("EXB_REC_STAGES", 0);
         pc.tc = EXB_CKPT_EVERY;
-        pc.stages = (V == 4) ? 3 : 4;
+        pc.stages = (V == 4) ? 2 : 4;
+        if (env_st >= 2 && env_st <= MAX_STAGES) pc.stages = env_st;
     }
     for (int i = 0; i < nmaps; ++i)
         if (!make_btm_tensor_map(&maps.m[i], ptrs[i], a.B, a.T, a.M, G::BW, pc.tc)) return cudaSuccess;
