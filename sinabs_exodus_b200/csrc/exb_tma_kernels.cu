@@ -295,6 +295,9 @@ static cudaError_t run_lif_fwd(const LifFwdArgs &a, cudaStream_t s, bool *used)
     const int64_t ctas = a.B * ((a.M + G::W - 1) / G::W);
     PipeCfg pc = pipe_cfg(G::W, 1, ctas);
     long_stages_for_wide_forward(pc, V, ctas, a.T);
+    // Checkpoints instead of v_mem: about as many bytes out as in, and two CTAs per SM measured best
+    // (8 x 500 x 262144: 1.372 ms with 16 x 3, 1.374 with 16 x 2, 1.387 with 8 x 4, 1.498 with 32 x 2, 1.567 with 16 x 4).
+    if (a.ckpt && pc.tc == 32 && pc.stages == 2) { pc.tc = 16; pc.stages = 3; }
     static const int env_tc = env_int("EXB_LIF_FWD_TC", 0), env_st = env_int("EXB_LIF_FWD_STAGES", 0);
     if (env_tc > 0 && env_tc <= 256) pc.tc = env_tc;
     if (env_st > 1 && env_st <= MAX_STAGES) pc.stages = env_st;
