@@ -841,7 +841,7 @@ def run_ours(args, wl):
 
     # ---- the same step without the v_mem tensor (layer.set_backward_recompute): extra key, not the headline
     recompute = None
-    if (not args.lean and not args.cuda_graph and args.layout == "btm" and wl["kind"] in ("lif", "iaf")
+    if (not args.lean and not args.cuda_graph and args.layout == "btm" and wl["kind"] in ("lif", "iaf", "lif5")
             and hasattr(w.layer, "set_backward_recompute")):
         w.layer.set_backward_recompute(True)
         try:
