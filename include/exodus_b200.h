@@ -103,7 +103,10 @@ int exb_set_wait_limit(int device, uint32_t polls, int withhold_scan_flags);
  * factor (layers/lif.py:206-209).
  * Optional fused outputs (NULL to skip): v_post_last[N] = state after the
  * reset of the last step; spike_count[1] += total number of spikes (exact
- * integer; the caller zeroes it). */
+ * integer; the caller zeroes it).
+ * v_mem may be NULL for a forward pass that is neither differentiated nor recorded (8 instead of
+ * 12 bytes per neuron-step): time-major layout, M % 4 == 0 and 16-byte aligned tensors only,
+ * otherwise EXB_ERR_UNSUPPORTED.  The reference always writes it (cuda/lif_kernels.h:88). */
 int exb_lif_forward(float *spikes, float *v_mem, const float *input, const float *v_init,
                     const float *in_scale, int in_scale_mode,
                     const float *alpha, int alpha_mode,

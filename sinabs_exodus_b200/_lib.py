@@ -223,11 +223,12 @@ class ParamSpec(tuple):
 
 def lif_forward(spikes, v_mem, inp, v_init, in_scale: Tuple, alpha: Tuple, subtract: Tuple, theta: Tuple,
                 theta_low: Tuple, max_spikes: Optional[int], reset_mode: int, v_post_last, spike_count,
-                B: int, T: int, M: int, layout: int, v_post=None) -> None:
+                B: int, T: int, M: int, layout: int, v_post=None) -> bool:
     """``v_post``: optional tensor like ``v_mem`` that receives the potential after each step's reset
-    (time-major layout only)."""
+    (time-major layout only).  ``v_mem`` may be None (spikes only); the call then returns False, without having
+    launched anything, when the shape is not one the spikes-only kernels take."""
     if B * T * M == 0:      # empty problem: nothing to launch (empty tensors have no storage to point at)
-        return
+        return True
     dev = _require_cuda(spikes, v_mem, inp, v_init, in_scale[0], alpha[0], subtract[0], theta[0], theta_low[0],
                         v_post_last, v_post)
     ms = MAX_SPIKES_UNLIMITED if max_spikes is None else int(max_spikes)
@@ -237,12 +238,15 @@ def lif_forward(spikes, v_mem, inp, v_init, in_scale: Tuple, alpha: Tuple, subtr
             B, T, M, layout, dev.index, _stream(dev))
     if v_post is None:
         st = load().exb_lif_forward(ptr(spikes), ptr(v_mem), ptr(inp), ptr(v_init), *tail)
+        if st == 4 and v_mem is None:
+            return False        # spikes-only is for shapes the TMA-staged kernels take: the caller passes a v_mem tensor
         _check(st, "exb_lif_forward")
         _after_launch(dev)
     else:
         st = load().exb_lif_forward_record(ptr(spikes), ptr(v_mem), ptr(v_post), ptr(inp), ptr(v_init), *tail)
         _check(st, "exb_lif_forward_record")
         _after_launch(dev)
+    return True
 
 
 def _require_u8(t: torch.Tensor) -> None:

@@ -162,8 +162,10 @@ static int lif_forward_impl(const char *who, float *spikes, uint8_t *spikes_u8, 
     } else if (spikes_u8) {
         if (!input) return fail(EXB_ERR_ARG, "%s: spikes and input are required", who);
         if (layout != EXB_LAYOUT_BTM) return fail(EXB_ERR_UNSUPPORTED, "%s: the compact raster is written by the time-major kernels only", who);
-    } else if (!spikes || !v_mem || !input) {
-        return fail(EXB_ERR_ARG, "%s: spikes, v_mem and input are required", who);
+    } else if (!spikes || !input) {
+        return fail(EXB_ERR_ARG, "%s: spikes and input are required", who);
+    } else if (!v_mem && (v_post || layout != EXB_LAYOUT_BTM)) {
+        return fail(EXB_ERR_UNSUPPORTED, "%s: v_mem may be omitted in the time-major layout without a post-reset record only", who);
     }
     if (!alpha || !theta) return fail(EXB_ERR_ARG, "%s: alpha and theta are required", who);
     if (!mode_ok(alpha_mode, DECAY_FLAGS) || !mode_ok(theta_mode) || (subtract && !mode_ok(subtract_mode)) ||
@@ -194,7 +196,7 @@ static int lif_forward_impl(const char *who, float *spikes, uint8_t *spikes_u8, 
     a.spikes_u8 = spikes_u8;
     a.ckpt = ckpt;
     a.B = B; a.T = T; a.M = M;
-    if (spikes_u8 || ckpt) {
+    if (spikes_u8 || ckpt || !v_mem) {
         bool used = false;
         cudaError_t e = exb::tma_enabled() ? exb::launch_lif_forward_tma(a, reset_mode, (cudaStream_t)stream, &used) : cudaSuccess;
         if (e != cudaSuccess) return launch_status(e, who);

@@ -297,7 +297,7 @@ static cudaError_t run_lif_fwd(const LifFwdArgs &a, cudaStream_t s, bool *used)
     long_stages_for_wide_forward(pc, V, ctas, a.T);
     // Checkpoints instead of v_mem: about as many bytes out as in, and two CTAs per SM measured best
     // (8 x 500 x 262144: 1.372 ms with 16 x 3, 1.374 with 16 x 2, 1.387 with 8 x 4, 1.498 with 32 x 2, 1.567 with 16 x 4).
-    if (a.ckpt && pc.tc == 32 && pc.stages == 2) { pc.tc = 16; pc.stages = 3; }
+    if ((a.ckpt || (!a.v_mem && !a.spikes_u8)) && pc.tc == 32 && pc.stages == 2) { pc.tc = 16; pc.stages = 3; }
     static const int env_tc = env_int("EXB_LIF_FWD_TC", 0), env_st = env_int("EXB_LIF_FWD_STAGES", 0);
     if (env_tc > 0 && env_tc <= 256) pc.tc = env_tc;
     if (env_st > 1 && env_st <= MAX_STAGES) pc.stages = env_st;
@@ -310,6 +310,7 @@ static cudaError_t run_lif_fwd(const LifFwdArgs &a, cudaStream_t s, bool *used)
     auto kern = a.spikes_u8 ? (a.v_mem ? lif_fwd_tma_kernel<RESET, NW, V, UNI, false, uint8_t, true>
                                        : lif_fwd_tma_kernel<RESET, NW, V, UNI, false, uint8_t, false>)
                 : a.ckpt    ? lif_fwd_tma_kernel<RESET, NW, V, UNI, false, float, false, true>
+                : !a.v_mem  ? lif_fwd_tma_kernel<RESET, NW, V, UNI, false, float, false>
                 : a.v_post  ? lif_fwd_tma_kernel<RESET, NW, V, UNI, true, float, true>
                             : lif_fwd_tma_kernel<RESET, NW, V, UNI, false, float, true>;
     cudaError_t e = set_smem(kern, smem);
@@ -327,6 +328,8 @@ cudaError_t launch_lif_forward_tma(const LifFwdArgs &a, int reset_mode, cudaStre
         if (!aligned16(a.spikes_u8) || (a.v_mem && !aligned16(a.v_mem)) || a.v_post || a.ckpt) return cudaSuccess;
     } else if (a.ckpt) {    // checkpoints instead of v_mem
         if (!aligned16(a.spikes) || !aligned16(a.ckpt) || a.v_mem || a.v_post) return cudaSuccess;
+    } else if (!a.v_mem) {  // spikes only: a forward pass that is neither differentiated nor recorded
+        if (!aligned16(a.spikes) || a.v_post) return cudaSuccess;
     } else if (!aligned16(a.spikes) || !aligned16(a.v_mem)) {
         return cudaSuccess;
     }

@@ -343,7 +343,8 @@ class LIF(LIFBase):
         spikes, v_pre, v_post_last = IntegrateAndFireTM.apply(
             i_syn, raw, self._state_flat(self.v_mem), threshold, subtract, min_v_mem, None,
             self.surrogate_grad_fn, self.max_num_spikes_per_bin, reset_mode, count,
-            scale_from_state, v_rec, dflags, sflags, acc, recompute)
+            scale_from_state, v_rec, dflags, sflags, acc, recompute,
+            torch.is_grad_enabled() or self.record_states)      # inference without recording: spikes only
         if self.record_states and not fused_record:
             c = threshold if subtract is None else subtract
             c = c if c.numel() == 1 else (c.view(1, 1, -1) if c.numel() == v_pre.shape[2] else c.view(batch, 1, -1))

@@ -93,7 +93,7 @@ class _LifCore:
     @staticmethod
     def forward(ctx, inp, alpha, v_init, theta, subtract, min_v_mem, in_scale, surrogate_fn, max_spikes,
                 reset_mode, spike_count, B, T, M, layout, scale_grad_from_state=False, record=None,
-                decay_flags=0, scale_flags=0, acc=None, recompute=False):
+                decay_flags=0, scale_flags=0, acc=None, recompute=False, keep_v_mem=True):
         """``decay_flags`` / ``scale_flags``: ``PARAM_IS_TAU`` and ``SCALE_*`` bits for the alpha and scale arguments
         (the kernels then derive alpha = exp(-1/tau) and the scale from alpha; the gradient returned for ``alpha`` is
         the one w.r.t. the values passed, scale part included).  ``acc``: zeroed float64 tensor shaped like the
@@ -101,7 +101,8 @@ class _LifCore:
         reduction or chain-rule launches).  ``recompute`` (time-major layout, built-in surrogates, no ``record``): keep
         the input and one checkpoint of the state per ``CKPT_EVERY`` steps instead of ``v_mem``; the backward kernel
         rebuilds ``v_mem`` bit for bit.  The second result is then ``None``.  Shapes the checkpointing kernels do not
-        take fall back to the ordinary pair."""
+        take fall back to the ordinary pair.  ``keep_v_mem=False`` (a call that is neither differentiated nor recorded):
+        ``v_mem`` is not written at all where the kernels allow it (second result ``None``)."""
         N = B * M
         a_f, th_f, c_f, lo_f, sc_f = map(_flat32, (alpha, theta, subtract, min_v_mem, in_scale))
         modes = dict(
@@ -122,13 +123,15 @@ class _LifCore:
                                          (c_f, modes["subtract"]), (th_f, modes["theta"]), (lo_f, modes["lo"]),
                                          max_spikes, reset_mode, v_post_last, spike_count, B, T, M):
                 ckpt = None
-        if ckpt is None:
+        v_mem = None
+        params = ((sc_f, modes["scale"]), (a_f, modes["alpha"]), (c_f, modes["subtract"]), (th_f, modes["theta"]),
+                  (lo_f, modes["lo"]), max_spikes, reset_mode, v_post_last, spike_count, B, T, M, layout)
+        done = ckpt is not None
+        if not done and not keep_v_mem and layout == _lib.LAYOUT_BTM and record is None and T > 0:
+            done = _lib.lif_forward(spikes, None, inp, vi_f, *params)
+        if not done:
             v_mem = torch.empty_like(inp)
-            _lib.lif_forward(spikes, v_mem, inp, vi_f, (sc_f, modes["scale"]), (a_f, modes["alpha"]),
-                             (c_f, modes["subtract"]), (th_f, modes["theta"]), (lo_f, modes["lo"]),
-                             max_spikes, reset_mode, v_post_last, spike_count, B, T, M, layout, v_post=record)
-        else:
-            v_mem = None
+            _lib.lif_forward(spikes, v_mem, inp, vi_f, *params, v_post=record)
         ctx.set_materialize_grads(False)
         ctx.geometry = (B, T, M, layout)
         ctx.modes = modes
@@ -149,6 +152,8 @@ class _LifCore:
         ctx.scale_shape = None if in_scale is None else in_scale.shape
         ctx.v_init_shape = None if v_init is None else v_init.shape
         ctx.has = tuple(t is not None for t in (c_f, lo_f, sc_f, vi_f))
+        if ckpt is None and v_mem is None:      # spikes only: nothing to differentiate
+            return spikes, None, v_post_last
         saved = [ckpt if ckpt is not None else v_mem, a_f, th_f]
         saved += [t for t in (c_f, lo_f, sc_f, vi_f) if t is not None]
         if ctx.save_input:
@@ -356,13 +361,14 @@ class IntegrateAndFireTM(torch.autograd.Function):
     gradient w.r.t. ``in_scale`` from the saved membrane potential instead of keeping and re-reading
     the input; the caller guarantees that no scale is zero.  ``record``: optional tensor like ``inp`` that
     the same launch fills with the potential after each step's reset (a plain side output, no gradient).
-    ``recompute=True``: ``v_mem`` is not materialised (second result ``None``); see ``_LifCore.forward``.
+    ``recompute=True`` / ``keep_v_mem=False``: ``v_mem`` is not materialised (second result ``None``); see
+    ``_LifCore.forward``.
     """
 
     @staticmethod
     def forward(ctx, inp, alpha, v_init, threshold, membrane_subtract, min_v_mem, in_scale,
                 surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count, scale_grad_from_state=False,
-                record=None, decay_flags=0, scale_flags=0, acc=None, recompute=False):
+                record=None, decay_flags=0, scale_flags=0, acc=None, recompute=False, keep_v_mem=True):
         if inp.ndim != 3:
             raise ValueError("'inp' must be 3D, (batch, time, neurons)")
         if not inp.is_contiguous():
@@ -373,13 +379,13 @@ class IntegrateAndFireTM(torch.autograd.Function):
         return _LifCore.forward(ctx, inp, alpha, v_init, threshold, membrane_subtract, min_v_mem, in_scale,
                                 surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count,
                                 B, T, M, _lib.LAYOUT_BTM, scale_grad_from_state, record, decay_flags, scale_flags, acc,
-                                recompute)
+                                recompute, keep_v_mem)
 
     @staticmethod
     def backward(ctx, grad_spikes, grad_v_mem, grad_v_last):
         grad_input, grad_alpha, grad_init, grad_scale = _LifCore.backward(ctx, grad_spikes, grad_v_mem, grad_v_last)
         return (grad_input, grad_alpha, grad_init, None, None, None, grad_scale, None, None, None, None, None, None,
-                None, None, None, None)
+                None, None, None, None, None)
 
 
 def fused_synaptic_eligible(inp: torch.Tensor) -> bool:

@@ -169,3 +169,59 @@ def test_layer_with_backward_recompute_falls_back():
         torch.testing.assert_close(xa.grad, xb.grad, rtol=0, atol=0)
         if kw.get("record_states"):
             assert "v_mem" in layer.recordings
+
+
+@pytest.mark.parametrize("B,T,M", [(3, 50, 36), (300, 21, 516), (2, 33, 10)])
+@pytest.mark.parametrize("reset_mode", [0, 1])
+def test_forward_without_v_mem(B, T, M, reset_mode):
+    """``exb_lif_forward`` with v_mem == NULL: the same spikes, final state and count; refused (nothing launched) for
+    shapes the TMA-staged kernels do not take (10 neurons)."""
+    import torch
+    from sinabs_exodus_b200 import _lib
+    from tests import _gpu
+    cs = _case(60 + B + T, B, T, M, 2, True)
+    if reset_mode == 1:
+        cs["subtract"] = (0.25 * cs["theta"]).astype(np.float32)
+    s_ref, v_ref = orc.lif_forward_ext(cs["inp"], cs["v_init"], cs["alpha"], cs["subtract"], cs["theta"], cs["theta_low"],
+                                       None, reset_to_value=bool(reset_mode))
+    x = _gpu.to_dev(cs["inp"], B, M, _lib.LAYOUT_BTM)
+    spikes = torch.full_like(x, float("nan"))
+    v_post = torch.full((B * M,), float("nan"), device=_gpu.DEV)
+    count = torch.zeros(1, dtype=torch.int64, device=_gpu.DEV)
+    P = lambda k: _gpu.param(cs[k], 2, B, M)
+    ok = _lib.lif_forward(spikes, None, x, _gpu.vec(cs["v_init"]), (None, 0), P("alpha"), P("subtract"), P("theta"),
+                          P("theta_low"), None, reset_mode, v_post, count, B, T, M, _lib.LAYOUT_BTM)
+    torch.cuda.synchronize()
+    if M % 4:
+        assert ok is False and bool(torch.isnan(spikes).all())
+        return
+    assert ok is True
+    np.testing.assert_array_equal(_gpu.from_dev(spikes, B, M, _lib.LAYOUT_BTM), s_ref)
+    assert int(count.item()) == int(s_ref.sum())
+    _, _, v_post_ref, _ = _gpu.lif_forward(cs, B, M, _lib.LAYOUT_BTM, 2, None, reset_mode=reset_mode)
+    np.testing.assert_array_equal(v_post.cpu().numpy(), v_post_ref)
+
+
+def test_layer_inference_writes_no_v_mem():
+    """Under ``torch.no_grad()`` and without ``record_states`` the layer's forward launch writes the spikes only."""
+    import torch
+    import sinabs_exodus_b200 as ex
+    dev = "cuda:0"
+    x = torch.rand(16, 200, 2048, device=dev) * 0.6
+    a = ex.layers.LIF(tau_mem=20.0, norm_input=False).to(dev)
+    b = ex.layers.LIF(tau_mem=20.0, norm_input=False).to(dev)
+    out_a = a(x)
+    torch.cuda.synchronize(); torch.cuda.reset_peak_memory_stats(); base = torch.cuda.memory_allocated()
+    with torch.no_grad():
+        out_b = b(x)
+    torch.cuda.synchronize()
+    peak = torch.cuda.max_memory_allocated() - base
+    assert out_a.sum() > 0
+    torch.testing.assert_close(out_b, out_a.detach(), rtol=0, atol=0)
+    torch.testing.assert_close(b.v_mem, a.v_mem.detach(), rtol=0, atol=0)
+    assert float(b.firing_rate) == float(a.firing_rate)
+    assert peak < 1.5 * x.numel() * 4          # one output tensor, not two
+    rec = ex.layers.LIF(tau_mem=20.0, norm_input=False, record_states=True).to(dev)
+    with torch.no_grad():
+        rec(x[:2])
+    assert rec.recordings["v_mem"].shape == x[:2].shape
