@@ -279,7 +279,8 @@ int exb_leaky_backward(float *grad_input, float *grad_alpha, float *grad_init, f
  * exb_lif_*).  The reference runs the two stages as separate kernels with PyTorch passes in between
  * (layers/lif.py:185-198, 200-258: leakyForward, x*alpha, (1-alpha)*i, lifForward).
  *   i_t = alpha_syn*i_{t-1} + scale_syn*in_t ;  membrane step of exb_lif_forward on scale_mem*i_t
- * Forward writes i_syn, spikes, v_mem (+ optional v_post_last[N], i_last[N], spike_count).
+ * Forward writes i_syn, spikes, v_mem (+ optional v_post_last[N], i_last[N], spike_count); v_mem and i_syn may
+ * both be NULL for a pass that is neither differentiated nor recorded (8 instead of 16 bytes per neuron-step).
  * Backward takes gradients w.r.t. spikes and optionally v_mem, v_post_last, i_syn, i_last, and
  * writes grad_input, optional grad_v_init / grad_i_init, and -- all four or none -- the
  * per-instance gradients w.r.t. alpha_mem, scale_mem, alpha_syn, scale_syn (these need `i_syn`;

@@ -630,8 +630,12 @@ static int lif_syn_forward_impl(const char *who, float *spikes, uint8_t *spikes_
             return fail(EXB_ERR_ARG, "%s: spikes, input, alpha_syn, alpha_mem and theta are required", who);
         if ((v_mem != nullptr) != (i_syn != nullptr))
             return fail(EXB_ERR_ARG, "%s: pass both v_mem and i_syn or neither", who);
-    } else if (!spikes || !v_mem || !i_syn || !input || !alpha_syn || !alpha_mem || !theta)
-        return fail(EXB_ERR_ARG, "exb_lif_syn_forward: spikes, v_mem, i_syn, input, alpha_syn, alpha_mem and theta are required");
+    } else {
+        if (!spikes || !input || !alpha_syn || !alpha_mem || !theta)
+            return fail(EXB_ERR_ARG, "%s: spikes, input, alpha_syn, alpha_mem and theta are required", who);
+        if ((v_mem != nullptr) != (i_syn != nullptr))
+            return fail(EXB_ERR_ARG, "%s: pass both v_mem and i_syn or neither", who);
+    }
     if (!mode_ok(alpha_syn_mode, DECAY_FLAGS) || !mode_ok(alpha_mem_mode, DECAY_FLAGS) || !mode_ok(theta_mode) ||
         !scale_arg_ok(scale_syn, scale_syn_mode) || !scale_arg_ok(scale_mem, scale_mem_mode) ||
         (subtract && !mode_ok(subtract_mode)) || (theta_low && !mode_ok(theta_low_mode)))

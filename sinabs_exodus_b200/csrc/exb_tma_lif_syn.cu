@@ -408,7 +408,8 @@ static cudaError_t run_syn_fwd(const LifSynFwdArgs &a, cudaStream_t s, bool *use
     const size_t smem = tma_smem_bytes<NW, V>(1, pc);
     auto kern = a.spikes_u8 ? (a.v_mem ? lif_syn_fwd_tma_kernel<RESET, NW, V, UNI, TC, uint8_t, true>
                                        : lif_syn_fwd_tma_kernel<RESET, NW, V, UNI, TC, uint8_t, false>)
-                            : lif_syn_fwd_tma_kernel<RESET, NW, V, UNI, TC, float, true>;
+                : a.v_mem   ? lif_syn_fwd_tma_kernel<RESET, NW, V, UNI, TC, float, true>
+                            : lif_syn_fwd_tma_kernel<RESET, NW, V, UNI, TC, float, false>;
     cudaError_t e = set_smem(kern, smem);
     if (e != cudaSuccess) return e;
     kern<<<(unsigned)(a.B * tiles_m), (NW + 1) * 32, smem, s>>>(maps, a, tiles_m, nstages);
@@ -433,12 +434,10 @@ cudaError_t launch_lif_syn_forward(const LifSynFwdArgs &a, int reset_mode, cudaS
 {
     *used = false;
     if (!eligible(a.B, a.T, a.M) || !aligned16(a.input) || a.T * a.M >= (1ll << 31)) return cudaSuccess;
-    if (a.spikes_u8) {      // compact raster: v_mem and i_syn are written together or not at all
-        if (!aligned16(a.spikes_u8) || (a.v_mem != nullptr) != (a.i_syn != nullptr)) return cudaSuccess;
-        if (a.v_mem && (!aligned16(a.v_mem) || !aligned16(a.i_syn))) return cudaSuccess;
-    } else if (!aligned16(a.spikes) || !aligned16(a.v_mem) || !aligned16(a.i_syn)) {
-        return cudaSuccess;
-    }
+    // v_mem and i_syn are written together or not at all (a forward pass that is neither differentiated nor recorded)
+    if ((a.v_mem != nullptr) != (a.i_syn != nullptr)) return cudaSuccess;
+    if (a.v_mem && (!aligned16(a.v_mem) || !aligned16(a.i_syn))) return cudaSuccess;
+    if (a.spikes_u8 ? !aligned16(a.spikes_u8) : !aligned16(a.spikes)) return cudaSuccess;
     return reset_mode == EXB_RESET_SUBTRACT ? pick_syn_fwd<EXB_RESET_SUBTRACT>(a, s, used)
                                             : pick_syn_fwd<EXB_RESET_TO_VALUE>(a, s, used);
 }

@@ -549,7 +549,8 @@ class LIF(LIFBase):
         spikes, v_pre, v_post_last, i_syn, i_last = LIFSynapticTM.apply(
             x, raw_syn, None, self._state_flat(self.i_syn), raw_mem, None,
             self._state_flat(self.v_mem), threshold, subtract, min_v_mem, self.surrogate_grad_fn,
-            self.max_num_spikes_per_bin, reset_mode, count, flags, acc)
+            self.max_num_spikes_per_bin, reset_mode, count, flags, acc,
+            torch.is_grad_enabled() or self.record_states)      # inference without recording: spikes only
         self._set_state("i_syn", self._unflatten(i_last, (batch_size,), trailing))
         self._set_state("v_mem", self._unflatten(v_post_last, (batch_size,), trailing))
         if self.record_states:

@@ -413,8 +413,10 @@ class LIFSynapticTM(torch.autograd.Function):
     @staticmethod
     def forward(ctx, inp, alpha_syn, scale_syn, i_init, alpha_mem, scale_mem, v_init, threshold, membrane_subtract,
                 min_v_mem, surrogate_grad_fn, max_num_spikes_per_bin, reset_mode, spike_count, flags=(0, 0, 0, 0),
-                acc=None):
-        """``flags``: (decay_syn, scale_syn, decay_mem, scale_mem) bits (``PARAM_IS_TAU``, ``SCALE_*``) for the four
+                acc=None, keep_states=True):
+        """``keep_states=False`` (a call that is neither differentiated nor recorded): ``v_mem`` and ``i_syn`` are not
+        written (second and fourth result ``None``).
+        ``flags``: (decay_syn, scale_syn, decay_mem, scale_mem) bits (``PARAM_IS_TAU``, ``SCALE_*``) for the four
         parameter arguments.  ``acc``: (acc_mem, acc_syn), zeroed float64 tensors shaped like the flattened
         ``alpha_mem`` / ``alpha_syn``, into which the backward kernel reduces the gradients w.r.t. the values passed
         for the two decays (scale parts included) when neither scale is a tensor of its own."""
@@ -427,7 +429,9 @@ class LIFSynapticTM(torch.autograd.Function):
         modes = {k: _mode_of(t, M, N, k) for k, t in f.items()}
         modes["a_syn"] |= flags[0]; modes["s_syn"] |= flags[1]; modes["a_mem"] |= flags[2]; modes["s_mem"] |= flags[3]
         vi_f, ii_f = _flat32(v_init), _flat32(i_init)
-        spikes = torch.empty_like(inp); v_mem = torch.empty_like(inp); i_syn = torch.empty_like(inp)
+        spikes = torch.empty_like(inp)
+        v_mem = torch.empty_like(inp) if keep_states else None
+        i_syn = torch.empty_like(inp) if keep_states else None
         v_post_last = torch.empty(N, dtype=torch.float32, device=inp.device)
         i_last = torch.empty(N, dtype=torch.float32, device=inp.device)
         spec = lambda k: (f[k], modes[k])
@@ -436,6 +440,8 @@ class LIFSynapticTM(torch.autograd.Function):
                                     v_post_last, i_last, spike_count, B, T, M)
         if not done:
             raise _lib.ExodusLibraryError("exb_lif_syn_forward refused a shape that passed the eligibility check")
+        if not keep_states:
+            return spikes, None, v_post_last, None, i_last
         ctx.set_materialize_grads(False)
         ctx.geometry = (B, T, M)
         ctx.modes = modes
@@ -507,7 +513,7 @@ class LIFSynapticTM(torch.autograd.Function):
             _lib.acc_finish(g_syn, ctx.acc[1])
             return (grad_input, g_syn.reshape(ctx.param_shapes["a_syn"]) if ctx.param_needs["a_syn"] else None, None, gi0,
                     g_mem.reshape(ctx.param_shapes["a_mem"]) if ctx.param_needs["a_mem"] else None, None, gv0,
-                    None, None, None, None, None, None, None, None, None)
+                    None, None, None, None, None, None, None, None, None, None)
         ga_mem, gs_mem, ga_syn, gs_syn = (new(), new(), new(), new()) if ctx.want_params else (None,) * 4
         _lib.lif_syn_backward(grad_input, ga_mem, gs_mem, ga_syn, gs_syn, *tail)
 
@@ -528,7 +534,7 @@ class LIFSynapticTM(torch.autograd.Function):
             fl = ctx.flags
             return (grad_input, fold("a_syn", "s_syn", fl[0], fl[1], ga_syn, gs_syn), None if fl[1] else red(gs_syn, "s_syn"),
                     gi0, fold("a_mem", "s_mem", fl[2], fl[3], ga_mem, gs_mem), None if fl[3] else red(gs_mem, "s_mem"),
-                    gv0, None, None, None, None, None, None, None, None, None)
+                    gv0, None, None, None, None, None, None, None, None, None, None)
 
         return (grad_input, red(ga_syn, "a_syn"), red(gs_syn, "s_syn"), gi0, red(ga_mem, "a_mem"), red(gs_mem, "s_mem"),
-                gv0, None, None, None, None, None, None, None, None, None)
+                gv0, None, None, None, None, None, None, None, None, None, None)

@@ -225,3 +225,28 @@ def test_layer_inference_writes_no_v_mem():
     with torch.no_grad():
         rec(x[:2])
     assert rec.recordings["v_mem"].shape == x[:2].shape
+
+
+def test_synaptic_layer_inference_writes_no_states():
+    """The fused synaptic forward under ``torch.no_grad()`` without ``record_states``: spikes only."""
+    import torch
+    import sinabs_exodus_b200 as ex
+    dev = "cuda:0"
+    x = torch.rand(16, 200, 2048, device=dev) * 3.0
+    mk = lambda **kw: ex.layers.LIF(tau_mem=20.0, tau_syn=8.0, **kw).to(dev)
+    a, b = mk(), mk()
+    out_a = a(x)
+    torch.cuda.synchronize(); torch.cuda.reset_peak_memory_stats(); base = torch.cuda.memory_allocated()
+    with torch.no_grad():
+        out_b = b(x)
+    torch.cuda.synchronize()
+    peak = torch.cuda.max_memory_allocated() - base
+    assert out_a.sum() > 0
+    torch.testing.assert_close(out_b, out_a.detach(), rtol=0, atol=0)
+    torch.testing.assert_close(b.v_mem, a.v_mem.detach(), rtol=0, atol=0)
+    torch.testing.assert_close(b.i_syn, a.i_syn.detach(), rtol=0, atol=0)
+    assert peak < 1.5 * x.numel() * 4          # one output tensor, not three
+    rec = mk(record_states=True)
+    with torch.no_grad():
+        rec(x[:2])
+    assert rec.recordings["v_mem"].shape == x[:2].shape and rec.recordings["i_syn"].shape == x[:2].shape
