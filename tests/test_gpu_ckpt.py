@@ -250,3 +250,31 @@ def test_synaptic_layer_inference_writes_no_states():
     with torch.no_grad():
         rec(x[:2])
     assert rec.recordings["v_mem"].shape == x[:2].shape and rec.recordings["i_syn"].shape == x[:2].shape
+
+
+def test_backward_recompute_in_a_captured_step():
+    """``GraphedStep`` over a layer that trains without the v_mem tensor replays to the eager results."""
+    import torch
+    import sinabs_exodus_b200 as ex
+    dev = "cuda:0"
+    layer = ex.layers.LIF(tau_mem=15.0, norm_input=False).to(dev)
+    layer.set_backward_recompute(True)
+    g = torch.Generator(device=dev).manual_seed(8)
+    xs = [torch.randn(4, 40, 64, device=dev, generator=g) + 0.4 for _ in range(3)]
+    gos = [torch.randn(4, 40, 64, device=dev, generator=g) for _ in range(3)]
+
+    def eager(x, go):
+        layer.reset_states(); layer.zero_grad(set_to_none=True)
+        x = x.clone().requires_grad_(True)
+        out = layer(x)
+        out.backward(go)
+        return out.detach().clone(), x.grad.clone(), layer.tau_mem.grad.clone()
+
+    want = [eager(x, go) for x, go in zip(xs, gos)]
+    step = ex.GraphedStep(layer, xs[0], gos[0], carry_state=False, input_grad=True)
+    for (out_w, gx_w, gt_w), x, go in zip(want, xs, gos):
+        out = step(x, go)
+        assert out_w.sum() > 0
+        torch.testing.assert_close(out, out_w, rtol=0, atol=0)
+        torch.testing.assert_close(step.input_grad, gx_w, rtol=0, atol=0)
+        torch.testing.assert_close(layer.tau_mem.grad, gt_w, rtol=1e-6, atol=0)
