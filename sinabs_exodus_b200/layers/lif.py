@@ -11,6 +11,7 @@ pass (``:256``) and ``sum()/numel()`` pass (``:305``) have no counterpart here.
 """
 from __future__ import annotations
 
+import os
 import weakref
 from typing import Callable, Optional, Tuple, Union
 
@@ -163,7 +164,7 @@ class LIF(LIFBase):
         )
         self.decay_early = decay_early
 
-    _recompute = False
+    _recompute = os.environ.get("EXODUS_B200_BACKWARD_RECOMPUTE", "0") == "1"      # default of set_backward_recompute
 
     def set_backward_recompute(self, enabled: bool = True) -> None:
         """Training without the membrane-potential tensor.  The reference's forward writes ``v_mem`` for every
@@ -174,7 +175,7 @@ class LIF(LIFBase):
         hence the same gradients -- at 20.5 instead of 24 bytes per neuron and step and without 7/8 of ``v_mem``'s
         memory.  Applies to spiking layers without a synaptic stage (or in front of it: the membrane stage of the
         two-kernel route), built-in surrogate gradients, shapes the TMA-staged kernels take; anything else runs as
-        before."""
+        before.  ``EXODUS_B200_BACKWARD_RECOMPUTE=1`` in the environment turns it on for every layer."""
         self.__dict__["_recompute"] = bool(enabled)
 
     def _set_state(self, name: str, value: torch.Tensor) -> None:
