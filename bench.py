@@ -593,12 +593,22 @@ def measure_other(name: str, timer: KernelTimer, dev, rank: int, world: int, ste
             return e0.elapsed_time(e1) / reps
         from sinabs_exodus_b200 import distributed as exd
         res["collective"]["nccl_alone_avg_ms"] = alone(lambda: exd.allreduce_gradients(w.tc_params))
+        one, why = None, ""
         try:
             one = exd.OneShotAllReduce(int(sum(p.numel() for p in w.tc_params)), dev)
-            res["collective"]["one_shot_alone_avg_ms"] = alone(lambda: one.allreduce_gradients(w.tc_params))
-            ex._lib.device_status(dev)
         except Exception as exc:
-            res["collective"]["one_shot_unavailable"] = f"{type(exc).__name__}: {str(exc)[:160]}"
+            why = f"{type(exc).__name__}: {str(exc)[:160]}"
+        import torch.distributed as dist
+        agreed = torch.tensor([1 if one is not None else 0], device=dev)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)        # every rank times it, or none does (the calls are collective)
+        if int(agreed.item()) == 1:
+            try:
+                res["collective"]["one_shot_alone_avg_ms"] = alone(lambda: one.allreduce_gradients(w.tc_params))
+                ex._lib.device_status(dev)
+            except Exception as exc:
+                res["collective"]["one_shot_unavailable"] = f"{type(exc).__name__}: {str(exc)[:160]}"
+        else:
+            res["collective"]["one_shot_unavailable"] = why or "not available on another rank"
     if name == "c1":
         # backward in the calling thread: no hand-over to PyTorch's autograd thread
         prev = torch.autograd.is_multithreading_enabled()
