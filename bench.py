@@ -875,6 +875,30 @@ def run_ours(args, wl):
             w.layer.set_backward_recompute(False)
             timer.reset()
 
+    # ---- forward passes that nobody differentiates (torch.no_grad, no recording): spikes only, as float and as bytes
+    inference = None
+    if (not args.lean and not args.cuda_graph and args.layout == "btm" and wl["kind"] in ("lif", "iaf", "lif5")):
+        xin = w.x.detach()
+
+        def infer():
+            w.layer.reset_states()
+            w.layer(xin)
+        inference = {"what": "layer forward under torch.no_grad() without record_states: no v_mem tensor is written"}
+        isteps = max(3, min(args.steps, 10))
+        with torch.no_grad():
+            for key, dtype, bytes_nts in (("float32_spikes", torch.float32, 8), ("uint8_spikes", torch.uint8, 5)):
+                w.layer.set_spike_output(dtype, saturate=True)
+                try:
+                    for _ in range(3):
+                        infer()
+                    ims = timed_steps(infer, isteps, world, dev)
+                    inference[key] = {"ms_per_forward": ims / isteps, "value": w.nts * world * isteps / (ims * 1e-3),
+                                      "unit": "nts/s (forward only)", "bytes_per_neuron_step": bytes_nts,
+                                      "gbs": bytes_nts * w.nts / (ims / isteps * 1e-3) / 1e9}
+                finally:
+                    w.layer.set_spike_output(torch.float32)
+        torch.cuda.empty_cache()
+
     # ---- end to end with host buffers (public layer API; copies inside the timed region)
     e2e = None
     if not args.no_e2e:
@@ -934,7 +958,7 @@ def run_ours(args, wl):
                     "cuda_graph": bool(args.cuda_graph),
                     "autograd": "single-threaded" if args.single_thread_autograd else "default (backward on PyTorch's autograd thread)"},
             "step_fraction_of_hbm_roofline": (step_bytes / (ms_total / args.steps * 1e-3) / 1e9) / peak,
-            "roofline": roof, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "recompute": recompute,
+            "roofline": roof, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "recompute": recompute, "inference": inference,
             "cpu_baseline": cpu, "other_configs": others, "reference_cuda": ref_cuda, "stream_mix_ceilings": mix,
         }
         print(json.dumps(line), flush=True)
