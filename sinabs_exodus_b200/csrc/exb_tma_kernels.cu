@@ -294,10 +294,17 @@ static cudaError_t run_lif_fwd(const LifFwdArgs &a, cudaStream_t s, bool *used)
     using G = TileGeom<NW, V>;
     const int64_t ctas = a.B * ((a.M + G::W - 1) / G::W);
     PipeCfg pc = pipe_cfg(G::W, 1, ctas);
-    long_stages_for_wide_forward(pc, V, ctas, a.T);
-    // Checkpoints instead of v_mem: about as many bytes out as in, and two CTAs per SM measured best
-    // (8 x 500 x 262144: 1.372 ms with 16 x 3, 1.374 with 16 x 2, 1.387 with 8 x 4, 1.498 with 32 x 2, 1.567 with 16 x 4).
-    if ((a.ckpt || (!a.v_mem && !a.spikes_u8)) && pc.tc == 32 && pc.stages == 2) { pc.tc = 16; pc.stages = 3; }
+    // The pipeline shape follows what the variant writes per float it reads (wide tiles on many waves; measured on
+    // 8 x 500 x 262144).  Two or three float tensors (spikes + v_mem [+ record]): long stages, one CTA per SM, see
+    // long_stages_for_wide_forward.  About one float tensor (spikes alone; spikes + checkpoints; bytes + v_mem):
+    // two CTAs per SM -- checkpoint variant 1.372 ms with 16 x 3, 1.374 with 16 x 2, 1.387 with 8 x 4, 1.498 with
+    // 32 x 2, 1.567 with 16 x 4.  The byte raster alone (a quarter of a tensor out) is a read stream and keeps the
+    // short default stages with many CTAs: 0.812 ms with 4 x 4, 0.832 with 16 x 2, 1.063 with 16 x 3, 1.806 with 32 x 2.
+    const int float_tensors_out = a.spikes_u8 ? (a.v_mem ? 1 : 0) : (1 + (a.v_mem ? 1 : 0) + (a.v_post ? 1 : 0));
+    if (float_tensors_out >= 1) {
+        long_stages_for_wide_forward(pc, V, ctas, a.T);
+        if (float_tensors_out == 1 && pc.tc == 32 && pc.stages == 2) { pc.tc = 16; pc.stages = 3; }
+    }
     static const int env_tc = env_int("EXB_LIF_FWD_TC", 0), env_st = env_int("EXB_LIF_FWD_STAGES", 0);
     if (env_tc > 0 && env_tc <= 256) pc.tc = env_tc;
     if (env_st > 1 && env_st <= MAX_STAGES) pc.stages = env_st;
