@@ -175,7 +175,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append(line.strip())
+            self.rows.append((time.monotonic(), line.strip()))
 
     def stop(self):
         if self.proc is None:
@@ -185,9 +185,15 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
+        return self.window(None, None)
+
+    def window(self, t0, t1):
+        """Statistics of the samples read between the host times t0 and t1 (time.monotonic; None = no bound)."""
         sm, smax, power, reasons = [], [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for row in self.rows:
+        for stamp, row in list(self.rows):
+            if (t0 is not None and stamp < t0) or (t1 is not None and stamp > t1):
+                continue
             parts = [p.strip() for p in row.split(",")]
             if len(parts) < 8 or (self.uuid and parts[0] != self.uuid):
                 continue
@@ -804,6 +810,9 @@ def run_ours(args, wl):
     if args.recompute:
         w.layer.set_backward_recompute(True)
     timer = KernelTimer()
+    sampler = ClockSampler(local) if rank == 0 else None      # started early: nvidia-smi takes a moment to deliver
+    if sampler:
+        sampler.start()
     for _ in range(args.warmup):
         w.step(world)
     torch.cuda.synchronize()
@@ -825,11 +834,9 @@ def run_ours(args, wl):
         for _ in range(3):
             run_step()
         torch.cuda.synchronize()
-    sampler = ClockSampler(local) if rank == 0 else None
-    if sampler:
-        sampler.start()
 
     # ---- timed region: K steps, device-timed, barrier + synchronize on both sides
+    t_region0 = time.monotonic()
     if w.nts >= (1 << 28):
         timer.enabled = True
         ms_total = timed_steps(run_step, args.steps, world, dev)
@@ -845,6 +852,7 @@ def run_ours(args, wl):
         timer.enabled = False
         launches = timer.launches()
     kernels = timer.summary()
+    t_region1 = time.monotonic()
     if args.cuda_graph:
         launches = launches_per_step * args.steps      # replays do not pass through the wrappers
     value = w.nts * world * args.steps / (ms_total * 1e-3)
@@ -903,8 +911,20 @@ def run_ours(args, wl):
     e2e = None
     if not args.no_e2e:
         timer.reset()
+        t_e2e0 = time.monotonic()
         e2e = run_e2e(w, world, args, timer)
-    clocks = sampler.stop() if sampler else None
+        if sampler:
+            e2e["clocks"] = sampler.window(t_e2e0, time.monotonic())
+    # Clocks: the samples that fell into the timed region; a region too short for the 100 ms sampling period to
+    # give at least three (the default run of the largest configuration lasts 0.3 s) takes the whole run instead
+    # -- warm-up, timed region and the extra measurements, all of them kernels of this library under load.
+    clocks = None
+    if sampler:
+        whole = sampler.stop()
+        clocks = sampler.window(t_region0, t_region1)
+        clocks["window"] = "timed region"
+        if (clocks.get("samples") or 0) < 3:
+            clocks = dict(whole, window="whole run (the timed region held fewer than 3 samples)")
 
     roof = roofline_of(name, wl["kind"], kernels, w.nts, peak, peak_src) if rank == 0 else None
     step_bytes = (wl["bytes_fwd"] + wl["bytes_bwd"]) * w.nts
