@@ -26,7 +26,7 @@ from . import layers  # noqa: E402
 from . import conversion  # noqa: E402
 from . import graphs  # noqa: E402
 from .graphs import GraphedStep  # noqa: E402
-from ._lib import device_status, set_status_checks  # noqa: E402
+from ._lib import device_status, set_nvtx_ranges, set_status_checks  # noqa: E402
 from .leaky import LeakyIntegrator, LeakyIntegratorTM  # noqa: E402
 from .spike import IntegrateAndFire, IntegrateAndFireTM, LIFSynapticTM  # noqa: E402
 

@@ -525,3 +525,39 @@ def lif_syn_backward(grad_input, grad_alpha_mem, grad_scale_mem, grad_alpha_syn,
         B, T, M, dev.index, _stream(dev))
     _check(st, "exb_lif_syn_backward")
     _after_launch(dev)
+
+
+# Tracing aid: NVTX ranges around the calls that launch kernels, named after the entry point, so that a timeline
+# shows which layer call a kernel belongs to.  Off unless asked for (a range costs a few microseconds per call).
+_LAUNCHERS = ("lif_forward", "lif_forward_u8", "lif_forward_ckpt", "lif_backward", "lif_backward_ckpt", "leaky_forward",
+              "leaky_backward", "leaky_forward_scan", "leaky_backward_scan", "leaky_forward_scan_static",
+              "lif_syn_forward", "lif_syn_forward_u8", "lif_syn_backward", "acc_finish", "allreduce_oneshot")
+_nvtx_on = False
+
+
+def set_nvtx_ranges(enabled: bool = True) -> None:
+    """Wrap every launching call of this module in an NVTX range ``exb.<name>`` (``EXODUS_B200_NVTX=1`` in the
+    environment does the same at import)."""
+    global _nvtx_on
+    if bool(enabled) == _nvtx_on:
+        return
+    module = globals()
+    for name in _LAUNCHERS:
+        fn = module[name]
+        if enabled:
+            def ranged(*args, __fn=fn, __label="exb." + name, **kwargs):
+                torch.cuda.nvtx.range_push(__label)
+                try:
+                    return __fn(*args, **kwargs)
+                finally:
+                    torch.cuda.nvtx.range_pop()
+            ranged.__wrapped__ = fn
+            ranged.__doc__ = fn.__doc__
+            module[name] = ranged
+        else:
+            module[name] = getattr(fn, "__wrapped__", fn)
+    _nvtx_on = bool(enabled)
+
+
+if os.environ.get("EXODUS_B200_NVTX", "0") == "1":
+    set_nvtx_ranges(True)

@@ -278,3 +278,23 @@ def test_backward_recompute_in_a_captured_step():
         torch.testing.assert_close(out, out_w, rtol=0, atol=0)
         torch.testing.assert_close(step.input_grad, gx_w, rtol=0, atol=0)
         torch.testing.assert_close(layer.tau_mem.grad, gt_w, rtol=1e-6, atol=0)
+
+
+def test_layer_step_with_nvtx_ranges_on():
+    """The tracing aid changes nothing but the timeline."""
+    import torch
+    import sinabs_exodus_b200 as ex
+    dev = "cuda:0"
+    x = torch.rand(2, 30, 16, device=dev) * 2
+    ref = ex.layers.LIF(tau_mem=10.0, norm_input=False).to(dev)
+    want = ref(x)
+    ex.set_nvtx_ranges(True)
+    try:
+        layer = ex.layers.LIF(tau_mem=10.0, norm_input=False).to(dev)
+        xin = x.clone().requires_grad_(True)
+        out = layer(xin)
+        out.sum().backward()
+    finally:
+        ex.set_nvtx_ranges(False)
+    torch.testing.assert_close(out.detach(), want.detach(), rtol=0, atol=0)
+    assert xin.grad is not None and layer.tau_mem.grad is not None

@@ -197,3 +197,17 @@ def test_value_checks_are_remembered_per_tensor():
             _check_values(torch.full((6,), 1.5), th, None)
     with pytest.raises(ValueError):
         _check_values(torch.rand(6), th, torch.full((6,), 2.0))
+
+
+def test_nvtx_ranges_wrap_and_unwrap_the_launching_calls():
+    from sinabs_exodus_b200 import _lib
+    plain = _lib.lif_forward
+    _lib.set_nvtx_ranges(True)
+    try:
+        assert _lib.lif_forward is not plain and _lib.lif_forward.__wrapped__ is plain
+        assert _lib.acc_finish.__wrapped__.__name__ == "acc_finish"
+        _lib.set_nvtx_ranges(True)                        # idempotent
+        assert _lib.lif_forward.__wrapped__ is plain
+    finally:
+        _lib.set_nvtx_ranges(False)
+    assert _lib.lif_forward is plain
