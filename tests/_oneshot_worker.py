@@ -43,6 +43,18 @@ def main() -> int:
     allreduce_gradients(pb)
     for a, b in zip(pa, pb):
         torch.testing.assert_close(a.grad, b.grad, rtol=1e-6, atol=1e-6)
+    # the NCCL route's branches: one parameter reduced in place (with averaging), several as one coalesced group
+    # (above), and the flat route when a rank has no gradient for a parameter
+    p1 = torch.nn.Parameter(torch.zeros(3, device=dev))
+    p1.grad = torch.full((3,), float(rank + 1), device=dev)
+    assert allreduce_gradients([p1], average=True) == 3
+    torch.testing.assert_close(p1.grad, torch.full((3,), (world + 1) / 2.0, device=dev))
+    p2 = [torch.nn.Parameter(torch.zeros(4, device=dev)), torch.nn.Parameter(torch.zeros(2, device=dev))]
+    p2[0].grad = torch.ones(4, device=dev)
+    p2[1].grad = None if rank == 0 else torch.ones(2, device=dev)
+    assert allreduce_gradients(p2) == 6
+    torch.testing.assert_close(p2[0].grad, torch.full((4,), float(world), device=dev))
+    torch.testing.assert_close(p2[1].grad, torch.full((2,), float(world - 1), device=dev))
     ex.device_status()
     torch.cuda.synchronize()
     dist.barrier()
