@@ -56,24 +56,6 @@ def allreduce_gradients(params: Iterable[torch.nn.Parameter], group=None, averag
     if not params or not dist.is_initialized() or dist.get_world_size(group) == 1:
         return 0
     dev = params[0].device
-    # NCCL, every gradient present, float32 and contiguous: reduce the gradient tensors where they are -- one
-    # collective for a single parameter, one coalesced NCCL group for several -- instead of flatten / reduce / scatter
-    # (three or more small launches less on a step that is bound by its launch path).
-    grads = [p.grad for p in params]
-    in_place = (dev.type == "cuda" and dist.get_backend(group) == "nccl"
-                and all(g is not None and g.dtype == torch.float32 and g.is_contiguous() and g.device == dev for g in grads)
-                and (len(grads) == 1 or hasattr(dist, "_coalescing_manager")))
-    if in_place:
-        if len(grads) == 1:
-            dist.all_reduce(grads[0], op=dist.ReduceOp.SUM, group=group)
-        else:
-            with dist._coalescing_manager(group=group, device=dev, async_ops=False):
-                for g in grads:
-                    dist.all_reduce(g, op=dist.ReduceOp.SUM, group=group)
-        if average:
-            for g in grads:
-                g /= dist.get_world_size(group)
-        return int(sum(g.numel() for g in grads))
     flat = torch.cat([(p.grad if p.grad is not None else torch.zeros_like(p)).reshape(-1).to(torch.float32)
                       for p in params]).to(dev)
     dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)

@@ -43,8 +43,8 @@ def main() -> int:
     allreduce_gradients(pb)
     for a, b in zip(pa, pb):
         torch.testing.assert_close(a.grad, b.grad, rtol=1e-6, atol=1e-6)
-    # the NCCL route's branches: one parameter reduced in place (with averaging), several as one coalesced group
-    # (above), and the flat route when a rank has no gradient for a parameter
+    # the NCCL route with averaging, and with a rank that has no gradient for a parameter (it contributes zeros, so
+    # that every rank issues the same collective)
     p1 = torch.nn.Parameter(torch.zeros(3, device=dev))
     p1.grad = torch.full((3,), float(rank + 1), device=dev)
     assert allreduce_gradients([p1], average=True) == 3
