@@ -808,7 +808,7 @@ def run_ours(args, wl):
     if args.layout == "nt":
         args.no_e2e = True
     if args.recompute:
-        w.layer.set_backward_recompute(True)
+        w.layer.set_backward_recompute(True, always=True)
     timer = KernelTimer()
     sampler = ClockSampler(local) if rank == 0 else None      # started early: nvidia-smi takes a moment to deliver
     if sampler:
@@ -860,8 +860,8 @@ def run_ours(args, wl):
     # ---- the same step without the v_mem tensor (layer.set_backward_recompute): extra key, not the headline
     recompute = None
     if (not args.lean and not args.cuda_graph and args.layout == "btm" and wl["kind"] in ("lif", "iaf", "lif5")
-            and hasattr(w.layer, "set_backward_recompute")):
-        w.layer.set_backward_recompute(True)
+            and hasattr(w.layer, "set_backward_recompute") and w.nts >= (1 << 28)):
+        w.layer.set_backward_recompute(True, always=True)
         try:
             for _ in range(3):
                 w.step(world)

@@ -119,6 +119,9 @@ class _DecayFromTau(torch.autograd.Function):
         return g * alpha * r * r, None      # d/dtau exp(-1/tau) = exp(-1/tau) / tau^2
 
 
+_SM_COUNT: dict = {}      # device -> number of SMs
+
+
 class LIF(LIFBase):
     """Leaky integrate-and-fire layer, forward and exact backward on the GPU.
 
@@ -164,19 +167,37 @@ class LIF(LIFBase):
         )
         self.decay_early = decay_early
 
-    _recompute = os.environ.get("EXODUS_B200_BACKWARD_RECOMPUTE", "0") == "1"      # default of set_backward_recompute
+    # 0: off; 1: where it pays; 2: wherever the kernels take the shape.  Default from the environment.
+    _recompute = {"1": 1, "always": 2}.get(os.environ.get("EXODUS_B200_BACKWARD_RECOMPUTE", "0"), 0)
 
-    def set_backward_recompute(self, enabled: bool = True) -> None:
+    def set_backward_recompute(self, enabled: bool = True, always: bool = False) -> None:
         """Training without the membrane-potential tensor.  The reference's forward writes ``v_mem`` for every
         neuron and step and its backward reads it back (``sinabs/exodus/spike.py:200,246``); a layer that does not
         record states needs it for nothing else.  With this switch on, the forward kernel writes the spikes and one
         checkpoint of the state per 8 steps, and the backward kernel rebuilds ``v_mem`` chunk by chunk from the
         layer's input and the checkpoints with the forward kernel's own arithmetic -- bit for bit the same tensor,
-        hence the same gradients -- at 20.5 instead of 24 bytes per neuron and step and without 7/8 of ``v_mem``'s
+        hence the same gradients -- at 21 instead of 24 bytes per neuron and step and without 7/8 of ``v_mem``'s
         memory.  Applies to spiking layers without a synaptic stage (or in front of it: the membrane stage of the
         two-kernel route), built-in surrogate gradients, shapes the TMA-staged kernels take; anything else runs as
-        before.  ``EXODUS_B200_BACKWARD_RECOMPUTE=1`` in the environment turns it on for every layer."""
-        self.__dict__["_recompute"] = bool(enabled)
+        before.
+
+        The rebuild costs instructions, which only a problem that keeps the memory system busy can hide: measured
+        +7 to +12 % on 32 x 500 x 262144 and +8 % on 32 x 300 x 36992, nothing on 64 x 500 x 4096, and -14 to -26 % on
+        32 x 300 x 2048 and 16 x 1000 x 1024.  So by default it is used only when the batch gives at least eight
+        512-neuron tiles per SM; ``always=True`` uses it for every shape the kernels take (for its memory saving).
+        ``EXODUS_B200_BACKWARD_RECOMPUTE=1`` (or ``always``) in the environment turns it on for every layer."""
+        self.__dict__["_recompute"] = (2 if always else 1) if enabled else 0
+
+    def _recompute_here(self, x: torch.Tensor) -> bool:
+        """Whether this (B, T, M) input takes the route without v_mem (see set_backward_recompute)."""
+        if self._recompute == 2:
+            return True
+        if self._recompute == 0:
+            return False
+        sms = _SM_COUNT.get(x.device)
+        if sms is None:
+            sms = _SM_COUNT[x.device] = torch.cuda.get_device_properties(x.device).multi_processor_count
+        return x.shape[0] * ((x.shape[2] + 511) // 512) >= 8 * sms
 
     def _set_state(self, name: str, value: torch.Tensor) -> None:
         # what ``self.<name> = value`` does for a registered buffer, without nn.Module.__setattr__'s searches
@@ -340,7 +361,7 @@ class LIF(LIFBase):
         # v_mem is an intermediate unless it is recorded: with set_backward_recompute the kernels keep checkpoints
         # instead (a derived scale's gradient is then rebuilt from the state, which needs the scale away from zero)
         recompute = (self._recompute and not self.record_states and torch.is_grad_enabled()
-                     and (not sflags or scale_from_state))
+                     and (not sflags or scale_from_state) and self._recompute_here(i_syn))
         spikes, v_pre, v_post_last = IntegrateAndFireTM.apply(
             i_syn, raw, self._state_flat(self.v_mem), threshold, subtract, min_v_mem, None,
             self.surrogate_grad_fn, self.max_num_spikes_per_bin, reset_mode, count,

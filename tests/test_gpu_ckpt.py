@@ -122,7 +122,7 @@ def test_checkpointed_pair_refuses_what_it_cannot_do():
 @pytest.mark.parametrize("norm_input", [True, False])
 @pytest.mark.parametrize("shape", [(8, 100, 128), (3, 37, 4, 6, 6), (300, 12, 516)])
 def test_layer_with_backward_recompute_equals_the_layer_without(shape, norm_input):
-    """``layer.set_backward_recompute(True)``: same spikes, same state, bit-identical input gradient; the tau gradient
+    """``layer.set_backward_recompute(True, always=True)``: same spikes, same state, bit-identical input gradient; the tau gradient
     comes out of the same per-neuron values through an atomic reduction, so it is compared to 1e-6."""
     import torch
     import sinabs_exodus_b200 as ex
@@ -135,7 +135,7 @@ def test_layer_with_backward_recompute_equals_the_layer_without(shape, norm_inpu
     results = []
     for recompute in (False, True):
         layer = ex.layers.LIF(tau_mem=20.0, min_v_mem=-1.0, norm_input=norm_input).to(dev)
-        layer.set_backward_recompute(recompute)
+        layer.set_backward_recompute(recompute, always=True)
         xin = x.clone().requires_grad_(True)
         before = torch.cuda.memory_allocated()
         out = layer(xin)
@@ -163,7 +163,7 @@ def test_layer_with_backward_recompute_falls_back():
     for kw in (dict(record_states=True), dict(surrogate_grad_fn=lambda v, th: torch.exp(-(v - th).abs())), dict()):
         layer = ex.layers.LIF(tau_mem=10.0, norm_input=False, **kw).to(dev)
         ref = ex.layers.LIF(tau_mem=10.0, norm_input=False, **kw).to(dev)
-        layer.set_backward_recompute(True)
+        layer.set_backward_recompute(True, always=True)
         xa = x.clone().requires_grad_(True); xb = x.clone().requires_grad_(True)
         layer(xa).sum().backward(); ref(xb).sum().backward()
         torch.testing.assert_close(xa.grad, xb.grad, rtol=0, atol=0)
@@ -258,7 +258,7 @@ def test_backward_recompute_in_a_captured_step():
     import sinabs_exodus_b200 as ex
     dev = "cuda:0"
     layer = ex.layers.LIF(tau_mem=15.0, norm_input=False).to(dev)
-    layer.set_backward_recompute(True)
+    layer.set_backward_recompute(True, always=True)
     g = torch.Generator(device=dev).manual_seed(8)
     xs = [torch.randn(4, 40, 64, device=dev, generator=g) + 0.4 for _ in range(3)]
     gos = [torch.randn(4, 40, 64, device=dev, generator=g) for _ in range(3)]
@@ -298,3 +298,23 @@ def test_layer_step_with_nvtx_ranges_on():
         ex.set_nvtx_ranges(False)
     torch.testing.assert_close(out.detach(), want.detach(), rtol=0, atol=0)
     assert xin.grad is not None and layer.tau_mem.grad is not None
+
+
+def test_backward_recompute_is_used_only_where_it_pays_by_default():
+    """Without ``always`` the switch leaves small problems on the ordinary pair (the rebuild costs more than the
+    traffic it saves there): the v_mem tensor is still held after the forward; with ``always`` it is not."""
+    import torch
+    import sinabs_exodus_b200 as ex
+    dev = "cuda:0"
+    x = torch.rand(8, 100, 4096, device=dev) * 0.4       # 64 tiles of 512 neurons: far below eight per SM
+    held = {}
+    for key, kw in (("default", dict()), ("always", dict(always=True))):
+        layer = ex.layers.LIF(tau_mem=20.0, norm_input=False).to(dev)
+        layer.set_backward_recompute(True, **kw)
+        xin = x.clone().requires_grad_(True)
+        torch.cuda.synchronize(); before = torch.cuda.memory_allocated()
+        out = layer(xin)
+        held[key] = torch.cuda.memory_allocated() - before
+        out.sum().backward()
+    assert held["default"] > 1.9 * x.numel() * 4          # spikes + v_mem
+    assert held["always"] < 1.3 * x.numel() * 4           # spikes + checkpoints
