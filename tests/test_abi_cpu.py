@@ -84,3 +84,28 @@ def test_static_scratch_size_has_one_source(lib):
     assert m and _lib.STATIC_SCRATCH_BYTES == lib.exb_static_scratch_bytes() == int(m.group(1)) << int(m.group(2)) == 1 << 20
     src = open(os.path.join(ROOT, "sinabs_exodus_b200", "csrc", "exb_tma_kernels.cu")).read()
     assert "g_static_scratch[EXB_STATIC_SCRATCH_BYTES]" in src and "1u << 20" not in src
+
+
+def test_checkpoint_pair_validates_before_any_cuda_call(lib):
+    """exb_lif_forward_ckpt / exb_lif_backward_ckpt and the spikes-only form of exb_lif_forward: bad arguments come
+    back as EXB_ERR_ARG / EXB_ERR_UNSUPPORTED without a device being touched."""
+    null = None
+    p = ctypes.c_void_p(64)        # never dereferenced
+    pairs = (null, 0, p, 0, null, 0, p, 0, null, 0)          # in_scale, alpha, subtract, theta, theta_low
+    geom = (1, 8, 4, 0, null)                                 # B, T, M, device, stream
+    # forward: ckpt is required
+    st = lib.exb_lif_forward_ckpt(p, null, p, null, *pairs, 1, 0, null, null, *geom)
+    assert st == 1 and b"ckpt" in lib.exb_last_error()
+    # backward: the generic surrogate cannot be served, and input + ckpt are required
+    st = lib.exb_lif_backward_ckpt(p, null, null, null, p, null, p, p, null, *pairs, 1, 0, 0, 0.0, 0.0, null, *geom)
+    assert st == 1 and b"built-in surrogates" in lib.exb_last_error()
+    st = lib.exb_lif_backward_ckpt(p, null, null, null, p, null, null, p, null, *pairs, 1, 0, 1, 0.5, 1.0, null, *geom)
+    assert st == 1 and b"required" in lib.exb_last_error()
+    # reset to a value needs the value
+    st = lib.exb_lif_forward_ckpt(p, p, p, null, *pairs, 1, 1, null, null, *geom)
+    assert st == 1 and b"reset-to-value" in lib.exb_last_error()
+    # spikes-only forward: only in the time-major layout (layout 0 is [N,T])
+    st = lib.exb_lif_forward(p, null, p, null, *pairs, 1, 0, null, null, 1, 8, 4, 0, 0, null)
+    assert st == 4 and b"v_mem may be omitted" in lib.exb_last_error()
+    # empty problems are a successful no-op
+    assert lib.exb_lif_forward_ckpt(p, p, p, null, *pairs, 1, 0, null, null, 0, 8, 4, 0, null) == 0
